@@ -1,0 +1,514 @@
+// Host side of layer 1 of the C ABI: shape checks, tensor-map construction, tile choice, launches.
+#include "../../include/alpha_conv_b200.h"
+#include "conv_kernels.cuh"
+#include "host_common.h"
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+
+namespace alpha {
+
+// ---- thread-local error text, process-wide settings ---------------------------------------------
+
+static thread_local char g_err[512] = "";
+static thread_local const char* g_last_algo = "";
+static std::atomic<unsigned long long> g_launches{0};
+
+int fail(int code, const char* fmt, ...)
+{
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+void note_launch(const char* algo)
+{
+    g_last_algo = algo;
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+}
+
+static int env_math()
+{
+    const char* e = getenv("ALPHA_CONV_MATH");
+    if (e && (!strcmp(e, "tf32") || !strcmp(e, "TF32"))) return ALPHA_MATH_TF32;
+    return ALPHA_MATH_3XTF32;
+}
+static int env_algo()
+{
+    const char* e = getenv("ALPHA_CONV_ALGO");
+    if (!e) return ALPHA_ALGO_AUTO;
+    if (!strcmp(e, "tensor") || !strcmp(e, "igemm")) return ALPHA_ALGO_TENSOR;
+    if (!strcmp(e, "simt")) return ALPHA_ALGO_SIMT;
+    if (!strcmp(e, "winograd")) return ALPHA_ALGO_WINOGRAD;
+    return ALPHA_ALGO_AUTO;
+}
+static std::atomic<int> g_math{env_math()};
+static std::atomic<int> g_algo{env_algo()};
+
+// ---- per-device context ----------------------------------------------------------------------
+
+struct DeviceCtx {
+    bool init = false;
+    int sm_count = 0;
+    int cc_major = 0;
+    int* status = nullptr;       // device status word
+    float* workspace = nullptr;  // split-K partials
+    size_t workspace_bytes = 0;
+};
+static DeviceCtx g_ctx[64];
+static std::mutex g_mu;
+
+static PFN_encodeTiled g_encodeTiled = nullptr;
+static PFN_encodeIm2col g_encodeIm2col = nullptr;
+
+static int load_driver_entry_points()
+{
+    if (g_encodeTiled && g_encodeIm2col) return ALPHA_OK;
+    cudaDriverEntryPointQueryResult q;
+    void* f = nullptr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess || !f)
+        return fail(ALPHA_E_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    g_encodeTiled = reinterpret_cast<PFN_encodeTiled>(f);
+    f = nullptr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeIm2col", &f, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess || !f)
+        return fail(ALPHA_E_CUDA, "cuTensorMapEncodeIm2col is not available from this driver");
+    g_encodeIm2col = reinterpret_cast<PFN_encodeIm2col>(f);
+    return ALPHA_OK;
+}
+
+int get_ctx(DeviceCtx** out)
+{
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail(ALPHA_E_CUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
+    if (dev < 0 || dev >= 64) return fail(ALPHA_E_DEVICE, "device index %d out of range", dev);
+    std::lock_guard<std::mutex> lock(g_mu);
+    DeviceCtx& c = g_ctx[dev];
+    if (!c.init) {
+        cudaDeviceProp prop;
+        e = cudaGetDeviceProperties(&prop, dev);
+        if (e != cudaSuccess) return fail(ALPHA_E_CUDA, "cudaGetDeviceProperties: %s", cudaGetErrorString(e));
+        if (prop.major != 10)
+            return fail(ALPHA_E_DEVICE, "device %d is sm_%d%d; this library is built for sm_100a only",
+                        dev, prop.major, prop.minor);
+        int rc = load_driver_entry_points();
+        if (rc) return rc;
+        e = cudaMalloc(&c.status, sizeof(int));
+        if (e != cudaSuccess) return fail(ALPHA_E_CUDA, "cudaMalloc(status): %s", cudaGetErrorString(e));
+        cudaMemset(c.status, 0, sizeof(int));
+        c.sm_count = prop.multiProcessorCount;
+        c.cc_major = prop.major;
+        const int max_smem = 227 * 1024;
+        cudaFuncSetAttribute(conv_igemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+        cudaFuncSetAttribute(conv_dw_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+        c.init = true;
+    }
+    *out = &c;
+    return ALPHA_OK;
+}
+
+// Grows the per-device split-K workspace.  Work already enqueued may still read the old block,
+// so the old block is released only after the device has drained.
+static int ensure_workspace(DeviceCtx* c, size_t bytes)
+{
+    std::lock_guard<std::mutex> lock(g_mu);
+    if (c->workspace_bytes >= bytes) return ALPHA_OK;
+    if (c->workspace) {
+        cudaDeviceSynchronize();
+        cudaFree(c->workspace);
+        c->workspace = nullptr;
+        c->workspace_bytes = 0;
+    }
+    size_t want = bytes + (bytes >> 2);
+    cudaError_t e = cudaMalloc(&c->workspace, want);
+    if (e != cudaSuccess) return fail(ALPHA_E_CUDA, "cudaMalloc(workspace %zu B): %s", want, cudaGetErrorString(e));
+    c->workspace_bytes = want;
+    return ALPHA_OK;
+}
+
+// ---- tensor maps -----------------------------------------------------------------------------
+
+static CUtensorMapSwizzle swizzle_for_row_bytes(int row_bytes)
+{
+    return row_bytes >= 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+           : row_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
+                             : CU_TENSOR_MAP_SWIZZLE_32B;
+}
+static uint32_t desc_layout_for_row_bytes(int row_bytes)
+{
+    return row_bytes >= 128 ? kSwizzle128B : row_bytes == 64 ? kSwizzle64B : kSwizzle32B;
+}
+
+// NHWC activation tensor [N,H,W,C] as an im2col-mode map over (C, W, H, N).
+// Base pixels run over w in [-pad_w, W + pad_w - (FW-1)) with step sw, likewise for h.
+static int make_im2col_map(CUtensorMap* m, const float* base, int N, int H, int W, int C, int FH,
+                           int FW, int sh, int sw, int pad_h, int pad_w, int channels, int pixels)
+{
+    cuuint64_t dims[4] = {(cuuint64_t)C, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)N};
+    cuuint64_t strides[3] = {(cuuint64_t)C * 4, (cuuint64_t)W * C * 4, (cuuint64_t)H * W * C * 4};
+    int lower[2] = {-pad_w, -pad_h};
+    int upper[2] = {pad_w - (FW - 1), pad_h - (FH - 1)};
+    cuuint32_t estr[4] = {1, (cuuint32_t)sw, (cuuint32_t)sh, 1};
+    CUresult r = g_encodeIm2col(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(base), dims,
+                                strides, lower, upper, (cuuint32_t)channels, (cuuint32_t)pixels, estr,
+                                CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_for_row_bytes(channels * 4),
+                                CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    // Drivers up to CUDA 13.1 set a descriptor bit for im2col maps that must be clear when the
+    // tensor is smaller than 128 KiB (the same correction CUTLASS applies after encoding).
+    int drv = 0;
+    if (r == CUDA_SUCCESS && cudaDriverGetVersion(&drv) == cudaSuccess && drv <= 13010 &&
+        (size_t)N * H * W * C * 4 < 131072)
+        reinterpret_cast<uint64_t*>(m)[1] &= ~(1ull << 21);
+    if (r != CUDA_SUCCESS)
+        return fail(ALPHA_E_CUDA,
+                    "cuTensorMapEncodeIm2col failed (%d): dims C=%d W=%d H=%d N=%d corners [%d,%d]/[%d,%d] "
+                    "channels=%d pixels=%d strides %d,%d",
+                    (int)r, C, W, H, N, lower[0], lower[1], upper[0], upper[1], channels, pixels, sw, sh);
+    return ALPHA_OK;
+}
+
+static int make_tiled_map(CUtensorMap* m, const float* base, int rank, const cuuint64_t* dims,
+                          const cuuint64_t* strides_bytes, const cuuint32_t* box, int inner_bytes)
+{
+    cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+    CUresult r = g_encodeTiled(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)rank,
+                               const_cast<float*>(base), dims, strides_bytes, box, estr,
+                               CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_for_row_bytes(inner_bytes),
+                               CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(ALPHA_E_CUDA, "cuTensorMapEncodeTiled failed (%d), rank %d box0 %u", (int)r, rank, box[0]);
+    return ALPHA_OK;
+}
+
+// ---- argument checks -------------------------------------------------------------------------
+
+static int check_shape(const AlphaConvShape* s, const void* a, const void* b, const void* c)
+{
+    if (!s || !a || !b || !c) return fail(ALPHA_E_ARG, "null shape or tensor pointer");
+    if (s->N <= 0 || s->IH <= 0 || s->IW <= 0 || s->IC <= 0 || s->OC <= 0 || s->FH <= 0 || s->FW <= 0 ||
+        s->OH <= 0 || s->OW <= 0 || s->sh <= 0 || s->sw <= 0 || s->ph < 0 || s->pw < 0)
+        return fail(ALPHA_E_ARG, "non-positive dimension in conv shape");
+    if ((s->IC & 3) || (s->OC & 3))
+        return fail(ALPHA_E_ARG, "IC=%d and OC=%d must be multiples of 4 (padded channel stride)", s->IC, s->OC);
+    if ((s->OH - 1) * s->sh - s->ph + s->FH > s->IH + s->ph || (s->OW - 1) * s->sw - s->pw + s->FW > s->IW + s->pw)
+        return fail(ALPHA_E_ARG, "OH/OW=%d/%d do not fit IH/IW=%d/%d with this filter, stride and padding",
+                    s->OH, s->OW, s->IH, s->IW);
+    if (((uintptr_t)a | (uintptr_t)b | (uintptr_t)c) & 15)
+        return fail(ALPHA_E_ARG, "tensor pointers must be 16-byte aligned");
+    const long long lim = 2147483647LL;
+    if ((long long)s->N * s->IH * s->IW * s->IC > lim || (long long)s->N * s->OH * s->OW * s->OC > lim ||
+        (long long)s->OC * s->FH * s->FW * s->IC > lim)
+        return fail(ALPHA_E_ARG, "tensor has more than 2^31-1 elements");
+    return ALPHA_OK;
+}
+
+static int pick_kc(int channels)
+{
+    return (channels % 32 == 0) ? 32 : (channels % 16 == 0) ? 16 : (channels % 8 == 0) ? 8 : 0;
+}
+
+static uint32_t pow2_cols(int n)
+{
+    uint32_t c = 32;
+    while ((int)c < n) c <<= 1;
+    return c;
+}
+
+static int check_launch(const char* what)
+{
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(ALPHA_E_CUDA, "%s launch failed: %s", what, cudaGetErrorString(e));
+    return ALPHA_OK;
+}
+
+static int simt_grid(size_t total, int sm_count)
+{
+    size_t blocks = (total + 255) / 256;
+    size_t cap = (size_t)sm_count * 32;
+    return (int)(blocks < cap ? (blocks ? blocks : 1) : cap);
+}
+
+static ConvShape to_dev_shape(const AlphaConvShape* s)
+{
+    ConvShape d{s->N, s->IH, s->IW, s->IC, s->OC, s->FH, s->FW, s->OH, s->OW, s->sh, s->sw, s->ph, s->pw};
+    return d;
+}
+
+// ---- implicit GEMM launch shared by forward and stride-1 deltaX -----------------------------------
+
+struct IgemmPlan {
+    // activation tensor seen by the im2col map
+    const float* act; int aN, aH, aW, aC;
+    int FH, FW, sh, sw, pad_h, pad_w;
+    // output
+    float* out; int oH, oW, ncols;
+    const float* W; int wOC, wIC;   // W[wOC][FH*FW][wIC]
+    const float* bias;
+    bool b_mn, flip;
+    int kdim;                        // reduction channels per tap
+};
+
+static int launch_igemm(DeviceCtx* c, const IgemmPlan& pl, int mode3x, cudaStream_t stream)
+{
+    const int KC = pick_kc(pl.kdim);
+    IgemmParams p{};
+    p.out = pl.out; p.bias = pl.bias; p.status = c->status;
+    p.M_total = pl.aN * pl.oH * pl.oW;
+    p.Ncols = pl.ncols; p.ldo = pl.ncols;
+    p.OHo = pl.oH; p.OWo = pl.oW;
+    p.sh = pl.sh; p.sw = pl.sw; p.ph = pl.pad_h; p.pw = pl.pad_w;
+    p.FH = pl.FH; p.FW = pl.FW;
+    p.KC = KC; p.kchunks = pl.kdim / KC;
+    p.mode3x = mode3x; p.b_mn = pl.b_mn; p.flip = pl.flip;
+    const int gran = pl.b_mn ? 32 : 16;
+    int BN = ((pl.ncols + gran - 1) / gran) * gran;
+    if (BN > 256) BN = (pl.ncols % 256 == 0 || pl.ncols > 512) ? 256 : 128;
+    p.BN = BN;
+    p.tmem_cols = pow2_cols(BN);
+    p.idesc = make_idesc_tf32(kBM, BN, false, pl.b_mn);
+    p.a_bytes = kBM * KC * 4;
+    p.b_tx = pl.b_mn ? (BN / 32) * KC * 128 : BN * KC * 4;
+    p.b_bytes = (p.b_tx + 1023) & ~1023u;
+    p.swz = desc_layout_for_row_bytes(KC * 4);
+    const uint32_t stage = (p.a_bytes + p.b_bytes) * (mode3x ? 2 : 1);
+    int stages = (int)((100u * 1024) / stage);      // aim at two resident CTAs per SM
+    if (stages < 3) stages = (int)((200u * 1024) / stage);
+    if (stages > 6) stages = 6;
+    const int num_it = pl.FH * pl.FW * p.kchunks;
+    if (stages > num_it) stages = num_it;
+    if (stages < 1) return fail(ALPHA_E_ARG, "tile of %u bytes per stage does not fit shared memory", stage);
+    p.stages = stages;
+    const size_t smem = (size_t)stages * stage + (3 * stages + 2) * 8 + 1024;
+
+    CUtensorMap tmA, tmB;
+    int rc = make_im2col_map(&tmA, pl.act, pl.aN, pl.aH, pl.aW, pl.aC, pl.FH, pl.FW, pl.sh, pl.sw,
+                             pl.pad_h, pl.pad_w, KC, kBM);
+    if (rc) return rc;
+    cuuint64_t wd[3] = {(cuuint64_t)pl.wIC, (cuuint64_t)pl.FH * pl.FW, (cuuint64_t)pl.wOC};
+    cuuint64_t ws[2] = {(cuuint64_t)pl.wIC * 4, (cuuint64_t)pl.FH * pl.FW * pl.wIC * 4};
+    if (!pl.b_mn) {
+        cuuint32_t box[3] = {(cuuint32_t)KC, 1, (cuuint32_t)BN};
+        rc = make_tiled_map(&tmB, pl.W, 3, wd, ws, box, KC * 4);
+    } else {
+        cuuint32_t box[3] = {32, 1, (cuuint32_t)KC};
+        rc = make_tiled_map(&tmB, pl.W, 3, wd, ws, box, 128);
+    }
+    if (rc) return rc;
+
+    dim3 grid((p.M_total + kBM - 1) / kBM, (pl.ncols + BN - 1) / BN, 1);
+    conv_igemm_kernel<<<grid, kIgemmThreads, smem, stream>>>(tmA, tmB, p);
+    note_launch("igemm");
+    return check_launch("conv_igemm_kernel");
+}
+
+// deltaW += sum of `part` split-K buffers of sizeW floats each (the reference's buf_summary).
+int launch_buf_summary(cudaStream_t stream, const float* buf, float* deltaW, int part, size_t sizeW)
+{
+    const size_t n4 = sizeW / 4;
+    dw_reduce_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, stream>>>(buf, sizeW, part, deltaW, n4, 1);
+    note_launch("buf_summary");
+    return check_launch("dw_reduce_kernel");
+}
+
+}  // namespace alpha
+
+using namespace alpha;
+
+// ---- C ABI, layer 1 ----------------------------------------------------------------------------
+
+extern "C" {
+
+const char* alpha_conv_last_error(void) { return g_err; }
+int alpha_conv_version(void) { return 100; }
+int alpha_conv_set_math_mode(int mode)
+{
+    if (mode != ALPHA_MATH_3XTF32 && mode != ALPHA_MATH_TF32) return fail(ALPHA_E_ARG, "unknown math mode %d", mode);
+    g_math.store(mode);
+    return ALPHA_OK;
+}
+int alpha_conv_get_math_mode(void) { return g_math.load(); }
+int alpha_conv_set_algo(int algo)
+{
+    if (algo < ALPHA_ALGO_AUTO || algo > ALPHA_ALGO_WINOGRAD) return fail(ALPHA_E_ARG, "unknown algo %d", algo);
+    g_algo.store(algo);
+    return ALPHA_OK;
+}
+int alpha_conv_get_algo(void) { return g_algo.load(); }
+unsigned long long alpha_conv_launch_count(void) { return g_launches.load(); }
+const char* alpha_conv_last_algo(void) { return g_last_algo; }
+
+int alpha_conv_device_status(void)
+{
+    DeviceCtx* c;
+    int rc = get_ctx(&c);
+    if (rc) return rc;
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return fail(ALPHA_E_CUDA, "cudaDeviceSynchronize: %s", cudaGetErrorString(e));
+    int h = 0;
+    e = cudaMemcpy(&h, c->status, sizeof(int), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return fail(ALPHA_E_CUDA, "cudaMemcpy(status): %s", cudaGetErrorString(e));
+    if (h != 0) {
+        cudaMemset(c->status, 0, sizeof(int));
+        fail(ALPHA_E_KERNEL, "a kernel left status %d (1 producer, 2 mma, 3 split, 4 epilogue wait ran out)", h);
+    }
+    return h;
+}
+
+int alpha_conv3d_forward(const AlphaConvShape* s, const float* X, const float* W, const float* bias,
+                         float* Y, alpha_stream_t stream_)
+{
+    int rc = check_shape(s, X, W, Y);
+    if (rc) return rc;
+    if (bias && ((uintptr_t)bias & 15)) return fail(ALPHA_E_ARG, "bias must be 16-byte aligned");
+    DeviceCtx* c;
+    rc = get_ctx(&c);
+    if (rc) return rc;
+    cudaStream_t stream = (cudaStream_t)stream_;
+    const int algo = g_algo.load();
+    const bool tensor_ok = pick_kc(s->IC) != 0 && s->ph < 128 && s->pw < 128 && s->FH <= 256 && s->FW <= 256;
+    if (algo == ALPHA_ALGO_TENSOR && !tensor_ok)
+        return fail(ALPHA_E_ARG, "tensor path needs IC %% 8 == 0 (IC=%d)", s->IC);
+    if (algo != ALPHA_ALGO_SIMT && tensor_ok) {
+        IgemmPlan pl{};
+        pl.act = X; pl.aN = s->N; pl.aH = s->IH; pl.aW = s->IW; pl.aC = s->IC;
+        pl.FH = s->FH; pl.FW = s->FW; pl.sh = s->sh; pl.sw = s->sw; pl.pad_h = s->ph; pl.pad_w = s->pw;
+        pl.out = Y; pl.oH = s->OH; pl.oW = s->OW; pl.ncols = s->OC;
+        pl.W = W; pl.wOC = s->OC; pl.wIC = s->IC; pl.bias = bias;
+        pl.b_mn = false; pl.flip = false; pl.kdim = s->IC;
+        return launch_igemm(c, pl, g_math.load() == ALPHA_MATH_3XTF32, stream);
+    }
+    const size_t total = (size_t)s->N * s->OH * s->OW * s->OC;
+    conv_fwd_simt<<<simt_grid(total, c->sm_count), 256, 0, stream>>>(X, W, bias, Y, to_dev_shape(s));
+    note_launch("simt");
+    return check_launch("conv_fwd_simt");
+}
+
+int alpha_conv3d_deltaX(const AlphaConvShape* s, const float* deltaY, const float* W, float* deltaX,
+                        alpha_stream_t stream_)
+{
+    int rc = check_shape(s, deltaY, W, deltaX);
+    if (rc) return rc;
+    DeviceCtx* c;
+    rc = get_ctx(&c);
+    if (rc) return rc;
+    cudaStream_t stream = (cudaStream_t)stream_;
+    const int algo = g_algo.load();
+    const int pad_h = s->FH - 1 - s->ph, pad_w = s->FW - 1 - s->pw;
+    const bool tensor_ok = s->sh == 1 && s->sw == 1 && pick_kc(s->OC) != 0 && pad_h >= 0 && pad_w >= 0 &&
+                           pad_h < 128 && pad_w < 128 && s->IH == s->OH + s->FH - 1 - 2 * s->ph &&
+                           s->IW == s->OW + s->FW - 1 - 2 * s->pw;
+    if (algo == ALPHA_ALGO_TENSOR && !tensor_ok)
+        return fail(ALPHA_E_ARG, "tensor deltaX path needs stride 1, OC %% 8 == 0 and padding < filter");
+    if (algo != ALPHA_ALGO_SIMT && tensor_ok) {
+        IgemmPlan pl{};
+        pl.act = deltaY; pl.aN = s->N; pl.aH = s->OH; pl.aW = s->OW; pl.aC = s->OC;
+        pl.FH = s->FH; pl.FW = s->FW; pl.sh = 1; pl.sw = 1; pl.pad_h = pad_h; pl.pad_w = pad_w;
+        pl.out = deltaX; pl.oH = s->IH; pl.oW = s->IW; pl.ncols = s->IC;
+        pl.W = W; pl.wOC = s->OC; pl.wIC = s->IC; pl.bias = nullptr;
+        pl.b_mn = true; pl.flip = true; pl.kdim = s->OC;
+        return launch_igemm(c, pl, g_math.load() == ALPHA_MATH_3XTF32, stream);
+    }
+    const size_t total = (size_t)s->N * s->IH * s->IW * s->IC;
+    conv_dx_simt<<<simt_grid(total, c->sm_count), 256, 0, stream>>>(deltaY, W, deltaX, to_dev_shape(s));
+    note_launch("simt");
+    return check_launch("conv_dx_simt");
+}
+
+int alpha_conv3d_deltaW(const AlphaConvShape* s, const float* X, const float* deltaY, float* deltaW,
+                        alpha_stream_t stream_)
+{
+    int rc = check_shape(s, X, deltaY, deltaW);
+    if (rc) return rc;
+    DeviceCtx* c;
+    rc = get_ctx(&c);
+    if (rc) return rc;
+    cudaStream_t stream = (cudaStream_t)stream_;
+    const int algo = g_algo.load();
+    const bool tensor_ok = (s->IC % 32 == 0) && s->ph < 128 && s->pw < 128 && s->FH <= 256 && s->FW <= 256;
+    if (algo == ALPHA_ALGO_TENSOR && !tensor_ok)
+        return fail(ALPHA_E_ARG, "tensor deltaW path needs IC %% 32 == 0 (IC=%d)", s->IC);
+    if (algo == ALPHA_ALGO_SIMT || !tensor_ok) {
+        const size_t total = (size_t)s->OC * s->FH * s->FW * s->IC;
+        conv_dw_simt<<<(unsigned)total, 128, 0, stream>>>(X, deltaY, deltaW, to_dev_shape(s));
+        note_launch("simt");
+        return check_launch("conv_dw_simt");
+    }
+
+    const int mode3x = g_math.load() == ALPHA_MATH_3XTF32;
+    DwParams p{};
+    p.status = c->status;
+    p.Npix = s->N * s->OH * s->OW;
+    p.OHo = s->OH; p.OWo = s->OW; p.sh = s->sh; p.sw = s->sw; p.ph = s->ph; p.pw = s->pw;
+    p.FH = s->FH; p.FW = s->FW; p.IC = s->IC; p.OC = s->OC;
+    p.icb = s->IC / 32;
+    p.MB = s->FH * s->FW * p.icb;
+    int BN = ((s->OC + 31) / 32) * 32;
+    if (BN > 256) BN = 256;
+    p.BN = BN;
+    const int MT = (p.MB + 3) / 4;
+    int G = 512 / BN;  // accumulators of BN columns that fit the 512 tensor-memory columns
+    if (G > MT) G = MT;
+    const int groups = (MT + G - 1) / G;
+    G = (MT + groups - 1) / groups;  // balance the groups
+    p.G = G;
+    p.KP = 32;
+    p.tmem_cols = pow2_cols(G * BN);
+    p.idesc = make_idesc_tf32(kBM, BN, true, true);
+    p.mode3x = mode3x;
+    const int n_tiles = (s->OC + BN - 1) / BN;
+    p.total_chunks = (p.Npix + p.KP - 1) / p.KP;
+    int splits = c->sm_count / (groups * n_tiles);
+    if (splits < 1) splits = 1;
+    if (splits > p.total_chunks) splits = p.total_chunks;
+    p.chunks_per_split = (p.total_chunks + splits - 1) / splits;
+    splits = (p.total_chunks + p.chunks_per_split - 1) / p.chunks_per_split;
+    const size_t sizeW = (size_t)s->OC * s->FH * s->FW * s->IC;
+    if (splits > 1) {
+        rc = ensure_workspace(c, sizeW * splits * sizeof(float));
+        if (rc) return rc;
+        p.out = c->workspace;
+        p.split_stride = sizeW;
+    } else {
+        p.out = deltaW;
+        p.split_stride = 0;
+    }
+    const uint32_t blk = p.KP * 128;
+    const uint32_t stage = (4 * blk + (BN / 32) * blk) * (mode3x ? 2 : 1);
+    int stages = (int)((200u * 1024) / stage);
+    if (stages > 6) stages = 6;
+    if (stages < 1) return fail(ALPHA_E_ARG, "deltaW stage of %u bytes does not fit shared memory", stage);
+    p.stages = stages;
+    const size_t smem = (size_t)stages * stage + (3 * stages + 2) * 8 + 1024;
+
+    CUtensorMap tmX, tmDY;
+    rc = make_im2col_map(&tmX, X, s->N, s->IH, s->IW, s->IC, s->FH, s->FW, s->sh, s->sw, s->ph, s->pw, 32, p.KP);
+    if (rc) return rc;
+    cuuint64_t dd[2] = {(cuuint64_t)s->OC, (cuuint64_t)p.Npix};
+    cuuint64_t ds[1] = {(cuuint64_t)s->OC * 4};
+    cuuint32_t box[2] = {32, (cuuint32_t)p.KP};
+    rc = make_tiled_map(&tmDY, deltaY, 2, dd, ds, box, 128);
+    if (rc) return rc;
+
+    dim3 grid(groups, n_tiles, splits);
+    conv_dw_kernel<<<grid, kIgemmThreads, smem, stream>>>(tmX, tmDY, p);
+    note_launch("dw");
+    rc = check_launch("conv_dw_kernel");
+    if (rc) return rc;
+    if (splits > 1) {
+        const size_t n4 = sizeW / 4;
+        dw_reduce_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, stream>>>(c->workspace, sizeW, splits, deltaW, n4, 0);
+        note_launch("dw");
+        rc = check_launch("dw_reduce_kernel");
+    }
+    return rc;
+}
+
+}  // extern "C"

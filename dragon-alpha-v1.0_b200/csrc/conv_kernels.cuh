@@ -1,0 +1,574 @@
+// Device kernels of the conv hot path for sm_100a.
+//
+//   conv_igemm_kernel   forward conv and stride-1 deltaX as an implicit GEMM:
+//                       D[128 pixels][BN channels] += im2col(act)[128][K] * Wt[BN][K]
+//                       A tiles come from an im2col-mode TMA of the NHWC activation tensor, B tiles
+//                       from a tiled TMA of W[OC,FH,FW,IC]; tcgen05.mma kind::tf32 accumulates in
+//                       tensor memory; 3xTF32 splits each staged tile into hi/lo planes.
+//   conv_dw_kernel      deltaW as a split-K GEMM whose K axis is the pixel axis; both operands are
+//                       MN-major (channels contiguous), several accumulators per CTA.
+//   dw_reduce_kernel    fixed-order (deterministic) compensated sum of the split-K partials.
+//   *_simt kernels      plain fp32 kernels for shapes the tensor path does not take (channel counts
+//                       that are not a multiple of 8, strided deltaX); they keep the library
+//                       complete on the GPU, there is no CPU path.
+#pragma once
+#include "sm100_ptx.cuh"
+
+namespace alpha {
+
+constexpr int kBM = 128;           // GEMM M tile = tensor-memory lanes
+constexpr int kIgemmThreads = 192;  // warp 0: TMA, warp 1: MMA, warps 2-5: split + epilogue
+
+enum KernelStatus : int {
+    kStatusOk = 0,
+    kStatusProducerTimeout = 1,
+    kStatusMmaTimeout = 2,
+    kStatusSplitTimeout = 3,
+    kStatusEpilogueTimeout = 4,
+};
+
+struct IgemmParams {
+    float* out;         // [M_total][ldo]
+    const float* bias;  // [Ncols] or nullptr
+    int* status;        // device status word, 0 = ok
+    int M_total;        // output pixels
+    int Ncols;          // output channels
+    int ldo;            // row stride of out in floats
+    int OHo, OWo;       // output spatial extent (pixel -> coordinates)
+    int sh, sw, ph, pw; // base pixel coordinate = (q*sw - pw, p*sh - ph)
+    int FH, FW;
+    int kchunks;        // channel chunks per filter tap
+    int KC;             // reduction channels per chunk: 32, 16 or 8
+    int BN;             // N tile, multiple of 16 (of 32 when b_mn)
+    int stages;
+    int mode3x;         // 1: 3xTF32 split, 0: plain TF32
+    int b_mn;           // 1: B operand is MN-major (deltaX reads W[oc][tap][ic] in place)
+    int flip;           // 1: B uses the 180-degree rotated tap
+    uint32_t tmem_cols;
+    uint32_t idesc;
+    uint32_t a_bytes;   // bytes of one A plane per stage
+    uint32_t b_bytes;   // bytes of one B plane per stage (rounded up to 1024)
+    uint32_t b_tx;      // bytes the B loads of one stage deliver
+    uint32_t swz;       // descriptor layout type of the K-major operands
+};
+
+__device__ __forceinline__ void report(int* status, int code)
+{
+    if (status) atomicCAS(status, 0, code);
+}
+
+__device__ __forceinline__ uint32_t to_tf32_rna(float x)
+{
+    uint32_t u;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
+    return u;
+}
+
+// hi = tf32(x), lo = tf32(x - hi): x = hi + lo up to 2^-22 |x|.
+__device__ __forceinline__ void split_tf32(float4& hi, float4& lo)
+{
+    float4 x = hi;
+    hi.x = __uint_as_float(to_tf32_rna(x.x));
+    hi.y = __uint_as_float(to_tf32_rna(x.y));
+    hi.z = __uint_as_float(to_tf32_rna(x.z));
+    hi.w = __uint_as_float(to_tf32_rna(x.w));
+    lo.x = __uint_as_float(to_tf32_rna(x.x - hi.x));
+    lo.y = __uint_as_float(to_tf32_rna(x.y - hi.y));
+    lo.z = __uint_as_float(to_tf32_rna(x.z - hi.z));
+    lo.w = __uint_as_float(to_tf32_rna(x.w - hi.w));
+}
+
+// Rewrites one staged plane in place as its hi part and fills the lo plane; 128 threads.
+__device__ __forceinline__ void split_plane(uint8_t* hi_plane, uint8_t* lo_plane, uint32_t bytes,
+                                            int tid128)
+{
+    float4* h = reinterpret_cast<float4*>(hi_plane);
+    float4* l = reinterpret_cast<float4*>(lo_plane);
+    const uint32_t nvec = bytes >> 4;
+    for (uint32_t v = tid128; v < nvec; v += 128) {
+        float4 a = h[v], b;
+        split_tf32(a, b);
+        h[v] = a;
+        l[v] = b;
+    }
+}
+
+__global__ void __launch_bounds__(kIgemmThreads)
+    conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA,
+                      const __grid_constant__ CUtensorMap tmB, const IgemmParams p)
+{
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                               ~static_cast<uintptr_t>(1023));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile_m = blockIdx.x, tile_n = blockIdx.y;
+    const int S = p.stages;
+    const uint32_t planes = p.mode3x ? 2u : 1u;
+    const uint32_t stage_bytes = (p.a_bytes + p.b_bytes) * planes;
+
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + static_cast<size_t>(S) * stage_bytes);
+    uint64_t* full = bars;
+    uint64_t* split_done = bars + S;
+    uint64_t* empty = bars + 2 * S;
+    uint64_t* accum = bars + 3 * S;
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 3 * S + 1);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&split_done[s], 128);
+            mbar_init(&empty[s], 1);
+        }
+        mbar_init(accum, 1);
+        fence_barrier_init();
+        prefetch_tmap(&tmA);
+        prefetch_tmap(&tmB);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_holder, p.tmem_cols);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_holder;
+
+    const int num_it = p.FH * p.FW * p.kchunks;
+    const int m0 = tile_m * kBM;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---- TMA producer ----
+            const int hw = p.OHo * p.OWo;
+            const int n_img = m0 / hw;
+            const int rem = m0 - n_img * hw;
+            const int pr = rem / p.OWo, qc = rem - pr * p.OWo;
+            const int w0 = qc * p.sw - p.pw, h0 = pr * p.sh - p.ph;
+            const int taps = p.FH * p.FW;
+            for (int it = 0; it < num_it; ++it) {
+                const int s = it % S;
+                const uint32_t par = (it / S) & 1;
+                if (!mbar_wait(&empty[s], par ^ 1)) { report(p.status, kStatusProducerTimeout); break; }
+                const int tap = it / p.kchunks, kc = it - tap * p.kchunks;
+                const int fh = tap / p.FW, fw = tap - fh * p.FW;
+                uint8_t* a_dst = smem + static_cast<size_t>(s) * stage_bytes;
+                uint8_t* b_dst = a_dst + p.a_bytes * planes;
+                mbar_arrive_expect_tx(&full[s], p.a_bytes + p.b_tx);
+                tma_load_im2col_4d(a_dst, &tmA, &full[s], kc * p.KC, w0, h0, n_img,
+                                   static_cast<uint16_t>(fw), static_cast<uint16_t>(fh));
+                if (!p.b_mn) {
+                    tma_load_3d(b_dst, &tmB, &full[s], kc * p.KC, tap, tile_n * p.BN);
+                } else {
+                    const int tapw = p.flip ? (taps - 1 - tap) : tap;
+                    for (int j = 0; j < p.BN / 32; ++j)
+                        tma_load_3d(b_dst + j * (p.KC * 128), &tmB, &full[s],
+                                    tile_n * p.BN + j * 32, tapw, kc * p.KC);
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // ---- MMA issuer ----
+            const uint32_t row_bytes = p.KC * 4;
+            const uint32_t sbo_k = 8 * row_bytes;
+            bool ok = true;
+            for (int it = 0; it < num_it && ok; ++it) {
+                const int s = it % S;
+                const uint32_t par = (it / S) & 1;
+                if (!mbar_wait(p.mode3x ? &split_done[s] : &full[s], par)) {
+                    report(p.status, kStatusMmaTimeout);
+                    ok = false;
+                    break;
+                }
+                tc_fence_after_sync();
+                const uint32_t a_hi = smem_u32(smem + static_cast<size_t>(s) * stage_bytes);
+                const uint32_t a_lo = a_hi + p.a_bytes;
+                const uint32_t b_hi = a_hi + p.a_bytes * planes;
+                const uint32_t b_lo = b_hi + p.b_bytes;
+                for (int kk = 0; kk < p.KC / 8; ++kk) {
+                    const uint32_t acc = (it | kk) ? 1u : 0u;
+                    const uint32_t a_off = kk * 32, b_off = p.b_mn ? kk * 1024 : kk * 32;
+                    const uint64_t ad = make_smem_desc(a_hi + a_off, 16, sbo_k, p.swz);
+                    const uint64_t bd = p.b_mn ? make_smem_desc(b_hi + b_off, p.KC * 128, 1024, kSwizzle128B)
+                                               : make_smem_desc(b_hi + b_off, 16, sbo_k, p.swz);
+                    if (p.mode3x) {
+                        const uint64_t adl = make_smem_desc(a_lo + a_off, 16, sbo_k, p.swz);
+                        const uint64_t bdl = p.b_mn ? make_smem_desc(b_lo + b_off, p.KC * 128, 1024, kSwizzle128B)
+                                                    : make_smem_desc(b_lo + b_off, 16, sbo_k, p.swz);
+                        mma_tf32_ss(tmem_base, adl, bd, p.idesc, acc);
+                        mma_tf32_ss(tmem_base, ad, bdl, p.idesc, 1u);
+                        mma_tf32_ss(tmem_base, ad, bd, p.idesc, 1u);
+                    } else {
+                        mma_tf32_ss(tmem_base, ad, bd, p.idesc, acc);
+                    }
+                }
+                mma_commit(&empty[s]);
+            }
+            mma_commit(accum);
+        }
+        __syncwarp();
+    } else {
+        // ---- operand split (3xTF32) and epilogue: warps 2..5 ----
+        const int tid128 = threadIdx.x - 64;
+        bool ok = true;
+        if (p.mode3x) {
+            for (int it = 0; it < num_it; ++it) {
+                const int s = it % S;
+                const uint32_t par = (it / S) & 1;
+                if (!mbar_wait(&full[s], par)) { report(p.status, kStatusSplitTimeout); ok = false; break; }
+                uint8_t* a_hi = smem + static_cast<size_t>(s) * stage_bytes;
+                uint8_t* b_hi = a_hi + p.a_bytes * 2;
+                split_plane(a_hi, a_hi + p.a_bytes, p.a_bytes, tid128);
+                split_plane(b_hi, b_hi + p.b_bytes, p.b_tx, tid128);
+                fence_proxy_async_smem();
+                mbar_arrive(&split_done[s]);
+            }
+        }
+        if (ok && !mbar_wait(accum, 0)) { report(p.status, kStatusEpilogueTimeout); ok = false; }
+        tc_fence_after_sync();
+        if (ok) {
+            const int quad = warp & 3;
+            const int row = quad * 32 + lane;
+            const long long m = static_cast<long long>(m0) + row;
+            float* orow = p.out + m * p.ldo;
+            const int n0 = tile_n * p.BN;
+            for (int c = 0; c < p.BN; c += 32) {
+                uint32_t r[32];
+                tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + c, r);
+                tmem_ld_wait();
+                if (m < p.M_total) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4) {
+                        const int col = n0 + c + j;
+                        if (c + j < p.BN && col < p.Ncols) {
+                            float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                                   __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                            if (p.bias) {
+                                const float4 b = *reinterpret_cast<const float4*>(p.bias + col);
+                                v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+                            }
+                            *reinterpret_cast<float4*>(orow + col) = v;
+                        }
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, p.tmem_cols);
+}
+
+// ---------------------------------------------------------------------------------------------
+// deltaW
+// ---------------------------------------------------------------------------------------------
+
+struct DwParams {
+    float* out;           // deltaW, or the partial buffer when splits > 1
+    size_t split_stride;  // floats between the partials of two splits
+    int* status;
+    int Npix;             // N*OH*OW, the reduction extent
+    int OHo, OWo, sh, sw, ph, pw, FH, FW;
+    int IC, OC;
+    int icb;              // 32-channel blocks per tap = IC/32
+    int MB;               // M blocks = taps * icb; 4 blocks make one 128-row M tile
+    int G;                // M tiles (accumulators) per CTA
+    int BN;               // N tile over OC, multiple of 32
+    int KP;               // pixels per reduction chunk (multiple of 8)
+    int chunks_per_split, total_chunks;
+    int stages, mode3x;
+    uint32_t tmem_cols, idesc;
+};
+
+__global__ void __launch_bounds__(kIgemmThreads)
+    conv_dw_kernel(const __grid_constant__ CUtensorMap tmX,
+                   const __grid_constant__ CUtensorMap tmDY, const DwParams p)
+{
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                               ~static_cast<uintptr_t>(1023));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int group = blockIdx.x, tile_n = blockIdx.y, split = blockIdx.z;
+    const int S = p.stages;
+    const uint32_t planes = p.mode3x ? 2u : 1u;
+    const uint32_t blk_bytes = p.KP * 128;           // one 32-channel block of KP pixels
+    const uint32_t a_bytes = 4 * blk_bytes;          // 128 rows of (tap, ic)
+    const uint32_t b_bytes = (p.BN / 32) * blk_bytes;
+    const uint32_t stage_bytes = (a_bytes + b_bytes) * planes;
+
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + static_cast<size_t>(S) * stage_bytes);
+    uint64_t* full = bars;
+    uint64_t* split_done = bars + S;
+    uint64_t* empty = bars + 2 * S;
+    uint64_t* accum = bars + 3 * S;
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 3 * S + 1);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&split_done[s], 128);
+            mbar_init(&empty[s], 1);
+        }
+        mbar_init(accum, 1);
+        fence_barrier_init();
+        prefetch_tmap(&tmX);
+        prefetch_tmap(&tmDY);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_holder, p.tmem_cols);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_holder;
+
+    const int MT = (p.MB + 3) / 4;                       // M tiles in total
+    const int g_count = min(p.G, MT - group * p.G);      // M tiles of this CTA
+    const int c_begin = split * p.chunks_per_split;
+    const int c_end = min(c_begin + p.chunks_per_split, p.total_chunks);
+    const int n_chunks = max(c_end - c_begin, 0);
+    const int num_it = n_chunks * g_count;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            const int hw = p.OHo * p.OWo;
+            for (int it = 0; it < num_it; ++it) {
+                const int s = it % S;
+                const uint32_t par = (it / S) & 1;
+                if (!mbar_wait(&empty[s], par ^ 1)) { report(p.status, kStatusProducerTimeout); break; }
+                const int ci = it / g_count, g = it - ci * g_count;
+                const int pix0 = (c_begin + ci) * p.KP;
+                const int n_img = pix0 / hw;
+                const int rem = pix0 - n_img * hw;
+                const int pr = rem / p.OWo, qc = rem - pr * p.OWo;
+                const int w0 = qc * p.sw - p.pw, h0 = pr * p.sh - p.ph;
+                uint8_t* a_dst = smem + static_cast<size_t>(s) * stage_bytes;
+                uint8_t* b_dst = a_dst + a_bytes * planes;
+                const int mb0 = (group * p.G + g) * 4;
+                const int nblk = min(4, p.MB - mb0);
+                mbar_arrive_expect_tx(&full[s], (nblk + p.BN / 32) * blk_bytes);
+                for (int b = 0; b < nblk; ++b) {
+                    const int mb = mb0 + b;
+                    const int tap = mb / p.icb, ic0 = (mb - tap * p.icb) * 32;
+                    const int fh = tap / p.FW, fw = tap - fh * p.FW;
+                    tma_load_im2col_4d(a_dst + b * blk_bytes, &tmX, &full[s], ic0, w0, h0, n_img,
+                                       static_cast<uint16_t>(fw), static_cast<uint16_t>(fh));
+                }
+                for (int j = 0; j < p.BN / 32; ++j)
+                    tma_load_2d(b_dst + j * blk_bytes, &tmDY, &full[s], tile_n * p.BN + j * 32, pix0);
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        if (lane == 0) {
+            for (int it = 0; it < num_it; ++it) {
+                const int s = it % S;
+                const uint32_t par = (it / S) & 1;
+                if (!mbar_wait(p.mode3x ? &split_done[s] : &full[s], par)) {
+                    report(p.status, kStatusMmaTimeout);
+                    break;
+                }
+                tc_fence_after_sync();
+                const int ci = it / g_count, g = it - ci * g_count;
+                const uint32_t d = tmem_base + g * p.BN;
+                const uint32_t a_hi = smem_u32(smem + static_cast<size_t>(s) * stage_bytes);
+                const uint32_t a_lo = a_hi + a_bytes;
+                const uint32_t b_hi = a_hi + a_bytes * planes;
+                const uint32_t b_lo = b_hi + b_bytes;
+                for (int kk = 0; kk < p.KP / 8; ++kk) {
+                    const uint32_t acc = (ci | kk) ? 1u : 0u;
+                    const uint32_t off = kk * 1024;
+                    const uint64_t ad = make_smem_desc(a_hi + off, blk_bytes, 1024, kSwizzle128B);
+                    const uint64_t bd = make_smem_desc(b_hi + off, blk_bytes, 1024, kSwizzle128B);
+                    if (p.mode3x) {
+                        const uint64_t adl = make_smem_desc(a_lo + off, blk_bytes, 1024, kSwizzle128B);
+                        const uint64_t bdl = make_smem_desc(b_lo + off, blk_bytes, 1024, kSwizzle128B);
+                        mma_tf32_ss(d, adl, bd, p.idesc, acc);
+                        mma_tf32_ss(d, ad, bdl, p.idesc, 1u);
+                        mma_tf32_ss(d, ad, bd, p.idesc, 1u);
+                    } else {
+                        mma_tf32_ss(d, ad, bd, p.idesc, acc);
+                    }
+                }
+                mma_commit(&empty[s]);
+            }
+            mma_commit(accum);
+        }
+        __syncwarp();
+    } else {
+        const int tid128 = threadIdx.x - 64;
+        bool ok = true;
+        if (p.mode3x) {
+            for (int it = 0; it < num_it; ++it) {
+                const int s = it % S;
+                const uint32_t par = (it / S) & 1;
+                if (!mbar_wait(&full[s], par)) { report(p.status, kStatusSplitTimeout); ok = false; break; }
+                uint8_t* a_hi = smem + static_cast<size_t>(s) * stage_bytes;
+                uint8_t* b_hi = a_hi + a_bytes * 2;
+                split_plane(a_hi, a_hi + a_bytes, a_bytes, tid128);
+                split_plane(b_hi, b_hi + b_bytes, b_bytes, tid128);
+                fence_proxy_async_smem();
+                mbar_arrive(&split_done[s]);
+            }
+        }
+        if (ok && !mbar_wait(accum, 0)) { report(p.status, kStatusEpilogueTimeout); ok = false; }
+        tc_fence_after_sync();
+        if (ok) {
+            const int quad = warp & 3;
+            const int taps = p.FH * p.FW;
+            float* obase = p.out + static_cast<size_t>(split) * p.split_stride;
+            for (int g = 0; g < g_count; ++g) {
+                const int mb = (group * p.G + g) * 4 + quad;
+                const int tap = mb / p.icb;
+                const int ic = (mb - tap * p.icb) * 32 + lane;
+                const bool row_ok = (mb < p.MB) && (ic < p.IC);
+                for (int c = 0; c < p.BN; c += 32) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + g * p.BN + c, r);
+                    tmem_ld_wait();
+                    if (row_ok) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const int oc = tile_n * p.BN + c + j;
+                            if (oc < p.OC) {
+                                const float v = (n_chunks > 0) ? __uint_as_float(r[j]) : 0.f;
+                                obase[(static_cast<size_t>(oc) * taps + tap) * p.IC + ic] = v;
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, p.tmem_cols);
+}
+
+// out[i] = sum over splits of part[s][i], in split order, with Kahan compensation (the reference
+// sums its split-K buffers the same way: Cuda_dconv3D_deltaW/dconv3d_dW_GemmSK_bufSum.cuh:41-63).
+// When `accumulate` is set, out[i] itself is the first term (deltaW += sum of buffers).
+__global__ void dw_reduce_kernel(const float* __restrict__ part, size_t split_stride, int splits,
+                                 float* __restrict__ out, size_t n4, int accumulate)
+{
+    const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= n4) return;
+    float4 s = accumulate ? reinterpret_cast<const float4*>(out)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 c = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int k = 0; k < splits; ++k) {
+        const float4 v = reinterpret_cast<const float4*>(part + k * split_stride)[i];
+        float y, t;
+        y = v.x - c.x; t = s.x + y; c.x = (t - s.x) - y; s.x = t;
+        y = v.y - c.y; t = s.y + y; c.y = (t - s.y) - y; s.y = t;
+        y = v.z - c.z; t = s.z + y; c.z = (t - s.z) - y; s.z = t;
+        y = v.w - c.w; t = s.w + y; c.w = (t - s.w) - y; s.w = t;
+    }
+    reinterpret_cast<float4*>(out)[i] = s;
+}
+
+// ---------------------------------------------------------------------------------------------
+// plain fp32 kernels for the shapes the tensor path leaves out
+// ---------------------------------------------------------------------------------------------
+
+struct ConvShape {
+    int N, IH, IW, IC, OC, FH, FW, OH, OW, sh, sw, ph, pw;
+};
+
+// One thread per output element (n, oh, ow, oc); taps in fh -> fw -> ic order.
+__global__ void conv_fwd_simt(const float* __restrict__ X, const float* __restrict__ W,
+                              const float* __restrict__ bias, float* __restrict__ Y, ConvShape s)
+{
+    const size_t total = static_cast<size_t>(s.N) * s.OH * s.OW * s.OC;
+    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const int oc = static_cast<int>(i % s.OC);
+        size_t t = i / s.OC;
+        const int ow = static_cast<int>(t % s.OW); t /= s.OW;
+        const int oh = static_cast<int>(t % s.OH);
+        const int n = static_cast<int>(t / s.OH);
+        float v = 0.f;
+        for (int fh = 0; fh < s.FH; ++fh) {
+            const int ih = oh * s.sh - s.ph + fh;
+            if (ih < 0 || ih >= s.IH) continue;
+            for (int fw = 0; fw < s.FW; ++fw) {
+                const int iw = ow * s.sw - s.pw + fw;
+                if (iw < 0 || iw >= s.IW) continue;
+                const float* x = X + ((static_cast<size_t>(n) * s.IH + ih) * s.IW + iw) * s.IC;
+                const float* w = W + ((static_cast<size_t>(oc) * s.FH + fh) * s.FW + fw) * s.IC;
+                for (int ic = 0; ic < s.IC; ++ic) v = fmaf(x[ic], w[ic], v);
+            }
+        }
+        if (bias) v += bias[oc];
+        Y[i] = v;
+    }
+}
+
+// One thread per (n, ih, iw, ic); gathers the taps whose stride phase matches, no atomics.
+__global__ void conv_dx_simt(const float* __restrict__ dY, const float* __restrict__ W,
+                             float* __restrict__ dX, ConvShape s)
+{
+    const size_t total = static_cast<size_t>(s.N) * s.IH * s.IW * s.IC;
+    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const int ic = static_cast<int>(i % s.IC);
+        size_t t = i / s.IC;
+        const int iw = static_cast<int>(t % s.IW); t /= s.IW;
+        const int ih = static_cast<int>(t % s.IH);
+        const int n = static_cast<int>(t / s.IH);
+        float v = 0.f;
+        for (int fh = 0; fh < s.FH; ++fh) {
+            const int a = ih + s.ph - fh;
+            if (a < 0 || a % s.sh != 0) continue;
+            const int oh = a / s.sh;
+            if (oh >= s.OH) continue;
+            for (int fw = 0; fw < s.FW; ++fw) {
+                const int b = iw + s.pw - fw;
+                if (b < 0 || b % s.sw != 0) continue;
+                const int ow = b / s.sw;
+                if (ow >= s.OW) continue;
+                const float* dy = dY + ((static_cast<size_t>(n) * s.OH + oh) * s.OW + ow) * s.OC;
+                const float* w = W + (static_cast<size_t>(fh) * s.FW + fw) * s.IC + ic;
+                const size_t wstride = static_cast<size_t>(s.FH) * s.FW * s.IC;
+                for (int oc = 0; oc < s.OC; ++oc) v = fmaf(dy[oc], w[oc * wstride], v);
+            }
+        }
+        dX[i] = v;
+    }
+}
+
+// One block per deltaW element (oc, fh, fw, ic): 128 threads stride over the pixels, then a
+// fixed-shape tree sum in shared memory (deterministic).
+__global__ void __launch_bounds__(128)
+    conv_dw_simt(const float* __restrict__ X, const float* __restrict__ dY, float* __restrict__ dW,
+                 ConvShape s)
+{
+    __shared__ float red[128];
+    const size_t e = blockIdx.x;
+    const int ic = static_cast<int>(e % s.IC);
+    size_t t = e / s.IC;
+    const int fw = static_cast<int>(t % s.FW); t /= s.FW;
+    const int fh = static_cast<int>(t % s.FH);
+    const int oc = static_cast<int>(t / s.FH);
+    const int npix = s.N * s.OH * s.OW;
+    float v = 0.f;
+    for (int k = threadIdx.x; k < npix; k += 128) {
+        const int n = k / (s.OH * s.OW);
+        const int r = k - n * s.OH * s.OW;
+        const int oh = r / s.OW, ow = r - oh * s.OW;
+        const int ih = oh * s.sh - s.ph + fh, iw = ow * s.sw - s.pw + fw;
+        if (ih < 0 || iw < 0 || ih >= s.IH || iw >= s.IW) continue;
+        v = fmaf(X[((static_cast<size_t>(n) * s.IH + ih) * s.IW + iw) * s.IC + ic],
+                 dY[static_cast<size_t>(k) * s.OC + oc], v);
+    }
+    red[threadIdx.x] = v;
+    __syncthreads();
+    for (int o = 64; o > 0; o >>= 1) {
+        if (threadIdx.x < o) red[threadIdx.x] += red[threadIdx.x + o];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) dW[e] = red[0];
+}
+
+}  // namespace alpha

@@ -1,0 +1,324 @@
+// JNI entry points of the three native classes this library replaces.  The exported names and
+// signatures are those of the reference's shims (Cuda_conv3D/A.cu:14-244, Cuda_dconv3D_deltaX/A.cu:14-325,
+// Cuda_dconv3D_deltaW/A.cu:16-154): each unpacks the Java stream array and forwards to the
+// alpha_Cuda_* function of the same name.  A non-zero status becomes a pending
+// z.dragon.engine.cuda.impl.CudaException carrying the library's error text (the reference looks up
+// the stale class path z/jcuda/exception/CudaException, Cuda_conv3D/JNITool.cuh:16).
+#include "../../include/alpha_conv_b200.h"
+#include "../../include/alpha_conv_jni.h"
+
+namespace {
+
+constexpr int kMaxStreams = 16;
+
+struct Streams {
+    int64_t v[kMaxStreams];
+    int n;
+};
+
+inline Streams get_streams(JNIEnv* env, jlongArray arr, jint length)
+{
+    Streams s{};
+    s.n = length < 0 ? 0 : (length > kMaxStreams ? kMaxStreams : length);
+    jlong tmp[kMaxStreams];
+    if (s.n > 0) env->GetLongArrayRegion(arr, 0, s.n, tmp);
+    for (int i = 0; i < s.n; ++i) s.v[i] = tmp[i];
+    return s;
+}
+
+inline void raise(JNIEnv* env, int rc)
+{
+    if (rc == ALPHA_OK || env->ExceptionCheck()) return;
+    jclass cls = env->FindClass("z/dragon/engine/cuda/impl/CudaException");
+    if (cls) env->ThrowNew(cls, alpha_conv_last_error());
+}
+
+inline float* fp(jlong a) { return reinterpret_cast<float*>(static_cast<intptr_t>(a)); }
+
+}  // namespace
+
+extern "C" {
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1conv3D_conv3D(JNIEnv* env, jclass,
+    jlongArray streamArray, jint length, jlong X_address, jint IH, jint IW, jlong W_address, jint
+    FH, jint FW, jlong Y_address, jint OH, jint OW, jint N, jint IC, jint OC, jint sh, jint sw,
+    jint ph, jint pw)
+{
+    Streams st = get_streams(env, streamArray, length);
+    raise(env, alpha_Cuda_conv3D_conv3D(st.v, st.n, fp(X_address), IH, IW, fp(W_address), FH, FW,
+    fp(Y_address), OH, OW, N, IC, OC, sh, sw, ph, pw));
+}
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1conv3D_conv3D_1texture(JNIEnv* env, jclass,
+    jlongArray streamArray, jint length, jlong X_address, jint IH, jint IW, jlong W_address, jint
+    FH, jint FW, jlong Y_address, jint OH, jint OW, jint N, jint IC, jint OC, jint sh, jint sw,
+    jint ph, jint pw)
+{
+    Streams st = get_streams(env, streamArray, length);
+    raise(env, alpha_Cuda_conv3D_conv3D_texture(st.v, st.n, fp(X_address), IH, IW, fp(W_address),
+    FH, FW, fp(Y_address), OH, OW, N, IC, OC, sh, sw, ph, pw));
+}
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1conv3D_conv3DV2(JNIEnv* env, jclass,
+    jboolean useTexture, jlongArray streamArray, jint length, jlong X_address, jint IH, jint IW,
+    jlong W_address, jint FH, jint FW, jlong Y_address, jint OH, jint OW, jint N, jint IC, jint
+    OC, jint sh, jint sw, jint ph, jint pw)
+{
+    Streams st = get_streams(env, streamArray, length);
+    raise(env, alpha_Cuda_conv3D_conv3DV2(useTexture ? 1 : 0, st.v, st.n, fp(X_address), IH, IW,
+    fp(W_address), FH, FW, fp(Y_address), OH, OW, N, IC, OC, sh, sw, ph, pw));
+}
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1conv3D_conv3D_1np(JNIEnv* env, jclass,
+    jlongArray streamArray, jint length, jlong X_address, jint IH, jint IW, jlong W_address, jint
+    FH, jint FW, jlong Y_address, jint OH, jint OW, jint N, jint IC, jint OC, jint sh, jint sw)
+{
+    Streams st = get_streams(env, streamArray, length);
+    raise(env, alpha_Cuda_conv3D_conv3D_np(st.v, st.n, fp(X_address), IH, IW, fp(W_address), FH,
+    FW, fp(Y_address), OH, OW, N, IC, OC, sh, sw));
+}
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1conv3D_conv3D_1W1(JNIEnv* env, jclass,
+    jlongArray streamArray, jint length, jlong X_address, jint IH, jint IW, jlong W_address, jlong
+    Y_address, jint N, jint IC, jint OC)
+{
+    Streams st = get_streams(env, streamArray, length);
+    raise(env, alpha_Cuda_conv3D_conv3D_W1(st.v, st.n, fp(X_address), IH, IW, fp(W_address),
+    fp(Y_address), N, IC, OC));
+}
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1conv3D_kernel_1remode(JNIEnv* env, jclass,
+    jlong stream_address, jlong W_address, jlong CW_address, jint FH, jint FW, jint OC, jint IC)
+{
+    raise(env, alpha_Cuda_conv3D_kernel_remode(stream_address, fp(W_address), fp(CW_address), FH,
+    FW, OC, IC));
+}
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1conv3D_conv3D_1GemmR(JNIEnv* env, jclass,
+    jlongArray streamArray, jint length, jlong X_address, jint IH, jint IW, jlong W_address, jlong
+    CW_address, jint FH, jint FW, jlong Y_address, jint OH, jint OW, jint N, jint IC, jint OC,
+    jint sh, jint sw, jint ph, jint pw)
+{
+    Streams st = get_streams(env, streamArray, length);
+    raise(env, alpha_Cuda_conv3D_conv3D_GemmR(st.v, st.n, fp(X_address), IH, IW, fp(W_address),
+    fp(CW_address), FH, FW, fp(Y_address), OH, OW, N, IC, OC, sh, sw, ph, pw));
+}
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1conv3D_conv3D_1GemmR_1texture(JNIEnv* env, jclass,
+    jlongArray streamArray, jint length, jlong X_address, jint IH, jint IW, jlong W_address, jlong
+    CW_address, jint FH, jint FW, jlong Y_address, jint OH, jint OW, jint N, jint IC, jint OC,
+    jint sh, jint sw, jint ph, jint pw)
+{
+    Streams st = get_streams(env, streamArray, length);
+    raise(env, alpha_Cuda_conv3D_conv3D_GemmR_texture(st.v, st.n, fp(X_address), IH, IW,
+    fp(W_address), fp(CW_address), FH, FW, fp(Y_address), OH, OW, N, IC, OC, sh, sw, ph, pw));
+}
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1conv3D_conv3D_1GemmV2R(JNIEnv* env, jclass,
+    jboolean useTexture, jlongArray streamArray, jint length, jlong X_address, jint IH, jint IW,
+    jlong W_address, jlong CW_address, jint FH, jint FW, jlong Y_address, jint OH, jint OW, jint
+    N, jint IC, jint OC, jint sh, jint sw, jint ph, jint pw)
+{
+    Streams st = get_streams(env, streamArray, length);
+    raise(env, alpha_Cuda_conv3D_conv3D_GemmV2R(useTexture ? 1 : 0, st.v, st.n, fp(X_address), IH,
+    IW, fp(W_address), fp(CW_address), FH, FW, fp(Y_address), OH, OW, N, IC, OC, sh, sw, ph, pw));
+}
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1conv3D_conv3D_1GemmR_1W1(JNIEnv* env, jclass,
+    jlongArray streamArray, jint length, jlong X_address, jint IH, jint IW, jlong W_address, jlong
+    CW_address, jlong Y_address, jint N, jint IC, jint OC)
+{
+    Streams st = get_streams(env, streamArray, length);
+    raise(env, alpha_Cuda_conv3D_conv3D_GemmR_W1(st.v, st.n, fp(X_address), IH, IW, fp(W_address),
+    fp(CW_address), fp(Y_address), N, IC, OC));
+}
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1dconv3D_1deltaX_dconv3D_1deltaX_1s1(JNIEnv* env, jclass,
+    jlongArray streamArray, jint length, jlong deltaY_address, jint OH, jint OW, jlong W_address,
+    jint FH, jint FW, jlong deltaX_address, jint IH, jint IW, jint N, jint IC, jint OC, jint ph,
+    jint pw)
+{
+    Streams st = get_streams(env, streamArray, length);
+    raise(env, alpha_Cuda_dconv3D_deltaX_dconv3D_deltaX_s1(st.v, st.n, fp(deltaY_address), OH, OW,
+    fp(W_address), FH, FW, fp(deltaX_address), IH, IW, N, IC, OC, ph, pw));
+}
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1dconv3D_1deltaX_dconv3D_1deltaX_1s1_1texture(JNIEnv* env, jclass,
+    jlongArray streamArray, jint length, jlong deltaY_address, jint OH, jint OW, jlong W_address,
+    jint FH, jint FW, jlong deltaX_address, jint IH, jint IW, jint N, jint IC, jint OC, jint ph,
+    jint pw)
+{
+    Streams st = get_streams(env, streamArray, length);
+    raise(env, alpha_Cuda_dconv3D_deltaX_dconv3D_deltaX_s1_texture(st.v, st.n, fp(deltaY_address),
+    OH, OW, fp(W_address), FH, FW, fp(deltaX_address), IH, IW, N, IC, OC, ph, pw));
+}
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1dconv3D_1deltaX_dconv3D_1deltaX_1V2_1s1(JNIEnv* env, jclass,
+    jboolean useTexture, jlongArray streamArray, jint length, jlong deltaY_address, jint OH, jint
+    OW, jlong W_address, jint FH, jint FW, jlong deltaX_address, jint IH, jint IW, jint N, jint
+    IC, jint OC, jint ph, jint pw)
+{
+    Streams st = get_streams(env, streamArray, length);
+    raise(env, alpha_Cuda_dconv3D_deltaX_dconv3D_deltaX_V2_s1(useTexture ? 1 : 0, st.v, st.n,
+    fp(deltaY_address), OH, OW, fp(W_address), FH, FW, fp(deltaX_address), IH, IW, N, IC, OC, ph,
+    pw));
+}
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1dconv3D_1deltaX_dconv3D_1deltaX_1W1(JNIEnv* env, jclass,
+    jlongArray streamArray, jint length, jlong deltaY_address, jlong W_address, jlong
+    deltaX_address, jint IH, jint IW, jint N, jint IC, jint OC)
+{
+    Streams st = get_streams(env, streamArray, length);
+    raise(env, alpha_Cuda_dconv3D_deltaX_dconv3D_deltaX_W1(st.v, st.n, fp(deltaY_address),
+    fp(W_address), fp(deltaX_address), IH, IW, N, IC, OC));
+}
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1dconv3D_1deltaX_ks_1remode(JNIEnv* env, jclass,
+    jlong stream_address, jlong W_address, jint FH, jint FW, jlong CW_address, jint CFH, jint CFW,
+    jint OC, jint IC, jint sh, jint sw)
+{
+    raise(env, alpha_Cuda_dconv3D_deltaX_ks_remode(stream_address, fp(W_address), FH, FW,
+    fp(CW_address), CFH, CFW, OC, IC, sh, sw));
+}
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1dconv3D_1deltaX_ks_1remodev2(JNIEnv* env, jclass,
+    jlong stream_address, jlong W_address, jint FH, jint FW, jlong CW_address, jint CFH, jint CFW,
+    jint OC, jint IC, jint sh, jint sw)
+{
+    raise(env, alpha_Cuda_dconv3D_deltaX_ks_remodev2(stream_address, fp(W_address), FH, FW,
+    fp(CW_address), CFH, CFW, OC, IC, sh, sw));
+}
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1dconv3D_1deltaX_dconv3D_1deltaX_1kernelSplit(JNIEnv* env, jclass,
+    jlongArray streamArray, jint length, jlong deltaY_address, jint OH, jint OW, jlong CW_address,
+    jint FH, jint FW, jlong deltaX_address, jint IH, jint IW, jint N, jint IC, jint OC, jint sh,
+    jint sw, jint ph, jint pw)
+{
+    Streams st = get_streams(env, streamArray, length);
+    raise(env, alpha_Cuda_dconv3D_deltaX_dconv3D_deltaX_kernelSplit(st.v, st.n,
+    fp(deltaY_address), OH, OW, fp(CW_address), FH, FW, fp(deltaX_address), IH, IW, N, IC, OC, sh,
+    sw, ph, pw));
+}
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1dconv3D_1deltaX_dconv3D_1deltaX_1ksImsR(JNIEnv* env, jclass,
+    jlongArray streamArray, jint length, jlong deltaY_address, jint OH, jint OW, jlong CW_address,
+    jint FH, jint FW, jlong deltaX_address, jint IH, jint IW, jint N, jint IC, jint OC, jint sh,
+    jint sw, jint ph, jint pw)
+{
+    Streams st = get_streams(env, streamArray, length);
+    raise(env, alpha_Cuda_dconv3D_deltaX_dconv3D_deltaX_ksImsR(st.v, st.n, fp(deltaY_address), OH,
+    OW, fp(CW_address), FH, FW, fp(deltaX_address), IH, IW, N, IC, OC, sh, sw, ph, pw));
+}
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1dconv3D_1deltaX_dconv3D_1deltaX_1ksImsR_1texture(JNIEnv* env, jclass,
+    jlongArray streamArray, jint length, jlong deltaY_address, jint OH, jint OW, jlong CW_address,
+    jint FH, jint FW, jlong deltaX_address, jint IH, jint IW, jint N, jint IC, jint OC, jint sh,
+    jint sw, jint ph, jint pw)
+{
+    Streams st = get_streams(env, streamArray, length);
+    raise(env, alpha_Cuda_dconv3D_deltaX_dconv3D_deltaX_ksImsR_texture(st.v, st.n,
+    fp(deltaY_address), OH, OW, fp(CW_address), FH, FW, fp(deltaX_address), IH, IW, N, IC, OC, sh,
+    sw, ph, pw));
+}
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1dconv3D_1deltaX_dconv3D_1deltaX_1ksIms2R(JNIEnv* env, jclass,
+    jlongArray streamArray, jint length, jlong deltaY_address, jint OH, jint OW, jlong CW_address,
+    jint FH, jint FW, jlong deltaX_address, jint IH, jint IW, jint N, jint IC, jint OC, jint ph,
+    jint pw)
+{
+    Streams st = get_streams(env, streamArray, length);
+    raise(env, alpha_Cuda_dconv3D_deltaX_dconv3D_deltaX_ksIms2R(st.v, st.n, fp(deltaY_address),
+    OH, OW, fp(CW_address), FH, FW, fp(deltaX_address), IH, IW, N, IC, OC, ph, pw));
+}
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1dconv3D_1deltaX_dconv3D_1deltaX_1ksIms2R_1texture(JNIEnv* env, jclass,
+    jlongArray streamArray, jint length, jlong deltaY_address, jint OH, jint OW, jlong CW_address,
+    jint FH, jint FW, jlong deltaX_address, jint IH, jint IW, jint N, jint IC, jint OC, jint ph,
+    jint pw)
+{
+    Streams st = get_streams(env, streamArray, length);
+    raise(env, alpha_Cuda_dconv3D_deltaX_dconv3D_deltaX_ksIms2R_texture(st.v, st.n,
+    fp(deltaY_address), OH, OW, fp(CW_address), FH, FW, fp(deltaX_address), IH, IW, N, IC, OC, ph,
+    pw));
+}
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1dconv3D_1deltaX_dconv3D_1deltaX_1ksV2_1Ims2R(JNIEnv* env, jclass,
+    jboolean useTexture, jlongArray streamArray, jint length, jlong deltaY_address, jint OH, jint
+    OW, jlong CW_address, jint FH, jint FW, jlong deltaX_address, jint IH, jint IW, jint N, jint
+    IC, jint OC, jint ph, jint pw)
+{
+    Streams st = get_streams(env, streamArray, length);
+    raise(env, alpha_Cuda_dconv3D_deltaX_dconv3D_deltaX_ksV2_Ims2R(useTexture ? 1 : 0, st.v, st.n,
+    fp(deltaY_address), OH, OW, fp(CW_address), FH, FW, fp(deltaX_address), IH, IW, N, IC, OC, ph,
+    pw));
+}
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1dconv3D_1deltaX_dconv3D_1deltaX_1crossAdd(JNIEnv* env, jclass,
+    jlongArray streamArray, jint length, jlong deltaY_address, jint OH, jint OW, jlong W_address,
+    jint FH, jint FW, jlong deltaX_address, jint IH, jint IW, jint N, jint IC, jint OC, jint sh,
+    jint sw, jint ph, jint pw)
+{
+    Streams st = get_streams(env, streamArray, length);
+    raise(env, alpha_Cuda_dconv3D_deltaX_dconv3D_deltaX_crossAdd(st.v, st.n, fp(deltaY_address),
+    OH, OW, fp(W_address), FH, FW, fp(deltaX_address), IH, IW, N, IC, OC, sh, sw, ph, pw));
+}
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1dconv3D_1deltaW_dconv3D_1deltaW(JNIEnv* env, jclass,
+    jlongArray streamArray, jint length, jlong X_address, jint IH, jint IW, jlong deltaY_address,
+    jint OH, jint OW, jlong deltaW_address, jint FH, jint FW, jint N, jint IC, jint OC, jint sh,
+    jint sw, jint ph, jint pw)
+{
+    Streams st = get_streams(env, streamArray, length);
+    raise(env, alpha_Cuda_dconv3D_deltaW_dconv3D_deltaW(st.v, st.n, fp(X_address), IH, IW,
+    fp(deltaY_address), OH, OW, fp(deltaW_address), FH, FW, N, IC, OC, sh, sw, ph, pw));
+}
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1dconv3D_1deltaW_dconv3D_1deltaW_1W1(JNIEnv* env, jclass,
+    jlongArray streamArray, jint length, jlong X_address, jint IH, jint IW, jlong deltaY_address,
+    jlong deltaW_address, jint N, jint IC, jint OC)
+{
+    Streams st = get_streams(env, streamArray, length);
+    raise(env, alpha_Cuda_dconv3D_deltaW_dconv3D_deltaW_W1(st.v, st.n, fp(X_address), IH, IW,
+    fp(deltaY_address), fp(deltaW_address), N, IC, OC));
+}
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1dconv3D_1deltaW_buf_1summary(JNIEnv* env, jclass,
+    jlong stream_address, jlong deltaW_buf_address, jlong deltaW_address, jint part, jint sizeW)
+{
+    raise(env, alpha_Cuda_dconv3D_deltaW_buf_summary(stream_address, fp(deltaW_buf_address),
+    fp(deltaW_address), part, sizeW));
+}
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1dconv3D_1deltaW_dconv3D_1deltaW_1GemmSK(JNIEnv* env, jclass,
+    jlongArray streamArray, jint length, jint GridZ, jlong X_address, jint IH, jint IW, jlong
+    deltaY_address, jint OH, jint OW, jlong deltaW_address, jlong deltaW_buf_address, jint FH,
+    jint FW, jint N, jint IC, jint OC, jint sh, jint sw, jint ph, jint pw)
+{
+    Streams st = get_streams(env, streamArray, length);
+    raise(env, alpha_Cuda_dconv3D_deltaW_dconv3D_deltaW_GemmSK(st.v, st.n, GridZ, fp(X_address),
+    IH, IW, fp(deltaY_address), OH, OW, fp(deltaW_address), fp(deltaW_buf_address), FH, FW, N, IC,
+    OC, sh, sw, ph, pw));
+}
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1dconv3D_1deltaW_dconv3D_1deltaW_1GemmV2SK(JNIEnv* env, jclass,
+    jlongArray streamArray, jint length, jint GridZ, jlong X_address, jint IH, jint IW, jlong
+    deltaY_address, jint OH, jint OW, jlong deltaW_address, jlong deltaW_buf_address, jint FH,
+    jint FW, jint N, jint IC, jint OC, jint sh, jint sw, jint ph, jint pw)
+{
+    Streams st = get_streams(env, streamArray, length);
+    raise(env, alpha_Cuda_dconv3D_deltaW_dconv3D_deltaW_GemmV2SK(st.v, st.n, GridZ, fp(X_address),
+    IH, IW, fp(deltaY_address), OH, OW, fp(deltaW_address), fp(deltaW_buf_address), FH, FW, N, IC,
+    OC, sh, sw, ph, pw));
+}
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1dconv3D_1deltaW_dconv3D_1deltaW_1GemmSK_1W1(JNIEnv* env, jclass,
+    jlongArray streamArray, jint length, jint GridZ, jlong X_address, jint IH, jint IW, jlong
+    deltaY_address, jlong deltaW_address, jlong deltaW_buf_address, jint N, jint IC, jint OC)
+{
+    Streams st = get_streams(env, streamArray, length);
+    raise(env, alpha_Cuda_dconv3D_deltaW_dconv3D_deltaW_GemmSK_W1(st.v, st.n, GridZ,
+    fp(X_address), IH, IW, fp(deltaY_address), fp(deltaW_address), fp(deltaW_buf_address), N, IC,
+    OC));
+}
+
+}  // extern "C"

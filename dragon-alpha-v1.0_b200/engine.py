@@ -1,0 +1,234 @@
+"""Host-side mirror of the conv section of Dragon-Alpha's CudaFloat32EngineBase.
+
+`CudaFloat32EngineBase` keeps the reference's address-level operator methods (same names, same
+argument order, same option setters and the same IllegalArgument checks, raised as ValueError):
+src/alpha_src/z/dragon/engine/cuda/CudaFloat32EngineBase.java:1322-2007.  `Engine` adds the
+tensor-level calls with the shape inference of src/alpha_src/z/dragon/engine/Engine.java:1541-1829
+and the pad-to-4 memory rule of src/alpha_src/z/dragon/engine/Tensor.java:208-221.
+
+PyTorch only provides device memory and streams here; every contraction runs in
+libalpha_conv_b200.so.  There is no CPU or PyTorch fallback: a missing library raises ImportError.
+"""
+import ctypes as C
+
+import torch
+
+from . import lib as _l
+
+
+def _ptr(t):
+    return C.c_void_p(t.data_ptr())
+
+
+def _stream(stream=None):
+    s = stream if stream is not None else torch.cuda.current_stream()
+    return C.c_void_p(s.cuda_stream)
+
+
+class CudaFloat32EngineBase:
+    """Address-level operators.  Arguments are device addresses (ints) or torch CUDA tensors."""
+
+    def __init__(self, stream=None):
+        self._lib = _l.load()
+        self._stream = stream
+        # option flags of the reference; they chose among SIMT kernel families there and are kept
+        # for API compatibility (every family maps onto the same tensor-core kernel here).
+        self._conv3D_useTexture = True
+        self._conv3D_remode = True
+        self._conv3D_remode_V2_Q = 1.05
+        self._conv3D_V2_Q = 1.25
+        self._dW_SplitKThreshold = 512
+        self._dW_SK_MaxPartNum = 16
+        self._dW_SK_V2_Q = 1.15
+        self._dX_s1_useTexture = True
+        self._dX_ks_useTexture = False
+        self._dX_ks_V2_Q = 1.1
+        self._dX_s1_V2_Q = 1.1
+
+    # ---- fluent option setters (CudaFloat32EngineBase.java:1324-1352, 1630-1663, 1765-1793) ----
+    def conv3D_useTexture(self, flag=None):
+        if flag is None:
+            return self._conv3D_useTexture
+        self._conv3D_useTexture = bool(flag)
+        return self
+
+    def conv3D_remode(self, flag=None):
+        if flag is None:
+            return self._conv3D_remode
+        self._conv3D_remode = bool(flag)
+        return self
+
+    def conv3D_remode_V2_Q(self, Q=None):
+        if Q is None:
+            return self._conv3D_remode_V2_Q
+        if Q < 1.04999:
+            raise ValueError("Q must >= 1.05")
+        self._conv3D_remode_V2_Q = float(Q)
+        return self
+
+    def conv3D_V2_Q(self, Q=None):
+        if Q is None:
+            return self._conv3D_V2_Q
+        if Q < 1.09999:
+            raise ValueError("Q must >= 1.1")
+        self._conv3D_V2_Q = float(Q)
+        return self
+
+    def dconv3D_deltaW_SplitKThreshold(self, threshold=None):
+        if threshold is None:
+            return self._dW_SplitKThreshold
+        if threshold & (threshold - 1):
+            raise ValueError("threshold must be a power of 2")
+        if threshold < 256:
+            raise ValueError("threshold must >= 256")
+        self._dW_SplitKThreshold = int(threshold)
+        return self
+
+    def dconv3D_deltaW_SK_MaxPartNum(self, maxPartNum=None):
+        if maxPartNum is None:
+            return self._dW_SK_MaxPartNum
+        if maxPartNum < 4:
+            raise ValueError("maxPartNum must >= 4")
+        self._dW_SK_MaxPartNum = int(maxPartNum)
+        return self
+
+    def dconv3DdeltaW_SK_V2_Q(self, Q=None):
+        if Q is None:
+            return self._dW_SK_V2_Q
+        if Q < 1.1:
+            raise ValueError("Q >= 1.1")
+        self._dW_SK_V2_Q = float(Q)
+        return self
+
+    def dconv3D_deltaX_s1_useTexture(self, flag=None):
+        if flag is None:
+            return self._dX_s1_useTexture
+        self._dX_s1_useTexture = bool(flag)
+        return self
+
+    def dconv3D_deltaX_ks_useTexture(self, flag=None):
+        if flag is None:
+            return self._dX_ks_useTexture
+        self._dX_ks_useTexture = bool(flag)
+        return self
+
+    # ---- operators ------------------------------------------------------------------------------
+    @staticmethod
+    def _addr(a):
+        return C.c_void_p(a.data_ptr()) if isinstance(a, torch.Tensor) else C.c_void_p(int(a))
+
+    def conv3D(self, Y_address, OH, OW, X_address, IH, IW, W_address, FH, FW, N, IC, OC, sh, sw, ph, pw):
+        """CudaFloat32EngineBase.conv3D (:1355-1474)."""
+        a = self._addr
+        _l.check(self._lib.alpha_engine_conv3D(a(Y_address), OH, OW, a(X_address), IH, IW, a(W_address),
+                                               FH, FW, N, IC, OC, sh, sw, ph, pw, _stream(self._stream)))
+
+    def conv3D_biased(self, Y_address, OH, OW, X_address, IH, IW, W_address, FH, FW, Bias_address, N, IC,
+                      OC, sh, sw, ph, pw):
+        """CudaFloat32EngineBase.conv3D_biased (:1478-1627); the bias add is fused in the epilogue."""
+        a = self._addr
+        _l.check(self._lib.alpha_engine_conv3D_biased(a(Y_address), OH, OW, a(X_address), IH, IW,
+                                                      a(W_address), FH, FW, a(Bias_address), N, IC, OC,
+                                                      sh, sw, ph, pw, _stream(self._stream)))
+
+    def dconv3D_deltaW(self, deltaW_address, FH, FW, X_address, IH, IW, deltaY_address, OH, OW, N, IC, OC,
+                       sh, sw, ph, pw):
+        """CudaFloat32EngineBase.dconv3D_deltaW (:1666-1762)."""
+        a = self._addr
+        _l.check(self._lib.alpha_engine_dconv3D_deltaW(a(deltaW_address), FH, FW, a(X_address), IH, IW,
+                                                       a(deltaY_address), OH, OW, N, IC, OC, sh, sw, ph,
+                                                       pw, _stream(self._stream)))
+
+    def dconv3D_deltaX(self, deltaX_address, IH, IW, deltaY_address, OH, OW, W_address, FH, FW, N, IC, OC,
+                       sh, sw, ph, pw):
+        """CudaFloat32EngineBase.dconv3D_deltaX (:1796-2005)."""
+        a = self._addr
+        _l.check(self._lib.alpha_engine_dconv3D_deltaX(a(deltaX_address), IH, IW, a(deltaY_address), OH,
+                                                       OW, a(W_address), FH, FW, N, IC, OC, sh, sw, ph,
+                                                       pw, _stream(self._stream)))
+
+
+def _pad4(n):
+    return (n + 3) & ~3
+
+
+def _pad_last(t, c4):
+    """Copy of t whose last dimension is zero-padded to c4 (Tensor.java:208-221 memory rule)."""
+    if t.shape[-1] == c4:
+        return t.contiguous()
+    out = torch.zeros(t.shape[:-1] + (c4,), dtype=t.dtype, device=t.device)
+    out[..., : t.shape[-1]] = t
+    return out
+
+
+def _pad_first(t, n4):
+    if t.shape[0] == n4:
+        return t
+    out = torch.zeros((n4,) + t.shape[1:], dtype=t.dtype, device=t.device)
+    out[: t.shape[0]] = t
+    return out
+
+
+class Engine:
+    """Tensor-level conv operators (Engine.java:1541, 1601, 1697, 1788) on torch CUDA tensors.
+
+    Tensors are NHWC float32.  Channel counts and the batch that are not multiples of 4 are padded
+    with zero lanes exactly as Dragon-Alpha's Tensor memory layout does, and sliced back.
+    """
+
+    def __init__(self, base=None):
+        self.base = base if base is not None else CudaFloat32EngineBase()
+
+    @staticmethod
+    def out_size(IH, IW, FH, FW, sh, sw, ph, pw):
+        return (IH - FH + 2 * ph) // sh + 1, (IW - FW + 2 * pw) // sw + 1
+
+    def conv3D(self, X, W, sh, sw, ph, pw, Bias=None):
+        N, IH, IW, IC = X.shape
+        OC, FH, FW, WIC = W.shape
+        if WIC != IC:
+            raise ValueError("W.IC=%d != X.IC=%d" % (WIC, IC))
+        OH, OW = self.out_size(IH, IW, FH, FW, sh, sw, ph, pw)
+        ic4, oc4 = _pad4(IC), _pad4(OC)
+        Xp = _pad_last(X, ic4)
+        Wp = _pad_first(_pad_last(W, ic4), oc4)
+        Y = torch.empty((N, OH, OW, oc4), dtype=torch.float32, device=X.device)
+        if Bias is None:
+            self.base.conv3D(Y, OH, OW, Xp, IH, IW, Wp, FH, FW, N, ic4, oc4, sh, sw, ph, pw)
+        else:
+            Bp = _pad_last(Bias.reshape(1, -1), oc4).reshape(-1)
+            self.base.conv3D_biased(Y, OH, OW, Xp, IH, IW, Wp, FH, FW, Bp, N, ic4, oc4, sh, sw, ph, pw)
+        return Y if oc4 == OC else Y[..., :OC]
+
+    def conv3D_biased(self, X, W, Bias, sh, sw, ph, pw):
+        return self.conv3D(X, W, sh, sw, ph, pw, Bias=Bias)
+
+    def dconv3D_deltaW(self, X, deltaY, FH, FW, sh, sw, ph, pw):
+        N, IH, IW, IC = X.shape
+        _, OH, OW, OC = deltaY.shape
+        ic4, oc4 = _pad4(IC), _pad4(OC)
+        Xp, dYp = _pad_last(X, ic4), _pad_last(deltaY, oc4)
+        dW = torch.empty((oc4, FH, FW, ic4), dtype=torch.float32, device=X.device)
+        self.base.dconv3D_deltaW(dW, FH, FW, Xp, IH, IW, dYp, OH, OW, N, ic4, oc4, sh, sw, ph, pw)
+        return dW if (ic4 == IC and oc4 == OC) else dW[:OC, :, :, :IC]
+
+    def dconv3D_deltaX(self, deltaY, W, IH, IW, sh, sw, ph, pw):
+        N, OH, OW, OC = deltaY.shape
+        _, FH, FW, IC = W.shape
+        ic4, oc4 = _pad4(IC), _pad4(OC)
+        dYp = _pad_last(deltaY, oc4)
+        Wp = _pad_first(_pad_last(W, ic4), oc4)
+        dX = torch.empty((N, IH, IW, ic4), dtype=torch.float32, device=deltaY.device)
+        self.base.dconv3D_deltaX(dX, IH, IW, dYp, OH, OW, Wp, FH, FW, N, ic4, oc4, sh, sw, ph, pw)
+        return dX if ic4 == IC else dX[..., :IC]
+
+    def dconv3D(self, X, W, sh, sw, ph, pw, OH=None, OW=None):
+        """Deconv3D forward = dconv3D_deltaX with the roles of input and output swapped
+        (Engine.java:1819-1829); W is [IC_in, FH, FW, OC_out]."""
+        N, IH, IW, _ = X.shape
+        _, FH, FW, _ = W.shape
+        if OH is None:
+            OH = (IH - 1) * sh + FH - 2 * ph
+        if OW is None:
+            OW = (IW - 1) * sw + FW - 2 * pw
+        return self.dconv3D_deltaX(X, W, OH, OW, sh, sw, ph, pw)

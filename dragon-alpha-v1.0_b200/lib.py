@@ -1,0 +1,120 @@
+"""ctypes binding of libalpha_conv_b200.so (the C ABI declared in include/alpha_conv_b200.h)."""
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libalpha_conv_b200.so")
+
+ALPHA_MATH_3XTF32, ALPHA_MATH_TF32 = 0, 1
+ALPHA_ALGO_AUTO, ALPHA_ALGO_TENSOR, ALPHA_ALGO_SIMT, ALPHA_ALGO_WINOGRAD = 0, 1, 2, 3
+
+
+class AlphaConvShape(C.Structure):
+    _fields_ = [(n, C.c_int) for n in
+                ("N", "IH", "IW", "IC", "OC", "FH", "FW", "OH", "OW", "sh", "sw", "ph", "pw")]
+
+
+class AlphaConvError(RuntimeError):
+    """A call into the library returned a non-zero status; .code holds the ALPHA_E_* value."""
+
+    def __init__(self, code, message):
+        super().__init__("alpha_conv_b200 error %d: %s" % (code, message))
+        self.code = code
+
+
+_lib = None
+
+
+def load():
+    """Loads the shared library; raises if it has not been built (there is no fallback path)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ImportError("%s is missing: run __graft_entry__.build() (nvcc, sm_100a) first" % LIB_PATH)
+    lib = C.CDLL(LIB_PATH)
+    lib.alpha_conv_last_error.restype = C.c_char_p
+    lib.alpha_conv_last_algo.restype = C.c_char_p
+    lib.alpha_conv_launch_count.restype = C.c_ulonglong
+    P, V, I, L = C.POINTER(AlphaConvShape), C.c_void_p, C.c_int, C.c_int64
+    lib.alpha_conv3d_forward.argtypes = [P, V, V, V, V, V]
+    lib.alpha_conv3d_deltaX.argtypes = [P, V, V, V, V]
+    lib.alpha_conv3d_deltaW.argtypes = [P, V, V, V, V]
+    lib.alpha_engine_conv3D.argtypes = [V, I, I, V, I, I, V, I, I] + [I] * 7 + [V]
+    lib.alpha_engine_conv3D_biased.argtypes = [V, I, I, V, I, I, V, I, I, V] + [I] * 7 + [V]
+    lib.alpha_engine_dconv3D_deltaW.argtypes = [V, I, I, V, I, I, V, I, I] + [I] * 7 + [V]
+    lib.alpha_engine_dconv3D_deltaX.argtypes = [V, I, I, V, I, I, V, I, I] + [I] * 7 + [V]
+    SA = C.POINTER(C.c_int64)
+    # Cuda_conv3D natives
+    conv = [SA, I, V, I, I, V, I, I, V, I, I] + [I] * 7
+    lib.alpha_Cuda_conv3D_conv3D.argtypes = conv
+    lib.alpha_Cuda_conv3D_conv3D_texture.argtypes = conv
+    lib.alpha_Cuda_conv3D_conv3DV2.argtypes = [I] + conv
+    lib.alpha_Cuda_conv3D_conv3D_np.argtypes = [SA, I, V, I, I, V, I, I, V, I, I] + [I] * 5
+    lib.alpha_Cuda_conv3D_conv3D_W1.argtypes = [SA, I, V, I, I, V, V, I, I, I]
+    lib.alpha_Cuda_conv3D_kernel_remode.argtypes = [L, V, V, I, I, I, I]
+    convR = [SA, I, V, I, I, V, V, I, I, V, I, I] + [I] * 7
+    lib.alpha_Cuda_conv3D_conv3D_GemmR.argtypes = convR
+    lib.alpha_Cuda_conv3D_conv3D_GemmR_texture.argtypes = convR
+    lib.alpha_Cuda_conv3D_conv3D_GemmV2R.argtypes = [I] + convR
+    lib.alpha_Cuda_conv3D_conv3D_GemmR_W1.argtypes = [SA, I, V, I, I, V, V, V, I, I, I]
+    # Cuda_dconv3D_deltaX natives
+    dxs1 = [SA, I, V, I, I, V, I, I, V, I, I] + [I] * 5
+    lib.alpha_Cuda_dconv3D_deltaX_dconv3D_deltaX_s1.argtypes = dxs1
+    lib.alpha_Cuda_dconv3D_deltaX_dconv3D_deltaX_s1_texture.argtypes = dxs1
+    lib.alpha_Cuda_dconv3D_deltaX_dconv3D_deltaX_V2_s1.argtypes = [I] + dxs1
+    lib.alpha_Cuda_dconv3D_deltaX_dconv3D_deltaX_W1.argtypes = [SA, I, V, V, V, I, I, I, I, I]
+    rem = [L, V, I, I, V, I, I, I, I, I, I]
+    lib.alpha_Cuda_dconv3D_deltaX_ks_remode.argtypes = rem
+    lib.alpha_Cuda_dconv3D_deltaX_ks_remodev2.argtypes = rem
+    dxks = [SA, I, V, I, I, V, I, I, V, I, I] + [I] * 7
+    lib.alpha_Cuda_dconv3D_deltaX_dconv3D_deltaX_kernelSplit.argtypes = dxks
+    lib.alpha_Cuda_dconv3D_deltaX_dconv3D_deltaX_ksImsR.argtypes = dxks
+    lib.alpha_Cuda_dconv3D_deltaX_dconv3D_deltaX_ksImsR_texture.argtypes = dxks
+    lib.alpha_Cuda_dconv3D_deltaX_dconv3D_deltaX_ksIms2R.argtypes = dxs1
+    lib.alpha_Cuda_dconv3D_deltaX_dconv3D_deltaX_ksIms2R_texture.argtypes = dxs1
+    lib.alpha_Cuda_dconv3D_deltaX_dconv3D_deltaX_ksV2_Ims2R.argtypes = [I] + dxs1
+    lib.alpha_Cuda_dconv3D_deltaX_dconv3D_deltaX_crossAdd.argtypes = dxks
+    # Cuda_dconv3D_deltaW natives
+    lib.alpha_Cuda_dconv3D_deltaW_dconv3D_deltaW.argtypes = [SA, I, V, I, I, V, I, I, V, I, I] + [I] * 7
+    lib.alpha_Cuda_dconv3D_deltaW_dconv3D_deltaW_W1.argtypes = [SA, I, V, I, I, V, V, I, I, I]
+    lib.alpha_Cuda_dconv3D_deltaW_buf_summary.argtypes = [L, V, V, I, I]
+    sk = [SA, I, I, V, I, I, V, I, I, V, V, I, I] + [I] * 7
+    lib.alpha_Cuda_dconv3D_deltaW_dconv3D_deltaW_GemmSK.argtypes = sk
+    lib.alpha_Cuda_dconv3D_deltaW_dconv3D_deltaW_GemmV2SK.argtypes = sk
+    lib.alpha_Cuda_dconv3D_deltaW_dconv3D_deltaW_GemmSK_W1.argtypes = [SA, I, I, V, I, I, V, V, V, I, I, I]
+    _lib = lib
+    return lib
+
+
+def check(rc):
+    if rc != 0:
+        raise AlphaConvError(rc, load().alpha_conv_last_error().decode("utf-8", "replace"))
+
+
+def last_error():
+    return load().alpha_conv_last_error().decode("utf-8", "replace")
+
+
+def last_algo():
+    return load().alpha_conv_last_algo().decode()
+
+
+def launch_count():
+    return int(load().alpha_conv_launch_count())
+
+
+def set_math_mode(mode):
+    """mode: '3xtf32' (default, fp32-faithful) or 'tf32'."""
+    m = {"3xtf32": ALPHA_MATH_3XTF32, "tf32": ALPHA_MATH_TF32}.get(mode, mode)
+    check(load().alpha_conv_set_math_mode(int(m)))
+
+
+def set_algo(algo):
+    a = {"auto": 0, "tensor": 1, "simt": 2, "winograd": 3}.get(algo, algo)
+    check(load().alpha_conv_set_algo(int(a)))
+
+
+def device_status():
+    """Synchronises the device and returns its kernel status word (0 = clean)."""
+    return int(load().alpha_conv_device_status())

@@ -1,0 +1,236 @@
+/*
+ * alpha_conv_b200 - C ABI of the B200 (sm_100a) convolution library for Dragon-Alpha.
+ *
+ * Three layers, all `extern "C"`, plain pointers and sizes:
+ *
+ *   1. alpha_conv3d_*            one call per contraction (forward, deltaX, deltaW); everything
+ *                                above is a thin wrapper over these.
+ *   2. alpha_Cuda_*              one function per `static native` of the reference's three JNI
+ *                                classes, same argument order minus (JNIEnv*, jclass); the JNI shim
+ *                                (Java_z_dragon_engine_cuda_impl_math_Cuda_1*) unpacks the stream
+ *                                array and forwards here.
+ *   3. alpha_engine_*            the four operator methods of CudaFloat32EngineBase that own this
+ *                                path (conv3D, conv3D_biased, dconv3D_deltaW, dconv3D_deltaX) in
+ *                                the Java argument order.
+ *
+ * Tensors are fp32, C-contiguous NHWC: X[N,IH,IW,IC], W[OC,FH,FW,IC], Y[N,OH,OW,OC]; deltaX,
+ * deltaY, deltaW are laid out like X, Y, W.  N, IC and OC arrive rounded up to a multiple of 4 with
+ * zero-filled padding lanes (src/alpha_src/z/dragon/engine/EngineCore.java:697-699), device
+ * pointers are 16-byte aligned.  Every call only enqueues work on the given stream and returns; it
+ * never synchronises.  All functions return 0 on success or a negative ALPHA_E_* code;
+ * alpha_conv_last_error() gives the message of the calling thread's last failure.
+ */
+#ifndef ALPHA_CONV_B200_H
+#define ALPHA_CONV_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ALPHA_OK 0
+#define ALPHA_E_ARG (-1)      /* bad shape, null or misaligned pointer */
+#define ALPHA_E_CUDA (-2)     /* a CUDA runtime or driver call failed */
+#define ALPHA_E_DEVICE (-3)   /* not an sm_100 device */
+#define ALPHA_E_KERNEL (-4)   /* a kernel reported a protocol error in its status word */
+
+/* math mode of the tensor-core kernels */
+#define ALPHA_MATH_3XTF32 0 /* default: hi/lo split, three TF32 MMAs per product, fp32-faithful */
+#define ALPHA_MATH_TF32 1   /* opt-in: one TF32 MMA per product */
+
+/* kernel family */
+#define ALPHA_ALGO_AUTO 0  /* tensor path where the shape allows it, plain fp32 kernels elsewhere */
+#define ALPHA_ALGO_TENSOR 1 /* tensor path or ALPHA_E_ARG */
+#define ALPHA_ALGO_SIMT 2   /* plain fp32 kernels */
+#define ALPHA_ALGO_WINOGRAD 3 /* forward 3x3 stride 1 only: Winograd F(2,3) */
+
+typedef struct AlphaConvShape {
+    int N, IH, IW, IC, OC, FH, FW, OH, OW, sh, sw, ph, pw;
+} AlphaConvShape;
+
+typedef void* alpha_stream_t; /* a cudaStream_t */
+
+/* ---- library state ------------------------------------------------------------------------- */
+
+const char* alpha_conv_last_error(void);
+int alpha_conv_version(void);
+/* Process-wide defaults; the environment variables ALPHA_CONV_MATH={3xtf32,tf32} and
+ * ALPHA_CONV_ALGO={auto,tensor,simt,winograd} seed them. */
+int alpha_conv_set_math_mode(int mode);
+int alpha_conv_get_math_mode(void);
+int alpha_conv_set_algo(int algo);
+int alpha_conv_get_algo(void);
+/* Reads (and clears) the current device's kernel status word; synchronises the device.
+ * 0 = every kernel so far finished its barrier protocol, otherwise the first failure code. */
+int alpha_conv_device_status(void);
+/* Number of kernel launches this library has issued from the calling process. */
+unsigned long long alpha_conv_launch_count(void);
+/* Name of the kernel family the last call of this thread used ("igemm", "dw", "simt", ...). */
+const char* alpha_conv_last_algo(void);
+
+/* ---- layer 1: one call per contraction ------------------------------------------------------ */
+
+/* Y = conv(X, W) (+ bias per output channel when bias != NULL).
+ * Replaces the kernels behind Cuda_conv3D's natives
+ * (src/cu32_src/Cuda_conv3D/Cuda_conv3D/conv3D.cuh:84-1651) and, with bias, the extra
+ * linear_dual2D_row pass of CudaFloat32EngineBase.conv3D_biased (CudaFloat32EngineBase.java:1548-1557). */
+int alpha_conv3d_forward(const AlphaConvShape* s, const float* X, const float* W, const float* bias,
+                         float* Y, alpha_stream_t stream);
+
+/* deltaX = transposed conv of deltaY with W (also Deconv3D's forward).
+ * Replaces src/cu32_src/Cuda_dconv3D_deltaX/Cuda_dconv3D_deltaX/dconv3D_dX.cuh:83-1769. */
+int alpha_conv3d_deltaX(const AlphaConvShape* s, const float* deltaY, const float* W, float* deltaX,
+                        alpha_stream_t stream);
+
+/* deltaW = correlation of X with deltaY summed over the batch.
+ * Replaces src/cu32_src/Cuda_dconv3D_deltaW/Cuda_dconv3D_deltaW/dconv3d_dW.cuh:72-700 including the
+ * split-K buffer sum (dconv3d_dW_GemmSK_bufSum.cuh:32-67).  Split-K partials live in a per-device
+ * workspace that the library allocates on first use and grows on demand. */
+int alpha_conv3d_deltaW(const AlphaConvShape* s, const float* X, const float* deltaY, float* deltaW,
+                        alpha_stream_t stream);
+
+/* ---- layer 2: the reference's natives ------------------------------------------------------- */
+/* `streams` holds `length` cudaStream_t values as 64-bit integers, as the Java side passes them;
+ * all work is enqueued on streams[0], which satisfies every Syncer the caller builds
+ * (CudaFloat32EngineBase.java:526-582, 715-796). */
+
+/* Cuda_conv3D natives: src/cu32_src/Cuda_conv3D/Cuda_conv3D/A.cu:14-244 */
+int alpha_Cuda_conv3D_conv3D(const int64_t* streams, int length, float* X, int IH, int IW, float* W,
+                             int FH, int FW, float* Y, int OH, int OW, int N, int IC, int OC, int sh,
+                             int sw, int ph, int pw);
+int alpha_Cuda_conv3D_conv3D_texture(const int64_t* streams, int length, float* X, int IH, int IW,
+                                     float* W, int FH, int FW, float* Y, int OH, int OW, int N,
+                                     int IC, int OC, int sh, int sw, int ph, int pw);
+int alpha_Cuda_conv3D_conv3DV2(int useTexture, const int64_t* streams, int length, float* X, int IH,
+                               int IW, float* W, int FH, int FW, float* Y, int OH, int OW, int N,
+                               int IC, int OC, int sh, int sw, int ph, int pw);
+int alpha_Cuda_conv3D_conv3D_np(const int64_t* streams, int length, float* X, int IH, int IW,
+                                float* W, int FH, int FW, float* Y, int OH, int OW, int N, int IC,
+                                int OC, int sh, int sw);
+int alpha_Cuda_conv3D_conv3D_W1(const int64_t* streams, int length, float* X, int IH, int IW,
+                                float* W, float* Y, int N, int IC, int OC);
+int alpha_Cuda_conv3D_kernel_remode(int64_t stream, float* W, float* CW, int FH, int FW, int OC,
+                                    int IC);
+int alpha_Cuda_conv3D_conv3D_GemmR(const int64_t* streams, int length, float* X, int IH, int IW,
+                                   float* W, float* CW, int FH, int FW, float* Y, int OH, int OW,
+                                   int N, int IC, int OC, int sh, int sw, int ph, int pw);
+int alpha_Cuda_conv3D_conv3D_GemmR_texture(const int64_t* streams, int length, float* X, int IH,
+                                           int IW, float* W, float* CW, int FH, int FW, float* Y,
+                                           int OH, int OW, int N, int IC, int OC, int sh, int sw,
+                                           int ph, int pw);
+int alpha_Cuda_conv3D_conv3D_GemmV2R(int useTexture, const int64_t* streams, int length, float* X,
+                                     int IH, int IW, float* W, float* CW, int FH, int FW, float* Y,
+                                     int OH, int OW, int N, int IC, int OC, int sh, int sw, int ph,
+                                     int pw);
+int alpha_Cuda_conv3D_conv3D_GemmR_W1(const int64_t* streams, int length, float* X, int IH, int IW,
+                                      float* W, float* CW, float* Y, int N, int IC, int OC);
+
+/* Cuda_dconv3D_deltaX natives: src/cu32_src/Cuda_dconv3D_deltaX/Cuda_dconv3D_deltaX/A.cu:14-325 */
+int alpha_Cuda_dconv3D_deltaX_dconv3D_deltaX_s1(const int64_t* streams, int length, float* deltaY,
+                                                int OH, int OW, float* W, int FH, int FW,
+                                                float* deltaX, int IH, int IW, int N, int IC, int OC,
+                                                int ph, int pw);
+int alpha_Cuda_dconv3D_deltaX_dconv3D_deltaX_s1_texture(const int64_t* streams, int length,
+                                                        float* deltaY, int OH, int OW, float* W,
+                                                        int FH, int FW, float* deltaX, int IH,
+                                                        int IW, int N, int IC, int OC, int ph,
+                                                        int pw);
+int alpha_Cuda_dconv3D_deltaX_dconv3D_deltaX_V2_s1(int useTexture, const int64_t* streams,
+                                                   int length, float* deltaY, int OH, int OW,
+                                                   float* W, int FH, int FW, float* deltaX, int IH,
+                                                   int IW, int N, int IC, int OC, int ph, int pw);
+int alpha_Cuda_dconv3D_deltaX_dconv3D_deltaX_W1(const int64_t* streams, int length, float* deltaY,
+                                                float* W, float* deltaX, int IH, int IW, int N,
+                                                int IC, int OC);
+/* ks_remode / ks_remodev2 leave in CW what the kernel-split entries below need, because those
+ * entries never see W.  This library's private CW layout is a plain copy of W[OC,FH,FW,IC]
+ * (CW holds OC*CFH*CFW*IC*sh*sw >= OC*FH*FW*IC floats). */
+int alpha_Cuda_dconv3D_deltaX_ks_remode(int64_t stream, float* W, int FH, int FW, float* CW, int CFH,
+                                        int CFW, int OC, int IC, int sh, int sw);
+int alpha_Cuda_dconv3D_deltaX_ks_remodev2(int64_t stream, float* W, int FH, int FW, float* CW,
+                                          int CFH, int CFW, int OC, int IC, int sh, int sw);
+int alpha_Cuda_dconv3D_deltaX_dconv3D_deltaX_kernelSplit(const int64_t* streams, int length,
+                                                         float* deltaY, int OH, int OW, float* CW,
+                                                         int FH, int FW, float* deltaX, int IH,
+                                                         int IW, int N, int IC, int OC, int sh,
+                                                         int sw, int ph, int pw);
+int alpha_Cuda_dconv3D_deltaX_dconv3D_deltaX_ksImsR(const int64_t* streams, int length,
+                                                    float* deltaY, int OH, int OW, float* CW, int FH,
+                                                    int FW, float* deltaX, int IH, int IW, int N,
+                                                    int IC, int OC, int sh, int sw, int ph, int pw);
+int alpha_Cuda_dconv3D_deltaX_dconv3D_deltaX_ksImsR_texture(const int64_t* streams, int length,
+                                                            float* deltaY, int OH, int OW, float* CW,
+                                                            int FH, int FW, float* deltaX, int IH,
+                                                            int IW, int N, int IC, int OC, int sh,
+                                                            int sw, int ph, int pw);
+int alpha_Cuda_dconv3D_deltaX_dconv3D_deltaX_ksIms2R(const int64_t* streams, int length,
+                                                     float* deltaY, int OH, int OW, float* CW,
+                                                     int FH, int FW, float* deltaX, int IH, int IW,
+                                                     int N, int IC, int OC, int ph, int pw);
+int alpha_Cuda_dconv3D_deltaX_dconv3D_deltaX_ksIms2R_texture(const int64_t* streams, int length,
+                                                             float* deltaY, int OH, int OW,
+                                                             float* CW, int FH, int FW,
+                                                             float* deltaX, int IH, int IW, int N,
+                                                             int IC, int OC, int ph, int pw);
+int alpha_Cuda_dconv3D_deltaX_dconv3D_deltaX_ksV2_Ims2R(int useTexture, const int64_t* streams,
+                                                        int length, float* deltaY, int OH, int OW,
+                                                        float* CW, int FH, int FW, float* deltaX,
+                                                        int IH, int IW, int N, int IC, int OC,
+                                                        int ph, int pw);
+int alpha_Cuda_dconv3D_deltaX_dconv3D_deltaX_crossAdd(const int64_t* streams, int length,
+                                                      float* deltaY, int OH, int OW, float* W,
+                                                      int FH, int FW, float* deltaX, int IH, int IW,
+                                                      int N, int IC, int OC, int sh, int sw, int ph,
+                                                      int pw);
+
+/* Cuda_dconv3D_deltaW natives: src/cu32_src/Cuda_dconv3D_deltaW/Cuda_dconv3D_deltaW/A.cu:16-154.
+ * The GemmSK entries write the complete gradient into deltaW and zero the (GridZ-1)*sizeW floats
+ * of deltaW_buf, so the caller's following buf_summary(deltaW += sum of buffers) adds zeros. */
+int alpha_Cuda_dconv3D_deltaW_dconv3D_deltaW(const int64_t* streams, int length, float* X, int IH,
+                                             int IW, float* deltaY, int OH, int OW, float* deltaW,
+                                             int FH, int FW, int N, int IC, int OC, int sh, int sw,
+                                             int ph, int pw);
+int alpha_Cuda_dconv3D_deltaW_dconv3D_deltaW_W1(const int64_t* streams, int length, float* X, int IH,
+                                                int IW, float* deltaY, float* deltaW, int N, int IC,
+                                                int OC);
+int alpha_Cuda_dconv3D_deltaW_buf_summary(int64_t stream, float* deltaW_buf, float* deltaW, int part,
+                                          int sizeW);
+int alpha_Cuda_dconv3D_deltaW_dconv3D_deltaW_GemmSK(const int64_t* streams, int length, int GridZ,
+                                                    float* X, int IH, int IW, float* deltaY, int OH,
+                                                    int OW, float* deltaW, float* deltaW_buf, int FH,
+                                                    int FW, int N, int IC, int OC, int sh, int sw,
+                                                    int ph, int pw);
+int alpha_Cuda_dconv3D_deltaW_dconv3D_deltaW_GemmV2SK(const int64_t* streams, int length, int GridZ,
+                                                      float* X, int IH, int IW, float* deltaY,
+                                                      int OH, int OW, float* deltaW,
+                                                      float* deltaW_buf, int FH, int FW, int N,
+                                                      int IC, int OC, int sh, int sw, int ph,
+                                                      int pw);
+int alpha_Cuda_dconv3D_deltaW_dconv3D_deltaW_GemmSK_W1(const int64_t* streams, int length, int GridZ,
+                                                       float* X, int IH, int IW, float* deltaY,
+                                                       float* deltaW, float* deltaW_buf, int N,
+                                                       int IC, int OC);
+
+/* ---- layer 3: CudaFloat32EngineBase's operator methods ------------------------------------- */
+/* Argument order of src/alpha_src/z/dragon/engine/cuda/CudaFloat32EngineBase.java:1355 (conv3D),
+ * :1478 (conv3D_biased), :1666 (dconv3D_deltaW), :1796 (dconv3D_deltaX); addresses are device
+ * pointers, the trailing stream replaces the engine's stream pool. */
+int alpha_engine_conv3D(float* Y, int OH, int OW, const float* X, int IH, int IW, const float* W,
+                        int FH, int FW, int N, int IC, int OC, int sh, int sw, int ph, int pw,
+                        alpha_stream_t stream);
+int alpha_engine_conv3D_biased(float* Y, int OH, int OW, const float* X, int IH, int IW,
+                               const float* W, int FH, int FW, const float* Bias, int N, int IC,
+                               int OC, int sh, int sw, int ph, int pw, alpha_stream_t stream);
+int alpha_engine_dconv3D_deltaW(float* deltaW, int FH, int FW, const float* X, int IH, int IW,
+                                const float* deltaY, int OH, int OW, int N, int IC, int OC, int sh,
+                                int sw, int ph, int pw, alpha_stream_t stream);
+int alpha_engine_dconv3D_deltaX(float* deltaX, int IH, int IW, const float* deltaY, int OH, int OW,
+                                const float* W, int FH, int FW, int N, int IC, int OC, int sh,
+                                int sw, int ph, int pw, alpha_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ALPHA_CONV_B200_H */

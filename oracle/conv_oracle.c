@@ -1,0 +1,384 @@
+/*
+ * CPU oracle for the Dragon-Alpha conv hot path (TEST INFRASTRUCTURE, not product code).
+ *
+ * A plain-C restatement of the reference's CPU convolution loops.  Only the test suite, the
+ * smoke check and the benchmark's cpu_baseline / reference arm may link or call this file;
+ * the CUDA library never does.
+ *
+ * Layouts (all fp32, C-contiguous, NHWC):
+ *   X[N,IH,IW,IC]  W[OC,FH,FW,IC]  Y[N,OH,OW,OC]   deltaX like X, deltaY like Y, deltaW like W.
+ *
+ * Every function states the reference loop it follows (path inside the reference project).
+ * Java semantics that matter for bit-exactness are kept:
+ *   - `double v; v += x*w` with float x, w: the product is rounded to float first, then widened.
+ *   - `float v; v += x*w`: float product, float add (no fused multiply-add).
+ * Compile with -ffp-contract=off so the compiler cannot fuse the multiply and the add.
+ *
+ * The *_mt variants split the outermost independent loop over OpenMP threads; each output element
+ * is still produced by exactly the same sequence of operations, so results are bit-identical.
+ */
+#include <stddef.h>
+#include <stdint.h>
+#include <string.h>
+#include <math.h>
+
+#if defined(_OPENMP)
+#include <omp.h>
+#endif
+
+#define IDX4(w, z, y, x, Sz, Sy, Sx) ((((size_t)(w) * (Sz) + (z)) * (Sy) + (y)) * (Sx) + (x))
+
+int oracle_max_threads(void)
+{
+#if defined(_OPENMP)
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}
+
+/*
+ * Forward convolution, double accumulator.
+ * Follows src/zutil_src/z/util/math/vector/Tense.java:143-173 (Tense.conv3D_naive):
+ * loop order n -> oc -> oh -> ow -> fh -> fw -> ic, `double v += X*W` (float product), cast to
+ * float on store (:170).  Taps outside the image are skipped (:168).
+ */
+void oracle_conv3D_naive(const float *X, int IH, int IW, const float *W, int FH, int FW, float *Y,
+                         int OH, int OW, int N, int IC, int OC, int sh, int sw, int ph, int pw,
+                         int threads)
+{
+    (void)threads;
+#if defined(_OPENMP)
+#pragma omp parallel for collapse(2) schedule(static) num_threads(threads > 0 ? threads : 1)
+#endif
+    for (int n = 0; n < N; n++)
+        for (int oc = 0; oc < OC; oc++) {
+            for (int oh = 0; oh < OH; oh++) {
+                int ih_s = -ph + oh * sh;
+                if (ih_s > IH + ph - FH) break;
+                for (int ow = 0; ow < OW; ow++) {
+                    int iw_s = -pw + ow * sw;
+                    if (iw_s > IW + pw - FW) break;
+                    double v = 0;
+                    for (int fh = 0; fh < FH; fh++)
+                        for (int fw = 0; fw < FW; fw++)
+                            for (int ic = 0; ic < IC; ic++) {
+                                int ih = ih_s + fh, iw = iw_s + fw;
+                                if (ih < 0 || iw < 0 || ih >= IH || iw >= IW) continue;
+                                float p = X[IDX4(n, ih, iw, ic, IH, IW, IC)] *
+                                          W[IDX4(oc, fh, fw, ic, FH, FW, IC)];
+                                v += (double)p;
+                            }
+                    Y[IDX4(n, oh, ow, oc, OH, OW, OC)] = (float)v;
+                }
+            }
+        }
+}
+
+/*
+ * Forward convolution, float accumulator.
+ * Follows CONV_3D_NAIVE, src/cu32_src/Cuda_conv3D/Cuda_conv3D/test.cuh:80-110: the same taps in the
+ * same fh -> fw -> ic order as the Java loop above, but `float v += X*W`.  Exists so that the
+ * restatement can be pinned bit-for-bit against the reference's own compiled C++ loop.
+ */
+void oracle_conv3D_naive_f32(const float *X, int IH, int IW, const float *W, int FH, int FW,
+                             float *Y, int OH, int OW, int N, int IC, int OC, int sh, int sw,
+                             int ph, int pw, int threads)
+{
+    (void)threads;
+#if defined(_OPENMP)
+#pragma omp parallel for collapse(2) schedule(static) num_threads(threads > 0 ? threads : 1)
+#endif
+    for (int oc = 0; oc < OC; oc++)
+        for (int n = 0; n < N; n++) {
+            int oh = 0;
+            for (int ih_s = -ph; ih_s <= (IH + ph - FH); ih_s += sh, oh++) {
+                int ow = 0;
+                for (int iw_s = -pw; iw_s <= (IW + pw - FW); iw_s += sw, ow++) {
+                    float v = 0;
+                    for (int fh = 0; fh < FH; fh++)
+                        for (int fw = 0; fw < FW; fw++)
+                            for (int ic = 0; ic < IC; ic++) {
+                                int ih = ih_s + fh, iw = iw_s + fw;
+                                if (ih < 0 || iw < 0 || ih >= IH || iw >= IW) continue;
+                                float p = X[IDX4(n, ih, iw, ic, IH, IW, IC)] *
+                                          W[IDX4(oc, fh, fw, ic, FH, FW, IC)];
+                                v = v + p;
+                            }
+                    Y[IDX4(n, oh, ow, oc, OH, OW, OC)] = v;
+                }
+            }
+        }
+}
+
+/*
+ * Forward convolution in full double precision (double products, double accumulator); used only
+ * for error analysis.  Follows Tense.conv3D_naive_double, Tense.java:175-205, with the float
+ * inputs widened first.  Also returns S[n,oh,ow,oc] = sum |x|*|w| when S != NULL: the
+ * denominator of the componentwise forward-error bound.
+ */
+void oracle_conv3D_f64(const float *X, int IH, int IW, const float *W, int FH, int FW, double *Y,
+                       double *S, int OH, int OW, int N, int IC, int OC, int sh, int sw, int ph,
+                       int pw, int threads)
+{
+    (void)threads;
+#if defined(_OPENMP)
+#pragma omp parallel for collapse(2) schedule(static) num_threads(threads > 0 ? threads : 1)
+#endif
+    for (int n = 0; n < N; n++)
+        for (int oc = 0; oc < OC; oc++)
+            for (int oh = 0; oh < OH; oh++)
+                for (int ow = 0; ow < OW; ow++) {
+                    double v = 0, s = 0;
+                    for (int fh = 0; fh < FH; fh++)
+                        for (int fw = 0; fw < FW; fw++) {
+                            int ih = oh * sh - ph + fh, iw = ow * sw - pw + fw;
+                            if (ih < 0 || iw < 0 || ih >= IH || iw >= IW) continue;
+                            const float *x = X + IDX4(n, ih, iw, 0, IH, IW, IC);
+                            const float *w = W + IDX4(oc, fh, fw, 0, FH, FW, IC);
+                            for (int ic = 0; ic < IC; ic++) {
+                                double p = (double)x[ic] * (double)w[ic];
+                                v += p;
+                                s += fabs(p);
+                            }
+                        }
+                    Y[IDX4(n, oh, ow, oc, OH, OW, OC)] = v;
+                    if (S) S[IDX4(n, oh, ow, oc, OH, OW, OC)] = s;
+                }
+}
+
+/*
+ * Row-broadcast bias add, Y[n,oh,ow,oc] += bias[oc], float add.
+ * Follows the bias stage of CudaFloat32EngineBase.conv3D_biased
+ * (src/alpha_src/z/dragon/engine/cuda/CudaFloat32EngineBase.java:1548-1557), which runs
+ * linear_dual2D_row with alpha = beta = 1, gamma = 0
+ * (src/cu32_src/Cuda_function/Cuda_function/type1_linear_dual2D_row.cuh:35-62).
+ */
+void oracle_add_bias_row(float *Y, const float *bias, size_t rows, int OC)
+{
+    for (size_t r = 0; r < rows; r++)
+        for (int oc = 0; oc < OC; oc++) Y[r * OC + oc] = Y[r * OC + oc] + bias[oc];
+}
+
+/*
+ * Input gradient / transposed convolution, float accumulator.
+ * Follows Tense.deconv3D_deltaX_img2col, Tense.java:334-375 (the same loop exists in C++ at
+ * src/cu32_src/Cuda_dconv3D_deltaX/Cuda_dconv3D_deltaX/test.cuh:89-131):
+ * for ic, for j=(n,ih,iw), for k=(oc,fh,fw): positions of the zero-stuffed, outer-padded deltaY
+ * that fall between real samples are skipped; W is read rotated by 180 degrees.
+ */
+void oracle_deconv3D_deltaX_img2col(const float *deltaY, int OH, int OW, const float *W, int FH,
+                                    int FW, float *deltaX, int IH, int IW, int N, int IC, int OC,
+                                    int sh, int sw, int ph, int pw, int threads)
+{
+    (void)threads;
+    const int GM = N * IH * IW, GK = OC * FH * FW;
+    const int OHp = OH + (OH - 1) * (sh - 1), OWp = OW + (OW - 1) * (sw - 1);
+    const int oph = FH - ph - 1, opw = FW - pw - 1;
+#if defined(_OPENMP)
+#pragma omp parallel for schedule(static) num_threads(threads > 0 ? threads : 1)
+#endif
+    for (int j = 0; j < GM; j++) {
+        int n = j / (IH * IW), j_res = j % (IH * IW);
+        int ih = j_res / IW, iw = j_res % IW;
+        for (int ic = 0; ic < IC; ic++) {
+            float v = 0;
+            for (int k = 0; k < GK; k++) {
+                int oc = k / (FH * FW), k_res = k % (FH * FW);
+                int fh = k_res / FW, fw = k_res % FW;
+                int oh = ih - oph + fh, ow = iw - opw + fw;
+                if (oh < 0 || ow < 0 || oh >= OHp || ow >= OWp) continue;
+                if (oh % sh != 0 || ow % sw != 0) continue;
+                float p = deltaY[IDX4(n, oh / sh, ow / sw, oc, OH, OW, OC)] *
+                          W[IDX4(oc, FH - 1 - fh, FW - 1 - fw, ic, FH, FW, IC)];
+                v = v + p;
+            }
+            deltaX[IDX4(n, ih, iw, ic, IH, IW, IC)] = v;
+        }
+    }
+}
+
+/*
+ * Input gradient in scatter form, float accumulation into deltaX (caller zeroes deltaX).
+ * Follows Tense.deconv3D_deltaX_crossAdd, Tense.java:441-469: loop order oc -> n -> oh -> ow ->
+ * fh -> fw -> ic, `deltaX[n][ih][iw][ic] += w*dy`.  Single-threaded: the order of the adds is
+ * part of the result.
+ */
+void oracle_deconv3D_deltaX_crossAdd(const float *deltaY, int OH, int OW, const float *W, int FH,
+                                     int FW, float *deltaX, int IH, int IW, int N, int IC, int OC,
+                                     int sh, int sw, int ph, int pw)
+{
+    for (int oc = 0; oc < OC; oc++)
+        for (int n = 0; n < N; n++)
+            for (int oh = 0; oh < OH; oh++)
+                for (int ow = 0; ow < OW; ow++) {
+                    float dy = deltaY[IDX4(n, oh, ow, oc, OH, OW, OC)];
+                    for (int fh = 0; fh < FH; fh++)
+                        for (int fw = 0; fw < FW; fw++) {
+                            int ih = oh * sh - ph + fh, iw = ow * sw - pw + fw;
+                            if (ih < 0 || iw < 0 || ih >= IH || iw >= IW) continue;
+                            for (int ic = 0; ic < IC; ic++) {
+                                float w = W[IDX4(oc, fh, fw, ic, FH, FW, IC)];
+                                float p = w * dy;
+                                float *d = deltaX + IDX4(n, ih, iw, ic, IH, IW, IC);
+                                *d = *d + p;
+                            }
+                        }
+                }
+}
+
+/* Input gradient in double precision with S = sum |dy|*|w| (error analysis only). */
+void oracle_deconv3D_deltaX_f64(const float *deltaY, int OH, int OW, const float *W, int FH, int FW,
+                                double *deltaX, double *S, int IH, int IW, int N, int IC, int OC,
+                                int sh, int sw, int ph, int pw, int threads)
+{
+    (void)threads;
+    const int GM = N * IH * IW;
+#if defined(_OPENMP)
+#pragma omp parallel for schedule(static) num_threads(threads > 0 ? threads : 1)
+#endif
+    for (int j = 0; j < GM; j++) {
+        int n = j / (IH * IW), j_res = j % (IH * IW);
+        int ih = j_res / IW, iw = j_res % IW;
+        for (int ic = 0; ic < IC; ic++) {
+            double v = 0, s = 0;
+            for (int fh = 0; fh < FH; fh++) {
+                int t = ih + ph - fh;
+                if (t < 0 || t % sh != 0 || t / sh >= OH) continue;
+                for (int fw = 0; fw < FW; fw++) {
+                    int u = iw + pw - fw;
+                    if (u < 0 || u % sw != 0 || u / sw >= OW) continue;
+                    for (int oc = 0; oc < OC; oc++) {
+                        double p = (double)deltaY[IDX4(n, t / sh, u / sw, oc, OH, OW, OC)] *
+                                   (double)W[IDX4(oc, fh, fw, ic, FH, FW, IC)];
+                        v += p;
+                        s += fabs(p);
+                    }
+                }
+            }
+            deltaX[IDX4(n, ih, iw, ic, IH, IW, IC)] = v;
+            if (S) S[IDX4(n, ih, iw, ic, IH, IW, IC)] = s;
+        }
+    }
+}
+
+/*
+ * Weight gradient, float accumulator.
+ * Follows Tense.deconv3D_deltaW_img2col2, Tense.java:1364-1401 (C++ twin:
+ * src/cu32_src/Cuda_dconv3D_deltaW/Cuda_dconv3D_deltaW/test.cuh:77-121):
+ * for oc, for j=(ic,fh,fw), for k=(n,oh,ow): float `v += X*deltaY`.
+ */
+void oracle_deconv3D_deltaW_img2col2(const float *X, int IH, int IW, const float *deltaY, int OH,
+                                     int OW, float *deltaW, int FH, int FW, int N, int IC, int OC,
+                                     int sh, int sw, int ph, int pw, int threads)
+{
+    (void)threads;
+    const int GM = IC * FH * FW, GK = N * OH * OW;
+#if defined(_OPENMP)
+#pragma omp parallel for collapse(2) schedule(static) num_threads(threads > 0 ? threads : 1)
+#endif
+    for (int oc = 0; oc < OC; oc++)
+        for (int j = 0; j < GM; j++) {
+            int ic = j / (FH * FW), j_res = j % (FH * FW);
+            int fh = j_res / FW, fw = j_res % FW;
+            float v = 0;
+            for (int k = 0; k < GK; k++) {
+                int n = k / (OH * OW), k_res = k % (OH * OW);
+                int oh = k_res / OW, ow = k_res % OW;
+                int ih = fh - ph + oh * sh, iw = fw - pw + ow * sw;
+                if (ih < 0 || iw < 0 || ih >= IH || iw >= IW) continue;
+                float p = X[IDX4(n, ih, iw, ic, IH, IW, IC)] *
+                          deltaY[IDX4(n, oh, ow, oc, OH, OW, OC)];
+                v = v + p;
+            }
+            deltaW[IDX4(oc, fh, fw, ic, FH, FW, IC)] = v;
+        }
+}
+
+/*
+ * Weight gradient, double accumulator.
+ * Follows Tense.deconv3d_deltaW_naive, Tense.java:1277-1319, which swaps the N and channel axes of
+ * X and of the zero-stuffed deltaY and runs Tense.conv3D_naive over them.  Unrolled, that is: for
+ * each (ic, oc, fh, fw) a double accumulator over oh -> ow -> n (the conv's fh', fw', ic' loops),
+ * float products; the zero-stuffed positions contribute an exact +0 and are skipped here.
+ */
+void oracle_deconv3d_deltaW_naive(const float *X, int IH, int IW, const float *deltaY, int OH,
+                                  int OW, float *deltaW, int FH, int FW, int N, int IC, int OC,
+                                  int sh, int sw, int ph, int pw, int threads)
+{
+    (void)threads;
+#if defined(_OPENMP)
+#pragma omp parallel for collapse(2) schedule(static) num_threads(threads > 0 ? threads : 1)
+#endif
+    for (int ic = 0; ic < IC; ic++)
+        for (int oc = 0; oc < OC; oc++)
+            for (int fh = 0; fh < FH; fh++)
+                for (int fw = 0; fw < FW; fw++) {
+                    double v = 0;
+                    for (int oh = 0; oh < OH; oh++) {
+                        int ih = fh - ph + oh * sh;
+                        if (ih < 0 || ih >= IH) continue;
+                        for (int ow = 0; ow < OW; ow++) {
+                            int iw = fw - pw + ow * sw;
+                            if (iw < 0 || iw >= IW) continue;
+                            for (int n = 0; n < N; n++) {
+                                float p = X[IDX4(n, ih, iw, ic, IH, IW, IC)] *
+                                          deltaY[IDX4(n, oh, ow, oc, OH, OW, OC)];
+                                v += (double)p;
+                            }
+                        }
+                    }
+                    deltaW[IDX4(oc, fh, fw, ic, FH, FW, IC)] = (float)v;
+                }
+}
+
+/* Weight gradient in double precision with S = sum |x|*|dy| (error analysis only). */
+void oracle_deconv3D_deltaW_f64(const float *X, int IH, int IW, const float *deltaY, int OH, int OW,
+                                double *deltaW, double *S, int FH, int FW, int N, int IC, int OC,
+                                int sh, int sw, int ph, int pw, int threads)
+{
+    (void)threads;
+#if defined(_OPENMP)
+#pragma omp parallel for collapse(2) schedule(static) num_threads(threads > 0 ? threads : 1)
+#endif
+    for (int oc = 0; oc < OC; oc++)
+        for (int fh = 0; fh < FH; fh++)
+            for (int fw = 0; fw < FW; fw++)
+                for (int ic = 0; ic < IC; ic++) {
+                    double v = 0, s = 0;
+                    for (int n = 0; n < N; n++)
+                        for (int oh = 0; oh < OH; oh++) {
+                            int ih = fh - ph + oh * sh;
+                            if (ih < 0 || ih >= IH) continue;
+                            for (int ow = 0; ow < OW; ow++) {
+                                int iw = fw - pw + ow * sw;
+                                if (iw < 0 || iw >= IW) continue;
+                                double p = (double)X[IDX4(n, ih, iw, ic, IH, IW, IC)] *
+                                           (double)deltaY[IDX4(n, oh, ow, oc, OH, OW, OC)];
+                                v += p;
+                                s += fabs(p);
+                            }
+                        }
+                    deltaW[IDX4(oc, fh, fw, ic, FH, FW, IC)] = v;
+                    if (S) S[IDX4(oc, fh, fw, ic, FH, FW, IC)] = s;
+                }
+}
+
+/*
+ * Fraction of elements that agree, the reference's acceptance metric.
+ * Follows Vector.samePercentRelative, src/zutil_src/z/util/math/vector/Vector.java:4109-4125:
+ * equal values count; otherwise |(a-b+MIN)/(a+b+MIN)| < threshold with MIN = Float.MIN_VALUE,
+ * evaluated in float; two NaNs count as equal.
+ */
+float oracle_samePercentRelative(const float *A, const float *B, size_t length, float threshold)
+{
+    const float MINV = 1.4e-45f; /* Float.MIN_VALUE */
+    size_t sum = 0;
+    for (size_t i = 0; i < length; i++) {
+        if (A[i] == B[i]) { sum++; continue; }
+        float div = fabsf((A[i] - B[i] + MINV) / (A[i] + B[i] + MINV));
+        if (div < threshold) { sum++; continue; }
+        if (isnan(A[i]) && isnan(B[i])) { sum++; continue; }
+    }
+    return (float)sum / (float)length;
+}

@@ -1,0 +1,251 @@
+"""ctypes front end of the CPU oracle (TEST INFRASTRUCTURE, not product code).
+
+`liboracle.so` is the plain-C restatement of the reference's Java CPU loops
+(src/zutil_src/z/util/math/vector/Tense.java); `_ref/libref_cpu.so`, when it has been built from a
+reference checkout, holds the reference project's own C++ loops (test.cuh of each cu32 library).
+Only the test suite, the smoke check and the benchmark's CPU-baseline legs may import this module.
+
+All arrays are C-contiguous float32 NHWC: X[N,IH,IW,IC], W[OC,FH,FW,IC], Y[N,OH,OW,OC].
+"""
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_F = C.POINTER(C.c_float)
+_D = C.POINTER(C.c_double)
+_i = C.c_int
+
+
+def build(ref_root="/root/reference"):
+    """Compile liboracle.so, and _ref/libref_cpu.so when a reference checkout is present."""
+    subprocess.check_call(["make", "-s", "-C", _HERE, "all"])
+    if os.path.isdir(os.path.join(ref_root, "src", "cu32_src")):
+        subprocess.check_call(["make", "-s", "-C", _HERE, "ref", "REF=" + ref_root])
+
+
+def _load(path):
+    if not os.path.exists(path):
+        return None
+    return C.CDLL(path)
+
+
+_lib = None
+_ref = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        path = os.path.join(_HERE, "liboracle.so")
+        if not os.path.exists(path):
+            build()
+        _lib = C.CDLL(path)
+        _lib.oracle_samePercentRelative.restype = C.c_float
+        _lib.oracle_max_threads.restype = C.c_int
+    return _lib
+
+
+def ref_lib():
+    """The reference's own C++ loops, or None when they were never built on this machine."""
+    global _ref
+    if _ref is None:
+        _ref = _load(os.path.join(_HERE, "_ref", "libref_cpu.so"))
+    return _ref
+
+
+def max_threads():
+    return int(lib().oracle_max_threads())
+
+
+def _f(a):
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    return a, a.ctypes.data_as(_F)
+
+
+def out_hw(IH, IW, FH, FW, sh, sw, ph, pw):
+    """OH, OW as Cuda_conv3D.java:154-155 computes them."""
+    return (IH + 2 * ph - FH) // sh + 1, (IW + 2 * pw - FW) // sw + 1
+
+
+def conv3D_naive(X, W, sh, sw, ph, pw, threads=1):
+    """Tense.conv3D_naive (Tense.java:143-173): double accumulator over float products."""
+    N, IH, IW, IC = X.shape
+    OC, FH, FW, _ = W.shape
+    OH, OW = out_hw(IH, IW, FH, FW, sh, sw, ph, pw)
+    X, px = _f(X)
+    W, pw_ = _f(W)
+    Y = np.zeros((N, OH, OW, OC), np.float32)
+    lib().oracle_conv3D_naive(px, _i(IH), _i(IW), pw_, _i(FH), _i(FW), Y.ctypes.data_as(_F),
+                              _i(OH), _i(OW), _i(N), _i(IC), _i(OC), _i(sh), _i(sw), _i(ph),
+                              _i(pw), _i(threads))
+    return Y
+
+
+def conv3D_naive_f32(X, W, sh, sw, ph, pw, threads=1):
+    """CONV_3D_NAIVE restated (Cuda_conv3D/test.cuh:80-110): float accumulator."""
+    N, IH, IW, IC = X.shape
+    OC, FH, FW, _ = W.shape
+    OH, OW = out_hw(IH, IW, FH, FW, sh, sw, ph, pw)
+    X, px = _f(X)
+    W, pw_ = _f(W)
+    Y = np.zeros((N, OH, OW, OC), np.float32)
+    lib().oracle_conv3D_naive_f32(px, _i(IH), _i(IW), pw_, _i(FH), _i(FW), Y.ctypes.data_as(_F),
+                                  _i(OH), _i(OW), _i(N), _i(IC), _i(OC), _i(sh), _i(sw), _i(ph),
+                                  _i(pw), _i(threads))
+    return Y
+
+
+def conv3D_f64(X, W, sh, sw, ph, pw, threads=1):
+    """fp64 forward conv and S = sum|x||w| per output (error analysis)."""
+    N, IH, IW, IC = X.shape
+    OC, FH, FW, _ = W.shape
+    OH, OW = out_hw(IH, IW, FH, FW, sh, sw, ph, pw)
+    X, px = _f(X)
+    W, pw_ = _f(W)
+    Y = np.zeros((N, OH, OW, OC), np.float64)
+    S = np.zeros((N, OH, OW, OC), np.float64)
+    lib().oracle_conv3D_f64(px, _i(IH), _i(IW), pw_, _i(FH), _i(FW), Y.ctypes.data_as(_D),
+                            S.ctypes.data_as(_D), _i(OH), _i(OW), _i(N), _i(IC), _i(OC), _i(sh),
+                            _i(sw), _i(ph), _i(pw), _i(threads))
+    return Y, S
+
+
+def add_bias_row(Y, bias):
+    """Y[..., oc] += bias[oc] in float (conv3D_biased's linear_dual2D_row stage)."""
+    Y = np.ascontiguousarray(Y, np.float32).copy()
+    b, pb = _f(bias)
+    lib().oracle_add_bias_row(Y.ctypes.data_as(_F), pb, C.c_size_t(Y.size // Y.shape[-1]),
+                              _i(Y.shape[-1]))
+    return Y
+
+
+def deconv3D_deltaX_img2col(dY, W, IH, IW, sh, sw, ph, pw, threads=1):
+    """Tense.deconv3D_deltaX_img2col (Tense.java:334-375): float accumulator."""
+    N, OH, OW, OC = dY.shape
+    _, FH, FW, IC = W.shape
+    dY, pdy = _f(dY)
+    W, pw_ = _f(W)
+    dX = np.zeros((N, IH, IW, IC), np.float32)
+    lib().oracle_deconv3D_deltaX_img2col(pdy, _i(OH), _i(OW), pw_, _i(FH), _i(FW),
+                                         dX.ctypes.data_as(_F), _i(IH), _i(IW), _i(N), _i(IC),
+                                         _i(OC), _i(sh), _i(sw), _i(ph), _i(pw), _i(threads))
+    return dX
+
+
+def deconv3D_deltaX_crossAdd(dY, W, IH, IW, sh, sw, ph, pw):
+    """Tense.deconv3D_deltaX_crossAdd (Tense.java:441-469): scatter form, float adds."""
+    N, OH, OW, OC = dY.shape
+    _, FH, FW, IC = W.shape
+    dY, pdy = _f(dY)
+    W, pw_ = _f(W)
+    dX = np.zeros((N, IH, IW, IC), np.float32)
+    lib().oracle_deconv3D_deltaX_crossAdd(pdy, _i(OH), _i(OW), pw_, _i(FH), _i(FW),
+                                          dX.ctypes.data_as(_F), _i(IH), _i(IW), _i(N), _i(IC),
+                                          _i(OC), _i(sh), _i(sw), _i(ph), _i(pw))
+    return dX
+
+
+def deconv3D_deltaX_f64(dY, W, IH, IW, sh, sw, ph, pw, threads=1):
+    N, OH, OW, OC = dY.shape
+    _, FH, FW, IC = W.shape
+    dY, pdy = _f(dY)
+    W, pw_ = _f(W)
+    dX = np.zeros((N, IH, IW, IC), np.float64)
+    S = np.zeros((N, IH, IW, IC), np.float64)
+    lib().oracle_deconv3D_deltaX_f64(pdy, _i(OH), _i(OW), pw_, _i(FH), _i(FW),
+                                     dX.ctypes.data_as(_D), S.ctypes.data_as(_D), _i(IH), _i(IW),
+                                     _i(N), _i(IC), _i(OC), _i(sh), _i(sw), _i(ph), _i(pw),
+                                     _i(threads))
+    return dX, S
+
+
+def deconv3D_deltaW_img2col2(X, dY, FH, FW, sh, sw, ph, pw, threads=1):
+    """Tense.deconv3D_deltaW_img2col2 (Tense.java:1364-1401): float accumulator."""
+    N, IH, IW, IC = X.shape
+    _, OH, OW, OC = dY.shape
+    X, px = _f(X)
+    dY, pdy = _f(dY)
+    dW = np.zeros((OC, FH, FW, IC), np.float32)
+    lib().oracle_deconv3D_deltaW_img2col2(px, _i(IH), _i(IW), pdy, _i(OH), _i(OW),
+                                          dW.ctypes.data_as(_F), _i(FH), _i(FW), _i(N), _i(IC),
+                                          _i(OC), _i(sh), _i(sw), _i(ph), _i(pw), _i(threads))
+    return dW
+
+
+def deconv3d_deltaW_naive(X, dY, FH, FW, sh, sw, ph, pw, threads=1):
+    """Tense.deconv3d_deltaW_naive (Tense.java:1277-1319): double accumulator."""
+    N, IH, IW, IC = X.shape
+    _, OH, OW, OC = dY.shape
+    X, px = _f(X)
+    dY, pdy = _f(dY)
+    dW = np.zeros((OC, FH, FW, IC), np.float32)
+    lib().oracle_deconv3d_deltaW_naive(px, _i(IH), _i(IW), pdy, _i(OH), _i(OW),
+                                       dW.ctypes.data_as(_F), _i(FH), _i(FW), _i(N), _i(IC),
+                                       _i(OC), _i(sh), _i(sw), _i(ph), _i(pw), _i(threads))
+    return dW
+
+
+def deconv3D_deltaW_f64(X, dY, FH, FW, sh, sw, ph, pw, threads=1):
+    N, IH, IW, IC = X.shape
+    _, OH, OW, OC = dY.shape
+    X, px = _f(X)
+    dY, pdy = _f(dY)
+    dW = np.zeros((OC, FH, FW, IC), np.float64)
+    S = np.zeros((OC, FH, FW, IC), np.float64)
+    lib().oracle_deconv3D_deltaW_f64(px, _i(IH), _i(IW), pdy, _i(OH), _i(OW),
+                                     dW.ctypes.data_as(_D), S.ctypes.data_as(_D), _i(FH), _i(FW),
+                                     _i(N), _i(IC), _i(OC), _i(sh), _i(sw), _i(ph), _i(pw),
+                                     _i(threads))
+    return dW, S
+
+
+def samePercentRelative(A, B, threshold):
+    """Vector.samePercentRelative (Vector.java:4109-4125)."""
+    A, pa = _f(np.ravel(A))
+    B, pb = _f(np.ravel(B))
+    return float(lib().oracle_samePercentRelative(pa, pb, C.c_size_t(A.size), C.c_float(threshold)))
+
+
+# ---- the reference's own C++ loops (only where _ref/libref_cpu.so was built) -------------------
+
+def ref_CONV_3D_NAIVE(X, W, sh, sw, ph, pw):
+    """CONV_3D_NAIVE, src/cu32_src/Cuda_conv3D/Cuda_conv3D/test.cuh:80-110 (float accumulator)."""
+    N, IH, IW, IC = X.shape
+    OC, FH, FW, _ = W.shape
+    OH, OW = out_hw(IH, IW, FH, FW, sh, sw, ph, pw)
+    X, px = _f(X)
+    W, pw_ = _f(W)
+    Y = np.zeros((N, OH, OW, OC), np.float32)
+    ref_lib().ref_CONV_3D_NAIVE(px, _i(IH), _i(IW), pw_, _i(FH), _i(FW), Y.ctypes.data_as(_F),
+                                _i(OH), _i(OW), _i(N), _i(IC), _i(OC), _i(sh), _i(sw), _i(ph),
+                                _i(pw))
+    return Y
+
+
+def ref_deconv3D_deltaX_img2col(dY, W, IH, IW, sh, sw, ph, pw):
+    """deconv3D_deltaX_img2col, src/cu32_src/Cuda_dconv3D_deltaX/Cuda_dconv3D_deltaX/test.cuh:89-131."""
+    N, OH, OW, OC = dY.shape
+    _, FH, FW, IC = W.shape
+    dY, pdy = _f(dY)
+    W, pw_ = _f(W)
+    dX = np.zeros((N, IH, IW, IC), np.float32)
+    ref_lib().ref_deconv3D_deltaX_img2col(pdy, _i(OH), _i(OW), pw_, _i(FH), _i(FW),
+                                          dX.ctypes.data_as(_F), _i(IH), _i(IW), _i(N), _i(IC),
+                                          _i(OC), _i(sh), _i(sw), _i(ph), _i(pw))
+    return dX
+
+
+def ref_deconv3D_deltaW_img2col2(X, dY, FH, FW, sh, sw, ph, pw):
+    """deconv3D_deltaW_img2col2, src/cu32_src/Cuda_dconv3D_deltaW/Cuda_dconv3D_deltaW/test.cuh:77-121."""
+    N, IH, IW, IC = X.shape
+    _, OH, OW, OC = dY.shape
+    X, px = _f(X)
+    dY, pdy = _f(dY)
+    dW = np.zeros((OC, FH, FW, IC), np.float32)
+    ref_lib().ref_deconv3D_deltaW_img2col2(px, _i(IH), _i(IW), pdy, _i(OH), _i(OW),
+                                           dW.ctypes.data_as(_F), _i(FH), _i(FW), _i(N), _i(IC),
+                                           _i(OC), _i(sh), _i(sw), _i(ph), _i(pw))
+    return dW

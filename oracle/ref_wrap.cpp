@@ -1,0 +1,43 @@
+// Thin C wrapper around the reference project's own C++ CPU convolution loops
+// (TEST INFRASTRUCTURE, not product code).
+//
+// The build recipe (Makefile, target `ref`) cuts three functions out of the reference checkout,
+// where they sit behind a disabled include guard, into generated .inc files next to the built
+// library:
+//   CONV_3D_NAIVE             src/cu32_src/Cuda_conv3D/Cuda_conv3D/test.cuh:80-110
+//   deconv3D_deltaX_img2col   src/cu32_src/Cuda_dconv3D_deltaX/Cuda_dconv3D_deltaX/test.cuh:89-131
+//   deconv3D_deltaW_img2col2  src/cu32_src/Cuda_dconv3D_deltaW/Cuda_dconv3D_deltaW/test.cuh:77-121
+// This file only supplies the one indexing macro they use (get4d, micro.cuh:93 of each library)
+// and exports them with C linkage.  No reference source text is stored in this repository.
+#include <cstddef>
+#include <cmath>
+
+#define get4d(A, w, z, y, x, Sz, Sy, Sx) A[(((w) * (Sz) + (z)) * (Sy) + (y)) * (Sx) + (x)]
+
+#include "conv3D_naive.inc"
+#include "deltaX_img2col.inc"
+#include "deltaW_img2col2.inc"
+
+extern "C" {
+
+void ref_CONV_3D_NAIVE(float *X, int IH, int IW, float *W, int FH, int FW, float *Y, int OH, int OW,
+                       int N, int IC, int OC, int sh, int sw, int ph, int pw)
+{
+    CONV_3D_NAIVE(X, IH, IW, W, FH, FW, Y, OH, OW, N, IC, OC, sh, sw, ph, pw);
+}
+
+void ref_deconv3D_deltaX_img2col(float *deltaY, int OH, int OW, float *W, int FH, int FW,
+                                 float *deltaX, int IH, int IW, int N, int IC, int OC, int sh,
+                                 int sw, int ph, int pw)
+{
+    deconv3D_deltaX_img2col(deltaY, OH, OW, W, FH, FW, deltaX, IH, IW, N, IC, OC, sh, sw, ph, pw);
+}
+
+void ref_deconv3D_deltaW_img2col2(float *X, int IH, int IW, float *deltaY, int OH, int OW,
+                                  float *deltaW, int FH, int FW, int N, int IC, int OC, int sh,
+                                  int sw, int ph, int pw)
+{
+    deconv3D_deltaW_img2col2(X, IH, IW, deltaY, OH, OW, deltaW, FH, FW, N, IC, OC, sh, sw, ph, pw);
+}
+
+}  // extern "C"

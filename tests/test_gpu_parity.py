@@ -1,0 +1,110 @@
+"""GPU parity: the CUDA library, called through its C ABI, against the CPU oracle.
+
+Every case runs the three contractions of one conv layer (forward with bias, deltaX, deltaW) on
+seeded inputs and compares with the oracle's fp64 loops under the bounds in helpers.TOL, and - on
+positive inputs, as the reference's own tests use - with the reference's samePercentRelative
+acceptance thresholds (experiments/test_cuda/Cuda_conv3D_test.java:86-97,
+Cuda_dconv3D_dX_test.java:93-100, Cuda_dconv3D_dW_test.java:98-105).
+"""
+import zlib
+
+import numpy as np
+import pytest
+
+from helpers import TOL, gen, metrics, out_hw, record
+
+pytestmark = pytest.mark.gpu
+
+# (N, IH, IW, IC, OC, FH, FW, sh, sw, ph, pw)
+CASES = {
+    "cfg1_32x32_ic16_oc32": (4, 32, 32, 16, 32, 3, 3, 1, 1, 1, 1),
+    "ic32_oc64_16x16": (8, 16, 16, 32, 64, 3, 3, 1, 1, 1, 1),
+    "ic64_oc64_14x14": (8, 14, 14, 64, 64, 3, 3, 1, 1, 1, 1),
+    "ic64_oc128_7x7": (12, 7, 7, 64, 128, 3, 3, 1, 1, 1, 1),
+    "ic8_oc16_9x7": (4, 9, 7, 8, 16, 3, 3, 1, 1, 1, 1),
+    "ic32_oc20_ragged": (4, 11, 13, 32, 20, 3, 3, 1, 1, 1, 1),
+    "ic96_oc36_5x5": (4, 12, 12, 96, 36, 5, 5, 1, 1, 2, 2),
+    "stride2_3x3": (4, 16, 16, 32, 64, 3, 3, 2, 2, 1, 1),
+    "stride2_4x4_dcgan": (4, 16, 16, 32, 64, 4, 4, 2, 2, 1, 1),
+    "w1_1x1": (4, 14, 14, 64, 96, 1, 1, 1, 1, 0, 0),
+    "nopad_3x3": (4, 10, 10, 32, 32, 3, 3, 1, 1, 0, 0),
+    "oc264_two_ntiles": (4, 8, 8, 32, 264, 3, 3, 1, 1, 1, 1),
+    "ic4_stem_7x7": (4, 32, 32, 4, 64, 7, 7, 2, 2, 3, 3),
+    "ic12_oc12": (4, 8, 8, 12, 12, 3, 3, 1, 1, 1, 1),
+    "rect_filter_3x5": (4, 12, 10, 32, 32, 3, 5, 1, 1, 1, 2),
+    "asym_stride_2x1": (4, 12, 12, 32, 32, 3, 3, 2, 1, 1, 1),
+}
+
+
+@pytest.fixture(scope="module")
+def eng(pkg):
+    import torch
+    assert torch.cuda.is_available()
+    torch.cuda.set_device(0)
+    return pkg.submodule("engine").Engine()
+
+
+def _run_case(pkg, eng, O, name, mode, dists=("u11", "u11", "n01")):
+    import torch
+    lib = pkg.submodule("lib")
+    lib.set_math_mode(mode)
+    N, IH, IW, IC, OC, FH, FW, sh, sw, ph, pw = CASES[name]
+    OH, OW = out_hw(IH, IW, FH, FW, sh, sw, ph, pw)
+    rng = np.random.default_rng(zlib.crc32(name.encode()))
+    X = gen((N, IH, IW, IC), dists[0], rng)
+    W = gen((OC, FH, FW, IC), dists[1], rng)
+    B = rng.uniform(-0.1, 0.1, (OC,)).astype(np.float32)
+    dY = gen((N, OH, OW, OC), dists[2], rng)
+    dev = torch.device("cuda:0")
+    tX, tW, tB, tdY = (torch.from_numpy(a).to(dev) for a in (X, W, B, dY))
+    res = {}
+    Y = eng.conv3D_biased(tX, tW, tB, sh, sw, ph, pw)
+    res["fwd_algo"] = lib.last_algo()
+    dX = eng.dconv3D_deltaX(tdY, tW, IH, IW, sh, sw, ph, pw)
+    res["dx_algo"] = lib.last_algo()
+    dW = eng.dconv3D_deltaW(tX, tdY, FH, FW, sh, sw, ph, pw)
+    res["dw_algo"] = lib.last_algo()
+    status = lib.device_status()
+    Y, dX, dW = Y.cpu().numpy(), dX.cpu().numpy(), dW.cpu().numpy()
+    Y64, SY = O.conv3D_f64(X, W, sh, sw, ph, pw, threads=8)
+    Y64 = Y64 + B.astype(np.float64)
+    SY = SY + np.abs(B).astype(np.float64)
+    dX64, SX = O.deconv3D_deltaX_f64(dY, W, IH, IW, sh, sw, ph, pw, threads=8)
+    dW64, SW = O.deconv3D_deltaW_f64(X, dY, FH, FW, sh, sw, ph, pw, threads=8)
+    res.update(case=name, mode=mode, status=status, fwd=metrics(Y, Y64, SY), dx=metrics(dX, dX64, SX),
+               dw=metrics(dW, dW64, SW))
+    record(res)
+    return res, (X, W, B, dY, Y, dX, dW)
+
+
+@pytest.mark.parametrize("mode", ["3xtf32", "tf32"])
+@pytest.mark.parametrize("name", list(CASES))
+def test_layer_parity(pkg, eng, oracle_mod, name, mode):
+    res, _ = _run_case(pkg, eng, oracle_mod, name, mode)
+    assert res["status"] == 0, "kernel status word %d" % res["status"]
+    tol = TOL[mode]
+    for op in ("fwd", "dx", "dw"):
+        m = res[op]
+        assert m["finite"], (op, m)
+        assert m["norm"] <= tol["norm"], (op, res[op + "_algo"], m)
+        assert m["comp"] <= tol["comp"], (op, res[op + "_algo"], m)
+
+
+@pytest.mark.parametrize("name", ["cfg1_32x32_ic16_oc32", "ic64_oc64_14x14", "stride2_3x3"])
+def test_reference_acceptance_thresholds(pkg, eng, oracle_mod, name):
+    """The reference's own pass criteria on its own kind of inputs (uniform [0,1))."""
+    O = oracle_mod
+    res, (X, W, B, dY, Y, dX, dW) = _run_case(pkg, eng, O, name, "3xtf32", dists=("u01", "u01", "u01"))
+    N, IH, IW, IC, OC, FH, FW, sh, sw, ph, pw = CASES[name]
+    Yo = O.add_bias_row(O.conv3D_naive(X, W, sh, sw, ph, pw, threads=8), B)
+    dXo = O.deconv3D_deltaX_img2col(dY, W, IH, IW, sh, sw, ph, pw, threads=8)
+    dWo = O.deconv3d_deltaW_naive(X, dY, FH, FW, sh, sw, ph, pw, threads=8)
+    assert O.samePercentRelative(Yo, Y, 1e-5) >= 0.999
+    assert O.samePercentRelative(dXo, dX, 1e-4) >= 0.999
+    assert O.samePercentRelative(dWo, dW, 1e-5) == 1.0
+
+
+def test_algo_selection(pkg, eng, oracle_mod):
+    """Shapes with channel counts that are multiples of 32 must run on the tensor path."""
+    res, _ = _run_case(pkg, eng, oracle_mod, "ic64_oc64_14x14", "3xtf32")
+    assert res["fwd_algo"] == "igemm" and res["dx_algo"] == "igemm" and res["dw_algo"] == "dw"
