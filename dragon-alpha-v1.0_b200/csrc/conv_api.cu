@@ -150,7 +150,8 @@ static uint32_t desc_layout_for_row_bytes(int row_bytes)
 // NHWC activation tensor [N,H,W,C] as an im2col-mode map over (C, W, H, N).
 // Base pixels run over w in [-pad_w, W + pad_w - (FW-1)) with step sw, likewise for h.
 static int make_im2col_map(CUtensorMap* m, const float* base, int N, int H, int W, int C, int FH,
-                           int FW, int sh, int sw, int pad_h, int pad_w, int channels, int pixels)
+                           int FW, int sh, int sw, int pad_h, int pad_w, int channels, int pixels,
+                           CUtensorMapSwizzle swz)
 {
     cuuint64_t dims[4] = {(cuuint64_t)C, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)N};
     cuuint64_t strides[3] = {(cuuint64_t)C * 4, (cuuint64_t)W * C * 4, (cuuint64_t)H * W * C * 4};
@@ -159,7 +160,7 @@ static int make_im2col_map(CUtensorMap* m, const float* base, int N, int H, int 
     cuuint32_t estr[4] = {1, (cuuint32_t)sw, (cuuint32_t)sh, 1};
     CUresult r = g_encodeIm2col(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(base), dims,
                                 strides, lower, upper, (cuuint32_t)channels, (cuuint32_t)pixels, estr,
-                                CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_for_row_bytes(channels * 4),
+                                CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
                                 CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     // Drivers up to CUDA 13.1 set a descriptor bit for im2col maps that must be clear when the
     // tensor is smaller than 128 KiB (the same correction CUTLASS applies after encoding).
@@ -176,12 +177,12 @@ static int make_im2col_map(CUtensorMap* m, const float* base, int N, int H, int 
 }
 
 static int make_tiled_map(CUtensorMap* m, const float* base, int rank, const cuuint64_t* dims,
-                          const cuuint64_t* strides_bytes, const cuuint32_t* box, int inner_bytes)
+                          const cuuint64_t* strides_bytes, const cuuint32_t* box, CUtensorMapSwizzle swz)
 {
     cuuint32_t estr[5] = {1, 1, 1, 1, 1};
     CUresult r = g_encodeTiled(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)rank,
                                const_cast<float*>(base), dims, strides_bytes, box, estr,
-                               CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_for_row_bytes(inner_bytes),
+                               CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
                                CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
         return fail(ALPHA_E_CUDA, "cuTensorMapEncodeTiled failed (%d), rank %d box0 %u", (int)r, rank, box[0]);
@@ -290,16 +291,16 @@ static int launch_igemm(DeviceCtx* c, const IgemmPlan& pl, int mode3x, cudaStrea
 
     CUtensorMap tmA, tmB;
     int rc = make_im2col_map(&tmA, pl.act, pl.aN, pl.aH, pl.aW, pl.aC, pl.FH, pl.FW, pl.sh, pl.sw,
-                             pl.pad_h, pl.pad_w, KC, kBM);
+                             pl.pad_h, pl.pad_w, KC, kBM, swizzle_for_row_bytes(KC * 4));
     if (rc) return rc;
     cuuint64_t wd[3] = {(cuuint64_t)pl.wIC, (cuuint64_t)pl.FH * pl.FW, (cuuint64_t)pl.wOC};
     cuuint64_t ws[2] = {(cuuint64_t)pl.wIC * 4, (cuuint64_t)pl.FH * pl.FW * pl.wIC * 4};
     if (!pl.b_mn) {
         cuuint32_t box[3] = {(cuuint32_t)KC, 1, (cuuint32_t)BN};
-        rc = make_tiled_map(&tmB, pl.W, 3, wd, ws, box, KC * 4);
+        rc = make_tiled_map(&tmB, pl.W, 3, wd, ws, box, swizzle_for_row_bytes(KC * 4));
     } else {
         cuuint32_t box[3] = {32, 1, (cuuint32_t)KC};
-        rc = make_tiled_map(&tmB, pl.W, 3, wd, ws, box, 128);
+        rc = make_tiled_map(&tmB, pl.W, 3, wd, ws, box, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
     }
     if (rc) return rc;
 
@@ -489,12 +490,13 @@ int alpha_conv3d_deltaW(const AlphaConvShape* s, const float* X, const float* de
     const size_t smem = (size_t)stages * stage + (3 * stages + 2) * 8 + 1024;
 
     CUtensorMap tmX, tmDY;
-    rc = make_im2col_map(&tmX, X, s->N, s->IH, s->IW, s->IC, s->FH, s->FW, s->sh, s->sw, s->ph, s->pw, 32, p.KP);
+    rc = make_im2col_map(&tmX, X, s->N, s->IH, s->IW, s->IC, s->FH, s->FW, s->sh, s->sw, s->ph, s->pw, 32, p.KP,
+                         CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
     if (rc) return rc;
     cuuint64_t dd[2] = {(cuuint64_t)s->OC, (cuuint64_t)p.Npix};
     cuuint64_t ds[1] = {(cuuint64_t)s->OC * 4};
     cuuint32_t box[2] = {32, (cuuint32_t)p.KP};
-    rc = make_tiled_map(&tmDY, deltaY, 2, dd, ds, box, 128);
+    rc = make_tiled_map(&tmDY, deltaY, 2, dd, ds, box, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
     if (rc) return rc;
 
     dim3 grid(groups, n_tiles, splits);

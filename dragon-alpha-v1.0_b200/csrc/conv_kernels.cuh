@@ -190,11 +190,11 @@ __global__ void __launch_bounds__(kIgemmThreads)
                     const uint32_t acc = (it | kk) ? 1u : 0u;
                     const uint32_t a_off = kk * 32, b_off = p.b_mn ? kk * 1024 : kk * 32;
                     const uint64_t ad = make_smem_desc(a_hi + a_off, 16, sbo_k, p.swz);
-                    const uint64_t bd = p.b_mn ? make_smem_desc(b_hi + b_off, p.KC * 128, 1024, kSwizzle128B)
+                    const uint64_t bd = p.b_mn ? make_smem_desc(b_hi + b_off, p.KC * 128, 512, kSwizzle128B_Base32B)
                                                : make_smem_desc(b_hi + b_off, 16, sbo_k, p.swz);
                     if (p.mode3x) {
                         const uint64_t adl = make_smem_desc(a_lo + a_off, 16, sbo_k, p.swz);
-                        const uint64_t bdl = p.b_mn ? make_smem_desc(b_lo + b_off, p.KC * 128, 1024, kSwizzle128B)
+                        const uint64_t bdl = p.b_mn ? make_smem_desc(b_lo + b_off, p.KC * 128, 512, kSwizzle128B_Base32B)
                                                     : make_smem_desc(b_lo + b_off, 16, sbo_k, p.swz);
                         mma_tf32_ss(tmem_base, adl, bd, p.idesc, acc);
                         mma_tf32_ss(tmem_base, ad, bdl, p.idesc, 1u);
@@ -380,11 +380,11 @@ __global__ void __launch_bounds__(kIgemmThreads)
                 for (int kk = 0; kk < p.KP / 8; ++kk) {
                     const uint32_t acc = (ci | kk) ? 1u : 0u;
                     const uint32_t off = kk * 1024;
-                    const uint64_t ad = make_smem_desc(a_hi + off, blk_bytes, 1024, kSwizzle128B);
-                    const uint64_t bd = make_smem_desc(b_hi + off, blk_bytes, 1024, kSwizzle128B);
+                    const uint64_t ad = make_smem_desc(a_hi + off, blk_bytes, 512, kSwizzle128B_Base32B);
+                    const uint64_t bd = make_smem_desc(b_hi + off, blk_bytes, 512, kSwizzle128B_Base32B);
                     if (p.mode3x) {
-                        const uint64_t adl = make_smem_desc(a_lo + off, blk_bytes, 1024, kSwizzle128B);
-                        const uint64_t bdl = make_smem_desc(b_lo + off, blk_bytes, 1024, kSwizzle128B);
+                        const uint64_t adl = make_smem_desc(a_lo + off, blk_bytes, 512, kSwizzle128B_Base32B);
+                        const uint64_t bdl = make_smem_desc(b_lo + off, blk_bytes, 512, kSwizzle128B_Base32B);
                         mma_tf32_ss(d, adl, bd, p.idesc, acc);
                         mma_tf32_ss(d, ad, bdl, p.idesc, 1u);
                         mma_tf32_ss(d, ad, bd, p.idesc, 1u);

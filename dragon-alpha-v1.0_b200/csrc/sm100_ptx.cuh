@@ -199,14 +199,18 @@ __device__ __forceinline__ void tmem_ld_wait()
 
 // ---- tcgen05.mma ----------------------------------------------------------------------------
 
-enum : uint32_t { kSwizzleNone = 0, kSwizzle128B = 2, kSwizzle64B = 4, kSwizzle32B = 6 };
+// kSwizzle128B_Base32B swizzles 32-byte chunks inside a 128-byte row over groups of 4 rows; it is
+// the only layout tcgen05 accepts for MN-major 32-bit (tf32) operands and pairs with the TMA mode
+// CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B.
+enum : uint32_t { kSwizzleNone = 0, kSwizzle128B_Base32B = 1, kSwizzle128B = 2, kSwizzle64B = 4, kSwizzle32B = 6 };
 
 // Shared-memory matrix descriptor (sm_100 format, descriptor version 1).
 //   addr      : byte address in shared memory of the (sub)tile
 //   lbo, sbo  : leading / stride byte offsets
 //   K-major,  swizzled rows of 128/64/32 B: sbo = distance between groups of 8 rows; lbo unused.
-//   MN-major, 128 B swizzle: a block is 32 elements (128 B) wide and 8 K-rows deep (1024 B);
-//             sbo = distance between 8-row K groups, lbo = distance between 32-wide MN blocks.
+//   MN-major tf32 (kSwizzle128B_Base32B): a block is 32 elements (128 B) wide, its swizzle atom
+//             4 K-rows deep (512 B); sbo = distance between 4-row K groups, lbo = distance between
+//             32-wide MN blocks.  One K=8 instruction spans two atoms.
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo,
                                                    uint32_t layout)
 {
