@@ -1,0 +1,65 @@
+"""Generates tests/golden/conv_golden.npz.
+
+Run in a container that has the reference checkout (so that `make -C oracle ref` has built
+oracle/_ref/libref_cpu.so).  For each small seeded case the file stores the inputs and
+  ref_*   outputs of the reference project's own C++ loops (CONV_3D_NAIVE, deconv3D_deltaX_img2col,
+          deconv3D_deltaW_img2col2), compiled unmodified from the checkout;
+  java_*  outputs of the C restatement of the Java loops (Tense.conv3D_naive, deconv3d_deltaW_naive),
+          which no JVM-less machine can run in the original; they are stored as a regression anchor
+          and must stay within fp32 round-off of the ref_* values.
+The GPU box has no reference checkout; the committed file is what travels.
+"""
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, ROOT)
+import oracle as O  # noqa: E402
+
+# name: (N, IH, IW, IC, OC, FH, FW, sh, sw, ph, pw, input distribution)
+CASES = {
+    "g_3x3_s1_p1": (2, 8, 8, 8, 12, 3, 3, 1, 1, 1, 1, "u11"),
+    "g_3x3_s2_p1": (2, 9, 7, 8, 8, 3, 3, 2, 2, 1, 1, "u11"),
+    "g_4x4_s2_p1": (2, 8, 8, 4, 8, 4, 4, 2, 2, 1, 1, "n01"),
+    "g_5x5_s1_p2": (1, 7, 9, 8, 4, 5, 5, 1, 1, 2, 2, "u01"),
+    "g_1x1": (2, 6, 6, 16, 8, 1, 1, 1, 1, 0, 0, "u11"),
+    "g_3x3_nopad": (2, 7, 7, 4, 4, 3, 3, 1, 1, 0, 0, "u01"),
+    "g_ic32_oc32": (2, 6, 6, 32, 32, 3, 3, 1, 1, 1, 1, "n01"),
+}
+
+
+def gen(shape, dist, rng):
+    if dist == "u11":
+        return rng.uniform(-1, 1, shape).astype(np.float32)
+    if dist == "u01":
+        return rng.uniform(0, 1, shape).astype(np.float32)
+    return rng.standard_normal(shape).astype(np.float32)
+
+
+def main():
+    if O.ref_lib() is None:
+        raise SystemExit("oracle/_ref/libref_cpu.so is missing: run `make -C oracle ref` first")
+    out = {}
+    for i, (name, c) in enumerate(CASES.items()):
+        N, IH, IW, IC, OC, FH, FW, sh, sw, ph, pw, dist = c
+        rng = np.random.Generator(np.random.Philox(1000 + i))
+        OH, OW = O.out_hw(IH, IW, FH, FW, sh, sw, ph, pw)
+        X = gen((N, IH, IW, IC), dist, rng)
+        W = gen((OC, FH, FW, IC), dist, rng)
+        dY = gen((N, OH, OW, OC), dist, rng)
+        out[name + "/shape"] = np.array(c[:11], np.int32)
+        out[name + "/X"], out[name + "/W"], out[name + "/dY"] = X, W, dY
+        out[name + "/ref_Y"] = O.ref_CONV_3D_NAIVE(X, W, sh, sw, ph, pw)
+        out[name + "/ref_dX"] = O.ref_deconv3D_deltaX_img2col(dY, W, IH, IW, sh, sw, ph, pw)
+        out[name + "/ref_dW"] = O.ref_deconv3D_deltaW_img2col2(X, dY, FH, FW, sh, sw, ph, pw)
+        out[name + "/java_Y"] = O.conv3D_naive(X, W, sh, sw, ph, pw)
+        out[name + "/java_dW"] = O.deconv3d_deltaW_naive(X, dY, FH, FW, sh, sw, ph, pw)
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "conv_golden.npz")
+    np.savez_compressed(path, **out)
+    print("wrote", path, os.path.getsize(path), "bytes")
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,101 @@
+"""CPU tests of the C-ABI boundary: the library loads without a GPU, exports every symbol the
+public headers declare, validates arguments before touching a device, and the JNI entry points
+drive a JNIEnv function table the way the specification lays it out."""
+import ctypes as C
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+INCLUDE = os.path.join(ROOT, "include")
+
+
+@pytest.fixture(scope="module")
+def lib(pkg):
+    pkg.submodule("build").build()
+    return pkg.submodule("lib").load()
+
+
+def _declared_symbols():
+    names = set()
+    for fn in sorted(os.listdir(INCLUDE)):
+        text = open(os.path.join(INCLUDE, fn)).read()
+        text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+        names.update(re.findall(r"\b(alpha_(?:conv|Cuda|engine)\w*)\s*\(", text))
+        names.update(re.findall(r"\b(Java_z_dragon_\w+)\s*\(", text))
+    return sorted(names)
+
+
+def test_every_declared_symbol_is_exported(lib):
+    names = _declared_symbols()
+    assert len([n for n in names if n.startswith("Java_")]) == 29
+    assert len([n for n in names if n.startswith("alpha_Cuda_")]) == 29
+    missing = [n for n in names if not hasattr(lib, n)]
+    assert not missing, missing
+
+
+def test_argument_errors_come_before_any_device_work(lib, pkg):
+    L = pkg.submodule("lib")
+    s = L.AlphaConvShape(4, 8, 8, 6, 8, 3, 3, 8, 8, 1, 1, 1, 1)  # IC = 6 is not a multiple of 4
+    rc = lib.alpha_conv3d_forward(C.byref(s), 16, 32, None, 48, None)
+    assert rc == -1 and b"multiples of 4" in lib.alpha_conv_last_error()
+    s = L.AlphaConvShape(4, 8, 8, 8, 8, 3, 3, 8, 8, 1, 1, 1, 1)
+    assert lib.alpha_conv3d_forward(C.byref(s), None, 32, None, 48, None) == -1  # null X
+    assert lib.alpha_conv3d_forward(C.byref(s), 20, 32, None, 48, None) == -1  # misaligned X
+    s = L.AlphaConvShape(4, 8, 8, 8, 8, 3, 3, 9, 9, 1, 1, 1, 1)  # OH/OW too large for IH/IW
+    assert lib.alpha_conv3d_deltaW(C.byref(s), 16, 32, 48, None) == -1
+    assert lib.alpha_conv_set_math_mode(7) == -1
+    assert lib.alpha_Cuda_dconv3D_deltaW_buf_summary(0, None, None, 3, 64) == -1
+
+
+def test_no_silent_fallback_without_a_gpu(lib, pkg):
+    """On a machine without a B200 a well-formed call fails loudly; there is no CPU path."""
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    L = pkg.submodule("lib")
+    s = L.AlphaConvShape(4, 8, 8, 8, 8, 3, 3, 8, 8, 1, 1, 1, 1)
+    rc = lib.alpha_conv3d_forward(C.byref(s), 16, 32, None, 48, None)
+    assert rc in (-2, -3)
+    with pytest.raises(L.AlphaConvError):
+        L.check(rc)
+
+
+def test_jni_entry_points_use_the_jnienv_table(lib):
+    """A fake JNIEnv with functions at the specification's slots (FindClass 6, ThrowNew 14,
+    GetLongArrayRegion 204, ExceptionCheck 228): the shim must fetch the stream array through it and
+    turn a failed call into a pending z.dragon.engine.cuda.impl.CudaException."""
+    log = {}
+    FINDCLASS = C.CFUNCTYPE(C.c_void_p, C.c_void_p, C.c_char_p)
+    THROWNEW = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_void_p, C.c_char_p)
+    GETREGION = C.CFUNCTYPE(None, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_int64))
+    EXCCHECK = C.CFUNCTYPE(C.c_uint8, C.c_void_p)
+
+    def find_class(env, name):
+        log["class"] = name
+        return 0x1234
+
+    def throw_new(env, cls, msg):
+        log["thrown"] = (cls, msg)
+        return 0
+
+    def get_region(env, arr, start, n, buf):
+        log["region"] = (arr, start, n)
+        for i in range(n):
+            buf[i] = 0
+    cbs = [FINDCLASS(find_class), THROWNEW(throw_new), GETREGION(get_region), EXCCHECK(lambda env: 0)]
+    table = (C.c_void_p * 235)()
+    for slot, cb in zip((6, 14, 204, 228), cbs):
+        table[slot] = C.cast(cb, C.c_void_p)
+    env = C.pointer(C.c_void_p(C.addressof(table)))  # JNIEnv*: pointer to {const table*}
+
+    f = lib.Java_z_dragon_engine_cuda_impl_math_Cuda_1conv3D_conv3D_1GemmR
+    f.restype = None
+    f.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_int, C.c_int64, C.c_int64,
+                  C.c_int, C.c_int, C.c_int64] + [C.c_int] * 9
+    # null tensor addresses: the call must fail in the argument check, on any machine
+    f(env, None, 0xABCD, 2, 0, 8, 8, 0, 0, 3, 3, 0, 8, 8, 4, 8, 8, 1, 1, 1, 1)
+    assert log["region"] == (0xABCD, 0, 2)
+    assert log["class"] == b"z/dragon/engine/cuda/impl/CudaException"
+    assert log["thrown"][0] == 0x1234 and b"null" in log["thrown"][1]

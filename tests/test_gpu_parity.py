@@ -108,3 +108,71 @@ def test_algo_selection(pkg, eng, oracle_mod):
     """Shapes with channel counts that are multiples of 32 must run on the tensor path."""
     res, _ = _run_case(pkg, eng, oracle_mod, "ic64_oc64_14x14", "3xtf32")
     assert res["fwd_algo"] == "igemm" and res["dx_algo"] == "igemm" and res["dw_algo"] == "dw"
+
+
+EDGE_CASES = {
+    "one_pixel_image": (4, 1, 1, 32, 32, 3, 3, 1, 1, 1, 1),
+    "single_image_tiny": (1, 3, 3, 8, 4, 3, 3, 1, 1, 1, 1),
+    "wide_pad_5x5_on_2x2": (4, 2, 2, 32, 32, 5, 5, 1, 1, 2, 2),
+    "m_is_one_tile_plus_one": (1, 43, 3, 32, 32, 3, 3, 1, 1, 1, 1),
+    "oc4_ic64": (4, 6, 6, 64, 4, 3, 3, 1, 1, 1, 1),
+    "stride3_7x7": (4, 20, 20, 32, 32, 7, 7, 3, 3, 3, 3),
+    "floor_division_output": (4, 10, 10, 32, 32, 3, 3, 2, 2, 0, 0),
+}
+CASES.update(EDGE_CASES)
+
+
+@pytest.mark.parametrize("name", list(EDGE_CASES))
+def test_edge_cases(pkg, eng, oracle_mod, name):
+    res, _ = _run_case(pkg, eng, oracle_mod, name, "3xtf32")
+    assert res["status"] == 0
+    for op in ("fwd", "dx", "dw"):
+        m = res[op]
+        assert m["finite"] and m["norm"] <= TOL["3xtf32"]["norm"] and m["comp"] <= TOL["3xtf32"]["comp"], (op, m)
+
+
+def test_golden_vectors(pkg, eng):
+    """Outputs of the reference's own compiled CPU loops (tests/golden/conv_golden.npz)."""
+    import os
+    import torch
+    lib = pkg.submodule("lib")
+    lib.set_math_mode("3xtf32")
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "conv_golden.npz"))
+    dev = torch.device("cuda:0")
+    for name in sorted({k.split("/")[0] for k in g.files}):
+        N, IH, IW, IC, OC, FH, FW, sh, sw, ph, pw = (int(v) for v in g[name + "/shape"])
+        X, W, dY = (torch.from_numpy(g[name + "/" + k]).to(dev) for k in ("X", "W", "dY"))
+        Y = eng.conv3D(X, W, sh, sw, ph, pw).cpu().numpy()
+        dX = eng.dconv3D_deltaX(dY, W, IH, IW, sh, sw, ph, pw).cpu().numpy()
+        dW = eng.dconv3D_deltaW(X, dY, FH, FW, sh, sw, ph, pw).cpu().numpy()
+        assert lib.device_status() == 0
+        for got, key in ((Y, "ref_Y"), (dX, "ref_dX"), (dW, "ref_dW")):
+            ref = g[name + "/" + key]
+            assert np.abs(got - ref).max() <= 1e-4 * np.abs(ref).max(), (name, key)
+
+
+def test_full_size_adjoint_identity(pkg, eng):
+    """At the benchmark's full size (X[256,56,56,64]) the oracle is too slow; the three kernels are
+    tied together instead by <conv(X,W), dY> = <X, deltaX(dY,W)> = <W, deltaW(X,dY)>."""
+    import torch
+    lib = pkg.submodule("lib")
+    lib.set_math_mode("3xtf32")
+    dev = torch.device("cuda:0")
+    gen = torch.Generator(device=dev).manual_seed(11)
+    N, HW, Cc = 256, 56, 64
+    X = torch.randn((N, HW, HW, Cc), device=dev, generator=gen).relu_()
+    W = torch.randn((Cc, 3, 3, Cc), device=dev, generator=gen) * (2.0 / (9 * Cc)) ** 0.5
+    dY = torch.randn((N, HW, HW, Cc), device=dev, generator=gen)
+    Y = eng.conv3D(X, W, 1, 1, 1, 1)
+    dX = eng.dconv3D_deltaX(dY, W, HW, HW, 1, 1, 1, 1)
+    dW = eng.dconv3D_deltaW(X, dY, 3, 3, 1, 1, 1, 1)
+    assert lib.device_status() == 0
+
+    def dot(a, b):
+        return float((a.double() * b.double()).sum())
+    a, b, c = dot(Y, dY), dot(X, dX), dot(W, dW)
+    scale = float(Y.double().norm() * dY.double().norm()) / (Y.numel() ** 0.5)
+    assert abs(a - b) <= 1e-4 * scale and abs(a - c) <= 1e-4 * scale, (a, b, c, scale)
+    # linearity in the weights: conv(X, 2W) = 2 conv(X, W) exactly (scaling by 2 is exact in fp32)
+    Y2 = eng.conv3D(X, W * 2, 1, 1, 1, 1)
+    assert torch.equal(Y2, Y * 2)
