@@ -319,6 +319,63 @@ int launch_buf_summary(cudaStream_t stream, const float* buf, float* deltaW, int
     return check_launch("dw_reduce_kernel");
 }
 
+
+// ---- deltaW without any allocation ---------------------------------------------------------------
+//
+// Some hosts of this library must not allocate device memory at call time: a Java caller whose
+// mempool has handed the whole card to the framework (Dragon-Alpha's engine owns every byte it
+// could get and hands natives only addresses), a caller running inside a region where the CUDA
+// allocator is off limits, or a real-time loop that cannot afford a cudaMalloc stall.  For them the
+// split-K partials of deltaW live in this fixed array instead of the growable workspace.  Every
+// GPU on which the library is loaded holds the array until the process exits.
+constexpr size_t kNoAllocScratchBytes = 32ull << 20;  // 32 MiB
+static __device__ __align__(256) float g_noalloc_scratch[kNoAllocScratchBytes / sizeof(float)];
+static __device__ int g_noalloc_status;               // kernel status word of this entry point
+
+struct NoAllocCtx {
+    bool init = false;
+    int sm_count = 0;
+    float* scratch = nullptr;  // device address of g_noalloc_scratch on this device
+    int* status = nullptr;     // device address of g_noalloc_status on this device
+};
+static NoAllocCtx g_noalloc_ctx[64];
+
+// Once per device, with that device current: resolves the device addresses of the two symbols.
+// In host code the names g_noalloc_scratch / g_noalloc_status are only handles; a kernel must be
+// given the addresses cudaGetSymbolAddress returns.
+static int get_noalloc_ctx(NoAllocCtx** out)
+{
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail(ALPHA_E_CUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
+    if (dev < 0 || dev >= 64) return fail(ALPHA_E_DEVICE, "device index %d out of range", dev);
+    std::lock_guard<std::mutex> lock(g_mu);
+    NoAllocCtx& c = g_noalloc_ctx[dev];
+    if (!c.init) {
+        int major = 0, sms = 0;
+        e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+        if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess) return fail(ALPHA_E_CUDA, "cudaDeviceGetAttribute: %s", cudaGetErrorString(e));
+        if (major != 10) return fail(ALPHA_E_DEVICE, "device %d is not sm_100; this library is built for sm_100a only", dev);
+        int rc = load_driver_entry_points();
+        if (rc) return rc;
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+        if (e != cudaSuccess || !p) return fail(ALPHA_E_CUDA, "cudaGetSymbolAddress(scratch): %s", cudaGetErrorString(e));
+        c.scratch = static_cast<float*>(p);
+        p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_noalloc_status);
+        if (e != cudaSuccess || !p) return fail(ALPHA_E_CUDA, "cudaGetSymbolAddress(status): %s", cudaGetErrorString(e));
+        c.status = static_cast<int*>(p);
+        e = cudaFuncSetAttribute(conv_dw_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (e != cudaSuccess) return fail(ALPHA_E_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+        c.sm_count = sms;
+        c.init = true;
+    }
+    *out = &c;
+    return ALPHA_OK;
+}
+
 }  // namespace alpha
 
 using namespace alpha;
@@ -511,6 +568,113 @@ int alpha_conv3d_deltaW(const AlphaConvShape* s, const float* X, const float* de
         rc = check_launch("dw_reduce_kernel");
     }
     return rc;
+}
+
+size_t alpha_conv3d_deltaW_noalloc_capacity(void) { return kNoAllocScratchBytes; }
+
+int alpha_conv3d_deltaW_noalloc(const AlphaConvShape* s, const float* X, const float* deltaY, float* deltaW,
+                                alpha_stream_t stream_)
+{
+    int rc = check_shape(s, X, deltaY, deltaW);
+    if (rc) return rc;
+    if (s->IC % 32 != 0 || s->ph >= 128 || s->pw >= 128 || s->FH > 256 || s->FW > 256)
+        return fail(ALPHA_E_ARG, "deltaW_noalloc runs the tensor-core kernel only: IC must be a multiple of 32 (IC=%d)", s->IC);
+    NoAllocCtx* c;
+    rc = get_noalloc_ctx(&c);
+    if (rc) return rc;
+    cudaStream_t stream = (cudaStream_t)stream_;
+
+    // Same tiling and split choice as alpha_conv3d_deltaW, so that both entry points return the
+    // same bits for the same input.
+    const int mode3x = g_math.load() == ALPHA_MATH_3XTF32;
+    DwParams p{};
+    p.status = c->status;
+    p.Npix = s->N * s->OH * s->OW;
+    p.OHo = s->OH; p.OWo = s->OW; p.sh = s->sh; p.sw = s->sw; p.ph = s->ph; p.pw = s->pw;
+    p.FH = s->FH; p.FW = s->FW; p.IC = s->IC; p.OC = s->OC;
+    p.icb = s->IC / 32;
+    p.MB = s->FH * s->FW * p.icb;
+    int BN = ((s->OC + 31) / 32) * 32;
+    if (BN > 256) BN = 256;
+    p.BN = BN;
+    const int MT = (p.MB + 3) / 4;
+    int G = 512 / BN;
+    if (G > MT) G = MT;
+    const int groups = (MT + G - 1) / G;
+    G = (MT + groups - 1) / groups;
+    p.G = G;
+    p.KP = 32;
+    p.tmem_cols = pow2_cols(G * BN);
+    p.idesc = make_idesc_tf32(kBM, BN, true, true);
+    p.mode3x = mode3x;
+    const int n_tiles = (s->OC + BN - 1) / BN;
+    p.total_chunks = (p.Npix + p.KP - 1) / p.KP;
+    int splits = c->sm_count / (groups * n_tiles);
+    if (splits < 1) splits = 1;
+    if (splits > p.total_chunks) splits = p.total_chunks;
+    p.chunks_per_split = (p.total_chunks + splits - 1) / splits;
+    splits = (p.total_chunks + p.chunks_per_split - 1) / p.chunks_per_split;
+    const size_t sizeW = (size_t)s->OC * s->FH * s->FW * s->IC;
+    if (splits > 1) {
+        const size_t need = sizeW * splits * sizeof(float);
+        if (need > kNoAllocScratchBytes)
+            return fail(ALPHA_E_NOSCRATCH,
+                        "deltaW_noalloc: %d split-K partials of %zu floats need %zu bytes, the fixed scratch holds %zu; "
+                        "use alpha_conv3d_deltaW for this shape",
+                        splits, sizeW, need, (size_t)kNoAllocScratchBytes);
+        p.out = c->scratch;
+        p.split_stride = sizeW;
+    } else {
+        p.out = deltaW;
+        p.split_stride = 0;
+    }
+    const uint32_t blk = p.KP * 128;
+    const uint32_t stage = (4 * blk + (BN / 32) * blk) * (mode3x ? 2 : 1);
+    int stages = (int)((200u * 1024) / stage);
+    if (stages > 6) stages = 6;
+    if (stages < 1) return fail(ALPHA_E_ARG, "deltaW stage of %u bytes does not fit shared memory", stage);
+    p.stages = stages;
+    const size_t smem = (size_t)stages * stage + (3 * stages + 2) * 8 + 1024;
+
+    CUtensorMap tmX, tmDY;
+    rc = make_im2col_map(&tmX, X, s->N, s->IH, s->IW, s->IC, s->FH, s->FW, s->sh, s->sw, s->ph, s->pw, 32, p.KP,
+                         CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
+    if (rc) return rc;
+    cuuint64_t dd[2] = {(cuuint64_t)s->OC, (cuuint64_t)p.Npix};
+    cuuint64_t ds[1] = {(cuuint64_t)s->OC * 4};
+    cuuint32_t box[2] = {32, (cuuint32_t)p.KP};
+    rc = make_tiled_map(&tmDY, deltaY, 2, dd, ds, box, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
+    if (rc) return rc;
+
+    dim3 grid(groups, n_tiles, splits);
+    conv_dw_kernel<<<grid, kIgemmThreads, smem, stream>>>(tmX, tmDY, p);
+    note_launch("dw_noalloc");
+    rc = check_launch("conv_dw_kernel");
+    if (rc) return rc;
+    if (splits > 1) {
+        const size_t n4 = sizeW / 4;
+        dw_reduce_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, stream>>>(c->scratch, sizeW, splits, deltaW, n4, 0);
+        note_launch("dw_noalloc");
+        rc = check_launch("dw_reduce_kernel");
+    }
+    return rc;
+}
+
+int alpha_conv3d_deltaW_noalloc_status(void)
+{
+    NoAllocCtx* c;
+    int rc = get_noalloc_ctx(&c);
+    if (rc) return rc;
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return fail(ALPHA_E_CUDA, "cudaDeviceSynchronize: %s", cudaGetErrorString(e));
+    int h = 0;
+    e = cudaMemcpy(&h, c->status, sizeof(int), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return fail(ALPHA_E_CUDA, "cudaMemcpy(status): %s", cudaGetErrorString(e));
+    if (h != 0) {
+        cudaMemset(c->status, 0, sizeof(int));
+        fail(ALPHA_E_KERNEL, "the no-allocation deltaW kernel left status %d", h);
+    }
+    return h;
 }
 
 }  // extern "C"

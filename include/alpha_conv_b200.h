@@ -35,6 +35,7 @@ extern "C" {
 #define ALPHA_E_CUDA (-2)     /* a CUDA runtime or driver call failed */
 #define ALPHA_E_DEVICE (-3)   /* not an sm_100 device */
 #define ALPHA_E_KERNEL (-4)   /* a kernel reported a protocol error in its status word */
+#define ALPHA_E_NOSCRATCH (-5) /* the problem needs more scratch than alpha_conv3d_deltaW_noalloc owns */
 
 /* math mode of the tensor-core kernels */
 #define ALPHA_MATH_3XTF32 0 /* default: hi/lo split, three TF32 MMAs per product, fp32-faithful */
@@ -90,6 +91,30 @@ int alpha_conv3d_deltaX(const AlphaConvShape* s, const float* deltaY, const floa
  * workspace that the library allocates on first use and grows on demand. */
 int alpha_conv3d_deltaW(const AlphaConvShape* s, const float* X, const float* deltaY, float* deltaW,
                         alpha_stream_t stream);
+
+/* deltaW for callers that cannot allocate device memory when they call.
+ * (No counterpart in the reference: its natives get every buffer, scratch included, from the Java
+ * mempool.)  A host such as Dragon-Alpha's engine claims the card's memory for its own pool up front
+ * and gives natives nothing but addresses, so a cudaMalloc inside a native can fail or stall; other
+ * callers sit in code that must never block on the allocator.  This entry point therefore calls no
+ * cudaMalloc, cudaFree or any allocating routine.  The split-K partial sums, which
+ * alpha_conv3d_deltaW keeps in a growable workspace, go into one fixed array of
+ * alpha_conv3d_deltaW_noalloc_capacity() bytes (32 MiB) that is part of the library image: every GPU
+ * on which the library is loaded holds it until the process exits.
+ *   - Shapes whose partial sums need more than that return ALPHA_E_NOSCRATCH; shapes the tensor-core
+ *     kernel does not take (IC not a multiple of 32) return ALPHA_E_ARG.  Results are the same bits
+ *     alpha_conv3d_deltaW produces.
+ *   - The first call on each device looks up the array's device address (with that device current);
+ *     make that first call before starting any stream capture.
+ *   - All calls on one device share the array, and it keeps what the last call left in it.  The
+ *     kernel overwrites every partial it later reads, so nothing has to be cleared between calls,
+ *     but two calls whose GPU work overlaps (different streams) race on it: serialise them.
+ *   - Kernel protocol errors of this entry point are reported by alpha_conv3d_deltaW_noalloc_status()
+ *     (synchronises the device; 0 = clean), not by alpha_conv_device_status(). */
+int alpha_conv3d_deltaW_noalloc(const AlphaConvShape* s, const float* X, const float* deltaY,
+                                float* deltaW, alpha_stream_t stream);
+size_t alpha_conv3d_deltaW_noalloc_capacity(void);
+int alpha_conv3d_deltaW_noalloc_status(void);
 
 /* ---- layer 2: the reference's natives ------------------------------------------------------- */
 /* `streams` holds `length` cudaStream_t values as 64-bit integers, as the Java side passes them;
