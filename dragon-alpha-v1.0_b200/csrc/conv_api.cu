@@ -1,6 +1,7 @@
 // Host side of layer 1 of the C ABI: shape checks, tensor-map construction, tile choice, launches.
 #include "../../include/alpha_conv_b200.h"
 #include "conv_kernels.cuh"
+#include "conv_halo.cuh"
 #include "host_common.h"
 
 #include <atomic>
@@ -8,6 +9,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <map>
 #include <mutex>
 
 namespace alpha {
@@ -58,8 +60,12 @@ struct DeviceCtx {
     int sm_count = 0;
     int cc_major = 0;
     int* status = nullptr;       // device status word
-    float* workspace = nullptr;  // split-K partials
-    size_t workspace_bytes = 0;
+    unsigned long long* prof = nullptr;  // cycle counters, allocated when ALPHA_CONV_PROF=1
+    // Scratch per (device, stream): split-K partials of deltaW and the hi/lo planes of W.  Work on
+    // one stream is ordered, so calls that share a stream can share its block; calls on different
+    // streams get different blocks and may overlap freely.
+    struct Block { float* ptr = nullptr; size_t bytes = 0; };
+    std::map<cudaStream_t, Block> workspace;
 };
 static DeviceCtx g_ctx[64];
 static std::mutex g_mu;
@@ -104,33 +110,48 @@ int get_ctx(DeviceCtx** out)
         e = cudaMalloc(&c.status, sizeof(int));
         if (e != cudaSuccess) return fail(ALPHA_E_CUDA, "cudaMalloc(status): %s", cudaGetErrorString(e));
         cudaMemset(c.status, 0, sizeof(int));
+        if (getenv("ALPHA_CONV_PROF") && atoi(getenv("ALPHA_CONV_PROF")) > 0) {
+            if (cudaMalloc(&c.prof, kProfSlots * sizeof(unsigned long long)) == cudaSuccess)
+                cudaMemset(c.prof, 0, kProfSlots * sizeof(unsigned long long));
+            else
+                c.prof = nullptr;
+        }
         c.sm_count = prop.multiProcessorCount;
         c.cc_major = prop.major;
         const int max_smem = 227 * 1024;
         cudaFuncSetAttribute(conv_igemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
         cudaFuncSetAttribute(conv_dw_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+        cudaFuncSetAttribute(conv_halo_kernel<0, 0, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+        cudaFuncSetAttribute(conv_halo_kernel<3, 1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+        cudaFuncSetAttribute(conv_halo_kernel<3, 1, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+        cudaFuncSetAttribute(conv_halo_kernel<3, 1, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+        cudaFuncSetAttribute(conv_halo_kernel<3, 2, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+        cudaFuncSetAttribute(conv_halo_kernel<3, 2, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
         c.init = true;
     }
     *out = &c;
     return ALPHA_OK;
 }
 
-// Grows the per-device split-K workspace.  Work already enqueued may still read the old block,
-// so the old block is released only after the device has drained.
-static int ensure_workspace(DeviceCtx* c, size_t bytes)
+// Returns the scratch block of `stream`, grown to at least `bytes`.  Growing waits for the stream
+// to drain first, because work already enqueued on it may still use the old block.
+static int get_workspace(DeviceCtx* c, cudaStream_t stream, size_t bytes, float** out)
 {
     std::lock_guard<std::mutex> lock(g_mu);
-    if (c->workspace_bytes >= bytes) return ALPHA_OK;
-    if (c->workspace) {
-        cudaDeviceSynchronize();
-        cudaFree(c->workspace);
-        c->workspace = nullptr;
-        c->workspace_bytes = 0;
+    DeviceCtx::Block& b = c->workspace[stream];
+    if (b.bytes < bytes) {
+        if (b.ptr) {
+            cudaStreamSynchronize(stream);
+            cudaFree(b.ptr);
+            b.ptr = nullptr;
+            b.bytes = 0;
+        }
+        const size_t want = bytes + (bytes >> 2);
+        cudaError_t e = cudaMalloc(&b.ptr, want);
+        if (e != cudaSuccess) return fail(ALPHA_E_CUDA, "cudaMalloc(workspace %zu B): %s", want, cudaGetErrorString(e));
+        b.bytes = want;
     }
-    size_t want = bytes + (bytes >> 2);
-    cudaError_t e = cudaMalloc(&c->workspace, want);
-    if (e != cudaSuccess) return fail(ALPHA_E_CUDA, "cudaMalloc(workspace %zu B): %s", want, cudaGetErrorString(e));
-    c->workspace_bytes = want;
+    *out = b.ptr;
     return ALPHA_OK;
 }
 
@@ -310,6 +331,189 @@ static int launch_igemm(DeviceCtx* c, const IgemmPlan& pl, int mode3x, cudaStrea
     return check_launch("conv_igemm_kernel");
 }
 
+// ---- halo-tile kernel (stride 1): plan and launch -------------------------------------------------
+
+static int env_int(const char* name, int dflt)
+{
+    const char* e = getenv(name);
+    return (e && *e) ? atoi(e) : dflt;
+}
+
+// 0 = choose by cost model, 1 = always the per-tap im2col kernel, 2 = halo kernel wherever it applies
+static int env_tile_mode()
+{
+    const char* e = getenv("ALPHA_CONV_TILE");
+    if (!e) return 0;
+    if (!strcmp(e, "im2col")) return 1;
+    if (!strcmp(e, "halo")) return 2;
+    return 0;
+}
+
+struct HaloChoice {
+    bool valid = false;
+    int JH = 1, JW = 1, npb = 1, sb = 2, acc_bufs = 1;
+    bool row = false;
+    double cost = 0, eff = 0;
+};
+
+// Picks the macro-tile shape.  Cost = estimated SM cycles per useful output pixel: the larger of the
+// MMA issue time and the L2->SM transfer time, divided by the fraction of tile pixels that are
+// real, with small penalties for single-buffered patches / accumulators.
+// The row-staged specialisations that exist (FW, JH, JW); everything else runs the generic form.
+static bool halo_has_row_kernel(int FW, int JH, int JW)
+{
+    if (FW != 3) return false;
+    return (JH == 1 && (JW == 1 || JW == 2 || JW == 4)) || (JH == 2 && (JW == 1 || JW == 2));
+}
+
+static HaloChoice plan_halo(const IgemmPlan& pl, int BN, int mode3x, int b_mn)
+{
+    HaloChoice best;
+    const int taps = pl.FH * pl.FW, kchunks = pl.kdim / 32;
+    const int planes = mode3x ? 2 : 1;
+    const uint32_t b_tx = b_mn ? (BN / 32) * 4096 : BN * 128;
+    const uint32_t b_tile = ((b_tx + 1023) & ~1023u) * planes;
+    const bool allow_row = env_int("ALPHA_HALO_ROW", 1) != 0;
+    const int force_jh = env_int("ALPHA_HALO_JH", 0), force_jw = env_int("ALPHA_HALO_JW", 0);
+    const size_t smem_cap = 226 * 1024;
+    for (int JH = 1; JH <= 2; ++JH)
+        for (int JW = 1; JW <= 4; ++JW) {
+            if (force_jh && JH != force_jh) continue;
+            if (force_jw && JW != force_jw) continue;
+            const int J = JH * JW;
+            if (J * BN > 512) continue;
+            const int PH = 16 * JH + pl.FH - 1, PW = 8 * JW + pl.FW - 1;
+            if (PH > 256 || PW > 256) continue;
+            const uint32_t patch_stride = (((uint32_t)PH * PW * 128 + 1023) & ~1023u) * planes;
+            bool row = allow_row && halo_has_row_kernel(pl.FW, JH, JW);
+            uint32_t b_stride = b_tile * (row ? pl.FW : 1);
+            if (row && (size_t)patch_stride + 2 * (size_t)b_stride + 32768 + 1536 > smem_cap) { row = false; b_stride = b_tile; }
+            const int max_sb = row ? pl.FH * 2 : 8;
+            int npb = 2, sb = row ? 3 : 4;
+            auto need = [&](int a, int b) { return (size_t)a * patch_stride + (size_t)b * b_stride + 32768 + 512 + 1024; };
+            while (need(npb, sb) > smem_cap && sb > 2) --sb;
+            if (need(npb, sb) > smem_cap) { npb = 1; sb = 4; while (need(npb, sb) > smem_cap && sb > 2) --sb; }
+            if (need(npb, sb) > smem_cap) continue;
+            while (sb < max_sb && need(npb, sb + 1) <= smem_cap && sb < taps) ++sb;
+            const int acc_bufs = (2 * J * BN <= 512) ? 2 : 1;
+            const int rbk = (pl.oH + 16 * JH - 1) / (16 * JH), cbk = (pl.oW + 8 * JW - 1) / (8 * JW);
+            const double eff = (double)pl.oH * pl.oW / ((double)rbk * 16 * JH * cbk * 8 * JW);
+            // cycles per macro tile
+            const double mma_clk = (BN / 2.0 > (4096.0 + BN * 32.0) / 128.0) ? BN / 2.0 : (4096.0 + BN * 32.0) / 128.0;
+            const double t_mma = (double)taps * kchunks * 4 * (mode3x ? 3 : 1) * J * mma_clk;
+            const double bytes = (double)kchunks * ((double)PH * PW * 128 + (double)taps * b_tx);
+            const double t_l2 = bytes / 40.0;  // ~40 B/clk/SM of L2->SM bandwidth when all SMs pull
+            double t = (t_mma > t_l2 ? t_mma : t_l2) + 1500.0;  // fixed per-tile overhead
+            if (npb == 1) t *= 1.10;
+            if (acc_bufs == 1) t *= 1.10;
+            const double cost = t / (128.0 * J * eff);
+            if (!best.valid || cost < best.cost) {
+                best.valid = true; best.JH = JH; best.JW = JW; best.npb = npb; best.sb = sb;
+                best.acc_bufs = acc_bufs; best.cost = cost; best.eff = eff; best.row = row;
+            }
+        }
+    return best;
+}
+
+// Returns 1 when the shape is left to the per-tap kernel, 0 on launch, < 0 on error.
+static int launch_halo(DeviceCtx* c, const IgemmPlan& pl, int mode3x, cudaStream_t stream)
+{
+    const int tile_mode = env_tile_mode();
+    if (tile_mode == 1) return 1;
+    if (pl.sh != 1 || pl.sw != 1 || pl.kdim % 32 != 0) return 1;
+    const int gran = pl.b_mn ? 32 : 16;
+    int BN = ((pl.ncols + gran - 1) / gran) * gran;
+    if (BN > 256) BN = (pl.ncols % 256 == 0 || pl.ncols > 512) ? 256 : 128;
+    HaloChoice ch = plan_halo(pl, BN, mode3x, pl.b_mn);
+    if (!ch.valid) return 1;
+    if (tile_mode == 0 && ch.eff < 0.6) return 1;
+
+    HaloParams p{};
+    p.out = pl.out; p.bias = pl.bias; p.status = c->status; p.prof = c->prof;
+    p.N = pl.aN; p.OH = pl.oH; p.OW = pl.oW;
+    p.Ncols = pl.ncols; p.ldo = pl.ncols;
+    p.FH = pl.FH; p.FW = pl.FW; p.pad_h = pl.pad_h; p.pad_w = pl.pad_w;
+    p.kchunks = pl.kdim / 32;
+    p.BN = BN; p.n_tiles = (pl.ncols + BN - 1) / BN;
+    p.JH = ch.JH; p.JW = ch.JW;
+    p.PH = 16 * ch.JH + pl.FH - 1; p.PW = 8 * ch.JW + pl.FW - 1;
+    p.row_blocks = (pl.oH + 16 * ch.JH - 1) / (16 * ch.JH);
+    p.col_blocks = (pl.oW + 8 * ch.JW - 1) / (8 * ch.JW);
+    const long long total = (long long)p.n_tiles * p.N * p.row_blocks * p.col_blocks;
+    if (total > 2147483647LL) return 1;
+    p.total_tiles = (int)total;
+    p.npb = ch.npb; p.sb = ch.sb; p.acc_bufs = ch.acc_bufs;
+    p.mode3x = mode3x; p.b_mn = pl.b_mn; p.flip = pl.flip;
+    p.idesc = make_idesc_tf32(kBM, BN, false, pl.b_mn);
+    p.tmem_cols = pow2_cols(ch.acc_bufs * ch.JH * ch.JW * BN);
+    p.patch_tx = (uint32_t)p.PH * p.PW * 128;
+    p.patch_bytes = (p.patch_tx + 1023) & ~1023u;
+    p.b_tx = pl.b_mn ? (BN / 32) * 4096 : BN * 128;
+    p.b_bytes = (p.b_tx + 1023) & ~1023u;
+    const uint32_t planes = mode3x ? 2 : 1;
+    const int tps = ch.row ? pl.FW : 1;
+    const size_t smem = (size_t)p.npb * p.patch_bytes * planes + (size_t)p.sb * p.b_bytes * planes * tps + 32768 +
+                        (3 * p.npb + 3 * p.sb + 5) * 8 + 1024;
+
+    CUtensorMap tmA, tmB;
+    cuuint64_t ad[4] = {(cuuint64_t)pl.aC, (cuuint64_t)pl.aW, (cuuint64_t)pl.aH, (cuuint64_t)pl.aN};
+    cuuint64_t as[3] = {(cuuint64_t)pl.aC * 4, (cuuint64_t)pl.aW * pl.aC * 4, (cuuint64_t)pl.aH * pl.aW * pl.aC * 4};
+    cuuint32_t abox[4] = {32, (cuuint32_t)p.PW, (cuuint32_t)p.PH, 1};
+    int rc = make_tiled_map(&tmA, pl.act, 4, ad, as, abox, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    // 3xTF32: split W into hi/lo planes once per call (scratch of this stream), load both by TMA
+    const float* w_hi = pl.W;
+    const float* w_lo = pl.W;
+    if (mode3x) {
+        const size_t nW = (size_t)pl.wOC * pl.FH * pl.FW * pl.wIC;
+        float* ws = nullptr;
+        rc = get_workspace(c, stream, 2 * nW * sizeof(float), &ws);
+        if (rc) return rc;
+        const size_t n4 = nW / 4;
+        size_t blocks = (n4 + 255) / 256;
+        if (blocks > (size_t)c->sm_count * 8) blocks = (size_t)c->sm_count * 8;
+        split_tensor_kernel<<<(unsigned)blocks, 256, 0, stream>>>(reinterpret_cast<const float4*>(pl.W),
+                                                                   reinterpret_cast<float4*>(ws),
+                                                                   reinterpret_cast<float4*>(ws + nW), n4);
+        note_launch("split_w");
+        rc = check_launch("split_tensor_kernel");
+        if (rc) return rc;
+        w_hi = ws;
+        w_lo = ws + nW;
+    }
+    CUtensorMap tmBlo, tmO;
+    cuuint64_t wd[3] = {(cuuint64_t)pl.wIC, (cuuint64_t)pl.FH * pl.FW, (cuuint64_t)pl.wOC};
+    cuuint64_t wst[2] = {(cuuint64_t)pl.wIC * 4, (cuuint64_t)pl.FH * pl.FW * pl.wIC * 4};
+    if (!pl.b_mn) {
+        cuuint32_t box[3] = {32, 1, (cuuint32_t)BN};
+        rc = make_tiled_map(&tmB, w_hi, 3, wd, wst, box, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (!rc) rc = make_tiled_map(&tmBlo, w_lo, 3, wd, wst, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    } else {
+        cuuint32_t box[3] = {32, 1, 32};
+        rc = make_tiled_map(&tmB, w_hi, 3, wd, wst, box, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
+        if (!rc) rc = make_tiled_map(&tmBlo, w_lo, 3, wd, wst, box, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
+    }
+    if (rc) return rc;
+    // output [N][OH][OW][ldo] for the epilogue's TMA stores: one slab = 32 channels x 8 columns x 16 rows
+    cuuint64_t od[4] = {(cuuint64_t)pl.ncols, (cuuint64_t)pl.oW, (cuuint64_t)pl.oH, (cuuint64_t)pl.aN};
+    cuuint64_t ost[3] = {(cuuint64_t)pl.ncols * 4, (cuuint64_t)pl.oW * pl.ncols * 4, (cuuint64_t)pl.oH * pl.oW * pl.ncols * 4};
+    cuuint32_t obox[4] = {32, 8, 16, 1};
+    rc = make_tiled_map(&tmO, pl.out, 4, od, ost, obox, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    int grid = c->sm_count < p.total_tiles ? c->sm_count : p.total_tiles;
+#define HALO_LAUNCH(FW_, JH_, JW_) conv_halo_kernel<FW_, JH_, JW_><<<grid, kHaloThreads, smem, stream>>>(tmA, tmB, tmBlo, tmO, p)
+    if (!ch.row) HALO_LAUNCH(0, 0, 0);
+    else if (ch.JH == 1 && ch.JW == 1) HALO_LAUNCH(3, 1, 1);
+    else if (ch.JH == 1 && ch.JW == 2) HALO_LAUNCH(3, 1, 2);
+    else if (ch.JH == 1 && ch.JW == 4) HALO_LAUNCH(3, 1, 4);
+    else if (ch.JH == 2 && ch.JW == 1) HALO_LAUNCH(3, 2, 1);
+    else HALO_LAUNCH(3, 2, 2);
+#undef HALO_LAUNCH
+    note_launch(ch.row ? "halo_row" : "halo");
+    rc = check_launch("conv_halo_kernel");
+    return rc;
+}
+
 // deltaW += sum of `part` split-K buffers of sizeW floats each (the reference's buf_summary).
 int launch_buf_summary(cudaStream_t stream, const float* buf, float* deltaW, int part, size_t sizeW)
 {
@@ -420,6 +624,18 @@ int alpha_conv_device_status(void)
     return h;
 }
 
+int alpha_conv_debug_counters(unsigned long long* out, int n)
+{
+    DeviceCtx* c;
+    int rc = get_ctx(&c);
+    if (rc) return rc;
+    if (!c->prof) return fail(ALPHA_E_ARG, "cycle counters are off: set ALPHA_CONV_PROF=1 before the first call");
+    if (n > kProfSlots) n = kProfSlots;
+    cudaError_t e = cudaMemcpy(out, c->prof, n * sizeof(unsigned long long), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return fail(ALPHA_E_CUDA, "cudaMemcpy(counters): %s", cudaGetErrorString(e));
+    return ALPHA_OK;
+}
+
 int alpha_conv3d_forward(const AlphaConvShape* s, const float* X, const float* W, const float* bias,
                          float* Y, alpha_stream_t stream_)
 {
@@ -441,6 +657,8 @@ int alpha_conv3d_forward(const AlphaConvShape* s, const float* X, const float* W
         pl.out = Y; pl.oH = s->OH; pl.oW = s->OW; pl.ncols = s->OC;
         pl.W = W; pl.wOC = s->OC; pl.wIC = s->IC; pl.bias = bias;
         pl.b_mn = false; pl.flip = false; pl.kdim = s->IC;
+        rc = launch_halo(c, pl, g_math.load() == ALPHA_MATH_3XTF32, stream);
+        if (rc != 1) return rc;
         return launch_igemm(c, pl, g_math.load() == ALPHA_MATH_3XTF32, stream);
     }
     const size_t total = (size_t)s->N * s->OH * s->OW * s->OC;
@@ -472,6 +690,8 @@ int alpha_conv3d_deltaX(const AlphaConvShape* s, const float* deltaY, const floa
         pl.out = deltaX; pl.oH = s->IH; pl.oW = s->IW; pl.ncols = s->IC;
         pl.W = W; pl.wOC = s->OC; pl.wIC = s->IC; pl.bias = nullptr;
         pl.b_mn = true; pl.flip = true; pl.kdim = s->OC;
+        rc = launch_halo(c, pl, g_math.load() == ALPHA_MATH_3XTF32, stream);
+        if (rc != 1) return rc;
         return launch_igemm(c, pl, g_math.load() == ALPHA_MATH_3XTF32, stream);
     }
     const size_t total = (size_t)s->N * s->IH * s->IW * s->IC;
@@ -529,10 +749,11 @@ int alpha_conv3d_deltaW(const AlphaConvShape* s, const float* X, const float* de
     p.chunks_per_split = (p.total_chunks + splits - 1) / splits;
     splits = (p.total_chunks + p.chunks_per_split - 1) / p.chunks_per_split;
     const size_t sizeW = (size_t)s->OC * s->FH * s->FW * s->IC;
+    float* ws = nullptr;
     if (splits > 1) {
-        rc = ensure_workspace(c, sizeW * splits * sizeof(float));
+        rc = get_workspace(c, stream, sizeW * splits * sizeof(float), &ws);
         if (rc) return rc;
-        p.out = c->workspace;
+        p.out = ws;
         p.split_stride = sizeW;
     } else {
         p.out = deltaW;
@@ -563,7 +784,7 @@ int alpha_conv3d_deltaW(const AlphaConvShape* s, const float* X, const float* de
     if (rc) return rc;
     if (splits > 1) {
         const size_t n4 = sizeW / 4;
-        dw_reduce_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, stream>>>(c->workspace, sizeW, splits, deltaW, n4, 0);
+        dw_reduce_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, stream>>>(ws, sizeW, splits, deltaW, n4, 0);
         note_launch("dw");
         rc = check_launch("dw_reduce_kernel");
     }

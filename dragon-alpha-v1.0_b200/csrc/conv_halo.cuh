@@ -1,0 +1,396 @@
+// Stride-1 forward conv / deltaX with each input tile fetched once.
+//
+// A persistent CTA walks macro tiles of JH x JW accumulators; one accumulator is 16 output rows x 8
+// output columns (128 tensor-memory lanes).  For every 32-channel chunk the CTA loads the input
+// patch that the macro tile needs - (16*JH + FH - 1) rows x (8*JW + FW - 1) columns of pixels,
+// 128 bytes each, zero-filled outside the image by the TMA - exactly once, and forms the A operand
+// of every filter tap as a shared-memory descriptor that starts (fh*PW + fw) pixel rows into the
+// patch: tcgen05 applies the 128-byte swizzle to absolute shared-memory addresses, so a descriptor
+// may start at any 128-byte row of a TMA-written tile, and the stride between groups of 8 rows
+// (SBO) is simply the patch pitch.  B tiles (one filter tap x 32 channels x BN) stream through a
+// ring.  In 3xTF32 mode four warps rewrite each landed patch and B tile as hi/lo planes once.
+// Accumulators are double-buffered in tensor memory when they fit, so the epilogue of one macro
+// tile overlaps the loads and MMAs of the next.
+//
+// Warps: 0 TMA producer, 1 MMA issuer (owns tensor memory), 2-5 epilogue, 6-9 operand split.
+//
+// One thread issues every MMA, and one tcgen05.mma of this shape takes 59-128 clocks, so the issue
+// loop is kept free of divisions, pointer conversions and per-iteration address arithmetic: ring
+// positions are counters, barriers and tiles are 32-bit shared-memory addresses, descriptors are a
+// constant high half plus a low half that only gets small additions.
+#pragma once
+#include "conv_kernels.cuh"
+
+namespace alpha {
+
+constexpr int kHaloThreads = 320;
+
+// Slots of the optional cycle counters (clock64 ticks of CTA 0, summed over the launch).
+enum HaloProf {
+    kProfProducerPatchWait = 0, kProfProducerBWait, kProfMmaPatchWait, kProfMmaBWait, kProfMmaAccWait,
+    kProfMmaTotal, kProfEpiWait, kProfEpiWork, kProfSplitWait, kProfSplitWork, kProfTotal, kProfSlots = 16
+};
+
+struct HaloParams {
+    float* out;          // [N][OH][OW][ldo]
+    const float* bias;   // [Ncols] or nullptr
+    int* status;
+    unsigned long long* prof;  // optional cycle counters of CTA 0 (nullptr = off), see HaloProf
+    int N, OH, OW;       // output geometry
+    int Ncols, ldo;
+    int FH, FW, pad_h, pad_w;
+    int kchunks;         // reduction channels / 32
+    int BN, n_tiles;
+    int JH, JW;          // accumulators per macro tile, vertically and horizontally
+    int PH, PW;          // patch rows and columns (pixels)
+    int row_blocks, col_blocks;
+    int total_tiles;     // n_tiles * N * row_blocks * col_blocks
+    int npb, sb;         // patch buffers, B ring stages
+    int acc_bufs;        // 1 or 2 accumulator sets
+    int mode3x, b_mn, flip;
+    uint32_t idesc, tmem_cols;
+    uint32_t patch_bytes;  // one plane of one patch buffer, multiple of 1024
+    uint32_t patch_tx;     // bytes one patch load delivers
+    uint32_t b_bytes;      // one plane of one B stage, multiple of 1024
+    uint32_t b_tx;
+};
+
+// Bounded wait that also charges the waited cycles to a counter when profiling is on.
+__device__ __forceinline__ bool wait_prof(uint32_t bar, uint32_t parity, bool prof, unsigned long long& acc)
+{
+    if (mbar_try_wait_a(bar, parity)) return true;
+    if (!prof) return mbar_wait_slow_a(bar, parity);
+    const long long t0 = clock64();
+    const bool ok = mbar_wait_slow_a(bar, parity);
+    acc += static_cast<unsigned long long>(clock64() - t0);
+    return ok;
+}
+
+// The four K=8 steps of one 32-channel chunk into one accumulator (12 MMAs in 3xTF32 mode).
+template <bool k3x>
+__device__ __forceinline__ void issue_chunk(uint32_t d, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
+                                            uint32_t b_kstep, uint32_t a_lo_off, uint32_t b_lo_off, uint32_t idesc,
+                                            uint32_t acc_first)
+{
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk) {
+        const uint32_t a_k = a_lo + kk * 2, b_k = b_lo + kk * b_kstep;
+        const uint32_t acc = kk == 0 ? acc_first : 1u;
+        if (k3x) {
+            mma_tf32_ss2(d, a_k + a_lo_off, a_hi, b_k, b_hi, idesc, acc);
+            mma_tf32_ss2(d, a_k, a_hi, b_k + b_lo_off, b_hi, idesc, 1u);
+            mma_tf32_ss2(d, a_k, a_hi, b_k, b_hi, idesc, 1u);
+        } else {
+            mma_tf32_ss2(d, a_k, a_hi, b_k, b_hi, idesc, acc);
+        }
+    }
+}
+
+// FW_T > 0 selects the row-staged specialisation: FW, JH and JW are compile-time, one B stage holds
+// the FW taps of one filter row, and the MMAs of a stage are issued as straight-line code with
+// immediate descriptor offsets.  FW_T == 0 is the generic form: any filter, one tap per B stage.
+template <int FW_T, int JH_T, int JW_T>
+__global__ void __launch_bounds__(kHaloThreads, 1)
+    conv_halo_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                     const __grid_constant__ CUtensorMap tmBlo, const __grid_constant__ CUtensorMap tmO,
+                     const HaloParams p)
+{
+    constexpr bool kRow = FW_T > 0;
+    const int tps = kRow ? FW_T : 1;              // taps per B stage
+    const int stages_per_chunk = kRow ? p.FH : p.FH * p.FW;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                               ~static_cast<uintptr_t>(1023));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t planes = p.mode3x ? 2u : 1u;
+    const uint32_t patch_stride = p.patch_bytes * planes;
+    const uint32_t b_tile = p.b_bytes * planes;   // hi (+ lo) planes of one tap
+    const uint32_t b_stride = b_tile * tps;       // one ring stage
+    uint8_t* patches = smem;
+    uint8_t* bring = smem + static_cast<size_t>(p.npb) * patch_stride;
+    uint8_t* staging = bring + static_cast<size_t>(p.sb) * b_stride;   // 2 x 16 KB epilogue slabs
+    uint64_t* bars = reinterpret_cast<uint64_t*>(staging + 2 * 16384);
+    uint64_t* patch_full = bars;
+    uint64_t* patch_ready = patch_full + p.npb;
+    uint64_t* patch_empty = patch_ready + p.npb;
+    uint64_t* b_full = patch_empty + p.npb;
+    uint64_t* b_ready = b_full + p.sb;
+    uint64_t* b_empty = b_ready + p.sb;
+    uint64_t* acc_full = b_empty + p.sb;
+    uint64_t* acc_empty = acc_full + 2;
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_empty + 2);
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < p.npb; ++i) {
+            mbar_init(&patch_full[i], 1);
+            mbar_init(&patch_ready[i], 128);
+            mbar_init(&patch_empty[i], 1);
+        }
+        for (int i = 0; i < p.sb; ++i) {
+            mbar_init(&b_full[i], 1);
+            mbar_init(&b_ready[i], 128);
+            mbar_init(&b_empty[i], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&acc_full[i], 1);
+            mbar_init(&acc_empty[i], 128);
+        }
+        fence_barrier_init();
+        prefetch_tmap(&tmA);
+        prefetch_tmap(&tmB);
+        prefetch_tmap(&tmBlo);
+        prefetch_tmap(&tmO);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_holder, p.tmem_cols);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_holder;
+
+    const int J = p.JH * p.JW;
+    const int per_img = p.row_blocks * p.col_blocks;
+    const bool prof_on = p.prof != nullptr && blockIdx.x == 0;
+    const long long t_kernel = clock64();
+
+    // 32-bit shared-memory addresses of everything the loops touch
+    const uint32_t patches_a = smem_u32(patches), bring_a = smem_u32(bring);
+    const uint32_t pfull_a = smem_u32(patch_full), pready_a = smem_u32(patch_ready), pempty_a = smem_u32(patch_empty);
+    const uint32_t bfull_a = smem_u32(b_full), bempty_a = smem_u32(b_empty);
+    const uint32_t afull_a = smem_u32(acc_full), aempty_a = smem_u32(acc_empty);
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---- TMA producer ----
+            RingPos pp, bp;
+            bool ok = true;
+            unsigned long long w_patch = 0, w_b = 0;
+            const int taps = p.FH * p.FW;
+            for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
+                const int tn = t / (p.N * per_img);
+                int r = t - tn * (p.N * per_img);
+                const int n = r / per_img;
+                r -= n * per_img;
+                const int rb = r / p.col_blocks, cb = r - rb * p.col_blocks;
+                const int h0 = rb * 16 * p.JH - p.pad_h, w0 = cb * 8 * p.JW - p.pad_w;
+                const int oc0 = tn * p.BN;
+                for (int c = 0; c < p.kchunks && ok; ++c) {
+                    if (!wait_prof(pempty_a + 8 * pp.idx, pp.phase ^ 1, prof_on, w_patch)) { report(p.status, kStatusProducerTimeout); ok = false; break; }
+                    mbar_arrive_expect_tx_a(pfull_a + 8 * pp.idx, p.patch_tx);
+                    tma_load_4d_a(patches_a + pp.idx * patch_stride, &tmA, pfull_a + 8 * pp.idx, c * 32, w0, h0, n);
+                    pp.advance(p.npb);
+                    for (int st = 0; st < stages_per_chunk; ++st) {
+                        if (!wait_prof(bempty_a + 8 * bp.idx, bp.phase ^ 1, prof_on, w_b)) { report(p.status, kStatusProducerTimeout); ok = false; break; }
+                        const uint32_t bar = bfull_a + 8 * bp.idx;
+                        mbar_arrive_expect_tx_a(bar, p.b_tx * tps * planes);
+                        for (int q = 0; q < tps; ++q) {
+                            const int tap = st * tps + q;
+                            const uint32_t b_dst = bring_a + bp.idx * b_stride + q * b_tile;
+                            if (!p.b_mn) {
+                                tma_load_3d_a(b_dst, &tmB, bar, c * 32, tap, oc0);
+                                if (p.mode3x) tma_load_3d_a(b_dst + p.b_bytes, &tmBlo, bar, c * 32, tap, oc0);
+                            } else {
+                                const int tapw = p.flip ? (taps - 1 - tap) : tap;
+                                for (int j = 0; j < p.BN / 32; ++j) {
+                                    tma_load_3d_a(b_dst + j * 4096, &tmB, bar, oc0 + j * 32, tapw, c * 32);
+                                    if (p.mode3x) tma_load_3d_a(b_dst + p.b_bytes + j * 4096, &tmBlo, bar, oc0 + j * 32, tapw, c * 32);
+                                }
+                            }
+                        }
+                        bp.advance(p.sb);
+                    }
+                }
+            }
+            if (prof_on) { p.prof[kProfProducerPatchWait] = w_patch; p.prof[kProfProducerBWait] = w_b; }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // ---- MMA issuer ----
+            RingPos pp, bp, ap;
+            bool ok = true;
+            unsigned long long w_patch = 0, w_b = 0, w_acc = 0;
+            const long long t_begin = clock64();
+            // descriptor halves that never change, and the steps of the low half (16-byte units)
+            const uint32_t a_dhi = smem_desc_hi(p.PW * 128, kSwizzle128B);
+            const uint32_t b_dhi = p.b_mn ? smem_desc_hi(512, kSwizzle128B_Base32B) : smem_desc_hi(1024, kSwizzle128B);
+            const uint32_t b_kstep = p.b_mn ? 64u : 2u;       // 1024 B or 32 B per K=8 step
+            const uint32_t a_lo_off = p.patch_bytes >> 4;     // hi plane -> lo plane
+            const uint32_t b_lo_off = p.b_bytes >> 4;
+            const uint32_t row_step = p.PW * 8u;              // one patch row down
+            const uint32_t jh_step = 16u * row_step;          // 16 patch rows down
+            const uint32_t patch_lo0 = smem_desc_lo(patches_a, 16), patch_stride16 = patch_stride >> 4;
+            const uint32_t bring_lo0 = smem_desc_lo(bring_a, p.b_mn ? 4096u : 16u), b_stride16 = b_stride >> 4;
+            const uint32_t pwait_a = p.mode3x ? pready_a : pfull_a, bwait_a = bfull_a;  // weights arrive pre-split
+            const uint32_t acc_cols = J * p.BN;
+            for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
+                if (!wait_prof(aempty_a + 8 * ap.idx, ap.phase ^ 1, prof_on, w_acc)) { report(p.status, kStatusMmaTimeout); ok = false; break; }
+                tc_fence_after_sync();
+                const uint32_t d0 = tmem_base + ap.idx * acc_cols;
+                uint32_t acc_first = 0u;  // the very first MMA into each accumulator overwrites it
+                for (int c = 0; c < p.kchunks && ok; ++c) {
+                    if (!wait_prof(pwait_a + 8 * pp.idx, pp.phase, prof_on, w_patch)) { report(p.status, kStatusMmaTimeout); ok = false; break; }
+                    tc_fence_after_sync();
+                    uint32_t a_row = patch_lo0 + pp.idx * patch_stride16;
+                    if constexpr (kRow) {
+                        constexpr uint32_t kPW8 = (8 * JW_T + FW_T - 1) * 8;  // one patch row, in 16-byte units
+                        const uint32_t b_tile16 = b_tile >> 4;
+                        for (int fh = 0; fh < p.FH; ++fh, a_row += kPW8) {
+                            if (!wait_prof(bwait_a + 8 * bp.idx, bp.phase, prof_on, w_b)) { report(p.status, kStatusMmaTimeout); ok = false; break; }
+                            tc_fence_after_sync();
+                            const uint32_t bl = bring_lo0 + bp.idx * b_stride16;
+                            if (p.mode3x) {
+#pragma unroll
+                                for (int fw = 0; fw < FW_T; ++fw)
+#pragma unroll
+                                    for (int jh = 0; jh < JH_T; ++jh)
+#pragma unroll
+                                        for (int jw = 0; jw < JW_T; ++jw)
+                                            issue_chunk<true>(d0 + (jh * JW_T + jw) * p.BN, a_row + fw * 8 + jh * 16 * kPW8 + jw * 64,
+                                                              a_dhi, bl + fw * b_tile16, b_dhi, b_kstep, a_lo_off, b_lo_off, p.idesc,
+                                                              fw == 0 ? acc_first : 1u);
+                            } else {
+#pragma unroll
+                                for (int fw = 0; fw < FW_T; ++fw)
+#pragma unroll
+                                    for (int jh = 0; jh < JH_T; ++jh)
+#pragma unroll
+                                        for (int jw = 0; jw < JW_T; ++jw)
+                                            issue_chunk<false>(d0 + (jh * JW_T + jw) * p.BN, a_row + fw * 8 + jh * 16 * kPW8 + jw * 64,
+                                                               a_dhi, bl + fw * b_tile16, b_dhi, b_kstep, a_lo_off, b_lo_off, p.idesc,
+                                                               fw == 0 ? acc_first : 1u);
+                            }
+                            acc_first = 1u;
+                            mma_commit_a(bempty_a + 8 * bp.idx);
+                            bp.advance(p.sb);
+                        }
+                    } else {
+                    for (int fh = 0; fh < p.FH && ok; ++fh, a_row += row_step) {
+                        uint32_t a_tap = a_row;
+                        for (int fw = 0; fw < p.FW; ++fw, a_tap += 8) {
+                            if (!wait_prof(bwait_a + 8 * bp.idx, bp.phase, prof_on, w_b)) { report(p.status, kStatusMmaTimeout); ok = false; break; }
+                            tc_fence_after_sync();
+                            const uint32_t bl = bring_lo0 + bp.idx * b_stride16;
+                            uint32_t d = d0, a_jh = a_tap;
+                            for (int jh = 0; jh < p.JH; ++jh, a_jh += jh_step) {
+                                uint32_t a_j = a_jh;
+                                for (int jw = 0; jw < p.JW; ++jw, a_j += 64, d += p.BN) {
+                                    if (p.mode3x) issue_chunk<true>(d, a_j, a_dhi, bl, b_dhi, b_kstep, a_lo_off, b_lo_off, p.idesc, acc_first);
+                                    else issue_chunk<false>(d, a_j, a_dhi, bl, b_dhi, b_kstep, a_lo_off, b_lo_off, p.idesc, acc_first);
+                                }
+                            }
+                            acc_first = 1u;
+                            mma_commit_a(bempty_a + 8 * bp.idx);
+                            bp.advance(p.sb);
+                        }
+                    }
+                    }
+                    mma_commit_a(pempty_a + 8 * pp.idx);
+                    pp.advance(p.npb);
+                }
+                mma_commit_a(afull_a + 8 * ap.idx);
+                ap.advance(p.acc_bufs);
+            }
+            if (prof_on) {
+                p.prof[kProfMmaPatchWait] = w_patch; p.prof[kProfMmaBWait] = w_b; p.prof[kProfMmaAccWait] = w_acc;
+                p.prof[kProfMmaTotal] = static_cast<unsigned long long>(clock64() - t_begin);
+            }
+        }
+        __syncwarp();
+    } else if (warp < 6) {
+        // ---- epilogue: warps 2..5, lane quadrant = warp % 4 ----
+        const int quad = warp & 3;
+        const int row = quad * 32 + lane;       // accumulator row = g*8 + i
+        RingPos ap;
+        unsigned long long w_acc = 0;
+        const long long t_begin = clock64();
+        const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
+        const uint32_t stage_a = smem_u32(staging);
+        uint32_t sbuf = 0;
+        for (int t = blockIdx.x; t < p.total_tiles; t += gridDim.x) {
+            if (!wait_prof(afull_a + 8 * ap.idx, ap.phase, prof_on, w_acc)) { report(p.status, kStatusEpilogueTimeout); break; }
+            tc_fence_after_sync();
+            const int tn = t / (p.N * per_img);
+            int r = t - tn * (p.N * per_img);
+            const int n = r / per_img;
+            r -= n * per_img;
+            const int rb = r / p.col_blocks, cb = r - rb * p.col_blocks;
+            const int n0 = tn * p.BN;
+            int j = 0;
+            for (int jh = 0; jh < p.JH; ++jh)
+                for (int jw = 0; jw < p.JW; ++jw, ++j) {
+                    const int oh0 = (rb * p.JH + jh) * 16, ow0 = (cb * p.JW + jw) * 8;
+                    if (oh0 >= p.OH || ow0 >= p.OW) continue;  // accumulator entirely outside the image
+                    const uint32_t tcol = lane_base + (ap.idx * J + j) * p.BN;
+                    for (int c = 0; c < p.BN; c += 32) {
+                        const int col0 = n0 + c;
+                        if (col0 >= p.Ncols) break;
+                        // slab `sbuf` was last read by the store issued two slabs ago
+                        if (threadIdx.x == 64) tma_store_wait_read<1>();
+                        named_barrier_sync(1, 128);
+                        uint32_t v[32];
+                        tmem_ld_32x32(tcol + c, v);
+                        tmem_ld_wait();
+                        const uint32_t srow = stage_a + sbuf * 16384 + row * 128;
+#pragma unroll
+                        for (int q = 0; q < 8; ++q) {
+                            float4 o = make_float4(__uint_as_float(v[4 * q]), __uint_as_float(v[4 * q + 1]),
+                                                   __uint_as_float(v[4 * q + 2]), __uint_as_float(v[4 * q + 3]));
+                            if (p.bias && col0 + 4 * q < p.Ncols) {
+                                const float4 b = *reinterpret_cast<const float4*>(p.bias + col0 + 4 * q);
+                                o.x += b.x; o.y += b.y; o.z += b.z; o.w += b.w;
+                            }
+                            // 128-byte swizzle: 16-byte chunk q of row r lives at chunk q ^ (r & 7)
+                            st_shared_v4(srow + ((q ^ (row & 7)) << 4), o);
+                        }
+                        fence_proxy_async_smem();
+                        named_barrier_sync(1, 128);
+                        if (threadIdx.x == 64) {
+                            tma_store_4d_a(&tmO, stage_a + sbuf * 16384, col0, ow0, oh0, n);
+                            tma_store_commit();
+                        }
+                        sbuf ^= 1u;
+                    }
+                }
+            tc_fence_before_sync();
+            mbar_arrive_a(aempty_a + 8 * ap.idx);
+            ap.advance(p.acc_bufs);
+        }
+        if (threadIdx.x == 64) tma_store_wait_all();  // the slabs must outlive their stores
+        if (prof_on && threadIdx.x == 64) {
+            p.prof[kProfEpiWait] = w_acc;
+            p.prof[kProfEpiWork] = static_cast<unsigned long long>(clock64() - t_begin) - w_acc;
+        }
+    } else {
+        // ---- operand split (3xTF32 only): warps 6..9 ----
+        if (p.mode3x) {
+            const int tid128 = threadIdx.x - 192;
+            RingPos pp;
+            bool ok = true;
+            unsigned long long w_in = 0;
+            const long long t_begin = clock64();
+            for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
+                for (int c = 0; c < p.kchunks && ok; ++c) {
+                    if (!wait_prof(pfull_a + 8 * pp.idx, pp.phase, prof_on, w_in)) { report(p.status, kStatusSplitTimeout); ok = false; break; }
+                    uint8_t* ph = patches + static_cast<size_t>(pp.idx) * patch_stride;
+                    split_plane_x4(ph, ph + p.patch_bytes, p.patch_tx, tid128, 128);
+                    fence_proxy_async_smem();
+                    mbar_arrive_a(pready_a + 8 * pp.idx);
+                    pp.advance(p.npb);
+                }
+            }
+            if (prof_on && threadIdx.x == 192) {
+                p.prof[kProfSplitWait] = w_in;
+                p.prof[kProfSplitWork] = static_cast<unsigned long long>(clock64() - t_begin) - w_in;
+            }
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (prof_on && threadIdx.x == 0) p.prof[kProfTotal] = static_cast<unsigned long long>(clock64() - t_kernel);
+    if (warp == 1) tmem_dealloc(tmem_base, p.tmem_cols);
+}
+
+}  // namespace alpha

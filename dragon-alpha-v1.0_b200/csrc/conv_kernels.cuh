@@ -93,6 +93,39 @@ __device__ __forceinline__ void split_plane(uint8_t* hi_plane, uint8_t* lo_plane
     }
 }
 
+// Same, four vectors per thread in flight so that the shared-memory latencies overlap.
+__device__ __forceinline__ void split_plane_x4(uint8_t* hi_plane, uint8_t* lo_plane, uint32_t bytes, int tid, int nthreads)
+{
+    float4* h = reinterpret_cast<float4*>(hi_plane);
+    float4* l = reinterpret_cast<float4*>(lo_plane);
+    const uint32_t nvec = bytes >> 4, n = nthreads;
+    uint32_t v = tid;
+    for (; v + 3 * n < nvec; v += 4 * n) {
+        float4 a0 = h[v], a1 = h[v + n], a2 = h[v + 2 * n], a3 = h[v + 3 * n], b0, b1, b2, b3;
+        split_tf32(a0, b0); split_tf32(a1, b1); split_tf32(a2, b2); split_tf32(a3, b3);
+        h[v] = a0; h[v + n] = a1; h[v + 2 * n] = a2; h[v + 3 * n] = a3;
+        l[v] = b0; l[v + n] = b1; l[v + 2 * n] = b2; l[v + 3 * n] = b3;
+    }
+    for (; v < nvec; v += n) {
+        float4 a = h[v], b;
+        split_tf32(a, b);
+        h[v] = a;
+        l[v] = b;
+    }
+}
+
+// hi/lo planes of a whole tensor in global memory (weights are split once per call, not per tile).
+__global__ void split_tensor_kernel(const float4* __restrict__ src, float4* __restrict__ hi, float4* __restrict__ lo, size_t n4)
+{
+    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n4;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        float4 a = src[i], b;
+        split_tf32(a, b);
+        hi[i] = a;
+        lo[i] = b;
+    }
+}
+
 __global__ void __launch_bounds__(kIgemmThreads)
     conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA,
                       const __grid_constant__ CUtensorMap tmB, const IgemmParams p)
@@ -170,8 +203,12 @@ __global__ void __launch_bounds__(kIgemmThreads)
     } else if (warp == 1) {
         if (lane == 0) {
             // ---- MMA issuer ----
-            const uint32_t row_bytes = p.KC * 4;
-            const uint32_t sbo_k = 8 * row_bytes;
+            const uint32_t sbo_k = 8 * p.KC * 4;  // 8 rows of KC floats
+            const uint32_t a_dhi = smem_desc_hi(sbo_k, p.swz);
+            const uint32_t b_dhi = p.b_mn ? smem_desc_hi(512, kSwizzle128B_Base32B) : smem_desc_hi(sbo_k, p.swz);
+            const uint32_t b_lbo = p.b_mn ? p.KC * 128u : 16u;
+            const uint32_t b_kstep = p.b_mn ? 64u : 2u;
+            const uint32_t a_lo_off = p.a_bytes >> 4, b_lo_off = p.b_bytes >> 4;
             bool ok = true;
             for (int it = 0; it < num_it && ok; ++it) {
                 const int s = it % S;
@@ -182,25 +219,18 @@ __global__ void __launch_bounds__(kIgemmThreads)
                     break;
                 }
                 tc_fence_after_sync();
-                const uint32_t a_hi = smem_u32(smem + static_cast<size_t>(s) * stage_bytes);
-                const uint32_t a_lo = a_hi + p.a_bytes;
-                const uint32_t b_hi = a_hi + p.a_bytes * planes;
-                const uint32_t b_lo = b_hi + p.b_bytes;
+                const uint32_t a_addr = smem_u32(smem + static_cast<size_t>(s) * stage_bytes);
+                const uint32_t al = smem_desc_lo(a_addr, 16);
+                const uint32_t bl = smem_desc_lo(a_addr + p.a_bytes * planes, b_lbo);
                 for (int kk = 0; kk < p.KC / 8; ++kk) {
                     const uint32_t acc = (it | kk) ? 1u : 0u;
-                    const uint32_t a_off = kk * 32, b_off = p.b_mn ? kk * 1024 : kk * 32;
-                    const uint64_t ad = make_smem_desc(a_hi + a_off, 16, sbo_k, p.swz);
-                    const uint64_t bd = p.b_mn ? make_smem_desc(b_hi + b_off, p.KC * 128, 512, kSwizzle128B_Base32B)
-                                               : make_smem_desc(b_hi + b_off, 16, sbo_k, p.swz);
+                    const uint32_t a_k = al + kk * 2, b_k = bl + kk * b_kstep;
                     if (p.mode3x) {
-                        const uint64_t adl = make_smem_desc(a_lo + a_off, 16, sbo_k, p.swz);
-                        const uint64_t bdl = p.b_mn ? make_smem_desc(b_lo + b_off, p.KC * 128, 512, kSwizzle128B_Base32B)
-                                                    : make_smem_desc(b_lo + b_off, 16, sbo_k, p.swz);
-                        mma_tf32_ss(tmem_base, adl, bd, p.idesc, acc);
-                        mma_tf32_ss(tmem_base, ad, bdl, p.idesc, 1u);
-                        mma_tf32_ss(tmem_base, ad, bd, p.idesc, 1u);
+                        mma_tf32_ss2(tmem_base, a_k + a_lo_off, a_dhi, b_k, b_dhi, p.idesc, acc);
+                        mma_tf32_ss2(tmem_base, a_k, a_dhi, b_k + b_lo_off, b_dhi, p.idesc, 1u);
+                        mma_tf32_ss2(tmem_base, a_k, a_dhi, b_k, b_dhi, p.idesc, 1u);
                     } else {
-                        mma_tf32_ss(tmem_base, ad, bd, p.idesc, acc);
+                        mma_tf32_ss2(tmem_base, a_k, a_dhi, b_k, b_dhi, p.idesc, acc);
                     }
                 }
                 mma_commit(&empty[s]);
@@ -363,6 +393,7 @@ __global__ void __launch_bounds__(kIgemmThreads)
         __syncwarp();
     } else if (warp == 1) {
         if (lane == 0) {
+            const uint32_t dhi = smem_desc_hi(512, kSwizzle128B_Base32B);
             for (int it = 0; it < num_it; ++it) {
                 const int s = it % S;
                 const uint32_t par = (it / S) & 1;
@@ -373,23 +404,18 @@ __global__ void __launch_bounds__(kIgemmThreads)
                 tc_fence_after_sync();
                 const int ci = it / g_count, g = it - ci * g_count;
                 const uint32_t d = tmem_base + g * p.BN;
-                const uint32_t a_hi = smem_u32(smem + static_cast<size_t>(s) * stage_bytes);
-                const uint32_t a_lo = a_hi + a_bytes;
-                const uint32_t b_hi = a_hi + a_bytes * planes;
-                const uint32_t b_lo = b_hi + b_bytes;
+                const uint32_t a_addr = smem_u32(smem + static_cast<size_t>(s) * stage_bytes);
+                const uint32_t al = smem_desc_lo(a_addr, blk_bytes);
+                const uint32_t bl = smem_desc_lo(a_addr + a_bytes * planes, blk_bytes);
                 for (int kk = 0; kk < p.KP / 8; ++kk) {
                     const uint32_t acc = (ci | kk) ? 1u : 0u;
-                    const uint32_t off = kk * 1024;
-                    const uint64_t ad = make_smem_desc(a_hi + off, blk_bytes, 512, kSwizzle128B_Base32B);
-                    const uint64_t bd = make_smem_desc(b_hi + off, blk_bytes, 512, kSwizzle128B_Base32B);
+                    const uint32_t a_k = al + kk * 64, b_k = bl + kk * 64;  // 1024 B per K=8 step
                     if (p.mode3x) {
-                        const uint64_t adl = make_smem_desc(a_lo + off, blk_bytes, 512, kSwizzle128B_Base32B);
-                        const uint64_t bdl = make_smem_desc(b_lo + off, blk_bytes, 512, kSwizzle128B_Base32B);
-                        mma_tf32_ss(d, adl, bd, p.idesc, acc);
-                        mma_tf32_ss(d, ad, bdl, p.idesc, 1u);
-                        mma_tf32_ss(d, ad, bd, p.idesc, 1u);
+                        mma_tf32_ss2(d, a_k + (a_bytes >> 4), dhi, b_k, dhi, p.idesc, acc);
+                        mma_tf32_ss2(d, a_k, dhi, b_k + (b_bytes >> 4), dhi, p.idesc, 1u);
+                        mma_tf32_ss2(d, a_k, dhi, b_k, dhi, p.idesc, 1u);
                     } else {
-                        mma_tf32_ss(d, ad, bd, p.idesc, acc);
+                        mma_tf32_ss2(d, a_k, dhi, b_k, dhi, p.idesc, acc);
                     }
                 }
                 mma_commit(&empty[s]);

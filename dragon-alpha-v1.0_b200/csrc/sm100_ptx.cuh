@@ -95,6 +95,59 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity)
     }
 }
 
+// The same operations on a barrier given by its 32-bit shared-memory address: issue loops keep
+// barrier addresses as integers and never convert pointers inside the loop.
+__device__ __forceinline__ bool mbar_try_wait_a(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __noinline__ bool mbar_wait_slow_a(uint32_t bar, uint32_t parity)
+{
+    const uint64_t t0 = globaltimer_ns();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 256; ++i)
+            if (mbar_try_wait_a(bar, parity)) return true;
+        if (globaltimer_ns() - t0 > kWaitLimitNs) return false;
+    }
+}
+__device__ __forceinline__ bool mbar_wait_a(uint32_t bar, uint32_t parity)
+{
+    if (mbar_try_wait_a(bar, parity)) return true;
+    return mbar_wait_slow_a(bar, parity);
+}
+__device__ __forceinline__ void mbar_arrive_a(uint32_t bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx_a(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mma_commit_a(uint32_t bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// Position in a ring of n slots with the mbarrier phase bit that goes with it.
+struct RingPos {
+    uint32_t idx = 0, phase = 0;
+    __device__ __forceinline__ void advance(uint32_t n)
+    {
+        if (++idx == n) { idx = 0; phase ^= 1u; }
+    }
+};
+
 // ---- TMA ------------------------------------------------------------------------------------
 
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* m)
@@ -145,6 +198,76 @@ __device__ __forceinline__ void tma_load_im2col_4d(void* dst, const CUtensorMap*
         "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(c), "r"(w), "r"(h), "r"(n),
         "h"(off_w), "h"(off_h)
         : "memory");
+}
+
+// Variants that take the destination and the barrier as 32-bit shared-memory addresses.
+__device__ __forceinline__ void tma_load_2d_a(uint32_t dst, const CUtensorMap* m, uint32_t bar, int c0, int c1)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+        "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(c0), "r"(c1)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_a(uint32_t dst, const CUtensorMap* m, uint32_t bar, int c0, int c1, int c2)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(dst),
+        "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_4d_a(uint32_t dst, const CUtensorMap* m, uint32_t bar, int c0, int c1, int c2, int c3)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(dst),
+        "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_im2col_4d_a(uint32_t dst, const CUtensorMap* m, uint32_t bar, int c, int w,
+                                                     int h, int n, uint16_t off_w, uint16_t off_h)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.im2col.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};" ::"r"(dst),
+        "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(c), "r"(w), "r"(h), "r"(n), "h"(off_w), "h"(off_h)
+        : "memory");
+}
+
+// Tiled TMA store shared -> global (bulk-group completion).  Coordinates must not be negative;
+// elements of the box that fall outside the tensor are not written.
+__device__ __forceinline__ void tma_store_4d_a(const CUtensorMap* m, uint32_t src, int c0, int c1, int c2, int c3)
+{
+    asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(
+                     reinterpret_cast<uint64_t>(m)),
+                 "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_store_commit()
+{
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+// Waits until at most N of this thread's store groups still read their shared-memory source.
+template <int N>
+__device__ __forceinline__ void tma_store_wait_read()
+{
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+// Waits until all of this thread's store groups have completed.
+__device__ __forceinline__ void tma_store_wait_all()
+{
+    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+}
+// Barrier among a subset of the CTA's warps (id 1..15, count a multiple of 32).
+__device__ __forceinline__ void named_barrier_sync(uint32_t id, uint32_t count)
+{
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, float4 v)
+{
+    asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
 }
 
 // ---- tensor memory --------------------------------------------------------------------------
@@ -223,6 +346,18 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo, 
     return d;
 }
 
+// The same descriptor as two 32-bit halves.  Only the low half changes while a kernel walks a tile
+// (the start address moves, strides and layout stay), so issue loops keep `hi` in a register and
+// add byte offsets, shifted right by 4, to `lo`.
+__device__ __forceinline__ uint32_t smem_desc_lo(uint32_t addr, uint32_t lbo)
+{
+    return ((addr & 0x3FFFFu) >> 4) | (((lbo >> 4) & 0x3FFFu) << 16);
+}
+__device__ __forceinline__ uint32_t smem_desc_hi(uint32_t sbo, uint32_t layout)
+{
+    return ((sbo >> 4) & 0x3FFFu) | (1u << 14) | ((layout & 7u) << 29);
+}
+
 // Instruction descriptor for kind::tf32 with fp32 accumulation.
 __host__ __device__ inline uint32_t make_idesc_tf32(int M, int N, bool a_mn_major, bool b_mn_major)
 {
@@ -248,6 +383,23 @@ __device__ __forceinline__ void mma_tf32_ss(uint32_t d_tmem, uint64_t a_desc, ui
         "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t"
         "}\n" ::"r"(d_tmem),
         "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// Same instruction with the descriptors given as (lo, hi) halves; `accumulate` = 0 overwrites D.
+__device__ __forceinline__ void mma_tf32_ss2(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                             uint32_t b_hi, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        ".reg .b64 da, db;\n\t"
+        "mov.b64 da, {%1, %2};\n\t"
+        "mov.b64 db, {%3, %4};\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], da, db, %5, p;\n\t"
+        "}\n" ::"r"(d_tmem),
+        "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
         : "memory");
 }
 

@@ -70,6 +70,11 @@ int alpha_conv_device_status(void);
 unsigned long long alpha_conv_launch_count(void);
 /* Name of the kernel family the last call of this thread used ("igemm", "dw", "simt", ...). */
 const char* alpha_conv_last_algo(void);
+/* Tracing aid: with ALPHA_CONV_PROF=1 in the environment the halo-tile kernel records, for its first
+ * CTA, the clock ticks each warp role spent waiting and working (slots: producer patch wait,
+ * producer B wait, MMA patch wait, MMA B wait, MMA accumulator wait, MMA total, epilogue wait,
+ * epilogue work, split wait, split work, kernel total).  Copies up to n slots of the last launch. */
+int alpha_conv_debug_counters(unsigned long long* out, int n);
 
 /* ---- layer 1: one call per contraction ------------------------------------------------------ */
 

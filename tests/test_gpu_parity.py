@@ -44,8 +44,10 @@ def eng(pkg):
     return pkg.submodule("engine").Engine()
 
 
-def _run_case(pkg, eng, O, name, mode, dists=("u11", "u11", "n01")):
+def _run_case(pkg, eng, O, name, mode, dists=("u11", "u11", "n01"), tile="auto"):
+    import os
     import torch
+    os.environ["ALPHA_CONV_TILE"] = tile  # read by the library at every call
     lib = pkg.submodule("lib")
     lib.set_math_mode(mode)
     N, IH, IW, IC, OC, FH, FW, sh, sw, ph, pw = CASES[name]
@@ -71,16 +73,19 @@ def _run_case(pkg, eng, O, name, mode, dists=("u11", "u11", "n01")):
     SY = SY + np.abs(B).astype(np.float64)
     dX64, SX = O.deconv3D_deltaX_f64(dY, W, IH, IW, sh, sw, ph, pw, threads=8)
     dW64, SW = O.deconv3D_deltaW_f64(X, dY, FH, FW, sh, sw, ph, pw, threads=8)
-    res.update(case=name, mode=mode, status=status, fwd=metrics(Y, Y64, SY), dx=metrics(dX, dX64, SX),
+    res.update(case=name, mode=mode, tile=tile, status=status, fwd=metrics(Y, Y64, SY), dx=metrics(dX, dX64, SX),
                dw=metrics(dW, dW64, SW))
     record(res)
     return res, (X, W, B, dY, Y, dX, dW)
 
 
+@pytest.mark.parametrize("tile", ["im2col", "halo"])
 @pytest.mark.parametrize("mode", ["3xtf32", "tf32"])
 @pytest.mark.parametrize("name", list(CASES))
-def test_layer_parity(pkg, eng, oracle_mod, name, mode):
-    res, _ = _run_case(pkg, eng, oracle_mod, name, mode)
+def test_layer_parity(pkg, eng, oracle_mod, name, mode, tile):
+    """tile: 'im2col' = one TMA load per filter tap, 'halo' = input tile fetched once with its halo
+    (stride-1 shapes; others fall back to the per-tap kernel)."""
+    res, _ = _run_case(pkg, eng, oracle_mod, name, mode, tile=tile)
     assert res["status"] == 0, "kernel status word %d" % res["status"]
     tol = TOL[mode]
     for op in ("fwd", "dx", "dw"):
@@ -106,8 +111,10 @@ def test_reference_acceptance_thresholds(pkg, eng, oracle_mod, name):
 
 def test_algo_selection(pkg, eng, oracle_mod):
     """Shapes with channel counts that are multiples of 32 must run on the tensor path."""
-    res, _ = _run_case(pkg, eng, oracle_mod, "ic64_oc64_14x14", "3xtf32")
+    res, _ = _run_case(pkg, eng, oracle_mod, "ic64_oc64_14x14", "3xtf32", tile="im2col")
     assert res["fwd_algo"] == "igemm" and res["dx_algo"] == "igemm" and res["dw_algo"] == "dw"
+    res, _ = _run_case(pkg, eng, oracle_mod, "ic64_oc64_14x14", "3xtf32", tile="halo")
+    assert res["fwd_algo"].startswith("halo") and res["dx_algo"].startswith("halo")
 
 
 EDGE_CASES = {
@@ -123,8 +130,9 @@ CASES.update(EDGE_CASES)
 
 
 @pytest.mark.parametrize("name", list(EDGE_CASES))
-def test_edge_cases(pkg, eng, oracle_mod, name):
-    res, _ = _run_case(pkg, eng, oracle_mod, name, "3xtf32")
+@pytest.mark.parametrize("tile", ["im2col", "halo"])
+def test_edge_cases(pkg, eng, oracle_mod, name, tile):
+    res, _ = _run_case(pkg, eng, oracle_mod, name, "3xtf32", tile=tile)
     assert res["status"] == 0
     for op in ("fwd", "dx", "dw"):
         m = res[op]
