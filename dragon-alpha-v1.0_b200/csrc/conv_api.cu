@@ -2,6 +2,7 @@
 #include "../../include/alpha_conv_b200.h"
 #include "conv_kernels.cuh"
 #include "conv_halo.cuh"
+#include "conv_dw_halo.cuh"
 #include "host_common.h"
 
 #include <atomic>
@@ -514,6 +515,120 @@ static int launch_halo(DeviceCtx* c, const IgemmPlan& pl, int mode3x, cudaStream
     return rc;
 }
 
+// ---- deltaW, halo-tile kernel (stride 1): plan and launch -----------------------------------------
+
+template <int FW_T, int R_T, int CW_T>
+static void dw_halo_set_attr()
+{
+    cudaFuncSetAttribute(conv_dw_halo_kernel<FW_T, R_T, CW_T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+}
+
+// Returns 1 when the shape is left to the split-K im2col kernel, 0 on launch, < 0 on error.
+static int launch_dw_halo(DeviceCtx* c, const AlphaConvShape* s, const float* X, const float* dY, float* dW,
+                          int mode3x, cudaStream_t stream)
+{
+    const char* e = getenv("ALPHA_CONV_DW");
+    if (e && !strcmp(e, "split")) return 1;
+    if (s->sh != 1 || s->sw != 1 || s->IC % 32 != 0) return 1;
+    if (s->FW > 8 || s->ph >= s->FH || s->pw >= s->FW) return 1;
+    // input channels per CTA: FW accumulators of NT columns must fit the 512 tensor-memory columns
+    int NT = 0;
+    for (int cand = 256; cand >= 32; cand >>= 1)
+        if (s->IC % cand == 0 && s->FW * cand <= 512) { NT = cand; break; }
+    if (!NT) return 1;
+    DwHaloParams p{};
+    p.status = c->status;
+    p.N = s->N; p.OH = s->OH; p.OW = s->OW;
+    p.IC = s->IC; p.OC = s->OC; p.FH = s->FH; p.FW = s->FW; p.ph = s->ph; p.pw = s->pw;
+    p.NT = NT; p.ic_tiles = s->IC / NT; p.oc_tiles = (s->OC + 127) / 128;
+    const int groups = s->FH * p.ic_tiles * p.oc_tiles;
+    if (groups > 65535) return 1;
+    // pixel tile: CW columns of 8-pixel groups, R rows, sized so that three stages fit shared memory
+    const int planes = mode3x ? 2 : 1;
+    int CW = env_int("ALPHA_DW_CW", 0);
+    if (!CW) CW = (s->OW > 8) ? 16 : 8;
+    const int PW = CW + s->FW - 1;
+    int R = env_int("ALPHA_DW_R", 0);
+    auto stage_bytes = [&](int r) {
+        const uint32_t dyb = ((uint32_t)r * CW * 128 + 1023) & ~1023u, xbk = ((uint32_t)r * PW * 128 + 1023) & ~1023u;
+        return (size_t)planes * (4 * dyb + (NT / 32) * xbk);
+    };
+    if (!R) {
+        R = 8;
+        while (R > 1 && (3 * stage_bytes(R) > 200 * 1024 || R > s->OH)) R >>= 1;
+    }
+    if (2 * stage_bytes(R) > 220 * 1024) return 1;
+    int stages = (int)((220 * 1024) / stage_bytes(R));
+    if (stages > 4) stages = 4;
+    p.R = R; p.CW = CW; p.PW = PW;
+    p.row_blocks = (s->OH + R - 1) / R; p.col_blocks = (s->OW + CW - 1) / CW;
+    p.tiles_per_img = p.row_blocks * p.col_blocks;
+    const long long total = (long long)s->N * p.tiles_per_img;
+    if (total > 2147483647LL) return 1;
+    p.total_tiles = (int)total;
+    int parts = c->sm_count / groups;
+    if (parts < 1) parts = 1;
+    if (parts > p.total_tiles) parts = p.total_tiles;
+    p.parts = parts;
+    p.stages = stages; p.mode3x = mode3x;
+    p.idesc = make_idesc_tf32(kBM, NT, true, true);
+    p.tmem_cols = pow2_cols(s->FW * NT);
+    p.dy_tx = (uint32_t)R * CW * 128; p.dy_blk = (p.dy_tx + 1023) & ~1023u;
+    p.x_tx = (uint32_t)R * PW * 128; p.x_blk = (p.x_tx + 1023) & ~1023u;
+    const size_t sizeW = (size_t)s->OC * s->FH * s->FW * s->IC;
+    float* ws = nullptr;
+    if (parts > 1) {
+        int rc = get_workspace(c, stream, sizeW * parts * sizeof(float), &ws);
+        if (rc) return rc;
+        p.out = ws;
+    } else {
+        p.out = dW;
+    }
+    p.part_stride = sizeW;
+    const size_t smem = (size_t)stages * stage_bytes(R) + (3 * stages + 2) * 8 + 1024;
+
+    CUtensorMap tmX, tmDY;
+    cuuint64_t xd[4] = {(cuuint64_t)s->IC, (cuuint64_t)s->IW, (cuuint64_t)s->IH, (cuuint64_t)s->N};
+    cuuint64_t xs[3] = {(cuuint64_t)s->IC * 4, (cuuint64_t)s->IW * s->IC * 4, (cuuint64_t)s->IH * s->IW * s->IC * 4};
+    cuuint32_t xbox[4] = {32, (cuuint32_t)PW, (cuuint32_t)R, 1};
+    int rc = make_tiled_map(&tmX, X, 4, xd, xs, xbox, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
+    if (rc) return rc;
+    cuuint64_t yd[4] = {(cuuint64_t)s->OC, (cuuint64_t)s->OW, (cuuint64_t)s->OH, (cuuint64_t)s->N};
+    cuuint64_t ys[3] = {(cuuint64_t)s->OC * 4, (cuuint64_t)s->OW * s->OC * 4, (cuuint64_t)s->OH * s->OW * s->OC * 4};
+    cuuint32_t ybox[4] = {32, (cuuint32_t)CW, (cuuint32_t)R, 1};
+    rc = make_tiled_map(&tmDY, dY, 4, yd, ys, ybox, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
+    if (rc) return rc;
+
+    dim3 grid(parts, groups, 1);
+    static bool attr_done = false;
+    if (!attr_done) {
+        dw_halo_set_attr<0, 0, 0>(); dw_halo_set_attr<3, 1, 16>(); dw_halo_set_attr<3, 2, 16>(); dw_halo_set_attr<3, 4, 16>();
+        dw_halo_set_attr<3, 8, 16>(); dw_halo_set_attr<3, 2, 8>(); dw_halo_set_attr<3, 4, 8>(); dw_halo_set_attr<3, 8, 8>();
+        attr_done = true;
+    }
+#define DWH_LAUNCH(FW_, R_, CW_) conv_dw_halo_kernel<FW_, R_, CW_><<<grid, kDwHaloThreads, smem, stream>>>(tmX, tmDY, p)
+    const bool st = s->FW == 3 && env_int("ALPHA_DW_STATIC", 1) != 0;
+    if (st && R == 1 && CW == 16) DWH_LAUNCH(3, 1, 16);
+    else if (st && R == 2 && CW == 16) DWH_LAUNCH(3, 2, 16);
+    else if (st && R == 4 && CW == 16) DWH_LAUNCH(3, 4, 16);
+    else if (st && R == 8 && CW == 16) DWH_LAUNCH(3, 8, 16);
+    else if (st && R == 2 && CW == 8) DWH_LAUNCH(3, 2, 8);
+    else if (st && R == 4 && CW == 8) DWH_LAUNCH(3, 4, 8);
+    else if (st && R == 8 && CW == 8) DWH_LAUNCH(3, 8, 8);
+    else DWH_LAUNCH(0, 0, 0);
+#undef DWH_LAUNCH
+    note_launch("dw_halo");
+    rc = check_launch("conv_dw_halo_kernel");
+    if (rc) return rc;
+    if (parts > 1) {
+        const size_t n4 = sizeW / 4;
+        dw_reduce_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, stream>>>(ws, sizeW, parts, dW, n4, 0);
+        note_launch("dw_halo");
+        rc = check_launch("dw_reduce_kernel");
+    }
+    return rc;
+}
+
 // deltaW += sum of `part` split-K buffers of sizeW floats each (the reference's buf_summary).
 int launch_buf_summary(cudaStream_t stream, const float* buf, float* deltaW, int part, size_t sizeW)
 {
@@ -721,6 +836,8 @@ int alpha_conv3d_deltaW(const AlphaConvShape* s, const float* X, const float* de
     }
 
     const int mode3x = g_math.load() == ALPHA_MATH_3XTF32;
+    rc = launch_dw_halo(c, s, X, deltaY, deltaW, mode3x, stream);
+    if (rc != 1) return rc;
     DwParams p{};
     p.status = c->status;
     p.Npix = s->N * s->OH * s->OW;

@@ -1,0 +1,234 @@
+// Stride-1 deltaW with each X and deltaY tile fetched once per filter row.
+//
+//   deltaW[oc][fh][fw][ic] = sum over pixels of deltaY[pix][oc] * X[pix shifted by (fh, fw)][ic]
+//
+// The reduction axis of this GEMM is the pixel axis, so both operands are MN-major in shared
+// memory: a tile row is one pixel, its 128 bytes are 32 channels.  One tcgen05.mma (K = 8) consumes
+// 8 consecutive pixels of one image row.  A CTA owns one accumulator group - one filter row fh
+// (FW taps), one block of up to 128 output channels (M) and one block of NT input channels (N) -
+// and a share of the pixel tiles.  For every pixel tile of R rows x CW columns it loads the
+// deltaY tile and the X tile (R rows x (CW + FW - 1) columns, shifted by fh) once; the FW taps of
+// the row are formed by starting the X descriptor fw pixel rows later (tensor cores apply the
+// shared-memory swizzle to absolute addresses, so any 128-byte row is a valid start).  The CTA
+// accumulates over all its pixel tiles in tensor memory and writes one partial per CTA at the end;
+// dw_reduce_kernel sums the partials in a fixed order.
+//
+// Warps: 0 TMA producer, 1 MMA issuer, 2-5 operand split (3xTF32) during the loop, epilogue after.
+#pragma once
+#include "conv_kernels.cuh"
+
+namespace alpha {
+
+constexpr int kDwHaloThreads = 192;
+
+struct DwHaloParams {
+    float* out;            // partials [parts][OC][FH*FW][IC] (or deltaW itself when parts == 1)
+    size_t part_stride;    // floats between two partials
+    int* status;
+    int N, OH, OW;         // deltaY geometry
+    int IC, OC, FH, FW, ph, pw;
+    int NT;                // input channels per CTA (multiple of 32, <= 256)
+    int ic_tiles, oc_tiles;  // IC / NT, ceil(OC / 128)
+    int R, CW;             // pixel tile: rows x columns (CW multiple of 8)
+    int PW;                // X tile columns = CW + FW - 1
+    int row_blocks, col_blocks, tiles_per_img;
+    int total_tiles;       // N * tiles_per_img
+    int parts;             // CTAs per accumulator group = gridDim.x
+    int stages, mode3x;
+    uint32_t idesc, tmem_cols;
+    uint32_t dy_blk, x_blk;   // bytes of one 32-channel block of the deltaY / X tile (multiples of 1024)
+    uint32_t dy_tx, x_tx;     // bytes one block load delivers
+};
+
+// FW_T > 0: FW, R and CW are compile-time and the MMAs of a stage are straight-line code.
+template <int FW_T, int R_T, int CW_T>
+__global__ void __launch_bounds__(kDwHaloThreads, 1)
+    conv_dw_halo_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmDY,
+                        const DwHaloParams p)
+{
+    constexpr bool kStatic = FW_T > 0;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                               ~static_cast<uintptr_t>(1023));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int S = p.stages;
+    const uint32_t planes = p.mode3x ? 2u : 1u;
+    const int xb = p.NT / 32;                       // X blocks per stage
+    const uint32_t dy_bytes = 4 * p.dy_blk;         // 128 output channels
+    const uint32_t x_bytes = xb * p.x_blk;
+    const uint32_t plane_bytes = dy_bytes + x_bytes;  // hi plane; the lo plane follows
+    const uint32_t stage_bytes = plane_bytes * planes;
+
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + static_cast<size_t>(S) * stage_bytes);
+    uint64_t* full = bars;
+    uint64_t* ready = bars + S;
+    uint64_t* empty = bars + 2 * S;
+    uint64_t* accum = bars + 3 * S;
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 3 * S + 1);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&ready[s], 128);
+            mbar_init(&empty[s], 1);
+        }
+        mbar_init(accum, 1);
+        fence_barrier_init();
+        prefetch_tmap(&tmX);
+        prefetch_tmap(&tmDY);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_holder, p.tmem_cols);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_holder;
+
+    // accumulator group of this CTA
+    const int grp = blockIdx.y;
+    const int fh = grp % p.FH;
+    const int ict = (grp / p.FH) % p.ic_tiles;
+    const int oct = grp / (p.FH * p.ic_tiles);
+    const int ic0 = ict * p.NT, oc0 = oct * 128;
+
+    const uint32_t smem_a = smem_u32(smem);
+    const uint32_t full_a = smem_u32(full), ready_a = smem_u32(ready), empty_a = smem_u32(empty);
+    const int FW = kStatic ? FW_T : p.FW;
+    const int R = kStatic ? R_T : p.R;
+    const int CW = kStatic ? CW_T : p.CW;
+    const int PW = CW + FW - 1;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---- TMA producer ----
+            RingPos rp;
+            for (int t = blockIdx.x; t < p.total_tiles; t += gridDim.x) {
+                const int n = t / p.tiles_per_img;
+                const int r = t - n * p.tiles_per_img;
+                const int rb = r / p.col_blocks, cb = r - rb * p.col_blocks;
+                if (!mbar_wait_a(empty_a + 8 * rp.idx, rp.phase ^ 1)) { report(p.status, kStatusProducerTimeout); break; }
+                const uint32_t bar = full_a + 8 * rp.idx;
+                const uint32_t dst = smem_a + rp.idx * stage_bytes;
+                mbar_arrive_expect_tx_a(bar, 4 * p.dy_tx + xb * p.x_tx);
+                const int oh0 = rb * R, ow0 = cb * CW;
+                for (int b = 0; b < 4; ++b)
+                    tma_load_4d_a(dst + b * p.dy_blk, &tmDY, bar, oc0 + b * 32, ow0, oh0, n);
+                for (int b = 0; b < xb; ++b)
+                    tma_load_4d_a(dst + dy_bytes + b * p.x_blk, &tmX, bar, ic0 + b * 32, ow0 - p.pw, oh0 + fh - p.ph, n);
+                rp.advance(S);
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // ---- MMA issuer ----
+            RingPos rp;
+            const uint32_t dhi = smem_desc_hi(512, kSwizzle128B_Base32B);
+            const uint32_t wait_a = p.mode3x ? ready_a : full_a;
+            const uint32_t stage16 = stage_bytes >> 4, lo_off = plane_bytes >> 4;
+            const uint32_t a_lo0 = smem_desc_lo(smem_a, p.dy_blk);              // LBO = block stride
+            const uint32_t b_lo0 = smem_desc_lo(smem_a + dy_bytes, p.x_blk);
+            uint32_t acc = 0u;  // the first MMA into each accumulator overwrites it
+            for (int t = blockIdx.x; t < p.total_tiles; t += gridDim.x) {
+                if (!mbar_wait_a(wait_a + 8 * rp.idx, rp.phase)) { report(p.status, kStatusMmaTimeout); break; }
+                tc_fence_after_sync();
+                const uint32_t a_s = a_lo0 + rp.idx * stage16, b_s = b_lo0 + rp.idx * stage16;
+                if constexpr (kStatic) {
+#pragma unroll
+                    for (int r = 0; r < R_T; ++r)
+#pragma unroll
+                        for (int g = 0; g < CW_T / 8; ++g) {
+                            constexpr int kPW = CW_T + FW_T - 1;
+                            const uint32_t a_k = a_s + (r * CW_T + g * 8) * 8;
+                            const uint32_t first = (r | g) ? 1u : acc;
+#pragma unroll
+                            for (int fw = 0; fw < FW_T; ++fw) {
+                                const uint32_t b_k = b_s + (r * kPW + g * 8 + fw) * 8;
+                                const uint32_t d = tmem_base + fw * p.NT;
+                                if (p.mode3x) {
+                                    mma_tf32_ss2(d, a_k + lo_off, dhi, b_k, dhi, p.idesc, first);
+                                    mma_tf32_ss2(d, a_k, dhi, b_k + lo_off, dhi, p.idesc, 1u);
+                                    mma_tf32_ss2(d, a_k, dhi, b_k, dhi, p.idesc, 1u);
+                                } else {
+                                    mma_tf32_ss2(d, a_k, dhi, b_k, dhi, p.idesc, first);
+                                }
+                            }
+                        }
+                } else {
+                    uint32_t a_row = a_s, b_row = b_s;
+                    uint32_t first = acc;
+                    for (int r = 0; r < R; ++r, a_row += CW * 8, b_row += PW * 8) {
+                        uint32_t a_k = a_row, b_g = b_row;
+                        for (int g = 0; g < CW / 8; ++g, a_k += 64, b_g += 64) {
+                            uint32_t b_k = b_g, d = tmem_base;
+                            for (int fw = 0; fw < FW; ++fw, b_k += 8, d += p.NT) {
+                                if (p.mode3x) {
+                                    mma_tf32_ss2(d, a_k + lo_off, dhi, b_k, dhi, p.idesc, first);
+                                    mma_tf32_ss2(d, a_k, dhi, b_k + lo_off, dhi, p.idesc, 1u);
+                                    mma_tf32_ss2(d, a_k, dhi, b_k, dhi, p.idesc, 1u);
+                                } else {
+                                    mma_tf32_ss2(d, a_k, dhi, b_k, dhi, p.idesc, first);
+                                }
+                            }
+                            first = 1u;
+                        }
+                    }
+                }
+                acc = 1u;
+                mma_commit_a(empty_a + 8 * rp.idx);
+                rp.advance(S);
+            }
+            mma_commit(accum);
+        }
+        __syncwarp();
+    } else {
+        // ---- operand split while the loop runs (3xTF32), epilogue afterwards: warps 2..5 ----
+        const int tid128 = threadIdx.x - 64;
+        bool ok = true;
+        if (p.mode3x) {
+            RingPos rp;
+            for (int t = blockIdx.x; t < p.total_tiles; t += gridDim.x) {
+                if (!mbar_wait_a(full_a + 8 * rp.idx, rp.phase)) { report(p.status, kStatusSplitTimeout); ok = false; break; }
+                uint8_t* hi = smem + static_cast<size_t>(rp.idx) * stage_bytes;
+                split_plane_x4(hi, hi + plane_bytes, plane_bytes, tid128, 128);
+                fence_proxy_async_smem();
+                mbar_arrive_a(ready_a + 8 * rp.idx);
+                rp.advance(S);
+            }
+        }
+        if (ok && !mbar_wait(accum, 0)) { report(p.status, kStatusEpilogueTimeout); ok = false; }
+        tc_fence_after_sync();
+        if (ok) {
+            const int quad = warp & 3;
+            const int oc = oc0 + quad * 32 + lane;
+            const int taps = p.FH * p.FW;
+            const bool has_tiles = static_cast<int>(blockIdx.x) < p.total_tiles;
+            float* obase = p.out + static_cast<size_t>(blockIdx.x) * p.part_stride;
+            for (int fw = 0; fw < FW; ++fw) {
+                const int tap = fh * p.FW + fw;
+                for (int c = 0; c < p.NT; c += 32) {
+                    uint32_t v[32];
+                    tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + fw * p.NT + c, v);
+                    tmem_ld_wait();
+                    if (oc < p.OC) {
+                        float* dst = obase + (static_cast<size_t>(oc) * taps + tap) * p.IC + ic0 + c;
+#pragma unroll
+                        for (int q = 0; q < 32; q += 4) {
+                            float4 o = has_tiles ? make_float4(__uint_as_float(v[q]), __uint_as_float(v[q + 1]),
+                                                               __uint_as_float(v[q + 2]), __uint_as_float(v[q + 3]))
+                                                 : make_float4(0.f, 0.f, 0.f, 0.f);
+                            *reinterpret_cast<float4*>(dst + q) = o;
+                        }
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, p.tmem_cols);
+}
+
+}  // namespace alpha

@@ -112,7 +112,7 @@ def test_reference_acceptance_thresholds(pkg, eng, oracle_mod, name):
 def test_algo_selection(pkg, eng, oracle_mod):
     """Shapes with channel counts that are multiples of 32 must run on the tensor path."""
     res, _ = _run_case(pkg, eng, oracle_mod, "ic64_oc64_14x14", "3xtf32", tile="im2col")
-    assert res["fwd_algo"] == "igemm" and res["dx_algo"] == "igemm" and res["dw_algo"] == "dw"
+    assert res["fwd_algo"] == "igemm" and res["dx_algo"] == "igemm" and res["dw_algo"].startswith("dw")
     res, _ = _run_case(pkg, eng, oracle_mod, "ic64_oc64_14x14", "3xtf32", tile="halo")
     assert res["fwd_algo"].startswith("halo") and res["dx_algo"].startswith("halo")
 

@@ -46,15 +46,15 @@ def test_deltaW_noalloc_matches_deltaW_on_two_calls(pkg):
         s = _shape(L, N, HW, IC, OC)
         p = lambda t: C.c_void_p(t.data_ptr())
         L.check(lib.alpha_conv3d_deltaW(C.byref(s), p(X), p(dY), p(ref), stream))
-        assert L.last_algo() == "dw"
+        assert L.last_algo().startswith("dw")
         L.check(lib.alpha_conv3d_deltaW_noalloc(C.byref(s), p(X), p(dY), p(got), stream))
         assert L.last_algo() == "dw_noalloc"
         assert lib.alpha_conv3d_deltaW_noalloc_status() == 0
         assert L.device_status() == 0
         a, b = got.cpu().numpy(), ref.cpu().numpy()
         assert np.isfinite(a).all()
-        # the tolerance of the parity tests (normwise 1e-4); the two entry points share tiling and
-        # summation order, so in practice the difference is zero
+        # the tolerance of the parity tests (normwise 1e-4); the two entry points may tile and order
+        # the pixel sum differently
         assert np.abs(a - b).max() <= 1e-4 * np.abs(b).max()
         # and against the fp64 result, independent of the other entry point
         d64 = torch.einsum("nhwc,nhwo->oc", X.double(), dY.double())  # centre tap only
