@@ -30,6 +30,8 @@ int fail(int code, const char* fmt, ...)
     return code;
 }
 
+static thread_local char g_plan[128] = "";
+
 void note_launch(const char* algo)
 {
     g_last_algo = algo;
@@ -352,7 +354,7 @@ static int env_tile_mode()
 
 struct HaloChoice {
     bool valid = false;
-    int JH = 1, JW = 1, npb = 1, sb = 2, acc_bufs = 1;
+    int JH = 1, JW = 1, npb = 1, sb = 2, acc_bufs = 1, NI = 1;
     bool row = false;
     double cost = 0, eff = 0;
 };
@@ -377,13 +379,19 @@ static HaloChoice plan_halo(const IgemmPlan& pl, int BN, int mode3x, int b_mn)
     const bool allow_row = env_int("ALPHA_HALO_ROW", 1) != 0;
     const int force_jh = env_int("ALPHA_HALO_JH", 0), force_jw = env_int("ALPHA_HALO_JW", 0);
     const size_t smem_cap = 226 * 1024;
+    // small images: NI images stacked in one accumulator, each in a slot of SG = OH + FH - 1 rows
+    const int SG = pl.oH + pl.FH - 1;
+    int ni_max = 1;
+    if (SG <= 16 && env_int("ALPHA_HALO_STACK", 1)) ni_max = 1 + (16 - pl.oH) / SG;
+    for (int NI = 1; NI <= ni_max; NI += (ni_max > 1 ? ni_max - 1 : 1))
     for (int JH = 1; JH <= 2; ++JH)
         for (int JW = 1; JW <= 4; ++JW) {
+            if (NI > 1 && (JH != 1 || JW != 1)) continue;
             if (force_jh && JH != force_jh) continue;
             if (force_jw && JW != force_jw) continue;
             const int J = JH * JW;
             if (J * BN > 512) continue;
-            const int PH = 16 * JH + pl.FH - 1, PW = 8 * JW + pl.FW - 1;
+            const int PH = NI > 1 ? NI * SG : 16 * JH + pl.FH - 1, PW = 8 * JW + pl.FW - 1;
             if (PH > 256 || PW > 256) continue;
             const uint32_t patch_stride = (((uint32_t)PH * PW * 128 + 1023) & ~1023u) * planes;
             bool row = allow_row && halo_has_row_kernel(pl.FW, JH, JW);
@@ -397,20 +405,23 @@ static HaloChoice plan_halo(const IgemmPlan& pl, int BN, int mode3x, int b_mn)
             if (need(npb, sb) > smem_cap) continue;
             while (sb < max_sb && need(npb, sb + 1) <= smem_cap && sb < taps) ++sb;
             const int acc_bufs = (2 * J * BN <= 512) ? 2 : 1;
-            const int rbk = (pl.oH + 16 * JH - 1) / (16 * JH), cbk = (pl.oW + 8 * JW - 1) / (8 * JW);
-            const double eff = (double)pl.oH * pl.oW / ((double)rbk * 16 * JH * cbk * 8 * JW);
-            // cycles per macro tile
-            const double mma_clk = (BN / 2.0 > (4096.0 + BN * 32.0) / 128.0) ? BN / 2.0 : (4096.0 + BN * 32.0) / 128.0;
+            const int rbk = NI > 1 ? 1 : (pl.oH + 16 * JH - 1) / (16 * JH), cbk = (pl.oW + 8 * JW - 1) / (8 * JW);
+            const double eff = NI > 1 ? (double)NI * pl.oH * pl.oW / (128.0 * cbk)
+                                      : (double)pl.oH * pl.oW / ((double)rbk * 16 * JH * cbk * 8 * JW);
+            // cycles per macro tile: one tcgen05.mma of this shape takes max(N/2, 59) clocks
+            const double mma_clk = BN / 2.0 > 59.0 ? BN / 2.0 : 59.0;
             const double t_mma = (double)taps * kchunks * 4 * (mode3x ? 3 : 1) * J * mma_clk;
-            const double bytes = (double)kchunks * ((double)PH * PW * 128 + (double)taps * b_tx);
-            const double t_l2 = bytes / 40.0;  // ~40 B/clk/SM of L2->SM bandwidth when all SMs pull
+            // W tiles are read by every CTA at about the same time and cost about half of private bytes
+            const double bytes = (double)kchunks * ((double)PH * PW * 128 + 0.5 * taps * b_tx * planes) + 128.0 * J * BN * 4;
+            const double t_l2 = bytes / 28.0;  // ~28 B/clk/SM between L2 and an SM when all SMs pull
             double t = (t_mma > t_l2 ? t_mma : t_l2) + 1500.0;  // fixed per-tile overhead
-            if (npb == 1) t *= 1.10;
-            if (acc_bufs == 1) t *= 1.10;
+            if (npb == 1) t *= 1.25;
+            if (acc_bufs == 1) t *= 1.15;
+            if (!row) t *= 1.15;
             const double cost = t / (128.0 * J * eff);
             if (!best.valid || cost < best.cost) {
                 best.valid = true; best.JH = JH; best.JW = JW; best.npb = npb; best.sb = sb;
-                best.acc_bufs = acc_bufs; best.cost = cost; best.eff = eff; best.row = row;
+                best.acc_bufs = acc_bufs; best.cost = cost; best.eff = eff; best.row = row; best.NI = NI;
             }
         }
     return best;
@@ -437,10 +448,12 @@ static int launch_halo(DeviceCtx* c, const IgemmPlan& pl, int mode3x, cudaStream
     p.kchunks = pl.kdim / 32;
     p.BN = BN; p.n_tiles = (pl.ncols + BN - 1) / BN;
     p.JH = ch.JH; p.JW = ch.JW;
-    p.PH = 16 * ch.JH + pl.FH - 1; p.PW = 8 * ch.JW + pl.FW - 1;
-    p.row_blocks = (pl.oH + 16 * ch.JH - 1) / (16 * ch.JH);
+    p.NI = ch.NI; p.SG = pl.oH + pl.FH - 1;
+    p.PH = ch.NI > 1 ? ch.NI * p.SG : 16 * ch.JH + pl.FH - 1; p.PW = 8 * ch.JW + pl.FW - 1;
+    p.row_blocks = ch.NI > 1 ? 1 : (pl.oH + 16 * ch.JH - 1) / (16 * ch.JH);
     p.col_blocks = (pl.oW + 8 * ch.JW - 1) / (8 * ch.JW);
-    const long long total = (long long)p.n_tiles * p.N * p.row_blocks * p.col_blocks;
+    p.n_blocks = (p.N + ch.NI - 1) / ch.NI;
+    const long long total = (long long)p.n_tiles * p.n_blocks * p.row_blocks * p.col_blocks;
     if (total > 2147483647LL) return 1;
     p.total_tiles = (int)total;
     p.npb = ch.npb; p.sb = ch.sb; p.acc_bufs = ch.acc_bufs;
@@ -459,7 +472,7 @@ static int launch_halo(DeviceCtx* c, const IgemmPlan& pl, int mode3x, cudaStream
     CUtensorMap tmA, tmB;
     cuuint64_t ad[4] = {(cuuint64_t)pl.aC, (cuuint64_t)pl.aW, (cuuint64_t)pl.aH, (cuuint64_t)pl.aN};
     cuuint64_t as[3] = {(cuuint64_t)pl.aC * 4, (cuuint64_t)pl.aW * pl.aC * 4, (cuuint64_t)pl.aH * pl.aW * pl.aC * 4};
-    cuuint32_t abox[4] = {32, (cuuint32_t)p.PW, (cuuint32_t)p.PH, 1};
+    cuuint32_t abox[4] = {32, (cuuint32_t)p.PW, (cuuint32_t)(ch.NI > 1 ? p.SG : p.PH), (cuuint32_t)ch.NI};
     int rc = make_tiled_map(&tmA, pl.act, 4, ad, as, abox, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
     // 3xTF32: split W into hi/lo planes once per call (scratch of this stream), load both by TMA
@@ -498,7 +511,7 @@ static int launch_halo(DeviceCtx* c, const IgemmPlan& pl, int mode3x, cudaStream
     // output [N][OH][OW][ldo] for the epilogue's TMA stores: one slab = 32 channels x 8 columns x 16 rows
     cuuint64_t od[4] = {(cuuint64_t)pl.ncols, (cuuint64_t)pl.oW, (cuuint64_t)pl.oH, (cuuint64_t)pl.aN};
     cuuint64_t ost[3] = {(cuuint64_t)pl.ncols * 4, (cuuint64_t)pl.oW * pl.ncols * 4, (cuuint64_t)pl.oH * pl.oW * pl.ncols * 4};
-    cuuint32_t obox[4] = {32, 8, 16, 1};
+    cuuint32_t obox[4] = {32, 8, (cuuint32_t)(ch.NI > 1 ? pl.oH : 16), 1};
     rc = make_tiled_map(&tmO, pl.out, 4, od, ost, obox, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
     int grid = c->sm_count < p.total_tiles ? c->sm_count : p.total_tiles;
@@ -511,6 +524,8 @@ static int launch_halo(DeviceCtx* c, const IgemmPlan& pl, int mode3x, cudaStream
     else HALO_LAUNCH(3, 2, 2);
 #undef HALO_LAUNCH
     note_launch(ch.row ? "halo_row" : "halo");
+    snprintf(g_plan, sizeof(g_plan), "halo%s JH=%d JW=%d NI=%d BN=%d npb=%d sb=%d acc=%d eff=%.2f", ch.row ? "_row" : "", ch.JH,
+             ch.JW, ch.NI, BN, ch.npb, ch.sb, ch.acc_bufs, ch.eff);
     rc = check_launch("conv_halo_kernel");
     return rc;
 }
@@ -546,7 +561,7 @@ static int launch_dw_halo(DeviceCtx* c, const AlphaConvShape* s, const float* X,
     // pixel tile: CW columns of 8-pixel groups, R rows, sized so that three stages fit shared memory
     const int planes = mode3x ? 2 : 1;
     int CW = env_int("ALPHA_DW_CW", 0);
-    if (!CW) CW = (s->OW > 8) ? 16 : 8;
+    if (!CW) CW = (s->OW <= 8 || (s->OW % 16 != 0 && s->OW % 16 <= 8)) ? 8 : 16;  // fewer idle columns
     const int PW = CW + s->FW - 1;
     int R = env_int("ALPHA_DW_R", 0);
     auto stage_bytes = [&](int r) {
@@ -555,7 +570,7 @@ static int launch_dw_halo(DeviceCtx* c, const AlphaConvShape* s, const float* X,
     };
     if (!R) {
         R = 8;
-        while (R > 1 && (3 * stage_bytes(R) > 200 * 1024 || R > s->OH)) R >>= 1;
+        while (R > 1 && (2 * stage_bytes(R) > 210 * 1024 || R > s->OH)) R >>= 1;
     }
     if (2 * stage_bytes(R) > 220 * 1024) return 1;
     int stages = (int)((220 * 1024) / stage_bytes(R));
@@ -618,6 +633,7 @@ static int launch_dw_halo(DeviceCtx* c, const AlphaConvShape* s, const float* X,
     else DWH_LAUNCH(0, 0, 0);
 #undef DWH_LAUNCH
     note_launch("dw_halo");
+    snprintf(g_plan, sizeof(g_plan), "dw_halo NT=%d R=%d CW=%d stages=%d parts=%d groups=%d", NT, R, CW, stages, parts, groups);
     rc = check_launch("conv_dw_halo_kernel");
     if (rc) return rc;
     if (parts > 1) {
@@ -721,6 +737,7 @@ int alpha_conv_set_algo(int algo)
 int alpha_conv_get_algo(void) { return g_algo.load(); }
 unsigned long long alpha_conv_launch_count(void) { return g_launches.load(); }
 const char* alpha_conv_last_algo(void) { return g_last_algo; }
+const char* alpha_conv_last_plan(void) { return g_plan; }
 
 int alpha_conv_device_status(void)
 {

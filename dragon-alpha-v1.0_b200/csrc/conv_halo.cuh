@@ -44,7 +44,9 @@ struct HaloParams {
     int JH, JW;          // accumulators per macro tile, vertically and horizontally
     int PH, PW;          // patch rows and columns (pixels)
     int row_blocks, col_blocks;
-    int total_tiles;     // n_tiles * N * row_blocks * col_blocks
+    int NI, SG;          // images stacked in one accumulator (small images) and rows per image slot
+    int n_blocks;        // ceil(N / NI)
+    int total_tiles;     // n_tiles * n_blocks * row_blocks * col_blocks
     int npb, sb;         // patch buffers, B ring stages
     int acc_bufs;        // 1 or 2 accumulator sets
     int mode3x, b_mn, flip;
@@ -169,12 +171,13 @@ __global__ void __launch_bounds__(kHaloThreads, 1)
             unsigned long long w_patch = 0, w_b = 0;
             const int taps = p.FH * p.FW;
             for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
-                const int tn = t / (p.N * per_img);
-                int r = t - tn * (p.N * per_img);
-                const int n = r / per_img;
-                r -= n * per_img;
+                const int tn = t / (p.n_blocks * per_img);
+                int r = t - tn * (p.n_blocks * per_img);
+                const int nb = r / per_img;
+                r -= nb * per_img;
                 const int rb = r / p.col_blocks, cb = r - rb * p.col_blocks;
                 const int h0 = rb * 16 * p.JH - p.pad_h, w0 = cb * 8 * p.JW - p.pad_w;
+                const int n = nb * p.NI;
                 const int oc0 = tn * p.BN;
                 for (int c = 0; c < p.kchunks && ok; ++c) {
                     if (!wait_prof(pempty_a + 8 * pp.idx, pp.phase ^ 1, prof_on, w_patch)) { report(p.status, kStatusProducerTimeout); ok = false; break; }
@@ -312,11 +315,12 @@ __global__ void __launch_bounds__(kHaloThreads, 1)
         for (int t = blockIdx.x; t < p.total_tiles; t += gridDim.x) {
             if (!wait_prof(afull_a + 8 * ap.idx, ap.phase, prof_on, w_acc)) { report(p.status, kStatusEpilogueTimeout); break; }
             tc_fence_after_sync();
-            const int tn = t / (p.N * per_img);
-            int r = t - tn * (p.N * per_img);
-            const int n = r / per_img;
-            r -= n * per_img;
+            const int tn = t / (p.n_blocks * per_img);
+            int r = t - tn * (p.n_blocks * per_img);
+            const int nb = r / per_img;
+            r -= nb * per_img;
             const int rb = r / p.col_blocks, cb = r - rb * p.col_blocks;
+            const int n = nb * p.NI;
             const int n0 = tn * p.BN;
             int j = 0;
             for (int jh = 0; jh < p.JH; ++jh)
@@ -348,7 +352,14 @@ __global__ void __launch_bounds__(kHaloThreads, 1)
                         fence_proxy_async_smem();
                         named_barrier_sync(1, 128);
                         if (threadIdx.x == 64) {
-                            tma_store_4d_a(&tmO, stage_a + sbuf * 16384, col0, ow0, oh0, n);
+                            if (p.NI == 1) {
+                                tma_store_4d_a(&tmO, stage_a + sbuf * 16384, col0, ow0, oh0, n);
+                            } else {
+                                // stacked images: image i starts SG groups (of 8 rows) further down the slab
+                                for (int img = 0; img < p.NI; ++img)
+                                    if (n + img < p.N)
+                                        tma_store_4d_a(&tmO, stage_a + sbuf * 16384 + img * p.SG * 1024, col0, ow0, 0, n + img);
+                            }
                             tma_store_commit();
                         }
                         sbuf ^= 1u;

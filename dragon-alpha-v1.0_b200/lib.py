@@ -35,6 +35,7 @@ def load():
     lib = C.CDLL(LIB_PATH)
     lib.alpha_conv_last_error.restype = C.c_char_p
     lib.alpha_conv_last_algo.restype = C.c_char_p
+    lib.alpha_conv_last_plan.restype = C.c_char_p
     lib.alpha_conv_launch_count.restype = C.c_ulonglong
     P, V, I, L = C.POINTER(AlphaConvShape), C.c_void_p, C.c_int, C.c_int64
     lib.alpha_conv3d_forward.argtypes = [P, V, V, V, V, V]
@@ -98,6 +99,10 @@ def last_error():
 
 def last_algo():
     return load().alpha_conv_last_algo().decode()
+
+
+def last_plan():
+    return load().alpha_conv_last_plan().decode()
 
 
 def launch_count():

@@ -70,6 +70,8 @@ int alpha_conv_device_status(void);
 unsigned long long alpha_conv_launch_count(void);
 /* Name of the kernel family the last call of this thread used ("igemm", "dw", "simt", ...). */
 const char* alpha_conv_last_algo(void);
+/* Tile plan of the last halo-tile launch of this thread (tile shape, buffers), for tuning. */
+const char* alpha_conv_last_plan(void);
 /* Tracing aid: with ALPHA_CONV_PROF=1 in the environment the halo-tile kernel records, for its first
  * CTA, the clock ticks each warp role spent waiting and working (slots: producer patch wait,
  * producer B wait, MMA patch wait, MMA B wait, MMA accumulator wait, MMA total, epilogue wait,
