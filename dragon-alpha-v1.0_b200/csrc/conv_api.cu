@@ -124,12 +124,20 @@ int get_ctx(DeviceCtx** out)
         const int max_smem = 227 * 1024;
         cudaFuncSetAttribute(conv_igemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
         cudaFuncSetAttribute(conv_dw_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
-        cudaFuncSetAttribute(conv_halo_kernel<0, 0, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
-        cudaFuncSetAttribute(conv_halo_kernel<3, 1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
-        cudaFuncSetAttribute(conv_halo_kernel<3, 1, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
-        cudaFuncSetAttribute(conv_halo_kernel<3, 1, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
-        cudaFuncSetAttribute(conv_halo_kernel<3, 2, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
-        cudaFuncSetAttribute(conv_halo_kernel<3, 2, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+        {
+            const auto attr = cudaFuncAttributeMaxDynamicSharedMemorySize;
+            cudaFuncSetAttribute(conv_halo_kernel<0, 0, 0, false>, attr, max_smem);
+            cudaFuncSetAttribute(conv_halo_kernel<3, 1, 1, true>, attr, max_smem);
+            cudaFuncSetAttribute(conv_halo_kernel<3, 1, 2, true>, attr, max_smem);
+            cudaFuncSetAttribute(conv_halo_kernel<3, 1, 4, true>, attr, max_smem);
+            cudaFuncSetAttribute(conv_halo_kernel<3, 2, 1, true>, attr, max_smem);
+            cudaFuncSetAttribute(conv_halo_kernel<3, 2, 2, true>, attr, max_smem);
+            cudaFuncSetAttribute(conv_halo_kernel<3, 1, 1, false>, attr, max_smem);
+            cudaFuncSetAttribute(conv_halo_kernel<3, 1, 2, false>, attr, max_smem);
+            cudaFuncSetAttribute(conv_halo_kernel<3, 1, 4, false>, attr, max_smem);
+            cudaFuncSetAttribute(conv_halo_kernel<3, 2, 1, false>, attr, max_smem);
+            cudaFuncSetAttribute(conv_halo_kernel<3, 2, 2, false>, attr, max_smem);
+        }
         c.init = true;
     }
     *out = &c;
@@ -279,6 +287,7 @@ struct IgemmPlan {
     const float* bias;
     bool b_mn, flip;
     int kdim;                        // reduction channels per tap
+    const float* W_lo = nullptr;     // when set, W and W_lo already are the hi and lo TF32 planes
 };
 
 static int launch_igemm(DeviceCtx* c, const IgemmPlan& pl, int mode3x, cudaStream_t stream)
@@ -355,7 +364,7 @@ static int env_tile_mode()
 struct HaloChoice {
     bool valid = false;
     int JH = 1, JW = 1, npb = 1, sb = 2, acc_bufs = 1, NI = 1;
-    bool row = false;
+    bool row = false, stat = false;
     double cost = 0, eff = 0;
 };
 
@@ -394,7 +403,8 @@ static HaloChoice plan_halo(const IgemmPlan& pl, int BN, int mode3x, int b_mn)
             const int PH = NI > 1 ? NI * SG : 16 * JH + pl.FH - 1, PW = 8 * JW + pl.FW - 1;
             if (PH > 256 || PW > 256) continue;
             const uint32_t patch_stride = (((uint32_t)PH * PW * 128 + 1023) & ~1023u) * planes;
-            bool row = allow_row && halo_has_row_kernel(pl.FW, JH, JW);
+            const bool stat = allow_row && halo_has_row_kernel(pl.FW, JH, JW);  // a static specialisation exists
+            bool row = stat;
             uint32_t b_stride = b_tile * (row ? pl.FW : 1);
             if (row && (size_t)patch_stride + 2 * (size_t)b_stride + 32768 + 1536 > smem_cap) { row = false; b_stride = b_tile; }
             const int max_sb = row ? pl.FH * 2 : 8;
@@ -417,11 +427,11 @@ static HaloChoice plan_halo(const IgemmPlan& pl, int BN, int mode3x, int b_mn)
             double t = (t_mma > t_l2 ? t_mma : t_l2) + 1500.0;  // fixed per-tile overhead
             if (npb == 1) t *= 1.25;
             if (acc_bufs == 1) t *= 1.15;
-            if (!row) t *= 1.15;
+            if (!stat) t *= 1.3; else if (!row) t *= 1.05;
             const double cost = t / (128.0 * J * eff);
             if (!best.valid || cost < best.cost) {
                 best.valid = true; best.JH = JH; best.JW = JW; best.npb = npb; best.sb = sb;
-                best.acc_bufs = acc_bufs; best.cost = cost; best.eff = eff; best.row = row; best.NI = NI;
+                best.acc_bufs = acc_bufs; best.cost = cost; best.eff = eff; best.row = row; best.stat = stat; best.NI = NI;
             }
         }
     return best;
@@ -477,8 +487,8 @@ static int launch_halo(DeviceCtx* c, const IgemmPlan& pl, int mode3x, cudaStream
     if (rc) return rc;
     // 3xTF32: split W into hi/lo planes once per call (scratch of this stream), load both by TMA
     const float* w_hi = pl.W;
-    const float* w_lo = pl.W;
-    if (mode3x) {
+    const float* w_lo = pl.W_lo ? pl.W_lo : pl.W;
+    if (mode3x && !pl.W_lo) {
         const size_t nW = (size_t)pl.wOC * pl.FH * pl.FW * pl.wIC;
         float* ws = nullptr;
         rc = get_workspace(c, stream, 2 * nW * sizeof(float), &ws);
@@ -515,16 +525,20 @@ static int launch_halo(DeviceCtx* c, const IgemmPlan& pl, int mode3x, cudaStream
     rc = make_tiled_map(&tmO, pl.out, 4, od, ost, obox, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
     int grid = c->sm_count < p.total_tiles ? c->sm_count : p.total_tiles;
-#define HALO_LAUNCH(FW_, JH_, JW_) conv_halo_kernel<FW_, JH_, JW_><<<grid, kHaloThreads, smem, stream>>>(tmA, tmB, tmBlo, tmO, p)
-    if (!ch.row) HALO_LAUNCH(0, 0, 0);
-    else if (ch.JH == 1 && ch.JW == 1) HALO_LAUNCH(3, 1, 1);
-    else if (ch.JH == 1 && ch.JW == 2) HALO_LAUNCH(3, 1, 2);
-    else if (ch.JH == 1 && ch.JW == 4) HALO_LAUNCH(3, 1, 4);
-    else if (ch.JH == 2 && ch.JW == 1) HALO_LAUNCH(3, 2, 1);
-    else HALO_LAUNCH(3, 2, 2);
+#define HALO_LAUNCH(FW_, JH_, JW_, ROW_) \
+    conv_halo_kernel<FW_, JH_, JW_, ROW_><<<grid, kHaloThreads, smem, stream>>>(tmA, tmB, tmBlo, tmO, p)
+#define HALO_LAUNCH_J(JH_, JW_) \
+    do { if (ch.row) HALO_LAUNCH(3, JH_, JW_, true); else HALO_LAUNCH(3, JH_, JW_, false); } while (0)
+    if (!ch.stat) HALO_LAUNCH(0, 0, 0, false);
+    else if (ch.JH == 1 && ch.JW == 1) HALO_LAUNCH_J(1, 1);
+    else if (ch.JH == 1 && ch.JW == 2) HALO_LAUNCH_J(1, 2);
+    else if (ch.JH == 1 && ch.JW == 4) HALO_LAUNCH_J(1, 4);
+    else if (ch.JH == 2 && ch.JW == 1) HALO_LAUNCH_J(2, 1);
+    else HALO_LAUNCH_J(2, 2);
+#undef HALO_LAUNCH_J
 #undef HALO_LAUNCH
-    note_launch(ch.row ? "halo_row" : "halo");
-    snprintf(g_plan, sizeof(g_plan), "halo%s JH=%d JW=%d NI=%d BN=%d npb=%d sb=%d acc=%d eff=%.2f", ch.row ? "_row" : "", ch.JH,
+    note_launch(ch.row ? "halo_row" : (ch.stat ? "halo_tap" : "halo"));
+    snprintf(g_plan, sizeof(g_plan), "halo%s JH=%d JW=%d NI=%d BN=%d npb=%d sb=%d acc=%d eff=%.2f", ch.row ? "_row" : (ch.stat ? "_tap" : ""), ch.JH,
              ch.JW, ch.NI, BN, ch.npb, ch.sb, ch.acc_bufs, ch.eff);
     rc = check_launch("conv_halo_kernel");
     return rc;
@@ -822,7 +836,28 @@ int alpha_conv3d_deltaX(const AlphaConvShape* s, const float* deltaY, const floa
         pl.out = deltaX; pl.oH = s->IH; pl.oW = s->IW; pl.ncols = s->IC;
         pl.W = W; pl.wOC = s->OC; pl.wIC = s->IC; pl.bias = nullptr;
         pl.b_mn = true; pl.flip = true; pl.kdim = s->OC;
-        rc = launch_halo(c, pl, g_math.load() == ALPHA_MATH_3XTF32, stream);
+        const int mode3x = g_math.load() == ALPHA_MATH_3XTF32;
+        if (env_tile_mode() != 1 && s->OC % 32 == 0 && env_int("ALPHA_DX_TRANSPOSE", 1)) {
+            // deltaX as a forward conv over deltaY with Wt[ic][rotated tap][oc], built once per call
+            const int taps = s->FH * s->FW;
+            const size_t nW = (size_t)s->OC * taps * s->IC;
+            float* ws = nullptr;
+            rc = get_workspace(c, stream, (mode3x ? 2 : 1) * nW * sizeof(float), &ws);
+            if (rc) return rc;
+            IgemmPlan pt = pl;
+            pt.W = ws; pt.W_lo = mode3x ? ws + nW : nullptr;
+            pt.wOC = s->IC; pt.wIC = s->OC; pt.b_mn = false; pt.flip = false;
+            // decide first whether the halo kernel takes the shape; only then pay for the transpose
+            dim3 tg((s->IC + 31) / 32, (s->OC + 31) / 32, taps);
+            transpose_weights_kernel<<<tg, 256, 0, stream>>>(W, ws, mode3x ? ws + nW : nullptr, s->OC, s->IC, taps, mode3x);
+            note_launch("transpose_w");
+            rc = check_launch("transpose_weights_kernel");
+            if (rc) return rc;
+            if (!mode3x) pt.W_lo = nullptr;
+            rc = launch_halo(c, pt, mode3x, stream);
+            if (rc != 1) return rc;
+        }
+        rc = launch_halo(c, pl, mode3x, stream);
         if (rc != 1) return rc;
         return launch_igemm(c, pl, g_math.load() == ALPHA_MATH_3XTF32, stream);
     }

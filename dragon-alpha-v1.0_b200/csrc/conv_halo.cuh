@@ -88,16 +88,17 @@ __device__ __forceinline__ void issue_chunk(uint32_t d, uint32_t a_lo, uint32_t 
     }
 }
 
-// FW_T > 0 selects the row-staged specialisation: FW, JH and JW are compile-time, one B stage holds
-// the FW taps of one filter row, and the MMAs of a stage are issued as straight-line code with
-// immediate descriptor offsets.  FW_T == 0 is the generic form: any filter, one tap per B stage.
-template <int FW_T, int JH_T, int JW_T>
+// FW_T > 0 selects a specialisation with compile-time FW, JH and JW whose MMAs are issued as
+// straight-line code with immediate descriptor offsets; with ROW_T one B stage holds the FW taps of
+// one filter row, otherwise one tap.  FW_T == 0 is the generic form: any filter, one tap per stage.
+template <int FW_T, int JH_T, int JW_T, bool ROW_T>
 __global__ void __launch_bounds__(kHaloThreads, 1)
     conv_halo_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                      const __grid_constant__ CUtensorMap tmBlo, const __grid_constant__ CUtensorMap tmO,
                      const HaloParams p)
 {
-    constexpr bool kRow = FW_T > 0;
+    constexpr bool kStatic = FW_T > 0;
+    constexpr bool kRow = kStatic && ROW_T;
     const int tps = kRow ? FW_T : 1;              // taps per B stage
     const int stages_per_chunk = kRow ? p.FH : p.FH * p.FW;
     extern __shared__ uint8_t smem_raw[];
@@ -268,6 +269,34 @@ __global__ void __launch_bounds__(kHaloThreads, 1)
                             acc_first = 1u;
                             mma_commit_a(bempty_a + 8 * bp.idx);
                             bp.advance(p.sb);
+                        }
+                    } else if constexpr (kStatic) {
+                        constexpr uint32_t kPW8 = (8 * JW_T + FW_T - 1) * 8;
+                        for (int fh = 0; fh < p.FH && ok; ++fh, a_row += kPW8) {
+#pragma unroll
+                            for (int fw = 0; fw < FW_T; ++fw) {
+                                if (!wait_prof(bwait_a + 8 * bp.idx, bp.phase, prof_on, w_b)) { report(p.status, kStatusMmaTimeout); ok = false; break; }
+                                tc_fence_after_sync();
+                                const uint32_t bl = bring_lo0 + bp.idx * b_stride16;
+                                if (p.mode3x) {
+#pragma unroll
+                                    for (int jh = 0; jh < JH_T; ++jh)
+#pragma unroll
+                                        for (int jw = 0; jw < JW_T; ++jw)
+                                            issue_chunk<true>(d0 + (jh * JW_T + jw) * p.BN, a_row + fw * 8 + jh * 16 * kPW8 + jw * 64,
+                                                              a_dhi, bl, b_dhi, b_kstep, a_lo_off, b_lo_off, p.idesc, acc_first);
+                                } else {
+#pragma unroll
+                                    for (int jh = 0; jh < JH_T; ++jh)
+#pragma unroll
+                                        for (int jw = 0; jw < JW_T; ++jw)
+                                            issue_chunk<false>(d0 + (jh * JW_T + jw) * p.BN, a_row + fw * 8 + jh * 16 * kPW8 + jw * 64,
+                                                               a_dhi, bl, b_dhi, b_kstep, a_lo_off, b_lo_off, p.idesc, acc_first);
+                                }
+                                acc_first = 1u;
+                                mma_commit_a(bempty_a + 8 * bp.idx);
+                                bp.advance(p.sb);
+                            }
                         }
                     } else {
                     for (int fh = 0; fh < p.FH && ok; ++fh, a_row += row_step) {
