@@ -29,6 +29,10 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under
+# profiles/ (kernel, launch shape, math mode) -> bytes
+NCU_TRAFFIC = {}
+
 METRIC = "conv fwd+deltaX+deltaW throughput, 3x3 layer sweep (batch 256 per GPU)"
 UNIT = "TFLOP/s"
 OPS = ("fwd", "dx", "dw")
@@ -265,7 +269,7 @@ def run_ours(args):
                 run_op(L, op)
                 if events is not None:
                     e1.record()
-                    events.append((li, op, e0, e1))
+                    events.append((li, op, e0, e1, lib.last_algo()))
             if world > 1 and "dw" in ops:
                 ready = torch.cuda.Event(); ready.record()
                 with torch.cuda.stream(comm_stream):
@@ -312,26 +316,37 @@ def run_ours(args):
     ms_step = ms_total / args.steps
     value = world * step_flops / (ms_step * 1e-3) / 1e12
 
-    # per-kernel-family time from the events of the timed region
-    fam = {"igemm": dict(ms=0.0, flops=0.0, n=0), "dw": dict(ms=0.0, flops=0.0, n=0)}  # fwd+deltaX | deltaW
-    per_op = {}
-    for li, op, e0, e1 in events:
+    # per-kernel time from the CUDA events of the timed region; the roofline is reported for the
+    # kernel with the largest share, on its longest-running launch shape
+    KERNELS = {"halo": "conv_halo_kernel", "halo_row": "conv_halo_kernel", "halo_tap": "conv_halo_kernel",
+               "igemm": "conv_igemm_kernel", "dw_halo": "conv_dw_halo_kernel", "dw": "conv_dw_kernel",
+               "simt": "conv_*_simt"}
+    fam, per_op = {}, {}
+    for li, op, e0, e1, algo in events:
         ms = e0.elapsed_time(e1)
-        f = fam["dw" if op == "dw" else "igemm"]
+        kname = KERNELS.get(algo, algo)
+        f = fam.setdefault(kname, dict(ms=0.0, flops=0.0, n=0))
         f["ms"] += ms; f["flops"] += layers[li]["flops"]; f["n"] += 1
         k = "%s_%dx%dx%d" % (op, layers[li]["hw"], layers[li]["hw"], layers[li]["c"])
-        per_op.setdefault(k, dict(ms=[], flops=layers[li]["flops"]))["ms"].append(ms)
+        e = per_op.setdefault(k, dict(ms=[], flops=layers[li]["flops"], kernel=kname, li=li, op=op))
+        e["ms"].append(ms)
     dom = max(fam, key=lambda k: fam[k]["ms"])
+    heavy = max((k for k in per_op if per_op[k]["kernel"] == dom), key=lambda k: statistics.mean(per_op[k]["ms"]))
+    h = per_op[heavy]
+    hl = layers[h["li"]]
     tf32_peak = peaks["bf16_sustained"] / 2.0
-    achieved = fam[dom]["flops"] / (fam[dom]["ms"] * 1e-3) / 1e12
+    achieved = h["flops"] / (statistics.mean(h["ms"]) * 1e-3) / 1e12
+    alg_bytes = synth.conv_bytes(B, hl["hw"], hl["hw"], hl["c"], hl["hw"], hl["hw"], hl["c"], 3, 3)
     roofline = {
-        "bound": "tensor", "kernel": "conv_igemm_kernel" if dom == "igemm" else "conv_dw_kernel",
-        "achieved": achieved, "peak": tf32_peak, "unit": "TFLOP/s", "frac": achieved / tf32_peak,
-        "traffic": None,
+        "bound": "tensor", "kernel": dom, "launch": heavy, "achieved": achieved, "peak": tf32_peak, "unit": "TFLOP/s",
+        "frac": achieved / tf32_peak,
+        "traffic": NCU_TRAFFIC.get((dom, heavy, args.math)),
+        "algorithmic_bytes": alg_bytes,
         "peak_source": "%s bf16 sustained %.1f TFLOP/s / 2 (dense TF32 rate is half the bf16 rate)" % (
             peaks["source"], peaks["bf16_sustained"]),
         "note": "3xTF32 issues three MMAs per product, so its useful-FLOP ceiling is peak/3" if args.math == "3xtf32" else "plain TF32",
         "time_share": fam[dom]["ms"] / max(sum(f["ms"] for f in fam.values()), 1e-9),
+        "kernel_time_shares": {k: round(v["ms"] / max(sum(f["ms"] for f in fam.values()), 1e-9), 3) for k, v in fam.items()},
     }
     per_op_tflops = {k: v["flops"] / (statistics.mean(v["ms"]) * 1e-3) / 1e12 for k, v in per_op.items()}
 

@@ -124,20 +124,6 @@ int get_ctx(DeviceCtx** out)
         const int max_smem = 227 * 1024;
         cudaFuncSetAttribute(conv_igemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
         cudaFuncSetAttribute(conv_dw_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
-        {
-            const auto attr = cudaFuncAttributeMaxDynamicSharedMemorySize;
-            cudaFuncSetAttribute(conv_halo_kernel<0, 0, 0, false>, attr, max_smem);
-            cudaFuncSetAttribute(conv_halo_kernel<3, 1, 1, true>, attr, max_smem);
-            cudaFuncSetAttribute(conv_halo_kernel<3, 1, 2, true>, attr, max_smem);
-            cudaFuncSetAttribute(conv_halo_kernel<3, 1, 4, true>, attr, max_smem);
-            cudaFuncSetAttribute(conv_halo_kernel<3, 2, 1, true>, attr, max_smem);
-            cudaFuncSetAttribute(conv_halo_kernel<3, 2, 2, true>, attr, max_smem);
-            cudaFuncSetAttribute(conv_halo_kernel<3, 1, 1, false>, attr, max_smem);
-            cudaFuncSetAttribute(conv_halo_kernel<3, 1, 2, false>, attr, max_smem);
-            cudaFuncSetAttribute(conv_halo_kernel<3, 1, 4, false>, attr, max_smem);
-            cudaFuncSetAttribute(conv_halo_kernel<3, 2, 1, false>, attr, max_smem);
-            cudaFuncSetAttribute(conv_halo_kernel<3, 2, 2, false>, attr, max_smem);
-        }
         c.init = true;
     }
     *out = &c;
@@ -288,6 +274,10 @@ struct IgemmPlan {
     bool b_mn, flip;
     int kdim;                        // reduction channels per tap
     const float* W_lo = nullptr;     // when set, W and W_lo already are the hi and lo TF32 planes
+    // output element (n, oh, ow, c) lives at out[((n * oNH + oh * oSH) * oNW + ow * oSW) * ncols + c]:
+    // a stride phase of deltaX writes every oSH-th row and oSW-th column of an oNH x oNW image
+    int oSH = 1, oSW = 1, oNH = 0, oNW = 0;
+    bool force = false;              // take the halo kernel even when few tile pixels are real
 };
 
 static int launch_igemm(DeviceCtx* c, const IgemmPlan& pl, int mode3x, cudaStream_t stream)
@@ -374,8 +364,39 @@ struct HaloChoice {
 // The row-staged specialisations that exist (FW, JH, JW); everything else runs the generic form.
 static bool halo_has_row_kernel(int FW, int JH, int JW)
 {
-    if (FW != 3) return false;
+    if (FW != 1 && FW != 2 && FW != 3 && FW != 5) return false;
     return (JH == 1 && (JW == 1 || JW == 2 || JW == 4)) || (JH == 2 && (JW == 1 || JW == 2));
+}
+
+struct HaloLaunch {
+    int grid;
+    size_t smem;
+    cudaStream_t stream;
+    const CUtensorMap *tmA, *tmB, *tmBlo, *tmO;
+    const HaloParams* p;
+};
+
+template <int FW_T, int JH_T, int JW_T, bool ROW_T>
+static void halo_launch_one(const HaloLaunch& L)
+{
+    static bool attr_done = false;  // per instantiation; the attribute is per function, any device
+    if (!attr_done) {
+        cudaFuncSetAttribute(conv_halo_kernel<FW_T, JH_T, JW_T, ROW_T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        attr_done = true;
+    }
+    conv_halo_kernel<FW_T, JH_T, JW_T, ROW_T><<<L.grid, kHaloThreads, L.smem, L.stream>>>(*L.tmA, *L.tmB, *L.tmBlo, *L.tmO, *L.p);
+}
+
+template <int FW_T>
+static void halo_launch_fw(const HaloLaunch& L, int JH, int JW, bool row)
+{
+#define HALO_J(JH_, JW_) do { if (row) halo_launch_one<FW_T, JH_, JW_, true>(L); else halo_launch_one<FW_T, JH_, JW_, false>(L); } while (0)
+    if (JH == 1 && JW == 1) HALO_J(1, 1);
+    else if (JH == 1 && JW == 2) HALO_J(1, 2);
+    else if (JH == 1 && JW == 4) HALO_J(1, 4);
+    else if (JH == 2 && JW == 1) HALO_J(2, 1);
+    else HALO_J(2, 2);
+#undef HALO_J
 }
 
 static HaloChoice plan_halo(const IgemmPlan& pl, int BN, int mode3x, int b_mn)
@@ -448,7 +469,7 @@ static int launch_halo(DeviceCtx* c, const IgemmPlan& pl, int mode3x, cudaStream
     if (BN > 256) BN = (pl.ncols % 256 == 0 || pl.ncols > 512) ? 256 : 128;
     HaloChoice ch = plan_halo(pl, BN, mode3x, pl.b_mn);
     if (!ch.valid) return 1;
-    if (tile_mode == 0 && ch.eff < 0.6) return 1;
+    if (tile_mode == 0 && ch.eff < 0.6 && !pl.force) return 1;
 
     HaloParams p{};
     p.out = pl.out; p.bias = pl.bias; p.status = c->status; p.prof = c->prof;
@@ -519,29 +540,86 @@ static int launch_halo(DeviceCtx* c, const IgemmPlan& pl, int mode3x, cudaStream
     }
     if (rc) return rc;
     // output [N][OH][OW][ldo] for the epilogue's TMA stores: one slab = 32 channels x 8 columns x 16 rows
+    const int oNH = pl.oNH ? pl.oNH : pl.oH, oNW = pl.oNW ? pl.oNW : pl.oW;
     cuuint64_t od[4] = {(cuuint64_t)pl.ncols, (cuuint64_t)pl.oW, (cuuint64_t)pl.oH, (cuuint64_t)pl.aN};
-    cuuint64_t ost[3] = {(cuuint64_t)pl.ncols * 4, (cuuint64_t)pl.oW * pl.ncols * 4, (cuuint64_t)pl.oH * pl.oW * pl.ncols * 4};
+    cuuint64_t ost[3] = {(cuuint64_t)pl.oSW * pl.ncols * 4, (cuuint64_t)pl.oSH * oNW * pl.ncols * 4,
+                         (cuuint64_t)oNH * oNW * pl.ncols * 4};
     cuuint32_t obox[4] = {32, 8, (cuuint32_t)(ch.NI > 1 ? pl.oH : 16), 1};
     rc = make_tiled_map(&tmO, pl.out, 4, od, ost, obox, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
     int grid = c->sm_count < p.total_tiles ? c->sm_count : p.total_tiles;
-#define HALO_LAUNCH(FW_, JH_, JW_, ROW_) \
-    conv_halo_kernel<FW_, JH_, JW_, ROW_><<<grid, kHaloThreads, smem, stream>>>(tmA, tmB, tmBlo, tmO, p)
-#define HALO_LAUNCH_J(JH_, JW_) \
-    do { if (ch.row) HALO_LAUNCH(3, JH_, JW_, true); else HALO_LAUNCH(3, JH_, JW_, false); } while (0)
-    if (!ch.stat) HALO_LAUNCH(0, 0, 0, false);
-    else if (ch.JH == 1 && ch.JW == 1) HALO_LAUNCH_J(1, 1);
-    else if (ch.JH == 1 && ch.JW == 2) HALO_LAUNCH_J(1, 2);
-    else if (ch.JH == 1 && ch.JW == 4) HALO_LAUNCH_J(1, 4);
-    else if (ch.JH == 2 && ch.JW == 1) HALO_LAUNCH_J(2, 1);
-    else HALO_LAUNCH_J(2, 2);
-#undef HALO_LAUNCH_J
-#undef HALO_LAUNCH
+    HaloLaunch L{grid, smem, stream, &tmA, &tmB, &tmBlo, &tmO, &p};
+    if (!ch.stat) halo_launch_one<0, 0, 0, false>(L);
+    else if (pl.FW == 1) halo_launch_fw<1>(L, ch.JH, ch.JW, ch.row);
+    else if (pl.FW == 2) halo_launch_fw<2>(L, ch.JH, ch.JW, ch.row);
+    else if (pl.FW == 3) halo_launch_fw<3>(L, ch.JH, ch.JW, ch.row);
+    else halo_launch_fw<5>(L, ch.JH, ch.JW, ch.row);
     note_launch(ch.row ? "halo_row" : (ch.stat ? "halo_tap" : "halo"));
     snprintf(g_plan, sizeof(g_plan), "halo%s JH=%d JW=%d NI=%d BN=%d npb=%d sb=%d acc=%d eff=%.2f", ch.row ? "_row" : (ch.stat ? "_tap" : ""), ch.JH,
              ch.JW, ch.NI, BN, ch.npb, ch.sb, ch.acc_bufs, ch.eff);
     rc = check_launch("conv_halo_kernel");
     return rc;
+}
+
+static bool taps_fit64(const AlphaConvShape* s) { return s->FH * s->FW <= 64; }
+
+// ---- strided deltaX: one stride-1 convolution per output phase ------------------------------------
+//
+// deltaX[n, sh*a + py, sw*b + px, :] only receives the filter taps fh = ry + sh*u, fw = rx + sw*v with
+// ry = (py + ph) % sh, rx = (px + pw) % sw.  Each of the sh*sw phases is therefore a stride-1
+// convolution of deltaY with a sub-filter (the reference's "kernel split",
+// Cuda_dconv3D_deltaX/dconv3D_dX_kernelSplit_remode_v2.cuh:35-66), run on the halo kernel with the
+// phase's weights transposed and pre-split, and written through a tensor map that addresses every
+// sh-th row and sw-th column of deltaX.
+// Returns 1 when the shape is left to the gather kernel, 0 when all phases were launched, < 0 on error.
+static int launch_dx_phases(DeviceCtx* c, const AlphaConvShape* s, const float* dY, const float* W, float* dX,
+                            int mode3x, cudaStream_t stream)
+{
+    if (env_tile_mode() == 1 || !env_int("ALPHA_DX_PHASES", 1)) return 1;
+    if (s->OC % 32 != 0 || s->sh > 8 || s->sw > 8 || !taps_fit64(s)) return 1;
+    if (s->FH < s->sh || s->FW < s->sw) return 1;  // some phase would get no tap at all
+    if (s->IH < s->sh || s->IW < s->sw) return 1;
+    const int taps = s->FH * s->FW;
+    const size_t nW = (size_t)s->OC * taps * s->IC;
+    float* ws = nullptr;
+    int rc = get_workspace(c, stream, (mode3x ? 2 : 1) * nW * sizeof(float), &ws);
+    if (rc) return rc;
+    size_t woff = 0;
+    for (int py = 0; py < s->sh; ++py)
+        for (int px = 0; px < s->sw; ++px) {
+            const int ry = (py + s->ph) % s->sh, rx = (px + s->pw) % s->sw;
+            const int Uy = (s->FH - ry + s->sh - 1) / s->sh, Ux = (s->FW - rx + s->sw - 1) / s->sw;
+            const int qy = (py + s->ph - ry) / s->sh, qx = (px + s->pw - rx) / s->sw;
+            const int A = (s->IH - py + s->sh - 1) / s->sh, Bw = (s->IW - px + s->sw - 1) / s->sw;
+            const int ptaps = Uy * Ux;
+            TapMap map{};
+            map.n = ptaps;
+            for (int u = 0; u < Uy; ++u)
+                for (int v = 0; v < Ux; ++v)
+                    map.src[u * Ux + v] = (ry + s->sh * (Uy - 1 - u)) * s->FW + (rx + s->sw * (Ux - 1 - v));
+            const size_t pn = (size_t)s->OC * ptaps * s->IC;
+            float* whi = ws + woff;
+            float* wlo = mode3x ? ws + nW + woff : nullptr;
+            woff += pn;
+            dim3 tg((s->IC + 31) / 32, (s->OC + 31) / 32, ptaps);
+            transpose_weights_kernel<<<tg, 256, 0, stream>>>(W, whi, wlo, s->OC, s->IC, taps, map, mode3x);
+            note_launch("transpose_w");
+            rc = check_launch("transpose_weights_kernel");
+            if (rc) return rc;
+            IgemmPlan pl{};
+            pl.act = dY; pl.aN = s->N; pl.aH = s->OH; pl.aW = s->OW; pl.aC = s->OC;
+            pl.FH = Uy; pl.FW = Ux; pl.sh = 1; pl.sw = 1;
+            pl.pad_h = Uy - 1 - qy; pl.pad_w = Ux - 1 - qx;
+            pl.out = dX + ((size_t)py * s->IW + px) * s->IC;
+            pl.oH = A; pl.oW = Bw; pl.ncols = s->IC;
+            pl.oSH = s->sh; pl.oSW = s->sw; pl.oNH = s->IH; pl.oNW = s->IW;
+            pl.W = whi; pl.W_lo = wlo; pl.wOC = s->IC; pl.wIC = s->OC; pl.bias = nullptr;
+            pl.b_mn = false; pl.flip = false; pl.kdim = s->OC; pl.force = true;
+            rc = launch_halo(c, pl, mode3x, stream);
+            if (rc == 1) return fail(ALPHA_E_ARG, "strided deltaX: phase (%d,%d) does not fit the halo kernel", py, px);
+            if (rc) return rc;
+        }
+    return ALPHA_OK;
 }
 
 // ---- deltaW, halo-tile kernel (stride 1): plan and launch -----------------------------------------
@@ -837,7 +915,7 @@ int alpha_conv3d_deltaX(const AlphaConvShape* s, const float* deltaY, const floa
         pl.W = W; pl.wOC = s->OC; pl.wIC = s->IC; pl.bias = nullptr;
         pl.b_mn = true; pl.flip = true; pl.kdim = s->OC;
         const int mode3x = g_math.load() == ALPHA_MATH_3XTF32;
-        if (env_tile_mode() != 1 && s->OC % 32 == 0 && env_int("ALPHA_DX_TRANSPOSE", 1)) {
+        if (env_tile_mode() != 1 && s->OC % 32 == 0 && taps_fit64(s) && env_int("ALPHA_DX_TRANSPOSE", 1)) {
             // deltaX as a forward conv over deltaY with Wt[ic][rotated tap][oc], built once per call
             const int taps = s->FH * s->FW;
             const size_t nW = (size_t)s->OC * taps * s->IC;
@@ -849,7 +927,10 @@ int alpha_conv3d_deltaX(const AlphaConvShape* s, const float* deltaY, const floa
             pt.wOC = s->IC; pt.wIC = s->OC; pt.b_mn = false; pt.flip = false;
             // decide first whether the halo kernel takes the shape; only then pay for the transpose
             dim3 tg((s->IC + 31) / 32, (s->OC + 31) / 32, taps);
-            transpose_weights_kernel<<<tg, 256, 0, stream>>>(W, ws, mode3x ? ws + nW : nullptr, s->OC, s->IC, taps, mode3x);
+            TapMap map{};
+            map.n = taps;
+            for (int t = 0; t < taps; ++t) map.src[t] = taps - 1 - t;
+            transpose_weights_kernel<<<tg, 256, 0, stream>>>(W, ws, mode3x ? ws + nW : nullptr, s->OC, s->IC, taps, map, mode3x);
             note_launch("transpose_w");
             rc = check_launch("transpose_weights_kernel");
             if (rc) return rc;
@@ -860,6 +941,10 @@ int alpha_conv3d_deltaX(const AlphaConvShape* s, const float* deltaY, const floa
         rc = launch_halo(c, pl, mode3x, stream);
         if (rc != 1) return rc;
         return launch_igemm(c, pl, g_math.load() == ALPHA_MATH_3XTF32, stream);
+    }
+    if (algo != ALPHA_ALGO_SIMT && (s->sh > 1 || s->sw > 1)) {
+        rc = launch_dx_phases(c, s, deltaY, W, deltaX, g_math.load() == ALPHA_MATH_3XTF32, stream);
+        if (rc != 1) return rc;
     }
     const size_t total = (size_t)s->N * s->IH * s->IW * s->IC;
     conv_dx_simt<<<simt_grid(total, c->sm_count), 256, 0, stream>>>(deltaY, W, deltaX, to_dev_shape(s));

@@ -126,27 +126,33 @@ __global__ void split_tensor_kernel(const float4* __restrict__ src, float4* __re
     }
 }
 
-// Wt[ic][taps-1-tap][oc] = W[oc][tap][ic]: the weights of deltaX seen as a forward convolution over
-// deltaY (channels swapped, filter rotated by 180 degrees), written as hi (and, when lo != nullptr,
-// lo) TF32 planes.  32 x 32 tiles through shared memory; grid (ceil(IC/32), ceil(OC/32), taps).
+// Source filter taps of a transposed weight tensor: output tap t reads W[.][src[t]][.].
+struct TapMap {
+    int n;
+    int src[64];
+};
+
+// Wt[ic][t][oc] = W[oc][map.src[t]][ic]: the weights of deltaX seen as a forward convolution over
+// deltaY (channels swapped; the tap list rotates the filter by 180 degrees and, for strided
+// convolutions, picks the sub-filter of one output phase), written as hi (and, when `split`, lo) TF32
+// planes.  32 x 32 tiles through shared memory; grid (ceil(IC/32), ceil(OC/32), map.n).
 __global__ void __launch_bounds__(256)
     transpose_weights_kernel(const float* __restrict__ W, float* __restrict__ hi, float* __restrict__ lo, int OC,
-                             int IC, int taps, int split)
+                             int IC, int taps, const TapMap map, int split)
 {
     __shared__ float tile[32][33];
-    const int tap = blockIdx.z, ic0 = blockIdx.x * 32, oc0 = blockIdx.y * 32;
+    const int t = blockIdx.z, tap = map.src[t], ic0 = blockIdx.x * 32, oc0 = blockIdx.y * 32;
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
     for (int r = ty; r < 32; r += 8) {
         const int oc = oc0 + r, ic = ic0 + tx;
         tile[r][tx] = (oc < OC && ic < IC) ? W[(static_cast<size_t>(oc) * taps + tap) * IC + ic] : 0.f;
     }
     __syncthreads();
-    const int tapf = taps - 1 - tap;
     for (int r = ty; r < 32; r += 8) {
         const int ic = ic0 + r, oc = oc0 + tx;
         if (ic < IC && oc < OC) {
             const float x = tile[tx][r];
-            const size_t o = (static_cast<size_t>(ic) * taps + tapf) * OC + oc;
+            const size_t o = (static_cast<size_t>(ic) * map.n + t) * OC + oc;
             if (split) {
                 const float h = __uint_as_float(to_tf32_rna(x));
                 hi[o] = h;
