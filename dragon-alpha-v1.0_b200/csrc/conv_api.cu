@@ -3,6 +3,7 @@
 #include "conv_kernels.cuh"
 #include "conv_halo.cuh"
 #include "conv_dw_halo.cuh"
+#include "winograd.cuh"
 #include "host_common.h"
 
 #include <atomic>
@@ -807,6 +808,62 @@ static int get_noalloc_ctx(NoAllocCtx** out)
 
 using namespace alpha;
 
+// ---- Winograd F(2,3) forward (3x3, stride 1) ----------------------------------------------------
+//
+// Filter, input and output transforms run as separate memory-bound kernels around four 3x1
+// tensor-core convolutions; the scratch (transformed filter, input and products, about
+// 2|X| + 2|Y| + 4/3|W|) comes from a second per-stream block, because the inner convolutions use
+// the first one for their weight planes.
+static int forward_direct(DeviceCtx* c, const AlphaConvShape* s, const float* X, const float* W, const float* bias,
+                          float* Y, cudaStream_t stream, int algo);
+
+static std::map<cudaStream_t, DeviceCtx::Block> g_wino_ws[64];
+
+static int launch_winograd(DeviceCtx* c, const AlphaConvShape* s, const float* X, const float* W, const float* bias,
+                           float* Y, cudaStream_t stream)
+{
+    if (s->FH != 3 || s->FW != 3 || s->sh != 1 || s->sw != 1)
+        return fail(ALPHA_E_ARG, "Winograd F(2,3) applies to 3x3 stride-1 convolutions only");
+    if (s->OW != s->IW + 2 * s->pw - 2) return fail(ALPHA_E_ARG, "Winograd F(2,3): OW does not match IW, pw");
+    const int OWp = (s->OW + 1) / 2;
+    const size_t nU = (size_t)4 * s->OC * 3 * s->IC;
+    const size_t nV = (size_t)4 * s->N * s->IH * OWp * s->IC;
+    const size_t nM = (size_t)4 * s->N * s->OH * OWp * s->OC;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    float* ws = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_mu);
+        DeviceCtx::Block& b = g_wino_ws[dev][stream];
+        const size_t bytes = (nU + nV + nM) * sizeof(float);
+        if (b.bytes < bytes) {
+            if (b.ptr) { cudaStreamSynchronize(stream); cudaFree(b.ptr); b.ptr = nullptr; b.bytes = 0; }
+            cudaError_t e = cudaMalloc(&b.ptr, bytes);
+            if (e != cudaSuccess) return fail(ALPHA_E_CUDA, "cudaMalloc(winograd scratch %zu B): %s", bytes, cudaGetErrorString(e));
+            b.bytes = bytes;
+        }
+        ws = b.ptr;
+    }
+    float *U = ws, *V = ws + nU, *M = ws + nU + nV;
+    const int cap = c->sm_count * 16;
+    auto blocks = [&](size_t n) { size_t b = (n + 255) / 256; return (unsigned)(b < (size_t)cap ? (b ? b : 1) : cap); };
+    wino_filter_kernel<<<blocks((size_t)s->OC * 3 * s->IC / 4), 256, 0, stream>>>(W, U, s->OC, s->IC);
+    wino_input_kernel<<<blocks(nV / 16), 256, 0, stream>>>(X, V, s->N, s->IH, s->IW, s->IC, OWp, s->pw);
+    note_launch("winograd");
+    int rc = check_launch("winograd transforms");
+    if (rc) return rc;
+    AlphaConvShape t = *s;
+    t.IW = OWp; t.OW = OWp; t.FW = 1; t.pw = 0;  // 3x1 convolution over column pairs
+    for (int k = 0; k < 4; ++k) {
+        rc = forward_direct(c, &t, V + (size_t)k * (nV / 4), U + (size_t)k * (nU / 4), nullptr, M + (size_t)k * (nM / 4),
+                            stream, ALPHA_ALGO_AUTO);
+        if (rc) return rc;
+    }
+    wino_output_kernel<<<blocks(nM / 16), 256, 0, stream>>>(M, bias, Y, s->N, s->OH, s->OW, s->OC, OWp);
+    note_launch("winograd");
+    return check_launch("wino_output_kernel");
+}
+
 // ---- C ABI, layer 1 ----------------------------------------------------------------------------
 
 extern "C" {
@@ -871,6 +928,16 @@ int alpha_conv3d_forward(const AlphaConvShape* s, const float* X, const float* W
     if (rc) return rc;
     cudaStream_t stream = (cudaStream_t)stream_;
     const int algo = g_algo.load();
+    if (algo == ALPHA_ALGO_WINOGRAD) return launch_winograd(c, s, X, W, bias, Y, stream);
+    return forward_direct(c, s, X, W, bias, Y, stream, algo);
+}
+
+}  // extern "C"
+
+static int forward_direct(DeviceCtx* c, const AlphaConvShape* s, const float* X, const float* W, const float* bias,
+                          float* Y, cudaStream_t stream, int algo)
+{
+    int rc;
     const bool tensor_ok = pick_kc(s->IC) != 0 && s->ph < 128 && s->pw < 128 && s->FH <= 256 && s->FW <= 256;
     if (algo == ALPHA_ALGO_TENSOR && !tensor_ok)
         return fail(ALPHA_E_ARG, "tensor path needs IC %% 8 == 0 (IC=%d)", s->IC);
@@ -890,6 +957,8 @@ int alpha_conv3d_forward(const AlphaConvShape* s, const float* X, const float* W
     note_launch("simt");
     return check_launch("conv_fwd_simt");
 }
+
+extern "C" {
 
 int alpha_conv3d_deltaX(const AlphaConvShape* s, const float* deltaY, const float* W, float* deltaX,
                         alpha_stream_t stream_)

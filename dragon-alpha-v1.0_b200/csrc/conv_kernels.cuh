@@ -216,26 +216,29 @@ __global__ void __launch_bounds__(kIgemmThreads)
             const int pr = rem / p.OWo, qc = rem - pr * p.OWo;
             const int w0 = qc * p.sw - p.pw, h0 = pr * p.sh - p.ph;
             const int taps = p.FH * p.FW;
-            for (int it = 0; it < num_it; ++it) {
-                const int s = it % S;
-                const uint32_t par = (it / S) & 1;
-                if (!mbar_wait(&empty[s], par ^ 1)) { report(p.status, kStatusProducerTimeout); break; }
-                const int tap = it / p.kchunks, kc = it - tap * p.kchunks;
-                const int fh = tap / p.FW, fw = tap - fh * p.FW;
-                uint8_t* a_dst = smem + static_cast<size_t>(s) * stage_bytes;
-                uint8_t* b_dst = a_dst + p.a_bytes * planes;
-                mbar_arrive_expect_tx(&full[s], p.a_bytes + p.b_tx);
-                tma_load_im2col_4d(a_dst, &tmA, &full[s], kc * p.KC, w0, h0, n_img,
-                                   static_cast<uint16_t>(fw), static_cast<uint16_t>(fh));
-                if (!p.b_mn) {
-                    tma_load_3d(b_dst, &tmB, &full[s], kc * p.KC, tap, tile_n * p.BN);
-                } else {
-                    const int tapw = p.flip ? (taps - 1 - tap) : tap;
-                    for (int j = 0; j < p.BN / 32; ++j)
-                        tma_load_3d(b_dst + j * (p.KC * 128), &tmB, &full[s],
-                                    tile_n * p.BN + j * 32, tapw, kc * p.KC);
-                }
-            }
+            const uint32_t smem_a = smem_u32(smem), full_a = smem_u32(full), empty_a = smem_u32(empty);
+            RingPos rp;
+            bool ok = true;
+            int tap = 0;
+            for (int fh = 0; fh < p.FH && ok; ++fh)
+                for (int fw = 0; fw < p.FW && ok; ++fw, ++tap)
+                    for (int kc = 0; kc < p.kchunks; ++kc) {
+                        if (!mbar_wait_a(empty_a + 8 * rp.idx, rp.phase ^ 1)) { report(p.status, kStatusProducerTimeout); ok = false; break; }
+                        const uint32_t a_dst = smem_a + rp.idx * stage_bytes;
+                        const uint32_t b_dst = a_dst + p.a_bytes * planes;
+                        const uint32_t bar = full_a + 8 * rp.idx;
+                        mbar_arrive_expect_tx_a(bar, p.a_bytes + p.b_tx);
+                        tma_load_im2col_4d_a(a_dst, &tmA, bar, kc * p.KC, w0, h0, n_img,
+                                             static_cast<uint16_t>(fw), static_cast<uint16_t>(fh));
+                        if (!p.b_mn) {
+                            tma_load_3d_a(b_dst, &tmB, bar, kc * p.KC, tap, tile_n * p.BN);
+                        } else {
+                            const int tapw = p.flip ? (taps - 1 - tap) : tap;
+                            for (int j = 0; j < p.BN / 32; ++j)
+                                tma_load_3d_a(b_dst + j * (p.KC * 128), &tmB, bar, tile_n * p.BN + j * 32, tapw, kc * p.KC);
+                        }
+                        rp.advance(S);
+                    }
         }
         __syncwarp();
     } else if (warp == 1) {
@@ -247,21 +250,18 @@ __global__ void __launch_bounds__(kIgemmThreads)
             const uint32_t b_lbo = p.b_mn ? p.KC * 128u : 16u;
             const uint32_t b_kstep = p.b_mn ? 64u : 2u;
             const uint32_t a_lo_off = p.a_bytes >> 4, b_lo_off = p.b_bytes >> 4;
-            bool ok = true;
-            for (int it = 0; it < num_it && ok; ++it) {
-                const int s = it % S;
-                const uint32_t par = (it / S) & 1;
-                if (!mbar_wait(p.mode3x ? &split_done[s] : &full[s], par)) {
-                    report(p.status, kStatusMmaTimeout);
-                    ok = false;
-                    break;
-                }
+            const uint32_t wait_a = smem_u32(p.mode3x ? split_done : full), empty_a = smem_u32(empty);
+            const uint32_t a_lo0 = smem_desc_lo(smem_u32(smem), 16);
+            const uint32_t b_lo0 = smem_desc_lo(smem_u32(smem) + p.a_bytes * planes, b_lbo);
+            const uint32_t stage16 = stage_bytes >> 4;
+            const int ksteps = p.KC / 8;
+            RingPos rp;
+            uint32_t acc = 0u;
+            for (int it = 0; it < num_it; ++it) {
+                if (!mbar_wait_a(wait_a + 8 * rp.idx, rp.phase)) { report(p.status, kStatusMmaTimeout); break; }
                 tc_fence_after_sync();
-                const uint32_t a_addr = smem_u32(smem + static_cast<size_t>(s) * stage_bytes);
-                const uint32_t al = smem_desc_lo(a_addr, 16);
-                const uint32_t bl = smem_desc_lo(a_addr + p.a_bytes * planes, b_lbo);
-                for (int kk = 0; kk < p.KC / 8; ++kk) {
-                    const uint32_t acc = (it | kk) ? 1u : 0u;
+                const uint32_t al = a_lo0 + rp.idx * stage16, bl = b_lo0 + rp.idx * stage16;
+                for (int kk = 0; kk < ksteps; ++kk) {
                     const uint32_t a_k = al + kk * 2, b_k = bl + kk * b_kstep;
                     if (p.mode3x) {
                         mma_tf32_ss2(tmem_base, a_k + a_lo_off, a_dhi, b_k, b_dhi, p.idesc, acc);
@@ -270,8 +270,10 @@ __global__ void __launch_bounds__(kIgemmThreads)
                     } else {
                         mma_tf32_ss2(tmem_base, a_k, a_dhi, b_k, b_dhi, p.idesc, acc);
                     }
+                    acc = 1u;
                 }
-                mma_commit(&empty[s]);
+                mma_commit_a(empty_a + 8 * rp.idx);
+                rp.advance(S);
             }
             mma_commit(accum);
         }
@@ -281,16 +283,17 @@ __global__ void __launch_bounds__(kIgemmThreads)
         const int tid128 = threadIdx.x - 64;
         bool ok = true;
         if (p.mode3x) {
+            const uint32_t full_a = smem_u32(full), done_a = smem_u32(split_done);
+            RingPos rp;
             for (int it = 0; it < num_it; ++it) {
-                const int s = it % S;
-                const uint32_t par = (it / S) & 1;
-                if (!mbar_wait(&full[s], par)) { report(p.status, kStatusSplitTimeout); ok = false; break; }
-                uint8_t* a_hi = smem + static_cast<size_t>(s) * stage_bytes;
+                if (!mbar_wait_a(full_a + 8 * rp.idx, rp.phase)) { report(p.status, kStatusSplitTimeout); ok = false; break; }
+                uint8_t* a_hi = smem + static_cast<size_t>(rp.idx) * stage_bytes;
                 uint8_t* b_hi = a_hi + p.a_bytes * 2;
-                split_plane(a_hi, a_hi + p.a_bytes, p.a_bytes, tid128);
-                split_plane(b_hi, b_hi + p.b_bytes, p.b_tx, tid128);
+                split_plane_x4(a_hi, a_hi + p.a_bytes, p.a_bytes, tid128, 128);
+                split_plane_x4(b_hi, b_hi + p.b_bytes, p.b_tx, tid128, 128);
                 fence_proxy_async_smem();
-                mbar_arrive(&split_done[s]);
+                mbar_arrive_a(done_a + 8 * rp.idx);
+                rp.advance(S);
             }
         }
         if (ok && !mbar_wait(accum, 0)) { report(p.status, kStatusEpilogueTimeout); ok = false; }

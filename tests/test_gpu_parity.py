@@ -184,3 +184,34 @@ def test_full_size_adjoint_identity(pkg, eng):
     # linearity in the weights: conv(X, 2W) = 2 conv(X, W) exactly (scaling by 2 is exact in fp32)
     Y2 = eng.conv3D(X, W * 2, 1, 1, 1, 1)
     assert torch.equal(Y2, Y * 2)
+
+
+@pytest.mark.parametrize("mode", ["3xtf32", "tf32"])
+@pytest.mark.parametrize("name", ["cfg1_32x32_ic16_oc32", "ic64_oc64_14x14", "ic32_oc20_ragged", "ic64_oc128_7x7", "ic8_oc16_9x7"])
+def test_winograd_forward(pkg, eng, oracle_mod, name, mode):
+    """Winograd F(2,3) forward variant (3x3, stride 1) against the fp64 loop, same bounds as the
+    direct kernels; ragged cases cover odd output widths."""
+    import torch
+    O = oracle_mod
+    lib = pkg.submodule("lib")
+    lib.set_math_mode(mode)
+    N, IH, IW, IC, OC, FH, FW, sh, sw, ph, pw = CASES[name]
+    rng = np.random.default_rng(zlib.crc32(name.encode()) + 1)
+    X = gen((N, IH, IW, IC), "u11", rng)
+    W = gen((OC, FH, FW, IC), "u11", rng)
+    B = rng.uniform(-0.1, 0.1, (OC,)).astype(np.float32)
+    dev = torch.device("cuda:0")
+    tX, tW, tB = (torch.from_numpy(a).to(dev) for a in (X, W, B))
+    lib.set_algo("winograd")
+    try:
+        Y = eng.conv3D_biased(tX, tW, tB, sh, sw, ph, pw)
+        algo = lib.last_algo()
+        status = lib.device_status()
+    finally:
+        lib.set_algo("auto")
+    assert status == 0 and algo == "winograd"
+    Y64, SY = O.conv3D_f64(X, W, sh, sw, ph, pw, threads=8)
+    m = metrics(Y.cpu().numpy(), Y64 + B.astype(np.float64), SY + np.abs(B).astype(np.float64))
+    record(dict(case=name, mode=mode, tile="winograd", fwd=m))
+    # the transforms add and halve in fp32 before the products: allow twice the direct bound
+    assert m["finite"] and m["norm"] <= TOL[mode]["norm"] and m["comp"] <= 2 * TOL[mode]["comp"], m
