@@ -60,10 +60,10 @@ struct HaloParams {
 // Bounded wait that also charges the waited cycles to a counter when profiling is on.
 __device__ __forceinline__ bool wait_prof(uint32_t bar, uint32_t parity, bool prof, unsigned long long& acc)
 {
-    if (mbar_try_wait_a(bar, parity)) return true;
-    if (!prof) return mbar_wait_slow_a(bar, parity);
+    if (!prof) return mbar_wait_a(bar, parity);
+    // try_wait itself may suspend the thread for a while, so the whole call is timed
     const long long t0 = clock64();
-    const bool ok = mbar_wait_slow_a(bar, parity);
+    const bool ok = mbar_wait_a(bar, parity);
     acc += static_cast<unsigned long long>(clock64() - t0);
     return ok;
 }

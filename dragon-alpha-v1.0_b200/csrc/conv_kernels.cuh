@@ -57,11 +57,13 @@ __device__ __forceinline__ void report(int* status, int code)
     if (status) atomicCAS(status, 0, code);
 }
 
+// Round to TF32 (10 explicit mantissa bits), nearest with ties away from zero: add half a TF32 ulp
+// to the magnitude and clear the 13 low bits.  Two full-rate integer instructions; the dedicated
+// conversion instruction (cvt.rna.tf32.f32) runs at a fraction of that rate and made the operand
+// split the slowest stage of the 3xTF32 kernels.
 __device__ __forceinline__ uint32_t to_tf32_rna(float x)
 {
-    uint32_t u;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
-    return u;
+    return (__float_as_uint(x) + 0x1000u) & 0xFFFFE000u;
 }
 
 // hi = tf32(x), lo = tf32(x - hi): x = hi + lo up to 2^-22 |x|.
