@@ -1,0 +1,29 @@
+#!/bin/bash
+# Builds the reference's three cu32 convolution libraries for sm_100 as a GPU-side oracle
+# (TEST INFRASTRUCTURE).  Needs the reference checkout; writes only into oracle/_ref/ (git-ignored):
+# a patched copy of the three source directories (MSVC-only declarator lists and two locals that
+# shadow a template parameter are rewritten, nothing else) and one shared object per library with
+# the reference's own JNI entry points.  usage: build_ref_gpu.sh [reference root]
+set -e
+REF=${1:-/root/reference}
+HERE=$(cd "$(dirname "$0")" && pwd)
+OUT=$HERE/_ref/cu32
+NVCC=${NVCC:-/usr/local/cuda/bin/nvcc}
+mkdir -p "$OUT"
+for lib in Cuda_conv3D Cuda_dconv3D_deltaX Cuda_dconv3D_deltaW; do
+    rm -rf "$OUT/$lib"
+    cp -r "$REF/src/cu32_src/$lib/$lib" "$OUT/$lib"
+    chmod -R u+w "$OUT/$lib"
+done
+# MSVC accepts `int a, int b;` - standard C++ does not
+sed -i -E 's/int X_fh, int X_fw;/int X_fh, X_fw;/' "$OUT"/Cuda_conv3D/*.cuh
+sed -i -E 's/int GNr = GN \& 127, int GMr = /int GNr = GN \& 127; int GMr = /' "$OUT"/Cuda_conv3D/conv3D.cuh
+# locals that redeclare the template parameter OH_OW
+sed -i -E 's/const int OH_OW = OH \* OW, GK = N \* OH_OW;/const int GK = N * OH_OW;/' "$OUT"/Cuda_dconv3D_deltaW/dconv3d_dW_Gemm_kernel_EX2.cuh
+sed -i -E 's/^\tint OH_OW = OH \* OW;\r?$//' "$OUT"/Cuda_dconv3D_deltaW/dconv3d_dW_GemmSK_kernel_EX2.cuh
+for lib in Cuda_conv3D Cuda_dconv3D_deltaX Cuda_dconv3D_deltaW; do
+    echo "building $lib ..."
+    (cd "$OUT/$lib" && "$NVCC" -gencode arch=compute_100,code=sm_100 -O2 -w -shared -Xcompiler -fPIC \
+        -I"$HERE/jni_stub" -o "$HERE/_ref/libcu32_$lib.so" A.cu)
+done
+ls -la "$HERE"/_ref/libcu32_*.so

@@ -1,0 +1,232 @@
+"""Driver of the reference's own cu32 CUDA kernels, rebuilt for sm_100 (TEST INFRASTRUCTURE).
+
+`oracle/build_ref_gpu.sh` compiles the reference's Cuda_conv3D, Cuda_dconv3D_deltaX and
+Cuda_dconv3D_deltaW libraries from its checkout into oracle/_ref/libcu32_*.so with their original JNI
+entry points.  This module calls those entry points through a hand-made JNIEnv function table and
+mirrors the kernel-family selection of CudaFloat32EngineBase
+(src/alpha_src/z/dragon/engine/cuda/CudaFloat32EngineBase.java:1355-1474, 1666-1762, 1796-2005), so
+that the tests can compare this repository's kernels with "what cu32 itself computes" on the same
+GPU and the benchmark can time the reference's SIMT kernels on the same box.  Only tests/ and
+bench.py may import it.
+"""
+import ctypes as C
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIBS = {}
+
+
+def available():
+    return all(os.path.exists(os.path.join(_HERE, "_ref", "libcu32_%s.so" % n))
+               for n in ("Cuda_conv3D", "Cuda_dconv3D_deltaX", "Cuda_dconv3D_deltaW"))
+
+
+def _lib(name):
+    if name not in _LIBS:
+        _LIBS[name] = C.CDLL(os.path.join(_HERE, "_ref", "libcu32_%s.so" % name))
+    return _LIBS[name]
+
+
+class _FakeEnv:
+    """JNIEnv whose GetLongArrayRegion (slot 204) hands out the stream handles of the current call."""
+
+    def __init__(self):
+        self.streams = []
+        GETREGION = C.CFUNCTYPE(None, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_int64))
+        FINDCLASS = C.CFUNCTYPE(C.c_void_p, C.c_void_p, C.c_char_p)
+
+        def get_region(env, arr, start, n, buf):
+            for i in range(n):
+                buf[i] = self.streams[start + i]
+
+        def find_class(env, name):
+            raise RuntimeError("the reference library raised a CUDA error (FindClass %r)" % name)
+        self._cbs = [GETREGION(get_region), FINDCLASS(find_class)]
+        self.table = (C.c_void_p * 235)()
+        self.table[204] = C.cast(self._cbs[0], C.c_void_p)
+        self.table[6] = C.cast(self._cbs[1], C.c_void_p)
+        self.env = C.pointer(C.c_void_p(C.addressof(self.table)))
+
+
+def _tile_count(g):
+    """One factor of the Java blockNum helpers (Cuda_conv3D.java:19-42): tiles of 128..4 along g."""
+    b = 0
+    if g > 127:
+        b += g >> 7
+    g &= 127
+    for t in (63, 31, 15, 7):
+        if g == 0:
+            return b
+        if g > t:
+            b += 1
+        g &= t
+    if g > 3:
+        b += 1
+    return b
+
+
+class Cu32Reference:
+    """The reference's conv3D / dconv3D_deltaX / dconv3D_deltaW on torch CUDA tensors (NHWC fp32,
+    N, IC, OC multiples of 4).  Every call synchronises the device before and after."""
+
+    N_STREAMS = 10
+
+    def __init__(self):
+        if not available():
+            raise ImportError("oracle/_ref/libcu32_*.so missing: run oracle/build_ref_gpu.sh where the reference is")
+        self.env = _FakeEnv()
+        self.streams = [torch.cuda.Stream() for _ in range(self.N_STREAMS)]
+        self.env.streams = [s.cuda_stream for s in self.streams]
+        self.c3, self.dx, self.dw = _lib("Cuda_conv3D"), _lib("Cuda_dconv3D_deltaX"), _lib("Cuda_dconv3D_deltaW")
+        self.last = ""
+
+    # -- helpers -----------------------------------------------------------------------------------
+    def _call(self, lib, name, *args):
+        f = getattr(lib, "Java_z_dragon_engine_cuda_impl_math_" + name)
+        f.restype = None
+        conv = []
+        for a in args:
+            if isinstance(a, torch.Tensor):
+                conv.append(C.c_int64(a.data_ptr()))
+            elif isinstance(a, bool):
+                conv.append(C.c_uint8(1 if a else 0))
+            elif a == "streams":
+                conv.append(C.c_void_p(0x5EED))  # the jlongArray handle; only the fake env looks at it
+            elif isinstance(a, tuple) and a[0] == "long":
+                conv.append(C.c_int64(a[1]))
+            else:
+                conv.append(C.c_int(int(a)))
+        f(self.env.env, None, *conv)
+        self.last = name
+
+    @staticmethod
+    def _scale_up(IH, IW, OH, OW, FH, FW, sh, sw):
+        return ((OH - 1) * sh + FH) * ((OW - 1) * sw + FW) / float(IH * IW)
+
+    # -- operators ---------------------------------------------------------------------------------
+    def conv3D(self, X, W, sh, sw, ph, pw):
+        """CudaFloat32EngineBase.conv3D (:1355-1474) with the default flags (remode, texture)."""
+        N, IH, IW, IC = X.shape
+        OC, FH, FW, _ = W.shape
+        OH, OW = (IH + 2 * ph - FH) // sh + 1, (IW + 2 * pw - FW) // sw + 1
+        Y = torch.empty((N, OH, OW, OC), device=X.device, dtype=torch.float32)
+        L = self.N_STREAMS
+        torch.cuda.synchronize()
+        if OC > 31 and N * OH * OW > 31:
+            V2 = N > 63 and OC > 63 and self._scale_up(IH, IW, OH, OW, FH, FW, sh, sw) > 1.05
+            CW = torch.empty(FH * FW * IC * OC, device=X.device, dtype=torch.float32)
+            self._call(self.c3, "Cuda_1conv3D_kernel_1remode", ("long", self.streams[0].cuda_stream), W, CW, FH, FW, OC, IC)
+            torch.cuda.synchronize()
+            if FH == 1 and FW == 1:
+                self._call(self.c3, "Cuda_1conv3D_conv3D_1GemmR_1W1", "streams", L, X, IH, IW, W, CW, Y, N, IC, OC)
+            elif V2:
+                self._call(self.c3, "Cuda_1conv3D_conv3D_1GemmV2R", True, "streams", L, X, IH, IW, W, CW, FH, FW, Y, OH, OW,
+                           N, IC, OC, sh, sw, ph, pw)
+            else:
+                self._call(self.c3, "Cuda_1conv3D_conv3D_1GemmR_1texture", "streams", L, X, IH, IW, W, CW, FH, FW, Y, OH, OW,
+                           N, IC, OC, sh, sw, ph, pw)
+        else:
+            V2 = N > 127 and OC > 127 and self._scale_up(IH, IW, OH, OW, FH, FW, sh, sw) >= 1.25
+            tex = OC > 15
+            if FH == 1 and FW == 1:
+                self._call(self.c3, "Cuda_1conv3D_conv3D_1W1", "streams", L, X, IH, IW, W, Y, N, IC, OC)
+            elif ph == 0 and pw == 0:
+                self._call(self.c3, "Cuda_1conv3D_conv3D_1np", "streams", L, X, IH, IW, W, FH, FW, Y, OH, OW, N, IC, OC, sh, sw)
+            elif V2:
+                self._call(self.c3, "Cuda_1conv3D_conv3DV2", tex, "streams", L, X, IH, IW, W, FH, FW, Y, OH, OW, N, IC, OC,
+                           sh, sw, ph, pw)
+            elif tex:
+                self._call(self.c3, "Cuda_1conv3D_conv3D_1texture", "streams", L, X, IH, IW, W, FH, FW, Y, OH, OW, N, IC, OC,
+                           sh, sw, ph, pw)
+            else:
+                self._call(self.c3, "Cuda_1conv3D_conv3D", "streams", L, X, IH, IW, W, FH, FW, Y, OH, OW, N, IC, OC, sh, sw, ph, pw)
+        torch.cuda.synchronize()
+        return Y
+
+    def dconv3D_deltaX(self, dY, W, IH, IW, sh, sw, ph, pw):
+        """CudaFloat32EngineBase.dconv3D_deltaX (:1796-2005) with the default flags."""
+        N, OH, OW, OC = dY.shape
+        _, FH, FW, IC = W.shape
+        dX = torch.empty((N, IH, IW, IC), device=dY.device, dtype=torch.float32)
+        L = self.N_STREAMS
+        P = "Cuda_1dconv3D_1deltaX_"
+        torch.cuda.synchronize()
+        if IC <= 8 or (IC <= 16 and sh * sw >= 4):
+            self._call(self.dx, P + "dconv3D_1deltaX_1crossAdd", "streams", 7, dY, OH, OW, W, FH, FW, dX, IH, IW, N, IC, OC,
+                       sh, sw, ph, pw)
+        elif FH == 1 and FW == 1:
+            self._call(self.dx, P + "dconv3D_1deltaX_1W1", "streams", L, dY, W, dX, IH, IW, N, IC, OC)
+        elif sh == 1 and sw == 1:
+            V2 = N > 63 and IC > 63 and ((IH - 1 + FH) * (IW - 1 + FW)) / float(OH * OW) > 1.1
+            tex = IC > 15
+            if V2:
+                self._call(self.dx, P + "dconv3D_1deltaX_1V2_1s1", tex, "streams", L, dY, OH, OW, W, FH, FW, dX, IH, IW, N, IC, OC, ph, pw)
+            elif tex:
+                self._call(self.dx, P + "dconv3D_1deltaX_1s1_1texture", "streams", L, dY, OH, OW, W, FH, FW, dX, IH, IW, N, IC, OC, ph, pw)
+            else:
+                self._call(self.dx, P + "dconv3D_1deltaX_1s1", "streams", L, dY, OH, OW, W, FH, FW, dX, IH, IW, N, IC, OC, ph, pw)
+        else:
+            CFH, CFW = (FH + sh - 1) // sh, (FW + sw - 1) // sw
+            CW = torch.empty(OC * CFH * CFW * IC * sh * sw, device=dY.device, dtype=torch.float32)
+            self._call(self.dx, P + "ks_1remodev2", ("long", self.streams[0].cuda_stream), W, FH, FW, CW, CFH, CFW, OC, IC, sh, sw)
+            torch.cuda.synchronize()
+            if sh == 2 and sw == 2 and IH % 2 == 0 and IW % 2 == 0:
+                OH0, OW0 = (IH >> 1) + ((FH + 1) >> 1) - 1, (IW >> 1) + ((FW + 1) >> 1) - 1
+                OH1, OW1 = (IH >> 1) + (FH >> 1) - 1, (IW >> 1) + (FW >> 1) - 1
+                V2 = N > 63 and IC > 63 and 0.25 * ((OH0 + OH1) * (OW0 + OW1)) / (OH * OW) > 1.1
+                if V2:
+                    self._call(self.dx, P + "dconv3D_1deltaX_1ksV2_1Ims2R", False, "streams", L, dY, OH, OW, CW, FH, FW, dX, IH, IW,
+                               N, IC, OC, ph, pw)
+                else:
+                    self._call(self.dx, P + "dconv3D_1deltaX_1ksIms2R", "streams", L, dY, OH, OW, CW, FH, FW, dX, IH, IW, N, IC, OC, ph, pw)
+            elif IH % sh == 0 and IW % sw == 0:
+                self._call(self.dx, P + "dconv3D_1deltaX_1ksImsR", "streams", L, dY, OH, OW, CW, FH, FW, dX, IH, IW, N, IC, OC,
+                           sh, sw, ph, pw)
+            else:
+                self._call(self.dx, P + "dconv3D_1deltaX_1kernelSplit", "streams", L, dY, OH, OW, CW, FH, FW, dX, IH, IW, N, IC, OC,
+                           sh, sw, ph, pw)
+        torch.cuda.synchronize()
+        return dX
+
+    def dconv3D_deltaW(self, X, dY, FH, FW, sh, sw, ph, pw):
+        """CudaFloat32EngineBase.dconv3D_deltaW (:1666-1762): split-K with GridZ from the block counts."""
+        N, IH, IW, IC = X.shape
+        _, OH, OW, OC = dY.shape
+        dW = torch.empty((OC, FH, FW, IC), device=X.device, dtype=torch.float32)
+        L = self.N_STREAMS
+        P = "Cuda_1dconv3D_1deltaW_"
+        GK = N * OH * OW
+        torch.cuda.synchronize()
+        if GK < 512:
+            if FH == 1 and FW == 1:
+                self._call(self.dw, P + "dconv3D_1deltaW_1W1", "streams", L, X, IH, IW, dY, dW, N, IC, OC)
+            else:
+                self._call(self.dw, P + "dconv3D_1deltaW", "streams", L, X, IH, IW, dY, OH, OW, dW, FH, FW, N, IC, OC, sh, sw, ph, pw)
+        else:
+            V2 = OC > 63 and IC > 63 and self._scale_up(IH, IW, OH, OW, FH, FW, sh, sw) >= 1.15
+            if V2:
+                b1 = _tile_count(OC) * _tile_count(N) * OH * OW
+                b2 = _tile_count(IC) * _tile_count(N) * IH * IW
+                b3 = _tile_count(OC) * _tile_count(IC) * FH * FW
+            else:
+                b1 = _tile_count(OC) * _tile_count(N * OH * OW)
+                b2 = _tile_count(IC) * _tile_count(N * IH * IW)
+                b3 = _tile_count(OC) * _tile_count(FH * FW * IC)
+            GridZ = max(2, (b1 + b2) // (b3 << 1))
+            GridZ = min(GridZ, 16, GK >> 8)
+            sizeW = OC * FH * FW * IC
+            buf = torch.empty(max(1, sizeW * (GridZ - 1)), device=X.device, dtype=torch.float32)
+            if FH == 1 and FW == 1:
+                self._call(self.dw, P + "dconv3D_1deltaW_1GemmSK_1W1", "streams", L, GridZ, X, IH, IW, dY, dW, buf, N, IC, OC)
+            elif V2:
+                self._call(self.dw, P + "dconv3D_1deltaW_1GemmV2SK", "streams", L, GridZ, X, IH, IW, dY, OH, OW, dW, buf, FH, FW,
+                           N, IC, OC, sh, sw, ph, pw)
+            else:
+                self._call(self.dw, P + "dconv3D_1deltaW_1GemmSK", "streams", L, GridZ, X, IH, IW, dY, OH, OW, dW, buf, FH, FW,
+                           N, IC, OC, sh, sw, ph, pw)
+            torch.cuda.synchronize()
+            self._call(self.dw, P + "buf_1summary", ("long", self.streams[0].cuda_stream), buf, dW, GridZ - 1, sizeW)
+        torch.cuda.synchronize()
+        return dW
