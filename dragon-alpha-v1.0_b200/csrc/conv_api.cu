@@ -355,7 +355,7 @@ static int env_tile_mode()
 struct HaloChoice {
     bool valid = false;
     int JH = 1, JW = 1, npb = 1, sb = 2, acc_bufs = 1, NI = 1;
-    bool row = false, stat = false;
+    bool row = false, stat = false, wide = false;
     double cost = 0, eff = 0;
 };
 
@@ -400,7 +400,7 @@ static void halo_launch_fw(const HaloLaunch& L, int JH, int JW, bool row)
 #undef HALO_J
 }
 
-static HaloChoice plan_halo(const IgemmPlan& pl, int BN, int mode3x, int b_mn)
+static HaloChoice plan_halo(const IgemmPlan& pl, int BN, int mode3x, int b_mn, int sm_count)
 {
     HaloChoice best;
     const int taps = pl.FH * pl.FW, kchunks = pl.kdim / 32;
@@ -414,14 +414,22 @@ static HaloChoice plan_halo(const IgemmPlan& pl, int BN, int mode3x, int b_mn)
     const int SG = pl.oH + pl.FH - 1;
     int ni_max = 1;
     if (SG <= 16 && env_int("ALPHA_HALO_STACK", 1)) ni_max = 1 + (16 - pl.oH) / SG;
+    // 3xTF32 with BN <= 128: the wide form (hi x [hi | lo] in one MMA of 2*BN columns, then lo x hi) needs
+    // max(BN, 59) + max(BN / 2, 59) clocks per step instead of 3 * max(BN / 2, 59) and reads the A
+    // operand twice instead of three times, at twice the tensor-memory columns per accumulator
+    const int wide_env = env_int("ALPHA_HALO_WIDE", -1);
+    const int wide_lo = (mode3x && BN <= 128 && wide_env != 0) ? (wide_env == 1 ? 1 : 0) : 0;
+    const int wide_hi = (mode3x && BN <= 128 && wide_env != 0) ? 1 : 0;
+    for (int wide = wide_lo; wide <= wide_hi; ++wide)
     for (int NI = 1; NI <= ni_max; NI += (ni_max > 1 ? ni_max - 1 : 1))
     for (int JH = 1; JH <= 2; ++JH)
         for (int JW = 1; JW <= 4; ++JW) {
+            const int accw = wide ? 2 * BN : BN;
             if (NI > 1 && (JH != 1 || JW != 1)) continue;
             if (force_jh && JH != force_jh) continue;
             if (force_jw && JW != force_jw) continue;
             const int J = JH * JW;
-            if (J * BN > 512) continue;
+            if (J * accw > 512) continue;
             const int PH = NI > 1 ? NI * SG : 16 * JH + pl.FH - 1, PW = 8 * JW + pl.FW - 1;
             if (PH > 256 || PW > 256) continue;
             const uint32_t patch_stride = (((uint32_t)PH * PW * 128 + 1023) & ~1023u) * planes;
@@ -436,24 +444,38 @@ static HaloChoice plan_halo(const IgemmPlan& pl, int BN, int mode3x, int b_mn)
             if (need(npb, sb) > smem_cap) { npb = 1; sb = 4; while (need(npb, sb) > smem_cap && sb > 2) --sb; }
             if (need(npb, sb) > smem_cap) continue;
             while (sb < max_sb && need(npb, sb + 1) <= smem_cap && sb < taps) ++sb;
-            const int acc_bufs = (2 * J * BN <= 512) ? 2 : 1;
+            const int acc_bufs = (2 * J * accw <= 512) ? 2 : 1;
             const int rbk = NI > 1 ? 1 : (pl.oH + 16 * JH - 1) / (16 * JH), cbk = (pl.oW + 8 * JW - 1) / (8 * JW);
             const double eff = NI > 1 ? (double)NI * pl.oH * pl.oW / (128.0 * cbk)
                                       : (double)pl.oH * pl.oW / ((double)rbk * 16 * JH * cbk * 8 * JW);
             // cycles per macro tile: one tcgen05.mma of this shape takes max(N/2, 59) clocks
-            const double mma_clk = BN / 2.0 > 59.0 ? BN / 2.0 : 59.0;
-            const double t_mma = (double)taps * kchunks * 4 * (mode3x ? 3 : 1) * J * mma_clk;
+            auto clk = [](double n) { return n / 2.0 > 59.0 ? n / 2.0 : 59.0; };
+            const double step_clk = wide ? clk(2.0 * BN) + clk(BN) : (mode3x ? 3 : 1) * clk(BN);
+            const double t_mma = (double)taps * kchunks * 4 * J * step_clk;
+            // shared-memory traffic per macro tile at 128 B/clk: the operands every MMA reads (4 KB of A,
+            // 32 B per column of B), what the TMA writes, the lo planes the split warps read and write,
+            // and the epilogue's staging.  A tcgen05.mma of 128 columns saturates this by itself.
+            const double step_bytes = wide ? (4096.0 + 64.0 * BN) + (4096.0 + 32.0 * BN)
+                                           : (mode3x ? 3 : 1) * (4096.0 + 32.0 * BN);
+            const double tma_bytes = (double)kchunks * ((double)PH * PW * 128 + (double)taps * b_tx * planes);
+            const double smem_bytes = (double)taps * kchunks * 4 * J * step_bytes + tma_bytes +
+                                      (mode3x ? 2.0 * kchunks * PH * PW * 128 : 0.0) + 2.0 * 128 * J * BN * 4;
+            const double t_smem = smem_bytes / 128.0;
             // W tiles are read by every CTA at about the same time and cost about half of private bytes
             const double bytes = (double)kchunks * ((double)PH * PW * 128 + 0.5 * taps * b_tx * planes) + 128.0 * J * BN * 4;
             const double t_l2 = bytes / 28.0;  // ~28 B/clk/SM between L2 and an SM when all SMs pull
-            double t = (t_mma > t_l2 ? t_mma : t_l2) + 1500.0;  // fixed per-tile overhead
+            double t = t_mma + 1500.0;         // fixed per-tile overhead of the issue loop
+            if (t_smem + 500.0 > t) t = t_smem + 500.0;
+            if (t_l2 > t) t = t_l2;
             if (npb == 1) t *= 1.25;
             if (acc_bufs == 1) t *= 1.15;
             if (!stat) t *= 1.3; else if (!row) t *= 1.05;
-            const double cost = t / (128.0 * J * eff);
+            // whole-launch cost: the busiest persistent CTA walks ceil(tiles / SMs) macro tiles
+            const long long n_macro = (long long)((pl.ncols + BN - 1) / BN) * ((pl.aN + NI - 1) / NI) * rbk * cbk;
+            const double cost = t * (double)((n_macro + sm_count - 1) / sm_count);
             if (!best.valid || cost < best.cost) {
                 best.valid = true; best.JH = JH; best.JW = JW; best.npb = npb; best.sb = sb;
-                best.acc_bufs = acc_bufs; best.cost = cost; best.eff = eff; best.row = row; best.stat = stat; best.NI = NI;
+                best.acc_bufs = acc_bufs; best.cost = cost; best.eff = eff; best.row = row; best.stat = stat; best.NI = NI; best.wide = wide != 0;
             }
         }
     return best;
@@ -468,7 +490,7 @@ static int launch_halo(DeviceCtx* c, const IgemmPlan& pl, int mode3x, cudaStream
     const int gran = pl.b_mn ? 32 : 16;
     int BN = ((pl.ncols + gran - 1) / gran) * gran;
     if (BN > 256) BN = (pl.ncols % 256 == 0 || pl.ncols > 512) ? 256 : 128;
-    HaloChoice ch = plan_halo(pl, BN, mode3x, pl.b_mn);
+    HaloChoice ch = plan_halo(pl, BN, mode3x, pl.b_mn, c->sm_count);
     if (!ch.valid) return 1;
     if (tile_mode == 0 && ch.eff < 0.6 && !pl.force) return 1;
 
@@ -489,9 +511,10 @@ static int launch_halo(DeviceCtx* c, const IgemmPlan& pl, int mode3x, cudaStream
     if (total > 2147483647LL) return 1;
     p.total_tiles = (int)total;
     p.npb = ch.npb; p.sb = ch.sb; p.acc_bufs = ch.acc_bufs;
-    p.mode3x = mode3x; p.b_mn = pl.b_mn; p.flip = pl.flip;
+    p.mode3x = ch.wide ? 2 : mode3x; p.b_mn = pl.b_mn; p.flip = pl.flip;
     p.idesc = make_idesc_tf32(kBM, BN, false, pl.b_mn);
-    p.tmem_cols = pow2_cols(ch.acc_bufs * ch.JH * ch.JW * BN);
+    p.idesc_wide = make_idesc_tf32(kBM, ch.wide ? 2 * BN : BN, false, pl.b_mn);
+    p.tmem_cols = pow2_cols(ch.acc_bufs * ch.JH * ch.JW * BN * (ch.wide ? 2 : 1));
     p.patch_tx = (uint32_t)p.PH * p.PW * 128;
     p.patch_bytes = (p.patch_tx + 1023) & ~1023u;
     p.b_tx = pl.b_mn ? (BN / 32) * 4096 : BN * 128;
@@ -556,8 +579,8 @@ static int launch_halo(DeviceCtx* c, const IgemmPlan& pl, int mode3x, cudaStream
     else if (pl.FW == 3) halo_launch_fw<3>(L, ch.JH, ch.JW, ch.row);
     else halo_launch_fw<5>(L, ch.JH, ch.JW, ch.row);
     note_launch(ch.row ? "halo_row" : (ch.stat ? "halo_tap" : "halo"));
-    snprintf(g_plan, sizeof(g_plan), "halo%s JH=%d JW=%d NI=%d BN=%d npb=%d sb=%d acc=%d eff=%.2f", ch.row ? "_row" : (ch.stat ? "_tap" : ""), ch.JH,
-             ch.JW, ch.NI, BN, ch.npb, ch.sb, ch.acc_bufs, ch.eff);
+    snprintf(g_plan, sizeof(g_plan), "halo%s%s JH=%d JW=%d NI=%d BN=%d npb=%d sb=%d acc=%d eff=%.2f", ch.row ? "_row" : (ch.stat ? "_tap" : ""),
+             ch.wide ? " wide" : "", ch.JH, ch.JW, ch.NI, BN, ch.npb, ch.sb, ch.acc_bufs, ch.eff);
     rc = check_launch("conv_halo_kernel");
     return rc;
 }
@@ -644,11 +667,30 @@ static int launch_dw_halo(DeviceCtx* c, const AlphaConvShape* s, const float* X,
     for (int cand = 256; cand >= 32; cand >>= 1)
         if (s->IC % cand == 0 && s->FW * cand <= 512) { NT = cand; break; }
     if (!NT) return 1;
+    // 3xTF32: three MMAs of (128 x NT), or one MMA on stacked hi/lo planes (64 + 64) x (NTq + NTq).
+    // An MMA of N columns costs max(N / 2, 59) clocks whatever its height, so the stacked form wins
+    // where 128 output channels or 64 input channels would be half empty.
+    bool stacked = false;
+    if (mode3x) {
+        int NTq = 0;
+        for (int cand = 128; cand >= 32; cand >>= 1)
+            if (s->IC % cand == 0 && s->FW * 2 * cand <= 512) { NTq = cand; break; }
+        if (NTq) {
+            auto mma_clk = [](int n) { return n / 2 > 59 ? n / 2 : 59; };
+            const long long std_cost = 3LL * mma_clk(NT) * ((s->OC + 127) / 128) * (s->IC / NT);
+            const long long stk_cost = 1LL * mma_clk(2 * NTq) * ((s->OC + 63) / 64) * (s->IC / NTq);
+            stacked = stk_cost < std_cost;
+            const int force = env_int("ALPHA_DW_STACKED", -1);
+            if (force >= 0) stacked = force != 0;
+            if (stacked) NT = NTq;
+        }
+    }
+    const int oc_tile = stacked ? 64 : 128, dyb = stacked ? 2 : 4, nsub = stacked ? 2 : 1;
     DwHaloParams p{};
-    p.status = c->status;
+    p.status = c->status; p.prof = c->prof;
     p.N = s->N; p.OH = s->OH; p.OW = s->OW;
     p.IC = s->IC; p.OC = s->OC; p.FH = s->FH; p.FW = s->FW; p.ph = s->ph; p.pw = s->pw;
-    p.NT = NT; p.ic_tiles = s->IC / NT; p.oc_tiles = (s->OC + 127) / 128;
+    p.NT = NT; p.ic_tiles = s->IC / NT; p.oc_tiles = (s->OC + oc_tile - 1) / oc_tile;
     const int groups = s->FH * p.ic_tiles * p.oc_tiles;
     if (groups > 65535) return 1;
     // pixel tile: CW columns of 8-pixel groups, R rows, sized so that three stages fit shared memory
@@ -658,8 +700,8 @@ static int launch_dw_halo(DeviceCtx* c, const AlphaConvShape* s, const float* X,
     const int PW = CW + s->FW - 1;
     int R = env_int("ALPHA_DW_R", 0);
     auto stage_bytes = [&](int r) {
-        const uint32_t dyb = ((uint32_t)r * CW * 128 + 1023) & ~1023u, xbk = ((uint32_t)r * PW * 128 + 1023) & ~1023u;
-        return (size_t)planes * (4 * dyb + (NT / 32) * xbk);
+        const uint32_t dyblk = ((uint32_t)r * CW * 128 + 1023) & ~1023u, xbk = ((uint32_t)r * PW * 128 + 1023) & ~1023u;
+        return (size_t)planes * (dyb * dyblk + (NT / 32) * xbk);
     };
     if (!R) {
         R = 8;
@@ -678,15 +720,15 @@ static int launch_dw_halo(DeviceCtx* c, const AlphaConvShape* s, const float* X,
     if (parts < 1) parts = 1;
     if (parts > p.total_tiles) parts = p.total_tiles;
     p.parts = parts;
-    p.stages = stages; p.mode3x = mode3x;
-    p.idesc = make_idesc_tf32(kBM, NT, true, true);
-    p.tmem_cols = pow2_cols(s->FW * NT);
+    p.stages = stages; p.mode3x = stacked ? 2 : mode3x;
+    p.idesc = make_idesc_tf32(kBM, stacked ? 2 * NT : NT, true, true);
+    p.tmem_cols = pow2_cols(s->FW * (stacked ? 2 * NT : NT));
     p.dy_tx = (uint32_t)R * CW * 128; p.dy_blk = (p.dy_tx + 1023) & ~1023u;
     p.x_tx = (uint32_t)R * PW * 128; p.x_blk = (p.x_tx + 1023) & ~1023u;
     const size_t sizeW = (size_t)s->OC * s->FH * s->FW * s->IC;
     float* ws = nullptr;
-    if (parts > 1) {
-        int rc = get_workspace(c, stream, sizeW * parts * sizeof(float), &ws);
+    if (parts * nsub > 1) {
+        int rc = get_workspace(c, stream, sizeW * parts * nsub * sizeof(float), &ws);
         if (rc) return rc;
         p.out = ws;
     } else {
@@ -726,12 +768,13 @@ static int launch_dw_halo(DeviceCtx* c, const AlphaConvShape* s, const float* X,
     else DWH_LAUNCH(0, 0, 0);
 #undef DWH_LAUNCH
     note_launch("dw_halo");
-    snprintf(g_plan, sizeof(g_plan), "dw_halo NT=%d R=%d CW=%d stages=%d parts=%d groups=%d", NT, R, CW, stages, parts, groups);
+    snprintf(g_plan, sizeof(g_plan), "dw_halo%s NT=%d R=%d CW=%d stages=%d parts=%d groups=%d", stacked ? " stacked" : "", NT, R, CW,
+             stages, parts, groups);
     rc = check_launch("conv_dw_halo_kernel");
     if (rc) return rc;
-    if (parts > 1) {
+    if (parts * nsub > 1) {
         const size_t n4 = sizeW / 4;
-        dw_reduce_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, stream>>>(ws, sizeW, parts, dW, n4, 0);
+        dw_reduce_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, stream>>>(ws, sizeW, parts * nsub, dW, n4, 0);
         note_launch("dw_halo");
         rc = check_launch("dw_reduce_kernel");
     }

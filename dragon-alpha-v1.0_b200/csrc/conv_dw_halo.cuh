@@ -13,9 +13,16 @@
 // accumulates over all its pixel tiles in tensor memory and writes one partial per CTA at the end;
 // dw_reduce_kernel sums the partials in a fixed order.
 //
+// 3xTF32 has two forms.  mode3x == 1: three MMAs per step (lo*hi, hi*lo, hi*hi) into one
+// accumulator.  mode3x == 2 ("stacked"), for blocks of at most 64 output and 64 input channels,
+// where an MMA costs the same as one twice as tall and twice as wide: the lo plane of deltaY is
+// stacked under its hi plane (M = 64 + 64) and the lo plane of X beside its hi plane (N = NT + NT),
+// so that ONE MMA forms all four products; the epilogue writes the hi rows (hi*hi + hi*lo) and the
+// lo rows (lo*hi + lo*lo) as two partials and the reduction adds them.
+//
 // Warps: 0 TMA producer, 1 MMA issuer, 2-5 operand split (3xTF32) during the loop, epilogue after.
 #pragma once
-#include "conv_kernels.cuh"
+#include "conv_halo.cuh"
 
 namespace alpha {
 
@@ -25,6 +32,8 @@ struct DwHaloParams {
     float* out;            // partials [parts][OC][FH*FW][IC] (or deltaW itself when parts == 1)
     size_t part_stride;    // floats between two partials
     int* status;
+    unsigned long long* prof;  // optional cycle counters of CTA (0,0): slots 0 producer wait, 2 MMA wait,
+                               // 5 MMA total, 8 split wait, 9 split work, 10 kernel total
     int N, OH, OW;         // deltaY geometry
     int IC, OC, FH, FW, ph, pw;
     int NT;                // input channels per CTA (multiple of 32, <= 256)
@@ -34,7 +43,7 @@ struct DwHaloParams {
     int row_blocks, col_blocks, tiles_per_img;
     int total_tiles;       // N * tiles_per_img
     int parts;             // CTAs per accumulator group = gridDim.x
-    int stages, mode3x;
+    int stages, mode3x;    // mode3x: 0 plain TF32, 1 three MMAs, 2 stacked planes
     uint32_t idesc, tmem_cols;
     uint32_t dy_blk, x_blk;   // bytes of one 32-channel block of the deltaY / X tile (multiples of 1024)
     uint32_t dy_tx, x_tx;     // bytes one block load delivers
@@ -54,10 +63,16 @@ __global__ void __launch_bounds__(kDwHaloThreads, 1)
     const int S = p.stages;
     const uint32_t planes = p.mode3x ? 2u : 1u;
     const int xb = p.NT / 32;                       // X blocks per stage
-    const uint32_t dy_bytes = 4 * p.dy_blk;         // 128 output channels
+    const bool stacked = p.mode3x == 2;
+    const int dyb = stacked ? 2 : 4;                // deltaY blocks per plane: 64 or 128 output channels
+    const uint32_t dy_bytes = dyb * p.dy_blk;
     const uint32_t x_bytes = xb * p.x_blk;
-    const uint32_t plane_bytes = dy_bytes + x_bytes;  // hi plane; the lo plane follows
+    const uint32_t plane_bytes = dy_bytes + x_bytes;
     const uint32_t stage_bytes = plane_bytes * planes;
+    // stage layout.  modes 0/1: [dY hi][X hi] [dY lo][X lo];  mode 2: [dY hi][dY lo] [X hi][X lo]
+    const uint32_t x_off = stacked ? 2 * dy_bytes : dy_bytes;
+    const int oc_tile = stacked ? 64 : 128;
+    const uint32_t acc_cols = stacked ? 2 * p.NT : p.NT;
 
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + static_cast<size_t>(S) * stage_bytes);
     uint64_t* full = bars;
@@ -91,7 +106,7 @@ __global__ void __launch_bounds__(kDwHaloThreads, 1)
     const int fh = grp % p.FH;
     const int ict = (grp / p.FH) % p.ic_tiles;
     const int oct = grp / (p.FH * p.ic_tiles);
-    const int ic0 = ict * p.NT, oc0 = oct * 128;
+    const int ic0 = ict * p.NT, oc0 = oct * oc_tile;
 
     const uint32_t smem_a = smem_u32(smem);
     const uint32_t full_a = smem_u32(full), ready_a = smem_u32(ready), empty_a = smem_u32(empty);
@@ -99,26 +114,30 @@ __global__ void __launch_bounds__(kDwHaloThreads, 1)
     const int R = kStatic ? R_T : p.R;
     const int CW = kStatic ? CW_T : p.CW;
     const int PW = CW + FW - 1;
+    const bool prof_on = p.prof != nullptr && blockIdx.x == 0 && blockIdx.y == 0;
+    const long long t_kernel = clock64();
 
     if (warp == 0) {
         if (lane == 0) {
             // ---- TMA producer ----
             RingPos rp;
+            unsigned long long w_empty = 0;
             for (int t = blockIdx.x; t < p.total_tiles; t += gridDim.x) {
                 const int n = t / p.tiles_per_img;
                 const int r = t - n * p.tiles_per_img;
                 const int rb = r / p.col_blocks, cb = r - rb * p.col_blocks;
-                if (!mbar_wait_a(empty_a + 8 * rp.idx, rp.phase ^ 1)) { report(p.status, kStatusProducerTimeout); break; }
+                if (!wait_prof(empty_a + 8 * rp.idx, rp.phase ^ 1, prof_on, w_empty)) { report(p.status, kStatusProducerTimeout); break; }
                 const uint32_t bar = full_a + 8 * rp.idx;
                 const uint32_t dst = smem_a + rp.idx * stage_bytes;
-                mbar_arrive_expect_tx_a(bar, 4 * p.dy_tx + xb * p.x_tx);
+                mbar_arrive_expect_tx_a(bar, dyb * p.dy_tx + xb * p.x_tx);
                 const int oh0 = rb * R, ow0 = cb * CW;
-                for (int b = 0; b < 4; ++b)
+                for (int b = 0; b < dyb; ++b)
                     tma_load_4d_a(dst + b * p.dy_blk, &tmDY, bar, oc0 + b * 32, ow0, oh0, n);
                 for (int b = 0; b < xb; ++b)
-                    tma_load_4d_a(dst + dy_bytes + b * p.x_blk, &tmX, bar, ic0 + b * 32, ow0 - p.pw, oh0 + fh - p.ph, n);
+                    tma_load_4d_a(dst + x_off + b * p.x_blk, &tmX, bar, ic0 + b * 32, ow0 - p.pw, oh0 + fh - p.ph, n);
                 rp.advance(S);
             }
+            if (prof_on) p.prof[kProfProducerPatchWait] = w_empty;
         }
         __syncwarp();
     } else if (warp == 1) {
@@ -127,12 +146,15 @@ __global__ void __launch_bounds__(kDwHaloThreads, 1)
             RingPos rp;
             const uint32_t dhi = smem_desc_hi(512, kSwizzle128B_Base32B);
             const uint32_t wait_a = p.mode3x ? ready_a : full_a;
+            const bool three = p.mode3x == 1;
             const uint32_t stage16 = stage_bytes >> 4, lo_off = plane_bytes >> 4;
             const uint32_t a_lo0 = smem_desc_lo(smem_a, p.dy_blk);              // LBO = block stride
-            const uint32_t b_lo0 = smem_desc_lo(smem_a + dy_bytes, p.x_blk);
+            const uint32_t b_lo0 = smem_desc_lo(smem_a + x_off, p.x_blk);
             uint32_t acc = 0u;  // the first MMA into each accumulator overwrites it
+            unsigned long long w_in = 0;
+            const long long t_begin = clock64();
             for (int t = blockIdx.x; t < p.total_tiles; t += gridDim.x) {
-                if (!mbar_wait_a(wait_a + 8 * rp.idx, rp.phase)) { report(p.status, kStatusMmaTimeout); break; }
+                if (!wait_prof(wait_a + 8 * rp.idx, rp.phase, prof_on, w_in)) { report(p.status, kStatusMmaTimeout); break; }
                 tc_fence_after_sync();
                 const uint32_t a_s = a_lo0 + rp.idx * stage16, b_s = b_lo0 + rp.idx * stage16;
                 if constexpr (kStatic) {
@@ -146,8 +168,8 @@ __global__ void __launch_bounds__(kDwHaloThreads, 1)
 #pragma unroll
                             for (int fw = 0; fw < FW_T; ++fw) {
                                 const uint32_t b_k = b_s + (r * kPW + g * 8 + fw) * 8;
-                                const uint32_t d = tmem_base + fw * p.NT;
-                                if (p.mode3x) {
+                                const uint32_t d = tmem_base + fw * acc_cols;
+                                if (three) {
                                     mma_tf32_ss2(d, a_k + lo_off, dhi, b_k, dhi, p.idesc, first);
                                     mma_tf32_ss2(d, a_k, dhi, b_k + lo_off, dhi, p.idesc, 1u);
                                     mma_tf32_ss2(d, a_k, dhi, b_k, dhi, p.idesc, 1u);
@@ -163,8 +185,8 @@ __global__ void __launch_bounds__(kDwHaloThreads, 1)
                         uint32_t a_k = a_row, b_g = b_row;
                         for (int g = 0; g < CW / 8; ++g, a_k += 64, b_g += 64) {
                             uint32_t b_k = b_g, d = tmem_base;
-                            for (int fw = 0; fw < FW; ++fw, b_k += 8, d += p.NT) {
-                                if (p.mode3x) {
+                            for (int fw = 0; fw < FW; ++fw, b_k += 8, d += acc_cols) {
+                                if (three) {
                                     mma_tf32_ss2(d, a_k + lo_off, dhi, b_k, dhi, p.idesc, first);
                                     mma_tf32_ss2(d, a_k, dhi, b_k + lo_off, dhi, p.idesc, 1u);
                                     mma_tf32_ss2(d, a_k, dhi, b_k, dhi, p.idesc, 1u);
@@ -181,6 +203,10 @@ __global__ void __launch_bounds__(kDwHaloThreads, 1)
                 rp.advance(S);
             }
             mma_commit(accum);
+            if (prof_on) {
+                p.prof[kProfMmaPatchWait] = w_in;
+                p.prof[kProfMmaTotal] = static_cast<unsigned long long>(clock64() - t_begin);
+            }
         }
         __syncwarp();
     } else {
@@ -189,29 +215,51 @@ __global__ void __launch_bounds__(kDwHaloThreads, 1)
         bool ok = true;
         if (p.mode3x) {
             RingPos rp;
+            unsigned long long w_full = 0;
+            const long long t_begin = clock64();
             for (int t = blockIdx.x; t < p.total_tiles; t += gridDim.x) {
-                if (!mbar_wait_a(full_a + 8 * rp.idx, rp.phase)) { report(p.status, kStatusSplitTimeout); ok = false; break; }
+                if (!wait_prof(full_a + 8 * rp.idx, rp.phase, prof_on, w_full)) { report(p.status, kStatusSplitTimeout); ok = false; break; }
                 uint8_t* hi = smem + static_cast<size_t>(rp.idx) * stage_bytes;
-                split_plane_x4(hi, hi + plane_bytes, plane_bytes, tid128, 128);
+                if (stacked) {
+                    split_plane_lo_x4(hi, hi + dy_bytes, dy_bytes, tid128, 128);
+                    split_plane_lo_x4(hi + x_off, hi + x_off + x_bytes, x_bytes, tid128, 128);
+                } else {
+                    split_plane_lo_x4(hi, hi + plane_bytes, plane_bytes, tid128, 128);
+                }
                 fence_proxy_async_smem();
                 mbar_arrive_a(ready_a + 8 * rp.idx);
                 rp.advance(S);
+            }
+            if (prof_on && tid128 == 0) {
+                p.prof[kProfSplitWait] = w_full;
+                p.prof[kProfSplitWork] = static_cast<unsigned long long>(clock64() - t_begin) - w_full;
             }
         }
         if (ok && !mbar_wait(accum, 0)) { report(p.status, kStatusEpilogueTimeout); ok = false; }
         tc_fence_after_sync();
         if (ok) {
             const int quad = warp & 3;
-            const int oc = oc0 + quad * 32 + lane;
+            // stacked: tensor-memory lanes 0-63 are the hi rows, 64-127 the lo rows of the same channels
+            const int oc = oc0 + (stacked ? (quad & 1) * 32 : quad * 32) + lane;
+            const int sub = stacked ? (quad >> 1) : 0;
+            const int nsub = stacked ? 2 : 1;
             const int taps = p.FH * p.FW;
             const bool has_tiles = static_cast<int>(blockIdx.x) < p.total_tiles;
-            float* obase = p.out + static_cast<size_t>(blockIdx.x) * p.part_stride;
+            float* obase = p.out + (static_cast<size_t>(blockIdx.x) * nsub + sub) * p.part_stride;
             for (int fw = 0; fw < FW; ++fw) {
                 const int tap = fh * p.FW + fw;
                 for (int c = 0; c < p.NT; c += 32) {
                     uint32_t v[32];
-                    tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + fw * p.NT + c, v);
+                    const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + fw * acc_cols + c;
+                    tmem_ld_32x32(taddr, v);
                     tmem_ld_wait();
+                    if (stacked) {
+                        uint32_t w[32];
+                        tmem_ld_32x32(taddr + p.NT, w);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int q = 0; q < 32; ++q) v[q] = __float_as_uint(__uint_as_float(v[q]) + __uint_as_float(w[q]));
+                    }
                     if (oc < p.OC) {
                         float* dst = obase + (static_cast<size_t>(oc) * taps + tap) * p.IC + ic0 + c;
 #pragma unroll
@@ -228,6 +276,7 @@ __global__ void __launch_bounds__(kDwHaloThreads, 1)
     }
     tc_fence_before_sync();
     __syncthreads();
+    if (prof_on && threadIdx.x == 0) p.prof[kProfTotal] = static_cast<unsigned long long>(clock64() - t_kernel);
     if (warp == 1) tmem_dealloc(tmem_base, p.tmem_cols);
 }
 

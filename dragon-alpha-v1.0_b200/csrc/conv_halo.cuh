@@ -8,7 +8,12 @@
 // patch: tcgen05 applies the 128-byte swizzle to absolute shared-memory addresses, so a descriptor
 // may start at any 128-byte row of a TMA-written tile, and the stride between groups of 8 rows
 // (SBO) is simply the patch pitch.  B tiles (one filter tap x 32 channels x BN) stream through a
-// ring.  In 3xTF32 mode four warps rewrite each landed patch and B tile as hi/lo planes once.
+// ring.  In 3xTF32 mode four warps rewrite each landed patch as hi/lo planes once; the weights
+// arrive pre-split.  3xTF32 has two forms: mode3x == 1 issues lo*hi, hi*lo and hi*hi as three MMAs
+// of BN columns into one accumulator; mode3x == 2 ("wide", for BN <= 64, where an MMA of 64 columns
+// costs almost as much as one of 128) issues hi x [hi | lo] as ONE MMA of 2*BN columns - the lo
+// plane of a B tile directly follows its hi plane in shared memory - plus lo x hi, and the epilogue
+// adds the two column halves of the accumulator.
 // Accumulators are double-buffered in tensor memory when they fit, so the epilogue of one macro
 // tile overlaps the loads and MMAs of the next.
 //
@@ -49,8 +54,8 @@ struct HaloParams {
     int total_tiles;     // n_tiles * n_blocks * row_blocks * col_blocks
     int npb, sb;         // patch buffers, B ring stages
     int acc_bufs;        // 1 or 2 accumulator sets
-    int mode3x, b_mn, flip;
-    uint32_t idesc, tmem_cols;
+    int mode3x, b_mn, flip;   // mode3x: 0 plain TF32, 1 three MMAs, 2 wide B
+    uint32_t idesc, idesc_wide, tmem_cols;   // idesc_wide: N = 2 * BN
     uint32_t patch_bytes;  // one plane of one patch buffer, multiple of 1024
     uint32_t patch_tx;     // bytes one patch load delivers
     uint32_t b_bytes;      // one plane of one B stage, multiple of 1024
@@ -68,24 +73,55 @@ __device__ __forceinline__ bool wait_prof(uint32_t bar, uint32_t parity, bool pr
     return ok;
 }
 
-// The four K=8 steps of one 32-channel chunk into one accumulator (12 MMAs in 3xTF32 mode).
-template <bool k3x>
+// The four K=8 steps of one 32-channel chunk into one accumulator.  MODE 0: 4 MMAs; 1: 12 MMAs
+// (three per step); 2: 8 MMAs (hi x [hi | lo] over 2*BN columns, then lo x hi over BN columns).
+template <int MODE>
 __device__ __forceinline__ void issue_chunk(uint32_t d, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
                                             uint32_t b_kstep, uint32_t a_lo_off, uint32_t b_lo_off, uint32_t idesc,
-                                            uint32_t acc_first)
+                                            uint32_t idesc_wide, uint32_t acc_first)
 {
 #pragma unroll
     for (int kk = 0; kk < 4; ++kk) {
         const uint32_t a_k = a_lo + kk * 2, b_k = b_lo + kk * b_kstep;
         const uint32_t acc = kk == 0 ? acc_first : 1u;
-        if (k3x) {
+        if (MODE == 1) {
             mma_tf32_ss2(d, a_k + a_lo_off, a_hi, b_k, b_hi, idesc, acc);
             mma_tf32_ss2(d, a_k, a_hi, b_k + b_lo_off, b_hi, idesc, 1u);
             mma_tf32_ss2(d, a_k, a_hi, b_k, b_hi, idesc, 1u);
+        } else if (MODE == 2) {
+            mma_tf32_ss2(d, a_k, a_hi, b_k, b_hi, idesc_wide, acc);
+            mma_tf32_ss2(d, a_k + a_lo_off, a_hi, b_k, b_hi, idesc, 1u);
         } else {
             mma_tf32_ss2(d, a_k, a_hi, b_k, b_hi, idesc, acc);
         }
     }
+}
+
+// Descriptor constants of the issue loop.
+struct IssueConsts {
+    uint32_t a_dhi, b_dhi, b_kstep, a_lo_off, b_lo_off, idesc, idesc_wide, accw;
+};
+
+// One filter tap into the JH_T x JW_T accumulators of a macro tile, straight-line.
+template <int MODE, int JH_T, int JW_T, uint32_t kPW8>
+__device__ __forceinline__ void issue_tap(uint32_t d0, uint32_t a_tap, uint32_t bl, const IssueConsts& k, uint32_t acc_first)
+{
+#pragma unroll
+    for (int jh = 0; jh < JH_T; ++jh)
+#pragma unroll
+        for (int jw = 0; jw < JW_T; ++jw)
+            issue_chunk<MODE>(d0 + (jh * JW_T + jw) * k.accw, a_tap + jh * 16 * kPW8 + jw * 64, k.a_dhi, bl, k.b_dhi, k.b_kstep,
+                              k.a_lo_off, k.b_lo_off, k.idesc, k.idesc_wide, acc_first);
+}
+
+// The FW_T taps of one filter row (B stage holds them back to back, b_tile16 apart).
+template <int MODE, int FW_T, int JH_T, int JW_T, uint32_t kPW8>
+__device__ __forceinline__ void issue_row(uint32_t d0, uint32_t a_row, uint32_t bl, uint32_t b_tile16, const IssueConsts& k,
+                                          uint32_t acc_first)
+{
+#pragma unroll
+    for (int fw = 0; fw < FW_T; ++fw)
+        issue_tap<MODE, JH_T, JW_T, kPW8>(d0, a_row + fw * 8, bl + fw * b_tile16, k, fw == 0 ? acc_first : 1u);
 }
 
 // FW_T > 0 selects a specialisation with compile-time FW, JH and JW whose MMAs are issued as
@@ -228,7 +264,9 @@ __global__ void __launch_bounds__(kHaloThreads, 1)
             const uint32_t patch_lo0 = smem_desc_lo(patches_a, 16), patch_stride16 = patch_stride >> 4;
             const uint32_t bring_lo0 = smem_desc_lo(bring_a, p.b_mn ? 4096u : 16u), b_stride16 = b_stride >> 4;
             const uint32_t pwait_a = p.mode3x ? pready_a : pfull_a, bwait_a = bfull_a;  // weights arrive pre-split
-            const uint32_t acc_cols = J * p.BN;
+            const uint32_t accw = p.mode3x == 2 ? 2u * p.BN : p.BN;   // columns of one accumulator
+            const uint32_t acc_cols = J * accw;
+            const IssueConsts k{a_dhi, b_dhi, b_kstep, a_lo_off, b_lo_off, p.idesc, p.idesc_wide, accw};
             for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
                 if (!wait_prof(aempty_a + 8 * ap.idx, ap.phase ^ 1, prof_on, w_acc)) { report(p.status, kStatusMmaTimeout); ok = false; break; }
                 tc_fence_after_sync();
@@ -245,27 +283,9 @@ __global__ void __launch_bounds__(kHaloThreads, 1)
                             if (!wait_prof(bwait_a + 8 * bp.idx, bp.phase, prof_on, w_b)) { report(p.status, kStatusMmaTimeout); ok = false; break; }
                             tc_fence_after_sync();
                             const uint32_t bl = bring_lo0 + bp.idx * b_stride16;
-                            if (p.mode3x) {
-#pragma unroll
-                                for (int fw = 0; fw < FW_T; ++fw)
-#pragma unroll
-                                    for (int jh = 0; jh < JH_T; ++jh)
-#pragma unroll
-                                        for (int jw = 0; jw < JW_T; ++jw)
-                                            issue_chunk<true>(d0 + (jh * JW_T + jw) * p.BN, a_row + fw * 8 + jh * 16 * kPW8 + jw * 64,
-                                                              a_dhi, bl + fw * b_tile16, b_dhi, b_kstep, a_lo_off, b_lo_off, p.idesc,
-                                                              fw == 0 ? acc_first : 1u);
-                            } else {
-#pragma unroll
-                                for (int fw = 0; fw < FW_T; ++fw)
-#pragma unroll
-                                    for (int jh = 0; jh < JH_T; ++jh)
-#pragma unroll
-                                        for (int jw = 0; jw < JW_T; ++jw)
-                                            issue_chunk<false>(d0 + (jh * JW_T + jw) * p.BN, a_row + fw * 8 + jh * 16 * kPW8 + jw * 64,
-                                                               a_dhi, bl + fw * b_tile16, b_dhi, b_kstep, a_lo_off, b_lo_off, p.idesc,
-                                                               fw == 0 ? acc_first : 1u);
-                            }
+                            if (p.mode3x == 1) issue_row<1, FW_T, JH_T, JW_T, kPW8>(d0, a_row, bl, b_tile16, k, acc_first);
+                            else if (p.mode3x == 2) issue_row<2, FW_T, JH_T, JW_T, kPW8>(d0, a_row, bl, b_tile16, k, acc_first);
+                            else issue_row<0, FW_T, JH_T, JW_T, kPW8>(d0, a_row, bl, b_tile16, k, acc_first);
                             acc_first = 1u;
                             mma_commit_a(bempty_a + 8 * bp.idx);
                             bp.advance(p.sb);
@@ -278,21 +298,9 @@ __global__ void __launch_bounds__(kHaloThreads, 1)
                                 if (!wait_prof(bwait_a + 8 * bp.idx, bp.phase, prof_on, w_b)) { report(p.status, kStatusMmaTimeout); ok = false; break; }
                                 tc_fence_after_sync();
                                 const uint32_t bl = bring_lo0 + bp.idx * b_stride16;
-                                if (p.mode3x) {
-#pragma unroll
-                                    for (int jh = 0; jh < JH_T; ++jh)
-#pragma unroll
-                                        for (int jw = 0; jw < JW_T; ++jw)
-                                            issue_chunk<true>(d0 + (jh * JW_T + jw) * p.BN, a_row + fw * 8 + jh * 16 * kPW8 + jw * 64,
-                                                              a_dhi, bl, b_dhi, b_kstep, a_lo_off, b_lo_off, p.idesc, acc_first);
-                                } else {
-#pragma unroll
-                                    for (int jh = 0; jh < JH_T; ++jh)
-#pragma unroll
-                                        for (int jw = 0; jw < JW_T; ++jw)
-                                            issue_chunk<false>(d0 + (jh * JW_T + jw) * p.BN, a_row + fw * 8 + jh * 16 * kPW8 + jw * 64,
-                                                               a_dhi, bl, b_dhi, b_kstep, a_lo_off, b_lo_off, p.idesc, acc_first);
-                                }
+                                if (p.mode3x == 1) issue_tap<1, JH_T, JW_T, kPW8>(d0, a_row + fw * 8, bl, k, acc_first);
+                                else if (p.mode3x == 2) issue_tap<2, JH_T, JW_T, kPW8>(d0, a_row + fw * 8, bl, k, acc_first);
+                                else issue_tap<0, JH_T, JW_T, kPW8>(d0, a_row + fw * 8, bl, k, acc_first);
                                 acc_first = 1u;
                                 mma_commit_a(bempty_a + 8 * bp.idx);
                                 bp.advance(p.sb);
@@ -308,9 +316,10 @@ __global__ void __launch_bounds__(kHaloThreads, 1)
                             uint32_t d = d0, a_jh = a_tap;
                             for (int jh = 0; jh < p.JH; ++jh, a_jh += jh_step) {
                                 uint32_t a_j = a_jh;
-                                for (int jw = 0; jw < p.JW; ++jw, a_j += 64, d += p.BN) {
-                                    if (p.mode3x) issue_chunk<true>(d, a_j, a_dhi, bl, b_dhi, b_kstep, a_lo_off, b_lo_off, p.idesc, acc_first);
-                                    else issue_chunk<false>(d, a_j, a_dhi, bl, b_dhi, b_kstep, a_lo_off, b_lo_off, p.idesc, acc_first);
+                                for (int jw = 0; jw < p.JW; ++jw, a_j += 64, d += accw) {
+                                    if (p.mode3x == 1) issue_chunk<1>(d, a_j, a_dhi, bl, b_dhi, b_kstep, a_lo_off, b_lo_off, p.idesc, p.idesc_wide, acc_first);
+                                    else if (p.mode3x == 2) issue_chunk<2>(d, a_j, a_dhi, bl, b_dhi, b_kstep, a_lo_off, b_lo_off, p.idesc, p.idesc_wide, acc_first);
+                                    else issue_chunk<0>(d, a_j, a_dhi, bl, b_dhi, b_kstep, a_lo_off, b_lo_off, p.idesc, p.idesc_wide, acc_first);
                                 }
                             }
                             acc_first = 1u;
@@ -341,6 +350,8 @@ __global__ void __launch_bounds__(kHaloThreads, 1)
         const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
         const uint32_t stage_a = smem_u32(staging);
         uint32_t sbuf = 0;
+        const bool wide = p.mode3x == 2;
+        const uint32_t accw = wide ? 2u * p.BN : p.BN;
         for (int t = blockIdx.x; t < p.total_tiles; t += gridDim.x) {
             if (!wait_prof(afull_a + 8 * ap.idx, ap.phase, prof_on, w_acc)) { report(p.status, kStatusEpilogueTimeout); break; }
             tc_fence_after_sync();
@@ -356,7 +367,7 @@ __global__ void __launch_bounds__(kHaloThreads, 1)
                 for (int jw = 0; jw < p.JW; ++jw, ++j) {
                     const int oh0 = (rb * p.JH + jh) * 16, ow0 = (cb * p.JW + jw) * 8;
                     if (oh0 >= p.OH || ow0 >= p.OW) continue;  // accumulator entirely outside the image
-                    const uint32_t tcol = lane_base + (ap.idx * J + j) * p.BN;
+                    const uint32_t tcol = lane_base + (ap.idx * J + j) * accw;
                     for (int c = 0; c < p.BN; c += 32) {
                         const int col0 = n0 + c;
                         if (col0 >= p.Ncols) break;
@@ -366,6 +377,13 @@ __global__ void __launch_bounds__(kHaloThreads, 1)
                         uint32_t v[32];
                         tmem_ld_32x32(tcol + c, v);
                         tmem_ld_wait();
+                        if (wide) {
+                            uint32_t w[32];
+                            tmem_ld_32x32(tcol + p.BN + c, w);
+                            tmem_ld_wait();
+#pragma unroll
+                            for (int q = 0; q < 32; ++q) v[q] = __float_as_uint(__uint_as_float(v[q]) + __uint_as_float(w[q]));
+                        }
                         const uint32_t srow = stage_a + sbuf * 16384 + row * 128;
 #pragma unroll
                         for (int q = 0; q < 8; ++q) {
@@ -415,7 +433,7 @@ __global__ void __launch_bounds__(kHaloThreads, 1)
                 for (int c = 0; c < p.kchunks && ok; ++c) {
                     if (!wait_prof(pfull_a + 8 * pp.idx, pp.phase, prof_on, w_in)) { report(p.status, kStatusSplitTimeout); ok = false; break; }
                     uint8_t* ph = patches + static_cast<size_t>(pp.idx) * patch_stride;
-                    split_plane_x4(ph, ph + p.patch_bytes, p.patch_tx, tid128, 128);
+                    split_plane_lo_x4(ph, ph + p.patch_bytes, p.patch_tx, tid128, 128);
                     fence_proxy_async_smem();
                     mbar_arrive_a(pready_a + 8 * pp.idx);
                     pp.advance(p.npb);

@@ -116,6 +116,35 @@ __device__ __forceinline__ void split_plane_x4(uint8_t* hi_plane, uint8_t* lo_pl
     }
 }
 
+// tcgen05.mma kind::tf32 reads only the upper 19 bits of each fp32 operand word, so a staged fp32
+// plane already acts as hi = x with the low 13 mantissa bits cleared, and only lo = tf32(x - hi)
+// has to be written: one shared-memory store per vector instead of two.
+__device__ __forceinline__ float tf32_lo_of_trunc(float x)
+{
+    const float hi = __uint_as_float(__float_as_uint(x) & 0xffffe000u);
+    return __uint_as_float(to_tf32_rna(x - hi));
+}
+
+__device__ __forceinline__ float4 tf32_lo_of_trunc(const float4& x)
+{
+    return make_float4(tf32_lo_of_trunc(x.x), tf32_lo_of_trunc(x.y), tf32_lo_of_trunc(x.z), tf32_lo_of_trunc(x.w));
+}
+
+// Fills the lo plane of a staged plane that stays as it is; four vectors per thread in flight.
+__device__ __forceinline__ void split_plane_lo_x4(const uint8_t* plane, uint8_t* lo_plane, uint32_t bytes, int tid, int nthreads)
+{
+    const float4* h = reinterpret_cast<const float4*>(plane);
+    float4* l = reinterpret_cast<float4*>(lo_plane);
+    const uint32_t nvec = bytes >> 4, n = nthreads;
+    uint32_t v = tid;
+    for (; v + 3 * n < nvec; v += 4 * n) {
+        const float4 a0 = h[v], a1 = h[v + n], a2 = h[v + 2 * n], a3 = h[v + 3 * n];
+        l[v] = tf32_lo_of_trunc(a0); l[v + n] = tf32_lo_of_trunc(a1);
+        l[v + 2 * n] = tf32_lo_of_trunc(a2); l[v + 3 * n] = tf32_lo_of_trunc(a3);
+    }
+    for (; v < nvec; v += n) l[v] = tf32_lo_of_trunc(h[v]);
+}
+
 // hi/lo planes of a whole tensor in global memory (weights are split once per call, not per tile).
 __global__ void split_tensor_kernel(const float4* __restrict__ src, float4* __restrict__ hi, float4* __restrict__ lo, size_t n4)
 {
