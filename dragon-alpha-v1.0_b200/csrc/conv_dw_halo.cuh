@@ -47,7 +47,36 @@ struct DwHaloParams {
     uint32_t idesc, tmem_cols;
     uint32_t dy_blk, x_blk;   // bytes of one 32-channel block of the deltaY / X tile (multiples of 1024)
     uint32_t dy_tx, x_tx;     // bytes one block load delivers
+    int debug;                // timing experiments only: 1 no loads, 2 no split, 4 no MMAs (results are wrong)
 };
+
+// The MMAs of one staged pixel tile as straight-line code: all steps of one tap back to back.
+// MODE 1 issues lo*hi, hi*lo, hi*hi per step; MODE 0 one MMA (plain TF32, or stacked planes).
+template <int MODE, int FW_T, int R_T, int CW_T>
+__device__ __forceinline__ void dw_issue_tile(uint32_t tmem_base, uint32_t acc_cols, uint32_t a_s, uint32_t b_s,
+                                              uint32_t lo_off, uint32_t dhi, uint32_t idesc, uint32_t acc)
+{
+    constexpr int kPW = CW_T + FW_T - 1;
+#pragma unroll
+    for (int fw = 0; fw < FW_T; ++fw) {
+        const uint32_t d = tmem_base + fw * acc_cols;
+#pragma unroll
+        for (int r = 0; r < R_T; ++r)
+#pragma unroll
+            for (int g = 0; g < CW_T / 8; ++g) {
+                const uint32_t a_k = a_s + (r * CW_T + g * 8) * 8;
+                const uint32_t b_k = b_s + (r * kPW + g * 8 + fw) * 8;
+                const uint32_t first = (r | g) ? 1u : acc;
+                if (MODE == 1) {
+                    mma_tf32_ss2(d, a_k + lo_off, dhi, b_k, dhi, idesc, first);
+                    mma_tf32_ss2(d, a_k, dhi, b_k + lo_off, dhi, idesc, 1u);
+                    mma_tf32_ss2(d, a_k, dhi, b_k, dhi, idesc, 1u);
+                } else {
+                    mma_tf32_ss2(d, a_k, dhi, b_k, dhi, idesc, first);
+                }
+            }
+    }
+}
 
 // FW_T > 0: FW, R and CW are compile-time and the MMAs of a stage are straight-line code.
 template <int FW_T, int R_T, int CW_T>
@@ -129,6 +158,7 @@ __global__ void __launch_bounds__(kDwHaloThreads, 1)
                 if (!wait_prof(empty_a + 8 * rp.idx, rp.phase ^ 1, prof_on, w_empty)) { report(p.status, kStatusProducerTimeout); break; }
                 const uint32_t bar = full_a + 8 * rp.idx;
                 const uint32_t dst = smem_a + rp.idx * stage_bytes;
+                if (p.debug & 1) { mbar_arrive_a(bar); rp.advance(S); continue; }
                 mbar_arrive_expect_tx_a(bar, dyb * p.dy_tx + xb * p.x_tx);
                 const int oh0 = rb * R, ow0 = cb * CW;
                 for (int b = 0; b < dyb; ++b)
@@ -151,41 +181,27 @@ __global__ void __launch_bounds__(kDwHaloThreads, 1)
             const uint32_t a_lo0 = smem_desc_lo(smem_a, p.dy_blk);              // LBO = block stride
             const uint32_t b_lo0 = smem_desc_lo(smem_a + x_off, p.x_blk);
             uint32_t acc = 0u;  // the first MMA into each accumulator overwrites it
-            unsigned long long w_in = 0;
+            unsigned long long w_in = 0, w_issue = 0, w_commit = 0;
             const long long t_begin = clock64();
             for (int t = blockIdx.x; t < p.total_tiles; t += gridDim.x) {
                 if (!wait_prof(wait_a + 8 * rp.idx, rp.phase, prof_on, w_in)) { report(p.status, kStatusMmaTimeout); break; }
                 tc_fence_after_sync();
+                const long long t_i0 = prof_on ? clock64() : 0;
                 const uint32_t a_s = a_lo0 + rp.idx * stage16, b_s = b_lo0 + rp.idx * stage16;
-                if constexpr (kStatic) {
-#pragma unroll
-                    for (int r = 0; r < R_T; ++r)
-#pragma unroll
-                        for (int g = 0; g < CW_T / 8; ++g) {
-                            constexpr int kPW = CW_T + FW_T - 1;
-                            const uint32_t a_k = a_s + (r * CW_T + g * 8) * 8;
-                            const uint32_t first = (r | g) ? 1u : acc;
-#pragma unroll
-                            for (int fw = 0; fw < FW_T; ++fw) {
-                                const uint32_t b_k = b_s + (r * kPW + g * 8 + fw) * 8;
-                                const uint32_t d = tmem_base + fw * acc_cols;
-                                if (three) {
-                                    mma_tf32_ss2(d, a_k + lo_off, dhi, b_k, dhi, p.idesc, first);
-                                    mma_tf32_ss2(d, a_k, dhi, b_k + lo_off, dhi, p.idesc, 1u);
-                                    mma_tf32_ss2(d, a_k, dhi, b_k, dhi, p.idesc, 1u);
-                                } else {
-                                    mma_tf32_ss2(d, a_k, dhi, b_k, dhi, p.idesc, first);
-                                }
-                            }
-                        }
+                if (p.debug & 4) {
+                } else if constexpr (kStatic) {
+                    // the mode test stays outside the unrolled MMAs: a branch per MMA costs the issuing
+                    // thread more than the MMA takes
+                    if (three) dw_issue_tile<1, FW_T, R_T, CW_T>(tmem_base, acc_cols, a_s, b_s, lo_off, dhi, p.idesc, acc);
+                    else dw_issue_tile<0, FW_T, R_T, CW_T>(tmem_base, acc_cols, a_s, b_s, lo_off, dhi, p.idesc, acc);
                 } else {
-                    uint32_t a_row = a_s, b_row = b_s;
-                    uint32_t first = acc;
-                    for (int r = 0; r < R; ++r, a_row += CW * 8, b_row += PW * 8) {
-                        uint32_t a_k = a_row, b_g = b_row;
-                        for (int g = 0; g < CW / 8; ++g, a_k += 64, b_g += 64) {
-                            uint32_t b_k = b_g, d = tmem_base;
-                            for (int fw = 0; fw < FW; ++fw, b_k += 8, d += acc_cols) {
+                    uint32_t d = tmem_base, b_tap = b_s;
+                    for (int fw = 0; fw < FW; ++fw, b_tap += 8, d += acc_cols) {
+                        uint32_t a_row = a_s, b_row = b_tap;
+                        uint32_t first = acc;
+                        for (int r = 0; r < R; ++r, a_row += CW * 8, b_row += PW * 8) {
+                            uint32_t a_k = a_row, b_k = b_row;
+                            for (int g = 0; g < CW / 8; ++g, a_k += 64, b_k += 64) {
                                 if (three) {
                                     mma_tf32_ss2(d, a_k + lo_off, dhi, b_k, dhi, p.idesc, first);
                                     mma_tf32_ss2(d, a_k, dhi, b_k + lo_off, dhi, p.idesc, 1u);
@@ -193,18 +209,20 @@ __global__ void __launch_bounds__(kDwHaloThreads, 1)
                                 } else {
                                     mma_tf32_ss2(d, a_k, dhi, b_k, dhi, p.idesc, first);
                                 }
+                                first = 1u;
                             }
-                            first = 1u;
                         }
                     }
                 }
                 acc = 1u;
+                const long long t_i1 = prof_on ? clock64() : 0;
                 mma_commit_a(empty_a + 8 * rp.idx);
                 rp.advance(S);
+                if (prof_on) { w_issue += t_i1 - t_i0; w_commit += clock64() - t_i1; }
             }
             mma_commit(accum);
             if (prof_on) {
-                p.prof[kProfMmaPatchWait] = w_in;
+                p.prof[kProfMmaPatchWait] = w_in; p.prof[kProfMmaBWait] = w_issue; p.prof[kProfMmaAccWait] = w_commit;
                 p.prof[kProfMmaTotal] = static_cast<unsigned long long>(clock64() - t_begin);
             }
         }
@@ -220,7 +238,8 @@ __global__ void __launch_bounds__(kDwHaloThreads, 1)
             for (int t = blockIdx.x; t < p.total_tiles; t += gridDim.x) {
                 if (!wait_prof(full_a + 8 * rp.idx, rp.phase, prof_on, w_full)) { report(p.status, kStatusSplitTimeout); ok = false; break; }
                 uint8_t* hi = smem + static_cast<size_t>(rp.idx) * stage_bytes;
-                if (stacked) {
+                if (p.debug & 2) {
+                } else if (stacked) {
                     split_plane_lo_x4(hi, hi + dy_bytes, dy_bytes, tid128, 128);
                     split_plane_lo_x4(hi + x_off, hi + x_off + x_bytes, x_bytes, tid128, 128);
                 } else {
