@@ -46,7 +46,7 @@ OPS = ("fwd", "dx", "dw")
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--math", default="3xtf32", choices=["3xtf32", "tf32"])
@@ -164,7 +164,11 @@ def run_reference(args):
 # ---------------------------------------------------------------------------------------------------
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons sampled every 200 ms while the timed region runs."""
+    """SM clock, power and clock-event reasons of one GPU, sampled while the timed region runs.
+
+    Reads NVML every 10 ms from a thread (queries only; nothing is set); falls back to an
+    `nvidia-smi -lms 200` child process when the NVML binding is missing.
+    """
 
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
@@ -174,8 +178,22 @@ class ClockSampler:
         self.uuid = uuid
         self.proc = None
         self.lines = []
+        self.samples = []      # (sm_mhz, power_w, reasons bitmask)
+        self.nvml = None
+        self.stop_flag = threading.Event()
 
     def start(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.handle = pynvml.nvmlDeviceGetHandleByUUID(self.uuid) if self.uuid else pynvml.nvmlDeviceGetHandleByIndex(0)
+            self.sm_max = pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM)
+            self.nvml = pynvml
+            self.thread = threading.Thread(target=self._poll, daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.nvml = None
         cmd = ["nvidia-smi", "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits", "-lms", "200"]
         if self.uuid:
             cmd += ["-i", self.uuid]
@@ -186,11 +204,38 @@ class ClockSampler:
         except OSError:
             self.proc = None
 
+    def _poll(self):
+        n = self.nvml
+        while not self.stop_flag.is_set():
+            try:
+                sm = n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM)
+                pw = n.nvmlDeviceGetPowerUsage(self.handle) / 1000.0
+                rs = n.nvmlDeviceGetCurrentClocksEventReasons(self.handle)
+                self.samples.append((float(sm), pw, int(rs)))
+            except Exception:
+                pass
+            time.sleep(0.01)
+
     def _pump(self):
         for ln in self.proc.stdout:
             self.lines.append(ln.strip())
 
     def stop(self):
+        if self.nvml is not None:
+            self.stop_flag.set()
+            self.thread.join(timeout=2)
+            n = self.nvml
+            names = (("hw_slowdown", n.nvmlClocksEventReasonHwSlowdown),
+                     ("hw_thermal_slowdown", n.nvmlClocksEventReasonHwThermalSlowdown),
+                     ("sw_thermal_slowdown", n.nvmlClocksEventReasonSwThermalSlowdown),
+                     ("sw_power_cap", n.nvmlClocksEventReasonSwPowerCap),
+                     ("hw_power_brake", n.nvmlClocksEventReasonHwPowerBrakeSlowdown))
+            reasons = sorted({nm for (_, _, r) in self.samples for nm, bit in names if r & bit})
+            sm = [x[0] for x in self.samples]
+            return {"sm_mhz": statistics.median(sm) if sm else None, "sm_min_mhz": min(sm) if sm else None,
+                    "sm_max_mhz": float(self.sm_max),
+                    "power_w_max": max((x[1] for x in self.samples), default=None), "samples": len(sm),
+                    "source": "nvml, 10 ms", "reasons": reasons}
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         time.sleep(0.25)
@@ -213,7 +258,8 @@ class ClockSampler:
                 if v.lower().startswith("active"):
                     reasons.add(nm)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
-                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+                "power_w_max": max(power) if power else None, "samples": len(sm), "source": "nvidia-smi, 200 ms",
+                "reasons": sorted(reasons)}
 
 
 def run_ours(args):
@@ -397,8 +443,9 @@ def run_ours(args):
 def run_e2e(args, torch, dist, dev, world, layers, run_op, step_flops, B, comm_stream):
     """Same step through the operator API with HOST buffers: every step copies that step's X,
     deltaY and W from pinned host memory, runs the twelve contractions and copies Y, deltaX and
-    deltaW back to pinned host memory.  Copies run on their own streams so that the transfer of
-    one layer overlaps the kernels of another."""
+    deltaW back to pinned host memory.  Copies run on their own streams and the device tensors are
+    double-buffered, so that uploads, kernels and downloads of neighbouring layers and steps overlap;
+    the clock stops when the last step's results are on the host."""
     pin = lambda a: torch.from_numpy(a).pin_memory()
     for L in layers:
         L["Xp"], L["Wp"], L["dYp"] = pin(L["Xh"]), pin(L["Wh"]), pin(L["dYh"])
@@ -409,16 +456,29 @@ def run_e2e(args, torch, dist, dev, world, layers, run_op, step_flops, B, comm_s
     d2h = sum(4 * (L["Yp"].numel() + L["dXp"].numel() + L["dWp"].numel()) for L in layers)
     s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
     main = torch.cuda.current_stream()
+    # two sets of device tensors: the uploads of step i+1 run while step i computes and downloads
+    dev_keys = ("X", "W", "dY", "Y", "dX", "dW")
+    sets = [layers, [dict(L, **{k: torch.empty_like(L[k]) for k in dev_keys}) for L in layers]]
+    consumed = [None, None]    # main-stream event: the kernels that read/wrote this set are done
+    downloaded = [None, None]  # s_out event: this set's results have reached the host
+    counter = [0]
 
     def step():
-        ins, works = [], []
+        s = counter[0] & 1
+        counter[0] += 1
+        cur = sets[s]
+        ins = []
         with torch.cuda.stream(s_in):
-            for L in layers:
+            if consumed[s] is not None:
+                s_in.wait_event(consumed[s])
+            for L in cur:
                 L["X"].copy_(L["Xp"], non_blocking=True)
                 L["W"].copy_(L["Wp"], non_blocking=True)
                 L["dY"].copy_(L["dYp"], non_blocking=True)
                 ev = torch.cuda.Event(); ev.record(s_in); ins.append(ev)
-        for L, ev in zip(layers, ins):
+        if downloaded[s] is not None:
+            main.wait_event(downloaded[s])
+        for L, ev in zip(cur, ins):
             main.wait_event(ev)
             for op in OPS:
                 run_op(L, op)
@@ -431,9 +491,8 @@ def run_e2e(args, torch, dist, dev, world, layers, run_op, step_flops, B, comm_s
                 L["Yp"].copy_(L["Y"], non_blocking=True)
                 L["dXp"].copy_(L["dX"], non_blocking=True)
                 L["dWp"].copy_(L["dW"], non_blocking=True)
-        main.wait_stream(s_out)
-        # the next step's uploads overwrite X/dY/W: they must follow this step's kernels
-        s_in.wait_stream(main)
+        consumed[s] = torch.cuda.Event(); consumed[s].record(main)
+        downloaded[s] = torch.cuda.Event(); downloaded[s].record(s_out)
 
     steps = max(3, min(args.steps, 10))
     for _ in range(2):
@@ -445,6 +504,7 @@ def run_e2e(args, torch, dist, dev, world, layers, run_op, step_flops, B, comm_s
     t0.record()
     for _ in range(steps):
         step()
+    main.wait_stream(s_out)   # the last step's results are on the host when the clock stops
     t1.record()
     if world > 1:
         dist.barrier()

@@ -70,6 +70,9 @@ struct DeviceCtx {
     // streams get different blocks and may overlap freely.
     struct Block { float* ptr = nullptr; size_t bytes = 0; };
     std::map<cudaStream_t, Block> workspace;
+    // second block per stream: the patch matrix of the small-channel paths, which is alive while
+    // the kernels it feeds use the first block
+    std::map<cudaStream_t, Block> workspace2;
 };
 static DeviceCtx g_ctx[64];
 static std::mutex g_mu;
@@ -133,10 +136,10 @@ int get_ctx(DeviceCtx** out)
 
 // Returns the scratch block of `stream`, grown to at least `bytes`.  Growing waits for the stream
 // to drain first, because work already enqueued on it may still use the old block.
-static int get_workspace(DeviceCtx* c, cudaStream_t stream, size_t bytes, float** out)
+static int get_workspace(DeviceCtx* c, cudaStream_t stream, size_t bytes, float** out, int slot = 0)
 {
     std::lock_guard<std::mutex> lock(g_mu);
-    DeviceCtx::Block& b = c->workspace[stream];
+    DeviceCtx::Block& b = slot ? c->workspace2[stream] : c->workspace[stream];
     if (b.bytes < bytes) {
         if (b.ptr) {
             cudaStreamSynchronize(stream);
@@ -585,6 +588,40 @@ static int launch_halo(DeviceCtx* c, const IgemmPlan& pl, int mode3x, cudaStream
     return rc;
 }
 
+// ---- channel counts the tensor kernels cannot stage: patch matrix + 1x1 convolution ---------------
+//
+// The forward kernels stage 8, 16 or 32 input channels per filter tap and the deltaW kernels 32,
+// so a first layer with IC = 4 (3 colour planes padded to 4) would fall to the gather kernels.
+// Instead the patches are written out once as a matrix A[N*OH*OW][Kp], Kp = FH*FW*IC rounded up to
+// 32 with zero columns, and the convolution becomes a 1x1 convolution over an "image" with Kp
+// channels: forward Y = A * W^T with W read in place as [OC][FH*FW*IC] (the tensor map zero-fills
+// the columns past FH*FW*IC), deltaW = deltaY^T * A, unpadded afterwards.
+static int make_patch_matrix(DeviceCtx* c, const AlphaConvShape* s, const float* X, cudaStream_t stream, float** A,
+                             int* K_out, int* Kp_out, size_t extra_floats)
+{
+    const int K = s->FH * s->FW * s->IC, Kp = (K + 31) / 32 * 32;
+    const size_t M = (size_t)s->N * s->OH * s->OW;
+    float* ws = nullptr;
+    int rc = get_workspace(c, stream, (M * Kp + extra_floats) * sizeof(float), &ws, 1);
+    if (rc) return rc;
+    PatchShape ps{s->N, s->IH, s->IW, s->IC, s->FH, s->FW, s->OH, s->OW, s->sh, s->sw, s->ph, s->pw, K, Kp};
+    const size_t total = M * (Kp / 4);
+    size_t blocks = (total + 255) / 256;
+    if (blocks > (size_t)c->sm_count * 16) blocks = (size_t)c->sm_count * 16;
+    patch_matrix_kernel<<<(unsigned)blocks, 256, 0, stream>>>(X, ws, ps);
+    note_launch("patch_matrix");
+    rc = check_launch("patch_matrix_kernel");
+    if (rc) return rc;
+    *A = ws; *K_out = K; *Kp_out = Kp;
+    return ALPHA_OK;
+}
+
+static bool patch_path_ok(const AlphaConvShape* s)
+{
+    const long long K = (long long)s->FH * s->FW * s->IC;
+    return s->IC % 4 == 0 && K <= 8192 && env_int("ALPHA_PATCH_MATRIX", 1) != 0;
+}
+
 static bool taps_fit64(const AlphaConvShape* s) { return s->FH * s->FW <= 64; }
 
 // ---- strided deltaX: one stride-1 convolution per output phase ------------------------------------
@@ -601,8 +638,12 @@ static int launch_dx_phases(DeviceCtx* c, const AlphaConvShape* s, const float* 
 {
     if (env_tile_mode() == 1 || !env_int("ALPHA_DX_PHASES", 1)) return 1;
     if (s->OC % 32 != 0 || s->sh > 8 || s->sw > 8 || !taps_fit64(s)) return 1;
-    if (s->FH < s->sh || s->FW < s->sw) return 1;  // some phase would get no tap at all
     if (s->IH < s->sh || s->IW < s->sw) return 1;
+    if (s->FH < s->sh || s->FW < s->sw) {
+        // some phases receive no filter tap at all (1x1 stride 2): those pixels of deltaX are zero
+        cudaError_t e = cudaMemsetAsync(dX, 0, (size_t)s->N * s->IH * s->IW * s->IC * sizeof(float), stream);
+        if (e != cudaSuccess) return fail(ALPHA_E_CUDA, "cudaMemsetAsync(deltaX): %s", cudaGetErrorString(e));
+    }
     const int taps = s->FH * s->FW;
     const size_t nW = (size_t)s->OC * taps * s->IC;
     float* ws = nullptr;
@@ -616,6 +657,7 @@ static int launch_dx_phases(DeviceCtx* c, const AlphaConvShape* s, const float* 
             const int qy = (py + s->ph - ry) / s->sh, qx = (px + s->pw - rx) / s->sw;
             const int A = (s->IH - py + s->sh - 1) / s->sh, Bw = (s->IW - px + s->sw - 1) / s->sw;
             const int ptaps = Uy * Ux;
+            if (ptaps == 0) continue;
             TapMap map{};
             map.n = ptaps;
             for (int u = 0; u < Uy; ++u)
@@ -775,7 +817,7 @@ static int launch_dw_halo(DeviceCtx* c, const AlphaConvShape* s, const float* X,
     if (rc) return rc;
     if (parts * nsub > 1) {
         const size_t n4 = sizeW / 4;
-        dw_reduce_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, stream>>>(ws, sizeW, parts * nsub, dW, n4, 0);
+        dw_reduce_kernel<<<(unsigned)((n4 + 63) / 64), 64, 0, stream>>>(ws, sizeW, parts * nsub, dW, n4, 0);
         note_launch("dw_halo");
         rc = check_launch("dw_reduce_kernel");
     }
@@ -786,7 +828,7 @@ static int launch_dw_halo(DeviceCtx* c, const AlphaConvShape* s, const float* X,
 int launch_buf_summary(cudaStream_t stream, const float* buf, float* deltaW, int part, size_t sizeW)
 {
     const size_t n4 = sizeW / 4;
-    dw_reduce_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, stream>>>(buf, sizeW, part, deltaW, n4, 1);
+    dw_reduce_kernel<<<(unsigned)((n4 + 63) / 64), 64, 0, stream>>>(buf, sizeW, part, deltaW, n4, 1);
     note_launch("buf_summary");
     return check_launch("dw_reduce_kernel");
 }
@@ -996,6 +1038,21 @@ static int forward_direct(DeviceCtx* c, const AlphaConvShape* s, const float* X,
         if (rc != 1) return rc;
         return launch_igemm(c, pl, g_math.load() == ALPHA_MATH_3XTF32, stream);
     }
+    if (algo != ALPHA_ALGO_SIMT && patch_path_ok(s)) {
+        float* A = nullptr;
+        int K = 0, Kp = 0;
+        rc = make_patch_matrix(c, s, X, stream, &A, &K, &Kp, 0);
+        if (rc) return rc;
+        IgemmPlan pl{};
+        pl.act = A; pl.aN = s->N; pl.aH = s->OH; pl.aW = s->OW; pl.aC = Kp;
+        pl.FH = 1; pl.FW = 1; pl.sh = 1; pl.sw = 1; pl.pad_h = 0; pl.pad_w = 0;
+        pl.out = Y; pl.oH = s->OH; pl.oW = s->OW; pl.ncols = s->OC;
+        pl.W = W; pl.wOC = s->OC; pl.wIC = K; pl.bias = bias;
+        pl.b_mn = false; pl.flip = false; pl.kdim = Kp;
+        rc = launch_halo(c, pl, g_math.load() == ALPHA_MATH_3XTF32, stream);
+        if (rc != 1) return rc;
+        return launch_igemm(c, pl, g_math.load() == ALPHA_MATH_3XTF32, stream);
+    }
     const size_t total = (size_t)s->N * s->OH * s->OW * s->OC;
     conv_fwd_simt<<<simt_grid(total, c->sm_count), 256, 0, stream>>>(X, W, bias, Y, to_dev_shape(s));
     note_launch("simt");
@@ -1078,6 +1135,27 @@ int alpha_conv3d_deltaW(const AlphaConvShape* s, const float* X, const float* de
     const bool tensor_ok = (s->IC % 32 == 0) && s->ph < 128 && s->pw < 128 && s->FH <= 256 && s->FW <= 256;
     if (algo == ALPHA_ALGO_TENSOR && !tensor_ok)
         return fail(ALPHA_E_ARG, "tensor deltaW path needs IC %% 32 == 0 (IC=%d)", s->IC);
+    if (algo != ALPHA_ALGO_SIMT && !tensor_ok && patch_path_ok(s)) {
+        // deltaW[oc][k] = sum over pixels of deltaY[pixel][oc] * A[pixel][k]: a 1x1 deltaW over the patch matrix
+        float* A = nullptr;
+        int K = 0, Kp = 0;
+        const size_t M = (size_t)s->N * s->OH * s->OW;
+        rc = make_patch_matrix(c, s, X, stream, &A, &K, &Kp, (size_t)s->OC * ((s->FH * s->FW * s->IC + 31) / 32 * 32));
+        if (rc) return rc;
+        float* dWp = A + M * Kp;
+        AlphaConvShape t = *s;
+        t.IH = s->OH; t.IW = s->OW; t.IC = Kp; t.FH = 1; t.FW = 1; t.sh = 1; t.sw = 1; t.ph = 0; t.pw = 0;
+        rc = launch_dw_halo(c, &t, A, deltaY, dWp, g_math.load() == ALPHA_MATH_3XTF32, stream);
+        if (rc < 0) return rc;
+        if (rc == 0) {
+            const size_t total4 = (size_t)s->OC * (K / 4);
+            size_t blocks = (total4 + 255) / 256;
+            if (blocks > (size_t)c->sm_count * 16) blocks = (size_t)c->sm_count * 16;
+            unpad_rows_kernel<<<(unsigned)blocks, 256, 0, stream>>>(dWp, deltaW, s->OC, K, Kp);
+            note_launch("dw_patch");
+            return check_launch("unpad_rows_kernel");
+        }
+    }
     if (algo == ALPHA_ALGO_SIMT || !tensor_ok) {
         const size_t total = (size_t)s->OC * s->FH * s->FW * s->IC;
         conv_dw_simt<<<(unsigned)total, 128, 0, stream>>>(X, deltaY, deltaW, to_dev_shape(s));
@@ -1151,7 +1229,7 @@ int alpha_conv3d_deltaW(const AlphaConvShape* s, const float* X, const float* de
     if (rc) return rc;
     if (splits > 1) {
         const size_t n4 = sizeW / 4;
-        dw_reduce_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, stream>>>(ws, sizeW, splits, deltaW, n4, 0);
+        dw_reduce_kernel<<<(unsigned)((n4 + 63) / 64), 64, 0, stream>>>(ws, sizeW, splits, deltaW, n4, 0);
         note_launch("dw");
         rc = check_launch("dw_reduce_kernel");
     }
@@ -1241,7 +1319,7 @@ int alpha_conv3d_deltaW_noalloc(const AlphaConvShape* s, const float* X, const f
     if (rc) return rc;
     if (splits > 1) {
         const size_t n4 = sizeW / 4;
-        dw_reduce_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, stream>>>(c->scratch, sizeW, splits, deltaW, n4, 0);
+        dw_reduce_kernel<<<(unsigned)((n4 + 63) / 64), 64, 0, stream>>>(c->scratch, sizeW, splits, deltaW, n4, 0);
         note_launch("dw_noalloc");
         rc = check_launch("dw_reduce_kernel");
     }

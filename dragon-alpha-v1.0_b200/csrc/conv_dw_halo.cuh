@@ -145,6 +145,7 @@ __global__ void __launch_bounds__(kDwHaloThreads, 1)
     const int PW = CW + FW - 1;
     const bool prof_on = p.prof != nullptr && blockIdx.x == 0 && blockIdx.y == 0;
     const long long t_kernel = clock64();
+    const unsigned long long ns_kernel = prof_on ? globaltimer_ns() : 0ull;
 
     if (warp == 0) {
         if (lane == 0) {
@@ -295,7 +296,10 @@ __global__ void __launch_bounds__(kDwHaloThreads, 1)
     }
     tc_fence_before_sync();
     __syncthreads();
-    if (prof_on && threadIdx.x == 0) p.prof[kProfTotal] = static_cast<unsigned long long>(clock64() - t_kernel);
+    if (prof_on && threadIdx.x == 0) {
+        p.prof[kProfTotal] = static_cast<unsigned long long>(clock64() - t_kernel);
+        p.prof[kProfTotal + 1] = globaltimer_ns() - ns_kernel;   // wall time of the same span, ns
+    }
     if (warp == 1) tmem_dealloc(tmem_base, p.tmem_cols);
 }
 

@@ -145,6 +145,50 @@ __device__ __forceinline__ void split_plane_lo_x4(const uint8_t* plane, uint8_t*
     for (; v < nvec; v += n) l[v] = tf32_lo_of_trunc(h[v]);
 }
 
+// Patch matrix of a convolution for channel counts the tensor kernels cannot stage directly:
+// A[m][k] with m = (n, oh, ow), k = (fh * FW + fw) * IC + ic < K, zero for K <= k < Kp and outside
+// the image.  One thread per four consecutive k (IC is a multiple of 4, so they share a pixel).
+struct PatchShape {
+    int N, IH, IW, IC, FH, FW, OH, OW, sh, sw, ph, pw, K, Kp;
+};
+
+__global__ void __launch_bounds__(256) patch_matrix_kernel(const float* __restrict__ X, float* __restrict__ A, const PatchShape s)
+{
+    const int k4n = s.Kp >> 2;
+    const size_t total = static_cast<size_t>(s.N) * s.OH * s.OW * k4n;
+    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const size_t m = i / k4n;
+        const int k = static_cast<int>(i - m * k4n) << 2;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (k < s.K) {
+            const int tap = k / s.IC, ic = k - tap * s.IC;
+            const int fh = tap / s.FW, fw = tap - fh * s.FW;
+            const int ow = static_cast<int>(m % s.OW);
+            const size_t t = m / s.OW;
+            const int oh = static_cast<int>(t % s.OH);
+            const size_t n = t / s.OH;
+            const int ih = oh * s.sh - s.ph + fh, iw = ow * s.sw - s.pw + fw;
+            if (ih >= 0 && ih < s.IH && iw >= 0 && iw < s.IW)
+                v = __ldg(reinterpret_cast<const float4*>(X + ((n * s.IH + ih) * s.IW + iw) * s.IC + ic));
+        }
+        reinterpret_cast<float4*>(A)[i] = v;
+    }
+}
+
+// dst[r][0..K) = src[r][0..K) of a matrix with row pitch Kp (drops the zero padding columns).
+__global__ void __launch_bounds__(256) unpad_rows_kernel(const float* __restrict__ src, float* __restrict__ dst, int rows, int K, int Kp)
+{
+    const int k4n = K >> 2;
+    const size_t total = static_cast<size_t>(rows) * k4n;
+    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const size_t r = i / k4n;
+        const int k = static_cast<int>(i - r * k4n) << 2;
+        reinterpret_cast<float4*>(dst)[i] = *reinterpret_cast<const float4*>(src + r * Kp + k);
+    }
+}
+
 // hi/lo planes of a whole tensor in global memory (weights are split once per call, not per tile).
 __global__ void split_tensor_kernel(const float4* __restrict__ src, float4* __restrict__ hi, float4* __restrict__ lo, size_t n4)
 {
@@ -555,14 +599,24 @@ __global__ void dw_reduce_kernel(const float* __restrict__ part, size_t split_st
     if (i >= n4) return;
     float4 s = accumulate ? reinterpret_cast<const float4*>(out)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
     float4 c = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int k = 0; k < splits; ++k) {
-        const float4 v = reinterpret_cast<const float4*>(part + k * split_stride)[i];
+    auto add = [&](const float4& v) {
         float y, t;
         y = v.x - c.x; t = s.x + y; c.x = (t - s.x) - y; s.x = t;
         y = v.y - c.y; t = s.y + y; c.y = (t - s.y) - y; s.y = t;
         y = v.z - c.z; t = s.z + y; c.z = (t - s.z) - y; s.z = t;
         y = v.w - c.w; t = s.w + y; c.w = (t - s.w) - y; s.w = t;
+    };
+    // eight loads in flight, then the compensated additions in split order: there are few threads
+    // (one per four weights), so the loop is bound by load latency, not bandwidth
+    int k = 0;
+    for (; k + 8 <= splits; k += 8) {
+        float4 v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = __ldg(reinterpret_cast<const float4*>(part + (k + j) * split_stride) + i);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) add(v[j]);
     }
+    for (; k < splits; ++k) add(__ldg(reinterpret_cast<const float4*>(part + k * split_stride) + i));
     reinterpret_cast<float4*>(out)[i] = s;
 }
 
