@@ -485,15 +485,32 @@ static HaloChoice plan_halo(const IgemmPlan& pl, int BN, int mode3x, int b_mn, i
 }
 
 // Returns 1 when the shape is left to the per-tap kernel, 0 on launch, < 0 on error.
-static int launch_halo(DeviceCtx* c, const IgemmPlan& pl, int mode3x, cudaStream_t stream)
+static int launch_halo(DeviceCtx* c, const IgemmPlan& pl_in, int mode3x, cudaStream_t stream)
 {
     const int tile_mode = env_tile_mode();
     if (tile_mode == 1) return 1;
+    IgemmPlan pl = pl_in;
     if (pl.sh != 1 || pl.sw != 1 || pl.kdim % 32 != 0) return 1;
+    // a 1x1 convolution does not care which pixels are neighbours: seen as one image of 8 columns
+    // every 16 x 8 tile is full, whatever the real image size
+    const long long flat_m = (long long)pl.aN * pl.aH * pl.aW;
+    if (pl.FH == 1 && pl.FW == 1 && pl.pad_h == 0 && pl.pad_w == 0 && pl.oSH == 1 && pl.oSW == 1 && pl.oNH == 0 &&
+        pl.oNW == 0 && pl.oH == pl.aH && pl.oW == pl.aW && flat_m % 8 == 0 && flat_m / 8 <= 2147483647LL &&
+        env_int("ALPHA_HALO_FLAT", 1)) {
+        pl.aN = 1; pl.aW = 8; pl.aH = (int)(flat_m / 8);
+        pl.oH = pl.aH; pl.oW = 8;
+    }
     const int gran = pl.b_mn ? 32 : 16;
     int BN = ((pl.ncols + gran - 1) / gran) * gran;
     if (BN > 256) BN = (pl.ncols % 256 == 0 || pl.ncols > 512) ? 256 : 128;
     HaloChoice ch = plan_halo(pl, BN, mode3x, pl.b_mn, c->sm_count);
+    // narrower column tiles when the wide ones leave SMs idle (small images, few pixels): the plan's
+    // cost is the time of the busiest CTA, so candidates compare directly
+    for (int cand = 128; cand >= 64; cand >>= 1) {
+        if (cand >= BN || pl.ncols % cand != 0 || !env_int("ALPHA_HALO_NARROW", 1)) continue;
+        HaloChoice alt = plan_halo(pl, cand, mode3x, pl.b_mn, c->sm_count);
+        if (alt.valid && (!ch.valid || alt.cost < 0.9 * ch.cost)) { ch = alt; BN = cand; }
+    }
     if (!ch.valid) return 1;
     if (tile_mode == 0 && ch.eff < 0.6 && !pl.force) return 1;
 
@@ -596,15 +613,15 @@ static int launch_halo(DeviceCtx* c, const IgemmPlan& pl, int mode3x, cudaStream
 // 32 with zero columns, and the convolution becomes a 1x1 convolution over an "image" with Kp
 // channels: forward Y = A * W^T with W read in place as [OC][FH*FW*IC] (the tensor map zero-fills
 // the columns past FH*FW*IC), deltaW = deltaY^T * A, unpadded afterwards.
-static int make_patch_matrix(DeviceCtx* c, const AlphaConvShape* s, const float* X, cudaStream_t stream, float** A,
-                             int* K_out, int* Kp_out, size_t extra_floats)
+static int make_patch_matrix(DeviceCtx* c, PatchShape ps, const float* X, cudaStream_t stream, float** A, int* K_out,
+                             int* Kp_out, size_t extra_floats)
 {
-    const int K = s->FH * s->FW * s->IC, Kp = (K + 31) / 32 * 32;
-    const size_t M = (size_t)s->N * s->OH * s->OW;
+    const int K = ps.FH * ps.FW * ps.IC, Kp = (K + 31) / 32 * 32;
+    ps.K = K; ps.Kp = Kp;
+    const size_t M = (size_t)ps.N * ps.OH * ps.OW;
     float* ws = nullptr;
     int rc = get_workspace(c, stream, (M * Kp + extra_floats) * sizeof(float), &ws, 1);
     if (rc) return rc;
-    PatchShape ps{s->N, s->IH, s->IW, s->IC, s->FH, s->FW, s->OH, s->OW, s->sh, s->sw, s->ph, s->pw, K, Kp};
     const size_t total = M * (Kp / 4);
     size_t blocks = (total + 255) / 256;
     if (blocks > (size_t)c->sm_count * 16) blocks = (size_t)c->sm_count * 16;
@@ -616,10 +633,37 @@ static int make_patch_matrix(DeviceCtx* c, const AlphaConvShape* s, const float*
     return ALPHA_OK;
 }
 
+static PatchShape patch_shape_of(const AlphaConvShape* s)
+{
+    return PatchShape{s->N, s->IH, s->IW, s->IC, s->FH, s->FW, s->OH, s->OW, s->sh, s->sw, s->ph, s->pw, 0, 0};
+}
+
+// Forward-form plan (K-major weights [wOC][taps][wIC], any stride) as patch matrix + 1x1 convolution.
+// Returns 1 when no tensor kernel takes the 1x1 problem.
+static int launch_patch_gemm(DeviceCtx* c, const IgemmPlan& pl, int mode3x, cudaStream_t stream)
+{
+    PatchShape ps{pl.aN, pl.aH, pl.aW, pl.aC, pl.FH, pl.FW, pl.oH, pl.oW, pl.sh, pl.sw, pl.pad_h, pl.pad_w, 0, 0};
+    float* A = nullptr;
+    int K = 0, Kp = 0;
+    int rc = make_patch_matrix(c, ps, pl.act, stream, &A, &K, &Kp, 0);
+    if (rc) return rc;
+    IgemmPlan g = pl;
+    g.act = A; g.aH = pl.oH; g.aW = pl.oW; g.aC = Kp;
+    g.FH = 1; g.FW = 1; g.sh = 1; g.sw = 1; g.pad_h = 0; g.pad_w = 0;
+    g.wIC = K; g.kdim = Kp; g.b_mn = false; g.flip = false; g.force = true;
+    rc = launch_halo(c, g, mode3x, stream);
+    if (rc != 1) return rc;
+    if (g.W_lo) return 1;   // the per-tap kernel splits W itself and cannot take pre-split planes
+    return launch_igemm(c, g, mode3x, stream);
+}
+
+// Images so small that the 16 x 8 pixel tiles of the halo kernel stay mostly empty
+static bool tiny_image(int oH, int oW) { return oH * oW <= 16; }
+
 static bool patch_path_ok(const AlphaConvShape* s)
 {
     const long long K = (long long)s->FH * s->FW * s->IC;
-    return s->IC % 4 == 0 && K <= 8192 && env_int("ALPHA_PATCH_MATRIX", 1) != 0;
+    return s->IC % 4 == 0 && K <= 16384 && env_int("ALPHA_PATCH_MATRIX", 1) != 0;
 }
 
 static bool taps_fit64(const AlphaConvShape* s) { return s->FH * s->FW <= 64; }
@@ -697,11 +741,21 @@ static void dw_halo_set_attr()
 }
 
 // Returns 1 when the shape is left to the split-K im2col kernel, 0 on launch, < 0 on error.
-static int launch_dw_halo(DeviceCtx* c, const AlphaConvShape* s, const float* X, const float* dY, float* dW,
+static int launch_dw_halo(DeviceCtx* c, const AlphaConvShape* s_in, const float* X, const float* dY, float* dW,
                           int mode3x, cudaStream_t stream)
 {
     const char* e = getenv("ALPHA_CONV_DW");
     if (e && !strcmp(e, "split")) return 1;
+    AlphaConvShape flat = *s_in;
+    const AlphaConvShape* s = s_in;
+    // a 1x1 deltaW sums over pixels in any order: one image of 16 columns fills every pixel tile
+    const long long flat_m = (long long)s_in->N * s_in->OH * s_in->OW;
+    if (s_in->FH == 1 && s_in->FW == 1 && s_in->ph == 0 && s_in->pw == 0 && s_in->sh == 1 && s_in->sw == 1 &&
+        s_in->IH == s_in->OH && s_in->IW == s_in->OW && flat_m % 16 == 0 && flat_m / 16 <= 2147483647LL &&
+        env_int("ALPHA_HALO_FLAT", 1)) {
+        flat.N = 1; flat.OW = flat.IW = 16; flat.OH = flat.IH = (int)(flat_m / 16);
+        s = &flat;
+    }
     if (s->sh != 1 || s->sw != 1 || s->IC % 32 != 0) return 1;
     if (s->FW > 8 || s->ph >= s->FH || s->pw >= s->FW) return 1;
     // input channels per CTA: FW accumulators of NT columns must fit the 512 tensor-memory columns
@@ -1034,24 +1088,23 @@ static int forward_direct(DeviceCtx* c, const AlphaConvShape* s, const float* X,
         pl.out = Y; pl.oH = s->OH; pl.oW = s->OW; pl.ncols = s->OC;
         pl.W = W; pl.wOC = s->OC; pl.wIC = s->IC; pl.bias = bias;
         pl.b_mn = false; pl.flip = false; pl.kdim = s->IC;
-        rc = launch_halo(c, pl, g_math.load() == ALPHA_MATH_3XTF32, stream);
+        const int mode3x = g_math.load() == ALPHA_MATH_3XTF32;
+        if (tiny_image(s->OH, s->OW) && (s->FH > 1 || s->FW > 1) && patch_path_ok(s) && env_tile_mode() != 1) {
+            rc = launch_patch_gemm(c, pl, mode3x, stream);
+            if (rc != 1) return rc;
+        }
+        rc = launch_halo(c, pl, mode3x, stream);
         if (rc != 1) return rc;
-        return launch_igemm(c, pl, g_math.load() == ALPHA_MATH_3XTF32, stream);
+        return launch_igemm(c, pl, mode3x, stream);
     }
     if (algo != ALPHA_ALGO_SIMT && patch_path_ok(s)) {
-        float* A = nullptr;
-        int K = 0, Kp = 0;
-        rc = make_patch_matrix(c, s, X, stream, &A, &K, &Kp, 0);
-        if (rc) return rc;
         IgemmPlan pl{};
-        pl.act = A; pl.aN = s->N; pl.aH = s->OH; pl.aW = s->OW; pl.aC = Kp;
-        pl.FH = 1; pl.FW = 1; pl.sh = 1; pl.sw = 1; pl.pad_h = 0; pl.pad_w = 0;
+        pl.act = X; pl.aN = s->N; pl.aH = s->IH; pl.aW = s->IW; pl.aC = s->IC;
+        pl.FH = s->FH; pl.FW = s->FW; pl.sh = s->sh; pl.sw = s->sw; pl.pad_h = s->ph; pl.pad_w = s->pw;
         pl.out = Y; pl.oH = s->OH; pl.oW = s->OW; pl.ncols = s->OC;
-        pl.W = W; pl.wOC = s->OC; pl.wIC = K; pl.bias = bias;
-        pl.b_mn = false; pl.flip = false; pl.kdim = Kp;
-        rc = launch_halo(c, pl, g_math.load() == ALPHA_MATH_3XTF32, stream);
+        pl.W = W; pl.wOC = s->OC; pl.wIC = s->IC; pl.bias = bias;
+        rc = launch_patch_gemm(c, pl, g_math.load() == ALPHA_MATH_3XTF32, stream);
         if (rc != 1) return rc;
-        return launch_igemm(c, pl, g_math.load() == ALPHA_MATH_3XTF32, stream);
     }
     const size_t total = (size_t)s->N * s->OH * s->OW * s->OC;
     conv_fwd_simt<<<simt_grid(total, c->sm_count), 256, 0, stream>>>(X, W, bias, Y, to_dev_shape(s));
@@ -1105,6 +1158,10 @@ int alpha_conv3d_deltaX(const AlphaConvShape* s, const float* deltaY, const floa
             rc = check_launch("transpose_weights_kernel");
             if (rc) return rc;
             if (!mode3x) pt.W_lo = nullptr;
+            if (tiny_image(s->IH, s->IW) && (s->FH > 1 || s->FW > 1) && (long long)taps * s->OC <= 16384) {
+                rc = launch_patch_gemm(c, pt, mode3x, stream);
+                if (rc != 1) return rc;
+            }
             rc = launch_halo(c, pt, mode3x, stream);
             if (rc != 1) return rc;
         }
@@ -1135,19 +1192,22 @@ int alpha_conv3d_deltaW(const AlphaConvShape* s, const float* X, const float* de
     const bool tensor_ok = (s->IC % 32 == 0) && s->ph < 128 && s->pw < 128 && s->FH <= 256 && s->FW <= 256;
     if (algo == ALPHA_ALGO_TENSOR && !tensor_ok)
         return fail(ALPHA_E_ARG, "tensor deltaW path needs IC %% 32 == 0 (IC=%d)", s->IC);
-    if (algo != ALPHA_ALGO_SIMT && !tensor_ok && patch_path_ok(s)) {
+    if (algo != ALPHA_ALGO_SIMT && patch_path_ok(s) && env_tile_mode() != 1 &&
+        (!tensor_ok || (tiny_image(s->OH, s->OW) && (s->FH > 1 || s->FW > 1)))) {
         // deltaW[oc][k] = sum over pixels of deltaY[pixel][oc] * A[pixel][k]: a 1x1 deltaW over the patch matrix
         float* A = nullptr;
         int K = 0, Kp = 0;
         const size_t M = (size_t)s->N * s->OH * s->OW;
-        rc = make_patch_matrix(c, s, X, stream, &A, &K, &Kp, (size_t)s->OC * ((s->FH * s->FW * s->IC + 31) / 32 * 32));
+        rc = make_patch_matrix(c, patch_shape_of(s), X, stream, &A, &K, &Kp,
+                               (size_t)s->OC * ((s->FH * s->FW * s->IC + 31) / 32 * 32));
         if (rc) return rc;
-        float* dWp = A + M * Kp;
+        float* dWp = K == Kp ? deltaW : A + M * Kp;
         AlphaConvShape t = *s;
         t.IH = s->OH; t.IW = s->OW; t.IC = Kp; t.FH = 1; t.FW = 1; t.sh = 1; t.sw = 1; t.ph = 0; t.pw = 0;
         rc = launch_dw_halo(c, &t, A, deltaY, dWp, g_math.load() == ALPHA_MATH_3XTF32, stream);
         if (rc < 0) return rc;
         if (rc == 0) {
+            if (K == Kp) return ALPHA_OK;
             const size_t total4 = (size_t)s->OC * (K / 4);
             size_t blocks = (total4 + 255) / 256;
             if (blocks > (size_t)c->sm_count * 16) blocks = (size_t)c->sm_count * 16;
