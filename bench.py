@@ -32,10 +32,12 @@ sys.path.insert(0, ROOT)
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under
 # profiles/ (kernel, launch shape, math mode) -> bytes
 NCU_TRAFFIC = {
-    ("conv_halo_kernel", "fwd_56x56x64", "3xtf32"): 369.2e6,   # profiles/conv_halo_fwd_3xtf32.md
-    ("conv_halo_kernel", "dx_56x56x64", "3xtf32"): 369.2e6,    # same kernel and shape as the forward launch
-    ("conv_halo_kernel", "fwd_28x28x128", "3xtf32"): 164.3e6,
-    ("conv_dw_halo_kernel", "dw_28x28x128", "3xtf32"): 209.2e6,  # profiles/conv_dw_halo_28x28x128_3xtf32.md
+    ("conv_halo_kernel", "fwd_56x56x64", "3xtf32"): 368.6e6,   # profiles/conv_halo_fwd_3xtf32.md
+    ("conv_halo_kernel", "dx_56x56x64", "3xtf32"): 368.6e6,    # same kernel and shape as the forward launch
+    ("conv_halo_kernel", "fwd_14x14x256", "3xtf32"): 90.3e6,
+    ("conv_halo_kernel", "fwd_28x28x128", "tf32"): 158.2e6,
+    ("conv_dw_halo_kernel", "dw_56x56x64", "3xtf32"): 415.5e6,  # profiles/conv_dw_halo_3xtf32.md
+    ("conv_dw_halo_kernel", "dw_28x28x128", "3xtf32"): 209.7e6,
 }
 
 METRIC = "conv fwd+deltaX+deltaW throughput, 3x3 layer sweep (batch 256 per GPU)"
