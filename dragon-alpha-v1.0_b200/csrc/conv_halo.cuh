@@ -12,8 +12,8 @@
 // arrive pre-split.  3xTF32 has two forms: mode3x == 1 issues lo*hi, hi*lo and hi*hi as three MMAs
 // of BN columns into one accumulator; mode3x == 2 ("wide", for BN <= 64, where an MMA of 64 columns
 // costs almost as much as one of 128) issues hi x [hi | lo] as ONE MMA of 2*BN columns - the lo
-// plane of a B tile directly follows its hi plane in shared memory - plus lo x hi, and the epilogue
-// adds the two column halves of the accumulator.
+// plane of a B tile directly follows its hi plane in shared memory - plus lo x hi into the second
+// half of those columns, and the epilogue adds the two column halves of the accumulator.
 // Accumulators are double-buffered in tensor memory when they fit, so the epilogue of one macro
 // tile overlaps the loads and MMAs of the next.
 //
@@ -78,7 +78,7 @@ __device__ __forceinline__ bool wait_prof(uint32_t bar, uint32_t parity, bool pr
 template <int MODE>
 __device__ __forceinline__ void issue_chunk(uint32_t d, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
                                             uint32_t b_kstep, uint32_t a_lo_off, uint32_t b_lo_off, uint32_t idesc,
-                                            uint32_t idesc_wide, uint32_t acc_first)
+                                            uint32_t idesc_wide, uint32_t acc_first, uint32_t side_off = 0)
 {
 #pragma unroll
     for (int kk = 0; kk < 4; ++kk) {
@@ -89,8 +89,11 @@ __device__ __forceinline__ void issue_chunk(uint32_t d, uint32_t a_lo, uint32_t 
             mma_tf32_ss2(d, a_k, a_hi, b_k + b_lo_off, b_hi, idesc, 1u);
             mma_tf32_ss2(d, a_k, a_hi, b_k, b_hi, idesc, 1u);
         } else if (MODE == 2) {
+            // hi*hi lands in columns [0, BN); both correction terms go to the side columns [BN, 2*BN):
+            // tensor-core accumulation truncates, so every MMA into the main sum costs up to one ulp
+            // of it, while truncation in the side sum is 2^-11 times smaller
             mma_tf32_ss2(d, a_k, a_hi, b_k, b_hi, idesc_wide, acc);
-            mma_tf32_ss2(d, a_k + a_lo_off, a_hi, b_k, b_hi, idesc, 1u);
+            mma_tf32_ss2(d + side_off, a_k + a_lo_off, a_hi, b_k, b_hi, idesc, 1u);
         } else {
             mma_tf32_ss2(d, a_k, a_hi, b_k, b_hi, idesc, acc);
         }
@@ -111,7 +114,7 @@ __device__ __forceinline__ void issue_tap(uint32_t d0, uint32_t a_tap, uint32_t 
 #pragma unroll
         for (int jw = 0; jw < JW_T; ++jw)
             issue_chunk<MODE>(d0 + (jh * JW_T + jw) * k.accw, a_tap + jh * 16 * kPW8 + jw * 64, k.a_dhi, bl, k.b_dhi, k.b_kstep,
-                              k.a_lo_off, k.b_lo_off, k.idesc, k.idesc_wide, acc_first);
+                              k.a_lo_off, k.b_lo_off, k.idesc, k.idesc_wide, acc_first, k.accw >> 1);
 }
 
 // The FW_T taps of one filter row (B stage holds them back to back, b_tile16 apart).
@@ -318,7 +321,7 @@ __global__ void __launch_bounds__(kHaloThreads, 1)
                                 uint32_t a_j = a_jh;
                                 for (int jw = 0; jw < p.JW; ++jw, a_j += 64, d += accw) {
                                     if (p.mode3x == 1) issue_chunk<1>(d, a_j, a_dhi, bl, b_dhi, b_kstep, a_lo_off, b_lo_off, p.idesc, p.idesc_wide, acc_first);
-                                    else if (p.mode3x == 2) issue_chunk<2>(d, a_j, a_dhi, bl, b_dhi, b_kstep, a_lo_off, b_lo_off, p.idesc, p.idesc_wide, acc_first);
+                                    else if (p.mode3x == 2) issue_chunk<2>(d, a_j, a_dhi, bl, b_dhi, b_kstep, a_lo_off, b_lo_off, p.idesc, p.idesc_wide, acc_first, accw >> 1);
                                     else issue_chunk<0>(d, a_j, a_dhi, bl, b_dhi, b_kstep, a_lo_off, b_lo_off, p.idesc, p.idesc_wide, acc_first);
                                 }
                             }
