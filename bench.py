@@ -302,6 +302,12 @@ def run_ours(args):
         layers.append(L)
     step_flops = sum(len(ops) * L["flops"] for L in layers)
     comm_stream = torch.cuda.Stream() if world > 1 else None
+    # the deltaW tensors of all layers are views of one flat buffer: one collective per step.  It runs
+    # after the last kernel: an all-reduce that overlaps the persistent conv kernels takes SMs from
+    # them, and a one-CTA-per-SM kernel that finds SMs busy runs those CTAs as a second wave.
+    bucket = submodule("sharding").GradientBucket([L["dW"].numel() for L in layers], dev)
+    for i, L in enumerate(layers):
+        L["dW"] = bucket.view(i, L["dW"].shape)
 
     def run_op(L, op):
         hw, c = L["hw"], L["c"]
@@ -323,13 +329,19 @@ def run_ours(args):
                 if events is not None:
                     e1.record()
                     events.append((li, op, e0, e1, lib.last_algo()))
-            if world > 1 and "dw" in ops:
+            if world > 1 and "dw" in ops and os.environ.get("BENCH_AR", "full") == "layer":
                 ready = torch.cuda.Event(); ready.record()
                 with torch.cuda.stream(comm_stream):
                     comm_stream.wait_event(ready)
                     works.append(dist.all_reduce(L["dW"], op=dist.ReduceOp.SUM, async_op=True))
         for w in works:
             w.wait()
+        if world > 1 and "dw" in ops:
+            mode = os.environ.get("BENCH_AR", "full")
+            if mode == "full":
+                dist.all_reduce(bucket.flat, op=dist.ReduceOp.SUM)
+            elif mode == "tiny":
+                dist.all_reduce(bucket.flat[:4], op=dist.ReduceOp.SUM)
 
     def barrier():
         if world > 1:
