@@ -781,6 +781,19 @@ static int launch_dw_halo(DeviceCtx* c, const AlphaConvShape* s_in, const float*
             if (stacked) NT = NTq;
         }
     }
+    // plain TF32 with at most 64 output channels: two half tiles side by side ("diagonal" form)
+    bool diag = false;
+    if (!mode3x && s->OC <= 64 && s->OH >= 2 && env_int("ALPHA_DW_DIAG", 1)) {
+        int NTd = 0;
+        for (int cand = 128; cand >= 32; cand >>= 1)
+            if (s->IC % cand == 0 && s->FW * 2 * cand <= 512) { NTd = cand; break; }
+        if (NTd) {
+            auto mma_clk = [](int n) { return n / 2 > 59 ? n / 2 : 59; };
+            // clocks per 8 pixels: one MMA of NT columns, or half an MMA of 2 * NTd columns
+            const long long std2 = 2LL * mma_clk(NT) * (s->IC / NT), dg2 = 1LL * mma_clk(2 * NTd) * (s->IC / NTd);
+            if (dg2 < std2) { diag = true; stacked = true; NT = NTd; }
+        }
+    }
     const int oc_tile = stacked ? 64 : 128, dyb = stacked ? 2 : 4, nsub = stacked ? 2 : 1;
     DwHaloParams p{};
     p.status = c->status; p.prof = c->prof;
@@ -791,7 +804,7 @@ static int launch_dw_halo(DeviceCtx* c, const AlphaConvShape* s_in, const float*
     const int groups = s->FH * p.ic_tiles * p.oc_tiles;
     if (groups > 65535) return 1;
     // pixel tile: CW columns of 8-pixel groups, R rows, sized so that three stages fit shared memory
-    const int planes = mode3x ? 2 : 1;
+    const int planes = (mode3x || diag) ? 2 : 1;   // diagonal: the second plane holds the second half tile
     int CW = env_int("ALPHA_DW_CW", 0);
     if (!CW) CW = (s->OW <= 8 || (s->OW % 16 != 0 && s->OW % 16 <= 8)) ? 8 : 16;  // fewer idle columns
     const int PW = CW + s->FW - 1;
@@ -802,13 +815,14 @@ static int launch_dw_halo(DeviceCtx* c, const AlphaConvShape* s_in, const float*
     };
     if (!R) {
         R = 8;
-        while (R > 1 && (2 * stage_bytes(R) > 210 * 1024 || R > s->OH)) R >>= 1;
+        while (R > 1 && (2 * stage_bytes(R) > 210 * 1024 || R * (diag ? 2 : 1) > s->OH)) R >>= 1;
     }
     if (2 * stage_bytes(R) > 220 * 1024) return 1;
     int stages = (int)((220 * 1024) / stage_bytes(R));
     if (stages > 4) stages = 4;
     p.R = R; p.CW = CW; p.PW = PW;
-    p.row_blocks = (s->OH + R - 1) / R; p.col_blocks = (s->OW + CW - 1) / CW;
+    const int tile_rows = diag ? 2 * R : R;   // R = rows per half tile in the diagonal form
+    p.row_blocks = (s->OH + tile_rows - 1) / tile_rows; p.col_blocks = (s->OW + CW - 1) / CW;
     p.tiles_per_img = p.row_blocks * p.col_blocks;
     const long long total = (long long)s->N * p.tiles_per_img;
     if (total > 2147483647LL) return 1;
@@ -817,7 +831,7 @@ static int launch_dw_halo(DeviceCtx* c, const AlphaConvShape* s_in, const float*
     if (parts < 1) parts = 1;
     if (parts > p.total_tiles) parts = p.total_tiles;
     p.parts = parts;
-    p.stages = stages; p.mode3x = stacked ? 2 : mode3x;
+    p.stages = stages; p.mode3x = diag ? 3 : (stacked ? 2 : mode3x);
     p.idesc = make_idesc_tf32(kBM, stacked ? 2 * NT : NT, true, true);
     p.tmem_cols = pow2_cols(s->FW * (stacked ? 2 * NT : NT));
     p.dy_tx = (uint32_t)R * CW * 128; p.dy_blk = (p.dy_tx + 1023) & ~1023u;
@@ -865,7 +879,7 @@ static int launch_dw_halo(DeviceCtx* c, const AlphaConvShape* s_in, const float*
     else DWH_LAUNCH(0, 0, 0);
 #undef DWH_LAUNCH
     note_launch("dw_halo");
-    snprintf(g_plan, sizeof(g_plan), "dw_halo%s NT=%d R=%d CW=%d stages=%d parts=%d groups=%d", stacked ? " stacked" : "", NT, R, CW,
+    snprintf(g_plan, sizeof(g_plan), "dw_halo%s NT=%d R=%d CW=%d stages=%d parts=%d groups=%d", diag ? " diagonal" : (stacked ? " stacked" : ""), NT, R, CW,
              stages, parts, groups);
     rc = check_launch("conv_dw_halo_kernel");
     if (rc) return rc;

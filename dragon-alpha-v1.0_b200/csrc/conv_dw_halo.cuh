@@ -20,6 +20,12 @@
 // so that ONE MMA forms all four products; the epilogue writes the hi rows (hi*hi + hi*lo) and the
 // lo rows (lo*hi + lo*lo) as two partials and the reduction adds them.
 //
+// mode3x == 3 ("diagonal", plain TF32 with at most 64 output channels) uses the same stacked layout
+// for two halves of the pixel tile instead of two precision planes: rows 0..R-1 and R..2R-1 of the
+// tile land where the hi and lo planes would, one MMA multiplies [dY_a; dY_b] by [X_a | X_b], the
+// diagonal quadrants dY_a*X_a and dY_b*X_b are the two partials and the off-diagonal ones are
+// ignored - twice the pixels per MMA where the 128-row operand would be half empty.
+//
 // Warps: 0 TMA producer, 1 MMA issuer, 2-5 operand split (3xTF32) during the loop, epilogue after.
 #pragma once
 #include "conv_halo.cuh"
@@ -43,7 +49,7 @@ struct DwHaloParams {
     int row_blocks, col_blocks, tiles_per_img;
     int total_tiles;       // N * tiles_per_img
     int parts;             // CTAs per accumulator group = gridDim.x
-    int stages, mode3x;    // mode3x: 0 plain TF32, 1 three MMAs, 2 stacked planes
+    int stages, mode3x;    // mode3x: 0 plain TF32, 1 three MMAs, 2 stacked planes, 3 diagonal (TF32, two half tiles)
     uint32_t idesc, tmem_cols;
     uint32_t dy_blk, x_blk;   // bytes of one 32-channel block of the deltaY / X tile (multiples of 1024)
     uint32_t dy_tx, x_tx;     // bytes one block load delivers
@@ -92,7 +98,8 @@ __global__ void __launch_bounds__(kDwHaloThreads, 1)
     const int S = p.stages;
     const uint32_t planes = p.mode3x ? 2u : 1u;
     const int xb = p.NT / 32;                       // X blocks per stage
-    const bool stacked = p.mode3x == 2;
+    const bool diag = p.mode3x == 3;
+    const bool stacked = p.mode3x == 2 || diag;   // layout [dY a][dY b] [X a][X b], M = 64 + 64, N = NT + NT
     const int dyb = stacked ? 2 : 4;                // deltaY blocks per plane: 64 or 128 output channels
     const uint32_t dy_bytes = dyb * p.dy_blk;
     const uint32_t x_bytes = xb * p.x_blk;
@@ -160,12 +167,16 @@ __global__ void __launch_bounds__(kDwHaloThreads, 1)
                 const uint32_t bar = full_a + 8 * rp.idx;
                 const uint32_t dst = smem_a + rp.idx * stage_bytes;
                 if (p.debug & 1) { mbar_arrive_a(bar); rp.advance(S); continue; }
-                mbar_arrive_expect_tx_a(bar, dyb * p.dy_tx + xb * p.x_tx);
-                const int oh0 = rb * R, ow0 = cb * CW;
-                for (int b = 0; b < dyb; ++b)
-                    tma_load_4d_a(dst + b * p.dy_blk, &tmDY, bar, oc0 + b * 32, ow0, oh0, n);
-                for (int b = 0; b < xb; ++b)
-                    tma_load_4d_a(dst + x_off + b * p.x_blk, &tmX, bar, ic0 + b * 32, ow0 - p.pw, oh0 + fh - p.ph, n);
+                const int halves = diag ? 2 : 1;
+                mbar_arrive_expect_tx_a(bar, halves * (dyb * p.dy_tx + xb * p.x_tx));
+                const int ow0 = cb * CW;
+                for (int h = 0; h < halves; ++h) {
+                    const int oh0 = (rb * halves + h) * R;   // diagonal: the tile is 2R rows, one half per slot
+                    for (int b = 0; b < dyb; ++b)
+                        tma_load_4d_a(dst + h * dy_bytes + b * p.dy_blk, &tmDY, bar, oc0 + b * 32, ow0, oh0, n);
+                    for (int b = 0; b < xb; ++b)
+                        tma_load_4d_a(dst + x_off + h * x_bytes + b * p.x_blk, &tmX, bar, ic0 + b * 32, ow0 - p.pw, oh0 + fh - p.ph, n);
+                }
                 rp.advance(S);
             }
             if (prof_on) p.prof[kProfProducerPatchWait] = w_empty;
@@ -176,7 +187,7 @@ __global__ void __launch_bounds__(kDwHaloThreads, 1)
             // ---- MMA issuer ----
             RingPos rp;
             const uint32_t dhi = smem_desc_hi(512, kSwizzle128B_Base32B);
-            const uint32_t wait_a = p.mode3x ? ready_a : full_a;
+            const uint32_t wait_a = (p.mode3x == 1 || p.mode3x == 2) ? ready_a : full_a;
             const bool three = p.mode3x == 1;
             const uint32_t stage16 = stage_bytes >> 4, lo_off = plane_bytes >> 4;
             const uint32_t a_lo0 = smem_desc_lo(smem_a, p.dy_blk);              // LBO = block stride
@@ -232,7 +243,7 @@ __global__ void __launch_bounds__(kDwHaloThreads, 1)
         // ---- operand split while the loop runs (3xTF32), epilogue afterwards: warps 2..5 ----
         const int tid128 = threadIdx.x - 64;
         bool ok = true;
-        if (p.mode3x) {
+        if (p.mode3x == 1 || p.mode3x == 2) {
             RingPos rp;
             unsigned long long w_full = 0;
             const long long t_begin = clock64();
@@ -273,7 +284,9 @@ __global__ void __launch_bounds__(kDwHaloThreads, 1)
                     const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + fw * acc_cols + c;
                     tmem_ld_32x32(taddr, v);
                     tmem_ld_wait();
-                    if (stacked) {
+                    if (diag) {
+                        if (sub) { tmem_ld_32x32(taddr + p.NT, v); tmem_ld_wait(); }   // second half tile: lower right quadrant
+                    } else if (stacked) {
                         uint32_t w[32];
                         tmem_ld_32x32(taddr + p.NT, w);
                         tmem_ld_wait();
