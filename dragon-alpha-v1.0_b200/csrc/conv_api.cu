@@ -725,6 +725,32 @@ static int launch_dx_phases(DeviceCtx* c, const AlphaConvShape* s, const float* 
             pl.oSH = s->sh; pl.oSW = s->sw; pl.oNH = s->IH; pl.oNW = s->IW;
             pl.W = whi; pl.W_lo = wlo; pl.wOC = s->IC; pl.wIC = s->OC; pl.bias = nullptr;
             pl.b_mn = false; pl.flip = false; pl.kdim = s->OC; pl.force = true;
+            if (tiny_image(A, Bw) && (long long)ptaps * s->OC <= 16384 && ptaps * s->OC >= 2048 &&
+                env_int("ALPHA_PATCH_MATRIX", 1)) {
+                // phases of a few pixels per image: patch matrix of deltaY, dense 1x1 product, scatter
+                PatchShape ps{s->N, s->OH, s->OW, s->OC, Uy, Ux, A, Bw, 1, 1, pl.pad_h, pl.pad_w, 0, 0};
+                const size_t M = (size_t)s->N * A * Bw;
+                float* P = nullptr;
+                int K = 0, Kp = 0;
+                rc = make_patch_matrix(c, ps, dY, stream, &P, &K, &Kp, M * s->IC);
+                if (rc) return rc;
+                float* Sp = P + M * Kp;
+                IgemmPlan g = pl;
+                g.act = P; g.aH = A; g.aW = Bw; g.aC = Kp; g.FH = 1; g.FW = 1; g.pad_h = 0; g.pad_w = 0;
+                g.out = Sp; g.oSH = 1; g.oSW = 1; g.oNH = 0; g.oNW = 0;
+                g.wIC = K; g.kdim = Kp;
+                rc = launch_halo(c, g, mode3x, stream);
+                if (rc == 1) return fail(ALPHA_E_ARG, "strided deltaX: phase (%d,%d) does not fit the halo kernel", py, px);
+                if (rc) return rc;
+                const size_t total4 = M * (s->IC / 4);
+                size_t blocks = (total4 + 255) / 256;
+                if (blocks > (size_t)c->sm_count * 16) blocks = (size_t)c->sm_count * 16;
+                scatter_phase_kernel<<<(unsigned)blocks, 256, 0, stream>>>(Sp, pl.out, s->N, A, Bw, s->IC, s->sh, s->sw, s->IH, s->IW);
+                note_launch("dx_patch");
+                rc = check_launch("scatter_phase_kernel");
+                if (rc) return rc;
+                continue;
+            }
             rc = launch_halo(c, pl, mode3x, stream);
             if (rc == 1) return fail(ALPHA_E_ARG, "strided deltaX: phase (%d,%d) does not fit the halo kernel", py, px);
             if (rc) return rc;

@@ -189,6 +189,26 @@ __global__ void __launch_bounds__(256) unpad_rows_kernel(const float* __restrict
     }
 }
 
+// dst[n][sh*a + py][sw*b + px][:] = src[(n*A + a)*B + b][:]: one stride phase of deltaX, computed
+// densely, placed on its pixels.  dst already points at pixel (py, px) of image 0.
+__global__ void __launch_bounds__(256) scatter_phase_kernel(const float* __restrict__ src, float* __restrict__ dst, int N, int A,
+                                                            int B, int C, int sh, int sw, int IH, int IW)
+{
+    const int c4n = C >> 2;
+    const size_t total = static_cast<size_t>(N) * A * B * c4n;
+    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const size_t m = i / c4n;
+        const int c = static_cast<int>(i - m * c4n) << 2;
+        const int b = static_cast<int>(m % B);
+        const size_t t = m / B;
+        const int a = static_cast<int>(t % A);
+        const size_t n = t / A;
+        *reinterpret_cast<float4*>(dst + ((n * IH + static_cast<size_t>(a) * sh) * IW + static_cast<size_t>(b) * sw) * C + c) =
+            reinterpret_cast<const float4*>(src)[i];
+    }
+}
+
 // hi/lo planes of a whole tensor in global memory (weights are split once per call, not per tile).
 __global__ void split_tensor_kernel(const float4* __restrict__ src, float4* __restrict__ hi, float4* __restrict__ lo, size_t n4)
 {
