@@ -2,6 +2,7 @@
 #include "../../include/alpha_conv_b200.h"
 #include "conv_kernels.cuh"
 #include "conv_halo.cuh"
+#include "conv_halo_pair.cuh"
 #include "conv_dw_halo.cuh"
 #include "winograd.cuh"
 #include "host_common.h"
@@ -484,6 +485,126 @@ static HaloChoice plan_halo(const IgemmPlan& pl, int BN, int mode3x, int b_mn, i
     return best;
 }
 
+// ---- halo kernel on CTA pairs ----------------------------------------------------------------------
+template <int FW_T, bool ROW_T>
+static void halo_pair_launch_one(const HaloLaunch& L)
+{
+    static bool attr_done = false;
+    if (!attr_done) {
+        cudaFuncSetAttribute(conv_halo_pair_kernel<FW_T, ROW_T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        attr_done = true;
+    }
+    conv_halo_pair_kernel<FW_T, ROW_T><<<L.grid, kHaloThreads, L.smem, L.stream>>>(*L.tmA, *L.tmB, *L.tmBlo, *L.tmO, *L.p);
+}
+
+// One 16 x 8 pixel accumulator per CTA, two CTAs per MMA.  Returns 1 when the shape does not fit.
+static int launch_halo_pair(DeviceCtx* c, const IgemmPlan& pl, int mode3x, cudaStream_t stream)
+{
+    if (pl.FW != 3 || pl.sh != 1 || pl.sw != 1 || pl.kdim % 32 != 0 || pl.b_mn) return 1;
+    int BN = ((pl.ncols + 15) / 16) * 16;
+    // wide 3xTF32 needs 2 * BN <= 256 columns per MMA; ALPHA_HALO_PAIR=2 takes three MMAs of BN <= 256 instead
+    const bool three = mode3x && env_int("ALPHA_HALO_PAIR", -1) == 2;
+    const int bn_max = (mode3x && !three) ? 128 : 256;
+    if (BN > bn_max) {
+        if (pl.ncols % bn_max == 0) BN = bn_max;
+        else if (pl.ncols % (bn_max / 2) == 0) BN = bn_max / 2;
+        else return 1;
+    }
+    const int SG = pl.oH + pl.FH - 1;
+    int NI = 1;
+    if (SG <= 16 && env_int("ALPHA_HALO_STACK", 1)) NI = 1 + (16 - pl.oH) / SG;
+    HaloParams p{};
+    p.out = pl.out; p.bias = pl.bias; p.status = c->status; p.prof = c->prof;
+    p.N = pl.aN; p.OH = pl.oH; p.OW = pl.oW;
+    p.Ncols = pl.ncols; p.ldo = pl.ncols;
+    p.FH = pl.FH; p.FW = pl.FW; p.pad_h = pl.pad_h; p.pad_w = pl.pad_w;
+    p.kchunks = pl.kdim / 32;
+    p.BN = BN; p.n_tiles = (pl.ncols + BN - 1) / BN;
+    p.JH = 1; p.JW = 1; p.NI = NI; p.SG = SG;
+    p.PH = NI > 1 ? NI * SG : 16 + pl.FH - 1; p.PW = 8 + pl.FW - 1;
+    if (p.PH > 256) return 1;
+    p.row_blocks = NI > 1 ? 1 : (pl.oH + 15) / 16;
+    p.col_blocks = (pl.oW + 7) / 8;
+    p.n_blocks = (p.N + NI - 1) / NI;
+    const long long per_ntile = (long long)p.n_blocks * p.row_blocks * p.col_blocks;
+    if (per_ntile % 2 != 0) return 1;   // the two tiles of a pair must share their W tiles
+    const long long total = per_ntile * p.n_tiles;
+    if (total > 2147483647LL) return 1;
+    p.total_tiles = (int)total;
+    const bool wide = mode3x != 0 && !three;
+    const uint32_t accw = wide ? 2 * BN : BN;
+    p.acc_bufs = 2 * accw <= 512 ? 2 : 1;
+    p.mode3x = wide ? 2 : (three ? 1 : 0); p.b_mn = 0; p.flip = 0;
+    p.idesc = make_idesc_tf32(256, BN, false, false);
+    p.idesc_wide = make_idesc_tf32(256, wide ? 2 * BN : BN, false, false);
+    p.tmem_cols = pow2_cols(p.acc_bufs * accw);
+    p.patch_tx = (uint32_t)p.PH * p.PW * 128;
+    p.patch_bytes = (p.patch_tx + 1023) & ~1023u;
+    p.b_tx = wide ? (uint32_t)BN * 192 : (three ? (uint32_t)BN * 128 : (uint32_t)BN * 64);   // P + Q, hi + lo halves, or BN/2 rows
+    p.b_bytes = p.b_tx;
+    const uint32_t planes = mode3x ? 2 : 1;
+    const size_t smem_cap = 226 * 1024;
+    bool row = env_int("ALPHA_HALO_ROW", 1) != 0;
+    p.npb = 2;
+    auto need = [&](bool r, int sb) {
+        return (size_t)p.npb * p.patch_bytes * planes + (size_t)sb * p.b_bytes * (r ? pl.FW : 1) + 32768 + 512 + 1024;
+    };
+    if (row && need(true, 2) > smem_cap) row = false;
+    int sb = 2;
+    if (need(row, sb) > smem_cap) return 1;
+    const int max_sb = row ? pl.FH * 2 : 8;
+    while (sb < max_sb && need(row, sb + 1) <= smem_cap) ++sb;
+    p.sb = sb;
+    const size_t smem = need(row, sb);
+
+    CUtensorMap tmA, tmB, tmBlo, tmO;
+    cuuint64_t ad[4] = {(cuuint64_t)pl.aC, (cuuint64_t)pl.aW, (cuuint64_t)pl.aH, (cuuint64_t)pl.aN};
+    cuuint64_t as[3] = {(cuuint64_t)pl.aC * 4, (cuuint64_t)pl.aW * pl.aC * 4, (cuuint64_t)pl.aH * pl.aW * pl.aC * 4};
+    cuuint32_t abox[4] = {32, (cuuint32_t)p.PW, (cuuint32_t)(NI > 1 ? p.SG : p.PH), (cuuint32_t)NI};
+    int rc = make_tiled_map(&tmA, pl.act, 4, ad, as, abox, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    const float* w_hi = pl.W;
+    const float* w_lo = pl.W_lo ? pl.W_lo : pl.W;
+    if (mode3x && !pl.W_lo) {
+        const size_t nW = (size_t)pl.wOC * pl.FH * pl.FW * pl.wIC;
+        float* ws = nullptr;
+        rc = get_workspace(c, stream, 2 * nW * sizeof(float), &ws);
+        if (rc) return rc;
+        const size_t n4 = nW / 4;
+        size_t blocks = (n4 + 255) / 256;
+        if (blocks > (size_t)c->sm_count * 8) blocks = (size_t)c->sm_count * 8;
+        split_tensor_kernel<<<(unsigned)blocks, 256, 0, stream>>>(reinterpret_cast<const float4*>(pl.W),
+                                                                   reinterpret_cast<float4*>(ws),
+                                                                   reinterpret_cast<float4*>(ws + nW), n4);
+        note_launch("split_w");
+        rc = check_launch("split_tensor_kernel");
+        if (rc) return rc;
+        w_hi = ws;
+        w_lo = ws + nW;
+    }
+    cuuint64_t wd[3] = {(cuuint64_t)pl.wIC, (cuuint64_t)pl.FH * pl.FW, (cuuint64_t)pl.wOC};
+    cuuint64_t wst[2] = {(cuuint64_t)pl.wIC * 4, (cuuint64_t)pl.FH * pl.FW * pl.wIC * 4};
+    cuuint32_t box[3] = {32, 1, (cuuint32_t)(BN / 2)};
+    rc = make_tiled_map(&tmB, w_hi, 3, wd, wst, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (!rc) rc = make_tiled_map(&tmBlo, w_lo, 3, wd, wst, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    const int oNH = pl.oNH ? pl.oNH : pl.oH, oNW = pl.oNW ? pl.oNW : pl.oW;
+    cuuint64_t od[4] = {(cuuint64_t)pl.ncols, (cuuint64_t)pl.oW, (cuuint64_t)pl.oH, (cuuint64_t)pl.aN};
+    cuuint64_t ost[3] = {(cuuint64_t)pl.oSW * pl.ncols * 4, (cuuint64_t)pl.oSH * oNW * pl.ncols * 4,
+                         (cuuint64_t)oNH * oNW * pl.ncols * 4};
+    cuuint32_t obox[4] = {32, 8, (cuuint32_t)(NI > 1 ? pl.oH : 16), 1};
+    rc = make_tiled_map(&tmO, pl.out, 4, od, ost, obox, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    int pairs = c->sm_count / 2;
+    if (pairs > p.total_tiles / 2) pairs = p.total_tiles / 2;
+    HaloLaunch L{2 * pairs, smem, stream, &tmA, &tmB, &tmBlo, &tmO, &p};
+    if (row) halo_pair_launch_one<3, true>(L); else halo_pair_launch_one<3, false>(L);
+    note_launch(row ? "halo_pair_row" : "halo_pair_tap");
+    snprintf(g_plan, sizeof(g_plan), "halo_pair%s%s NI=%d BN=%d npb=%d sb=%d acc=%d", row ? "_row" : "_tap", wide ? " wide" : (three ? " three" : ""), NI, BN,
+             p.npb, sb, p.acc_bufs);
+    return check_launch("conv_halo_pair_kernel");
+}
+
 // Returns 1 when the shape is left to the per-tap kernel, 0 on launch, < 0 on error.
 static int launch_halo(DeviceCtx* c, const IgemmPlan& pl_in, int mode3x, cudaStream_t stream)
 {
@@ -491,6 +612,14 @@ static int launch_halo(DeviceCtx* c, const IgemmPlan& pl_in, int mode3x, cudaStr
     if (tile_mode == 1) return 1;
     IgemmPlan pl = pl_in;
     if (pl.sh != 1 || pl.sw != 1 || pl.kdim % 32 != 0) return 1;
+    // CTA pairs: measured faster where one MMA covers 256 output channels (plain TF32, OC % 256 == 0:
+    // 14x14x256 forward 0.111 -> 0.096 ms); elsewhere the single-CTA forms win.  ALPHA_HALO_PAIR = 0
+    // never, 1 always (wide 3xTF32), 2 always (three-MMA 3xTF32).
+    const int pair_env = env_int("ALPHA_HALO_PAIR", -1);
+    if (pair_env > 0 || (pair_env < 0 && !mode3x && pl.ncols % 256 == 0 && tile_mode == 0)) {
+        const int rc2 = launch_halo_pair(c, pl, mode3x, stream);
+        if (rc2 != 1) return rc2;
+    }
     // a 1x1 convolution does not care which pixels are neighbours: seen as one image of 8 columns
     // every 16 x 8 tile is full, whatever the real image size
     const long long flat_m = (long long)pl.aN * pl.aH * pl.aW;
