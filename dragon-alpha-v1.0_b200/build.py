@@ -6,7 +6,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libalpha_conv_b200.so")
 SOURCES = ["conv_api.cu", "native_api.cu", "jni_shim.cpp"]
-HEADERS = ["conv_kernels.cuh", "conv_halo.cuh", "conv_dw_halo.cuh", "winograd.cuh", "sm100_ptx.cuh", "host_common.h"]
+HEADERS = ["conv_kernels.cuh", "conv_halo.cuh", "conv_halo_pair.cuh", "conv_dw_halo.cuh", "winograd.cuh", "sm100_ptx.cuh",
+           "host_common.h"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-shared", "-Xcompiler", "-fPIC"]
 
@@ -26,7 +27,8 @@ def build(force=False, verbose=False):
     if not force and not _stale():
         return LIB
     nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
-    cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-o", LIB] + SOURCES
+    extra = os.environ.get("ALPHA_NVCC_EXTRA", "").split()   # e.g. -D switches for experiments
+    cmd = [nvcc] + NVCC_FLAGS + extra + (["-Xptxas", "-v"] if verbose else []) + ["-o", LIB] + SOURCES
     subprocess.check_call(cmd, cwd=CSRC)
     return LIB
 
