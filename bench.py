@@ -384,6 +384,7 @@ def run_ours(args):
     # per-kernel time from the CUDA events of the timed region; the roofline is reported for the
     # kernel with the largest share, on its longest-running launch shape
     KERNELS = {"halo": "conv_halo_kernel", "halo_row": "conv_halo_kernel", "halo_tap": "conv_halo_kernel",
+               "halo_pair_row": "conv_halo_pair_kernel", "halo_pair_tap": "conv_halo_pair_kernel",
                "igemm": "conv_igemm_kernel", "dw_halo": "conv_dw_halo_kernel", "dw": "conv_dw_kernel",
                "simt": "conv_*_simt"}
     fam, per_op = {}, {}
