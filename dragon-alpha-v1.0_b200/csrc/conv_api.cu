@@ -437,7 +437,7 @@ static HaloChoice plan_halo(const IgemmPlan& pl, int BN, int mode3x, int b_mn, i
             const int PH = NI > 1 ? NI * SG : 16 * JH + pl.FH - 1, PW = 8 * JW + pl.FW - 1;
             if (PH > 256 || PW > 256) continue;
             const uint32_t patch_stride = (((uint32_t)PH * PW * 128 + 1023) & ~1023u) * planes;
-            const bool stat = allow_row && halo_has_row_kernel(pl.FW, JH, JW);  // a static specialisation exists
+            const bool stat = allow_row && !b_mn && halo_has_row_kernel(pl.FW, JH, JW);  // a static specialisation exists (K-major W only)
             bool row = stat;
             uint32_t b_stride = b_tile * (row ? pl.FW : 1);
             if (row && (size_t)patch_stride + 2 * (size_t)b_stride + 32768 + 1536 > smem_cap) { row = false; b_stride = b_tile; }

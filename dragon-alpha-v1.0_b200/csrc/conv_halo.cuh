@@ -105,16 +105,50 @@ struct IssueConsts {
     uint32_t a_dhi, b_dhi, b_kstep, a_lo_off, b_lo_off, idesc, idesc_wide, accw;
 };
 
-// One filter tap into the JH_T x JW_T accumulators of a macro tile, straight-line.
-template <int MODE, int JH_T, int JW_T, uint32_t kPW8>
-__device__ __forceinline__ void issue_tap(uint32_t d0, uint32_t a_tap, uint32_t bl, const IssueConsts& k, uint32_t acc_first)
+// Static specialisations (K-major W tiles only): every descriptor offset is a compile-time constant
+// handed to the MMA wrapper as an immediate, so a stage costs the issuing thread a handful of
+// additions up front and nothing between MMAs.
+//
+// The four K=8 steps of one 32-channel chunk into one accumulator; A_OFF = offset of the tap and
+// accumulator inside the patch (16-byte units).  a / a_lo: hi and lo plane of the patch row,
+// b / b_lo: hi and lo plane of the tap's W tile, d / d_side: main and side accumulator columns.
+template <int MODE, uint32_t A_OFF>
+__device__ __forceinline__ void issue_chunk_imm(uint32_t d, uint32_t d_side, uint32_t a, uint32_t a_lo, uint32_t a_hi, uint32_t b,
+                                                uint32_t b_lo, uint32_t b_hi, uint32_t idesc, uint32_t idesc_wide,
+                                                uint32_t acc_first)
 {
-#pragma unroll
-    for (int jh = 0; jh < JH_T; ++jh)
-#pragma unroll
-        for (int jw = 0; jw < JW_T; ++jw)
-            issue_chunk<MODE>(d0 + (jh * JW_T + jw) * k.accw, a_tap + jh * 16 * kPW8 + jw * 64, k.a_dhi, bl, k.b_dhi, k.b_kstep,
-                              k.a_lo_off, k.b_lo_off, k.idesc, k.idesc_wide, acc_first, k.accw >> 1);
+    static_for<0, 4>([&](auto kk_) {
+        constexpr uint32_t kk = decltype(kk_)::value;
+        const uint32_t acc = kk == 0 ? acc_first : 1u;
+        if constexpr (MODE == 1) {
+            mma_tf32_ss2_imm<A_OFF + kk * 2, kk * 2>(d, a_lo, a_hi, b, b_hi, idesc, acc);
+            mma_tf32_ss2_imm<A_OFF + kk * 2, kk * 2>(d, a, a_hi, b_lo, b_hi, idesc, 1u);
+            mma_tf32_ss2_imm<A_OFF + kk * 2, kk * 2>(d, a, a_hi, b, b_hi, idesc, 1u);
+        } else if constexpr (MODE == 2) {
+            // hi*hi lands in columns [0, BN); both correction terms go to the side columns [BN, 2*BN):
+            // tensor-core accumulation truncates, so every MMA into the main sum costs up to one ulp
+            // of it, while truncation in the side sum is 2^-11 times smaller
+            mma_tf32_ss2_imm<A_OFF + kk * 2, kk * 2>(d, a, a_hi, b, b_hi, idesc_wide, acc);
+            mma_tf32_ss2_imm<A_OFF + kk * 2, kk * 2>(d_side, a_lo, a_hi, b, b_hi, idesc, 1u);
+        } else {
+            mma_tf32_ss2_imm<A_OFF + kk * 2, kk * 2>(d, a, a_hi, b, b_hi, idesc, acc);
+        }
+    });
+}
+
+// One filter tap into the JH_T x JW_T accumulators of a macro tile.  a_row / a_row_lo: descriptor
+// low halves of the patch row of this filter row (hi / lo plane); TAP_OFF = fw * 8.
+template <int MODE, int JH_T, int JW_T, uint32_t kPW8, uint32_t TAP_OFF>
+__device__ __forceinline__ void issue_tap(uint32_t d0, uint32_t a_row, uint32_t a_row_lo, uint32_t bl, const IssueConsts& k,
+                                          uint32_t acc_first)
+{
+    const uint32_t bl_lo = bl + k.b_lo_off;
+    static_for<0, JH_T * JW_T>([&](auto j_) {
+        constexpr uint32_t j = decltype(j_)::value, jh = j / JW_T, jw = j % JW_T;
+        const uint32_t d = d0 + j * k.accw;
+        issue_chunk_imm<MODE, TAP_OFF + jh * 16 * kPW8 + jw * 64>(d, d + (k.accw >> 1), a_row, a_row_lo, k.a_dhi, bl, bl_lo, k.b_dhi,
+                                                                   k.idesc, k.idesc_wide, acc_first);
+    });
 }
 
 // The FW_T taps of one filter row (B stage holds them back to back, b_tile16 apart).
@@ -122,9 +156,11 @@ template <int MODE, int FW_T, int JH_T, int JW_T, uint32_t kPW8>
 __device__ __forceinline__ void issue_row(uint32_t d0, uint32_t a_row, uint32_t bl, uint32_t b_tile16, const IssueConsts& k,
                                           uint32_t acc_first)
 {
-#pragma unroll
-    for (int fw = 0; fw < FW_T; ++fw)
-        issue_tap<MODE, JH_T, JW_T, kPW8>(d0, a_row + fw * 8, bl + fw * b_tile16, k, fw == 0 ? acc_first : 1u);
+    const uint32_t a_row_lo = a_row + k.a_lo_off;
+    static_for<0, FW_T>([&](auto fw_) {
+        constexpr uint32_t fw = decltype(fw_)::value;
+        issue_tap<MODE, JH_T, JW_T, kPW8, fw * 8>(d0, a_row, a_row_lo, bl + fw * b_tile16, k, fw == 0 ? acc_first : 1u);
+    });
 }
 
 // FW_T > 0 selects a specialisation with compile-time FW, JH and JW whose MMAs are issued as
@@ -296,18 +332,20 @@ __global__ void __launch_bounds__(kHaloThreads, 1)
                     } else if constexpr (kStatic) {
                         constexpr uint32_t kPW8 = (8 * JW_T + FW_T - 1) * 8;
                         for (int fh = 0; fh < p.FH && ok; ++fh, a_row += kPW8) {
-#pragma unroll
-                            for (int fw = 0; fw < FW_T; ++fw) {
-                                if (!wait_prof(bwait_a + 8 * bp.idx, bp.phase, prof_on, w_b)) { report(p.status, kStatusMmaTimeout); ok = false; break; }
+                            const uint32_t a_row_lo = a_row + a_lo_off;
+                            static_for<0, FW_T>([&](auto fw_) {
+                                constexpr uint32_t fw = decltype(fw_)::value;
+                                if (!ok) return;
+                                if (!wait_prof(bwait_a + 8 * bp.idx, bp.phase, prof_on, w_b)) { report(p.status, kStatusMmaTimeout); ok = false; return; }
                                 tc_fence_after_sync();
                                 const uint32_t bl = bring_lo0 + bp.idx * b_stride16;
-                                if (p.mode3x == 1) issue_tap<1, JH_T, JW_T, kPW8>(d0, a_row + fw * 8, bl, k, acc_first);
-                                else if (p.mode3x == 2) issue_tap<2, JH_T, JW_T, kPW8>(d0, a_row + fw * 8, bl, k, acc_first);
-                                else issue_tap<0, JH_T, JW_T, kPW8>(d0, a_row + fw * 8, bl, k, acc_first);
+                                if (p.mode3x == 1) issue_tap<1, JH_T, JW_T, kPW8, fw * 8>(d0, a_row, a_row_lo, bl, k, acc_first);
+                                else if (p.mode3x == 2) issue_tap<2, JH_T, JW_T, kPW8, fw * 8>(d0, a_row, a_row_lo, bl, k, acc_first);
+                                else issue_tap<0, JH_T, JW_T, kPW8, fw * 8>(d0, a_row, a_row_lo, bl, k, acc_first);
                                 acc_first = 1u;
                                 mma_commit_a(bempty_a + 8 * bp.idx);
                                 bp.advance(p.sb);
-                            }
+                            });
                         }
                     } else {
                     for (int fh = 0; fh < p.FH && ok; ++fh, a_row += row_step) {

@@ -2,6 +2,7 @@
 // Every wait in this file is bounded: a wait that runs out returns false and the caller leaves the
 // kernel through its error path (status word set, tensor memory freed) instead of spinning forever.
 #pragma once
+#include <type_traits>
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -512,6 +513,38 @@ __device__ __forceinline__ void mma_tf32_ss2(uint32_t d_tmem, uint32_t a_lo, uin
         "}\n" ::"r"(d_tmem),
         "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
         : "memory");
+}
+
+// Same with compile-time offsets (16-byte units) added to the descriptor low halves inside the asm
+// block, so that the address arithmetic of an unrolled stage stays next to its MMA.
+template <uint32_t A_OFF, uint32_t B_OFF>
+__device__ __forceinline__ void mma_tf32_ss2_imm(uint32_t d_tmem, uint32_t a_base, uint32_t a_hi, uint32_t b_base,
+                                                 uint32_t b_hi, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        ".reg .b64 da, db;\n\t"
+        ".reg .b32 ra, rb;\n\t"
+        "add.u32 ra, %1, %7;\n\t"
+        "add.u32 rb, %3, %8;\n\t"
+        "mov.b64 da, {ra, %2};\n\t"
+        "mov.b64 db, {rb, %4};\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], da, db, %5, p;\n\t"
+        "}\n" ::"r"(d_tmem),
+        "r"(a_base), "r"(a_hi), "r"(b_base), "r"(b_hi), "r"(idesc), "r"(accumulate), "n"(A_OFF), "n"(B_OFF)
+        : "memory");
+}
+
+// Compile-time loop: f(std::integral_constant<int, I>) for I in [0, N).
+template <int I, int N, class F>
+__device__ __forceinline__ void static_for(F&& f)
+{
+    if constexpr (I < N) {
+        f(std::integral_constant<int, I>{});
+        static_for<I + 1, N>(f);
+    }
 }
 
 // Arrives on `bar` once every tcgen05.mma issued so far by this thread has completed.
