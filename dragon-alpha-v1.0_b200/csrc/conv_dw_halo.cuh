@@ -26,13 +26,14 @@
 // diagonal quadrants dY_a*X_a and dY_b*X_b are the two partials and the off-diagonal ones are
 // ignored - twice the pixels per MMA where the 128-row operand would be half empty.
 //
-// Warps: 0 TMA producer, 1 MMA issuer, 2-5 operand split (3xTF32) during the loop, epilogue after.
+// Warps: 0 TMA producer, 1 MMA issuer, 2-9 operand split (3xTF32) during the loop, 2-5 epilogue after.
 #pragma once
 #include "conv_halo.cuh"
 
 namespace alpha {
 
-constexpr int kDwHaloThreads = 192;
+constexpr int kDwHaloThreads = 320;   // warp 0 TMA, 1 MMA, 2-9 operand split (3xTF32), 2-5 also epilogue
+constexpr int kDwSplitThreads = 256;
 
 struct DwHaloParams {
     float* out;            // partials [parts][OC][FH*FW][IC] (or deltaW itself when parts == 1)
@@ -120,7 +121,7 @@ __global__ void __launch_bounds__(kDwHaloThreads, 1)
     if (threadIdx.x == 0) {
         for (int s = 0; s < S; ++s) {
             mbar_init(&full[s], 1);
-            mbar_init(&ready[s], 128);
+            mbar_init(&ready[s], kDwSplitThreads);
             mbar_init(&empty[s], 1);
         }
         mbar_init(accum, 1);
@@ -240,8 +241,8 @@ __global__ void __launch_bounds__(kDwHaloThreads, 1)
         }
         __syncwarp();
     } else {
-        // ---- operand split while the loop runs (3xTF32), epilogue afterwards: warps 2..5 ----
-        const int tid128 = threadIdx.x - 64;
+        // ---- operand split while the loop runs (3xTF32): warps 2..9; epilogue afterwards: warps 2..5 ----
+        const int tid128 = threadIdx.x - 64;   // index among the split threads
         bool ok = true;
         if (p.mode3x == 1 || p.mode3x == 2) {
             RingPos rp;
@@ -252,10 +253,10 @@ __global__ void __launch_bounds__(kDwHaloThreads, 1)
                 uint8_t* hi = smem + static_cast<size_t>(rp.idx) * stage_bytes;
                 if (p.debug & 2) {
                 } else if (stacked) {
-                    split_plane_lo_x4(hi, hi + dy_bytes, dy_bytes, tid128, 128);
-                    split_plane_lo_x4(hi + x_off, hi + x_off + x_bytes, x_bytes, tid128, 128);
+                    split_plane_lo_x4(hi, hi + dy_bytes, dy_bytes, tid128, kDwSplitThreads);
+                    split_plane_lo_x4(hi + x_off, hi + x_off + x_bytes, x_bytes, tid128, kDwSplitThreads);
                 } else {
-                    split_plane_lo_x4(hi, hi + plane_bytes, plane_bytes, tid128, 128);
+                    split_plane_lo_x4(hi, hi + plane_bytes, plane_bytes, tid128, kDwSplitThreads);
                 }
                 fence_proxy_async_smem();
                 mbar_arrive_a(ready_a + 8 * rp.idx);
@@ -266,6 +267,7 @@ __global__ void __launch_bounds__(kDwHaloThreads, 1)
                 p.prof[kProfSplitWork] = static_cast<unsigned long long>(clock64() - t_begin) - w_full;
             }
         }
+        if (warp >= 6) ok = false;   // the extra split warps take no part in the epilogue
         if (ok && !mbar_wait(accum, 0)) { report(p.status, kStatusEpilogueTimeout); ok = false; }
         tc_fence_after_sync();
         if (ok) {
