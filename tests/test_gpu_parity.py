@@ -21,6 +21,7 @@ CASES = {
     "ic32_oc64_16x16": (8, 16, 16, 32, 64, 3, 3, 1, 1, 1, 1),
     "ic64_oc64_14x14": (8, 14, 14, 64, 64, 3, 3, 1, 1, 1, 1),
     "ic64_oc128_7x7": (12, 7, 7, 64, 128, 3, 3, 1, 1, 1, 1),
+    "ic64_oc256_14x14": (8, 14, 14, 64, 256, 3, 3, 1, 1, 1, 1),   # plain TF32 takes the CTA-pair kernel here
     "ic8_oc16_9x7": (4, 9, 7, 8, 16, 3, 3, 1, 1, 1, 1),
     "ic32_oc20_ragged": (4, 11, 13, 32, 20, 3, 3, 1, 1, 1, 1),
     "ic96_oc36_5x5": (4, 12, 12, 96, 36, 5, 5, 1, 1, 2, 2),
@@ -229,3 +230,9 @@ def test_cta_pair_kernel(pkg, eng, oracle_mod, pair, mode, monkeypatch):
         for op in ("fwd", "dx"):
             m = res[op]
             assert m["finite"] and m["norm"] <= tol["norm"] and m["comp"] <= tol["comp"], (name, op, res[op + "_algo"], m)
+
+
+def test_pair_kernel_is_chosen_for_256_channel_blocks(pkg, eng, oracle_mod):
+    res, _ = _run_case(pkg, eng, oracle_mod, "ic64_oc256_14x14", "tf32")
+    assert res["fwd_algo"].startswith("halo_pair"), res["fwd_algo"]
+    assert res["fwd"]["norm"] <= TOL["tf32"]["norm"] and res["fwd"]["comp"] <= TOL["tf32"]["comp"], res["fwd"]
