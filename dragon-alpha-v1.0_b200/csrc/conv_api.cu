@@ -952,7 +952,6 @@ static int launch_dw_halo(DeviceCtx* c, const AlphaConvShape* s_in, const float*
     const int oc_tile = stacked ? 64 : 128, dyb = stacked ? 2 : 4, nsub = stacked ? 2 : 1;
     DwHaloParams p{};
     p.status = c->status; p.prof = c->prof;
-    p.debug = env_int("ALPHA_DW_DEBUG", 0);
     p.N = s->N; p.OH = s->OH; p.OW = s->OW;
     p.IC = s->IC; p.OC = s->OC; p.FH = s->FH; p.FW = s->FW; p.ph = s->ph; p.pw = s->pw;
     p.NT = NT; p.ic_tiles = s->IC / NT; p.oc_tiles = (s->OC + oc_tile - 1) / oc_tile;

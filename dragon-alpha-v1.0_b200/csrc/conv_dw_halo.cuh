@@ -54,7 +54,6 @@ struct DwHaloParams {
     uint32_t idesc, tmem_cols;
     uint32_t dy_blk, x_blk;   // bytes of one 32-channel block of the deltaY / X tile (multiples of 1024)
     uint32_t dy_tx, x_tx;     // bytes one block load delivers
-    int debug;                // timing experiments only: 1 no loads, 2 no split, 4 no MMAs (results are wrong)
 };
 
 // The MMAs of one staged pixel tile as straight-line code: all steps of one tap back to back.
@@ -167,7 +166,6 @@ __global__ void __launch_bounds__(kDwHaloThreads, 1)
                 if (!wait_prof(empty_a + 8 * rp.idx, rp.phase ^ 1, prof_on, w_empty)) { report(p.status, kStatusProducerTimeout); break; }
                 const uint32_t bar = full_a + 8 * rp.idx;
                 const uint32_t dst = smem_a + rp.idx * stage_bytes;
-                if (p.debug & 1) { mbar_arrive_a(bar); rp.advance(S); continue; }
                 const int halves = diag ? 2 : 1;
                 mbar_arrive_expect_tx_a(bar, halves * (dyb * p.dy_tx + xb * p.x_tx));
                 const int ow0 = cb * CW;
@@ -201,8 +199,7 @@ __global__ void __launch_bounds__(kDwHaloThreads, 1)
                 tc_fence_after_sync();
                 const long long t_i0 = prof_on ? clock64() : 0;
                 const uint32_t a_s = a_lo0 + rp.idx * stage16, b_s = b_lo0 + rp.idx * stage16;
-                if (p.debug & 4) {
-                } else if constexpr (kStatic) {
+                if constexpr (kStatic) {
                     // the mode test stays outside the unrolled MMAs: a branch per MMA costs the issuing
                     // thread more than the MMA takes
                     if (three) dw_issue_tile<1, FW_T, R_T, CW_T>(tmem_base, acc_cols, a_s, b_s, lo_off, dhi, p.idesc, acc);
@@ -251,8 +248,7 @@ __global__ void __launch_bounds__(kDwHaloThreads, 1)
             for (int t = blockIdx.x; t < p.total_tiles; t += gridDim.x) {
                 if (!wait_prof(full_a + 8 * rp.idx, rp.phase, prof_on, w_full)) { report(p.status, kStatusSplitTimeout); ok = false; break; }
                 uint8_t* hi = smem + static_cast<size_t>(rp.idx) * stage_bytes;
-                if (p.debug & 2) {
-                } else if (stacked) {
+                if (stacked) {
                     split_plane_lo_x4(hi, hi + dy_bytes, dy_bytes, tid128, kDwSplitThreads);
                     split_plane_lo_x4(hi + x_off, hi + x_off + x_bytes, x_bytes, tid128, kDwSplitThreads);
                 } else {
