@@ -56,6 +56,7 @@ def parse_args():
     ap.add_argument("--cpu-sample-batch", type=int, default=2)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="launch every kernel eagerly instead of replaying a CUDA graph of the step")
     ap.add_argument("--only-layer", type=int, default=None, help="profiling aid: run one sweep layer")
     ap.add_argument("--only-op", default=None, choices=list(OPS), help="profiling aid: run one contraction")
     return ap.parse_args()
@@ -318,7 +319,26 @@ def run_ours(args):
         else:
             base.dconv3D_deltaW(L["dW"], 3, 3, L["X"], hw, hw, L["dY"], hw, hw, B, c, c, 1, 1, 1, 1)
 
+    def compute(events=None):
+        for li, L in enumerate(layers):
+            for op in ops:
+                if events is not None:
+                    e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                run_op(L, op)
+                if events is not None:
+                    e1.record()
+                    events.append((li, op, e0, e1, lib.last_algo()))
+
+    def reduce_gradients():
+        if world > 1 and "dw" in ops and os.environ.get("BENCH_AR", "full") != "none":
+            dist.all_reduce(bucket.flat, op=dist.ReduceOp.SUM)
+
     def step(events=None):
+        if os.environ.get("BENCH_AR", "full") not in ("layer", "tiny"):
+            compute(events)
+            reduce_gradients()
+            return
         works = []
         for li, L in enumerate(layers):
             for op in ops:
@@ -352,6 +372,34 @@ def run_ours(args):
     for _ in range(max(args.warmup, 3)):
         step()
     barrier()
+    # The 24 kernel launches of a step are captured once into a CUDA graph and replayed: the tensor
+    # maps and shapes of a training step do not change, and the replay removes the launch gaps
+    # between the 0.1-0.4 ms kernels.  The collective stays outside the graph.
+    graph, launches_per_step, graph_error = None, None, None
+    if not args.no_graph and os.environ.get("BENCH_AR", "full") in ("full", "none"):
+        try:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                compute()
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            gobj = torch.cuda.CUDAGraph()
+            n0 = lib.launch_count()
+            with torch.cuda.graph(gobj, stream=side):
+                compute()
+            launches_per_step = lib.launch_count() - n0
+            for _ in range(3):
+                gobj.replay(); reduce_gradients()
+            torch.cuda.synchronize()
+            if lib.device_status() != 0:
+                raise RuntimeError("kernel status %d after graph replay" % lib.device_status())
+            graph = gobj
+        except Exception as e:  # fall back to eager launches, and say so in the JSON line
+            graph = None
+            graph_error = str(e).splitlines()[0][:200]
+            torch.cuda.synchronize()
+        barrier()
     uuid = None
     try:
         uuid = "GPU-" + str(torch.cuda.get_device_properties(dev).uuid)
@@ -364,12 +412,23 @@ def run_ours(args):
     events = []
     t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
     t0.record()
-    for _ in range(args.steps):
-        step(events)
+    if graph is not None:
+        for _ in range(args.steps):
+            graph.replay()
+            reduce_gradients()
+    else:
+        for _ in range(args.steps):
+            step(events)
     t1.record()
     barrier()
     ms_total = t0.elapsed_time(t1)
-    launches = lib.launch_count() - launches0
+    launches = launches_per_step * args.steps if graph is not None else lib.launch_count() - launches0
+    if graph is not None:
+        # per-op times for the roofline come from a few eager steps outside the timed region
+        step()
+        for _ in range(8):
+            step(events)
+        torch.cuda.synchronize()
     clocks = sampler.stop() if sampler else None
     status = lib.device_status()
     if status != 0:
@@ -446,7 +505,8 @@ def run_ours(args):
                        "batch_per_gpu": B, "global_batch": B * world, "math": args.math,
                        "parallelism": "batch-sharded x%d, deltaW all-reduce" % world if world > 1 else "single GPU",
                        "l2": "inputs larger than L2 (%.2f GB of tensors per step)" % (
-                           sum(4.0 * (2 * L["X"].numel() + 2 * L["Y"].numel() + 2 * L["W"].numel()) for L in layers) / 1e9)},
+                           sum(4.0 * (2 * L["X"].numel() + 2 * L["Y"].numel() + 2 * L["W"].numel()) for L in layers) / 1e9),
+                       "launch": "CUDA graph of the step's kernels, replayed" if graph is not None else "eager launches"},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
             "per_op_tflops": {k: round(v, 1) for k, v in per_op_tflops.items()},
         }
