@@ -56,6 +56,8 @@ def parse_args():
     ap.add_argument("--cpu-sample-batch", type=int, default=2)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--streams", type=int, default=3, choices=[1, 3],
+                    help="3: forward, deltaX and deltaW of a layer go to three streams (graph branches), so the tail of one kernel overlaps the start of another")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel eagerly instead of replaying a CUDA graph of the step")
     ap.add_argument("--only-layer", type=int, default=None, help="profiling aid: run one sweep layer")
     ap.add_argument("--only-op", default=None, choices=list(OPS), help="profiling aid: run one contraction")
@@ -319,7 +321,25 @@ def run_ours(args):
         else:
             base.dconv3D_deltaW(L["dW"], 3, 3, L["X"], hw, hw, L["dY"], hw, hw, B, c, c, 1, 1, 1, 1)
 
+    op_streams = [torch.cuda.Stream() for _ in range(2)] if args.streams == 3 else []
+
     def compute(events=None):
+        if op_streams and events is None and len(ops) == 3:
+            # the three contractions of a layer are independent: one stream each (the library keeps a
+            # workspace per stream).  Every kernel fills the GPU, so only their tails overlap.
+            cur = torch.cuda.current_stream()
+            fork = torch.cuda.Event(); fork.record(cur)
+            for s_ in op_streams:
+                s_.wait_event(fork)
+            for L in layers:
+                run_op(L, "fwd")
+                with torch.cuda.stream(op_streams[0]):
+                    run_op(L, "dx")
+                with torch.cuda.stream(op_streams[1]):
+                    run_op(L, "dw")
+            for s_ in op_streams:
+                cur.wait_stream(s_)
+            return
         for li, L in enumerate(layers):
             for op in ops:
                 if events is not None:
@@ -506,7 +526,8 @@ def run_ours(args):
                        "parallelism": "batch-sharded x%d, deltaW all-reduce" % world if world > 1 else "single GPU",
                        "l2": "inputs larger than L2 (%.2f GB of tensors per step)" % (
                            sum(4.0 * (2 * L["X"].numel() + 2 * L["Y"].numel() + 2 * L["W"].numel()) for L in layers) / 1e9),
-                       "launch": "CUDA graph of the step's kernels, replayed" if graph is not None else "eager launches"},
+                       "launch": ("CUDA graph of the step's kernels, replayed" if graph is not None else "eager launches") +
+                                 (", forward / deltaX / deltaW on three streams" if op_streams else "")},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
             "per_op_tflops": {k: round(v, 1) for k, v in per_op_tflops.items()},
         }
