@@ -445,7 +445,7 @@ def run_ours(args):
     launches = launches_per_step * args.steps if graph is not None else lib.launch_count() - launches0
     if graph is not None:
         # per-op times for the roofline come from a few eager steps outside the timed region
-        step()
+        step([])   # single-stream warm-up: the library keeps one workspace per stream
         for _ in range(8):
             step(events)
         torch.cuda.synchronize()
