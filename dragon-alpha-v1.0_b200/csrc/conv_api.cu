@@ -1017,12 +1017,15 @@ static int launch_dw_halo(DeviceCtx* c, const AlphaConvShape* s_in, const float*
     dim3 grid(parts, groups, 1);
     static bool attr_done = false;
     if (!attr_done) {
-        dw_halo_set_attr<0, 0, 0>(); dw_halo_set_attr<3, 1, 16>(); dw_halo_set_attr<3, 2, 16>(); dw_halo_set_attr<3, 4, 16>();
-        dw_halo_set_attr<3, 8, 16>(); dw_halo_set_attr<3, 2, 8>(); dw_halo_set_attr<3, 4, 8>(); dw_halo_set_attr<3, 8, 8>();
+        dw_halo_set_attr<0, 0, 0>();
+        dw_halo_set_attr<3, 1, 16>(); dw_halo_set_attr<3, 2, 16>(); dw_halo_set_attr<3, 4, 16>(); dw_halo_set_attr<3, 8, 16>();
+        dw_halo_set_attr<3, 2, 8>(); dw_halo_set_attr<3, 4, 8>(); dw_halo_set_attr<3, 8, 8>();
+        dw_halo_set_attr<1, 2, 16>(); dw_halo_set_attr<1, 4, 16>(); dw_halo_set_attr<1, 8, 16>();
         attr_done = true;
     }
 #define DWH_LAUNCH(FW_, R_, CW_) conv_dw_halo_kernel<FW_, R_, CW_><<<grid, kDwHaloThreads, smem, stream>>>(tmX, tmDY, p)
     const bool st = s->FW == 3 && env_int("ALPHA_DW_STATIC", 1) != 0;
+    const bool st1 = s->FW == 1 && CW == 16 && env_int("ALPHA_DW_STATIC", 1) != 0;   // 1x1 (flat 16-column view)
     if (st && R == 1 && CW == 16) DWH_LAUNCH(3, 1, 16);
     else if (st && R == 2 && CW == 16) DWH_LAUNCH(3, 2, 16);
     else if (st && R == 4 && CW == 16) DWH_LAUNCH(3, 4, 16);
@@ -1030,6 +1033,9 @@ static int launch_dw_halo(DeviceCtx* c, const AlphaConvShape* s_in, const float*
     else if (st && R == 2 && CW == 8) DWH_LAUNCH(3, 2, 8);
     else if (st && R == 4 && CW == 8) DWH_LAUNCH(3, 4, 8);
     else if (st && R == 8 && CW == 8) DWH_LAUNCH(3, 8, 8);
+    else if (st1 && R == 2) DWH_LAUNCH(1, 2, 16);
+    else if (st1 && R == 4) DWH_LAUNCH(1, 4, 16);
+    else if (st1 && R == 8) DWH_LAUNCH(1, 8, 16);
     else DWH_LAUNCH(0, 0, 0);
 #undef DWH_LAUNCH
     note_launch("dw_halo");

@@ -84,6 +84,32 @@ __device__ __forceinline__ void dw_issue_tile(uint32_t tmem_base, uint32_t acc_c
     }
 }
 
+// The same with run-time filter width and tile shape (any filter); the math mode stays a template
+// parameter so that no branch sits between two MMAs.
+template <int MODE>
+__device__ __forceinline__ void dw_issue_tile_rt(uint32_t tmem_base, uint32_t acc_cols, uint32_t a_s, uint32_t b_s, uint32_t lo_off,
+                                                 uint32_t dhi, uint32_t idesc, uint32_t acc, int FW, int R, int CW, int PW)
+{
+    uint32_t d = tmem_base, b_tap = b_s;
+    for (int fw = 0; fw < FW; ++fw, b_tap += 8, d += acc_cols) {
+        uint32_t a_row = a_s, b_row = b_tap;
+        uint32_t first = acc;
+        for (int r = 0; r < R; ++r, a_row += CW * 8, b_row += PW * 8) {
+            uint32_t a_k = a_row, b_k = b_row;
+            for (int g = 0; g < CW / 8; ++g, a_k += 64, b_k += 64) {
+                if (MODE == 1) {
+                    mma_tf32_ss2(d, a_k + lo_off, dhi, b_k, dhi, idesc, first);
+                    mma_tf32_ss2(d, a_k, dhi, b_k + lo_off, dhi, idesc, 1u);
+                    mma_tf32_ss2(d, a_k, dhi, b_k, dhi, idesc, 1u);
+                } else {
+                    mma_tf32_ss2(d, a_k, dhi, b_k, dhi, idesc, first);
+                }
+                first = 1u;
+            }
+        }
+    }
+}
+
 // FW_T > 0: FW, R and CW are compile-time and the MMAs of a stage are straight-line code.
 template <int FW_T, int R_T, int CW_T>
 __global__ void __launch_bounds__(kDwHaloThreads, 1)
@@ -205,24 +231,8 @@ __global__ void __launch_bounds__(kDwHaloThreads, 1)
                     if (three) dw_issue_tile<1, FW_T, R_T, CW_T>(tmem_base, acc_cols, a_s, b_s, lo_off, dhi, p.idesc, acc);
                     else dw_issue_tile<0, FW_T, R_T, CW_T>(tmem_base, acc_cols, a_s, b_s, lo_off, dhi, p.idesc, acc);
                 } else {
-                    uint32_t d = tmem_base, b_tap = b_s;
-                    for (int fw = 0; fw < FW; ++fw, b_tap += 8, d += acc_cols) {
-                        uint32_t a_row = a_s, b_row = b_tap;
-                        uint32_t first = acc;
-                        for (int r = 0; r < R; ++r, a_row += CW * 8, b_row += PW * 8) {
-                            uint32_t a_k = a_row, b_k = b_row;
-                            for (int g = 0; g < CW / 8; ++g, a_k += 64, b_k += 64) {
-                                if (three) {
-                                    mma_tf32_ss2(d, a_k + lo_off, dhi, b_k, dhi, p.idesc, first);
-                                    mma_tf32_ss2(d, a_k, dhi, b_k + lo_off, dhi, p.idesc, 1u);
-                                    mma_tf32_ss2(d, a_k, dhi, b_k, dhi, p.idesc, 1u);
-                                } else {
-                                    mma_tf32_ss2(d, a_k, dhi, b_k, dhi, p.idesc, first);
-                                }
-                                first = 1u;
-                            }
-                        }
-                    }
+                    if (three) dw_issue_tile_rt<1>(tmem_base, acc_cols, a_s, b_s, lo_off, dhi, p.idesc, acc, FW, R, CW, PW);
+                    else dw_issue_tile_rt<0>(tmem_base, acc_cols, a_s, b_s, lo_off, dhi, p.idesc, acc, FW, R, CW, PW);
                 }
                 acc = 1u;
                 const long long t_i1 = prof_on ? clock64() : 0;
