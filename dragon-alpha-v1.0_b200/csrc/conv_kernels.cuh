@@ -356,16 +356,18 @@ __global__ void __launch_bounds__(kIgemmThreads)
                 if (!mbar_wait_a(wait_a + 8 * rp.idx, rp.phase)) { report(p.status, kStatusMmaTimeout); break; }
                 tc_fence_after_sync();
                 const uint32_t al = a_lo0 + rp.idx * stage16, bl = b_lo0 + rp.idx * stage16;
-                for (int kk = 0; kk < ksteps; ++kk) {
-                    const uint32_t a_k = al + kk * 2, b_k = bl + kk * b_kstep;
-                    if (p.mode3x) {
+                // the math-mode test stays outside the K steps: a branch between two MMAs costs the
+                // issuing thread about as much as an MMA
+                if (p.mode3x) {
+                    for (int kk = 0; kk < ksteps; ++kk, acc = 1u) {
+                        const uint32_t a_k = al + kk * 2, b_k = bl + kk * b_kstep;
                         mma_tf32_ss2(tmem_base, a_k + a_lo_off, a_dhi, b_k, b_dhi, p.idesc, acc);
                         mma_tf32_ss2(tmem_base, a_k, a_dhi, b_k + b_lo_off, b_dhi, p.idesc, 1u);
                         mma_tf32_ss2(tmem_base, a_k, a_dhi, b_k, b_dhi, p.idesc, 1u);
-                    } else {
-                        mma_tf32_ss2(tmem_base, a_k, a_dhi, b_k, b_dhi, p.idesc, acc);
                     }
-                    acc = 1u;
+                } else {
+                    for (int kk = 0; kk < ksteps; ++kk, acc = 1u)
+                        mma_tf32_ss2(tmem_base, al + kk * 2, a_dhi, bl + kk * b_kstep, b_dhi, p.idesc, acc);
                 }
                 mma_commit_a(empty_a + 8 * rp.idx);
                 rp.advance(S);
@@ -530,31 +532,40 @@ __global__ void __launch_bounds__(kIgemmThreads)
     } else if (warp == 1) {
         if (lane == 0) {
             const uint32_t dhi = smem_desc_hi(512, kSwizzle128B_Base32B);
+            // ring and group positions as counters, barriers and tiles as 32-bit addresses: the issuing
+            // thread does no division, pointer conversion or mode branch between two MMAs
+            const uint32_t wait_a = smem_u32(p.mode3x ? split_done : full), empty_a = smem_u32(empty);
+            const uint32_t smem_a = smem_u32(smem);
+            const uint32_t a_lo_off = a_bytes >> 4, b_lo_off = b_bytes >> 4;
+            const int ksteps = p.KP / 8;
+            RingPos rp;
+            int g = 0;            // accumulator of this iteration
+            uint32_t first = 0u;  // 0 during the first pass over the accumulators
             for (int it = 0; it < num_it; ++it) {
-                const int s = it % S;
-                const uint32_t par = (it / S) & 1;
-                if (!mbar_wait(p.mode3x ? &split_done[s] : &full[s], par)) {
+                if (!mbar_wait_a(wait_a + 8 * rp.idx, rp.phase)) {
                     report(p.status, kStatusMmaTimeout);
                     break;
                 }
                 tc_fence_after_sync();
-                const int ci = it / g_count, g = it - ci * g_count;
                 const uint32_t d = tmem_base + g * p.BN;
-                const uint32_t a_addr = smem_u32(smem + static_cast<size_t>(s) * stage_bytes);
+                const uint32_t a_addr = smem_a + rp.idx * stage_bytes;
                 const uint32_t al = smem_desc_lo(a_addr, blk_bytes);
                 const uint32_t bl = smem_desc_lo(a_addr + a_bytes * planes, blk_bytes);
-                for (int kk = 0; kk < p.KP / 8; ++kk) {
-                    const uint32_t acc = (ci | kk) ? 1u : 0u;
-                    const uint32_t a_k = al + kk * 64, b_k = bl + kk * 64;  // 1024 B per K=8 step
-                    if (p.mode3x) {
-                        mma_tf32_ss2(d, a_k + (a_bytes >> 4), dhi, b_k, dhi, p.idesc, acc);
-                        mma_tf32_ss2(d, a_k, dhi, b_k + (b_bytes >> 4), dhi, p.idesc, 1u);
+                if (p.mode3x) {
+                    for (int kk = 0; kk < ksteps; ++kk) {
+                        const uint32_t acc = kk ? 1u : first;
+                        const uint32_t a_k = al + kk * 64, b_k = bl + kk * 64;  // 1024 B per K=8 step
+                        mma_tf32_ss2(d, a_k + a_lo_off, dhi, b_k, dhi, p.idesc, acc);
+                        mma_tf32_ss2(d, a_k, dhi, b_k + b_lo_off, dhi, p.idesc, 1u);
                         mma_tf32_ss2(d, a_k, dhi, b_k, dhi, p.idesc, 1u);
-                    } else {
-                        mma_tf32_ss2(d, a_k, dhi, b_k, dhi, p.idesc, acc);
                     }
+                } else {
+                    for (int kk = 0; kk < ksteps; ++kk)
+                        mma_tf32_ss2(d, al + kk * 64, dhi, bl + kk * 64, dhi, p.idesc, kk ? 1u : first);
                 }
-                mma_commit(&empty[s]);
+                mma_commit_a(empty_a + 8 * rp.idx);
+                rp.advance(S);
+                if (++g == g_count) { g = 0; first = 1u; }
             }
             mma_commit(accum);
         }
