@@ -887,6 +887,51 @@ static int launch_dx_phases(DeviceCtx* c, const AlphaConvShape* s, const float* 
     return ALPHA_OK;
 }
 
+// ---- deltaX with few input channels (image planes): 1x1 product + col2im ---------------------------
+//
+// With IC = 4 the phase kernels would run MMAs of 16 columns.  Instead P = deltaY x Wt as a 1x1
+// convolution with IC * FH * FW output columns (Wt[ic][tap][oc], what transpose_weights_kernel
+// writes), then every input pixel gathers its taps from P.  Any stride.
+// Returns 1 when the shape is left to the other paths.
+static int launch_dx_col2im(DeviceCtx* c, const AlphaConvShape* s, const float* dY, const float* W, float* dX, int mode3x,
+                            cudaStream_t stream)
+{
+    const int taps = s->FH * s->FW, cols = s->IC * taps;
+    if (s->IC > 8 || s->IC % 4 != 0 || cols > 512 || s->OC % 32 != 0 || taps > 64) return 1;
+    if (!env_int("ALPHA_DX_COL2IM", 1) || env_tile_mode() == 1) return 1;
+    const size_t M = (size_t)s->N * s->OH * s->OW, nW = (size_t)s->OC * cols;
+    float* ws = nullptr;
+    int rc = get_workspace(c, stream, (mode3x ? 2 : 1) * nW * sizeof(float), &ws);
+    if (rc) return rc;
+    float* P = nullptr;
+    rc = get_workspace(c, stream, M * cols * sizeof(float), &P, 1);
+    if (rc) return rc;
+    TapMap map{};
+    map.n = taps;
+    for (int t = 0; t < taps; ++t) map.src[t] = t;
+    dim3 tg((s->IC + 31) / 32, (s->OC + 31) / 32, taps);
+    transpose_weights_kernel<<<tg, 256, 0, stream>>>(W, ws, mode3x ? ws + nW : nullptr, s->OC, s->IC, taps, map, mode3x);
+    note_launch("transpose_w");
+    rc = check_launch("transpose_weights_kernel");
+    if (rc) return rc;
+    IgemmPlan pl{};
+    pl.act = dY; pl.aN = s->N; pl.aH = s->OH; pl.aW = s->OW; pl.aC = s->OC;
+    pl.FH = 1; pl.FW = 1; pl.sh = 1; pl.sw = 1; pl.pad_h = 0; pl.pad_w = 0;
+    pl.out = P; pl.oH = s->OH; pl.oW = s->OW; pl.ncols = cols;
+    pl.W = ws; pl.W_lo = mode3x ? ws + nW : nullptr; pl.wOC = cols; pl.wIC = s->OC; pl.bias = nullptr;
+    pl.b_mn = false; pl.flip = false; pl.kdim = s->OC; pl.force = true;
+    rc = launch_halo(c, pl, mode3x, stream);
+    if (rc == 1) return 1;
+    if (rc) return rc;
+    PatchShape ps{s->N, s->IH, s->IW, s->IC, s->FH, s->FW, s->OH, s->OW, s->sh, s->sw, s->ph, s->pw, 0, 0};
+    const size_t total = (size_t)s->N * s->IH * s->IW * (s->IC / 4);
+    size_t blocks = (total + 255) / 256;
+    if (blocks > (size_t)c->sm_count * 16) blocks = (size_t)c->sm_count * 16;
+    col2im_gather_kernel<<<(unsigned)blocks, 256, 0, stream>>>(P, dX, ps);
+    note_launch("dx_col2im");
+    return check_launch("col2im_gather_kernel");
+}
+
 // ---- deltaW, halo-tile kernel (stride 1): plan and launch -----------------------------------------
 
 template <int FW_T, int R_T, int CW_T>
@@ -1344,6 +1389,8 @@ int alpha_conv3d_deltaX(const AlphaConvShape* s, const float* deltaY, const floa
         return launch_igemm(c, pl, g_math.load() == ALPHA_MATH_3XTF32, stream);
     }
     if (algo != ALPHA_ALGO_SIMT && (s->sh > 1 || s->sw > 1)) {
+        rc = launch_dx_col2im(c, s, deltaY, W, deltaX, g_math.load() == ALPHA_MATH_3XTF32, stream);
+        if (rc != 1) return rc;
         rc = launch_dx_phases(c, s, deltaY, W, deltaX, g_math.load() == ALPHA_MATH_3XTF32, stream);
         if (rc != 1) return rc;
     }

@@ -209,6 +209,37 @@ __global__ void __launch_bounds__(256) scatter_phase_kernel(const float* __restr
     }
 }
 
+// col2im of a deltaX with few input channels: P[(n, oh, ow)][ic * taps + fh * FW + fw] holds the
+// contribution of output pixel (oh, ow) to input pixel (oh*sh - ph + fh, ow*sw - pw + fw); every
+// input pixel gathers its (at most ceil(FH/sh) * ceil(FW/sw)) contributions in a fixed order.
+// One thread per four input channels.
+__global__ void __launch_bounds__(256) col2im_gather_kernel(const float* __restrict__ P, float* __restrict__ dX, const PatchShape s)
+{
+    const int c4n = s.IC >> 2, taps = s.FH * s.FW, ldp = s.IC * taps;
+    const size_t total = static_cast<size_t>(s.N) * s.IH * s.IW * c4n;
+    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const int c0 = static_cast<int>(i % c4n) << 2;
+        size_t t = i / c4n;
+        const int iw = static_cast<int>(t % s.IW); t /= s.IW;
+        const int ih = static_cast<int>(t % s.IH);
+        const size_t n = t / s.IH;
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int fh = (ih + s.ph) % s.sh; fh < s.FH; fh += s.sh) {
+            const int oh = (ih + s.ph - fh) / s.sh;
+            if (ih + s.ph - fh < 0 || oh >= s.OH) continue;
+            for (int fw = (iw + s.pw) % s.sw; fw < s.FW; fw += s.sw) {
+                const int ow = (iw + s.pw - fw) / s.sw;
+                if (iw + s.pw - fw < 0 || ow >= s.OW) continue;
+                const float* row = P + ((n * s.OH + oh) * s.OW + ow) * ldp + fh * s.FW + fw;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) acc[q] += __ldg(row + (c0 + q) * taps);
+            }
+        }
+        *reinterpret_cast<float4*>(dX + i * 4) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    }
+}
+
 // hi/lo planes of a whole tensor in global memory (weights are split once per call, not per tile).
 __global__ void split_tensor_kernel(const float4* __restrict__ src, float4* __restrict__ hi, float4* __restrict__ lo, size_t n4)
 {
