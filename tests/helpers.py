@@ -42,7 +42,7 @@ _REPORT = []
 
 
 def record(entry):
-    """Appends one case to gpurun_out/parity_report.json (diagnostics for a failed run)."""
+    """Appends one case to the parity report written at the end of the run (diagnostics for a failed run)."""
     _REPORT.append(entry)
     out = os.path.join(ROOT, "gpurun_out")
     try:
