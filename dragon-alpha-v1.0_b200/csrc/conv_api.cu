@@ -389,7 +389,7 @@ static void halo_launch_one(const HaloLaunch& L)
         cudaFuncSetAttribute(conv_halo_kernel<FW_T, JH_T, JW_T, ROW_T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         attr_done = true;
     }
-    conv_halo_kernel<FW_T, JH_T, JW_T, ROW_T><<<L.grid, kHaloThreads, L.smem, L.stream>>>(*L.tmA, *L.tmB, *L.tmBlo, *L.tmO, *L.p);
+    conv_halo_kernel<FW_T, JH_T, JW_T, ROW_T><<<L.grid, kHaloThreads2, L.smem, L.stream>>>(*L.tmA, *L.tmB, *L.tmBlo, *L.tmO, *L.p);
 }
 
 template <int FW_T>
@@ -661,6 +661,12 @@ static int launch_halo(DeviceCtx* c, const IgemmPlan& pl_in, int mode3x, cudaStr
     p.total_tiles = (int)total;
     p.npb = ch.npb; p.sb = ch.sb; p.acc_bufs = ch.acc_bufs;
     p.mode3x = ch.wide ? 2 : mode3x; p.b_mn = pl.b_mn; p.flip = pl.flip;
+    // plain TF32 is bound by one thread's MMA issue interval, not by the tensor pipe: two issuing
+    // threads alternate over the ring's stages (the ring then needs an even number of slots).
+    // The 3xTF32 forms run N >= 128 per MMA, are pipe-bound and keep one issuer (and with it a
+    // fixed accumulation order).
+    p.dual = (p.mode3x == 0 && p.sb >= 2 && env_int("ALPHA_HALO_DUAL", 1)) ? 1 : 0;
+    if (p.dual) p.sb &= ~1;
     p.idesc = make_idesc_tf32(kBM, BN, false, pl.b_mn);
     p.idesc_wide = make_idesc_tf32(kBM, ch.wide ? 2 * BN : BN, false, pl.b_mn);
     p.tmem_cols = pow2_cols(ch.acc_bufs * ch.JH * ch.JW * BN * (ch.wide ? 2 : 1));
@@ -671,7 +677,7 @@ static int launch_halo(DeviceCtx* c, const IgemmPlan& pl_in, int mode3x, cudaStr
     const uint32_t planes = mode3x ? 2 : 1;
     const int tps = ch.row ? pl.FW : 1;
     const size_t smem = (size_t)p.npb * p.patch_bytes * planes + (size_t)p.sb * p.b_bytes * planes * tps + 32768 +
-                        (3 * p.npb + 3 * p.sb + 5) * 8 + 1024;
+                        (3 * p.npb + 3 * p.sb + 8) * 8 + 1024;
 
     CUtensorMap tmA, tmB;
     cuuint64_t ad[4] = {(cuuint64_t)pl.aC, (cuuint64_t)pl.aW, (cuuint64_t)pl.aH, (cuuint64_t)pl.aN};
@@ -728,8 +734,8 @@ static int launch_halo(DeviceCtx* c, const IgemmPlan& pl_in, int mode3x, cudaStr
     else if (pl.FW == 3) halo_launch_fw<3>(L, ch.JH, ch.JW, ch.row);
     else halo_launch_fw<5>(L, ch.JH, ch.JW, ch.row);
     note_launch(ch.row ? "halo_row" : (ch.stat ? "halo_tap" : "halo"));
-    snprintf(g_plan, sizeof(g_plan), "halo%s%s JH=%d JW=%d NI=%d BN=%d npb=%d sb=%d acc=%d eff=%.2f", ch.row ? "_row" : (ch.stat ? "_tap" : ""),
-             ch.wide ? " wide" : "", ch.JH, ch.JW, ch.NI, BN, ch.npb, ch.sb, ch.acc_bufs, ch.eff);
+    snprintf(g_plan, sizeof(g_plan), "halo%s%s%s JH=%d JW=%d NI=%d BN=%d npb=%d sb=%d acc=%d eff=%.2f", ch.row ? "_row" : (ch.stat ? "_tap" : ""),
+             ch.wide ? " wide" : "", p.dual ? " dual" : "", ch.JH, ch.JW, ch.NI, BN, ch.npb, p.sb, ch.acc_bufs, ch.eff);
     rc = check_launch("conv_halo_kernel");
     return rc;
 }

@@ -17,9 +17,21 @@
 // Accumulators are double-buffered in tensor memory when they fit, so the epilogue of one macro
 // tile overlaps the loads and MMAs of the next.
 //
-// Warps: 0 TMA producer, 1 MMA issuer (owns tensor memory), 2-5 epilogue, 6-9 operand split.
+// Warps: 0 TMA producer, 1 and 10 MMA issuers (1 owns tensor memory), 2-5 epilogue, 6-9 operand split.
 //
-// One thread issues every MMA, and one tcgen05.mma of this shape takes 59-128 clocks, so the issue
+// Two issuers (p.dual): one thread can start a tcgen05.mma only every ~59 clocks and pays the
+// barrier wait, fence and commit of every stage in series with its MMAs.  The W-tile stages of the
+// ring alternate between two issuing threads that accumulate into the same tensor-memory columns
+// (stage s belongs to issuer s & 1; the ring has an even number of slots, so every slot and its
+// barriers always meet the same issuer, in order).  The issuer of a tile's first stage overwrites
+// the accumulator and then releases a "tile started" barrier that the other one waits for before
+// its first MMA of the tile; patch-empty and accumulator-full collect the commits of both.
+// The host turns this on for plain TF32 only (N = 64..128 per MMA, where the issue interval and
+// not the tensor pipe is the bound).  The order in which the two issuers' MMAs reach the pipe
+// depends on timing, so the fp32 accumulation order, and with it the last bits of a TF32 result,
+// can differ between runs; the 3xTF32 forms keep one issuer and a fixed order.
+//
+// One tcgen05.mma of this shape takes 59-128 clocks of its issuing thread, so the issue
 // loop is kept free of divisions, pointer conversions and per-iteration address arithmetic: ring
 // positions are counters, barriers and tiles are 32-bit shared-memory addresses, descriptors are a
 // constant high half plus a low half that only gets small additions.
@@ -28,7 +40,8 @@
 
 namespace alpha {
 
-constexpr int kHaloThreads = 320;
+constexpr int kHaloThreads = 320;    // CTA-pair kernel: warps 0 TMA, 1 MMA, 2-5 epilogue, 6-9 split
+constexpr int kHaloThreads2 = 352;   // single-CTA kernel: one more warp (10) as second MMA issuer
 
 // Slots of the optional cycle counters (clock64 ticks of CTA 0, summed over the launch).
 enum HaloProf {
@@ -55,6 +68,7 @@ struct HaloParams {
     int npb, sb;         // patch buffers, B ring stages
     int acc_bufs;        // 1 or 2 accumulator sets
     int mode3x, b_mn, flip;   // mode3x: 0 plain TF32, 1 three MMAs, 2 wide B
+    int dual;                 // 1: two MMA-issuing threads take alternate W-tile stages (sb is even)
     uint32_t idesc, idesc_wide, tmem_cols;   // idesc_wide: N = 2 * BN
     uint32_t patch_bytes;  // one plane of one patch buffer, multiple of 1024
     uint32_t patch_tx;     // bytes one patch load delivers
@@ -167,7 +181,7 @@ __device__ __forceinline__ void issue_row(uint32_t d0, uint32_t a_row, uint32_t 
 // straight-line code with immediate descriptor offsets; with ROW_T one B stage holds the FW taps of
 // one filter row, otherwise one tap.  FW_T == 0 is the generic form: any filter, one tap per stage.
 template <int FW_T, int JH_T, int JW_T, bool ROW_T>
-__global__ void __launch_bounds__(kHaloThreads, 1)
+__global__ void __launch_bounds__(kHaloThreads2, 1)
     conv_halo_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                      const __grid_constant__ CUtensorMap tmBlo, const __grid_constant__ CUtensorMap tmO,
                      const HaloParams p)
@@ -196,13 +210,14 @@ __global__ void __launch_bounds__(kHaloThreads, 1)
     uint64_t* b_empty = b_ready + p.sb;
     uint64_t* acc_full = b_empty + p.sb;
     uint64_t* acc_empty = acc_full + 2;
-    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    uint64_t* tile_started = acc_empty + 2;
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tile_started + 2);
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < p.npb; ++i) {
             mbar_init(&patch_full[i], 1);
             mbar_init(&patch_ready[i], 128);
-            mbar_init(&patch_empty[i], 1);
+            mbar_init(&patch_empty[i], p.dual ? 2 : 1);
         }
         for (int i = 0; i < p.sb; ++i) {
             mbar_init(&b_full[i], 1);
@@ -210,8 +225,9 @@ __global__ void __launch_bounds__(kHaloThreads, 1)
             mbar_init(&b_empty[i], 1);
         }
         for (int i = 0; i < 2; ++i) {
-            mbar_init(&acc_full[i], 1);
+            mbar_init(&acc_full[i], p.dual ? 2 : 1);
             mbar_init(&acc_empty[i], 128);
+            mbar_init(&tile_started[i], 1);
         }
         fence_barrier_init();
         prefetch_tmap(&tmA);
@@ -285,9 +301,14 @@ __global__ void __launch_bounds__(kHaloThreads, 1)
             if (prof_on) { p.prof[kProfProducerPatchWait] = w_patch; p.prof[kProfProducerBWait] = w_b; }
         }
         __syncwarp();
-    } else if (warp == 1) {
-        if (lane == 0) {
-            // ---- MMA issuer ----
+    } else if (warp == 1 || warp == 10) {
+        if (lane == 0 && (warp == 1 || p.dual)) {
+            // ---- MMA issuer(s) ----
+            const uint32_t which = warp == 1 ? 0u : 1u;
+            const bool dual = p.dual != 0;
+            const bool prof_on = p.prof != nullptr && blockIdx.x == 0 && which == 0;
+            const uint32_t started_a = smem_u32(tile_started);
+            uint32_t sg = 0;   // W-tile stages of this CTA so far; with two issuers stage sg belongs to issuer sg & 1
             RingPos pp, bp, ap;
             bool ok = true;
             unsigned long long w_patch = 0, w_b = 0, w_acc = 0;
@@ -310,7 +331,11 @@ __global__ void __launch_bounds__(kHaloThreads, 1)
                 if (!wait_prof(aempty_a + 8 * ap.idx, ap.phase ^ 1, prof_on, w_acc)) { report(p.status, kStatusMmaTimeout); ok = false; break; }
                 tc_fence_after_sync();
                 const uint32_t d0 = tmem_base + ap.idx * acc_cols;
-                uint32_t acc_first = 0u;  // the very first MMA into each accumulator overwrites it
+                // the issuer of the tile's first stage overwrites the accumulator; the other one must
+                // not touch it before that MMA has been issued
+                const bool owner = !dual || (sg & 1u) == which;
+                uint32_t acc_first = owner ? 0u : 1u;
+                bool announce = dual && owner, must_wait = dual && !owner;
                 for (int c = 0; c < p.kchunks && ok; ++c) {
                     if (!wait_prof(pwait_a + 8 * pp.idx, pp.phase, prof_on, w_patch)) { report(p.status, kStatusMmaTimeout); ok = false; break; }
                     tc_fence_after_sync();
@@ -318,7 +343,13 @@ __global__ void __launch_bounds__(kHaloThreads, 1)
                     if constexpr (kRow) {
                         constexpr uint32_t kPW8 = (8 * JW_T + FW_T - 1) * 8;  // one patch row, in 16-byte units
                         const uint32_t b_tile16 = b_tile >> 4;
-                        for (int fh = 0; fh < p.FH; ++fh, a_row += kPW8) {
+                        for (int fh = 0; fh < p.FH; ++fh, a_row += kPW8, bp.advance(p.sb)) {
+                            if (dual && ((sg++) & 1u) != which) continue;   // the other issuer's stage
+                            if (must_wait) {
+                                if (!mbar_wait_a(started_a + 8 * ap.idx, ap.phase)) { report(p.status, kStatusMmaTimeout); ok = false; break; }
+                                must_wait = false;
+                                tc_fence_after_sync();
+                            }
                             if (!wait_prof(bwait_a + 8 * bp.idx, bp.phase, prof_on, w_b)) { report(p.status, kStatusMmaTimeout); ok = false; break; }
                             tc_fence_after_sync();
                             const uint32_t bl = bring_lo0 + bp.idx * b_stride16;
@@ -326,8 +357,8 @@ __global__ void __launch_bounds__(kHaloThreads, 1)
                             else if (p.mode3x == 2) issue_row<2, FW_T, JH_T, JW_T, kPW8>(d0, a_row, bl, b_tile16, k, acc_first);
                             else issue_row<0, FW_T, JH_T, JW_T, kPW8>(d0, a_row, bl, b_tile16, k, acc_first);
                             acc_first = 1u;
+                            if (announce) { tc_fence_before_sync(); mbar_arrive_a(started_a + 8 * ap.idx); announce = false; }
                             mma_commit_a(bempty_a + 8 * bp.idx);
-                            bp.advance(p.sb);
                         }
                     } else if constexpr (kStatic) {
                         constexpr uint32_t kPW8 = (8 * JW_T + FW_T - 1) * 8;
@@ -336,21 +367,36 @@ __global__ void __launch_bounds__(kHaloThreads, 1)
                             static_for<0, FW_T>([&](auto fw_) {
                                 constexpr uint32_t fw = decltype(fw_)::value;
                                 if (!ok) return;
-                                if (!wait_prof(bwait_a + 8 * bp.idx, bp.phase, prof_on, w_b)) { report(p.status, kStatusMmaTimeout); ok = false; return; }
-                                tc_fence_after_sync();
-                                const uint32_t bl = bring_lo0 + bp.idx * b_stride16;
-                                if (p.mode3x == 1) issue_tap<1, JH_T, JW_T, kPW8, fw * 8>(d0, a_row, a_row_lo, bl, k, acc_first);
-                                else if (p.mode3x == 2) issue_tap<2, JH_T, JW_T, kPW8, fw * 8>(d0, a_row, a_row_lo, bl, k, acc_first);
-                                else issue_tap<0, JH_T, JW_T, kPW8, fw * 8>(d0, a_row, a_row_lo, bl, k, acc_first);
-                                acc_first = 1u;
-                                mma_commit_a(bempty_a + 8 * bp.idx);
+                                const bool take = !dual || ((sg++) & 1u) == which;
+                                if (take) {
+                                    if (must_wait) {
+                                        if (!mbar_wait_a(started_a + 8 * ap.idx, ap.phase)) { report(p.status, kStatusMmaTimeout); ok = false; return; }
+                                        must_wait = false;
+                                        tc_fence_after_sync();
+                                    }
+                                    if (!wait_prof(bwait_a + 8 * bp.idx, bp.phase, prof_on, w_b)) { report(p.status, kStatusMmaTimeout); ok = false; return; }
+                                    tc_fence_after_sync();
+                                    const uint32_t bl = bring_lo0 + bp.idx * b_stride16;
+                                    if (p.mode3x == 1) issue_tap<1, JH_T, JW_T, kPW8, fw * 8>(d0, a_row, a_row_lo, bl, k, acc_first);
+                                    else if (p.mode3x == 2) issue_tap<2, JH_T, JW_T, kPW8, fw * 8>(d0, a_row, a_row_lo, bl, k, acc_first);
+                                    else issue_tap<0, JH_T, JW_T, kPW8, fw * 8>(d0, a_row, a_row_lo, bl, k, acc_first);
+                                    acc_first = 1u;
+                                    if (announce) { tc_fence_before_sync(); mbar_arrive_a(started_a + 8 * ap.idx); announce = false; }
+                                    mma_commit_a(bempty_a + 8 * bp.idx);
+                                }
                                 bp.advance(p.sb);
                             });
                         }
                     } else {
                     for (int fh = 0; fh < p.FH && ok; ++fh, a_row += row_step) {
                         uint32_t a_tap = a_row;
-                        for (int fw = 0; fw < p.FW; ++fw, a_tap += 8) {
+                        for (int fw = 0; fw < p.FW; ++fw, a_tap += 8, bp.advance(p.sb)) {
+                            if (dual && ((sg++) & 1u) != which) continue;   // the other issuer's stage
+                            if (must_wait) {
+                                if (!mbar_wait_a(started_a + 8 * ap.idx, ap.phase)) { report(p.status, kStatusMmaTimeout); ok = false; break; }
+                                must_wait = false;
+                                tc_fence_after_sync();
+                            }
                             if (!wait_prof(bwait_a + 8 * bp.idx, bp.phase, prof_on, w_b)) { report(p.status, kStatusMmaTimeout); ok = false; break; }
                             tc_fence_after_sync();
                             const uint32_t bl = bring_lo0 + bp.idx * b_stride16;
@@ -364,8 +410,8 @@ __global__ void __launch_bounds__(kHaloThreads, 1)
                                 }
                             }
                             acc_first = 1u;
+                            if (announce) { tc_fence_before_sync(); mbar_arrive_a(started_a + 8 * ap.idx); announce = false; }
                             mma_commit_a(bempty_a + 8 * bp.idx);
-                            bp.advance(p.sb);
                         }
                     }
                     }
