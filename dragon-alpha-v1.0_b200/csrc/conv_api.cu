@@ -503,8 +503,11 @@ static int launch_halo_pair(DeviceCtx* c, const IgemmPlan& pl, int mode3x, cudaS
     if (pl.FW != 3 || pl.sh != 1 || pl.sw != 1 || pl.kdim % 32 != 0 || pl.b_mn) return 1;
     int BN = ((pl.ncols + 15) / 16) * 16;
     // wide 3xTF32 needs 2 * BN <= 256 columns per MMA; ALPHA_HALO_PAIR=2 takes three MMAs of BN <= 256 instead
-    const bool three = mode3x && env_int("ALPHA_HALO_PAIR", -1) == 2;
-    const int bn_max = (mode3x && !three) ? 128 : 256;
+    const int pair_env = env_int("ALPHA_HALO_PAIR", -1);
+    const bool three = mode3x && pair_env != 1;
+    // the side-column form of the three-MMA mode needs 2 * BN columns per accumulator, twice
+    const bool side3 = three && pair_env != 2;
+    const int bn_max = (mode3x && !(three && !side3)) ? 128 : 256;
     if (BN > bn_max) {
         if (pl.ncols % bn_max == 0) BN = bn_max;
         else if (pl.ncols % (bn_max / 2) == 0) BN = bn_max / 2;
@@ -532,9 +535,9 @@ static int launch_halo_pair(DeviceCtx* c, const IgemmPlan& pl, int mode3x, cudaS
     if (total > 2147483647LL) return 1;
     p.total_tiles = (int)total;
     const bool wide = mode3x != 0 && !three;
-    const uint32_t accw = wide ? 2 * BN : BN;
+    const uint32_t accw = (wide || side3) ? 2 * BN : BN;
     p.acc_bufs = 2 * accw <= 512 ? 2 : 1;
-    p.mode3x = wide ? 2 : (three ? 1 : 0); p.b_mn = 0; p.flip = 0;
+    p.mode3x = wide ? 2 : (three ? (side3 ? 4 : 1) : 0); p.b_mn = 0; p.flip = 0;
     p.idesc = make_idesc_tf32(256, BN, false, false);
     p.idesc_wide = make_idesc_tf32(256, wide ? 2 * BN : BN, false, false);
     p.tmem_cols = pow2_cols(p.acc_bufs * accw);
@@ -600,7 +603,7 @@ static int launch_halo_pair(DeviceCtx* c, const IgemmPlan& pl, int mode3x, cudaS
     HaloLaunch L{2 * pairs, smem, stream, &tmA, &tmB, &tmBlo, &tmO, &p};
     if (row) halo_pair_launch_one<3, true>(L); else halo_pair_launch_one<3, false>(L);
     note_launch(row ? "halo_pair_row" : "halo_pair_tap");
-    snprintf(g_plan, sizeof(g_plan), "halo_pair%s%s NI=%d BN=%d npb=%d sb=%d acc=%d", row ? "_row" : "_tap", wide ? " wide" : (three ? " three" : ""), NI, BN,
+    snprintf(g_plan, sizeof(g_plan), "halo_pair%s%s NI=%d BN=%d npb=%d sb=%d acc=%d", row ? "_row" : "_tap", wide ? " wide" : (three ? (side3 ? " three+side" : " three") : ""), NI, BN,
              p.npb, sb, p.acc_bufs);
     return check_launch("conv_halo_pair_kernel");
 }
@@ -612,11 +615,17 @@ static int launch_halo(DeviceCtx* c, const IgemmPlan& pl_in, int mode3x, cudaStr
     if (tile_mode == 1) return 1;
     IgemmPlan pl = pl_in;
     if (pl.sh != 1 || pl.sw != 1 || pl.kdim % 32 != 0) return 1;
-    // CTA pairs: measured faster where one MMA covers 256 output channels (plain TF32, OC % 256 == 0:
-    // 14x14x256 forward 0.111 -> 0.096 ms); elsewhere the single-CTA forms win.  ALPHA_HALO_PAIR = 0
-    // never, 1 always (wide 3xTF32), 2 always (three-MMA 3xTF32).
+    // CTA pairs: the single-CTA forms are bound by shared-memory bandwidth once an MMA covers 128 or
+    // more columns (operand reads alone take 128 B/clk at N = 128), and a pair halves the W-tile part
+    // of it.  Measured faster in plain TF32 where one MMA covers 256 output channels (OC % 256 == 0:
+    // 14x14x256 forward 0.111 -> 0.096 ms) and in 3xTF32 with blocks of 128 channels (three MMAs with
+    // side columns: 28x28x128 0.304 -> 0.287 ms, 14x14x256 0.294 -> 0.281 ms); with 64-column MMAs
+    // the single-CTA forms win.  ALPHA_HALO_PAIR = 0
+    // never, 1 always (wide 3xTF32), 2 always (three-MMA 3xTF32, one accumulator), 3 always (three MMAs,
+    // correction terms in side columns).
     const int pair_env = env_int("ALPHA_HALO_PAIR", -1);
-    if (pair_env > 0 || (pair_env < 0 && !mode3x && pl.ncols % 256 == 0 && tile_mode == 0)) {
+    const bool pair_auto = mode3x ? pl.ncols % 128 == 0 : pl.ncols % 256 == 0;
+    if (pair_env > 0 || (pair_env < 0 && pair_auto && tile_mode == 0)) {
         const int rc2 = launch_halo_pair(c, pl, mode3x, stream);
         if (rc2 != 1) return rc2;
     }

@@ -10,7 +10,8 @@
 //
 // W tile of one tap in each CTA (K-major, 128-byte rows, BN = output channels of the block):
 //   plain TF32:  rows [rank * BN/2, (rank+1) * BN/2) of W.                   N = BN
-//   3xTF32:      the CTA's BN/2 rows of W_hi followed by its BN/2 rows of W_lo; three MMAs of N = BN.
+//   3xTF32:      the CTA's BN/2 rows of W_hi followed by its BN/2 rows of W_lo; three MMAs of N = BN,
+//                with BN <= 128 the two correction terms into a second set of BN columns.
 //   wide 3xTF32: region P (BN rows): all of W_hi in the leader, all of W_lo in the peer, so that
 //                x_hi * [W_hi | W_lo] is one MMA of N = 2*BN; region Q (BN/2 rows): the CTA's half
 //                of W_hi for x_lo * W_hi (N = BN), which accumulates in the second BN columns.
@@ -39,6 +40,12 @@ __device__ __forceinline__ void issue_chunk_pair(uint32_t d, uint32_t a_lo, uint
         if (MODE == 2) {
             mma_tf32_pair(d, a_k, a_hi, b_k, b_hi, idesc_wide, acc);
             mma_tf32_pair(d + side_off, a_k + a_lo_off, a_hi, b_k + q_off, b_hi, idesc, 1u);
+        } else if (MODE == 4) {
+            // three products, the two correction terms into the side columns (see conv_halo.cuh: the
+            // tensor core truncates when it accumulates, so only hi x hi goes into the main sum)
+            mma_tf32_pair(d + side_off, a_k + a_lo_off, a_hi, b_k, b_hi, idesc, acc);
+            mma_tf32_pair(d + side_off, a_k, a_hi, b_k + q_off, b_hi, idesc, 1u);
+            mma_tf32_pair(d, a_k, a_hi, b_k, b_hi, idesc, acc);
         } else if (MODE == 1) {
             // three products into one accumulator; q_off = distance from this CTA's W_hi rows to its W_lo rows
             mma_tf32_pair(d, a_k + a_lo_off, a_hi, b_k, b_hi, idesc, acc);
@@ -51,7 +58,7 @@ __device__ __forceinline__ void issue_chunk_pair(uint32_t d, uint32_t a_lo, uint
 }
 
 // FW_T: compile-time filter width; ROW_T: one B stage holds the FW_T taps of a filter row.
-// p.mode3x is 0 (plain TF32), 1 (3xTF32, three MMAs) or 2 (wide 3xTF32); p.JH == p.JW == 1; p.total_tiles is even and the
+// p.mode3x is 0 (plain TF32), 1 (3xTF32, three MMAs), 4 (the same with side columns) or 2 (wide 3xTF32); p.JH == p.JW == 1; p.total_tiles is even and the
 // tiles 2k, 2k+1 lie in the same output-channel block.  p.b_bytes = bytes of one tap's W tile per CTA.
 template <int FW_T, bool ROW_T>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kHaloThreads, 1)
@@ -67,7 +74,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kHaloThreads, 1)
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();
     const bool leader = rank == 0;
-    const bool wide = p.mode3x == 2, three = p.mode3x == 1;
+    const bool wide = p.mode3x == 2, three = p.mode3x == 1 || p.mode3x == 4;
+    const bool side = wide || p.mode3x == 4;   // accumulators are 2 * BN columns, the epilogue adds the halves
     const uint32_t planes = p.mode3x ? 2u : 1u;
     const uint32_t patch_stride = p.patch_bytes * planes;
     const uint32_t b_tile = p.b_bytes;             // one tap, this CTA's share
@@ -200,7 +208,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kHaloThreads, 1)
             const uint32_t patch_lo0 = smem_desc_lo(patches_a, 16), patch_stride16 = patch_stride >> 4;
             const uint32_t bring_lo0 = smem_desc_lo(bring_a, 16), b_stride16 = b_stride >> 4, b_tile16 = b_tile >> 4;
             const uint32_t pwait_a = p.mode3x ? pready_a : pfull_a;
-            const uint32_t accw = wide ? 2u * p.BN : p.BN;
+            const uint32_t accw = side ? 2u * p.BN : p.BN;
             const bool prof_on = p.prof != nullptr && blockIdx.x == 0;
             unsigned long long w_patch = 0, w_b = 0, w_acc = 0;
             const long long t_begin = clock64();
@@ -230,6 +238,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kHaloThreads, 1)
                                 for (int fw = 0; fw < FW_T; ++fw)
                                     issue_chunk_pair<2, kPW8>(d0, a_row + fw * 8, a_dhi, bl + fw * b_tile16, b_dhi, a_lo_off, q_off,
                                                               p.idesc, p.idesc_wide, p.BN, fw == 0 ? acc_first : 1u);
+                            } else if (p.mode3x == 4) {
+#pragma unroll
+                                for (int fw = 0; fw < FW_T; ++fw)
+                                    issue_chunk_pair<4, kPW8>(d0, a_row + fw * 8, a_dhi, bl + fw * b_tile16, b_dhi, a_lo_off, q_off,
+                                                              p.idesc, p.idesc_wide, p.BN, fw == 0 ? acc_first : 1u);
                             } else if (three) {
 #pragma unroll
                                 for (int fw = 0; fw < FW_T; ++fw)
@@ -253,6 +266,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kHaloThreads, 1)
                                 const uint32_t bl = bring_lo0 + bp.idx * b_stride16;
                                 if (wide)
                                     issue_chunk_pair<2, kPW8>(d0, a_row + fw * 8, a_dhi, bl, b_dhi, a_lo_off, q_off, p.idesc,
+                                                              p.idesc_wide, p.BN, acc_first);
+                                else if (p.mode3x == 4)
+                                    issue_chunk_pair<4, kPW8>(d0, a_row + fw * 8, a_dhi, bl, b_dhi, a_lo_off, q_off, p.idesc,
                                                               p.idesc_wide, p.BN, acc_first);
                                 else if (three)
                                     issue_chunk_pair<1, kPW8>(d0, a_row + fw * 8, a_dhi, bl, b_dhi, a_lo_off, q_off, p.idesc,
@@ -289,7 +305,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kHaloThreads, 1)
         const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
         const uint32_t stage_a = smem_u32(staging);
         uint32_t sbuf = 0;
-        const uint32_t accw = wide ? 2u * p.BN : p.BN;
+        const uint32_t accw = side ? 2u * p.BN : p.BN;
         for (int pt = pair_id; pt < pair_tiles; pt += n_pairs) {
             if (!mbar_wait_a(afull_a + 8 * ap.idx, ap.phase)) { report(p.status, kStatusEpilogueTimeout); break; }
             tc_fence_after_sync();
@@ -311,7 +327,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kHaloThreads, 1)
                 uint32_t v[32];
                 tmem_ld_32x32(tcol + c, v);
                 tmem_ld_wait();
-                if (wide) {
+                if (side) {
                     uint32_t w[32];
                     tmem_ld_32x32(tcol + p.BN + c, w);
                     tmem_ld_wait();

@@ -218,10 +218,10 @@ def test_winograd_forward(pkg, eng, oracle_mod, name, mode):
     assert m["finite"] and m["norm"] <= TOL[mode]["norm"] and m["comp"] <= 2 * TOL[mode]["comp"], m
 
 
-@pytest.mark.parametrize("pair,mode", [("1", "tf32"), ("1", "3xtf32"), ("2", "3xtf32")])
+@pytest.mark.parametrize("pair,mode", [("1", "tf32"), ("1", "3xtf32"), ("2", "3xtf32"), ("3", "3xtf32")])
 def test_cta_pair_kernel(pkg, eng, oracle_mod, pair, mode, monkeypatch):
     """The cta_group::2 form of the halo kernel (two CTAs per MMA) in plain TF32, wide 3xTF32 and
-    three-MMA 3xTF32, forced on shapes it would not be chosen for, against the oracle."""
+    three-MMA 3xTF32 (one accumulator, and with the correction terms in side columns), forced on shapes it would not be chosen for, against the oracle."""
     monkeypatch.setenv("ALPHA_HALO_PAIR", pair)
     for name in ("ic64_oc64_14x14", "ic64_oc128_7x7", "ic32_oc64_16x16"):
         res, _ = _run_case(pkg, eng, oracle_mod, name, mode)
