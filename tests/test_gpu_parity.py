@@ -187,6 +187,32 @@ def test_full_size_adjoint_identity(pkg, eng):
     assert torch.equal(Y2, Y * 2)
 
 
+def test_run_to_run_reproducibility(pkg, eng):
+    """3xTF32 results are bit-identical from run to run (one MMA issuer, fixed reduction order). Plain
+    TF32 forward / deltaX alternates W-tile stages between two issuing threads, so its accumulation
+    order depends on timing: equal to a few ulps there."""
+    import torch
+    lib = pkg.submodule("lib")
+    dev = torch.device("cuda:0")
+    gen = torch.Generator(device=dev).manual_seed(23)
+    for (N, HW, Cc) in ((64, 56, 64), (64, 28, 128), (32, 14, 256)):
+        X = torch.randn((N, HW, HW, Cc), device=dev, generator=gen)
+        W = torch.randn((Cc, 3, 3, Cc), device=dev, generator=gen) * 0.05
+        dY = torch.randn((N, HW, HW, Cc), device=dev, generator=gen)
+        for mode in ("3xtf32", "tf32"):
+            lib.set_math_mode(mode)
+            runs = [(eng.conv3D(X, W, 1, 1, 1, 1), eng.dconv3D_deltaX(dY, W, HW, HW, 1, 1, 1, 1),
+                     eng.dconv3D_deltaW(X, dY, 3, 3, 1, 1, 1, 1)) for _ in range(3)]
+            assert lib.device_status() == 0
+            for r in runs[1:]:
+                for a, b in zip(runs[0], r):
+                    if mode == "3xtf32":
+                        assert torch.equal(a, b), (N, HW, Cc, mode)
+                    else:
+                        assert float((a - b).abs().max()) <= 2e-6 * float(a.abs().max()), (N, HW, Cc, mode)
+    lib.set_math_mode("3xtf32")
+
+
 @pytest.mark.parametrize("mode", ["3xtf32", "tf32"])
 @pytest.mark.parametrize("name", ["cfg1_32x32_ic16_oc32", "ic64_oc64_14x14", "ic32_oc20_ragged", "ic64_oc128_7x7", "ic8_oc16_9x7"])
 def test_winograd_forward(pkg, eng, oracle_mod, name, mode):
