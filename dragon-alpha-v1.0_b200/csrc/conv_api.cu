@@ -1306,6 +1306,41 @@ int alpha_conv3d_forward(const AlphaConvShape* s, const float* X, const float* W
     return forward_direct(c, s, X, W, bias, Y, stream, algo);
 }
 
+int alpha_conv_bias_grad(const float* deltaY, long long rows, int OC, float* deltaB, alpha_stream_t stream_)
+{
+    if (!deltaY || !deltaB || rows <= 0 || OC <= 0) return fail(ALPHA_E_ARG, "bias_grad: null pointer or empty matrix");
+    if (OC % 4 != 0) return fail(ALPHA_E_ARG, "bias_grad: OC must be a multiple of 4 (the engine pads channels to 4)");
+    if (((uintptr_t)deltaY & 15) || ((uintptr_t)deltaB & 15)) return fail(ALPHA_E_ARG, "bias_grad: pointers must be 16-byte aligned");
+    DeviceCtx* c;
+    int rc = get_ctx(&c);
+    if (rc) return rc;
+    cudaStream_t stream = (cudaStream_t)stream_;
+    const int cols4 = OC / 4;
+    // first pass: up to 64 float4 columns (1 KB of a row) per CTA, the rest of the 256 threads as row lanes
+    const int CT = cols4 < 64 ? cols4 : 64;
+    const int RL = kFieldSumThreads / CT;
+    const int gy = (cols4 + CT - 1) / CT;
+    // enough CTAs to keep every SM's memory pipeline full, at least 8 * RL rows each
+    long long gx = ((long long)c->sm_count * 4 + gy - 1) / gy;
+    const long long by_rows = (rows + 8LL * RL - 1) / (8LL * RL);
+    if (gx > by_rows) gx = by_rows;
+    float* ws = nullptr;
+    rc = get_workspace(c, stream, (size_t)gx * OC * sizeof(float), &ws);
+    if (rc) return rc;
+    field_sum_partial_kernel<<<dim3((unsigned)gx, (unsigned)gy), kFieldSumThreads, 0, stream>>>(
+        reinterpret_cast<const float4*>(deltaY), rows, cols4, CT, RL, reinterpret_cast<float4*>(ws));
+    note_launch("field_sum");
+    rc = check_launch("field_sum_partial_kernel");
+    if (rc) return rc;
+    // the gx partial rows are again a matrix whose columns want summing: 16 float4 columns x 16 row lanes per CTA
+    const int CT2 = cols4 < 16 ? cols4 : 16;
+    const int RL2 = kFieldSumThreads / CT2 > 16 ? 16 : kFieldSumThreads / CT2;
+    field_sum_partial_kernel<<<dim3(1, (unsigned)((cols4 + CT2 - 1) / CT2)), kFieldSumThreads, 0, stream>>>(
+        reinterpret_cast<const float4*>(ws), gx, cols4, CT2, RL2, reinterpret_cast<float4*>(deltaB));
+    note_launch("field_sum");
+    return check_launch("field_sum_partial_kernel");
+}
+
 }  // extern "C"
 
 static int forward_direct(DeviceCtx* c, const AlphaConvShape* s, const float* X, const float* W, const float* bias,

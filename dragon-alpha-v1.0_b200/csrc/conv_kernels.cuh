@@ -682,6 +682,51 @@ __global__ void dw_reduce_kernel(const float* __restrict__ part, size_t split_st
     reinterpret_cast<float4*>(out)[i] = s;
 }
 
+// Column sums of a row-major matrix x[rows][cols4 * 4] (the bias gradient: deltaY summed over batch
+// and pixels, Engine.field_sum(deltaY, OC) in nn/unit/simple/Conv3D.java:160).  HBM-bound: every
+// byte is read once, 8 independent 16-byte loads in flight per thread.  CTA (bx, by) owns the rows
+// [rows*bx/Gx, rows*(bx+1)/Gx) of the CT float4 columns starting at by*CT; thread (rl, ct) of
+// RL x CT adds rows rl, rl+RL, ... of its column; the RL row lanes are then added in lane order and
+// the CTA writes its piece of partial row bx.  A second launch sums the partial rows the same way,
+// so the result does not depend on timing.
+constexpr int kFieldSumThreads = 256;
+__global__ void __launch_bounds__(kFieldSumThreads)
+    field_sum_partial_kernel(const float4* __restrict__ x, long long rows, int cols4, int CT, int RL,
+                             float4* __restrict__ partials)
+{
+    __shared__ float4 red[kFieldSumThreads];
+    const int tid = threadIdx.x;
+    const int rl = tid / CT, ct = tid - rl * CT;
+    const int c = blockIdx.y * CT + ct;
+    const bool on = rl < RL && c < cols4;
+    const long long r0 = rows * blockIdx.x / gridDim.x, r1 = rows * (blockIdx.x + 1) / gridDim.x;
+    auto add4 = [](float4& a, const float4& v) { a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w; };
+    float4 acc[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (on) {
+        const float4* col = x + c;
+        long long r = r0 + rl;
+        for (; r + 7LL * RL < r1; r += 8LL * RL) {
+            float4 v[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) v[k] = __ldg(col + (r + static_cast<long long>(k) * RL) * cols4);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) add4(acc[k], v[k]);
+        }
+        for (; r < r1; r += RL) add4(acc[0], __ldg(col + r * cols4));
+        add4(acc[0], acc[1]); add4(acc[2], acc[3]); add4(acc[4], acc[5]); add4(acc[6], acc[7]);
+        add4(acc[0], acc[2]); add4(acc[4], acc[6]); add4(acc[0], acc[4]);
+    }
+    red[tid] = acc[0];
+    __syncthreads();
+    if (rl == 0 && c < cols4) {
+        float4 sum = red[ct];
+        for (int l = 1; l < RL; ++l) add4(sum, red[l * CT + ct]);
+        partials[static_cast<size_t>(blockIdx.x) * cols4 + c] = sum;
+    }
+}
+
 // ---------------------------------------------------------------------------------------------
 // plain fp32 kernels for the shapes the tensor path leaves out
 // ---------------------------------------------------------------------------------------------

@@ -203,6 +203,21 @@ class Engine:
     def conv3D_biased(self, X, W, Bias, sh, sw, ph, pw):
         return self.conv3D(X, W, sh, sw, ph, pw, Bias=Bias)
 
+    def field_sum(self, X, row_length=-1):
+        """Engine.field_sum(X, row_length) (Engine.java:6945): sums the rows of X seen as a matrix of
+        `row_length` columns; Conv3D.__backward__ calls it on deltaY with OC for the bias gradient."""
+        if row_length == -1:
+            row_length = X.shape[-1]
+        if X.shape[-1] != row_length:
+            raise ValueError("field_sum: row_length must be the last dimension")
+        oc4 = _pad4(row_length)
+        Xp = _pad_last(X, oc4).contiguous()
+        out = torch.empty((oc4,), dtype=torch.float32, device=X.device)
+        rows = Xp.numel() // oc4
+        _l.check(self.base._lib.alpha_conv_bias_grad(self.base._addr(Xp), rows, oc4, self.base._addr(out),
+                                                     _stream(self.base._stream)))
+        return out if oc4 == row_length else out[:row_length]
+
     def dconv3D_deltaW(self, X, deltaY, FH, FW, sh, sw, ph, pw):
         N, IH, IW, IC = X.shape
         _, OH, OW, OC = deltaY.shape

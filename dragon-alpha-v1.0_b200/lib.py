@@ -41,6 +41,7 @@ def load():
     lib.alpha_conv3d_forward.argtypes = [P, V, V, V, V, V]
     lib.alpha_conv3d_deltaX.argtypes = [P, V, V, V, V]
     lib.alpha_conv3d_deltaW.argtypes = [P, V, V, V, V]
+    lib.alpha_conv_bias_grad.argtypes = [V, C.c_longlong, I, V, V]
     lib.alpha_engine_conv3D.argtypes = [V, I, I, V, I, I, V, I, I] + [I] * 7 + [V]
     lib.alpha_engine_conv3D_biased.argtypes = [V, I, I, V, I, I, V, I, I, V] + [I] * 7 + [V]
     lib.alpha_engine_dconv3D_deltaW.argtypes = [V, I, I, V, I, I, V, I, I] + [I] * 7 + [V]

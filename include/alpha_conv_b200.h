@@ -99,6 +99,13 @@ int alpha_conv3d_deltaX(const AlphaConvShape* s, const float* deltaY, const floa
 int alpha_conv3d_deltaW(const AlphaConvShape* s, const float* X, const float* deltaY, float* deltaW,
                         alpha_stream_t stream);
 
+/* deltaB[oc] = sum over the `rows` = N*OH*OW rows of deltaY[rows][OC]: the bias gradient of a biased
+ * convolution, Engine.field_sum(deltaY, OC) in the backward pass of nn/unit/simple/Conv3D.java:160
+ * (Engine.java:6945 -> field_linear(X, row_length, 1, 0)).  OC is the padded channel count (a
+ * multiple of 4).  One pass over deltaY at HBM speed plus a fixed-order sum of the per-CTA partial
+ * rows; the result is the same bits on every run. */
+int alpha_conv_bias_grad(const float* deltaY, long long rows, int OC, float* deltaB, alpha_stream_t stream);
+
 /* deltaW for callers that cannot allocate device memory when they call.
  * (No counterpart in the reference: its natives get every buffer, scratch included, from the Java
  * mempool.)  A host such as Dragon-Alpha's engine claims the card's memory for its own pool up front

@@ -122,6 +122,27 @@ def add_bias_row(Y, bias):
     return Y
 
 
+def field_sum(X, row_length=-1):
+    """Column sums of X seen as [rows][row_length], accumulated row after row in float as the
+    reference's CPU loop does (z/util/math/vector/Matrix.java:2119-2127, field_linear with alpha = 1,
+    beta = 0; Engine.field_sum, Engine.java:6945, is the GPU operator Conv3D's backward pass calls
+    for the bias gradient).  No golden vector of the reference covers it: parity unpinned."""
+    X = np.ascontiguousarray(X, np.float32)
+    if row_length == -1:
+        row_length = X.shape[-1]
+    A = X.reshape(-1, row_length)
+    return np.cumsum(A, axis=0, dtype=np.float32)[-1].copy()
+
+
+def field_sum_f64(X, row_length=-1):
+    """The same sums in double, and the sums of magnitudes that scale the error bound."""
+    X = np.ascontiguousarray(X, np.float32)
+    if row_length == -1:
+        row_length = X.shape[-1]
+    A = X.reshape(-1, row_length).astype(np.float64)
+    return A.sum(axis=0), np.abs(A).sum(axis=0)
+
+
 def deconv3D_deltaX_img2col(dY, W, IH, IW, sh, sw, ph, pw, threads=1):
     """Tense.deconv3D_deltaX_img2col (Tense.java:334-375): float accumulator."""
     N, OH, OW, OC = dY.shape

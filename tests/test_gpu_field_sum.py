@@ -1,0 +1,74 @@
+"""Bias gradient (Engine.field_sum of deltaY, nn/unit/simple/Conv3D.java:160) on the GPU against the
+oracle's double-precision column sums, through the C ABI entry point alpha_conv_bias_grad."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def eng(pkg):
+    return pkg.submodule("engine").Engine()
+
+
+# fp32 accumulation in a tree of (rows / CTAs / 64 lanes) levels: far below this bound in practice
+REL = 2e-6
+
+
+@pytest.mark.parametrize("shape", [
+    (1, 1, 1, 4),          # a single row
+    (4, 32, 32, 32),       # the reference's own small test shape
+    (3, 7, 5, 12),         # ragged rows, 3 float4 columns
+    (2, 9, 9, 6),          # channels padded to 8 by the engine layer
+    (5, 3, 3, 1028),       # more float4 columns than threads in a CTA
+    (16, 28, 28, 96),      # row lanes do not divide the CTA (24 float4 columns)
+    (256, 56, 56, 64),     # benchmark size: 205 MB
+])
+def test_field_sum_matches_oracle(pkg, eng, oracle_mod, shape):
+    import torch
+    lib = pkg.submodule("lib")
+    gen = torch.Generator(device="cuda:0").manual_seed(sum(shape))
+    dY = torch.randn(shape, device="cuda:0", generator=gen)
+    got = eng.field_sum(dY, shape[-1]).cpu().numpy()
+    assert lib.device_status() == 0 and got.shape == (shape[-1],)
+    ref, mag = oracle_mod.field_sum_f64(dY.cpu().numpy(), shape[-1])
+    assert np.all(np.abs(got - ref) <= REL * mag + 1e-30), float(np.max(np.abs(got - ref) / (mag + 1e-30)))
+    if dY.numel() <= 1 << 20:
+        # the reference's sequential float loop agrees to its own rounding error
+        seq = oracle_mod.field_sum(dY.cpu().numpy(), shape[-1])
+        assert np.all(np.abs(seq - ref) <= 1e-4 * mag + 1e-30)
+
+
+def test_field_sum_positive_inputs_and_reproducibility(pkg, eng, oracle_mod):
+    """All-positive input (a long sum without cancellation) and bit-identical repeats."""
+    import torch
+    gen = torch.Generator(device="cuda:0").manual_seed(3)
+    dY = torch.rand((64, 56, 56, 64), device="cuda:0", generator=gen)
+    a = eng.field_sum(dY, 64)
+    b = eng.field_sum(dY, 64)
+    assert torch.equal(a, b)
+    ref, mag = oracle_mod.field_sum_f64(dY.cpu().numpy(), 64)
+    assert np.all(np.abs(a.cpu().numpy() - ref) <= REL * mag)
+
+
+def test_bias_grad_of_a_biased_layer(pkg, eng, oracle_mod):
+    """The three gradients of Conv3D.__backward__ (deltaW, deltaB, deltaX) of one biased layer tie together:
+    <Y(X, W, B), dY> = <X, deltaX> + <B, deltaB> = <W, deltaW> + <B, deltaB>."""
+    import torch
+    gen = torch.Generator(device="cuda:0").manual_seed(5)
+    N, HW, IC, OC = 8, 14, 32, 64
+    X = torch.randn((N, HW, HW, IC), device="cuda:0", generator=gen)
+    W = torch.randn((OC, 3, 3, IC), device="cuda:0", generator=gen) * 0.1
+    B = torch.randn((OC,), device="cuda:0", generator=gen)
+    dY = torch.randn((N, HW, HW, OC), device="cuda:0", generator=gen)
+    Y = eng.conv3D_biased(X, W, B, 1, 1, 1, 1)
+    dX = eng.dconv3D_deltaX(dY, W, HW, HW, 1, 1, 1, 1)
+    dW = eng.dconv3D_deltaW(X, dY, 3, 3, 1, 1, 1, 1)
+    dB = eng.field_sum(dY, OC)
+
+    def dot(a, b):
+        return float((a.double() * b.double()).sum())
+    lhs = dot(Y, dY)
+    scale = float(Y.double().norm() * dY.double().norm())
+    assert abs(lhs - (dot(X, dX) + dot(B, dB))) <= 1e-5 * scale
+    assert abs(lhs - (dot(W, dW) + dot(B, dB))) <= 1e-5 * scale

@@ -115,3 +115,20 @@ def test_reference_loops_when_built(golden, oracle_mod):
         assert np.array_equal(O.ref_CONV_3D_NAIVE(X, W, sh, sw, ph, pw), g[name + "/ref_Y"])
         assert np.array_equal(O.ref_deconv3D_deltaX_img2col(dY, W, IH, IW, sh, sw, ph, pw), g[name + "/ref_dX"])
         assert np.array_equal(O.ref_deconv3D_deltaW_img2col2(X, dY, FH, FW, sh, sw, ph, pw), g[name + "/ref_dW"])
+
+
+def test_field_sum_follows_the_reference_loop(oracle_mod):
+    """field_sum restates Matrix.field_linear (alpha = 1, beta = 0): V[j] = sum over rows, in float,
+    row after row."""
+    rng = np.random.default_rng(9)
+    A = rng.standard_normal((37, 12)).astype(np.float32)
+    want = np.zeros(12, np.float32)
+    for j in range(12):
+        v = np.float32(0)
+        for i in range(37):
+            v = np.float32(v + A[i, j])
+        want[j] = v
+    got = oracle_mod.field_sum(A, 12)
+    assert np.array_equal(got, want)
+    d, mag = oracle_mod.field_sum_f64(A, 12)
+    assert np.all(np.abs(d - want) <= 1e-5 * mag)
