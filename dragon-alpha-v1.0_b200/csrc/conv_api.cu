@@ -1332,9 +1332,10 @@ int alpha_conv_bias_grad(const float* deltaY, long long rows, int OC, float* del
     note_launch("field_sum");
     rc = check_launch("field_sum_partial_kernel");
     if (rc) return rc;
-    // the gx partial rows are again a matrix whose columns want summing: 16 float4 columns x 16 row lanes per CTA
-    const int CT2 = cols4 < 16 ? cols4 : 16;
-    const int RL2 = kFieldSumThreads / CT2 > 16 ? 16 : kFieldSumThreads / CT2;
+    // the gx partial rows are again a matrix whose columns want summing: 4 float4 columns x 64 row lanes per CTA
+    // (few rows, so the pass is bound by load latency: many lanes, few loads each)
+    const int CT2 = cols4 < 4 ? cols4 : 4;
+    const int RL2 = 64;
     field_sum_partial_kernel<<<dim3(1, (unsigned)((cols4 + CT2 - 1) / CT2)), kFieldSumThreads, 0, stream>>>(
         reinterpret_cast<const float4*>(ws), gx, cols4, CT2, RL2, reinterpret_cast<float4*>(deltaB));
     note_launch("field_sum");
