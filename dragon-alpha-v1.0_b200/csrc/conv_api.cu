@@ -276,6 +276,7 @@ struct IgemmPlan {
     float* out; int oH, oW, ncols;
     const float* W; int wOC, wIC;   // W[wOC][FH*FW][wIC]
     const float* bias;
+    int act_on = 0; float act_k = 0.f;   // LeakyReLU after the bias (forward only)
     bool b_mn, flip;
     int kdim;                        // reduction channels per tap
     const float* W_lo = nullptr;     // when set, W and W_lo already are the hi and lo TF32 planes
@@ -289,7 +290,7 @@ static int launch_igemm(DeviceCtx* c, const IgemmPlan& pl, int mode3x, cudaStrea
 {
     const int KC = pick_kc(pl.kdim);
     IgemmParams p{};
-    p.out = pl.out; p.bias = pl.bias; p.status = c->status;
+    p.out = pl.out; p.bias = pl.bias; p.act_on = pl.act_on; p.act_k = pl.act_k; p.status = c->status;
     p.M_total = pl.aN * pl.oH * pl.oW;
     p.Ncols = pl.ncols; p.ldo = pl.ncols;
     p.OHo = pl.oH; p.OWo = pl.oW;
@@ -517,7 +518,7 @@ static int launch_halo_pair(DeviceCtx* c, const IgemmPlan& pl, int mode3x, cudaS
     int NI = 1;
     if (SG <= 16 && env_int("ALPHA_HALO_STACK", 1)) NI = 1 + (16 - pl.oH) / SG;
     HaloParams p{};
-    p.out = pl.out; p.bias = pl.bias; p.status = c->status; p.prof = c->prof;
+    p.out = pl.out; p.bias = pl.bias; p.act_on = pl.act_on; p.act_k = pl.act_k; p.status = c->status; p.prof = c->prof;
     p.N = pl.aN; p.OH = pl.oH; p.OW = pl.oW;
     p.Ncols = pl.ncols; p.ldo = pl.ncols;
     p.FH = pl.FH; p.FW = pl.FW; p.pad_h = pl.pad_h; p.pad_w = pl.pad_w;
@@ -653,7 +654,7 @@ static int launch_halo(DeviceCtx* c, const IgemmPlan& pl_in, int mode3x, cudaStr
     if (tile_mode == 0 && ch.eff < 0.6 && !pl.force) return 1;
 
     HaloParams p{};
-    p.out = pl.out; p.bias = pl.bias; p.status = c->status; p.prof = c->prof;
+    p.out = pl.out; p.bias = pl.bias; p.act_on = pl.act_on; p.act_k = pl.act_k; p.status = c->status; p.prof = c->prof;
     p.N = pl.aN; p.OH = pl.oH; p.OW = pl.oW;
     p.Ncols = pl.ncols; p.ldo = pl.ncols;
     p.FH = pl.FH; p.FW = pl.FW; p.pad_h = pl.pad_h; p.pad_w = pl.pad_w;
@@ -1189,7 +1190,7 @@ using namespace alpha;
 // 2|X| + 2|Y| + 4/3|W|) comes from a second per-stream block, because the inner convolutions use
 // the first one for their weight planes.
 static int forward_direct(DeviceCtx* c, const AlphaConvShape* s, const float* X, const float* W, const float* bias,
-                          float* Y, cudaStream_t stream, int algo);
+                          float* Y, cudaStream_t stream, int algo, int act_on = 0, float act_k = 0.f);
 
 static std::map<cudaStream_t, DeviceCtx::Block> g_wino_ws[64];
 
@@ -1342,10 +1343,25 @@ int alpha_conv_bias_grad(const float* deltaY, long long rows, int OC, float* del
     return check_launch("field_sum_partial_kernel");
 }
 
+int alpha_conv3d_forward_leakyRelu(const AlphaConvShape* s, const float* X, const float* W, const float* bias,
+                                   float k, float* Y, alpha_stream_t stream_)
+{
+    int rc = check_shape(s, X, W, Y);
+    if (rc) return rc;
+    if (bias && ((uintptr_t)bias & 15)) return fail(ALPHA_E_ARG, "bias must be 16-byte aligned");
+    if (!(k == k)) return fail(ALPHA_E_ARG, "leakyRelu: slope is NaN");
+    DeviceCtx* c;
+    rc = get_ctx(&c);
+    if (rc) return rc;
+    int algo = g_algo.load();
+    if (algo == ALPHA_ALGO_WINOGRAD) algo = ALPHA_ALGO_AUTO;   // the Winograd output pass has no activation stage
+    return forward_direct(c, s, X, W, bias, Y, (cudaStream_t)stream_, algo, 1, k);
+}
+
 }  // extern "C"
 
 static int forward_direct(DeviceCtx* c, const AlphaConvShape* s, const float* X, const float* W, const float* bias,
-                          float* Y, cudaStream_t stream, int algo)
+                          float* Y, cudaStream_t stream, int algo, int act_on, float act_k)
 {
     int rc;
     const bool tensor_ok = pick_kc(s->IC) != 0 && s->ph < 128 && s->pw < 128 && s->FH <= 256 && s->FW <= 256;
@@ -1356,7 +1372,7 @@ static int forward_direct(DeviceCtx* c, const AlphaConvShape* s, const float* X,
         pl.act = X; pl.aN = s->N; pl.aH = s->IH; pl.aW = s->IW; pl.aC = s->IC;
         pl.FH = s->FH; pl.FW = s->FW; pl.sh = s->sh; pl.sw = s->sw; pl.pad_h = s->ph; pl.pad_w = s->pw;
         pl.out = Y; pl.oH = s->OH; pl.oW = s->OW; pl.ncols = s->OC;
-        pl.W = W; pl.wOC = s->OC; pl.wIC = s->IC; pl.bias = bias;
+        pl.W = W; pl.wOC = s->OC; pl.wIC = s->IC; pl.bias = bias; pl.act_on = act_on; pl.act_k = act_k;
         pl.b_mn = false; pl.flip = false; pl.kdim = s->IC;
         const int mode3x = g_math.load() == ALPHA_MATH_3XTF32;
         if (tiny_image(s->OH, s->OW) && (s->FH > 1 || s->FW > 1) && patch_path_ok(s) && env_tile_mode() != 1) {
@@ -1372,12 +1388,12 @@ static int forward_direct(DeviceCtx* c, const AlphaConvShape* s, const float* X,
         pl.act = X; pl.aN = s->N; pl.aH = s->IH; pl.aW = s->IW; pl.aC = s->IC;
         pl.FH = s->FH; pl.FW = s->FW; pl.sh = s->sh; pl.sw = s->sw; pl.pad_h = s->ph; pl.pad_w = s->pw;
         pl.out = Y; pl.oH = s->OH; pl.oW = s->OW; pl.ncols = s->OC;
-        pl.W = W; pl.wOC = s->OC; pl.wIC = s->IC; pl.bias = bias;
+        pl.W = W; pl.wOC = s->OC; pl.wIC = s->IC; pl.bias = bias; pl.act_on = act_on; pl.act_k = act_k;
         rc = launch_patch_gemm(c, pl, g_math.load() == ALPHA_MATH_3XTF32, stream);
         if (rc != 1) return rc;
     }
     const size_t total = (size_t)s->N * s->OH * s->OW * s->OC;
-    conv_fwd_simt<<<simt_grid(total, c->sm_count), 256, 0, stream>>>(X, W, bias, Y, to_dev_shape(s));
+    conv_fwd_simt<<<simt_grid(total, c->sm_count), 256, 0, stream>>>(X, W, bias, Y, to_dev_shape(s), act_on, act_k);
     note_launch("simt");
     return check_launch("conv_fwd_simt");
 }

@@ -52,6 +52,8 @@ enum HaloProf {
 struct HaloParams {
     float* out;          // [N][OH][OW][ldo]
     const float* bias;   // [Ncols] or nullptr
+    int act_on;          // 1: LeakyReLU with slope act_k after the bias
+    float act_k;
     int* status;
     unsigned long long* prof;  // optional cycle counters of CTA 0 (nullptr = off), see HaloProf
     int N, OH, OW;       // output geometry
@@ -480,6 +482,7 @@ __global__ void __launch_bounds__(kHaloThreads2, 1)
                                 const float4 b = *reinterpret_cast<const float4*>(p.bias + col0 + 4 * q);
                                 o.x += b.x; o.y += b.y; o.z += b.z; o.w += b.w;
                             }
+                            if (p.act_on) leaky_relu4(o, p.act_k);
                             // 128-byte swizzle: 16-byte chunk q of row r lives at chunk q ^ (r & 7)
                             st_shared_v4(srow + ((q ^ (row & 7)) << 4), o);
                         }

@@ -343,6 +343,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kHaloThreads, 1)
                         const float4 b = *reinterpret_cast<const float4*>(p.bias + col0 + 4 * q);
                         o.x += b.x; o.y += b.y; o.z += b.z; o.w += b.w;
                     }
+                    if (p.act_on) leaky_relu4(o, p.act_k);
                     st_shared_v4(srow + ((q ^ (row & 7)) << 4), o);
                 }
                 fence_proxy_async_smem();

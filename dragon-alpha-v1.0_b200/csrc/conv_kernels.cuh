@@ -27,9 +27,19 @@ enum KernelStatus : int {
     kStatusEpilogueTimeout = 4,
 };
 
+// The reference's LeakyReLU, x * ((x > 0) + k * (x < 0)) (Cuda_function/type4_leakyRelu2D.cuh:32);
+// k = 0 is ReLU.  Applied after the bias in the forward epilogues when a plan asks for it.
+__device__ __forceinline__ float leaky_relu(float x, float k) { return x > 0.f ? x : k * x; }
+__device__ __forceinline__ void leaky_relu4(float4& v, float k)
+{
+    v.x = leaky_relu(v.x, k); v.y = leaky_relu(v.y, k); v.z = leaky_relu(v.z, k); v.w = leaky_relu(v.w, k);
+}
+
 struct IgemmParams {
     float* out;         // [M_total][ldo]
     const float* bias;  // [Ncols] or nullptr
+    int act_on;         // 1: LeakyReLU with slope act_k after the bias
+    float act_k;
     int* status;        // device status word, 0 = ok
     int M_total;        // output pixels
     int Ncols;          // output channels
@@ -447,6 +457,7 @@ __global__ void __launch_bounds__(kIgemmThreads)
                                 const float4 b = *reinterpret_cast<const float4*>(p.bias + col);
                                 v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
                             }
+                            if (p.act_on) leaky_relu4(v, p.act_k);
                             *reinterpret_cast<float4*>(orow + col) = v;
                         }
                     }
@@ -737,7 +748,8 @@ struct ConvShape {
 
 // One thread per output element (n, oh, ow, oc); taps in fh -> fw -> ic order.
 __global__ void conv_fwd_simt(const float* __restrict__ X, const float* __restrict__ W,
-                              const float* __restrict__ bias, float* __restrict__ Y, ConvShape s)
+                              const float* __restrict__ bias, float* __restrict__ Y, ConvShape s, int act_on,
+                              float act_k)
 {
     const size_t total = static_cast<size_t>(s.N) * s.OH * s.OW * s.OC;
     for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
@@ -760,6 +772,7 @@ __global__ void conv_fwd_simt(const float* __restrict__ X, const float* __restri
             }
         }
         if (bias) v += bias[oc];
+        if (act_on) v = leaky_relu(v, act_k);
         Y[i] = v;
     }
 }

@@ -203,6 +203,26 @@ class Engine:
     def conv3D_biased(self, X, W, Bias, sh, sw, ph, pw):
         return self.conv3D(X, W, sh, sw, ph, pw, Bias=Bias)
 
+    def conv3D_leakyRelu(self, X, W, Bias, k, sh, sw, ph, pw):
+        """leakyRelu(conv3D(_biased)(X, W[, Bias]), k) with the activation in the kernel's epilogue: what a
+        Conv3D unit followed by a LeakyRelu unit computes (Engine.leakyRelu, Cuda_function's
+        leakyRelu2D); k = 0 is relu."""
+        N, IH, IW, IC = X.shape
+        OC, FH, FW, WIC = W.shape
+        if WIC != IC:
+            raise ValueError("W.IC=%d != X.IC=%d" % (WIC, IC))
+        OH, OW = self.out_size(IH, IW, FH, FW, sh, sw, ph, pw)
+        ic4, oc4 = _pad4(IC), _pad4(OC)
+        Xp = _pad_last(X, ic4)
+        Wp = _pad_first(_pad_last(W, ic4), oc4)
+        Bp = None if Bias is None else _pad_last(Bias.reshape(1, -1), oc4).reshape(-1)
+        Y = torch.empty((N, OH, OW, oc4), dtype=torch.float32, device=X.device)
+        shape = _l.AlphaConvShape(N, IH, IW, ic4, oc4, FH, FW, OH, OW, sh, sw, ph, pw)
+        a = self.base._addr
+        _l.check(self.base._lib.alpha_conv3d_forward_leakyRelu(C.byref(shape), a(Xp), a(Wp), a(Bp) if Bp is not None else None,
+                                                               float(k), a(Y), _stream(self.base._stream)))
+        return Y if oc4 == OC else Y[..., :OC]
+
     def field_sum(self, X, row_length=-1):
         """Engine.field_sum(X, row_length) (Engine.java:6945): sums the rows of X seen as a matrix of
         `row_length` columns; Conv3D.__backward__ calls it on deltaY with OC for the bias gradient."""

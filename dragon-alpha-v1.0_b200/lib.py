@@ -40,6 +40,7 @@ def load():
     P, V, I, L = C.POINTER(AlphaConvShape), C.c_void_p, C.c_int, C.c_int64
     lib.alpha_conv3d_forward.argtypes = [P, V, V, V, V, V]
     lib.alpha_conv3d_deltaX.argtypes = [P, V, V, V, V]
+    lib.alpha_conv3d_forward_leakyRelu.argtypes = [P, V, V, V, C.c_float, V, V]
     lib.alpha_conv3d_deltaW.argtypes = [P, V, V, V, V]
     lib.alpha_conv_bias_grad.argtypes = [V, C.c_longlong, I, V, V]
     lib.alpha_engine_conv3D.argtypes = [V, I, I, V, I, I, V, I, I] + [I] * 7 + [V]

@@ -87,6 +87,14 @@ int alpha_conv_debug_counters(unsigned long long* out, int n);
 int alpha_conv3d_forward(const AlphaConvShape* s, const float* X, const float* W, const float* bias,
                          float* Y, alpha_stream_t stream);
 
+/* Y = leakyRelu(conv(X, W) + bias, k), the activation applied in the epilogue of the same kernel
+ * instead of a second pass over Y: Engine.leakyRelu after conv3D(_biased), i.e. the kernel
+ * src/cu32_src/Cuda_function/Cuda_function/type4_leakyRelu2D.cuh:32-59 (y = x * ((x > 0) + k * (x < 0)));
+ * k = 0 is ReLU.  bias may be NULL.  The backward pass keeps using the reference's own
+ * leakyRelu2D_deltaX on Y before alpha_conv3d_deltaX / deltaW. */
+int alpha_conv3d_forward_leakyRelu(const AlphaConvShape* s, const float* X, const float* W, const float* bias,
+                                   float k, float* Y, alpha_stream_t stream);
+
 /* deltaX = transposed conv of deltaY with W (also Deconv3D's forward).
  * Replaces src/cu32_src/Cuda_dconv3D_deltaX/Cuda_dconv3D_deltaX/dconv3D_dX.cuh:83-1769. */
 int alpha_conv3d_deltaX(const AlphaConvShape* s, const float* deltaY, const float* W, float* deltaX,
