@@ -508,7 +508,11 @@ static int launch_halo_pair(DeviceCtx* c, const IgemmPlan& pl, int mode3x, cudaS
     const bool three = mode3x && pair_env != 1;
     // the side-column form of the three-MMA mode needs 2 * BN columns per accumulator, twice
     const bool side3 = three && pair_env != 2;
-    const int bn_max = (mode3x && !(three && !side3)) ? 128 : 256;
+    // side columns with BN = 256 fill all 512 tensor-memory columns with ONE accumulator set, so the
+    // epilogue no longer overlaps the next tile; that pays once the reduction is long (7x7x512:
+    // 0.320 -> 0.296 ms, half as many patch loads), not before (14x14x256: 0.281 -> 0.314 ms)
+    const bool side_wide = side3 && ((pl.ncols % 256 == 0 && pl.kdim >= 512) || pair_env == 4);
+    const int bn_max = (mode3x && !(three && !side3) && !side_wide) ? 128 : 256;
     if (BN > bn_max) {
         if (pl.ncols % bn_max == 0) BN = bn_max;
         else if (pl.ncols % (bn_max / 2) == 0) BN = bn_max / 2;
