@@ -47,6 +47,14 @@ def test_argument_errors_come_before_any_device_work(lib, pkg):
     assert lib.alpha_conv3d_deltaW(C.byref(s), 16, 32, 48, None) == -1
     assert lib.alpha_conv_set_math_mode(7) == -1
     assert lib.alpha_Cuda_dconv3D_deltaW_buf_summary(0, None, None, 3, 64) == -1
+    # the bias gradient and the fused-activation forward check their arguments the same way
+    assert lib.alpha_conv_bias_grad(None, 16, 8, 32, None) == -1          # null deltaY
+    assert lib.alpha_conv_bias_grad(16, 16, 6, 32, None) == -1            # OC not a multiple of 4
+    assert lib.alpha_conv_bias_grad(16, 0, 8, 32, None) == -1             # no rows
+    assert lib.alpha_conv_bias_grad(20, 16, 8, 32, None) == -1            # misaligned
+    s = L.AlphaConvShape(4, 8, 8, 8, 8, 3, 3, 8, 8, 1, 1, 1, 1)
+    assert lib.alpha_conv3d_forward_leakyRelu(C.byref(s), None, 32, None, 0.1, 48, None) == -1
+    assert lib.alpha_conv3d_forward_leakyRelu(C.byref(s), 16, 32, None, float("nan"), 48, None) == -1
 
 
 def test_no_silent_fallback_without_a_gpu(lib, pkg):
@@ -58,6 +66,8 @@ def test_no_silent_fallback_without_a_gpu(lib, pkg):
     s = L.AlphaConvShape(4, 8, 8, 8, 8, 3, 3, 8, 8, 1, 1, 1, 1)
     rc = lib.alpha_conv3d_forward(C.byref(s), 16, 32, None, 48, None)
     assert rc in (-2, -3)
+    assert lib.alpha_conv_bias_grad(16, 16, 8, 32, None) in (-2, -3)
+    assert lib.alpha_conv3d_forward_leakyRelu(C.byref(s), 16, 32, None, 0.1, 48, None) in (-2, -3)
     with pytest.raises(L.AlphaConvError):
         L.check(rc)
 
