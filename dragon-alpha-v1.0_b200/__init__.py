@@ -7,7 +7,6 @@ benchmark:
 
     lib       ctypes binding of the C ABI
     engine    CudaFloat32EngineBase / Engine operator methods
-    natives   the three JNI classes' static natives and host helpers
     sharding  batch-sharded multi-GPU layer (forward / deltaX local, deltaW all-reduced)
     synth     seeded synthetic inputs for the benchmark configurations
 """

@@ -14,6 +14,8 @@
 #include <cstring>
 #include <map>
 #include <mutex>
+#include <tuple>
+#include <vector>
 
 namespace alpha {
 
@@ -33,11 +35,65 @@ int fail(int code, const char* fmt, ...)
 }
 
 static thread_local char g_plan[128] = "";
+// The calling thread is sizing a call (alpha_conv_workspace_bytes): scratch requests are added up
+// and answered with a placeholder address; nothing is allocated, launched or copied.
+static thread_local bool t_dry = false;
 
 void note_launch(const char* algo)
 {
+    if (t_dry) return;
     g_last_algo = algo;
     g_launches.fetch_add(1, std::memory_order_relaxed);
+}
+
+// ---- tuning options -----------------------------------------------------------------------------
+//
+// Every switch the planners consult lives in one table.  The environment (ALPHA_<NAME>) seeds the
+// table once, at the first call into the library; afterwards alpha_conv_set_option() is the only
+// way to change a value, so no call reads the environment on its way to a launch.
+enum Opt {
+    OPT_CONV_TILE,      // 0 = choose by cost model, 1 = always the per-tap im2col kernel, 2 = halo kernel wherever it applies
+    OPT_CONV_DW,        // 1 = split-K im2col deltaW kernel even where the halo-tile kernel applies
+    OPT_HALO_ROW, OPT_HALO_JH, OPT_HALO_JW, OPT_HALO_STACK, OPT_HALO_WIDE, OPT_HALO_PAIR, OPT_HALO_FLAT,
+    OPT_HALO_NARROW, OPT_HALO_DUAL, OPT_PATCH_MATRIX, OPT_DX_PHASES, OPT_DX_COL2IM, OPT_DX_TRANSPOSE,
+    OPT_DW_STACKED, OPT_DW_DIAG, OPT_DW_CW, OPT_DW_R, OPT_DW_STATIC, OPT_CONV_PROF, OPT_SM_BUDGET,
+    OPT_SKINNY,
+    OPT_COUNT
+};
+struct OptDef { const char* name; int dflt; };
+static const OptDef kOptDefs[OPT_COUNT] = {
+    {"CONV_TILE", 0}, {"CONV_DW", 0},
+    {"HALO_ROW", 1}, {"HALO_JH", 0}, {"HALO_JW", 0}, {"HALO_STACK", 1}, {"HALO_WIDE", -1}, {"HALO_PAIR", -1}, {"HALO_FLAT", 1},
+    {"HALO_NARROW", 1}, {"HALO_DUAL", 1}, {"PATCH_MATRIX", 1}, {"DX_PHASES", 1}, {"DX_COL2IM", 1}, {"DX_TRANSPOSE", 1},
+    {"DW_STACKED", -1}, {"DW_DIAG", 1}, {"DW_CW", 0}, {"DW_R", 0}, {"DW_STATIC", 1}, {"CONV_PROF", 0}, {"SM_BUDGET", 0},
+    {"SKINNY", 1},
+};
+static std::atomic<int> g_opt[OPT_COUNT];
+static std::once_flag g_opt_once;
+
+static int parse_opt(int which, const char* e)
+{
+    if (which == OPT_CONV_TILE) {
+        if (!strcmp(e, "im2col")) return 1;
+        if (!strcmp(e, "halo")) return 2;
+        if (!strcmp(e, "auto")) return 0;
+    }
+    if (which == OPT_CONV_DW && !strcmp(e, "split")) return 1;
+    return atoi(e);
+}
+static void init_opts()
+{
+    for (int i = 0; i < OPT_COUNT; ++i) {
+        char name[64];
+        snprintf(name, sizeof(name), "ALPHA_%s", kOptDefs[i].name);
+        const char* e = getenv(name);
+        g_opt[i].store((e && *e) ? parse_opt(i, e) : kOptDefs[i].dflt);
+    }
+}
+static inline int opt(Opt which)
+{
+    std::call_once(g_opt_once, init_opts);
+    return g_opt[which].load(std::memory_order_relaxed);
 }
 
 static int env_math()
@@ -55,8 +111,19 @@ static int env_algo()
     if (!strcmp(e, "winograd")) return ALPHA_ALGO_WINOGRAD;
     return ALPHA_ALGO_AUTO;
 }
+// Process-wide defaults of the math mode and kernel family, and the per-call values the *_ex entry
+// points put in their place for the calling thread while they run.
 static std::atomic<int> g_math{env_math()};
 static std::atomic<int> g_algo{env_algo()};
+static thread_local int t_math = -1, t_algo = -1;
+static inline int cur_math() { return t_math >= 0 ? t_math : g_math.load(std::memory_order_relaxed); }
+static inline int cur_algo() { return t_algo >= 0 ? t_algo : g_algo.load(std::memory_order_relaxed); }
+static inline int cur_mode3x() { return cur_math() == ALPHA_MATH_3XTF32; }
+struct CallOptions {
+    int save_math, save_algo;
+    CallOptions(int math, int algo) : save_math(t_math), save_algo(t_algo) { if (math >= 0) t_math = math; if (algo >= 0) t_algo = algo; }
+    ~CallOptions() { t_math = save_math; t_algo = save_algo; }
+};
 
 // ---- per-device context ----------------------------------------------------------------------
 
@@ -66,14 +133,30 @@ struct DeviceCtx {
     int cc_major = 0;
     int* status = nullptr;       // device status word
     unsigned long long* prof = nullptr;  // cycle counters, allocated when ALPHA_CONV_PROF=1
-    // Scratch per (device, stream): split-K partials of deltaW and the hi/lo planes of W.  Work on
-    // one stream is ordered, so calls that share a stream can share its block; calls on different
-    // streams get different blocks and may overlap freely.
-    struct Block { float* ptr = nullptr; size_t bytes = 0; };
+    // Scratch per (device, stream), one block each.  Work on one stream is ordered, so calls that
+    // share a stream share its block (every call carves its requests from offset 0 again); calls on
+    // different streams get different blocks and may overlap freely.  A block is library-owned and
+    // grown on demand, or caller-owned (alpha_conv_set_workspace) and then never grown.
+    struct Block {
+        char* base = nullptr; size_t bytes = 0, used = 0;
+        bool external = false;   // the caller's memory
+        bool captured = false;   // handed out while its stream was being captured into a CUDA graph
+    };
     std::map<cudaStream_t, Block> workspace;
-    // second block per stream: the patch matrix of the small-channel paths, which is alive while
-    // the kernels it feeds use the first block
-    std::map<cudaStream_t, Block> workspace2;
+    // Blocks that were outgrown.  Work enqueued earlier may still use one, so it is freed only after
+    // the event recorded at retirement has completed; a block that a graph capture saw is kept until
+    // alpha_conv_release_workspace() because replays of that graph still address it.
+    // The event is recorded at the start of the NEXT call on the stream: the call that outgrew the block
+    // may still enqueue kernels that read what it was given from it.
+    struct Retired { void* ptr; size_t bytes; cudaEvent_t done; bool captured; cudaStream_t stream; };
+    std::vector<Retired> retired;
+    // Weight-side transforms kept across calls (alpha_conv_weight_cache): hi/lo planes, transposes.
+    struct WeightKey {
+        const void* W; int kind, a, b, c, d, e;
+        bool operator<(const WeightKey& o) const { return std::tie(W, kind, a, b, c, d, e) < std::tie(o.W, o.kind, o.a, o.b, o.c, o.d, o.e); }
+    };
+    struct WeightEntry { float* ptr = nullptr; size_t bytes = 0; bool valid = false; cudaEvent_t ready = nullptr; cudaStream_t stream = nullptr; };
+    std::map<WeightKey, WeightEntry> weights;
 };
 static DeviceCtx g_ctx[64];
 static std::mutex g_mu;
@@ -98,6 +181,10 @@ static int load_driver_entry_points()
     return ALPHA_OK;
 }
 
+// SMs the persistent kernels spread over: all of them, or the part alpha_conv_set_option("SM_BUDGET")
+// leaves when some are to stay free for a collective that runs beside the convolutions.
+static inline int sm_budget(const DeviceCtx* c);
+
 int get_ctx(DeviceCtx** out)
 {
     int dev = 0;
@@ -118,7 +205,7 @@ int get_ctx(DeviceCtx** out)
         e = cudaMalloc(&c.status, sizeof(int));
         if (e != cudaSuccess) return fail(ALPHA_E_CUDA, "cudaMalloc(status): %s", cudaGetErrorString(e));
         cudaMemset(c.status, 0, sizeof(int));
-        if (getenv("ALPHA_CONV_PROF") && atoi(getenv("ALPHA_CONV_PROF")) > 0) {
+        if (opt(OPT_CONV_PROF) > 0) {
             if (cudaMalloc(&c.prof, kProfSlots * sizeof(unsigned long long)) == cudaSuccess)
                 cudaMemset(c.prof, 0, kProfSlots * sizeof(unsigned long long));
             else
@@ -135,25 +222,231 @@ int get_ctx(DeviceCtx** out)
     return ALPHA_OK;
 }
 
-// Returns the scratch block of `stream`, grown to at least `bytes`.  Growing waits for the stream
-// to drain first, because work already enqueued on it may still use the old block.
-static int get_workspace(DeviceCtx* c, cudaStream_t stream, size_t bytes, float** out, int slot = 0)
+static inline int sm_budget(const DeviceCtx* c)
 {
-    std::lock_guard<std::mutex> lock(g_mu);
-    DeviceCtx::Block& b = slot ? c->workspace2[stream] : c->workspace[stream];
-    if (b.bytes < bytes) {
-        if (b.ptr) {
-            cudaStreamSynchronize(stream);
-            cudaFree(b.ptr);
-            b.ptr = nullptr;
-            b.bytes = 0;
+    const int b = opt(OPT_SM_BUDGET);
+    return (b > 0 && b < c->sm_count) ? b : c->sm_count;
+}
+
+// ---- scratch memory ----------------------------------------------------------------------------
+//
+// t_caller: scratch the caller of a native handed over for this one call (the CW / deltaW_buf
+// arguments of the reference's JNI signatures); requests that fit are served from it first.
+static thread_local size_t t_dry_cur = 0, t_dry_peak = 0;
+struct CallerScratch { char* ptr = nullptr; size_t bytes = 0, used = 0; };
+static thread_local CallerScratch t_caller;
+
+void set_caller_scratch(void* ptr, size_t bytes)
+{
+    t_caller.ptr = static_cast<char*>(ptr);
+    t_caller.bytes = ptr ? bytes : 0;
+    t_caller.used = 0;
+}
+
+static void sweep_retired(DeviceCtx* c)   // g_mu held
+{
+    for (size_t i = 0; i < c->retired.size();) {
+        DeviceCtx::Retired& r = c->retired[i];
+        if (!r.captured && r.done && cudaEventQuery(r.done) == cudaSuccess) {
+            cudaEventDestroy(r.done);
+            cudaFree(r.ptr);
+            c->retired.erase(c->retired.begin() + i);
+        } else {
+            ++i;
         }
-        const size_t want = bytes + (bytes >> 2);
-        cudaError_t e = cudaMalloc(&b.ptr, want);
-        if (e != cudaSuccess) return fail(ALPHA_E_CUDA, "cudaMalloc(workspace %zu B): %s", want, cudaGetErrorString(e));
-        b.bytes = want;
     }
-    *out = b.ptr;
+    cudaGetLastError();   // cudaEventQuery reports "not ready" through the error state
+}
+
+static bool stream_is_capturing(cudaStream_t stream)
+{
+    cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream, &st) != cudaSuccess) { cudaGetLastError(); return false; }
+    return st != cudaStreamCaptureStatusNone;
+}
+
+// Starts one API call on `stream`: its scratch requests are carved from the start of the block again.
+static void ws_begin(DeviceCtx* c, cudaStream_t stream)
+{
+    if (t_dry) { t_dry_cur = t_dry_peak = 0; return; }
+    std::lock_guard<std::mutex> lock(g_mu);
+    auto it = c->workspace.find(stream);
+    if (it != c->workspace.end()) it->second.used = 0;
+    t_caller.used = 0;
+    for (DeviceCtx::Retired& r : c->retired)
+        if (!r.done && !r.captured && r.stream == stream && !stream_is_capturing(stream) &&
+            cudaEventCreateWithFlags(&r.done, cudaEventDisableTiming) == cudaSuccess)
+            cudaEventRecord(r.done, stream);
+}
+
+static int grow_block(DeviceCtx* c, cudaStream_t stream, DeviceCtx::Block& b, size_t need)   // g_mu held
+{
+    if (b.external)
+        return fail(ALPHA_E_NOSCRATCH, "the workspace given by alpha_conv_set_workspace holds %zu bytes, this call needs %zu "
+                    "(alpha_conv_workspace_bytes tells in advance)", b.bytes, need);
+    if (stream_is_capturing(stream))
+        return fail(ALPHA_E_CAPTURE, "the call needs %zu bytes of scratch, the stream's block holds %zu, and the stream is being "
+                    "captured: run the step once eagerly or call alpha_conv_reserve_workspace before capturing", need, b.bytes);
+    sweep_retired(c);
+    const size_t want = need + (need >> 2);
+    void* p = nullptr;
+    cudaError_t e = cudaMalloc(&p, want);
+    if (e != cudaSuccess) { cudaGetLastError(); return fail(ALPHA_E_CUDA, "cudaMalloc(workspace %zu B): %s", want, cudaGetErrorString(e)); }
+    if (b.base) {
+        c->retired.push_back(DeviceCtx::Retired{b.base, b.bytes, nullptr, b.captured, stream});
+    }
+    b.base = static_cast<char*>(p); b.bytes = want; b.captured = false;
+    return ALPHA_OK;
+}
+
+// `bytes` of scratch for the current call on `stream`, valid until the work enqueued by this call
+// has run.  Requests of one call do not overlap each other.
+static int get_workspace(DeviceCtx* c, cudaStream_t stream, size_t bytes, float** out, int = 0)
+{
+    bytes = (bytes + 255) & ~static_cast<size_t>(255);
+    if (t_dry) {
+        t_dry_cur += bytes;
+        if (t_dry_cur > t_dry_peak) t_dry_peak = t_dry_cur;
+        *out = reinterpret_cast<float*>(static_cast<uintptr_t>(1) << 30);   // aligned placeholder, never dereferenced
+        return ALPHA_OK;
+    }
+    if (t_caller.ptr && t_caller.used + bytes <= t_caller.bytes) {
+        *out = reinterpret_cast<float*>(t_caller.ptr + t_caller.used);
+        t_caller.used += bytes;
+        return ALPHA_OK;
+    }
+    std::lock_guard<std::mutex> lock(g_mu);
+    DeviceCtx::Block& b = c->workspace[stream];
+    if (b.used + bytes > b.bytes) {
+        int rc = grow_block(c, stream, b, b.used + bytes);
+        if (rc) return rc;
+    }
+    if (!b.captured && !b.external && stream_is_capturing(stream)) b.captured = true;
+    *out = reinterpret_cast<float*>(b.base + b.used);
+    b.used += bytes;
+    return ALPHA_OK;
+}
+
+// A loop whose iterations each need scratch that is dead once the iteration's kernels have been
+// enqueued (they all run on one stream, in order) takes a mark before the loop body and rewinds to
+// it afterwards, so that the iterations reuse the same bytes.
+struct WsMark { size_t block_used, caller_used, dry_cur; };
+static WsMark ws_mark(DeviceCtx* c, cudaStream_t stream)
+{
+    WsMark m{0, t_caller.used, t_dry_cur};
+    if (!t_dry) {
+        std::lock_guard<std::mutex> lock(g_mu);
+        auto it = c->workspace.find(stream);
+        if (it != c->workspace.end()) m.block_used = it->second.used;
+    }
+    return m;
+}
+static void ws_rewind(DeviceCtx* c, cudaStream_t stream, const WsMark& m)
+{
+    t_caller.used = m.caller_used;
+    t_dry_cur = m.dry_cur;
+    if (t_dry) return;
+    std::lock_guard<std::mutex> lock(g_mu);
+    auto it = c->workspace.find(stream);
+    if (it != c->workspace.end()) it->second.used = m.block_used;
+}
+
+static int check_launch(const char* what);
+
+// ---- weight-side transforms --------------------------------------------------------------------
+//
+// The forward kernels in 3xTF32 need the lo plane of W, deltaX needs W transposed (and rotated, or cut
+// into stride phases) in hi and lo planes.  Weights change only when the optimizer updates them
+// (the reference's contract: Tensor.java:208-221, Engine.java:341-350), so with the weight cache on
+// (alpha_conv_weight_cache) a transform is computed once and kept in library-owned memory until
+// alpha_conv_weights_updated() names its source tensor; with the cache off it is recomputed by
+// every call into that call's scratch.
+enum { WK_FWD_LO = 1, WK_DX_S1 = 2, WK_DX_PHASES = 3, WK_DX_COL2IM = 4 };
+static std::atomic<int> g_weight_cache{0};
+
+// A forward native that was handed the caller's CW block finds the lo plane kernel_remode left there.
+struct PreparedLo { const float* W = nullptr; const float* lo = nullptr; };
+static thread_local PreparedLo t_prepared_lo;
+void set_prepared_lo(const float* W, const float* lo) { t_prepared_lo.W = W; t_prepared_lo.lo = lo; }
+
+// Memory for one transform of `bytes`; *fresh says whether the caller still has to compute it (then
+// it calls weight_planes_ready after enqueuing the kernels that do).
+static int weight_planes(DeviceCtx* c, cudaStream_t stream, const DeviceCtx::WeightKey& key, size_t bytes, float** out, bool* fresh)
+{
+    *fresh = true;
+    if (t_dry || !g_weight_cache.load(std::memory_order_relaxed)) return get_workspace(c, stream, bytes, out);
+    std::lock_guard<std::mutex> lock(g_mu);
+    DeviceCtx::WeightEntry& e = c->weights[key];
+    if (e.valid && e.bytes >= bytes) {
+        // computed by an earlier call; a different stream waits for the kernels that wrote it
+        if (e.stream != stream && e.ready && cudaEventQuery(e.ready) != cudaSuccess) {
+            cudaGetLastError();
+            cudaStreamWaitEvent(stream, e.ready, 0);
+        }
+        *out = e.ptr; *fresh = false;
+        return ALPHA_OK;
+    }
+    if (e.bytes < bytes) {
+        if (stream_is_capturing(stream))
+            return fail(ALPHA_E_CAPTURE, "the weight cache has no entry for this tensor yet and the stream is being captured: "
+                        "run the layer once eagerly before capturing");
+        if (e.ptr) c->retired.push_back(DeviceCtx::Retired{e.ptr, e.bytes, nullptr, false, e.stream});
+        void* p = nullptr;
+        cudaError_t err = cudaMalloc(&p, bytes);
+        if (err != cudaSuccess) { cudaGetLastError(); e = DeviceCtx::WeightEntry{}; return fail(ALPHA_E_CUDA, "cudaMalloc(weight cache %zu B): %s", bytes, cudaGetErrorString(err)); }
+        e.ptr = static_cast<float*>(p); e.bytes = bytes;
+    }
+    e.valid = false; e.stream = stream;
+    *out = e.ptr;
+    return ALPHA_OK;
+}
+static void weight_planes_ready(DeviceCtx* c, cudaStream_t stream, const DeviceCtx::WeightKey& key)
+{
+    if (t_dry || !g_weight_cache.load(std::memory_order_relaxed)) return;
+    std::lock_guard<std::mutex> lock(g_mu);
+    auto it = c->weights.find(key);
+    if (it == c->weights.end()) return;
+    DeviceCtx::WeightEntry& e = it->second;
+    if (!e.ready && cudaEventCreateWithFlags(&e.ready, cudaEventDisableTiming) != cudaSuccess) { cudaGetLastError(); e.ready = nullptr; }
+    if (e.ready && !stream_is_capturing(stream)) cudaEventRecord(e.ready, stream);
+    e.valid = true;
+}
+
+// 3xTF32 forward: W serves as its own hi plane, this returns the lo plane.
+static int forward_lo_plane(DeviceCtx* c, cudaStream_t stream, const float* W, size_t nW, const float** lo)
+{
+    if (t_prepared_lo.W == W && t_prepared_lo.lo) { *lo = t_prepared_lo.lo; return ALPHA_OK; }
+    float* ws = nullptr;
+    bool fresh = true;
+    const DeviceCtx::WeightKey key{W, WK_FWD_LO, (int)(nW & 0x7fffffff), 0, 0, 0, 0};
+    int rc = weight_planes(c, stream, key, nW * sizeof(float), &ws, &fresh);
+    if (rc) return rc;
+    if (fresh) {
+        const size_t n4 = nW / 4;
+        size_t blocks = (n4 + 255) / 256;
+        if (blocks > (size_t)c->sm_count * 8) blocks = (size_t)c->sm_count * 8;
+        if (!t_dry) split_lo_kernel<<<(unsigned)blocks, 256, 0, stream>>>(reinterpret_cast<const float4*>(W), reinterpret_cast<float4*>(ws), n4);
+        note_launch("split_w");
+        rc = check_launch("split_lo_kernel");
+        if (rc) return rc;
+        weight_planes_ready(c, stream, key);
+    }
+    *lo = ws;
+    return ALPHA_OK;
+}
+
+// lo = lo plane of W (n floats) for alpha_Cuda_conv3D_kernel_remode: the one thing the forward natives need prepared.
+int launch_split_lo(cudaStream_t stream, const float* W, float* lo, size_t n)
+{
+    int sms = 148;
+    const size_t n4 = n / 4;
+    size_t blocks = (n4 + 255) / 256;
+    if (blocks > (size_t)sms * 8) blocks = (size_t)sms * 8;
+    if (blocks < 1) blocks = 1;
+    split_lo_kernel<<<(unsigned)blocks, 256, 0, stream>>>(reinterpret_cast<const float4*>(W), reinterpret_cast<float4*>(lo), n4);
+    note_launch("split_w");
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(ALPHA_E_CUDA, "split_lo_kernel launch failed: %s", cudaGetErrorString(e));
     return ALPHA_OK;
 }
 
@@ -334,28 +627,14 @@ static int launch_igemm(DeviceCtx* c, const IgemmPlan& pl, int mode3x, cudaStrea
     if (rc) return rc;
 
     dim3 grid((p.M_total + kBM - 1) / kBM, (pl.ncols + BN - 1) / BN, 1);
-    conv_igemm_kernel<<<grid, kIgemmThreads, smem, stream>>>(tmA, tmB, p);
+    if (!t_dry) conv_igemm_kernel<<<grid, kIgemmThreads, smem, stream>>>(tmA, tmB, p);
     note_launch("igemm");
     return check_launch("conv_igemm_kernel");
 }
 
 // ---- halo-tile kernel (stride 1): plan and launch -------------------------------------------------
 
-static int env_int(const char* name, int dflt)
-{
-    const char* e = getenv(name);
-    return (e && *e) ? atoi(e) : dflt;
-}
-
-// 0 = choose by cost model, 1 = always the per-tap im2col kernel, 2 = halo kernel wherever it applies
-static int env_tile_mode()
-{
-    const char* e = getenv("ALPHA_CONV_TILE");
-    if (!e) return 0;
-    if (!strcmp(e, "im2col")) return 1;
-    if (!strcmp(e, "halo")) return 2;
-    return 0;
-}
+static inline int env_tile_mode() { return opt(OPT_CONV_TILE); }
 
 struct HaloChoice {
     bool valid = false;
@@ -390,7 +669,7 @@ static void halo_launch_one(const HaloLaunch& L)
         cudaFuncSetAttribute(conv_halo_kernel<FW_T, JH_T, JW_T, ROW_T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         attr_done = true;
     }
-    conv_halo_kernel<FW_T, JH_T, JW_T, ROW_T><<<L.grid, kHaloThreads2, L.smem, L.stream>>>(*L.tmA, *L.tmB, *L.tmBlo, *L.tmO, *L.p);
+    if (!t_dry) conv_halo_kernel<FW_T, JH_T, JW_T, ROW_T><<<L.grid, kHaloThreads2, L.smem, L.stream>>>(*L.tmA, *L.tmB, *L.tmBlo, *L.tmO, *L.p);
 }
 
 template <int FW_T>
@@ -412,17 +691,17 @@ static HaloChoice plan_halo(const IgemmPlan& pl, int BN, int mode3x, int b_mn, i
     const int planes = mode3x ? 2 : 1;
     const uint32_t b_tx = b_mn ? (BN / 32) * 4096 : BN * 128;
     const uint32_t b_tile = ((b_tx + 1023) & ~1023u) * planes;
-    const bool allow_row = env_int("ALPHA_HALO_ROW", 1) != 0;
-    const int force_jh = env_int("ALPHA_HALO_JH", 0), force_jw = env_int("ALPHA_HALO_JW", 0);
+    const bool allow_row = opt(OPT_HALO_ROW) != 0;
+    const int force_jh = opt(OPT_HALO_JH), force_jw = opt(OPT_HALO_JW);
     const size_t smem_cap = 226 * 1024;
     // small images: NI images stacked in one accumulator, each in a slot of SG = OH + FH - 1 rows
     const int SG = pl.oH + pl.FH - 1;
     int ni_max = 1;
-    if (SG <= 16 && env_int("ALPHA_HALO_STACK", 1)) ni_max = 1 + (16 - pl.oH) / SG;
+    if (SG <= 16 && opt(OPT_HALO_STACK)) ni_max = 1 + (16 - pl.oH) / SG;
     // 3xTF32 with BN <= 128: the wide form (hi x [hi | lo] in one MMA of 2*BN columns, then lo x hi) needs
     // max(BN, 59) + max(BN / 2, 59) clocks per step instead of 3 * max(BN / 2, 59) and reads the A
     // operand twice instead of three times, at twice the tensor-memory columns per accumulator
-    const int wide_env = env_int("ALPHA_HALO_WIDE", -1);
+    const int wide_env = opt(OPT_HALO_WIDE);
     const int wide_lo = (mode3x && BN <= 128 && wide_env != 0) ? (wide_env == 1 ? 1 : 0) : 0;
     const int wide_hi = (mode3x && BN <= 128 && wide_env != 0) ? 1 : 0;
     for (int wide = wide_lo; wide <= wide_hi; ++wide)
@@ -495,7 +774,7 @@ static void halo_pair_launch_one(const HaloLaunch& L)
         cudaFuncSetAttribute(conv_halo_pair_kernel<FW_T, ROW_T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         attr_done = true;
     }
-    conv_halo_pair_kernel<FW_T, ROW_T><<<L.grid, kHaloThreads, L.smem, L.stream>>>(*L.tmA, *L.tmB, *L.tmBlo, *L.tmO, *L.p);
+    if (!t_dry) conv_halo_pair_kernel<FW_T, ROW_T><<<L.grid, kHaloThreads, L.smem, L.stream>>>(*L.tmA, *L.tmB, *L.tmBlo, *L.tmO, *L.p);
 }
 
 // One 16 x 8 pixel accumulator per CTA, two CTAs per MMA.  Returns 1 when the shape does not fit.
@@ -504,7 +783,7 @@ static int launch_halo_pair(DeviceCtx* c, const IgemmPlan& pl, int mode3x, cudaS
     if (pl.FW != 3 || pl.sh != 1 || pl.sw != 1 || pl.kdim % 32 != 0 || pl.b_mn) return 1;
     int BN = ((pl.ncols + 15) / 16) * 16;
     // wide 3xTF32 needs 2 * BN <= 256 columns per MMA; ALPHA_HALO_PAIR=2 takes three MMAs of BN <= 256 instead
-    const int pair_env = env_int("ALPHA_HALO_PAIR", -1);
+    const int pair_env = opt(OPT_HALO_PAIR);
     const bool three = mode3x && pair_env != 1;
     // the side-column form of the three-MMA mode needs 2 * BN columns per accumulator, twice
     const bool side3 = three && pair_env != 2;
@@ -520,7 +799,7 @@ static int launch_halo_pair(DeviceCtx* c, const IgemmPlan& pl, int mode3x, cudaS
     }
     const int SG = pl.oH + pl.FH - 1;
     int NI = 1;
-    if (SG <= 16 && env_int("ALPHA_HALO_STACK", 1)) NI = 1 + (16 - pl.oH) / SG;
+    if (SG <= 16 && opt(OPT_HALO_STACK)) NI = 1 + (16 - pl.oH) / SG;
     HaloParams p{};
     p.out = pl.out; p.bias = pl.bias; p.act_on = pl.act_on; p.act_k = pl.act_k; p.status = c->status; p.prof = c->prof;
     p.N = pl.aN; p.OH = pl.oH; p.OW = pl.oW;
@@ -552,7 +831,7 @@ static int launch_halo_pair(DeviceCtx* c, const IgemmPlan& pl, int mode3x, cudaS
     p.b_bytes = p.b_tx;
     const uint32_t planes = mode3x ? 2 : 1;
     const size_t smem_cap = 226 * 1024;
-    bool row = env_int("ALPHA_HALO_ROW", 1) != 0;
+    bool row = opt(OPT_HALO_ROW) != 0;
     p.npb = 2;
     auto need = [&](bool r, int sb) {
         return (size_t)p.npb * p.patch_bytes * planes + (size_t)sb * p.b_bytes * (r ? pl.FW : 1) + 32768 + 512 + 1024;
@@ -574,21 +853,8 @@ static int launch_halo_pair(DeviceCtx* c, const IgemmPlan& pl, int mode3x, cudaS
     const float* w_hi = pl.W;
     const float* w_lo = pl.W_lo ? pl.W_lo : pl.W;
     if (mode3x && !pl.W_lo) {
-        const size_t nW = (size_t)pl.wOC * pl.FH * pl.FW * pl.wIC;
-        float* ws = nullptr;
-        rc = get_workspace(c, stream, 2 * nW * sizeof(float), &ws);
+        rc = forward_lo_plane(c, stream, pl.W, (size_t)pl.wOC * pl.FH * pl.FW * pl.wIC, &w_lo);
         if (rc) return rc;
-        const size_t n4 = nW / 4;
-        size_t blocks = (n4 + 255) / 256;
-        if (blocks > (size_t)c->sm_count * 8) blocks = (size_t)c->sm_count * 8;
-        split_tensor_kernel<<<(unsigned)blocks, 256, 0, stream>>>(reinterpret_cast<const float4*>(pl.W),
-                                                                   reinterpret_cast<float4*>(ws),
-                                                                   reinterpret_cast<float4*>(ws + nW), n4);
-        note_launch("split_w");
-        rc = check_launch("split_tensor_kernel");
-        if (rc) return rc;
-        w_hi = ws;
-        w_lo = ws + nW;
     }
     cuuint64_t wd[3] = {(cuuint64_t)pl.wIC, (cuuint64_t)pl.FH * pl.FW, (cuuint64_t)pl.wOC};
     cuuint64_t wst[2] = {(cuuint64_t)pl.wIC * 4, (cuuint64_t)pl.FH * pl.FW * pl.wIC * 4};
@@ -603,7 +869,7 @@ static int launch_halo_pair(DeviceCtx* c, const IgemmPlan& pl, int mode3x, cudaS
     cuuint32_t obox[4] = {32, 8, (cuuint32_t)(NI > 1 ? pl.oH : 16), 1};
     rc = make_tiled_map(&tmO, pl.out, 4, od, ost, obox, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
-    int pairs = c->sm_count / 2;
+    int pairs = sm_budget(c) / 2;
     if (pairs > p.total_tiles / 2) pairs = p.total_tiles / 2;
     HaloLaunch L{2 * pairs, smem, stream, &tmA, &tmB, &tmBlo, &tmO, &p};
     if (row) halo_pair_launch_one<3, true>(L); else halo_pair_launch_one<3, false>(L);
@@ -628,7 +894,7 @@ static int launch_halo(DeviceCtx* c, const IgemmPlan& pl_in, int mode3x, cudaStr
     // the single-CTA forms win.  ALPHA_HALO_PAIR = 0
     // never, 1 always (wide 3xTF32), 2 always (three-MMA 3xTF32, one accumulator), 3 always (three MMAs,
     // correction terms in side columns).
-    const int pair_env = env_int("ALPHA_HALO_PAIR", -1);
+    const int pair_env = opt(OPT_HALO_PAIR);
     const bool pair_auto = mode3x ? pl.ncols % 128 == 0 : pl.ncols % 256 == 0;
     if (pair_env > 0 || (pair_env < 0 && pair_auto && tile_mode == 0)) {
         const int rc2 = launch_halo_pair(c, pl, mode3x, stream);
@@ -639,19 +905,19 @@ static int launch_halo(DeviceCtx* c, const IgemmPlan& pl_in, int mode3x, cudaStr
     const long long flat_m = (long long)pl.aN * pl.aH * pl.aW;
     if (pl.FH == 1 && pl.FW == 1 && pl.pad_h == 0 && pl.pad_w == 0 && pl.oSH == 1 && pl.oSW == 1 && pl.oNH == 0 &&
         pl.oNW == 0 && pl.oH == pl.aH && pl.oW == pl.aW && flat_m % 8 == 0 && flat_m / 8 <= 2147483647LL &&
-        env_int("ALPHA_HALO_FLAT", 1)) {
+        opt(OPT_HALO_FLAT)) {
         pl.aN = 1; pl.aW = 8; pl.aH = (int)(flat_m / 8);
         pl.oH = pl.aH; pl.oW = 8;
     }
     const int gran = pl.b_mn ? 32 : 16;
     int BN = ((pl.ncols + gran - 1) / gran) * gran;
     if (BN > 256) BN = (pl.ncols % 256 == 0 || pl.ncols > 512) ? 256 : 128;
-    HaloChoice ch = plan_halo(pl, BN, mode3x, pl.b_mn, c->sm_count);
+    HaloChoice ch = plan_halo(pl, BN, mode3x, pl.b_mn, sm_budget(c));
     // narrower column tiles when the wide ones leave SMs idle (small images, few pixels): the plan's
     // cost is the time of the busiest CTA, so candidates compare directly
     for (int cand = 128; cand >= 64; cand >>= 1) {
-        if (cand >= BN || pl.ncols % cand != 0 || !env_int("ALPHA_HALO_NARROW", 1)) continue;
-        HaloChoice alt = plan_halo(pl, cand, mode3x, pl.b_mn, c->sm_count);
+        if (cand >= BN || pl.ncols % cand != 0 || !opt(OPT_HALO_NARROW)) continue;
+        HaloChoice alt = plan_halo(pl, cand, mode3x, pl.b_mn, sm_budget(c));
         if (alt.valid && (!ch.valid || alt.cost < 0.9 * ch.cost)) { ch = alt; BN = cand; }
     }
     if (!ch.valid) return 1;
@@ -679,7 +945,7 @@ static int launch_halo(DeviceCtx* c, const IgemmPlan& pl_in, int mode3x, cudaStr
     // threads alternate over the ring's stages (the ring then needs an even number of slots).
     // The 3xTF32 forms run N >= 128 per MMA, are pipe-bound and keep one issuer (and with it a
     // fixed accumulation order).
-    p.dual = (p.mode3x == 0 && p.sb >= 2 && env_int("ALPHA_HALO_DUAL", 1)) ? 1 : 0;
+    p.dual = (p.mode3x == 0 && p.sb >= 2 && opt(OPT_HALO_DUAL)) ? 1 : 0;
     if (p.dual) p.sb &= ~1;
     p.idesc = make_idesc_tf32(kBM, BN, false, pl.b_mn);
     p.idesc_wide = make_idesc_tf32(kBM, ch.wide ? 2 * BN : BN, false, pl.b_mn);
@@ -703,21 +969,8 @@ static int launch_halo(DeviceCtx* c, const IgemmPlan& pl_in, int mode3x, cudaStr
     const float* w_hi = pl.W;
     const float* w_lo = pl.W_lo ? pl.W_lo : pl.W;
     if (mode3x && !pl.W_lo) {
-        const size_t nW = (size_t)pl.wOC * pl.FH * pl.FW * pl.wIC;
-        float* ws = nullptr;
-        rc = get_workspace(c, stream, 2 * nW * sizeof(float), &ws);
+        rc = forward_lo_plane(c, stream, pl.W, (size_t)pl.wOC * pl.FH * pl.FW * pl.wIC, &w_lo);
         if (rc) return rc;
-        const size_t n4 = nW / 4;
-        size_t blocks = (n4 + 255) / 256;
-        if (blocks > (size_t)c->sm_count * 8) blocks = (size_t)c->sm_count * 8;
-        split_tensor_kernel<<<(unsigned)blocks, 256, 0, stream>>>(reinterpret_cast<const float4*>(pl.W),
-                                                                   reinterpret_cast<float4*>(ws),
-                                                                   reinterpret_cast<float4*>(ws + nW), n4);
-        note_launch("split_w");
-        rc = check_launch("split_tensor_kernel");
-        if (rc) return rc;
-        w_hi = ws;
-        w_lo = ws + nW;
     }
     CUtensorMap tmBlo, tmO;
     cuuint64_t wd[3] = {(cuuint64_t)pl.wIC, (cuuint64_t)pl.FH * pl.FW, (cuuint64_t)pl.wOC};
@@ -740,7 +993,7 @@ static int launch_halo(DeviceCtx* c, const IgemmPlan& pl_in, int mode3x, cudaStr
     cuuint32_t obox[4] = {32, 8, (cuuint32_t)(ch.NI > 1 ? pl.oH : 16), 1};
     rc = make_tiled_map(&tmO, pl.out, 4, od, ost, obox, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
-    int grid = c->sm_count < p.total_tiles ? c->sm_count : p.total_tiles;
+    int grid = sm_budget(c) < p.total_tiles ? sm_budget(c) : p.total_tiles;
     HaloLaunch L{grid, smem, stream, &tmA, &tmB, &tmBlo, &tmO, &p};
     if (!ch.stat) halo_launch_one<0, 0, 0, false>(L);
     else if (pl.FW == 1) halo_launch_fw<1>(L, ch.JH, ch.JW, ch.row);
@@ -774,7 +1027,7 @@ static int make_patch_matrix(DeviceCtx* c, PatchShape ps, const float* X, cudaSt
     const size_t total = M * (Kp / 4);
     size_t blocks = (total + 255) / 256;
     if (blocks > (size_t)c->sm_count * 16) blocks = (size_t)c->sm_count * 16;
-    patch_matrix_kernel<<<(unsigned)blocks, 256, 0, stream>>>(X, ws, ps);
+    if (!t_dry) patch_matrix_kernel<<<(unsigned)blocks, 256, 0, stream>>>(X, ws, ps);
     note_launch("patch_matrix");
     rc = check_launch("patch_matrix_kernel");
     if (rc) return rc;
@@ -812,7 +1065,7 @@ static bool tiny_image(int oH, int oW) { return oH * oW <= 16; }
 static bool patch_path_ok(const AlphaConvShape* s)
 {
     const long long K = (long long)s->FH * s->FW * s->IC;
-    return s->IC % 4 == 0 && K <= 16384 && env_int("ALPHA_PATCH_MATRIX", 1) != 0;
+    return s->IC % 4 == 0 && K <= 16384 && opt(OPT_PATCH_MATRIX) != 0;
 }
 
 static bool taps_fit64(const AlphaConvShape* s) { return s->FH * s->FW <= 64; }
@@ -829,18 +1082,21 @@ static bool taps_fit64(const AlphaConvShape* s) { return s->FH * s->FW <= 64; }
 static int launch_dx_phases(DeviceCtx* c, const AlphaConvShape* s, const float* dY, const float* W, float* dX,
                             int mode3x, cudaStream_t stream)
 {
-    if (env_tile_mode() == 1 || !env_int("ALPHA_DX_PHASES", 1)) return 1;
+    if (env_tile_mode() == 1 || !opt(OPT_DX_PHASES)) return 1;
     if (s->OC % 32 != 0 || s->sh > 8 || s->sw > 8 || !taps_fit64(s)) return 1;
     if (s->IH < s->sh || s->IW < s->sw) return 1;
     if (s->FH < s->sh || s->FW < s->sw) {
         // some phases receive no filter tap at all (1x1 stride 2): those pixels of deltaX are zero
-        cudaError_t e = cudaMemsetAsync(dX, 0, (size_t)s->N * s->IH * s->IW * s->IC * sizeof(float), stream);
+        cudaError_t e = t_dry ? cudaSuccess : cudaMemsetAsync(dX, 0, (size_t)s->N * s->IH * s->IW * s->IC * sizeof(float), stream);
         if (e != cudaSuccess) return fail(ALPHA_E_CUDA, "cudaMemsetAsync(deltaX): %s", cudaGetErrorString(e));
     }
     const int taps = s->FH * s->FW;
     const size_t nW = (size_t)s->OC * taps * s->IC;
     float* ws = nullptr;
-    int rc = get_workspace(c, stream, (mode3x ? 2 : 1) * nW * sizeof(float), &ws);
+    bool fresh = true;
+    const DeviceCtx::WeightKey wkey{W, WK_DX_PHASES, s->OC, s->IC, s->FH * 256 + s->FW,
+                                    (s->sh << 24) | (s->sw << 16) | (s->ph << 8) | s->pw, mode3x};
+    int rc = weight_planes(c, stream, wkey, (mode3x ? 2 : 1) * nW * sizeof(float), &ws, &fresh);
     if (rc) return rc;
     size_t woff = 0;
     for (int py = 0; py < s->sh; ++py)
@@ -860,11 +1116,13 @@ static int launch_dx_phases(DeviceCtx* c, const AlphaConvShape* s, const float* 
             float* whi = ws + woff;
             float* wlo = mode3x ? ws + nW + woff : nullptr;
             woff += pn;
-            dim3 tg((s->IC + 31) / 32, (s->OC + 31) / 32, ptaps);
-            transpose_weights_kernel<<<tg, 256, 0, stream>>>(W, whi, wlo, s->OC, s->IC, taps, map, mode3x);
-            note_launch("transpose_w");
-            rc = check_launch("transpose_weights_kernel");
-            if (rc) return rc;
+            if (fresh) {
+                dim3 tg((s->IC + 31) / 32, (s->OC + 31) / 32, ptaps);
+                if (!t_dry) transpose_weights_kernel<<<tg, 256, 0, stream>>>(W, whi, wlo, s->OC, s->IC, taps, map, mode3x);
+                note_launch("transpose_w");
+                rc = check_launch("transpose_weights_kernel");
+                if (rc) return rc;
+            }
             IgemmPlan pl{};
             pl.act = dY; pl.aN = s->N; pl.aH = s->OH; pl.aW = s->OW; pl.aC = s->OC;
             pl.FH = Uy; pl.FW = Ux; pl.sh = 1; pl.sw = 1;
@@ -875,12 +1133,13 @@ static int launch_dx_phases(DeviceCtx* c, const AlphaConvShape* s, const float* 
             pl.W = whi; pl.W_lo = wlo; pl.wOC = s->IC; pl.wIC = s->OC; pl.bias = nullptr;
             pl.b_mn = false; pl.flip = false; pl.kdim = s->OC; pl.force = true;
             if (tiny_image(A, Bw) && (long long)ptaps * s->OC <= 16384 && ptaps * s->OC >= 2048 &&
-                env_int("ALPHA_PATCH_MATRIX", 1)) {
+                opt(OPT_PATCH_MATRIX)) {
                 // phases of a few pixels per image: patch matrix of deltaY, dense 1x1 product, scatter
                 PatchShape ps{s->N, s->OH, s->OW, s->OC, Uy, Ux, A, Bw, 1, 1, pl.pad_h, pl.pad_w, 0, 0};
                 const size_t M = (size_t)s->N * A * Bw;
                 float* P = nullptr;
                 int K = 0, Kp = 0;
+                const WsMark mark = ws_mark(c, stream);   // every phase reuses the same patch-matrix bytes
                 rc = make_patch_matrix(c, ps, dY, stream, &P, &K, &Kp, M * s->IC);
                 if (rc) return rc;
                 float* Sp = P + M * Kp;
@@ -894,16 +1153,18 @@ static int launch_dx_phases(DeviceCtx* c, const AlphaConvShape* s, const float* 
                 const size_t total4 = M * (s->IC / 4);
                 size_t blocks = (total4 + 255) / 256;
                 if (blocks > (size_t)c->sm_count * 16) blocks = (size_t)c->sm_count * 16;
-                scatter_phase_kernel<<<(unsigned)blocks, 256, 0, stream>>>(Sp, pl.out, s->N, A, Bw, s->IC, s->sh, s->sw, s->IH, s->IW);
+                if (!t_dry) scatter_phase_kernel<<<(unsigned)blocks, 256, 0, stream>>>(Sp, pl.out, s->N, A, Bw, s->IC, s->sh, s->sw, s->IH, s->IW);
                 note_launch("dx_patch");
                 rc = check_launch("scatter_phase_kernel");
                 if (rc) return rc;
+                ws_rewind(c, stream, mark);
                 continue;
             }
             rc = launch_halo(c, pl, mode3x, stream);
             if (rc == 1) return fail(ALPHA_E_ARG, "strided deltaX: phase (%d,%d) does not fit the halo kernel", py, px);
             if (rc) return rc;
         }
+    if (fresh) weight_planes_ready(c, stream, wkey);
     return ALPHA_OK;
 }
 
@@ -918,22 +1179,27 @@ static int launch_dx_col2im(DeviceCtx* c, const AlphaConvShape* s, const float* 
 {
     const int taps = s->FH * s->FW, cols = s->IC * taps;
     if (s->IC > 8 || s->IC % 4 != 0 || cols > 512 || s->OC % 32 != 0 || taps > 64) return 1;
-    if (!env_int("ALPHA_DX_COL2IM", 1) || env_tile_mode() == 1) return 1;
+    if (!opt(OPT_DX_COL2IM) || env_tile_mode() == 1) return 1;
     const size_t M = (size_t)s->N * s->OH * s->OW, nW = (size_t)s->OC * cols;
     float* ws = nullptr;
-    int rc = get_workspace(c, stream, (mode3x ? 2 : 1) * nW * sizeof(float), &ws);
+    bool fresh = true;
+    const DeviceCtx::WeightKey wkey{W, WK_DX_COL2IM, s->OC, s->IC, s->FH * 256 + s->FW, 0, mode3x};
+    int rc = weight_planes(c, stream, wkey, (mode3x ? 2 : 1) * nW * sizeof(float), &ws, &fresh);
     if (rc) return rc;
     float* P = nullptr;
     rc = get_workspace(c, stream, M * cols * sizeof(float), &P, 1);
     if (rc) return rc;
-    TapMap map{};
-    map.n = taps;
-    for (int t = 0; t < taps; ++t) map.src[t] = t;
-    dim3 tg((s->IC + 31) / 32, (s->OC + 31) / 32, taps);
-    transpose_weights_kernel<<<tg, 256, 0, stream>>>(W, ws, mode3x ? ws + nW : nullptr, s->OC, s->IC, taps, map, mode3x);
-    note_launch("transpose_w");
-    rc = check_launch("transpose_weights_kernel");
-    if (rc) return rc;
+    if (fresh) {
+        TapMap map{};
+        map.n = taps;
+        for (int t = 0; t < taps; ++t) map.src[t] = t;
+        dim3 tg((s->IC + 31) / 32, (s->OC + 31) / 32, taps);
+        if (!t_dry) transpose_weights_kernel<<<tg, 256, 0, stream>>>(W, ws, mode3x ? ws + nW : nullptr, s->OC, s->IC, taps, map, mode3x);
+        note_launch("transpose_w");
+        rc = check_launch("transpose_weights_kernel");
+        if (rc) return rc;
+        weight_planes_ready(c, stream, wkey);
+    }
     IgemmPlan pl{};
     pl.act = dY; pl.aN = s->N; pl.aH = s->OH; pl.aW = s->OW; pl.aC = s->OC;
     pl.FH = 1; pl.FW = 1; pl.sh = 1; pl.sw = 1; pl.pad_h = 0; pl.pad_w = 0;
@@ -947,7 +1213,7 @@ static int launch_dx_col2im(DeviceCtx* c, const AlphaConvShape* s, const float* 
     const size_t total = (size_t)s->N * s->IH * s->IW * (s->IC / 4);
     size_t blocks = (total + 255) / 256;
     if (blocks > (size_t)c->sm_count * 16) blocks = (size_t)c->sm_count * 16;
-    col2im_gather_kernel<<<(unsigned)blocks, 256, 0, stream>>>(P, dX, ps);
+    if (!t_dry) col2im_gather_kernel<<<(unsigned)blocks, 256, 0, stream>>>(P, dX, ps);
     note_launch("dx_col2im");
     return check_launch("col2im_gather_kernel");
 }
@@ -964,15 +1230,14 @@ static void dw_halo_set_attr()
 static int launch_dw_halo(DeviceCtx* c, const AlphaConvShape* s_in, const float* X, const float* dY, float* dW,
                           int mode3x, cudaStream_t stream)
 {
-    const char* e = getenv("ALPHA_CONV_DW");
-    if (e && !strcmp(e, "split")) return 1;
+    if (opt(OPT_CONV_DW) == 1) return 1;
     AlphaConvShape flat = *s_in;
     const AlphaConvShape* s = s_in;
     // a 1x1 deltaW sums over pixels in any order: one image of 16 columns fills every pixel tile
     const long long flat_m = (long long)s_in->N * s_in->OH * s_in->OW;
     if (s_in->FH == 1 && s_in->FW == 1 && s_in->ph == 0 && s_in->pw == 0 && s_in->sh == 1 && s_in->sw == 1 &&
         s_in->IH == s_in->OH && s_in->IW == s_in->OW && flat_m % 16 == 0 && flat_m / 16 <= 2147483647LL &&
-        env_int("ALPHA_HALO_FLAT", 1)) {
+        opt(OPT_HALO_FLAT)) {
         flat.N = 1; flat.OW = flat.IW = 16; flat.OH = flat.IH = (int)(flat_m / 16);
         s = &flat;
     }
@@ -996,14 +1261,14 @@ static int launch_dw_halo(DeviceCtx* c, const AlphaConvShape* s_in, const float*
             const long long std_cost = 3LL * mma_clk(NT) * ((s->OC + 127) / 128) * (s->IC / NT);
             const long long stk_cost = 1LL * mma_clk(2 * NTq) * ((s->OC + 63) / 64) * (s->IC / NTq);
             stacked = stk_cost < std_cost;
-            const int force = env_int("ALPHA_DW_STACKED", -1);
+            const int force = opt(OPT_DW_STACKED);
             if (force >= 0) stacked = force != 0;
             if (stacked) NT = NTq;
         }
     }
     // plain TF32 with at most 64 output channels: two half tiles side by side ("diagonal" form)
     bool diag = false;
-    if (!mode3x && s->OC <= 64 && s->OH >= 2 && env_int("ALPHA_DW_DIAG", 1)) {
+    if (!mode3x && s->OC <= 64 && s->OH >= 2 && opt(OPT_DW_DIAG)) {
         int NTd = 0;
         for (int cand = 128; cand >= 32; cand >>= 1)
             if (s->IC % cand == 0 && s->FW * 2 * cand <= 512) { NTd = cand; break; }
@@ -1024,10 +1289,10 @@ static int launch_dw_halo(DeviceCtx* c, const AlphaConvShape* s_in, const float*
     if (groups > 65535) return 1;
     // pixel tile: CW columns of 8-pixel groups, R rows, sized so that three stages fit shared memory
     const int planes = (mode3x || diag) ? 2 : 1;   // diagonal: the second plane holds the second half tile
-    int CW = env_int("ALPHA_DW_CW", 0);
+    int CW = opt(OPT_DW_CW);
     if (!CW) CW = (s->OW <= 8 || (s->OW % 16 != 0 && s->OW % 16 <= 8)) ? 8 : 16;  // fewer idle columns
     const int PW = CW + s->FW - 1;
-    int R = env_int("ALPHA_DW_R", 0);
+    int R = opt(OPT_DW_R);
     auto stage_bytes = [&](int r) {
         const uint32_t dyblk = ((uint32_t)r * CW * 128 + 1023) & ~1023u, xbk = ((uint32_t)r * PW * 128 + 1023) & ~1023u;
         return (size_t)planes * (dyb * dyblk + (NT / 32) * xbk);
@@ -1046,7 +1311,7 @@ static int launch_dw_halo(DeviceCtx* c, const AlphaConvShape* s_in, const float*
     const long long total = (long long)s->N * p.tiles_per_img;
     if (total > 2147483647LL) return 1;
     p.total_tiles = (int)total;
-    int parts = c->sm_count / groups;
+    int parts = sm_budget(c) / groups;
     if (parts < 1) parts = 1;
     if (parts > p.total_tiles) parts = p.total_tiles;
     p.parts = parts;
@@ -1088,9 +1353,9 @@ static int launch_dw_halo(DeviceCtx* c, const AlphaConvShape* s_in, const float*
         dw_halo_set_attr<1, 2, 16>(); dw_halo_set_attr<1, 4, 16>(); dw_halo_set_attr<1, 8, 16>();
         attr_done = true;
     }
-#define DWH_LAUNCH(FW_, R_, CW_) conv_dw_halo_kernel<FW_, R_, CW_><<<grid, kDwHaloThreads, smem, stream>>>(tmX, tmDY, p)
-    const bool st = s->FW == 3 && env_int("ALPHA_DW_STATIC", 1) != 0;
-    const bool st1 = s->FW == 1 && CW == 16 && env_int("ALPHA_DW_STATIC", 1) != 0;   // 1x1 (flat 16-column view)
+#define DWH_LAUNCH(FW_, R_, CW_) do { if (!t_dry) conv_dw_halo_kernel<FW_, R_, CW_><<<grid, kDwHaloThreads, smem, stream>>>(tmX, tmDY, p); } while (0)
+    const bool st = s->FW == 3 && opt(OPT_DW_STATIC) != 0;
+    const bool st1 = s->FW == 1 && CW == 16 && opt(OPT_DW_STATIC) != 0;   // 1x1 (flat 16-column view)
     if (st && R == 1 && CW == 16) DWH_LAUNCH(3, 1, 16);
     else if (st && R == 2 && CW == 16) DWH_LAUNCH(3, 2, 16);
     else if (st && R == 4 && CW == 16) DWH_LAUNCH(3, 4, 16);
@@ -1110,7 +1375,7 @@ static int launch_dw_halo(DeviceCtx* c, const AlphaConvShape* s_in, const float*
     if (rc) return rc;
     if (parts * nsub > 1) {
         const size_t n4 = sizeW / 4;
-        dw_reduce_kernel<<<(unsigned)((n4 + 63) / 64), 64, 0, stream>>>(ws, sizeW, parts * nsub, dW, n4, 0);
+        if (!t_dry) dw_reduce_kernel<<<(unsigned)((n4 + 63) / 64), 64, 0, stream>>>(ws, sizeW, parts * nsub, dW, n4, 0);
         note_launch("dw_halo");
         rc = check_launch("dw_reduce_kernel");
     }
@@ -1121,11 +1386,95 @@ static int launch_dw_halo(DeviceCtx* c, const AlphaConvShape* s_in, const float*
 int launch_buf_summary(cudaStream_t stream, const float* buf, float* deltaW, int part, size_t sizeW)
 {
     const size_t n4 = sizeW / 4;
-    dw_reduce_kernel<<<(unsigned)((n4 + 63) / 64), 64, 0, stream>>>(buf, sizeW, part, deltaW, n4, 1);
+    if (!t_dry) dw_reduce_kernel<<<(unsigned)((n4 + 63) / 64), 64, 0, stream>>>(buf, sizeW, part, deltaW, n4, 1);
     note_launch("buf_summary");
     return check_launch("dw_reduce_kernel");
 }
 
+
+// ---- deltaW, split-K im2col kernel: plan and launch -----------------------------------------------
+//
+// One plan serves alpha_conv3d_deltaW (strides, and shapes the halo-tile kernel leaves) and
+// alpha_conv3d_deltaW_noalloc; they differ only in where the split-K partial sums live.
+struct DwSplitPlan {
+    DwParams p;
+    int groups = 0, n_tiles = 0, splits = 0, stages = 0;
+    size_t sizeW = 0, smem = 0;
+};
+
+static int plan_dw_split(const AlphaConvShape* s, int mode3x, int sm_count, DwSplitPlan* out)
+{
+    DwSplitPlan pl;
+    DwParams& p = pl.p;
+    p = DwParams{};
+    p.Npix = s->N * s->OH * s->OW;
+    p.OHo = s->OH; p.OWo = s->OW; p.sh = s->sh; p.sw = s->sw; p.ph = s->ph; p.pw = s->pw;
+    p.FH = s->FH; p.FW = s->FW; p.IC = s->IC; p.OC = s->OC;
+    p.icb = s->IC / 32;
+    p.MB = s->FH * s->FW * p.icb;
+    int BN = ((s->OC + 31) / 32) * 32;
+    if (BN > 256) BN = 256;
+    p.BN = BN;
+    const int MT = (p.MB + 3) / 4;
+    int G = 512 / BN;  // accumulators of BN columns that fit the 512 tensor-memory columns
+    if (G > MT) G = MT;
+    const int groups = (MT + G - 1) / G;
+    G = (MT + groups - 1) / groups;  // balance the groups
+    p.G = G;
+    p.KP = 32;
+    p.tmem_cols = pow2_cols(G * BN);
+    p.idesc = make_idesc_tf32(kBM, BN, true, true);
+    p.mode3x = mode3x;
+    const int n_tiles = (s->OC + BN - 1) / BN;
+    p.total_chunks = (p.Npix + p.KP - 1) / p.KP;
+    int splits = sm_count / (groups * n_tiles);
+    if (splits < 1) splits = 1;
+    if (splits > p.total_chunks) splits = p.total_chunks;
+    p.chunks_per_split = (p.total_chunks + splits - 1) / splits;
+    splits = (p.total_chunks + p.chunks_per_split - 1) / p.chunks_per_split;
+    pl.sizeW = (size_t)s->OC * s->FH * s->FW * s->IC;
+    const uint32_t blk = p.KP * 128;
+    const uint32_t stage = (4 * blk + (BN / 32) * blk) * (mode3x ? 2 : 1);
+    int stages = (int)((200u * 1024) / stage);
+    if (stages > 6) stages = 6;
+    if (stages < 1) return fail(ALPHA_E_ARG, "deltaW stage of %u bytes does not fit shared memory", stage);
+    p.stages = stages;
+    pl.smem = (size_t)stages * stage + (3 * stages + 2) * 8 + 1024;
+    pl.groups = groups; pl.n_tiles = n_tiles; pl.splits = splits; pl.stages = stages;
+    *out = pl;
+    return ALPHA_OK;
+}
+
+// `partials` holds plan.splits * plan.sizeW floats when plan.splits > 1 and is not used otherwise.
+static int launch_dw_split(const AlphaConvShape* s, const float* X, const float* deltaY, float* deltaW, float* partials,
+                           int* status, const DwSplitPlan& pl, cudaStream_t stream, const char* tag)
+{
+    DwParams p = pl.p;
+    p.status = status;
+    if (pl.splits > 1) { p.out = partials; p.split_stride = pl.sizeW; }
+    else { p.out = deltaW; p.split_stride = 0; }
+    CUtensorMap tmX, tmDY;
+    int rc = make_im2col_map(&tmX, X, s->N, s->IH, s->IW, s->IC, s->FH, s->FW, s->sh, s->sw, s->ph, s->pw, 32, p.KP,
+                             CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
+    if (rc) return rc;
+    cuuint64_t dd[2] = {(cuuint64_t)s->OC, (cuuint64_t)p.Npix};
+    cuuint64_t ds[1] = {(cuuint64_t)s->OC * 4};
+    cuuint32_t box[2] = {32, (cuuint32_t)p.KP};
+    rc = make_tiled_map(&tmDY, deltaY, 2, dd, ds, box, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
+    if (rc) return rc;
+    dim3 grid(pl.groups, pl.n_tiles, pl.splits);
+    if (!t_dry) conv_dw_kernel<<<grid, kIgemmThreads, pl.smem, stream>>>(tmX, tmDY, p);
+    note_launch(tag);
+    rc = check_launch("conv_dw_kernel");
+    if (rc) return rc;
+    if (pl.splits > 1) {
+        const size_t n4 = pl.sizeW / 4;
+        if (!t_dry) dw_reduce_kernel<<<(unsigned)((n4 + 63) / 64), 64, 0, stream>>>(partials, pl.sizeW, pl.splits, deltaW, n4, 0);
+        note_launch(tag);
+        rc = check_launch("dw_reduce_kernel");
+    }
+    return rc;
+}
 
 // ---- deltaW without any allocation ---------------------------------------------------------------
 //
@@ -1191,12 +1540,10 @@ using namespace alpha;
 //
 // Filter, input and output transforms run as separate memory-bound kernels around four 3x1
 // tensor-core convolutions; the scratch (transformed filter, input and products, about
-// 2|X| + 2|Y| + 4/3|W|) comes from a second per-stream block, because the inner convolutions use
-// the first one for their weight planes.
+// 2|X| + 2|Y| + 4/3|W|) and the weight planes of the inner convolutions are carved from the
+// stream's block one after the other.
 static int forward_direct(DeviceCtx* c, const AlphaConvShape* s, const float* X, const float* W, const float* bias,
                           float* Y, cudaStream_t stream, int algo, int act_on = 0, float act_k = 0.f);
-
-static std::map<cudaStream_t, DeviceCtx::Block> g_wino_ws[64];
 
 static int launch_winograd(DeviceCtx* c, const AlphaConvShape* s, const float* X, const float* W, const float* bias,
                            float* Y, cudaStream_t stream)
@@ -1208,26 +1555,14 @@ static int launch_winograd(DeviceCtx* c, const AlphaConvShape* s, const float* X
     const size_t nU = (size_t)4 * s->OC * 3 * s->IC;
     const size_t nV = (size_t)4 * s->N * s->IH * OWp * s->IC;
     const size_t nM = (size_t)4 * s->N * s->OH * OWp * s->OC;
-    int dev = 0;
-    cudaGetDevice(&dev);
     float* ws = nullptr;
-    {
-        std::lock_guard<std::mutex> lock(g_mu);
-        DeviceCtx::Block& b = g_wino_ws[dev][stream];
-        const size_t bytes = (nU + nV + nM) * sizeof(float);
-        if (b.bytes < bytes) {
-            if (b.ptr) { cudaStreamSynchronize(stream); cudaFree(b.ptr); b.ptr = nullptr; b.bytes = 0; }
-            cudaError_t e = cudaMalloc(&b.ptr, bytes);
-            if (e != cudaSuccess) return fail(ALPHA_E_CUDA, "cudaMalloc(winograd scratch %zu B): %s", bytes, cudaGetErrorString(e));
-            b.bytes = bytes;
-        }
-        ws = b.ptr;
-    }
+    int rc0 = get_workspace(c, stream, (nU + nV + nM) * sizeof(float), &ws);
+    if (rc0) return rc0;
     float *U = ws, *V = ws + nU, *M = ws + nU + nV;
     const int cap = c->sm_count * 16;
     auto blocks = [&](size_t n) { size_t b = (n + 255) / 256; return (unsigned)(b < (size_t)cap ? (b ? b : 1) : cap); };
-    wino_filter_kernel<<<blocks((size_t)s->OC * 3 * s->IC / 4), 256, 0, stream>>>(W, U, s->OC, s->IC);
-    wino_input_kernel<<<blocks(nV / 16), 256, 0, stream>>>(X, V, s->N, s->IH, s->IW, s->IC, OWp, s->pw);
+    if (!t_dry) wino_filter_kernel<<<blocks((size_t)s->OC * 3 * s->IC / 4), 256, 0, stream>>>(W, U, s->OC, s->IC);
+    if (!t_dry) wino_input_kernel<<<blocks(nV / 16), 256, 0, stream>>>(X, V, s->N, s->IH, s->IW, s->IC, OWp, s->pw);
     note_launch("winograd");
     int rc = check_launch("winograd transforms");
     if (rc) return rc;
@@ -1238,7 +1573,7 @@ static int launch_winograd(DeviceCtx* c, const AlphaConvShape* s, const float* X
                             stream, ALPHA_ALGO_AUTO);
         if (rc) return rc;
     }
-    wino_output_kernel<<<blocks(nM / 16), 256, 0, stream>>>(M, bias, Y, s->N, s->OH, s->OW, s->OC, OWp);
+    if (!t_dry) wino_output_kernel<<<blocks(nM / 16), 256, 0, stream>>>(M, bias, Y, s->N, s->OH, s->OW, s->OC, OWp);
     note_launch("winograd");
     return check_launch("wino_output_kernel");
 }
@@ -1266,6 +1601,113 @@ int alpha_conv_get_algo(void) { return g_algo.load(); }
 unsigned long long alpha_conv_launch_count(void) { return g_launches.load(); }
 const char* alpha_conv_last_algo(void) { return g_last_algo; }
 const char* alpha_conv_last_plan(void) { return g_plan; }
+
+int alpha_conv_set_option(const char* name, int value)
+{
+    if (!name) return fail(ALPHA_E_ARG, "set_option: null name");
+    if (!strncmp(name, "ALPHA_", 6)) name += 6;
+    for (int i = 0; i < OPT_COUNT; ++i)
+        if (!strcmp(name, kOptDefs[i].name)) {
+            opt(static_cast<Opt>(i));   // seed the table from the environment first
+            g_opt[i].store(value);
+            return ALPHA_OK;
+        }
+    return fail(ALPHA_E_ARG, "set_option: unknown option %s", name);
+}
+int alpha_conv_get_option(const char* name, int* value)
+{
+    if (!name || !value) return fail(ALPHA_E_ARG, "get_option: null argument");
+    if (!strncmp(name, "ALPHA_", 6)) name += 6;
+    for (int i = 0; i < OPT_COUNT; ++i)
+        if (!strcmp(name, kOptDefs[i].name)) { *value = opt(static_cast<Opt>(i)); return ALPHA_OK; }
+    return fail(ALPHA_E_ARG, "get_option: unknown option %s", name);
+}
+
+int alpha_conv_set_workspace(alpha_stream_t stream_, void* ptr, size_t bytes)
+{
+    DeviceCtx* c;
+    int rc = get_ctx(&c);
+    if (rc) return rc;
+    if (ptr && ((uintptr_t)ptr & 255)) return fail(ALPHA_E_ARG, "set_workspace: the block must be 256-byte aligned");
+    cudaStream_t stream = (cudaStream_t)stream_;
+    std::lock_guard<std::mutex> lock(g_mu);
+    DeviceCtx::Block& b = c->workspace[stream];
+    if (b.base && !b.external) c->retired.push_back(DeviceCtx::Retired{b.base, b.bytes, nullptr, b.captured, stream});
+    b = DeviceCtx::Block{};
+    if (ptr) { b.base = static_cast<char*>(ptr); b.bytes = bytes; b.external = true; }
+    return ALPHA_OK;
+}
+
+int alpha_conv_reserve_workspace(alpha_stream_t stream_, size_t bytes)
+{
+    DeviceCtx* c;
+    int rc = get_ctx(&c);
+    if (rc) return rc;
+    cudaStream_t stream = (cudaStream_t)stream_;
+    std::lock_guard<std::mutex> lock(g_mu);
+    DeviceCtx::Block& b = c->workspace[stream];
+    if (b.bytes >= bytes) return ALPHA_OK;
+    rc = grow_block(c, stream, b, bytes);
+    if (rc) return rc;
+    // nothing of the old block is in use by a call in progress: its event can be recorded right away
+    if (!c->retired.empty() && !c->retired.back().done && !c->retired.back().captured &&
+        cudaEventCreateWithFlags(&c->retired.back().done, cudaEventDisableTiming) == cudaSuccess)
+        cudaEventRecord(c->retired.back().done, stream);
+    return ALPHA_OK;
+}
+
+int alpha_conv_release_workspace(void)
+{
+    DeviceCtx* c;
+    int rc = get_ctx(&c);
+    if (rc) return rc;
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return fail(ALPHA_E_CUDA, "cudaDeviceSynchronize: %s", cudaGetErrorString(e));
+    std::lock_guard<std::mutex> lock(g_mu);
+    for (auto& kv : c->workspace)
+        if (kv.second.base && !kv.second.external) cudaFree(kv.second.base);
+    c->workspace.clear();
+    for (DeviceCtx::Retired& r : c->retired) {
+        if (r.done) cudaEventDestroy(r.done);
+        cudaFree(r.ptr);
+    }
+    c->retired.clear();
+    for (auto& kv : c->weights) {
+        if (kv.second.ready) cudaEventDestroy(kv.second.ready);
+        if (kv.second.ptr) cudaFree(kv.second.ptr);
+    }
+    c->weights.clear();
+    return ALPHA_OK;
+}
+
+size_t alpha_conv_workspace_in_use(void)
+{
+    DeviceCtx* c;
+    if (get_ctx(&c)) return 0;
+    std::lock_guard<std::mutex> lock(g_mu);
+    size_t total = 0;
+    for (auto& kv : c->workspace) if (!kv.second.external) total += kv.second.bytes;
+    for (DeviceCtx::Retired& r : c->retired) total += r.bytes;
+    for (auto& kv : c->weights) total += kv.second.bytes;
+    return total;
+}
+
+int alpha_conv_weight_cache(int enable)
+{
+    g_weight_cache.store(enable ? 1 : 0);
+    return ALPHA_OK;
+}
+
+int alpha_conv_weights_updated(const float* W)
+{
+    DeviceCtx* c;
+    int rc = get_ctx(&c);
+    if (rc) return rc;
+    std::lock_guard<std::mutex> lock(g_mu);
+    for (auto& kv : c->weights)
+        if (!W || kv.first.W == W) kv.second.valid = false;
+    return ALPHA_OK;
+}
 
 int alpha_conv_device_status(void)
 {
@@ -1306,7 +1748,8 @@ int alpha_conv3d_forward(const AlphaConvShape* s, const float* X, const float* W
     rc = get_ctx(&c);
     if (rc) return rc;
     cudaStream_t stream = (cudaStream_t)stream_;
-    const int algo = g_algo.load();
+    ws_begin(c, stream);
+    const int algo = cur_algo();
     if (algo == ALPHA_ALGO_WINOGRAD) return launch_winograd(c, s, X, W, bias, Y, stream);
     return forward_direct(c, s, X, W, bias, Y, stream, algo);
 }
@@ -1320,6 +1763,7 @@ int alpha_conv_bias_grad(const float* deltaY, long long rows, int OC, float* del
     int rc = get_ctx(&c);
     if (rc) return rc;
     cudaStream_t stream = (cudaStream_t)stream_;
+    ws_begin(c, stream);
     const int cols4 = OC / 4;
     // first pass: up to 64 float4 columns (1 KB of a row) per CTA, the rest of the 256 threads as row lanes
     const int CT = cols4 < 64 ? cols4 : 64;
@@ -1332,7 +1776,7 @@ int alpha_conv_bias_grad(const float* deltaY, long long rows, int OC, float* del
     float* ws = nullptr;
     rc = get_workspace(c, stream, (size_t)gx * OC * sizeof(float), &ws);
     if (rc) return rc;
-    field_sum_partial_kernel<<<dim3((unsigned)gx, (unsigned)gy), kFieldSumThreads, 0, stream>>>(
+    if (!t_dry) field_sum_partial_kernel<<<dim3((unsigned)gx, (unsigned)gy), kFieldSumThreads, 0, stream>>>(
         reinterpret_cast<const float4*>(deltaY), rows, cols4, CT, RL, reinterpret_cast<float4*>(ws));
     note_launch("field_sum");
     rc = check_launch("field_sum_partial_kernel");
@@ -1341,7 +1785,7 @@ int alpha_conv_bias_grad(const float* deltaY, long long rows, int OC, float* del
     // (few rows, so the pass is bound by load latency: many lanes, few loads each)
     const int CT2 = cols4 < 4 ? cols4 : 4;
     const int RL2 = 64;
-    field_sum_partial_kernel<<<dim3(1, (unsigned)((cols4 + CT2 - 1) / CT2)), kFieldSumThreads, 0, stream>>>(
+    if (!t_dry) field_sum_partial_kernel<<<dim3(1, (unsigned)((cols4 + CT2 - 1) / CT2)), kFieldSumThreads, 0, stream>>>(
         reinterpret_cast<const float4*>(ws), gx, cols4, CT2, RL2, reinterpret_cast<float4*>(deltaB));
     note_launch("field_sum");
     return check_launch("field_sum_partial_kernel");
@@ -1357,8 +1801,9 @@ int alpha_conv3d_forward_leakyRelu(const AlphaConvShape* s, const float* X, cons
     DeviceCtx* c;
     rc = get_ctx(&c);
     if (rc) return rc;
-    int algo = g_algo.load();
+    int algo = cur_algo();
     if (algo == ALPHA_ALGO_WINOGRAD) algo = ALPHA_ALGO_AUTO;   // the Winograd output pass has no activation stage
+    ws_begin(c, (cudaStream_t)stream_);
     return forward_direct(c, s, X, W, bias, Y, (cudaStream_t)stream_, algo, 1, k);
 }
 
@@ -1378,7 +1823,7 @@ static int forward_direct(DeviceCtx* c, const AlphaConvShape* s, const float* X,
         pl.out = Y; pl.oH = s->OH; pl.oW = s->OW; pl.ncols = s->OC;
         pl.W = W; pl.wOC = s->OC; pl.wIC = s->IC; pl.bias = bias; pl.act_on = act_on; pl.act_k = act_k;
         pl.b_mn = false; pl.flip = false; pl.kdim = s->IC;
-        const int mode3x = g_math.load() == ALPHA_MATH_3XTF32;
+        const int mode3x = cur_mode3x();
         if (tiny_image(s->OH, s->OW) && (s->FH > 1 || s->FW > 1) && patch_path_ok(s) && env_tile_mode() != 1) {
             rc = launch_patch_gemm(c, pl, mode3x, stream);
             if (rc != 1) return rc;
@@ -1393,11 +1838,11 @@ static int forward_direct(DeviceCtx* c, const AlphaConvShape* s, const float* X,
         pl.FH = s->FH; pl.FW = s->FW; pl.sh = s->sh; pl.sw = s->sw; pl.pad_h = s->ph; pl.pad_w = s->pw;
         pl.out = Y; pl.oH = s->OH; pl.oW = s->OW; pl.ncols = s->OC;
         pl.W = W; pl.wOC = s->OC; pl.wIC = s->IC; pl.bias = bias; pl.act_on = act_on; pl.act_k = act_k;
-        rc = launch_patch_gemm(c, pl, g_math.load() == ALPHA_MATH_3XTF32, stream);
+        rc = launch_patch_gemm(c, pl, cur_mode3x(), stream);
         if (rc != 1) return rc;
     }
     const size_t total = (size_t)s->N * s->OH * s->OW * s->OC;
-    conv_fwd_simt<<<simt_grid(total, c->sm_count), 256, 0, stream>>>(X, W, bias, Y, to_dev_shape(s), act_on, act_k);
+    if (!t_dry) conv_fwd_simt<<<simt_grid(total, c->sm_count), 256, 0, stream>>>(X, W, bias, Y, to_dev_shape(s), act_on, act_k);
     note_launch("simt");
     return check_launch("conv_fwd_simt");
 }
@@ -1413,7 +1858,8 @@ int alpha_conv3d_deltaX(const AlphaConvShape* s, const float* deltaY, const floa
     rc = get_ctx(&c);
     if (rc) return rc;
     cudaStream_t stream = (cudaStream_t)stream_;
-    const int algo = g_algo.load();
+    ws_begin(c, stream);
+    const int algo = cur_algo();
     const int pad_h = s->FH - 1 - s->ph, pad_w = s->FW - 1 - s->pw;
     const bool tensor_ok = s->sh == 1 && s->sw == 1 && pick_kc(s->OC) != 0 && pad_h >= 0 && pad_w >= 0 &&
                            pad_h < 128 && pad_w < 128 && s->IH == s->OH + s->FH - 1 - 2 * s->ph &&
@@ -1427,26 +1873,30 @@ int alpha_conv3d_deltaX(const AlphaConvShape* s, const float* deltaY, const floa
         pl.out = deltaX; pl.oH = s->IH; pl.oW = s->IW; pl.ncols = s->IC;
         pl.W = W; pl.wOC = s->OC; pl.wIC = s->IC; pl.bias = nullptr;
         pl.b_mn = true; pl.flip = true; pl.kdim = s->OC;
-        const int mode3x = g_math.load() == ALPHA_MATH_3XTF32;
-        if (env_tile_mode() != 1 && s->OC % 32 == 0 && taps_fit64(s) && env_int("ALPHA_DX_TRANSPOSE", 1)) {
+        const int mode3x = cur_mode3x();
+        if (env_tile_mode() != 1 && s->OC % 32 == 0 && taps_fit64(s) && opt(OPT_DX_TRANSPOSE)) {
             // deltaX as a forward conv over deltaY with Wt[ic][rotated tap][oc], built once per call
             const int taps = s->FH * s->FW;
             const size_t nW = (size_t)s->OC * taps * s->IC;
             float* ws = nullptr;
-            rc = get_workspace(c, stream, (mode3x ? 2 : 1) * nW * sizeof(float), &ws);
+            bool fresh = true;
+            const DeviceCtx::WeightKey wkey{W, WK_DX_S1, s->OC, s->IC, s->FH * 256 + s->FW, 0, mode3x};
+            rc = weight_planes(c, stream, wkey, (mode3x ? 2 : 1) * nW * sizeof(float), &ws, &fresh);
             if (rc) return rc;
             IgemmPlan pt = pl;
             pt.W = ws; pt.W_lo = mode3x ? ws + nW : nullptr;
             pt.wOC = s->IC; pt.wIC = s->OC; pt.b_mn = false; pt.flip = false;
-            // decide first whether the halo kernel takes the shape; only then pay for the transpose
-            dim3 tg((s->IC + 31) / 32, (s->OC + 31) / 32, taps);
-            TapMap map{};
-            map.n = taps;
-            for (int t = 0; t < taps; ++t) map.src[t] = taps - 1 - t;
-            transpose_weights_kernel<<<tg, 256, 0, stream>>>(W, ws, mode3x ? ws + nW : nullptr, s->OC, s->IC, taps, map, mode3x);
-            note_launch("transpose_w");
-            rc = check_launch("transpose_weights_kernel");
-            if (rc) return rc;
+            if (fresh) {
+                dim3 tg((s->IC + 31) / 32, (s->OC + 31) / 32, taps);
+                TapMap map{};
+                map.n = taps;
+                for (int t = 0; t < taps; ++t) map.src[t] = taps - 1 - t;
+                if (!t_dry) transpose_weights_kernel<<<tg, 256, 0, stream>>>(W, ws, mode3x ? ws + nW : nullptr, s->OC, s->IC, taps, map, mode3x);
+                note_launch("transpose_w");
+                rc = check_launch("transpose_weights_kernel");
+                if (rc) return rc;
+                weight_planes_ready(c, stream, wkey);
+            }
             if (!mode3x) pt.W_lo = nullptr;
             if (tiny_image(s->IH, s->IW) && (s->FH > 1 || s->FW > 1) && (long long)taps * s->OC <= 16384) {
                 rc = launch_patch_gemm(c, pt, mode3x, stream);
@@ -1457,16 +1907,16 @@ int alpha_conv3d_deltaX(const AlphaConvShape* s, const float* deltaY, const floa
         }
         rc = launch_halo(c, pl, mode3x, stream);
         if (rc != 1) return rc;
-        return launch_igemm(c, pl, g_math.load() == ALPHA_MATH_3XTF32, stream);
+        return launch_igemm(c, pl, cur_mode3x(), stream);
     }
     if (algo != ALPHA_ALGO_SIMT && (s->sh > 1 || s->sw > 1)) {
-        rc = launch_dx_col2im(c, s, deltaY, W, deltaX, g_math.load() == ALPHA_MATH_3XTF32, stream);
+        rc = launch_dx_col2im(c, s, deltaY, W, deltaX, cur_mode3x(), stream);
         if (rc != 1) return rc;
-        rc = launch_dx_phases(c, s, deltaY, W, deltaX, g_math.load() == ALPHA_MATH_3XTF32, stream);
+        rc = launch_dx_phases(c, s, deltaY, W, deltaX, cur_mode3x(), stream);
         if (rc != 1) return rc;
     }
     const size_t total = (size_t)s->N * s->IH * s->IW * s->IC;
-    conv_dx_simt<<<simt_grid(total, c->sm_count), 256, 0, stream>>>(deltaY, W, deltaX, to_dev_shape(s));
+    if (!t_dry) conv_dx_simt<<<simt_grid(total, c->sm_count), 256, 0, stream>>>(deltaY, W, deltaX, to_dev_shape(s));
     note_launch("simt");
     return check_launch("conv_dx_simt");
 }
@@ -1480,7 +1930,8 @@ int alpha_conv3d_deltaW(const AlphaConvShape* s, const float* X, const float* de
     rc = get_ctx(&c);
     if (rc) return rc;
     cudaStream_t stream = (cudaStream_t)stream_;
-    const int algo = g_algo.load();
+    ws_begin(c, stream);
+    const int algo = cur_algo();
     const bool tensor_ok = (s->IC % 32 == 0) && s->ph < 128 && s->pw < 128 && s->FH <= 256 && s->FW <= 256;
     if (algo == ALPHA_ALGO_TENSOR && !tensor_ok)
         return fail(ALPHA_E_ARG, "tensor deltaW path needs IC %% 32 == 0 (IC=%d)", s->IC);
@@ -1496,95 +1947,93 @@ int alpha_conv3d_deltaW(const AlphaConvShape* s, const float* X, const float* de
         float* dWp = K == Kp ? deltaW : A + M * Kp;
         AlphaConvShape t = *s;
         t.IH = s->OH; t.IW = s->OW; t.IC = Kp; t.FH = 1; t.FW = 1; t.sh = 1; t.sw = 1; t.ph = 0; t.pw = 0;
-        rc = launch_dw_halo(c, &t, A, deltaY, dWp, g_math.load() == ALPHA_MATH_3XTF32, stream);
+        rc = launch_dw_halo(c, &t, A, deltaY, dWp, cur_mode3x(), stream);
         if (rc < 0) return rc;
         if (rc == 0) {
             if (K == Kp) return ALPHA_OK;
             const size_t total4 = (size_t)s->OC * (K / 4);
             size_t blocks = (total4 + 255) / 256;
             if (blocks > (size_t)c->sm_count * 16) blocks = (size_t)c->sm_count * 16;
-            unpad_rows_kernel<<<(unsigned)blocks, 256, 0, stream>>>(dWp, deltaW, s->OC, K, Kp);
+            if (!t_dry) unpad_rows_kernel<<<(unsigned)blocks, 256, 0, stream>>>(dWp, deltaW, s->OC, K, Kp);
             note_launch("dw_patch");
             return check_launch("unpad_rows_kernel");
         }
     }
     if (algo == ALPHA_ALGO_SIMT || !tensor_ok) {
         const size_t total = (size_t)s->OC * s->FH * s->FW * s->IC;
-        conv_dw_simt<<<(unsigned)total, 128, 0, stream>>>(X, deltaY, deltaW, to_dev_shape(s));
+        if (!t_dry) conv_dw_simt<<<(unsigned)total, 128, 0, stream>>>(X, deltaY, deltaW, to_dev_shape(s));
         note_launch("simt");
         return check_launch("conv_dw_simt");
     }
 
-    const int mode3x = g_math.load() == ALPHA_MATH_3XTF32;
+    const int mode3x = cur_mode3x();
     rc = launch_dw_halo(c, s, X, deltaY, deltaW, mode3x, stream);
     if (rc != 1) return rc;
-    DwParams p{};
-    p.status = c->status;
-    p.Npix = s->N * s->OH * s->OW;
-    p.OHo = s->OH; p.OWo = s->OW; p.sh = s->sh; p.sw = s->sw; p.ph = s->ph; p.pw = s->pw;
-    p.FH = s->FH; p.FW = s->FW; p.IC = s->IC; p.OC = s->OC;
-    p.icb = s->IC / 32;
-    p.MB = s->FH * s->FW * p.icb;
-    int BN = ((s->OC + 31) / 32) * 32;
-    if (BN > 256) BN = 256;
-    p.BN = BN;
-    const int MT = (p.MB + 3) / 4;
-    int G = 512 / BN;  // accumulators of BN columns that fit the 512 tensor-memory columns
-    if (G > MT) G = MT;
-    const int groups = (MT + G - 1) / G;
-    G = (MT + groups - 1) / groups;  // balance the groups
-    p.G = G;
-    p.KP = 32;
-    p.tmem_cols = pow2_cols(G * BN);
-    p.idesc = make_idesc_tf32(kBM, BN, true, true);
-    p.mode3x = mode3x;
-    const int n_tiles = (s->OC + BN - 1) / BN;
-    p.total_chunks = (p.Npix + p.KP - 1) / p.KP;
-    int splits = c->sm_count / (groups * n_tiles);
-    if (splits < 1) splits = 1;
-    if (splits > p.total_chunks) splits = p.total_chunks;
-    p.chunks_per_split = (p.total_chunks + splits - 1) / splits;
-    splits = (p.total_chunks + p.chunks_per_split - 1) / p.chunks_per_split;
-    const size_t sizeW = (size_t)s->OC * s->FH * s->FW * s->IC;
+    DwSplitPlan pl;
+    rc = plan_dw_split(s, mode3x, sm_budget(c), &pl);
+    if (rc) return rc;
     float* ws = nullptr;
-    if (splits > 1) {
-        rc = get_workspace(c, stream, sizeW * splits * sizeof(float), &ws);
+    if (pl.splits > 1) {
+        rc = get_workspace(c, stream, pl.sizeW * pl.splits * sizeof(float), &ws);
         if (rc) return rc;
-        p.out = ws;
-        p.split_stride = sizeW;
-    } else {
-        p.out = deltaW;
-        p.split_stride = 0;
     }
-    const uint32_t blk = p.KP * 128;
-    const uint32_t stage = (4 * blk + (BN / 32) * blk) * (mode3x ? 2 : 1);
-    int stages = (int)((200u * 1024) / stage);
-    if (stages > 6) stages = 6;
-    if (stages < 1) return fail(ALPHA_E_ARG, "deltaW stage of %u bytes does not fit shared memory", stage);
-    p.stages = stages;
-    const size_t smem = (size_t)stages * stage + (3 * stages + 2) * 8 + 1024;
+    return launch_dw_split(s, X, deltaY, deltaW, ws, c->status, pl, stream, "dw");
+}
 
-    CUtensorMap tmX, tmDY;
-    rc = make_im2col_map(&tmX, X, s->N, s->IH, s->IW, s->IC, s->FH, s->FW, s->sh, s->sw, s->ph, s->pw, 32, p.KP,
-                         CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
-    if (rc) return rc;
-    cuuint64_t dd[2] = {(cuuint64_t)s->OC, (cuuint64_t)p.Npix};
-    cuuint64_t ds[1] = {(cuuint64_t)s->OC * 4};
-    cuuint32_t box[2] = {32, (cuuint32_t)p.KP};
-    rc = make_tiled_map(&tmDY, deltaY, 2, dd, ds, box, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
-    if (rc) return rc;
+static int check_call_options(int math_mode, int algo)
+{
+    if (math_mode != -1 && math_mode != ALPHA_MATH_3XTF32 && math_mode != ALPHA_MATH_TF32)
+        return fail(ALPHA_E_ARG, "unknown math mode %d (-1 = the process default)", math_mode);
+    if (algo != -1 && (algo < ALPHA_ALGO_AUTO || algo > ALPHA_ALGO_WINOGRAD))
+        return fail(ALPHA_E_ARG, "unknown algo %d (-1 = the process default)", algo);
+    return ALPHA_OK;
+}
 
-    dim3 grid(groups, n_tiles, splits);
-    conv_dw_kernel<<<grid, kIgemmThreads, smem, stream>>>(tmX, tmDY, p);
-    note_launch("dw");
-    rc = check_launch("conv_dw_kernel");
+int alpha_conv3d_forward_ex(const AlphaConvShape* s, const float* X, const float* W, const float* bias, float* Y,
+                            int math_mode, int algo, alpha_stream_t stream)
+{
+    int rc = check_call_options(math_mode, algo);
     if (rc) return rc;
-    if (splits > 1) {
-        const size_t n4 = sizeW / 4;
-        dw_reduce_kernel<<<(unsigned)((n4 + 63) / 64), 64, 0, stream>>>(ws, sizeW, splits, deltaW, n4, 0);
-        note_launch("dw");
-        rc = check_launch("dw_reduce_kernel");
+    CallOptions guard(math_mode, algo);
+    return alpha_conv3d_forward(s, X, W, bias, Y, stream);
+}
+
+int alpha_conv3d_deltaX_ex(const AlphaConvShape* s, const float* deltaY, const float* W, float* deltaX, int math_mode,
+                           int algo, alpha_stream_t stream)
+{
+    int rc = check_call_options(math_mode, algo);
+    if (rc) return rc;
+    CallOptions guard(math_mode, algo);
+    return alpha_conv3d_deltaX(s, deltaY, W, deltaX, stream);
+}
+
+int alpha_conv3d_deltaW_ex(const AlphaConvShape* s, const float* X, const float* deltaY, float* deltaW, int math_mode,
+                           int algo, alpha_stream_t stream)
+{
+    int rc = check_call_options(math_mode, algo);
+    if (rc) return rc;
+    CallOptions guard(math_mode, algo);
+    return alpha_conv3d_deltaW(s, X, deltaY, deltaW, stream);
+}
+
+int alpha_conv_workspace_bytes(const AlphaConvShape* s, int op, size_t* bytes)
+{
+    if (!s || !bytes) return fail(ALPHA_E_ARG, "workspace_bytes: null argument");
+    // the call itself, with launches and copies switched off and placeholder addresses: what it asks
+    // get_workspace for is what it will ask for with real tensors
+    float* fake = reinterpret_cast<float*>(static_cast<uintptr_t>(1) << 31);
+    t_dry = true;
+    t_dry_cur = t_dry_peak = 0;
+    int rc;
+    switch (op) {
+    case ALPHA_OP_FORWARD: rc = alpha_conv3d_forward(s, fake, fake, nullptr, fake, nullptr); break;
+    case ALPHA_OP_DELTAX: rc = alpha_conv3d_deltaX(s, fake, fake, fake, nullptr); break;
+    case ALPHA_OP_DELTAW: rc = alpha_conv3d_deltaW(s, fake, fake, fake, nullptr); break;
+    case ALPHA_OP_BIAS_GRAD: rc = alpha_conv_bias_grad(fake, (long long)s->N * s->OH * s->OW, s->OC, fake, nullptr); break;
+    default: rc = fail(ALPHA_E_ARG, "workspace_bytes: unknown op %d", op);
     }
+    t_dry = false;
+    *bytes = t_dry_peak;
     return rc;
 }
 
@@ -1595,87 +2044,28 @@ int alpha_conv3d_deltaW_noalloc(const AlphaConvShape* s, const float* X, const f
 {
     int rc = check_shape(s, X, deltaY, deltaW);
     if (rc) return rc;
-    if (s->IC % 32 != 0 || s->ph >= 128 || s->pw >= 128 || s->FH > 256 || s->FW > 256)
+    if (s->IC % 32 != 0)
         return fail(ALPHA_E_ARG, "deltaW_noalloc runs the tensor-core kernel only: IC must be a multiple of 32 (IC=%d)", s->IC);
+    if (s->ph >= 128 || s->pw >= 128 || s->FH > 256 || s->FW > 256)
+        return fail(ALPHA_E_ARG, "deltaW_noalloc: the im2col tensor map takes padding < 128 and filters up to 256 x 256 "
+                    "(ph=%d pw=%d FH=%d FW=%d)", s->ph, s->pw, s->FH, s->FW);
     NoAllocCtx* c;
     rc = get_noalloc_ctx(&c);
     if (rc) return rc;
-    cudaStream_t stream = (cudaStream_t)stream_;
-
-    // Same tiling and split choice as alpha_conv3d_deltaW, so that both entry points return the
-    // same bits for the same input.
-    const int mode3x = g_math.load() == ALPHA_MATH_3XTF32;
-    DwParams p{};
-    p.status = c->status;
-    p.Npix = s->N * s->OH * s->OW;
-    p.OHo = s->OH; p.OWo = s->OW; p.sh = s->sh; p.sw = s->sw; p.ph = s->ph; p.pw = s->pw;
-    p.FH = s->FH; p.FW = s->FW; p.IC = s->IC; p.OC = s->OC;
-    p.icb = s->IC / 32;
-    p.MB = s->FH * s->FW * p.icb;
-    int BN = ((s->OC + 31) / 32) * 32;
-    if (BN > 256) BN = 256;
-    p.BN = BN;
-    const int MT = (p.MB + 3) / 4;
-    int G = 512 / BN;
-    if (G > MT) G = MT;
-    const int groups = (MT + G - 1) / G;
-    G = (MT + groups - 1) / groups;
-    p.G = G;
-    p.KP = 32;
-    p.tmem_cols = pow2_cols(G * BN);
-    p.idesc = make_idesc_tf32(kBM, BN, true, true);
-    p.mode3x = mode3x;
-    const int n_tiles = (s->OC + BN - 1) / BN;
-    p.total_chunks = (p.Npix + p.KP - 1) / p.KP;
-    int splits = c->sm_count / (groups * n_tiles);
-    if (splits < 1) splits = 1;
-    if (splits > p.total_chunks) splits = p.total_chunks;
-    p.chunks_per_split = (p.total_chunks + splits - 1) / splits;
-    splits = (p.total_chunks + p.chunks_per_split - 1) / p.chunks_per_split;
-    const size_t sizeW = (size_t)s->OC * s->FH * s->FW * s->IC;
-    if (splits > 1) {
-        const size_t need = sizeW * splits * sizeof(float);
+    // The split-K im2col kernel with the plan alpha_conv3d_deltaW uses for it (plan_dw_split), the
+    // partial sums in the fixed array instead of the growable workspace.
+    DwSplitPlan pl;
+    rc = plan_dw_split(s, cur_mode3x(), c->sm_count, &pl);
+    if (rc) return rc;
+    if (pl.splits > 1) {
+        const size_t need = pl.sizeW * pl.splits * sizeof(float);
         if (need > kNoAllocScratchBytes)
             return fail(ALPHA_E_NOSCRATCH,
                         "deltaW_noalloc: %d split-K partials of %zu floats need %zu bytes, the fixed scratch holds %zu; "
                         "use alpha_conv3d_deltaW for this shape",
-                        splits, sizeW, need, (size_t)kNoAllocScratchBytes);
-        p.out = c->scratch;
-        p.split_stride = sizeW;
-    } else {
-        p.out = deltaW;
-        p.split_stride = 0;
+                        pl.splits, pl.sizeW, need, (size_t)kNoAllocScratchBytes);
     }
-    const uint32_t blk = p.KP * 128;
-    const uint32_t stage = (4 * blk + (BN / 32) * blk) * (mode3x ? 2 : 1);
-    int stages = (int)((200u * 1024) / stage);
-    if (stages > 6) stages = 6;
-    if (stages < 1) return fail(ALPHA_E_ARG, "deltaW stage of %u bytes does not fit shared memory", stage);
-    p.stages = stages;
-    const size_t smem = (size_t)stages * stage + (3 * stages + 2) * 8 + 1024;
-
-    CUtensorMap tmX, tmDY;
-    rc = make_im2col_map(&tmX, X, s->N, s->IH, s->IW, s->IC, s->FH, s->FW, s->sh, s->sw, s->ph, s->pw, 32, p.KP,
-                         CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
-    if (rc) return rc;
-    cuuint64_t dd[2] = {(cuuint64_t)s->OC, (cuuint64_t)p.Npix};
-    cuuint64_t ds[1] = {(cuuint64_t)s->OC * 4};
-    cuuint32_t box[2] = {32, (cuuint32_t)p.KP};
-    rc = make_tiled_map(&tmDY, deltaY, 2, dd, ds, box, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
-    if (rc) return rc;
-
-    dim3 grid(groups, n_tiles, splits);
-    conv_dw_kernel<<<grid, kIgemmThreads, smem, stream>>>(tmX, tmDY, p);
-    note_launch("dw_noalloc");
-    rc = check_launch("conv_dw_kernel");
-    if (rc) return rc;
-    if (splits > 1) {
-        const size_t n4 = sizeW / 4;
-        dw_reduce_kernel<<<(unsigned)((n4 + 63) / 64), 64, 0, stream>>>(c->scratch, sizeW, splits, deltaW, n4, 0);
-        note_launch("dw_noalloc");
-        rc = check_launch("dw_reduce_kernel");
-    }
-    return rc;
+    return launch_dw_split(s, X, deltaY, deltaW, c->scratch, c->status, pl, (cudaStream_t)stream_, "dw_noalloc");
 }
 
 int alpha_conv3d_deltaW_noalloc_status(void)

@@ -262,6 +262,17 @@ __global__ void split_tensor_kernel(const float4* __restrict__ src, float4* __re
     }
 }
 
+// lo plane of a tensor whose fp32 words serve as the hi plane where they lie (the tensor core reads
+// only the upper 19 bits of an operand word): lo = tf32(x - trunc19(x)).
+__global__ void split_lo_kernel(const float4* __restrict__ src, float4* __restrict__ lo, size_t n4)
+{
+    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n4;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const float4 a = src[i];
+        lo[i] = make_float4(tf32_lo_of_trunc(a.x), tf32_lo_of_trunc(a.y), tf32_lo_of_trunc(a.z), tf32_lo_of_trunc(a.w));
+    }
+}
+
 // Source filter taps of a transposed weight tensor: output tap t reads W[.][src[t]][.].
 struct TapMap {
     int n;

@@ -19,9 +19,14 @@ struct Streams {
 inline Streams get_streams(JNIEnv* env, jlongArray arr, jint length)
 {
     Streams s{};
+    // a null array, or a length beyond the Java array (GetLongArrayRegion then leaves an
+    // ArrayIndexOutOfBoundsException pending and the buffer unwritten), yields an empty list: the
+    // native fails with "empty stream array" or the pending exception reaches the Java caller
+    if (!arr) return s;
     s.n = length < 0 ? 0 : (length > kMaxStreams ? kMaxStreams : length);
-    jlong tmp[kMaxStreams];
+    jlong tmp[kMaxStreams] = {};
     if (s.n > 0) env->GetLongArrayRegion(arr, 0, s.n, tmp);
+    if (env->ExceptionCheck()) { s.n = 0; return s; }
     for (int i = 0; i < s.n; ++i) s.v[i] = tmp[i];
     return s;
 }

@@ -8,6 +8,9 @@
 
 namespace alpha {
 int launch_buf_summary(cudaStream_t stream, const float* buf, float* deltaW, int part, size_t sizeW);
+int launch_split_lo(cudaStream_t stream, const float* W, float* lo, size_t n);
+void set_prepared_lo(const float* W, const float* lo);
+void set_caller_scratch(void* ptr, size_t bytes);
 }
 using namespace alpha;
 
@@ -48,16 +51,31 @@ static int dw(const int64_t* streams, int length, float* X, int IH, int IW, floa
     return alpha_conv3d_deltaW(&s, X, dY, dW, first_stream(streams, length));
 }
 
-// deltaW through a split-K entry: full gradient into deltaW, zeros into the caller's buffers.
+// Forward through a native that carries CW: kernel_remode has left the lo plane of W there, so the
+// 3xTF32 kernels take W as the hi plane and CW as the lo plane and the call needs no scratch of its own.
+static int fwd_cw(const int64_t* streams, int length, float* X, int IH, int IW, float* W, float* CW, int FH, int FW,
+                  float* Y, int OH, int OW, int N, int IC, int OC, int sh, int sw, int ph, int pw)
+{
+    if (CW && (reinterpret_cast<uintptr_t>(CW) & 15) == 0) set_prepared_lo(W, CW);
+    const int rc = fwd(streams, length, X, IH, IW, W, FH, FW, Y, OH, OW, N, IC, OC, sh, sw, ph, pw);
+    set_prepared_lo(nullptr, nullptr);
+    return rc;
+}
+
+// deltaW through a split-K entry: full gradient into deltaW, zeros into the caller's buffers.  The
+// buffers serve as this call's scratch (per-CTA partial sums) as far as they reach.
 static int dw_sk(const int64_t* streams, int length, int GridZ, float* X, int IH, int IW, float* dY,
                  int OH, int OW, float* dW, float* dW_buf, int FH, int FW, int N, int IC, int OC,
                  int sh, int sw, int ph, int pw)
 {
+    if (GridZ > 1 && !dW_buf) return fail(ALPHA_E_ARG, "GridZ=%d but deltaW_buf is null", GridZ);
+    const size_t buf_bytes = GridZ > 1 ? static_cast<size_t>(GridZ - 1) * OC * FH * FW * IC * sizeof(float) : 0;
+    if (buf_bytes && (reinterpret_cast<uintptr_t>(dW_buf) & 255) == 0) set_caller_scratch(dW_buf, buf_bytes);
     int rc = dw(streams, length, X, IH, IW, dY, OH, OW, dW, FH, FW, N, IC, OC, sh, sw, ph, pw);
+    set_caller_scratch(nullptr, 0);
     if (rc) return rc;
     if (GridZ > 1) {
-        if (!dW_buf) return fail(ALPHA_E_ARG, "GridZ=%d but deltaW_buf is null", GridZ);
-        const size_t bytes = static_cast<size_t>(GridZ - 1) * OC * FH * FW * IC * sizeof(float);
+        const size_t bytes = buf_bytes;
         cudaError_t e = cudaMemsetAsync(dW_buf, 0, bytes, (cudaStream_t)first_stream(streams, length));
         if (e != cudaSuccess) return fail(ALPHA_E_CUDA, "cudaMemsetAsync(deltaW_buf): %s", cudaGetErrorString(e));
     }
@@ -107,36 +125,40 @@ int alpha_Cuda_conv3D_conv3D_W1(const int64_t* streams, int length, float* X, in
 {
     return fwd(streams, length, X, IH, IW, W, 1, 1, Y, IH, IW, N, IC, OC, 1, 1, 0, 0);
 }
-// The reference transposes W into CW[FH,FW,IC,OC] here; the tensor path reads W in place through
-// its own tensor map, so nothing has to be prepared and CW stays untouched.
-int alpha_Cuda_conv3D_kernel_remode(int64_t, float* W, float* CW, int FH, int FW, int OC, int IC)
+// The reference transposes W into CW[FH,FW,IC,OC] here.  The tensor path reads W in place through its
+// own tensor map; what it needs prepared is the lo plane of the 3xTF32 split, lo = tf32(W - trunc19(W)),
+// and CW (OC*FH*FW*IC floats, private between this native and the conv3D_GemmR* consumers) holds it.
+int alpha_Cuda_conv3D_kernel_remode(int64_t stream, float* W, float* CW, int FH, int FW, int OC, int IC)
 {
     if (!W || !CW || FH <= 0 || FW <= 0 || OC <= 0 || IC <= 0) return fail(ALPHA_E_ARG, "bad kernel_remode arguments");
-    return ALPHA_OK;
+    if ((IC & 3) || ((reinterpret_cast<uintptr_t>(W) | reinterpret_cast<uintptr_t>(CW)) & 15))
+        return fail(ALPHA_E_ARG, "kernel_remode: IC must be a multiple of 4 and W, CW 16-byte aligned");
+    return launch_split_lo(reinterpret_cast<cudaStream_t>(static_cast<intptr_t>(stream)), W, CW,
+                           static_cast<size_t>(OC) * FH * FW * IC);
 }
 int alpha_Cuda_conv3D_conv3D_GemmR(const int64_t* streams, int length, float* X, int IH, int IW,
-                                   float* W, float*, int FH, int FW, float* Y, int OH, int OW, int N,
+                                   float* W, float* CW, int FH, int FW, float* Y, int OH, int OW, int N,
                                    int IC, int OC, int sh, int sw, int ph, int pw)
 {
-    return fwd(streams, length, X, IH, IW, W, FH, FW, Y, OH, OW, N, IC, OC, sh, sw, ph, pw);
+    return fwd_cw(streams, length, X, IH, IW, W, CW, FH, FW, Y, OH, OW, N, IC, OC, sh, sw, ph, pw);
 }
 int alpha_Cuda_conv3D_conv3D_GemmR_texture(const int64_t* streams, int length, float* X, int IH,
-                                           int IW, float* W, float*, int FH, int FW, float* Y,
+                                           int IW, float* W, float* CW, int FH, int FW, float* Y,
                                            int OH, int OW, int N, int IC, int OC, int sh, int sw,
                                            int ph, int pw)
 {
-    return fwd(streams, length, X, IH, IW, W, FH, FW, Y, OH, OW, N, IC, OC, sh, sw, ph, pw);
+    return fwd_cw(streams, length, X, IH, IW, W, CW, FH, FW, Y, OH, OW, N, IC, OC, sh, sw, ph, pw);
 }
 int alpha_Cuda_conv3D_conv3D_GemmV2R(int, const int64_t* streams, int length, float* X, int IH,
-                                     int IW, float* W, float*, int FH, int FW, float* Y, int OH,
+                                     int IW, float* W, float* CW, int FH, int FW, float* Y, int OH,
                                      int OW, int N, int IC, int OC, int sh, int sw, int ph, int pw)
 {
-    return fwd(streams, length, X, IH, IW, W, FH, FW, Y, OH, OW, N, IC, OC, sh, sw, ph, pw);
+    return fwd_cw(streams, length, X, IH, IW, W, CW, FH, FW, Y, OH, OW, N, IC, OC, sh, sw, ph, pw);
 }
 int alpha_Cuda_conv3D_conv3D_GemmR_W1(const int64_t* streams, int length, float* X, int IH, int IW,
-                                      float* W, float*, float* Y, int N, int IC, int OC)
+                                      float* W, float* CW, float* Y, int N, int IC, int OC)
 {
-    return fwd(streams, length, X, IH, IW, W, 1, 1, Y, IH, IW, N, IC, OC, 1, 1, 0, 0);
+    return fwd_cw(streams, length, X, IH, IW, W, CW, 1, 1, Y, IH, IW, N, IC, OC, 1, 1, 0, 0);
 }
 
 // ---- Cuda_dconv3D_deltaX ------------------------------------------------------------------------

@@ -28,11 +28,18 @@ def _stream(stream=None):
 class CudaFloat32EngineBase:
     """Address-level operators.  Arguments are device addresses (ints) or torch CUDA tensors."""
 
-    def __init__(self, stream=None):
+    def __init__(self, stream=None, math=None, algo=None):
+        """math ('3xtf32' / 'tf32') and algo ('auto' / 'tensor' / 'simt' / 'winograd') are this engine's own
+        settings, passed with every call; None follows the process-wide default of lib.set_math_mode /
+        lib.set_algo.  Two engines of one process may differ."""
         self._lib = _l.load()
         self._stream = stream
-        # option flags of the reference; they chose among SIMT kernel families there and are kept
-        # for API compatibility (every family maps onto the same tensor-core kernel here).
+        self._math = -1 if math is None else {"3xtf32": _l.ALPHA_MATH_3XTF32, "tf32": _l.ALPHA_MATH_TF32}[math]
+        self._algo = -1 if algo is None else {"auto": 0, "tensor": 1, "simt": 2, "winograd": 3}[algo]
+        # Option flags of the reference.  There they choose among SIMT kernel families (texture loads,
+        # remoded weights, the V2 tilings, split-K part counts); every family maps onto the same
+        # tensor-core kernels here, so the setters below only store the value: they exist so that host
+        # code written against the reference's engine runs unchanged, and nothing reads them.
         self._conv3D_useTexture = True
         self._conv3D_remode = True
         self._conv3D_remode_V2_Q = 1.05
@@ -113,6 +120,9 @@ class CudaFloat32EngineBase:
         return self
 
     # ---- operators ------------------------------------------------------------------------------
+    def _own_settings(self):
+        return self._math >= 0 or self._algo >= 0
+
     @staticmethod
     def _addr(a):
         return C.c_void_p(a.data_ptr()) if isinstance(a, torch.Tensor) else C.c_void_p(int(a))
@@ -120,6 +130,10 @@ class CudaFloat32EngineBase:
     def conv3D(self, Y_address, OH, OW, X_address, IH, IW, W_address, FH, FW, N, IC, OC, sh, sw, ph, pw):
         """CudaFloat32EngineBase.conv3D (:1355-1474)."""
         a = self._addr
+        if self._own_settings():
+            shp = _l.AlphaConvShape(N, IH, IW, IC, OC, FH, FW, OH, OW, sh, sw, ph, pw)
+            return _l.check(self._lib.alpha_conv3d_forward_ex(C.byref(shp), a(X_address), a(W_address), None, a(Y_address),
+                                                              self._math, self._algo, _stream(self._stream)))
         _l.check(self._lib.alpha_engine_conv3D(a(Y_address), OH, OW, a(X_address), IH, IW, a(W_address),
                                                FH, FW, N, IC, OC, sh, sw, ph, pw, _stream(self._stream)))
 
@@ -127,6 +141,10 @@ class CudaFloat32EngineBase:
                       OC, sh, sw, ph, pw):
         """CudaFloat32EngineBase.conv3D_biased (:1478-1627); the bias add is fused in the epilogue."""
         a = self._addr
+        if self._own_settings():
+            shp = _l.AlphaConvShape(N, IH, IW, IC, OC, FH, FW, OH, OW, sh, sw, ph, pw)
+            return _l.check(self._lib.alpha_conv3d_forward_ex(C.byref(shp), a(X_address), a(W_address), a(Bias_address),
+                                                              a(Y_address), self._math, self._algo, _stream(self._stream)))
         _l.check(self._lib.alpha_engine_conv3D_biased(a(Y_address), OH, OW, a(X_address), IH, IW,
                                                       a(W_address), FH, FW, a(Bias_address), N, IC, OC,
                                                       sh, sw, ph, pw, _stream(self._stream)))
@@ -135,6 +153,10 @@ class CudaFloat32EngineBase:
                        sh, sw, ph, pw):
         """CudaFloat32EngineBase.dconv3D_deltaW (:1666-1762)."""
         a = self._addr
+        if self._own_settings():
+            shp = _l.AlphaConvShape(N, IH, IW, IC, OC, FH, FW, OH, OW, sh, sw, ph, pw)
+            return _l.check(self._lib.alpha_conv3d_deltaW_ex(C.byref(shp), a(X_address), a(deltaY_address), a(deltaW_address),
+                                                             self._math, self._algo, _stream(self._stream)))
         _l.check(self._lib.alpha_engine_dconv3D_deltaW(a(deltaW_address), FH, FW, a(X_address), IH, IW,
                                                        a(deltaY_address), OH, OW, N, IC, OC, sh, sw, ph,
                                                        pw, _stream(self._stream)))
@@ -143,6 +165,10 @@ class CudaFloat32EngineBase:
                        sh, sw, ph, pw):
         """CudaFloat32EngineBase.dconv3D_deltaX (:1796-2005)."""
         a = self._addr
+        if self._own_settings():
+            shp = _l.AlphaConvShape(N, IH, IW, IC, OC, FH, FW, OH, OW, sh, sw, ph, pw)
+            return _l.check(self._lib.alpha_conv3d_deltaX_ex(C.byref(shp), a(deltaY_address), a(W_address), a(deltaX_address),
+                                                             self._math, self._algo, _stream(self._stream)))
         _l.check(self._lib.alpha_engine_dconv3D_deltaX(a(deltaX_address), IH, IW, a(deltaY_address), OH,
                                                        OW, a(W_address), FH, FW, N, IC, OC, sh, sw, ph,
                                                        pw, _stream(self._stream)))

@@ -43,6 +43,19 @@ def load():
     lib.alpha_conv3d_forward_leakyRelu.argtypes = [P, V, V, V, C.c_float, V, V]
     lib.alpha_conv3d_deltaW.argtypes = [P, V, V, V, V]
     lib.alpha_conv_bias_grad.argtypes = [V, C.c_longlong, I, V, V]
+    lib.alpha_conv3d_forward_ex.argtypes = [P, V, V, V, V, I, I, V]
+    lib.alpha_conv3d_deltaX_ex.argtypes = [P, V, V, V, I, I, V]
+    lib.alpha_conv3d_deltaW_ex.argtypes = [P, V, V, V, I, I, V]
+    lib.alpha_conv3d_deltaW_noalloc.argtypes = [P, V, V, V, V]
+    lib.alpha_conv3d_deltaW_noalloc_capacity.restype = C.c_size_t
+    lib.alpha_conv_set_option.argtypes = [C.c_char_p, I]
+    lib.alpha_conv_get_option.argtypes = [C.c_char_p, C.POINTER(I)]
+    lib.alpha_conv_workspace_bytes.argtypes = [P, I, C.POINTER(C.c_size_t)]
+    lib.alpha_conv_set_workspace.argtypes = [V, V, C.c_size_t]
+    lib.alpha_conv_reserve_workspace.argtypes = [V, C.c_size_t]
+    lib.alpha_conv_workspace_in_use.restype = C.c_size_t
+    lib.alpha_conv_weight_cache.argtypes = [I]
+    lib.alpha_conv_weights_updated.argtypes = [V]
     lib.alpha_engine_conv3D.argtypes = [V, I, I, V, I, I, V, I, I] + [I] * 7 + [V]
     lib.alpha_engine_conv3D_biased.argtypes = [V, I, I, V, I, I, V, I, I, V] + [I] * 7 + [V]
     lib.alpha_engine_dconv3D_deltaW.argtypes = [V, I, I, V, I, I, V, I, I] + [I] * 7 + [V]
@@ -120,6 +133,55 @@ def set_math_mode(mode):
 def set_algo(algo):
     a = {"auto": 0, "tensor": 1, "simt": 2, "winograd": 3}.get(algo, algo)
     check(load().alpha_conv_set_algo(int(a)))
+
+
+OPS = {"forward": 0, "deltaX": 1, "deltaW": 2, "bias_grad": 3}
+_OPTION_WORDS = {"auto": 0, "im2col": 1, "halo": 2, "split": 1}
+
+
+def set_option(name, value):
+    """Sets one tuning switch of the tile planners (alpha_conv_set_option); returns the old value."""
+    old = get_option(name)
+    check(load().alpha_conv_set_option(name.encode(), int(_OPTION_WORDS.get(value, value))))
+    return old
+
+
+def get_option(name):
+    v = C.c_int(0)
+    check(load().alpha_conv_get_option(name.encode(), C.byref(v)))
+    return v.value
+
+
+def workspace_bytes(shape, op):
+    """Scratch bytes one call of `op` ('forward', 'deltaX', 'deltaW', 'bias_grad') on `shape` needs."""
+    n = C.c_size_t(0)
+    check(load().alpha_conv_workspace_bytes(C.byref(shape), OPS[op], C.byref(n)))
+    return n.value
+
+
+def set_workspace(stream, ptr, nbytes):
+    check(load().alpha_conv_set_workspace(C.c_void_p(stream), C.c_void_p(ptr) if ptr else None, nbytes))
+
+
+def reserve_workspace(stream, nbytes):
+    check(load().alpha_conv_reserve_workspace(C.c_void_p(stream), nbytes))
+
+
+def release_workspace():
+    check(load().alpha_conv_release_workspace())
+
+
+def workspace_in_use():
+    return int(load().alpha_conv_workspace_in_use())
+
+
+def weight_cache(enable):
+    check(load().alpha_conv_weight_cache(1 if enable else 0))
+
+
+def weights_updated(W=None):
+    """Tells the weight cache that tensor W (a device address; None = every tensor) has new values."""
+    check(load().alpha_conv_weights_updated(C.c_void_p(W) if W else None))
 
 
 def device_status():

@@ -39,15 +39,28 @@ def single_conv(seed=0):
     return X, W, B
 
 
-# ResNet-18-shaped conv stack on 32x32 images (shapes of the reference's CIFAR-10 network,
-# experiments/alpha_code/src/cifar10/resnet18/Net.java:24-77): (IH, IC, OC, F, stride, pad)
+# ResNet-18-shaped conv stack on 32x32 images, the 20 convolutions of the reference's CIFAR-10 network
+# (experiments/alpha_code/src/cifar10/resnet18/Net.java:24-77) in forward order: (IH, IC, OC, F, stride, pad).
+# Every convolution is unbiased (nn.conv3D(false, ...)); the shortcut of a down-sampling block is a 3x3
+# stride-2 convolution there (Net.java:30-34), not a 1x1 one.  The stem's 3 colour planes arrive padded to 4.
+def _basic_block(ih, cin, cout, stride):
+    oh = ih // stride
+    convs = [(ih, cin, cout, 3, stride, 1), (oh, cout, cout, 3, 1, 1)]
+    if stride != 1 or cin != cout:
+        convs.append((ih, cin, cout, 3, stride, 1))
+    return convs
+
+
 RESNET18_CONVS = (
     [(32, 4, 64, 7, 2, 3)]
-    + [(16, 64, 64, 3, 1, 1)] * 4
-    + [(16, 64, 128, 3, 2, 1), (8, 128, 128, 3, 1, 1), (16, 64, 128, 1, 2, 0), (8, 128, 128, 3, 1, 1), (8, 128, 128, 3, 1, 1)]
-    + [(8, 128, 256, 3, 2, 1), (4, 256, 256, 3, 1, 1), (8, 128, 256, 1, 2, 0), (4, 256, 256, 3, 1, 1), (4, 256, 256, 3, 1, 1)]
-    + [(4, 256, 512, 3, 2, 1), (2, 512, 512, 3, 1, 1), (4, 256, 512, 1, 2, 0), (2, 512, 512, 3, 1, 1), (2, 512, 512, 3, 1, 1)]
+    + _basic_block(16, 64, 64, 1) + _basic_block(16, 64, 64, 1)
+    + _basic_block(16, 64, 128, 2) + _basic_block(8, 128, 128, 1)
+    + _basic_block(8, 128, 256, 2) + _basic_block(4, 256, 256, 1)
+    + _basic_block(4, 256, 512, 2) + _basic_block(2, 512, 512, 1)
 )
+# 1x1 stride-2 shortcuts (the usual ResNet form), kept as parity-test shapes
+SHORTCUT_1X1_CONVS = [(16, 64, 128, 1, 2, 0), (8, 128, 256, 1, 2, 0), (4, 256, 512, 1, 2, 0)]
+RESNET18_BATCH = 512
 
 # DCGAN-style generator as transposed convolutions: (IH_in, C_in, C_out), 4x4 stride 2 pad 1
 DCGAN_DECONVS = [(4, 512, 256), (8, 256, 128), (16, 128, 64), (32, 64, 4)]

@@ -35,7 +35,8 @@ extern "C" {
 #define ALPHA_E_CUDA (-2)     /* a CUDA runtime or driver call failed */
 #define ALPHA_E_DEVICE (-3)   /* not an sm_100 device */
 #define ALPHA_E_KERNEL (-4)   /* a kernel reported a protocol error in its status word */
-#define ALPHA_E_NOSCRATCH (-5) /* the problem needs more scratch than alpha_conv3d_deltaW_noalloc owns */
+#define ALPHA_E_NOSCRATCH (-5) /* the call needs more scratch than the fixed or caller-given block holds */
+#define ALPHA_E_CAPTURE (-6)  /* the call would have to allocate while its stream is being captured */
 
 /* math mode of the tensor-core kernels */
 #define ALPHA_MATH_3XTF32 0 /* default: hi/lo split, three TF32 MMAs per product, fp32-faithful */
@@ -63,6 +64,22 @@ int alpha_conv_set_math_mode(int mode);
 int alpha_conv_get_math_mode(void);
 int alpha_conv_set_algo(int algo);
 int alpha_conv_get_algo(void);
+/* Per-call math mode and kernel family: the same three contractions with the two settings as
+ * arguments (-1 = the process default above), for hosts that run engines with different settings in
+ * one process.  (The reference has no such switch: its kernels are fp32 FFMA only.) */
+int alpha_conv3d_forward_ex(const AlphaConvShape* s, const float* X, const float* W, const float* bias,
+                            float* Y, int math_mode, int algo, alpha_stream_t stream);
+int alpha_conv3d_deltaX_ex(const AlphaConvShape* s, const float* deltaY, const float* W, float* deltaX,
+                           int math_mode, int algo, alpha_stream_t stream);
+int alpha_conv3d_deltaW_ex(const AlphaConvShape* s, const float* X, const float* deltaY, float* deltaW,
+                           int math_mode, int algo, alpha_stream_t stream);
+/* Tuning switches of the tile planners by name ("HALO_PAIR", "CONV_TILE", "SM_BUDGET", ...; an
+ * "ALPHA_" prefix is accepted).  The environment variables ALPHA_<NAME> seed them once, at the first
+ * call into the library; no call reads the environment afterwards.  SM_BUDGET = n makes the
+ * persistent kernels spread over n SMs instead of all of them (0 = all), leaving the others to a
+ * collective that runs beside them. */
+int alpha_conv_set_option(const char* name, int value);
+int alpha_conv_get_option(const char* name, int* value);
 /* Reads (and clears) the current device's kernel status word; synchronises the device.
  * 0 = every kernel so far finished its barrier protocol, otherwise the first failure code. */
 int alpha_conv_device_status(void);
@@ -77,6 +94,54 @@ const char* alpha_conv_last_plan(void);
  * producer B wait, MMA patch wait, MMA B wait, MMA accumulator wait, MMA total, epilogue wait,
  * epilogue work, split wait, split work, kernel total).  Copies up to n slots of the last launch. */
 int alpha_conv_debug_counters(unsigned long long* out, int n);
+
+/* ---- scratch memory ----------------------------------------------------------------------------
+ *
+ * The reference's natives get every scratch block (CW, deltaW_buf) from the Java mempool
+ * (CudaFloat32EngineBase.java:1370-1385, 1707-1722).  The kernels here need other scratch: the lo
+ * plane of W in 3xTF32, transposed weights for deltaX, per-CTA partial sums of deltaW, the patch
+ * matrix of the small-channel paths.  Per (device, stream) the library keeps ONE block for it; every
+ * call carves what it needs from the start of its stream's block, so calls on one stream reuse the
+ * same bytes and calls on different streams never share any.
+ *   - By default the block is library-owned and grown on demand with cudaMalloc.  An outgrown block
+ *     is freed once the work that could still use it has finished; nothing is synchronised.  If the
+ *     stream is being captured into a CUDA graph a call that would have to grow the block fails with
+ *     ALPHA_E_CAPTURE instead: run the step once eagerly, or alpha_conv_reserve_workspace, before
+ *     capturing.  A block that a capture saw stays allocated until alpha_conv_release_workspace,
+ *     because replays of that graph keep addressing it.
+ *   - A host that owns all device memory hands in its own block with alpha_conv_set_workspace
+ *     (256-byte aligned; NULL returns the stream to library-owned scratch).  The library then never
+ *     allocates for calls on that stream: a call that needs more fails with ALPHA_E_NOSCRATCH.
+ *     alpha_conv_workspace_bytes tells in advance what one call needs (op: ALPHA_OP_*; current math
+ *     mode, algo and options; it sizes the call by walking its planner without launching anything).
+ *   - alpha_conv_release_workspace synchronises the current device and frees every library-owned
+ *     block, retired block and cached weight transform on it (graphs captured earlier are invalid
+ *     afterwards).  alpha_conv_workspace_in_use reports the bytes currently held.
+ *   - The natives of layer 2 additionally use the scratch their own signature carries: kernel_remode
+ *     leaves the lo plane of W in CW for the conv3D_GemmR* natives, and the GemmSK natives put their
+ *     partial sums into deltaW_buf when it is large enough. */
+#define ALPHA_OP_FORWARD 0
+#define ALPHA_OP_DELTAX 1
+#define ALPHA_OP_DELTAW 2
+#define ALPHA_OP_BIAS_GRAD 3
+int alpha_conv_workspace_bytes(const AlphaConvShape* s, int op, size_t* bytes);
+int alpha_conv_set_workspace(alpha_stream_t stream, void* block, size_t bytes);
+int alpha_conv_reserve_workspace(alpha_stream_t stream, size_t bytes);
+int alpha_conv_release_workspace(void);
+size_t alpha_conv_workspace_in_use(void);
+
+/* ---- weight-side transforms kept across calls --------------------------------------------------
+ *
+ * Weights change only when the optimizer updates them (the reference's tensors carry that contract:
+ * src/alpha_src/z/dragon/engine/Tensor.java:208-221, Engine.java:341-350), yet every forward call
+ * needs the lo plane of W and every deltaX call needs W transposed, rotated and split.  With
+ * alpha_conv_weight_cache(1) the library keeps each transform in memory of its own, keyed by the
+ * address and shape of W, and reuses it until alpha_conv_weights_updated(W) (NULL = every tensor)
+ * says the values changed; the host calls that after its optimizer step.  Off by default: a host
+ * that does not announce updates would compute with stale weights.  The first use of a tensor
+ * allocates (not inside a stream capture: ALPHA_E_CAPTURE). */
+int alpha_conv_weight_cache(int enable);
+int alpha_conv_weights_updated(const float* W);
 
 /* ---- layer 1: one call per contraction ------------------------------------------------------ */
 
@@ -102,8 +167,8 @@ int alpha_conv3d_deltaX(const AlphaConvShape* s, const float* deltaY, const floa
 
 /* deltaW = correlation of X with deltaY summed over the batch.
  * Replaces src/cu32_src/Cuda_dconv3D_deltaW/Cuda_dconv3D_deltaW/dconv3d_dW.cuh:72-700 including the
- * split-K buffer sum (dconv3d_dW_GemmSK_bufSum.cuh:32-67).  Split-K partials live in a per-device
- * workspace that the library allocates on first use and grows on demand. */
+ * split-K buffer sum (dconv3d_dW_GemmSK_bufSum.cuh:32-67).  The per-CTA partial sums live in the
+ * stream's scratch block (see "scratch memory" above). */
 int alpha_conv3d_deltaW(const AlphaConvShape* s, const float* X, const float* deltaY, float* deltaW,
                         alpha_stream_t stream);
 
@@ -124,8 +189,11 @@ int alpha_conv_bias_grad(const float* deltaY, long long rows, int OC, float* del
  * alpha_conv3d_deltaW_noalloc_capacity() bytes (32 MiB) that is part of the library image: every GPU
  * on which the library is loaded holds it until the process exits.
  *   - Shapes whose partial sums need more than that return ALPHA_E_NOSCRATCH; shapes the tensor-core
- *     kernel does not take (IC not a multiple of 32) return ALPHA_E_ARG.  Results are the same bits
- *     alpha_conv3d_deltaW produces.
+ *     kernel does not take (IC not a multiple of 32) return ALPHA_E_ARG.  It always runs the split-K
+ *     im2col kernel.  alpha_conv3d_deltaW runs that kernel, with the same plan and then the same bits,
+ *     for strided layers; for stride 1 it prefers its halo-tile kernel, whose pixel sum is ordered
+ *     differently, so there the two results agree to rounding (1e-4 of the largest element, the
+ *     parity bound), not bit for bit.
  *   - The first call on each device looks up the array's device address (with that device current);
  *     make that first call before starting any stream capture.
  *   - All calls on one device share the array, and it keeps what the last call left in it.  The

@@ -73,14 +73,28 @@ class Cu32Reference:
 
     N_STREAMS = 10
 
-    def __init__(self):
-        if not available():
-            raise ImportError("oracle/_ref/libcu32_*.so missing: run oracle/build_ref_gpu.sh where the reference is")
-        self.env = _FakeEnv()
+    def __init__(self, libs=None, env=None, fill=None):
+        """libs: (conv3D, deltaX, deltaW) libraries that export the reference's JNI symbols - the
+        rebuilt reference by default; a test passes another implementation of the same natives to
+        drive it in the engine's call order.  env: a JNIEnv stand-in with `.env` and `.streams`.
+        fill: value the output tensors hold before the natives run (NaN shows what a kernel left
+        unwritten); None leaves them uninitialised."""
+        if libs is None:
+            if not available():
+                raise ImportError("oracle/_ref/libcu32_*.so missing: run oracle/build_ref_gpu.sh where the reference is")
+            libs = (_lib("Cuda_conv3D"), _lib("Cuda_dconv3D_deltaX"), _lib("Cuda_dconv3D_deltaW"))
+        self.env = env if env is not None else _FakeEnv()
         self.streams = [torch.cuda.Stream() for _ in range(self.N_STREAMS)]
         self.env.streams = [s.cuda_stream for s in self.streams]
-        self.c3, self.dx, self.dw = _lib("Cuda_conv3D"), _lib("Cuda_dconv3D_deltaX"), _lib("Cuda_dconv3D_deltaW")
+        self.c3, self.dx, self.dw = libs
+        self.fill = fill
         self.last = ""
+        self.called = []     # every native called so far, in order
+
+    def _out(self, shape, device):
+        if self.fill is None:
+            return torch.empty(shape, device=device, dtype=torch.float32)
+        return torch.full(shape, float(self.fill), device=device, dtype=torch.float32)
 
     # -- helpers -----------------------------------------------------------------------------------
     def _call(self, lib, name, *args):
@@ -100,6 +114,7 @@ class Cu32Reference:
                 conv.append(C.c_int(int(a)))
         f(self.env.env, None, *conv)
         self.last = name
+        self.called.append(name)
 
     @staticmethod
     def _scale_up(IH, IW, OH, OW, FH, FW, sh, sw):
@@ -111,7 +126,7 @@ class Cu32Reference:
         N, IH, IW, IC = X.shape
         OC, FH, FW, _ = W.shape
         OH, OW = (IH + 2 * ph - FH) // sh + 1, (IW + 2 * pw - FW) // sw + 1
-        Y = torch.empty((N, OH, OW, OC), device=X.device, dtype=torch.float32)
+        Y = self._out((N, OH, OW, OC), X.device)
         L = self.N_STREAMS
         torch.cuda.synchronize()
         if OC > 31 and N * OH * OW > 31:
@@ -149,7 +164,7 @@ class Cu32Reference:
         """CudaFloat32EngineBase.dconv3D_deltaX (:1796-2005) with the default flags."""
         N, OH, OW, OC = dY.shape
         _, FH, FW, IC = W.shape
-        dX = torch.empty((N, IH, IW, IC), device=dY.device, dtype=torch.float32)
+        dX = self._out((N, IH, IW, IC), dY.device)
         L = self.N_STREAMS
         P = "Cuda_1dconv3D_1deltaX_"
         torch.cuda.synchronize()
@@ -194,7 +209,7 @@ class Cu32Reference:
         """CudaFloat32EngineBase.dconv3D_deltaW (:1666-1762): split-K with GridZ from the block counts."""
         N, IH, IW, IC = X.shape
         _, OH, OW, OC = dY.shape
-        dW = torch.empty((OC, FH, FW, IC), device=X.device, dtype=torch.float32)
+        dW = self._out((OC, FH, FW, IC), X.device)
         L = self.N_STREAMS
         P = "Cuda_1dconv3D_1deltaW_"
         GK = N * OH * OW

@@ -30,24 +30,52 @@ def gen(shape, dist, rng):
     raise ValueError(dist)
 
 
+FLOOR_TAU = 1e-3
+
+
+def floor_rel(got, ref64):
+    """max |a-b| / max(|b|, tau * max|b|), tau = 1e-3: the relative error of every element, with the
+    denominators of the elements that pass through zero (zero-mean inputs) floored at a thousandth of
+    the largest reference value."""
+    ref64 = np.asarray(ref64, np.float64)
+    err = np.abs(np.asarray(got, np.float64) - ref64)
+    big = max(float(np.abs(ref64).max()), 1e-30)
+    return float((err / np.maximum(np.abs(ref64), FLOOR_TAU * big)).max())
+
+
 def metrics(got, ref64, S):
     got = np.asarray(got, np.float64)
     err = np.abs(got - ref64)
     norm = float(err.max() / max(np.abs(ref64).max(), 1e-30))
     comp = float((err / np.maximum(S, 1e-30)).max())
-    return dict(norm=norm, comp=comp, max_abs=float(err.max()), finite=bool(np.isfinite(got).all()))
+    return dict(norm=norm, comp=comp, floor_rel=floor_rel(got, ref64), max_abs=float(err.max()),
+                finite=bool(np.isfinite(got).all()))
 
 
 _REPORT = []
 
 
+def worst_floor_rel():
+    """Largest floor-relative error per math mode over every case recorded so far."""
+    worst = {}
+    for e in _REPORT:
+        mode = e.get("mode", "3xtf32")
+        for v in e.values():
+            if isinstance(v, dict) and "floor_rel" in v:
+                worst[mode] = max(worst.get(mode, 0.0), v["floor_rel"])
+    return worst
+
+
 def record(entry):
-    """Appends one case to the parity report written at the end of the run (diagnostics for a failed run)."""
+    """Appends one case to the parity report (diagnostics for a failed run).  The report is written as
+    JSON only where ALPHA_PARITY_REPORT names a file."""
     _REPORT.append(entry)
-    out = os.path.join(ROOT, "gpurun_out")
+    out = os.environ.get("ALPHA_PARITY_REPORT")
+    if not out:
+        return
     try:
-        os.makedirs(out, exist_ok=True)
-        with open(os.path.join(out, "parity_report.json"), "w") as f:
+        os.makedirs(os.path.dirname(os.path.abspath(out)), exist_ok=True)
+        with open(out, "w") as f:
             json.dump(_REPORT, f, indent=1)
     except OSError:
         pass

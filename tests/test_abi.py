@@ -57,6 +57,26 @@ def test_argument_errors_come_before_any_device_work(lib, pkg):
     assert lib.alpha_conv3d_forward_leakyRelu(C.byref(s), 16, 32, None, float("nan"), 48, None) == -1
 
 
+def test_options_and_per_call_settings_need_no_device(lib, pkg):
+    """The tuning table is seeded from the environment once and changed by name afterwards; unknown names
+    and out-of-range per-call settings are argument errors."""
+    L = pkg.submodule("lib")
+    old = L.set_option("HALO_PAIR", 3)
+    assert L.get_option("ALPHA_HALO_PAIR") == 3       # the environment variable's name is accepted too
+    L.set_option("HALO_PAIR", old)
+    assert L.get_option("HALO_PAIR") == old
+    assert L.set_option("CONV_TILE", "im2col") in (0, 1, 2) and L.get_option("CONV_TILE") == 1
+    L.set_option("CONV_TILE", "auto")
+    assert lib.alpha_conv_set_option(b"NO_SUCH_SWITCH", 1) == -1 and b"unknown option" in lib.alpha_conv_last_error()
+    s = L.AlphaConvShape(4, 8, 8, 8, 8, 3, 3, 8, 8, 1, 1, 1, 1)
+    assert lib.alpha_conv3d_forward_ex(C.byref(s), 16, 32, None, 48, 2, -1, None) == -1      # math mode 2 does not exist
+    assert lib.alpha_conv3d_deltaX_ex(C.byref(s), 16, 32, 48, -1, 9, None) == -1             # nor algo 9
+    assert lib.alpha_conv3d_deltaW_ex(C.byref(s), None, 32, 48, -1, -1, None) == -1          # null X, default settings
+    n = C.c_size_t(0)
+    assert lib.alpha_conv_workspace_bytes(C.byref(s), 17, C.byref(n)) == -1                  # unknown op
+    assert lib.alpha_conv_workspace_bytes(None, 0, C.byref(n)) == -1
+
+
 def test_no_silent_fallback_without_a_gpu(lib, pkg):
     """On a machine without a B200 a well-formed call fails loudly; there is no CPU path."""
     import torch

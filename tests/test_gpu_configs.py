@@ -52,7 +52,8 @@ def test_resnet18_conv_stack(pkg, eng, oracle_mod):
     1x1 s2 shortcuts), batch 8: forward, deltaX and deltaW of every layer."""
     synth = pkg.submodule("synth")
     seen = set()
-    for i, (IH, IC, OC, F, s, p) in enumerate(synth.RESNET18_CONVS):
+    assert len(synth.RESNET18_CONVS) == 20
+    for i, (IH, IC, OC, F, s, p) in enumerate(list(synth.RESNET18_CONVS) + synth.SHORTCUT_1X1_CONVS):
         if (IH, IC, OC, F, s, p) in seen:
             continue
         seen.add((IH, IC, OC, F, s, p))

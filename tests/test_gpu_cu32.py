@@ -2,6 +2,8 @@
 
 oracle/build_ref_gpu.sh compiles the reference's three CUDA libraries where its checkout exists;
 the built libraries travel with the repository snapshot.  Where they are missing the tests skip.
+The rebuilt reference kernels are the only oracle of these tests: whatever they write must agree with
+the reference's own CPU loop, and ours with them.
 Bar: max|ours - cu32| / max|cu32| <= 1e-4 in 3xTF32 mode, 5e-3 in TF32 mode, on identical seeded
 inputs, plus the reference's own samePercentRelative thresholds on positive inputs.
 """
@@ -10,7 +12,7 @@ import zlib
 import numpy as np
 import pytest
 
-from helpers import gen, out_hw, record
+from helpers import floor_rel, gen, out_hw, record
 
 pytestmark = pytest.mark.gpu
 
@@ -35,7 +37,36 @@ def ref():
     if not cu32_ref.available():
         pytest.skip("oracle/_ref/libcu32_*.so not built (needs the reference checkout)")
     torch.cuda.set_device(0)
-    return cu32_ref.Cu32Reference()
+    # outputs start as NaN, so that an element no reference kernel wrote shows as such
+    return cu32_ref.Cu32Reference(fill=float("nan"))
+
+
+def _pixels_the_reference_leaves_unwritten(name, shape):
+    """Elements of deltaX the reference's own dispatcher never writes, as a boolean mask, or None.
+
+    Its stride-1 "A" kernels (u88As1W3_oc2pow and relatives, chosen when N % 8 == 0:
+    Cuda_dconv3D_deltaX/dconv3D_dX.cuh:171, 414) number the GM = N*IH*IW output pixels with the image
+    index innermost, j = (ih*IW + iw)*N + n (get_ih_iw_n, micro.cuh:193-194), while the kernels that
+    take the remainder GM % 64 (k84s1_pure ..., dconv3D_dX.cuh:305-323, 467, 470-472) number them
+    j = n*IH*IW + ih*IW + iw (get_n_ih_iw, micro.cuh:190-191).  The remainder is handed over as a bare
+    j_index, so when GM is not a multiple of the A kernel's 64-pixel tile the two numberings do not
+    describe the same pixels: the tail of the A ordering is never computed, and the tail of the
+    (n, ih, iw) ordering is computed twice.  For 8 images of 14 x 14 (GM = 1568 = 24*64 + 32) the A
+    kernel covers positions p = ih*IW + iw < 192 of every image, the remainder kernel positions
+    164..195 of image 7 only: positions 192..195 of images 0..6 keep whatever the buffer held.
+    """
+    if name != "s1_64_64":
+        return None
+    N, IH, IW, IC = shape
+    gm = N * IH * IW
+    covered_a = (gm // 64) * 64
+    mask = np.zeros((N, IH * IW, IC), bool)
+    for n in range(N):
+        for p in range(IH * IW):
+            in_a = p * N + n < covered_a
+            in_rem = n * IH * IW + p >= covered_a
+            mask[n, p] = not (in_a or in_rem)
+    return mask.reshape(N, IH, IW, IC)
 
 
 @pytest.fixture(scope="module")
@@ -65,21 +96,31 @@ def test_against_cu32_outputs(pkg, eng, ref, oracle_mod, name, mode):
     k_dx = ref.last
     want["dw"] = ref.dconv3D_deltaW(X, dY, FH, FW, sh, sw, ph, pw)
     tol = 1e-4 if mode == "3xtf32" else 5e-3
-    # The Pascal-era kernels are not reliable on sm_100 for every shape (deltaX_s1_texture returns
-    # wrong numbers for this file's s1_64_64 inputs): an op counts only where cu32 agrees with the
-    # reference's own CPU loop; where it does not, ours must agree with the CPU loop instead.
     Xn, Wn, dYn = X.cpu().numpy(), W.cpu().numpy(), dY.cpu().numpy()
     cpu = dict(fwd=O.conv3D_f64(Xn, Wn, sh, sw, ph, pw, threads=8)[0],
                dx=O.deconv3D_deltaX_f64(dYn, Wn, IH, IW, sh, sw, ph, pw, threads=8)[0],
                dw=O.deconv3D_deltaW_f64(Xn, dYn, FH, FW, sh, sw, ph, pw, threads=8)[0])
-    errs, cu32_ok = {}, {}
+    errs, cu32_vs_cpu, floor = {}, {}, {}
     for op in ("fwd", "dx", "dw"):
         a, b, c = got[op].double().cpu().numpy(), want[op].double().cpu().numpy(), cpu[op]
-        cu32_ok[op] = bool(np.abs(b - c).max() <= 1e-3 * np.abs(c).max())
-        errs[op] = float(np.abs(a - b).max() / np.abs(b).max()) if cu32_ok[op] else float(np.abs(a - c).max() / np.abs(c).max())
-    record(dict(case=name, mode=mode, vs="cu32", ref_kernels=[k_fwd, k_dx, ref.last], cu32_agrees_with_cpu=cu32_ok, **errs))
+        written = ~np.isnan(b)
+        expected_holes = _pixels_the_reference_leaves_unwritten(name, (N, IH, IW, IC)) if op == "dx" else None
+        if expected_holes is None:
+            assert written.all(), (op, "cu32 left %d elements unwritten" % int((~written).sum()))
+        else:
+            # the reference's dispatcher leaves exactly these elements unwritten (see the helper's note)
+            assert np.array_equal(~written, expected_holes), (op, int((~written).sum()), int(expected_holes.sum()))
+        # everything cu32 did write must agree with the reference's own CPU loop: no fallback oracle
+        cu32_vs_cpu[op] = float(np.abs(b - c)[written].max() / np.abs(c).max())
+        assert cu32_vs_cpu[op] <= 1e-4, (op, cu32_vs_cpu)
+        errs[op] = float(np.abs(a - b)[written].max() / np.abs(b[written]).max())
+        floor[op] = floor_rel(a[written], b[written])
+        if not written.all():   # the elements cu32 never wrote: against the CPU loop
+            errs[op] = max(errs[op], float(np.abs(a - c)[~written].max() / np.abs(c).max()))
+    record(dict(case=name, mode=mode, vs="cu32", ref_kernels=[k_fwd, k_dx, ref.last], cu32_vs_cpu_loop=cu32_vs_cpu,
+                floor_rel_vs_cu32=floor, **errs))
     for op in ("fwd", "dx", "dw"):
-        assert errs[op] <= tol, (op, errs, cu32_ok)
+        assert errs[op] <= tol, (op, errs)
 
 
 def test_reference_thresholds_against_cu32(pkg, eng, ref, oracle_mod):

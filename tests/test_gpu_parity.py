@@ -46,10 +46,9 @@ def eng(pkg):
 
 
 def _run_case(pkg, eng, O, name, mode, dists=("u11", "u11", "n01"), tile="auto"):
-    import os
     import torch
-    os.environ["ALPHA_CONV_TILE"] = tile  # read by the library at every call
     lib = pkg.submodule("lib")
+    lib.set_option("CONV_TILE", tile)
     lib.set_math_mode(mode)
     N, IH, IW, IC, OC, FH, FW, sh, sw, ph, pw = CASES[name]
     OH, OW = out_hw(IH, IW, FH, FW, sh, sw, ph, pw)
@@ -116,6 +115,50 @@ def test_algo_selection(pkg, eng, oracle_mod):
     assert res["fwd_algo"] == "igemm" and res["dx_algo"] == "igemm" and res["dw_algo"].startswith("dw")
     res, _ = _run_case(pkg, eng, oracle_mod, "ic64_oc64_14x14", "3xtf32", tile="halo")
     assert res["fwd_algo"].startswith("halo") and res["dx_algo"].startswith("halo")
+
+
+# The channel configurations of the benchmark's 3x3 sweep at a batch the oracle finishes in seconds.
+# They take kernel forms the smaller cases never reach: CTA pairs with side columns (128- and
+# 256-channel blocks), and at 7x7x512 two stacked images per accumulator with 256-column tiles.
+BENCH_CASES = {
+    "bench_56x56x64": (2, 56, 56, 64, 64, 3, 3, 1, 1, 1, 1),
+    "bench_28x28x128": (8, 28, 28, 128, 128, 3, 3, 1, 1, 1, 1),
+    "bench_14x14x256": (8, 14, 14, 256, 256, 3, 3, 1, 1, 1, 1),
+    "bench_7x7x512": (4, 7, 7, 512, 512, 3, 3, 1, 1, 1, 1),
+}
+CASES.update(BENCH_CASES)
+
+
+@pytest.mark.parametrize("mode", ["3xtf32", "tf32"])
+@pytest.mark.parametrize("name", list(BENCH_CASES))
+def test_bench_channel_configurations(pkg, eng, oracle_mod, name, mode):
+    import torch
+    lib = pkg.submodule("lib")
+    res, (X, W, B, dY, Y, dX, dW) = _run_case(pkg, eng, oracle_mod, name, mode, dists=("relu", "n01", "n01"))
+    assert res["status"] == 0
+    tol = TOL[mode]
+    for op in ("fwd", "dx", "dw"):
+        m = res[op]
+        assert m["finite"] and m["norm"] <= tol["norm"] and m["comp"] <= tol["comp"], (name, op, res[op + "_algo"], m)
+    # the kernel form must be the one the benchmark's batch-256 launch of this layer takes
+    N, IH, IW, IC, OC = CASES[name][:5]
+    dev = torch.device("cuda:0")
+    eng.conv3D(torch.from_numpy(X).to(dev), torch.from_numpy(W).to(dev), 1, 1, 1, 1)
+    small = lib.last_plan()
+    big_X = torch.zeros((256, IH, IW, IC), device=dev)
+    eng.conv3D(big_X, torch.from_numpy(W).to(dev), 1, 1, 1, 1)
+    big = lib.last_plan()
+    assert lib.device_status() == 0
+    assert res["fwd_algo"].startswith("halo") and big.startswith("halo"), (res["fwd_algo"], big)
+    if "halo_pair" in big:
+        assert small == big, (small, big)   # the pair kernel's form does not depend on the batch
+    if mode == "3xtf32":
+        if OC == 512:
+            assert "halo_pair" in big and "three+side" in big and "BN=256" in big and "NI=2" in big, big
+        elif OC >= 128:
+            assert "halo_pair" in big and "three+side" in big, big
+    elif OC % 256 == 0:
+        assert "halo_pair" in big, big
 
 
 EDGE_CASES = {
@@ -245,17 +288,21 @@ def test_winograd_forward(pkg, eng, oracle_mod, name, mode):
 
 
 @pytest.mark.parametrize("pair,mode", [("1", "tf32"), ("1", "3xtf32"), ("2", "3xtf32"), ("3", "3xtf32")])
-def test_cta_pair_kernel(pkg, eng, oracle_mod, pair, mode, monkeypatch):
+def test_cta_pair_kernel(pkg, eng, oracle_mod, pair, mode):
     """The cta_group::2 form of the halo kernel (two CTAs per MMA) in plain TF32, wide 3xTF32 and
     three-MMA 3xTF32 (one accumulator, and with the correction terms in side columns), forced on shapes it would not be chosen for, against the oracle."""
-    monkeypatch.setenv("ALPHA_HALO_PAIR", pair)
-    for name in ("ic64_oc64_14x14", "ic64_oc128_7x7", "ic32_oc64_16x16"):
-        res, _ = _run_case(pkg, eng, oracle_mod, name, mode)
-        assert res["fwd_algo"].startswith("halo_pair"), res["fwd_algo"]
-        tol = TOL[mode]
-        for op in ("fwd", "dx"):
-            m = res[op]
-            assert m["finite"] and m["norm"] <= tol["norm"] and m["comp"] <= tol["comp"], (name, op, res[op + "_algo"], m)
+    L = pkg.submodule("lib")
+    old = L.set_option("HALO_PAIR", int(pair))
+    try:
+        for name in ("ic64_oc64_14x14", "ic64_oc128_7x7", "ic32_oc64_16x16"):
+            res, _ = _run_case(pkg, eng, oracle_mod, name, mode)
+            assert res["fwd_algo"].startswith("halo_pair"), res["fwd_algo"]
+            tol = TOL[mode]
+            for op in ("fwd", "dx"):
+                m = res[op]
+                assert m["finite"] and m["norm"] <= tol["norm"] and m["comp"] <= tol["comp"], (name, op, res[op + "_algo"], m)
+    finally:
+        L.set_option("HALO_PAIR", old)
 
 
 def test_pair_kernel_is_chosen_for_256_channel_blocks(pkg, eng, oracle_mod):

@@ -4,8 +4,10 @@ A host that has given all device memory to its own pool (Dragon-Alpha's engine d
 from code where the CUDA allocator must not be entered, cannot let a native call cudaMalloc.  This
 entry point keeps its split-K partial sums in a fixed 32 MiB array inside the library instead.  The
 test calls it through the C ABI twice in a row - the second call finds the first call's partials
-still in the array - and compares each result with alpha_conv3d_deltaW on the same input; it also
-checks that a shape whose partials do not fit is refused with a clear message.
+still in the array - and compares each result with alpha_conv3d_deltaW on the same input (to
+rounding against its default kernel, bit for bit against the same split-K kernel); it checks that
+the free device memory does not move across a call, and that a shape whose partials do not fit is
+refused with a clear message.
 
 The file name sorts last so that a run that stops at the first failure has already run every other
 test; the test does not depend on any of them having run.
@@ -28,8 +30,6 @@ def test_deltaW_noalloc_matches_deltaW_on_two_calls(pkg):
     torch.cuda.set_device(0)
     L = pkg.submodule("lib")
     lib = L.load()
-    lib.alpha_conv3d_deltaW_noalloc.argtypes = [C.POINTER(L.AlphaConvShape)] + [C.c_void_p] * 4
-    lib.alpha_conv3d_deltaW_noalloc_capacity.restype = C.c_size_t
     assert lib.alpha_conv3d_deltaW_noalloc_capacity() == 32 << 20
     L.set_math_mode("3xtf32")
     L.set_algo("auto")
@@ -38,6 +38,7 @@ def test_deltaW_noalloc_matches_deltaW_on_two_calls(pkg):
     stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
 
     # two different layers back to back: the second call runs over the first call's leftovers
+    calls = 0
     for (N, HW, IC, OC) in [(32, 28, 64, 64), (16, 14, 128, 96)]:
         X = torch.randn((N, HW, HW, IC), device=dev, generator=gen).relu_()
         dY = torch.randn((N, HW, HW, OC), device=dev, generator=gen)
@@ -47,8 +48,30 @@ def test_deltaW_noalloc_matches_deltaW_on_two_calls(pkg):
         p = lambda t: C.c_void_p(t.data_ptr())
         L.check(lib.alpha_conv3d_deltaW(C.byref(s), p(X), p(dY), p(ref), stream))
         assert L.last_algo().startswith("dw")
+        # the same split-K im2col kernel through the allocating entry point: bit-for-bit the same result
+        same_kernel = torch.empty((OC, 3, 3, IC), device=dev)
+        old = L.set_option("CONV_DW", "split")
+        try:
+            L.check(lib.alpha_conv3d_deltaW(C.byref(s), p(X), p(dY), p(same_kernel), stream))
+            assert L.last_algo() == "dw"
+        finally:
+            L.set_option("CONV_DW", old)
+        calls += 1
+        if calls == 2:
+            # the property the entry point exists for: the second call (the first one on this device may
+            # load the kernel image) takes no device memory, neither through the CUDA allocator nor torch's
+            torch.cuda.synchronize()
+            free_before, _ = torch.cuda.mem_get_info()
+            reserved_before = torch.cuda.memory_reserved()
+            held_before = L.workspace_in_use()
         L.check(lib.alpha_conv3d_deltaW_noalloc(C.byref(s), p(X), p(dY), p(got), stream))
         assert L.last_algo() == "dw_noalloc"
+        if calls == 2:
+            torch.cuda.synchronize()
+            assert torch.cuda.mem_get_info()[0] == free_before
+            assert torch.cuda.memory_reserved() == reserved_before
+            assert L.workspace_in_use() == held_before
+        assert torch.equal(got, same_kernel)
         assert lib.alpha_conv3d_deltaW_noalloc_status() == 0
         assert L.device_status() == 0
         a, b = got.cpu().numpy(), ref.cpu().numpy()
@@ -67,7 +90,6 @@ def test_deltaW_noalloc_rejects_what_does_not_fit(pkg):
     torch.cuda.set_device(0)
     L = pkg.submodule("lib")
     lib = L.load()
-    lib.alpha_conv3d_deltaW_noalloc.argtypes = [C.POINTER(L.AlphaConvShape)] + [C.c_void_p] * 4
     L.set_math_mode("3xtf32")
     dev = torch.device("cuda:0")
     # 3x3, 256 -> 256 channels on 14x14 images: 16 partials of 589824 floats = 36 MiB > 32 MiB
