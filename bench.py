@@ -64,6 +64,8 @@ def parse_args():
     ap.add_argument("--no-peak", action="store_true", help="skip the in-run measurement of the TF32 matmul peak")
     ap.add_argument("--no-cu32", action="store_true")
     ap.add_argument("--no-config3", action="store_true")
+    ap.add_argument("--config3-batch", type=int, default=None,
+                    help="global batch of the ResNet-18 stack (default 512); 64 on one GPU shows the per-GPU compute of the 8-GPU case")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--streams", type=int, default=3, choices=[1, 3],
                     help="3: forward, deltaX and deltaW of a layer go to three streams (graph branches), so the tail of one kernel overlaps the start of another")
@@ -822,7 +824,7 @@ def run_ours(args):
     config3 = None
     if extras and not args.no_config3:
         sweep.graph = None
-        c3 = Config3(env, synth.RESNET18_BATCH)
+        c3 = Config3(env, args.config3_batch or synth.RESNET18_BATCH)
         config3 = c3.run(max(10, args.steps), max(3, args.repeats), barrier)
 
     # ---- CPU baseline (rank 0, single GPU runs only) ----

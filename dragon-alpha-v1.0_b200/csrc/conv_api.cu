@@ -896,7 +896,17 @@ static int launch_halo(DeviceCtx* c, const IgemmPlan& pl_in, int mode3x, cudaStr
     // correction terms in side columns).
     const int pair_env = opt(OPT_HALO_PAIR);
     const bool pair_auto = mode3x ? pl.ncols % 128 == 0 : pl.ncols % 256 == 0;
-    if (pair_env > 0 || (pair_env < 0 && pair_auto && tile_mode == 0)) {
+    // few output tiles and a long reduction: the single-CTA kernel splits the reduction over the idle SMs
+    bool skinny = false;
+    if (opt(OPT_SKINNY) && pl.oSH == 1 && pl.oSW == 1 && pl.oNH == 0 && pl.oNW == 0) {
+        const int sg = pl.oH + pl.FH - 1;
+        const int ni = (sg <= 16 && opt(OPT_HALO_STACK)) ? 1 + (16 - pl.oH) / sg : 1;
+        const long long tiles128 = (long long)((pl.aN + ni - 1) / ni) * (ni > 1 ? 1 : (pl.oH + 15) / 16) * ((pl.oW + 7) / 8) *
+                                   ((pl.ncols + 127) / 128);
+        skinny = 2 * tiles128 <= sm_budget(c) && (long long)(pl.kdim / 32) * pl.FH * pl.FW >= 32;
+    }
+    const bool try_pair = pair_env > 0 || (pair_env < 0 && pair_auto && tile_mode == 0);
+    if (try_pair && !skinny) {
         const int rc2 = launch_halo_pair(c, pl, mode3x, stream);
         if (rc2 != 1) return rc2;
     }
@@ -920,8 +930,14 @@ static int launch_halo(DeviceCtx* c, const IgemmPlan& pl_in, int mode3x, cudaStr
         HaloChoice alt = plan_halo(pl, cand, mode3x, pl.b_mn, sm_budget(c));
         if (alt.valid && (!ch.valid || alt.cost < 0.9 * ch.cost)) { ch = alt; BN = cand; }
     }
-    if (!ch.valid) return 1;
-    if (tile_mode == 0 && ch.eff < 0.6 && !pl.force) return 1;
+    if (!ch.valid || (tile_mode == 0 && ch.eff < 0.6 && !pl.force)) {
+        // a skinny shape whose tiles the single-CTA kernel would leave mostly empty: the pair kernel after all
+        if (try_pair && skinny) {
+            const int rc2 = launch_halo_pair(c, pl_in, mode3x, stream);
+            if (rc2 != 1) return rc2;
+        }
+        return 1;
+    }
 
     HaloParams p{};
     p.out = pl.out; p.bias = pl.bias; p.act_on = pl.act_on; p.act_k = pl.act_k; p.status = c->status; p.prof = c->prof;
@@ -985,15 +1001,43 @@ static int launch_halo(DeviceCtx* c, const IgemmPlan& pl_in, int mode3x, cudaStr
         if (!rc) rc = make_tiled_map(&tmBlo, w_lo, 3, wd, wst, box, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
     }
     if (rc) return rc;
+    // Split-K: a layer with few output tiles and a long reduction (small images or batch, many channels)
+    // would leave most SMs idle while a handful of CTAs stream the whole filter.  Every tile is then
+    // computed as ksplit partial sums over disjoint ranges of the reduction chunks, each by its own
+    // CTA, into scratch laid out as ksplit copies of the output; a second kernel adds them in order
+    // (with the bias and the activation, which the partial sums must not see).
+    int ksplit = 1;
+    const bool dense_out = pl.oSH == 1 && pl.oSW == 1 && pl.oNH == 0 && pl.oNW == 0;
+    if (dense_out && opt(OPT_SKINNY) && p.kchunks >= 2 && 2 * p.total_tiles <= sm_budget(c) &&
+        (long long)p.kchunks * pl.FH * pl.FW >= 16) {
+        ksplit = sm_budget(c) / p.total_tiles;
+        if (ksplit > 16) ksplit = 16;
+        if (ksplit > p.kchunks) ksplit = p.kchunks;
+        // every part gets at least four W-tile stages to amortise its prologue and epilogue
+        while (ksplit > 1 && (long long)((p.kchunks + ksplit - 1) / ksplit) * pl.FH * pl.FW < 4) --ksplit;
+        const int cps = (p.kchunks + ksplit - 1) / ksplit;
+        ksplit = (p.kchunks + cps - 1) / cps;
+        p.cps = cps;
+    }
+    p.ksplit = ksplit;
+    float* out_ptr = pl.out;
+    const size_t out_floats = (size_t)pl.aN * pl.oH * pl.oW * pl.ncols;
+    if (ksplit > 1) {
+        if ((long long)pl.aN * ksplit > 2147483647LL) return 1;
+        rc = get_workspace(c, stream, (size_t)ksplit * out_floats * sizeof(float), &out_ptr);
+        if (rc) return rc;
+        p.bias = nullptr; p.act_on = 0;
+    }
     // output [N][OH][OW][ldo] for the epilogue's TMA stores: one slab = 32 channels x 8 columns x 16 rows
     const int oNH = pl.oNH ? pl.oNH : pl.oH, oNW = pl.oNW ? pl.oNW : pl.oW;
-    cuuint64_t od[4] = {(cuuint64_t)pl.ncols, (cuuint64_t)pl.oW, (cuuint64_t)pl.oH, (cuuint64_t)pl.aN};
+    cuuint64_t od[4] = {(cuuint64_t)pl.ncols, (cuuint64_t)pl.oW, (cuuint64_t)pl.oH, (cuuint64_t)pl.aN * ksplit};
     cuuint64_t ost[3] = {(cuuint64_t)pl.oSW * pl.ncols * 4, (cuuint64_t)pl.oSH * oNW * pl.ncols * 4,
                          (cuuint64_t)oNH * oNW * pl.ncols * 4};
     cuuint32_t obox[4] = {32, 8, (cuuint32_t)(ch.NI > 1 ? pl.oH : 16), 1};
-    rc = make_tiled_map(&tmO, pl.out, 4, od, ost, obox, CU_TENSOR_MAP_SWIZZLE_128B);
+    rc = make_tiled_map(&tmO, out_ptr, 4, od, ost, obox, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
-    int grid = sm_budget(c) < p.total_tiles ? sm_budget(c) : p.total_tiles;
+    const long long vtiles = (long long)p.total_tiles * ksplit;
+    int grid = sm_budget(c) < vtiles ? sm_budget(c) : (int)vtiles;
     HaloLaunch L{grid, smem, stream, &tmA, &tmB, &tmBlo, &tmO, &p};
     if (!ch.stat) halo_launch_one<0, 0, 0, false>(L);
     else if (pl.FW == 1) halo_launch_fw<1>(L, ch.JH, ch.JW, ch.row);
@@ -1001,10 +1045,17 @@ static int launch_halo(DeviceCtx* c, const IgemmPlan& pl_in, int mode3x, cudaStr
     else if (pl.FW == 3) halo_launch_fw<3>(L, ch.JH, ch.JW, ch.row);
     else halo_launch_fw<5>(L, ch.JH, ch.JW, ch.row);
     note_launch(ch.row ? "halo_row" : (ch.stat ? "halo_tap" : "halo"));
-    snprintf(g_plan, sizeof(g_plan), "halo%s%s%s JH=%d JW=%d NI=%d BN=%d npb=%d sb=%d acc=%d eff=%.2f", ch.row ? "_row" : (ch.stat ? "_tap" : ""),
-             ch.wide ? " wide" : "", p.dual ? " dual" : "", ch.JH, ch.JW, ch.NI, BN, ch.npb, p.sb, ch.acc_bufs, ch.eff);
+    snprintf(g_plan, sizeof(g_plan), "halo%s%s%s JH=%d JW=%d NI=%d BN=%d npb=%d sb=%d acc=%d eff=%.2f ksplit=%d", ch.row ? "_row" : (ch.stat ? "_tap" : ""),
+             ch.wide ? " wide" : "", p.dual ? " dual" : "", ch.JH, ch.JW, ch.NI, BN, ch.npb, p.sb, ch.acc_bufs, ch.eff, ksplit);
     rc = check_launch("conv_halo_kernel");
-    return rc;
+    if (rc || ksplit == 1) return rc;
+    const size_t n4 = out_floats / 4;
+    size_t blocks = (n4 + 255) / 256;
+    if (blocks > (size_t)c->sm_count * 8) blocks = (size_t)c->sm_count * 8;
+    if (!t_dry) splitk_reduce_kernel<<<(unsigned)blocks, 256, 0, stream>>>(reinterpret_cast<const float4*>(out_ptr), n4, ksplit, pl.bias, pl.ncols / 4,
+                                                               pl.act_on, pl.act_k, reinterpret_cast<float4*>(pl.out));
+    note_launch(ch.row ? "halo_row" : (ch.stat ? "halo_tap" : "halo"));
+    return check_launch("splitk_reduce_kernel");
 }
 
 // ---- channel counts the tensor kernels cannot stage: patch matrix + 1x1 convolution ---------------
@@ -1177,13 +1228,22 @@ static int launch_dx_phases(DeviceCtx* c, const AlphaConvShape* s, const float* 
 static int launch_dx_col2im(DeviceCtx* c, const AlphaConvShape* s, const float* dY, const float* W, float* dX, int mode3x,
                             cudaStream_t stream)
 {
-    const int taps = s->FH * s->FW, cols = s->IC * taps;
-    if (s->IC > 8 || s->IC % 4 != 0 || cols > 512 || s->OC % 32 != 0 || taps > 64) return 1;
+    const int taps = s->FH * s->FW;
+    const long long cols = (long long)s->IC * taps;
+    if (s->IC % 4 != 0 || s->OC % 32 != 0 || taps > 64) return 1;
     if (!opt(OPT_DX_COL2IM) || env_tile_mode() == 1) return 1;
     const size_t M = (size_t)s->N * s->OH * s->OW, nW = (size_t)s->OC * cols;
+    // Image planes (IC <= 8): always.  More channels: while the product matrix P[pixels][taps * IC] stays
+    // small enough to live in the L2 cache between the kernel that writes it and the one that gathers
+    // from it, one dense product beats sh * sw phase convolutions with a few taps each; larger P would
+    // cost 2 * |P| of HBM traffic and the phases win.
+    const bool planes = s->IC <= 8 && cols <= 512;
+    const bool small_p = opt(OPT_DX_COL2IM) >= 1 && M * (size_t)cols * sizeof(float) <= (size_t)96 << 20 && cols <= 65536;
+    if (!planes && !small_p) return 1;
+    const int tap_major = planes ? 0 : 1;
     float* ws = nullptr;
     bool fresh = true;
-    const DeviceCtx::WeightKey wkey{W, WK_DX_COL2IM, s->OC, s->IC, s->FH * 256 + s->FW, 0, mode3x};
+    const DeviceCtx::WeightKey wkey{W, WK_DX_COL2IM, s->OC, s->IC, s->FH * 256 + s->FW, tap_major, mode3x};
     int rc = weight_planes(c, stream, wkey, (mode3x ? 2 : 1) * nW * sizeof(float), &ws, &fresh);
     if (rc) return rc;
     float* P = nullptr;
@@ -1194,7 +1254,7 @@ static int launch_dx_col2im(DeviceCtx* c, const AlphaConvShape* s, const float* 
         map.n = taps;
         for (int t = 0; t < taps; ++t) map.src[t] = t;
         dim3 tg((s->IC + 31) / 32, (s->OC + 31) / 32, taps);
-        if (!t_dry) transpose_weights_kernel<<<tg, 256, 0, stream>>>(W, ws, mode3x ? ws + nW : nullptr, s->OC, s->IC, taps, map, mode3x);
+        if (!t_dry) transpose_weights_kernel<<<tg, 256, 0, stream>>>(W, ws, mode3x ? ws + nW : nullptr, s->OC, s->IC, taps, map, mode3x, tap_major);
         note_launch("transpose_w");
         rc = check_launch("transpose_weights_kernel");
         if (rc) return rc;
@@ -1203,8 +1263,8 @@ static int launch_dx_col2im(DeviceCtx* c, const AlphaConvShape* s, const float* 
     IgemmPlan pl{};
     pl.act = dY; pl.aN = s->N; pl.aH = s->OH; pl.aW = s->OW; pl.aC = s->OC;
     pl.FH = 1; pl.FW = 1; pl.sh = 1; pl.sw = 1; pl.pad_h = 0; pl.pad_w = 0;
-    pl.out = P; pl.oH = s->OH; pl.oW = s->OW; pl.ncols = cols;
-    pl.W = ws; pl.W_lo = mode3x ? ws + nW : nullptr; pl.wOC = cols; pl.wIC = s->OC; pl.bias = nullptr;
+    pl.out = P; pl.oH = s->OH; pl.oW = s->OW; pl.ncols = (int)cols;
+    pl.W = ws; pl.W_lo = mode3x ? ws + nW : nullptr; pl.wOC = (int)cols; pl.wIC = s->OC; pl.bias = nullptr;
     pl.b_mn = false; pl.flip = false; pl.kdim = s->OC; pl.force = true;
     rc = launch_halo(c, pl, mode3x, stream);
     if (rc == 1) return 1;
@@ -1213,7 +1273,11 @@ static int launch_dx_col2im(DeviceCtx* c, const AlphaConvShape* s, const float* 
     const size_t total = (size_t)s->N * s->IH * s->IW * (s->IC / 4);
     size_t blocks = (total + 255) / 256;
     if (blocks > (size_t)c->sm_count * 16) blocks = (size_t)c->sm_count * 16;
-    if (!t_dry) col2im_gather_kernel<<<(unsigned)blocks, 256, 0, stream>>>(P, dX, ps);
+    if (tap_major) {
+        if (!t_dry) col2im_gather_tapmajor_kernel<<<(unsigned)blocks, 256, 0, stream>>>(P, dX, ps);
+    } else {
+        if (!t_dry) col2im_gather_kernel<<<(unsigned)blocks, 256, 0, stream>>>(P, dX, ps);
+    }
     note_launch("dx_col2im");
     return check_launch("col2im_gather_kernel");
 }

@@ -71,6 +71,8 @@ struct HaloParams {
     int acc_bufs;        // 1 or 2 accumulator sets
     int mode3x, b_mn, flip;   // mode3x: 0 plain TF32, 1 three MMAs, 2 wide B
     int dual;                 // 1: two MMA-issuing threads take alternate W-tile stages (sb is even)
+    int ksplit, cps;          // split-K: every tile is computed as ksplit partial sums over cps reduction chunks each;
+                              // partial sp of image n is stored as image sp * N + n of the output map
     uint32_t idesc, idesc_wide, tmem_cols;   // idesc_wide: N = 2 * BN
     uint32_t patch_bytes;  // one plane of one patch buffer, multiple of 1024
     uint32_t patch_tx;     // bytes one patch load delivers
@@ -87,6 +89,20 @@ __device__ __forceinline__ bool wait_prof(uint32_t bar, uint32_t parity, bool pr
     const bool ok = mbar_wait_a(bar, parity);
     acc += static_cast<unsigned long long>(clock64() - t0);
     return ok;
+}
+
+// Virtual tile v -> tile t and the range of reduction chunks [c0, c1) of its split-K part sp.
+struct TilePart { int t, sp, c0, c1; };
+__device__ __forceinline__ TilePart tile_part(const HaloParams& p, int v)
+{
+    TilePart r{v, 0, 0, p.kchunks};
+    if (p.ksplit > 1) {
+        r.t = v / p.ksplit;
+        r.sp = v - r.t * p.ksplit;
+        r.c0 = r.sp * p.cps;
+        r.c1 = r.c0 + p.cps < p.kchunks ? r.c0 + p.cps : p.kchunks;
+    }
+    return r;
 }
 
 // The four K=8 steps of one 32-channel chunk into one accumulator.  MODE 0: 4 MMAs; 1: 12 MMAs
@@ -248,6 +264,7 @@ __global__ void __launch_bounds__(kHaloThreads2, 1)
 
     const int J = p.JH * p.JW;
     const int per_img = p.row_blocks * p.col_blocks;
+    const int vtiles = p.total_tiles * (p.ksplit > 1 ? p.ksplit : 1);
     const bool prof_on = p.prof != nullptr && blockIdx.x == 0;
     const long long t_kernel = clock64();
 
@@ -264,7 +281,9 @@ __global__ void __launch_bounds__(kHaloThreads2, 1)
             bool ok = true;
             unsigned long long w_patch = 0, w_b = 0;
             const int taps = p.FH * p.FW;
-            for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
+            for (int v = blockIdx.x; v < vtiles && ok; v += gridDim.x) {
+                const TilePart tp = tile_part(p, v);
+                const int t = tp.t;
                 const int tn = t / (p.n_blocks * per_img);
                 int r = t - tn * (p.n_blocks * per_img);
                 const int nb = r / per_img;
@@ -273,7 +292,7 @@ __global__ void __launch_bounds__(kHaloThreads2, 1)
                 const int h0 = rb * 16 * p.JH - p.pad_h, w0 = cb * 8 * p.JW - p.pad_w;
                 const int n = nb * p.NI;
                 const int oc0 = tn * p.BN;
-                for (int c = 0; c < p.kchunks && ok; ++c) {
+                for (int c = tp.c0; c < tp.c1 && ok; ++c) {
                     if (!wait_prof(pempty_a + 8 * pp.idx, pp.phase ^ 1, prof_on, w_patch)) { report(p.status, kStatusProducerTimeout); ok = false; break; }
                     mbar_arrive_expect_tx_a(pfull_a + 8 * pp.idx, p.patch_tx);
                     tma_load_4d_a(patches_a + pp.idx * patch_stride, &tmA, pfull_a + 8 * pp.idx, c * 32, w0, h0, n);
@@ -329,7 +348,8 @@ __global__ void __launch_bounds__(kHaloThreads2, 1)
             const uint32_t accw = p.mode3x == 2 ? 2u * p.BN : p.BN;   // columns of one accumulator
             const uint32_t acc_cols = J * accw;
             const IssueConsts k{a_dhi, b_dhi, b_kstep, a_lo_off, b_lo_off, p.idesc, p.idesc_wide, accw};
-            for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
+            for (int v = blockIdx.x; v < vtiles && ok; v += gridDim.x) {
+                const TilePart tp = tile_part(p, v);
                 if (!wait_prof(aempty_a + 8 * ap.idx, ap.phase ^ 1, prof_on, w_acc)) { report(p.status, kStatusMmaTimeout); ok = false; break; }
                 tc_fence_after_sync();
                 const uint32_t d0 = tmem_base + ap.idx * acc_cols;
@@ -338,7 +358,7 @@ __global__ void __launch_bounds__(kHaloThreads2, 1)
                 const bool owner = !dual || (sg & 1u) == which;
                 uint32_t acc_first = owner ? 0u : 1u;
                 bool announce = dual && owner, must_wait = dual && !owner;
-                for (int c = 0; c < p.kchunks && ok; ++c) {
+                for (int c = tp.c0; c < tp.c1 && ok; ++c) {
                     if (!wait_prof(pwait_a + 8 * pp.idx, pp.phase, prof_on, w_patch)) { report(p.status, kStatusMmaTimeout); ok = false; break; }
                     tc_fence_after_sync();
                     uint32_t a_row = patch_lo0 + pp.idx * patch_stride16;
@@ -441,7 +461,9 @@ __global__ void __launch_bounds__(kHaloThreads2, 1)
         uint32_t sbuf = 0;
         const bool wide = p.mode3x == 2;
         const uint32_t accw = wide ? 2u * p.BN : p.BN;
-        for (int t = blockIdx.x; t < p.total_tiles; t += gridDim.x) {
+        for (int v = blockIdx.x; v < vtiles; v += gridDim.x) {
+            const TilePart tp = tile_part(p, v);
+            const int t = tp.t;
             if (!wait_prof(afull_a + 8 * ap.idx, ap.phase, prof_on, w_acc)) { report(p.status, kStatusEpilogueTimeout); break; }
             tc_fence_after_sync();
             const int tn = t / (p.n_blocks * per_img);
@@ -490,12 +512,12 @@ __global__ void __launch_bounds__(kHaloThreads2, 1)
                         named_barrier_sync(1, 128);
                         if (threadIdx.x == 64) {
                             if (p.NI == 1) {
-                                tma_store_4d_a(&tmO, stage_a + sbuf * 16384, col0, ow0, oh0, n);
+                                tma_store_4d_a(&tmO, stage_a + sbuf * 16384, col0, ow0, oh0, n + tp.sp * p.N);
                             } else {
                                 // stacked images: image i starts SG groups (of 8 rows) further down the slab
                                 for (int img = 0; img < p.NI; ++img)
                                     if (n + img < p.N)
-                                        tma_store_4d_a(&tmO, stage_a + sbuf * 16384 + img * p.SG * 1024, col0, ow0, 0, n + img);
+                                        tma_store_4d_a(&tmO, stage_a + sbuf * 16384 + img * p.SG * 1024, col0, ow0, 0, n + img + tp.sp * p.N);
                             }
                             tma_store_commit();
                         }
@@ -519,8 +541,9 @@ __global__ void __launch_bounds__(kHaloThreads2, 1)
             bool ok = true;
             unsigned long long w_in = 0;
             const long long t_begin = clock64();
-            for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
-                for (int c = 0; c < p.kchunks && ok; ++c) {
+            for (int v = blockIdx.x; v < vtiles && ok; v += gridDim.x) {
+                const TilePart tp = tile_part(p, v);
+                for (int c = tp.c0; c < tp.c1 && ok; ++c) {
                     if (!wait_prof(pfull_a + 8 * pp.idx, pp.phase, prof_on, w_in)) { report(p.status, kStatusSplitTimeout); ok = false; break; }
                     uint8_t* ph = patches + static_cast<size_t>(pp.idx) * patch_stride;
                     split_plane_lo_x4(ph, ph + p.patch_bytes, p.patch_tx, tid128, 128);

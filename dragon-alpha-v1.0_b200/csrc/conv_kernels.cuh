@@ -250,6 +250,36 @@ __global__ void __launch_bounds__(256) col2im_gather_kernel(const float* __restr
     }
 }
 
+// The same gather for any channel count, with P laid out tap-major: P[pixel][tap][ic], so that the
+// threads of a warp read neighbouring channels.  One thread per four input channels.
+__global__ void __launch_bounds__(256) col2im_gather_tapmajor_kernel(const float* __restrict__ P, float* __restrict__ dX, const PatchShape s)
+{
+    const int c4n = s.IC >> 2, taps = s.FH * s.FW;
+    const size_t ldp = static_cast<size_t>(s.IC) * taps;
+    const size_t total = static_cast<size_t>(s.N) * s.IH * s.IW * c4n;
+    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const int c0 = static_cast<int>(i % c4n) << 2;
+        size_t t = i / c4n;
+        const int iw = static_cast<int>(t % s.IW); t /= s.IW;
+        const int ih = static_cast<int>(t % s.IH);
+        const size_t n = t / s.IH;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int fh = (ih + s.ph) % s.sh; fh < s.FH; fh += s.sh) {
+            const int oh = (ih + s.ph - fh) / s.sh;
+            if (ih + s.ph - fh < 0 || oh >= s.OH) continue;
+            for (int fw = (iw + s.pw) % s.sw; fw < s.FW; fw += s.sw) {
+                const int ow = (iw + s.pw - fw) / s.sw;
+                if (iw + s.pw - fw < 0 || ow >= s.OW) continue;
+                const float4 v = __ldg(reinterpret_cast<const float4*>(
+                    P + ((n * s.OH + oh) * s.OW + ow) * ldp + static_cast<size_t>(fh * s.FW + fw) * s.IC + c0));
+                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+            }
+        }
+        *reinterpret_cast<float4*>(dX + i * 4) = acc;
+    }
+}
+
 // hi/lo planes of a whole tensor in global memory (weights are split once per call, not per tile).
 __global__ void split_tensor_kernel(const float4* __restrict__ src, float4* __restrict__ hi, float4* __restrict__ lo, size_t n4)
 {
@@ -259,6 +289,28 @@ __global__ void split_tensor_kernel(const float4* __restrict__ src, float4* __re
         split_tf32(a, b);
         hi[i] = a;
         lo[i] = b;
+    }
+}
+
+// out = sum of `splits` partial results of n4 float4 each (+ bias per column, + LeakyReLU): the tail of a
+// split-K forward / deltaX launch.  Partials are added in index order, so the result does not depend
+// on how the CTAs were scheduled.
+__global__ void splitk_reduce_kernel(const float4* __restrict__ part, size_t n4, int splits, const float* __restrict__ bias,
+                                     int ncols4, int act_on, float act_k, float4* __restrict__ out)
+{
+    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n4;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        float4 a = part[i];
+        for (int s = 1; s < splits; ++s) {
+            const float4 b = part[static_cast<size_t>(s) * n4 + i];
+            a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+        }
+        if (bias) {
+            const float4 b = *reinterpret_cast<const float4*>(bias + 4 * (i % ncols4));
+            a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+        }
+        if (act_on) leaky_relu4(a, act_k);
+        out[i] = a;
     }
 }
 
@@ -285,7 +337,7 @@ struct TapMap {
 // planes.  32 x 32 tiles through shared memory; grid (ceil(IC/32), ceil(OC/32), map.n).
 __global__ void __launch_bounds__(256)
     transpose_weights_kernel(const float* __restrict__ W, float* __restrict__ hi, float* __restrict__ lo, int OC,
-                             int IC, int taps, const TapMap map, int split)
+                             int IC, int taps, const TapMap map, int split, int tap_major = 0)
 {
     __shared__ float tile[32][33];
     const int t = blockIdx.z, tap = map.src[t], ic0 = blockIdx.x * 32, oc0 = blockIdx.y * 32;
@@ -299,7 +351,9 @@ __global__ void __launch_bounds__(256)
         const int ic = ic0 + r, oc = oc0 + tx;
         if (ic < IC && oc < OC) {
             const float x = tile[tx][r];
-            const size_t o = (static_cast<size_t>(ic) * map.n + t) * OC + oc;
+            // rows of Wt ordered (ic, tap), or (tap, ic) when tap_major
+            const size_t o = tap_major ? (static_cast<size_t>(t) * IC + ic) * OC + oc
+                                       : (static_cast<size_t>(ic) * map.n + t) * OC + oc;
             if (split) {
                 const float h = __uint_as_float(to_tf32_rna(x));
                 hi[o] = h;

@@ -23,6 +23,43 @@ def available():
                for n in ("Cuda_conv3D", "Cuda_dconv3D_deltaX", "Cuda_dconv3D_deltaW"))
 
 
+def reduce_available():
+    return os.path.exists(os.path.join(_HERE, "_ref", "libcu32_Cuda_reduce.so"))
+
+
+def field_nextN(N, M):
+    """Rows of the partial-sum block the next stage reads (Cuda_reduce.java:35-45)."""
+    if M > 15:
+        if N > 63:
+            return N >> 6
+        if N > 15:
+            return 1
+    if M > 7:
+        if N > 127:
+            return N >> 7
+        if N > 31:
+            return 1
+    return (N + 63) >> 6
+
+
+def field_linear(X2d, alpha=1.0, beta=0.0):
+    """The reference's Engine.field_sum on the GPU: CudaFloat32EngineBase.field_linear (:5811-5834) ->
+    Cuda_reduce.field_linear (Cuda_reduce/A.cu:117-131): column sums of alpha * X + beta over the rows
+    of X2d [N, M] (M a multiple of 4), with the partial-sum block V the Java side allocates."""
+    lib = _lib("Cuda_reduce")
+    f = lib.Java_z_dragon_engine_cuda_impl_math_Cuda_1reduce_field_1linear
+    f.restype = C.c_int
+    N, M = X2d.shape
+    nxt = field_nextN(N, M)
+    V = torch.empty(max(1, nxt * M), device=X2d.device, dtype=torch.float32)
+    Y = torch.full((M,), float("nan"), device=X2d.device, dtype=torch.float32)
+    torch.cuda.synchronize()
+    f(None, None, C.c_int64(torch.cuda.current_stream().cuda_stream), C.c_int64(X2d.data_ptr()), C.c_float(alpha), C.c_float(beta),
+      C.c_int(N), C.c_int(M), C.c_int64(V.data_ptr() if nxt != 1 else 0), C.c_int64(Y.data_ptr()), C.c_int(M), C.c_int(M), C.c_int(1))
+    torch.cuda.synchronize()
+    return Y
+
+
 def _lib(name):
     if name not in _LIBS:
         _LIBS[name] = C.CDLL(os.path.join(_HERE, "_ref", "libcu32_%s.so" % name))

@@ -10,6 +10,11 @@
 typedef int32_t jint;
 typedef int64_t jlong;
 typedef uint8_t jboolean;
+typedef float jfloat;
+typedef double jdouble;
+typedef int8_t jbyte;
+typedef uint16_t jchar;
+typedef int16_t jshort;
 typedef jint jsize;
 struct _jobject;
 typedef struct _jobject* jobject;

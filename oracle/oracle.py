@@ -126,7 +126,9 @@ def field_sum(X, row_length=-1):
     """Column sums of X seen as [rows][row_length], accumulated row after row in float as the
     reference's CPU loop does (z/util/math/vector/Matrix.java:2119-2127, field_linear with alpha = 1,
     beta = 0; Engine.field_sum, Engine.java:6945, is the GPU operator Conv3D's backward pass calls
-    for the bias gradient).  No golden vector of the reference covers it: parity unpinned."""
+    for the bias gradient).  The reference holds no golden vector for it; it is pinned on the GPU box
+    against the reference's own Cuda_reduce.field_linear kernel rebuilt from its checkout
+    (oracle/cu32_ref.field_linear, tests/test_gpu_field_sum.py)."""
     X = np.ascontiguousarray(X, np.float32)
     if row_length == -1:
         row_length = X.shape[-1]

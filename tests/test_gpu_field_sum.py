@@ -39,6 +39,28 @@ def test_field_sum_matches_oracle(pkg, eng, oracle_mod, shape):
         assert np.all(np.abs(seq - ref) <= 1e-4 * mag + 1e-30)
 
 
+@pytest.mark.parametrize("shape", [(4, 32, 32, 32), (3, 7, 5, 12), (16, 28, 28, 96), (64, 56, 56, 64), (5, 3, 3, 1028), (2, 2, 2, 8)])
+def test_field_sum_against_the_reference_gpu_kernel(pkg, eng, oracle_mod, shape):
+    """Pin against the reference itself: its Cuda_reduce.field_linear (Cuda_reduce/A.cu:117-131, what
+    Engine.field_sum runs), rebuilt for sm_100 from its checkout, on the same device tensor.  Both results
+    are fp32 sums in different orders: they agree within the rounding of such sums, and each agrees with
+    the double-precision sum."""
+    import torch
+    from oracle import cu32_ref
+    if not cu32_ref.reduce_available():
+        pytest.skip("oracle/_ref/libcu32_Cuda_reduce.so not built (needs the reference checkout)")
+    gen = torch.Generator(device="cuda:0").manual_seed(sum(shape) + 1)
+    dY = torch.randn(shape, device="cuda:0", generator=gen)
+    OC = shape[-1]
+    ours = eng.field_sum(dY, OC).cpu().numpy()
+    theirs = cu32_ref.field_linear(dY.view(-1, OC)).cpu().numpy()
+    ref, mag = oracle_mod.field_sum_f64(dY.cpu().numpy(), OC)
+    assert np.isfinite(theirs).all()
+    assert np.all(np.abs(theirs - ref) <= 1e-5 * mag + 1e-30), float(np.max(np.abs(theirs - ref) / (mag + 1e-30)))
+    assert np.all(np.abs(ours - theirs) <= 1e-5 * mag + 1e-30), float(np.max(np.abs(ours - theirs) / (mag + 1e-30)))
+    assert np.all(np.abs(ours - ref) <= REL * mag + 1e-30)
+
+
 def test_field_sum_positive_inputs_and_reproducibility(pkg, eng, oracle_mod):
     """All-positive input (a long sum without cancellation) and bit-identical repeats."""
     import torch

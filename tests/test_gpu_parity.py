@@ -143,8 +143,13 @@ def test_bench_channel_configurations(pkg, eng, oracle_mod, name, mode):
     # the kernel form must be the one the benchmark's batch-256 launch of this layer takes
     N, IH, IW, IC, OC = CASES[name][:5]
     dev = torch.device("cuda:0")
-    eng.conv3D(torch.from_numpy(X).to(dev), torch.from_numpy(W).to(dev), 1, 1, 1, 1)
-    small = lib.last_plan()
+    old = lib.set_option("SKINNY", 0)    # at this reduced batch the layer has few tiles; the benchmark's batch does not
+    try:
+        _, (X, W, B, dY, Y, dX, dW) = _run_case(pkg, eng, oracle_mod, name, mode, dists=("relu", "n01", "n01"))
+        eng.conv3D(torch.from_numpy(X).to(dev), torch.from_numpy(W).to(dev), 1, 1, 1, 1)
+        small = lib.last_plan()
+    finally:
+        lib.set_option("SKINNY", old)
     big_X = torch.zeros((256, IH, IW, IC), device=dev)
     eng.conv3D(big_X, torch.from_numpy(W).to(dev), 1, 1, 1, 1)
     big = lib.last_plan()
@@ -159,6 +164,57 @@ def test_bench_channel_configurations(pkg, eng, oracle_mod, name, mode):
             assert "halo_pair" in big and "three+side" in big, big
     elif OC % 256 == 0:
         assert "halo_pair" in big, big
+
+
+# Few output tiles and a long reduction (deep layers at a small batch): the forward / deltaX kernel
+# splits the reduction over otherwise idle SMs and a second kernel adds the partial sums.
+SKINNY_CASES = {
+    "skinny_2x2x512": (8, 2, 2, 512, 512, 3, 3, 1, 1, 1, 1),
+    "skinny_4x4x256": (16, 4, 4, 256, 256, 3, 3, 1, 1, 1, 1),
+    "skinny_16x16x128": (4, 16, 16, 128, 128, 3, 3, 1, 1, 1, 1),
+    "skinny_1x1_1024": (4, 7, 7, 1024, 256, 1, 1, 1, 1, 0, 0),
+    "skinny_ragged_oc": (4, 16, 8, 160, 72, 3, 3, 1, 1, 1, 1),
+}
+CASES.update(SKINNY_CASES)
+
+
+@pytest.mark.parametrize("mode", ["3xtf32", "tf32"])
+@pytest.mark.parametrize("name", list(SKINNY_CASES))
+def test_split_reduction_for_skinny_layers(pkg, eng, oracle_mod, name, mode):
+    import re
+    import torch
+    lib = pkg.submodule("lib")
+    res, (X, W, B, dY, Y, dX, dW) = _run_case(pkg, eng, oracle_mod, name, mode)
+    assert res["status"] == 0
+    tol = TOL[mode]
+    for op in ("fwd", "dx", "dw"):
+        m = res[op]
+        assert m["finite"] and m["norm"] <= tol["norm"] and m["comp"] <= tol["comp"], (name, op, res[op + "_algo"], m)
+    N, IH, IW, IC, OC, FH, FW, sh, sw, ph, pw = CASES[name]
+    dev = torch.device("cuda:0")
+    tX, tW, tB = (torch.from_numpy(a).to(dev) for a in (X, W, B))
+    y1 = eng.conv3D_biased(tX, tW, tB, sh, sw, ph, pw)
+    plan = lib.last_plan()
+    found = re.search(r"ksplit=(\d+)", plan)
+    assert found and int(found.group(1)) > 1, plan
+    ks = int(found.group(1))
+    # bit-identical repeats (the partial sums are added in a fixed order), in either math mode's one-issuer forms
+    y2 = eng.conv3D_biased(tX, tW, tB, sh, sw, ph, pw)
+    if mode == "3xtf32":
+        assert torch.equal(y1, y2)
+    # the same layer with the reduction in one piece: equal to rounding
+    old = lib.set_option("SKINNY", 0)
+    try:
+        y3 = eng.conv3D_biased(tX, tW, tB, sh, sw, ph, pw)
+        assert "ksplit=1" in lib.last_plan() or "halo_pair" in lib.last_plan(), lib.last_plan()
+    finally:
+        lib.set_option("SKINNY", old)
+    assert float((y1 - y3).abs().max()) <= tol["norm"] * float(y3.abs().max())
+    # bias and activation are applied once, by the kernel that adds the partial sums
+    ya = eng.conv3D_leakyRelu(tX, tW, tB, 0.1, sh, sw, ph, pw)
+    assert "ksplit=%d" % ks in lib.last_plan()
+    assert torch.equal(ya, torch.where(y1 > 0, y1, y1 * 0.1)) or float((ya - torch.where(y1 > 0, y1, y1 * 0.1)).abs().max()) <= 1e-6 * float(y1.abs().max())
+    assert lib.device_status() == 0
 
 
 EDGE_CASES = {
