@@ -64,6 +64,8 @@ def parse_args():
     ap.add_argument("--no-peak", action="store_true", help="skip the in-run measurement of the TF32 matmul peak")
     ap.add_argument("--no-cu32", action="store_true")
     ap.add_argument("--no-config3", action="store_true")
+    ap.add_argument("--config3-only", action="store_true",
+                    help="profiling aid: run only the ResNet-18 conv stack (with --no-graph: eager launches) and print its record")
     ap.add_argument("--config3-batch", type=int, default=None,
                     help="global batch of the ResNet-18 stack (default 512); 64 on one GPU shows the per-GPU compute of the 8-GPU case")
     ap.add_argument("--no-cpu", action="store_true")
@@ -558,14 +560,14 @@ class Config3:
         if self.env["world"] > 1:
             self.env["dist"].all_reduce(self.bucket.flat, op=self.env["dist"].ReduceOp.SUM)
 
-    def run(self, steps, repeats, barrier):
+    def run(self, steps, repeats, barrier, use_graph=True):
         torch, lib, dist, world, dev = self.env["torch"], self.env["lib"], self.env["dist"], self.env["world"], self.env["dev"]
         for _ in range(3):
             self.compute(); self.reduce()
         torch.cuda.synchronize()
         graph, in_graph, err, launches = None, False, None, None
         with_ar = world > 1 and os.environ.get("BENCH_GRAPH_AR", "1") != "0"
-        for attempt in ((True, False) if with_ar else (False,)):
+        for attempt in (() if not use_graph else (True, False) if with_ar else (False,)):
             try:
                 side = torch.cuda.Stream()
                 side.wait_stream(torch.cuda.current_stream())
@@ -689,6 +691,14 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    if args.config3_only:
+        rec = Config3(env, args.config3_batch or synth.RESNET18_BATCH).run(args.steps, args.repeats, barrier, use_graph=not args.no_graph)
+        if rank == 0:
+            print(json.dumps({"metric": "ResNet-18 conv stack step (profiling aid)", "value": rec["img_s"], "unit": "img/s",
+                              "n_gpus": world, "steps": args.steps, "config3": rec}))
+        if world > 1:
+            dist.destroy_process_group()
+        return
     sweep = Sweep(args, env)
     B = sweep.B
     warm = max(args.warmup, 3)

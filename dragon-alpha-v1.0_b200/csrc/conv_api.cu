@@ -57,7 +57,7 @@ enum Opt {
     OPT_HALO_ROW, OPT_HALO_JH, OPT_HALO_JW, OPT_HALO_STACK, OPT_HALO_WIDE, OPT_HALO_PAIR, OPT_HALO_FLAT,
     OPT_HALO_NARROW, OPT_HALO_DUAL, OPT_PATCH_MATRIX, OPT_DX_PHASES, OPT_DX_COL2IM, OPT_DX_TRANSPOSE,
     OPT_DW_STACKED, OPT_DW_DIAG, OPT_DW_CW, OPT_DW_R, OPT_DW_STATIC, OPT_CONV_PROF, OPT_SM_BUDGET,
-    OPT_SKINNY,
+    OPT_SKINNY, OPT_HALO_DEEP,
     OPT_COUNT
 };
 struct OptDef { const char* name; int dflt; };
@@ -66,7 +66,7 @@ static const OptDef kOptDefs[OPT_COUNT] = {
     {"HALO_ROW", 1}, {"HALO_JH", 0}, {"HALO_JW", 0}, {"HALO_STACK", 1}, {"HALO_WIDE", -1}, {"HALO_PAIR", -1}, {"HALO_FLAT", 1},
     {"HALO_NARROW", 1}, {"HALO_DUAL", 1}, {"PATCH_MATRIX", 1}, {"DX_PHASES", 1}, {"DX_COL2IM", 1}, {"DX_TRANSPOSE", 1},
     {"DW_STACKED", -1}, {"DW_DIAG", 1}, {"DW_CW", 0}, {"DW_R", 0}, {"DW_STATIC", 1}, {"CONV_PROF", 0}, {"SM_BUDGET", 0},
-    {"SKINNY", 1},
+    {"SKINNY", 1}, {"HALO_DEEP", 1},
 };
 static std::atomic<int> g_opt[OPT_COUNT];
 static std::once_flag g_opt_once;
@@ -728,6 +728,13 @@ static HaloChoice plan_halo(const IgemmPlan& pl, int BN, int mode3x, int b_mn, i
             if (need(npb, sb) > smem_cap) { npb = 1; sb = 4; while (need(npb, sb) > smem_cap && sb > 2) --sb; }
             if (need(npb, sb) > smem_cap) continue;
             while (sb < max_sb && need(npb, sb + 1) <= smem_cap && sb < taps) ++sb;
+            if (taps == 1 && opt(OPT_HALO_DEEP)) {
+                // a 1x1 product (also every patch-matrix form): one chunk is four K steps of work, far less
+                // than the latency of the loads that feed it, so the rings go as deep as shared memory allows
+                for (int cand = 6; cand > npb; --cand)
+                    if (need(cand, cand) <= smem_cap) { npb = cand; sb = cand; break; }
+                while (need(npb, sb + 1) <= smem_cap && sb < 8) ++sb;
+            }
             const int acc_bufs = (2 * J * accw <= 512) ? 2 : 1;
             const int rbk = NI > 1 ? 1 : (pl.oH + 16 * JH - 1) / (16 * JH), cbk = (pl.oW + 8 * JW - 1) / (8 * JW);
             const double eff = NI > 1 ? (double)NI * pl.oH * pl.oW / (128.0 * cbk)
@@ -2000,7 +2007,7 @@ int alpha_conv3d_deltaW(const AlphaConvShape* s, const float* X, const float* de
     if (algo == ALPHA_ALGO_TENSOR && !tensor_ok)
         return fail(ALPHA_E_ARG, "tensor deltaW path needs IC %% 32 == 0 (IC=%d)", s->IC);
     if (algo != ALPHA_ALGO_SIMT && patch_path_ok(s) && env_tile_mode() != 1 &&
-        (!tensor_ok || (tiny_image(s->OH, s->OW) && (s->FH > 1 || s->FW > 1)))) {
+        (!tensor_ok || (s->OH * s->OW <= 9 && (s->FH > 1 || s->FW > 1)))) {
         // deltaW[oc][k] = sum over pixels of deltaY[pixel][oc] * A[pixel][k]: a 1x1 deltaW over the patch matrix
         float* A = nullptr;
         int K = 0, Kp = 0;
