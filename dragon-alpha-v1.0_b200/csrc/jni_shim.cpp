@@ -1,6 +1,6 @@
-// JNI entry points of the three native classes this library replaces.  The exported names and
+// JNI entry points of the native classes this library replaces.  The exported names and
 // signatures are those of the reference's shims (Cuda_conv3D/A.cu:14-244, Cuda_dconv3D_deltaX/A.cu:14-325,
-// Cuda_dconv3D_deltaW/A.cu:16-154): each unpacks the Java stream array and forwards to the
+// Cuda_dconv3D_deltaW/A.cu:16-154, Cuda_matMul/A.cu:18-120): each unpacks the Java stream array and forwards to the
 // alpha_Cuda_* function of the same name.  A non-zero status becomes a pending
 // z.dragon.engine.cuda.impl.CudaException carrying the library's error text (the reference looks up
 // the stale class path z/jcuda/exception/CudaException, Cuda_conv3D/JNITool.cuh:16).
@@ -324,6 +324,44 @@ JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1dconv3D_1deltaW
     raise(env, alpha_Cuda_dconv3D_deltaW_dconv3D_deltaW_GemmSK_W1(st.v, st.n, GridZ,
     fp(X_address), IH, IW, fp(deltaY_address), fp(deltaW_address), fp(deltaW_buf_address), N, IC,
     OC));
+}
+
+// ---- Cuda_matMul (src/cu32_src/Cuda_matMul/Cuda_matMul/A.cu:18-120) ---------------------------------
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1matMul_SKbuf_1summary(JNIEnv* env, jclass,
+    jlong stream_address, jlong dCbuf_address, jlong dC_address, jint part, jint sizeC)
+{
+    raise(env, alpha_Cuda_matMul_SKbuf_summary(stream_address, fp(dCbuf_address), fp(dC_address), part, sizeC));
+}
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1matMul_matMul(JNIEnv* env, jclass,
+    jlongArray streamArray, jint length, jlong dA_address, jlong dB_address, jlong dC_address, jint N, jint M, jint K)
+{
+    Streams st = get_streams(env, streamArray, length);
+    raise(env, alpha_Cuda_matMul_matMul(st.v, st.n, fp(dA_address), fp(dB_address), fp(dC_address), N, M, K));
+}
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1matMul_matMulT1(JNIEnv* env, jclass,
+    jlongArray streamArray, jint length, jlong dA_address, jlong dB_address, jlong dC_address, jint N, jint M, jint K)
+{
+    Streams st = get_streams(env, streamArray, length);
+    raise(env, alpha_Cuda_matMul_matMulT1(st.v, st.n, fp(dA_address), fp(dB_address), fp(dC_address), N, M, K));
+}
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1matMul_matMulT1SK(JNIEnv* env, jclass,
+    jlongArray streamArray, jint length, jint GridZ, jlong dA_address, jlong dB_address, jlong dC_address,
+    jlong dCbuf_address, jint N, jint M, jint K)
+{
+    Streams st = get_streams(env, streamArray, length);
+    raise(env, alpha_Cuda_matMul_matMulT1SK(st.v, st.n, GridZ, fp(dA_address), fp(dB_address), fp(dC_address),
+    fp(dCbuf_address), N, M, K));
+}
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1matMul_matMulT2(JNIEnv* env, jclass,
+    jlongArray streamArray, jint length, jlong dA_address, jlong dB_address, jlong dC_address, jint N, jint M, jint K)
+{
+    Streams st = get_streams(env, streamArray, length);
+    raise(env, alpha_Cuda_matMul_matMulT2(st.v, st.n, fp(dA_address), fp(dB_address), fp(dC_address), N, M, K));
 }
 
 }  // extern "C"

@@ -1,0 +1,161 @@
+// Matrix products of the FullConnect path behind the reference's Cuda_matMul natives, on the kernels of
+// the convolution path: a matrix product is a 1x1 convolution over a "batch" of rows.
+//   C = A * B^T  (matMulT2)  forward:  Y[row][oc] = sum_ic X[row][ic] * W[oc][ic]
+//   C = A * B    (matMul)    deltaX:   dX[row][ic] = sum_oc dY[row][oc] * W[oc][ic]
+//   C = A^T * B  (matMulT1)  deltaW:   dW[oc][ic] = sum_row dY[row][oc] * X[row][ic]
+// so each form runs the tensor-core kernel (and every fallback) of the contraction it maps to.
+#include "../../include/alpha_conv_b200.h"
+#include "host_common.h"
+
+namespace alpha {
+int launch_buf_summary(cudaStream_t stream, const float* buf, float* deltaW, int part, size_t sizeW);
+void set_caller_scratch(void* ptr, size_t bytes);
+}
+using namespace alpha;
+
+namespace {
+
+// C[i][j] += bias[j]: the row-bias stage of matMul_biased (the reference runs linear_dual2D_row after
+// the product, CudaFloat32EngineBase.java:1156-1165).
+__global__ void add_bias_rows_kernel(float4* __restrict__ C, const float* __restrict__ bias, size_t n4, int cols4)
+{
+    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n4;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        float4 c = C[i];
+        const float4 b = *reinterpret_cast<const float4*>(bias + 4 * (i % cols4));
+        c.x += b.x; c.y += b.y; c.z += b.z; c.w += b.w;
+        C[i] = c;
+    }
+}
+
+// `rows` matrix rows as the pixels of a 1x1 convolution: images of 1 x 4 pixels when the row count
+// allows it (the engine pads every dimension to a multiple of 4), single pixels otherwise.  The
+// kernels flatten 1x1 problems over all pixels anyway; the image shape only matters to their fallbacks.
+AlphaConvShape rows_as_pixels(long long rows, int IC, int OC)
+{
+    AlphaConvShape s{};
+    const int w = rows % 4 == 0 ? 4 : 1;
+    s.N = static_cast<int>(rows / w);
+    s.IH = s.OH = 1; s.IW = s.OW = w;
+    s.IC = IC; s.OC = OC; s.FH = s.FW = 1; s.sh = s.sw = 1; s.ph = s.pw = 0;
+    return s;
+}
+
+int check_dims(const char* what, const void* A, const void* B, const void* C, int N, int M, int K)
+{
+    if (!A || !B || !C) return fail(ALPHA_E_ARG, "%s: null matrix pointer", what);
+    if (N <= 0 || M <= 0 || K <= 0) return fail(ALPHA_E_ARG, "%s: non-positive dimension (N=%d M=%d K=%d)", what, N, M, K);
+    return ALPHA_OK;
+}
+
+inline alpha_stream_t first_stream(const int64_t* streams, int length)
+{
+    return (streams && length > 0) ? reinterpret_cast<alpha_stream_t>(static_cast<intptr_t>(streams[0])) : nullptr;
+}
+
+}  // namespace
+
+extern "C" {
+
+int alpha_matMul(const float* A, const float* B, const float* bias, float* C, int N, int M, int K, alpha_stream_t stream)
+{
+    int rc = check_dims("matMul", A, B, C, N, M, K);
+    if (rc) return rc;
+    if (bias && (reinterpret_cast<uintptr_t>(bias) & 15)) return fail(ALPHA_E_ARG, "matMul: bias must be 16-byte aligned");
+    // B[K][M] is W[OC = K][IC = M]; A[N][K] is deltaY; C[N][M] is deltaX
+    AlphaConvShape s = rows_as_pixels(N, M, K);
+    rc = alpha_conv3d_deltaX(&s, A, B, C, stream);
+    if (rc || !bias) return rc;
+    const size_t n4 = static_cast<size_t>(N) * M / 4;
+    size_t blocks = (n4 + 255) / 256;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    add_bias_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<float4*>(C), bias, n4, M / 4);
+    note_launch("matmul_bias");
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(ALPHA_E_CUDA, "add_bias_rows_kernel launch failed: %s", cudaGetErrorString(e));
+    return ALPHA_OK;
+}
+
+int alpha_matMulT1(const float* A, const float* B, float* C, int N, int M, int K, alpha_stream_t stream)
+{
+    int rc = check_dims("matMulT1", A, B, C, N, M, K);
+    if (rc) return rc;
+    // A[K][N] is deltaY[row][OC = N]; B[K][M] is X[row][IC = M]; C[N][M] is deltaW[OC][IC]
+    AlphaConvShape s = rows_as_pixels(K, M, N);
+    return alpha_conv3d_deltaW(&s, B, A, C, stream);
+}
+
+int alpha_matMulT2(const float* A, const float* B, const float* bias, float* C, int N, int M, int K, alpha_stream_t stream)
+{
+    int rc = check_dims("matMulT2", A, B, C, N, M, K);
+    if (rc) return rc;
+    // A[N][K] is X[row][IC = K]; B[M][K] is W[OC = M][IC = K]; C[N][M] is Y; the bias is fused into the epilogue
+    AlphaConvShape s = rows_as_pixels(N, K, M);
+    return alpha_conv3d_forward(&s, A, B, bias, C, stream);
+}
+
+// ---- Cuda_matMul natives (src/cu32_src/Cuda_matMul/Cuda_matMul/A.cu:18-120) --------------------------
+
+int alpha_Cuda_matMul_matMul(const int64_t* streams, int length, float* A, float* B, float* C, int N, int M, int K)
+{
+    if (!streams || length < 1) return fail(ALPHA_E_ARG, "empty stream array");
+    return alpha_matMul(A, B, nullptr, C, N, M, K, first_stream(streams, length));
+}
+int alpha_Cuda_matMul_matMulT1(const int64_t* streams, int length, float* A, float* B, float* C, int N, int M, int K)
+{
+    if (!streams || length < 1) return fail(ALPHA_E_ARG, "empty stream array");
+    return alpha_matMulT1(A, B, C, N, M, K, first_stream(streams, length));
+}
+// Split-K entry: the complete product goes to C, the caller's (GridZ - 1) * N * M floats of Cbuf serve as
+// scratch and are left zero, so that the SKbuf_summary the engine runs next (C += sum of buffers) adds zeros.
+int alpha_Cuda_matMul_matMulT1SK(const int64_t* streams, int length, int GridZ, float* A, float* B, float* C, float* Cbuf,
+                                 int N, int M, int K)
+{
+    if (!streams || length < 1) return fail(ALPHA_E_ARG, "empty stream array");
+    if (GridZ > 1 && !Cbuf) return fail(ALPHA_E_ARG, "GridZ=%d but Cbuf is null", GridZ);
+    const size_t bytes = GridZ > 1 ? static_cast<size_t>(GridZ - 1) * N * M * sizeof(float) : 0;
+    if (bytes && (reinterpret_cast<uintptr_t>(Cbuf) & 255) == 0) set_caller_scratch(Cbuf, bytes);
+    const int rc = alpha_matMulT1(A, B, C, N, M, K, first_stream(streams, length));
+    set_caller_scratch(nullptr, 0);
+    if (rc) return rc;
+    if (bytes) {
+        cudaError_t e = cudaMemsetAsync(Cbuf, 0, bytes, static_cast<cudaStream_t>(first_stream(streams, length)));
+        if (e != cudaSuccess) return fail(ALPHA_E_CUDA, "cudaMemsetAsync(Cbuf): %s", cudaGetErrorString(e));
+    }
+    return ALPHA_OK;
+}
+int alpha_Cuda_matMul_matMulT2(const int64_t* streams, int length, float* A, float* B, float* C, int N, int M, int K)
+{
+    if (!streams || length < 1) return fail(ALPHA_E_ARG, "empty stream array");
+    return alpha_matMulT2(A, B, nullptr, C, N, M, K, first_stream(streams, length));
+}
+int alpha_Cuda_matMul_SKbuf_summary(int64_t stream, float* Cbuf, float* C, int part, int sizeC)
+{
+    if (part < 0 || sizeC <= 0 || (sizeC & 3) || !C || (part > 0 && !Cbuf))
+        return fail(ALPHA_E_ARG, "bad SKbuf_summary arguments (part=%d sizeC=%d)", part, sizeC);
+    if (part == 0) return ALPHA_OK;
+    return launch_buf_summary(reinterpret_cast<cudaStream_t>(static_cast<intptr_t>(stream)), Cbuf, C, part, static_cast<size_t>(sizeC));
+}
+
+// ---- CudaFloat32EngineBase operator methods (CudaFloat32EngineBase.java:1129-1245) -------------------
+
+int alpha_engine_matMul(float* C, const float* A, const float* B, int N, int M, int K, alpha_stream_t stream)
+{
+    return alpha_matMul(A, B, nullptr, C, N, M, K, stream);
+}
+int alpha_engine_matMul_biased(float* C, const float* A, const float* B, int N, int M, int K, const float* Bias, alpha_stream_t stream)
+{
+    if (!Bias) return fail(ALPHA_E_ARG, "matMul_biased needs a bias vector");
+    return alpha_matMul(A, B, Bias, C, N, M, K, stream);
+}
+int alpha_engine_matMulT1(float* C, const float* A, const float* B, int N, int M, int K, alpha_stream_t stream)
+{
+    return alpha_matMulT1(A, B, C, N, M, K, stream);
+}
+int alpha_engine_matMulT2(float* C, const float* A, const float* B, int N, int M, int K, alpha_stream_t stream)
+{
+    return alpha_matMulT2(A, B, nullptr, C, N, M, K, stream);
+}
+
+}  // extern "C"

@@ -174,6 +174,40 @@ class CudaFloat32EngineBase:
                                                        pw, _stream(self._stream)))
 
 
+    # ---- matrix products (CudaFloat32EngineBase.java:1129-1245) ---------------------------------------
+    def _mm(self, fn, *args):
+        if self._math >= 0:
+            old = self._lib.alpha_conv_get_math_mode()
+            _l.check(self._lib.alpha_conv_set_math_mode(self._math))
+            try:
+                _l.check(fn(*args))
+            finally:
+                self._lib.alpha_conv_set_math_mode(old)
+        else:
+            _l.check(fn(*args))
+
+    def matMul(self, C_address, A_address, B_address, N, M, K):
+        """C[N,M] = A[N,K] * B[K,M] (CudaFloat32EngineBase.matMul, :1129-1139)."""
+        a = self._addr
+        self._mm(self._lib.alpha_engine_matMul, a(C_address), a(A_address), a(B_address), N, M, K, _stream(self._stream))
+
+    def matMul_biased(self, C_address, A_address, B_address, N, M, K, Bias_address):
+        """C = A * B + Bias per row (CudaFloat32EngineBase.matMul_biased, :1142-1168)."""
+        a = self._addr
+        self._mm(self._lib.alpha_engine_matMul_biased, a(C_address), a(A_address), a(B_address), N, M, K, a(Bias_address),
+                 _stream(self._stream))
+
+    def matMulT1(self, C_address, A_address, B_address, N, M, K):
+        """C[N,M] = A[K,N]^T * B[K,M] (CudaFloat32EngineBase.matMulT1, :1185-1230)."""
+        a = self._addr
+        self._mm(self._lib.alpha_engine_matMulT1, a(C_address), a(A_address), a(B_address), N, M, K, _stream(self._stream))
+
+    def matMulT2(self, C_address, A_address, B_address, N, M, K):
+        """C[N,M] = A[N,K] * B[M,K]^T (CudaFloat32EngineBase.matMulT2, :1233-1245)."""
+        a = self._addr
+        self._mm(self._lib.alpha_engine_matMulT2, a(C_address), a(A_address), a(B_address), N, M, K, _stream(self._stream))
+
+
 def _pad4(n):
     return (n + 3) & ~3
 
@@ -282,6 +316,51 @@ class Engine:
         dX = torch.empty((N, IH, IW, ic4), dtype=torch.float32, device=deltaY.device)
         self.base.dconv3D_deltaX(dX, IH, IW, dYp, OH, OW, Wp, FH, FW, N, ic4, oc4, sh, sw, ph, pw)
         return dX if ic4 == IC else dX[..., :IC]
+
+    # ---- matrix products (Engine.matMul / matMulT1 / matMulT2, Engine.java) -------------------------------
+    @staticmethod
+    def _pad2(t):
+        r4, c4 = _pad4(t.shape[0]), _pad4(t.shape[1])
+        if (r4, c4) == tuple(t.shape):
+            return t.contiguous()
+        out = torch.zeros((r4, c4), dtype=t.dtype, device=t.device)
+        out[: t.shape[0], : t.shape[1]] = t
+        return out
+
+    def matMul(self, A, B, Bias=None):
+        """C[N,M] = A[N,K] * B[K,M] (+ Bias[M] per row); dimensions are zero-padded to multiples of 4 as the
+        engine's tensor memory is, and sliced back."""
+        (N, K), (K2, M) = A.shape, B.shape
+        if K != K2:
+            raise ValueError("A.width=%d != B.height=%d" % (K, K2))
+        Ap, Bp = self._pad2(A), self._pad2(B)
+        C = torch.empty((Ap.shape[0], Bp.shape[1]), dtype=torch.float32, device=A.device)
+        if Bias is None:
+            self.base.matMul(C, Ap, Bp, Ap.shape[0], Bp.shape[1], Ap.shape[1])
+        else:
+            bp = _pad_last(Bias.reshape(1, -1), Bp.shape[1]).reshape(-1)
+            self.base.matMul_biased(C, Ap, Bp, Ap.shape[0], Bp.shape[1], Ap.shape[1], bp)
+        return C[:N, :M]
+
+    def matMulT1(self, A, B):
+        """C[N,M] = A[K,N]^T * B[K,M]."""
+        (K, N), (K2, M) = A.shape, B.shape
+        if K != K2:
+            raise ValueError("A.height=%d != B.height=%d" % (K, K2))
+        Ap, Bp = self._pad2(A), self._pad2(B)
+        C = torch.empty((Ap.shape[1], Bp.shape[1]), dtype=torch.float32, device=A.device)
+        self.base.matMulT1(C, Ap, Bp, Ap.shape[1], Bp.shape[1], Ap.shape[0])
+        return C[:N, :M]
+
+    def matMulT2(self, A, B):
+        """C[N,M] = A[N,K] * B[M,K]^T."""
+        (N, K), (M, K2) = A.shape, B.shape
+        if K != K2:
+            raise ValueError("A.width=%d != B.width=%d" % (K, K2))
+        Ap, Bp = self._pad2(A), self._pad2(B)
+        C = torch.empty((Ap.shape[0], Bp.shape[0]), dtype=torch.float32, device=A.device)
+        self.base.matMulT2(C, Ap, Bp, Ap.shape[0], Bp.shape[0], Ap.shape[1])
+        return C[:N, :M]
 
     def dconv3D(self, X, W, sh, sw, ph, pw, OH=None, OW=None):
         """Deconv3D forward = dconv3D_deltaX with the roles of input and output swapped

@@ -99,6 +99,20 @@ def load():
     lib.alpha_Cuda_dconv3D_deltaW_dconv3D_deltaW_GemmSK.argtypes = sk
     lib.alpha_Cuda_dconv3D_deltaW_dconv3D_deltaW_GemmV2SK.argtypes = sk
     lib.alpha_Cuda_dconv3D_deltaW_dconv3D_deltaW_GemmSK_W1.argtypes = [SA, I, I, V, I, I, V, V, V, I, I, I]
+    # matrix products
+    lib.alpha_matMul.argtypes = [V, V, V, V, I, I, I, V]
+    lib.alpha_matMulT1.argtypes = [V, V, V, I, I, I, V]
+    lib.alpha_matMulT2.argtypes = [V, V, V, V, I, I, I, V]
+    lib.alpha_engine_matMul.argtypes = [V, V, V, I, I, I, V]
+    lib.alpha_engine_matMul_biased.argtypes = [V, V, V, I, I, I, V, V]
+    lib.alpha_engine_matMulT1.argtypes = [V, V, V, I, I, I, V]
+    lib.alpha_engine_matMulT2.argtypes = [V, V, V, I, I, I, V]
+    mm = [SA, I, V, V, V, I, I, I]
+    lib.alpha_Cuda_matMul_matMul.argtypes = mm
+    lib.alpha_Cuda_matMul_matMulT1.argtypes = mm
+    lib.alpha_Cuda_matMul_matMulT2.argtypes = mm
+    lib.alpha_Cuda_matMul_matMulT1SK.argtypes = [SA, I, I, V, V, V, V, I, I, I]
+    lib.alpha_Cuda_matMul_SKbuf_summary.argtypes = [L, V, V, I, I]
     _lib = lib
     return lib
 

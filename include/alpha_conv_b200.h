@@ -345,6 +345,35 @@ int alpha_engine_dconv3D_deltaX(float* deltaX, int IH, int IW, const float* delt
                                 const float* W, int FH, int FW, int N, int IC, int OC, int sh,
                                 int sw, int ph, int pw, alpha_stream_t stream);
 
+/* ---- matrix products (the FullConnect path; SURVEY's next contraction after the convolutions) ----------
+ *
+ * Row-major fp32 matrices whose dimensions arrive padded to multiples of 4 like every tensor of the
+ * engine.  A matrix product is a 1x1 convolution over rows, so each form runs on the kernels of the
+ * contraction it maps to (forward / deltaX / deltaW), tensor cores, math modes and fallbacks included.
+ * Replace the SIMT kernels behind src/cu32_src/Cuda_matMul/Cuda_matMul/matMul.cuh, matMulT1.cuh, matMulT2.cuh. */
+/* C[N,M] = A[N,K] * B[K,M] (+ bias[M] per row when bias != NULL: matMul_biased, CudaFloat32EngineBase.java:1142-1168) */
+int alpha_matMul(const float* A, const float* B, const float* bias, float* C, int N, int M, int K, alpha_stream_t stream);
+/* C[N,M] = A[K,N]^T * B[K,M] (Cuda_matMul.matMulT1 / matMulT1SK + SKbuf_summary, CudaFloat32EngineBase.java:1185-1230) */
+int alpha_matMulT1(const float* A, const float* B, float* C, int N, int M, int K, alpha_stream_t stream);
+/* C[N,M] = A[N,K] * B[M,K]^T (+ bias[M], fused into the epilogue) (CudaFloat32EngineBase.java:1233-1245) */
+int alpha_matMulT2(const float* A, const float* B, const float* bias, float* C, int N, int M, int K, alpha_stream_t stream);
+
+/* Cuda_matMul natives: src/cu32_src/Cuda_matMul/Cuda_matMul/A.cu:18-120.  matMulT1SK writes the complete
+ * product into C, uses the caller's Cbuf as scratch and leaves it zero; SKbuf_summary is C += sum of buffers. */
+int alpha_Cuda_matMul_SKbuf_summary(int64_t stream, float* Cbuf, float* C, int part, int sizeC);
+int alpha_Cuda_matMul_matMul(const int64_t* streams, int length, float* A, float* B, float* C, int N, int M, int K);
+int alpha_Cuda_matMul_matMulT1(const int64_t* streams, int length, float* A, float* B, float* C, int N, int M, int K);
+int alpha_Cuda_matMul_matMulT1SK(const int64_t* streams, int length, int GridZ, float* A, float* B, float* C,
+                                 float* Cbuf, int N, int M, int K);
+int alpha_Cuda_matMul_matMulT2(const int64_t* streams, int length, float* A, float* B, float* C, int N, int M, int K);
+
+/* CudaFloat32EngineBase.matMul / matMul_biased / matMulT1 / matMulT2 in the Java argument order. */
+int alpha_engine_matMul(float* C, const float* A, const float* B, int N, int M, int K, alpha_stream_t stream);
+int alpha_engine_matMul_biased(float* C, const float* A, const float* B, int N, int M, int K, const float* Bias,
+                               alpha_stream_t stream);
+int alpha_engine_matMulT1(float* C, const float* A, const float* B, int N, int M, int K, alpha_stream_t stream);
+int alpha_engine_matMulT2(float* C, const float* A, const float* B, int N, int M, int K, alpha_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

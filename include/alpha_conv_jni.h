@@ -148,6 +148,24 @@ JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1dconv3D_1deltaW
     jlongArray streamArray, jint length, jint GridZ, jlong X_address, jint IH, jint IW, jlong
     deltaY_address, jlong deltaW_address, jlong deltaW_buf_address, jint N, jint IC, jint OC);
 
+/* Cuda_matMul: src/cu32_src/Cuda_matMul/Cuda_matMul/A.cu:18 (SKbuf_summary), :36 (matMul), :59 (matMulT1),
+ * :76 (matMulT1SK), :104 (matMulT2); Java declarations in z/dragon/engine/cuda/impl/math/Cuda_matMul.java. */
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1matMul_SKbuf_1summary(JNIEnv* env, jclass cls,
+    jlong stream_address, jlong dCbuf_address, jlong dC_address, jint part, jint sizeC);
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1matMul_matMul(JNIEnv* env, jclass cls,
+    jlongArray streamArray, jint length, jlong dA_address, jlong dB_address, jlong dC_address, jint N, jint M, jint K);
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1matMul_matMulT1(JNIEnv* env, jclass cls,
+    jlongArray streamArray, jint length, jlong dA_address, jlong dB_address, jlong dC_address, jint N, jint M, jint K);
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1matMul_matMulT1SK(JNIEnv* env, jclass cls,
+    jlongArray streamArray, jint length, jint GridZ, jlong dA_address, jlong dB_address, jlong dC_address,
+    jlong dCbuf_address, jint N, jint M, jint K);
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1matMul_matMulT2(JNIEnv* env, jclass cls,
+    jlongArray streamArray, jint length, jlong dA_address, jlong dB_address, jlong dC_address, jint N, jint M, jint K);
+
 #ifdef __cplusplus
 }
 #endif

@@ -382,3 +382,48 @@ float oracle_samePercentRelative(const float *A, const float *B, size_t length, 
     }
     return (float)sum / (float)length;
 }
+
+/*
+ * Matrix products of the FullConnect path (the "next" contraction after the convolutions).
+ * Follow the CPU loops of the reference's own tests, experiments/test_cuda/Cuda_matMul_test.java:28-36
+ * (multiply), Cuda_matMul_test_T1.java:27-35 (multiplyT1), Cuda_matMul_test_T2.java:27-35 (multiplyT2),
+ * and the same loops in src/cu32_src/Cuda_matMul/Cuda_matMul/test.cuh:59-81: loop order k -> i -> j,
+ * `float C[i][j] += A * B` (float product, float add), C zero at the start.
+ *   variant 0: C[N,M] = A[N,K]   * B[K,M]
+ *   variant 1: C[N,M] = A[K,N]^T * B[K,M]
+ *   variant 2: C[N,M] = A[N,K]   * B[M,K]^T
+ */
+void oracle_matmul(const float *A, const float *B, float *C, int N, int M, int K, int variant)
+{
+    memset(C, 0, sizeof(float) * (size_t)N * M);
+    for (int k = 0; k < K; k++)
+        for (int i = 0; i < N; i++) {
+            const float a = variant == 1 ? A[(size_t)k * N + i] : A[(size_t)i * K + k];
+            for (int j = 0; j < M; j++) {
+                const float b = variant == 2 ? B[(size_t)j * K + k] : B[(size_t)k * M + j];
+                C[(size_t)i * M + j] += a * b;
+            }
+        }
+}
+
+/* The same products in double, with S[i][j] = sum_k |a||b| (the scale of the forward error bound). */
+void oracle_matmul_f64(const float *A, const float *B, double *C, double *S, int N, int M, int K, int variant,
+                       int threads)
+{
+    (void)threads;
+#if defined(_OPENMP)
+#pragma omp parallel for schedule(static) num_threads(threads > 0 ? threads : 1)
+#endif
+    for (int i = 0; i < N; i++)
+        for (int j = 0; j < M; j++) {
+            double v = 0, sa = 0;
+            for (int k = 0; k < K; k++) {
+                const double a = variant == 1 ? A[(size_t)k * N + i] : A[(size_t)i * K + k];
+                const double b = variant == 2 ? B[(size_t)j * K + k] : B[(size_t)k * M + j];
+                v += a * b;
+                sa += fabs(a * b);
+            }
+            C[(size_t)i * M + j] = v;
+            S[(size_t)i * M + j] = sa;
+        }
+}

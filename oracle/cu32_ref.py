@@ -60,6 +60,71 @@ def field_linear(X2d, alpha=1.0, beta=0.0):
     return Y
 
 
+def matmul_available():
+    return os.path.exists(os.path.join(_HERE, "_ref", "libcu32_Cuda_matMul.so"))
+
+
+class Cu32MatMul:
+    """The reference's matMul / matMulT1 / matMulT2 on the GPU, natives called as CudaFloat32EngineBase
+    does (:1129-1245): matMulT1 switches to the split-K native plus SKbuf_summary from K = 512 on.
+    `lib` is the rebuilt reference library by default; a test passes another implementation of the natives."""
+
+    def __init__(self, lib=None, env=None):
+        self.lib = lib if lib is not None else _lib("Cuda_matMul")
+        self.env = env if env is not None else _FakeEnv()
+        self.streams = [torch.cuda.Stream() for _ in range(10)]
+        self.env.streams = [s.cuda_stream for s in self.streams]
+        self.called = []
+
+    def _call(self, name, *args):
+        f = getattr(self.lib, "Java_z_dragon_engine_cuda_impl_math_Cuda_1matMul_" + name)
+        f.restype = None
+        conv = []
+        for a in args:
+            if isinstance(a, torch.Tensor):
+                conv.append(C.c_int64(a.data_ptr()))
+            elif a == "streams":
+                conv.append(C.c_void_p(0x5EED))
+            elif isinstance(a, tuple) and a[0] == "long":
+                conv.append(C.c_int64(a[1]))
+            else:
+                conv.append(C.c_int(int(a)))
+        f(self.env.env, None, *conv)
+        self.called.append(name)
+
+    def matMul(self, A, B):
+        (N, K), (_, M) = A.shape, B.shape
+        Cm = torch.full((N, M), float("nan"), device=A.device, dtype=torch.float32)
+        torch.cuda.synchronize()
+        self._call("matMul", "streams", 10, A, B, Cm, N, M, K)
+        torch.cuda.synchronize()
+        return Cm
+
+    def matMulT2(self, A, B):
+        (N, K), (M, _) = A.shape, B.shape
+        Cm = torch.full((N, M), float("nan"), device=A.device, dtype=torch.float32)
+        torch.cuda.synchronize()
+        self._call("matMulT2", "streams", 10, A, B, Cm, N, M, K)
+        torch.cuda.synchronize()
+        return Cm
+
+    def matMulT1(self, A, B, threshold=512, max_part=16):
+        (K, N), (_, M) = A.shape, B.shape
+        Cm = torch.full((N, M), float("nan"), device=A.device, dtype=torch.float32)
+        torch.cuda.synchronize()
+        if K < threshold:
+            self._call("matMulT1", "streams", 10, A, B, Cm, N, M, K)
+        else:
+            GridZ = K >> 8 if K < 1024 else (K >> 9 if K < 2048 else K >> 10)
+            GridZ = min(GridZ, max_part)
+            buf = torch.empty(max(1, N * M * (GridZ - 1)), device=A.device, dtype=torch.float32)
+            self._call("matMulT1SK", "streams", 10, GridZ, A, B, Cm, buf, N, M, K)
+            torch.cuda.synchronize()
+            self._call("SKbuf_1summary", ("long", self.streams[0].cuda_stream), buf, Cm, GridZ - 1, N * M)
+        torch.cuda.synchronize()
+        return Cm
+
+
 def _lib(name):
     if name not in _LIBS:
         _LIBS[name] = C.CDLL(os.path.join(_HERE, "_ref", "libcu32_%s.so" % name))

@@ -272,3 +272,55 @@ def ref_deconv3D_deltaW_img2col2(X, dY, FH, FW, sh, sw, ph, pw):
                                            dW.ctypes.data_as(_F), _i(FH), _i(FW), _i(N), _i(IC),
                                            _i(OC), _i(sh), _i(sw), _i(ph), _i(pw))
     return dW
+
+
+# ---- matrix products (FullConnect path) ----------------------------------------------------------
+
+_MM_VARIANT = {"matMul": 0, "matMulT1": 1, "matMulT2": 2}
+
+
+def _mm_dims(A, B, variant):
+    if variant == 0:
+        (N, K), (K2, M) = A.shape, B.shape
+    elif variant == 1:
+        (K, N), (K2, M) = A.shape, B.shape
+    else:
+        (N, K), (M, K2) = A.shape, B.shape
+    if K != K2:
+        raise ValueError("inner dimensions differ: %d, %d" % (K, K2))
+    return N, M, K
+
+
+def matmul(A, B, variant="matMul"):
+    """C = A*B ('matMul', A[N,K], B[K,M]), A^T*B ('matMulT1', A[K,N], B[K,M]) or A*B^T ('matMulT2', A[N,K], B[M,K]) with
+    the float loops of the reference's own tests (Cuda_matMul_test*.java:27-36; Cuda_matMul/test.cuh:59-81)."""
+    v = _MM_VARIANT[variant]
+    A, pa = _f(A)
+    B, pb = _f(B)
+    N, M, K = _mm_dims(A, B, v)
+    Cm = np.empty((N, M), np.float32)
+    lib().oracle_matmul(pa, pb, Cm.ctypes.data_as(_F), _i(N), _i(M), _i(K), _i(v))
+    return Cm
+
+
+def matmul_f64(A, B, variant="matMul", threads=1):
+    """The same product in double, and S = sum_k |a||b| per element."""
+    v = _MM_VARIANT[variant]
+    A, pa = _f(A)
+    B, pb = _f(B)
+    N, M, K = _mm_dims(A, B, v)
+    Cm, S = np.empty((N, M), np.float64), np.empty((N, M), np.float64)
+    lib().oracle_matmul_f64(pa, pb, Cm.ctypes.data_as(_D), S.ctypes.data_as(_D), _i(N), _i(M), _i(K), _i(v), _i(threads))
+    return Cm, S
+
+
+def ref_matmul(A, B, variant="matMul"):
+    """The reference project's own C++ loop (multiply / multiplyT1 / multiplyT2 of Cuda_matMul/test.cuh)."""
+    v = _MM_VARIANT[variant]
+    A, pa = _f(A)
+    B, pb = _f(B)
+    N, M, K = _mm_dims(A, B, v)
+    Cm = np.zeros((N, M), np.float32)
+    fn = getattr(ref_lib(), ("ref_multiply", "ref_multiplyT1", "ref_multiplyT2")[v])
+    fn(pa, pb, Cm.ctypes.data_as(_F), _i(N), _i(M), _i(K))
+    return Cm

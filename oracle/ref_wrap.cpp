@@ -7,16 +7,23 @@
 //   CONV_3D_NAIVE             src/cu32_src/Cuda_conv3D/Cuda_conv3D/test.cuh:80-110
 //   deconv3D_deltaX_img2col   src/cu32_src/Cuda_dconv3D_deltaX/Cuda_dconv3D_deltaX/test.cuh:89-131
 //   deconv3D_deltaW_img2col2  src/cu32_src/Cuda_dconv3D_deltaW/Cuda_dconv3D_deltaW/test.cuh:77-121
-// This file only supplies the one indexing macro they use (get4d, micro.cuh:93 of each library)
-// and exports them with C linkage.  No reference source text is stored in this repository.
+// and, for the matrix products of the FullConnect path,
+//   multiply, multiplyT1, multiplyT2   src/cu32_src/Cuda_matMul/Cuda_matMul/test.cuh:59-81
+// This file only supplies the indexing macros they use (get4d, micro.cuh:93 of each conv library; get,
+// Cuda_matMul/micro.cuh:21) and exports them with C linkage.  No reference source text is stored in this repository.
 #include <cstddef>
 #include <cmath>
 
 #define get4d(A, w, z, y, x, Sz, Sy, Sx) A[(((w) * (Sz) + (z)) * (Sy) + (y)) * (Sx) + (x)]
 
+#define get(A, i, j, stride) A[(i) * (stride) + (j)]
+
 #include "conv3D_naive.inc"
 #include "deltaX_img2col.inc"
 #include "deltaW_img2col2.inc"
+#include "matmul.inc"
+#include "matmulT1.inc"
+#include "matmulT2.inc"
 
 extern "C" {
 
@@ -39,5 +46,10 @@ void ref_deconv3D_deltaW_img2col2(float *X, int IH, int IW, float *deltaY, int O
 {
     deconv3D_deltaW_img2col2(X, IH, IW, deltaY, OH, OW, deltaW, FH, FW, N, IC, OC, sh, sw, ph, pw);
 }
+
+// C must be zero on entry (the loops accumulate into it), as in the reference's own test driver.
+void ref_multiply(float *A, float *B, float *C, int N, int M, int K) { multiply(A, B, C, N, M, K); }
+void ref_multiplyT1(float *A, float *B, float *C, int N, int M, int K) { multiplyT1(A, B, C, N, M, K); }
+void ref_multiplyT2(float *A, float *B, float *C, int N, int M, int K) { multiplyT2(A, B, C, N, M, K); }
 
 }  // extern "C"

@@ -1,4 +1,4 @@
-"""Generates tests/golden/conv_golden.npz.
+"""Generates tests/golden/conv_golden.npz and tests/golden/matmul_golden.npz.
 
 Run in a container that has the reference checkout (so that `make -C oracle ref` has built
 oracle/_ref/libref_cpu.so).  For each small seeded case the file stores the inputs and
@@ -7,7 +7,9 @@ oracle/_ref/libref_cpu.so).  For each small seeded case the file stores the inpu
   java_*  outputs of the C restatement of the Java loops (Tense.conv3D_naive, deconv3d_deltaW_naive),
           which no JVM-less machine can run in the original; they are stored as a regression anchor
           and must stay within fp32 round-off of the ref_* values.
-The GPU box has no reference checkout; the committed file is what travels.
+matmul_golden.npz holds, for small seeded matrices, the outputs of the reference's own multiply /
+multiplyT1 / multiplyT2 loops (src/cu32_src/Cuda_matMul/Cuda_matMul/test.cuh:59-81).
+The GPU box has no reference checkout; the committed files are what travels.
 """
 import os
 import sys
@@ -27,6 +29,15 @@ CASES = {
     "g_1x1": (2, 6, 6, 16, 8, 1, 1, 1, 1, 0, 0, "u11"),
     "g_3x3_nopad": (2, 7, 7, 4, 4, 3, 3, 1, 1, 0, 0, "u01"),
     "g_ic32_oc32": (2, 6, 6, 32, 32, 3, 3, 1, 1, 1, 1, "n01"),
+}
+
+
+# name: (N, M, K, input distribution); N, M, K multiples of 4 as the engine pads them
+MATMUL_CASES = {
+    "m_small": (8, 12, 16, "u11"),
+    "m_k32": (16, 8, 32, "n01"),
+    "m_ragged": (20, 36, 44, "u01"),
+    "m_tall": (64, 4, 8, "u11"),
 }
 
 
@@ -58,6 +69,16 @@ def main():
         out[name + "/java_dW"] = O.deconv3d_deltaW_naive(X, dY, FH, FW, sh, sw, ph, pw)
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "conv_golden.npz")
     np.savez_compressed(path, **out)
+    print("wrote", path, os.path.getsize(path), "bytes")
+    mm = {}
+    for i, (name, (N, M, K, dist)) in enumerate(MATMUL_CASES.items()):
+        rng = np.random.Generator(np.random.Philox(2000 + i))
+        for variant, (sa, sb) in (("matMul", ((N, K), (K, M))), ("matMulT1", ((K, N), (K, M))), ("matMulT2", ((N, K), (M, K)))):
+            A, B = gen(sa, dist, rng), gen(sb, dist, rng)
+            mm["%s/%s/A" % (name, variant)], mm["%s/%s/B" % (name, variant)] = A, B
+            mm["%s/%s/ref_C" % (name, variant)] = O.ref_matmul(A, B, variant)
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "matmul_golden.npz")
+    np.savez_compressed(path, **mm)
     print("wrote", path, os.path.getsize(path), "bytes")
 
 

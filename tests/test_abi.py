@@ -22,15 +22,17 @@ def _declared_symbols():
     for fn in sorted(os.listdir(INCLUDE)):
         text = open(os.path.join(INCLUDE, fn)).read()
         text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-        names.update(re.findall(r"\b(alpha_(?:conv|Cuda|engine)\w*)\s*\(", text))
+        names.update(re.findall(r"\b(alpha_(?:conv|Cuda|engine|matMul)\w*)\s*\(", text))
         names.update(re.findall(r"\b(Java_z_dragon_\w+)\s*\(", text))
     return sorted(names)
 
 
 def test_every_declared_symbol_is_exported(lib):
     names = _declared_symbols()
-    assert len([n for n in names if n.startswith("Java_")]) == 29
-    assert len([n for n in names if n.startswith("alpha_Cuda_")]) == 29
+    # 29 natives of the three convolution classes + 5 of Cuda_matMul
+    assert len([n for n in names if n.startswith("Java_")]) == 34
+    assert len([n for n in names if n.startswith("alpha_Cuda_")]) == 34
+    assert len([n for n in names if n.startswith("alpha_matMul")]) == 3
     missing = [n for n in names if not hasattr(lib, n)]
     assert not missing, missing
 
@@ -72,6 +74,10 @@ def test_options_and_per_call_settings_need_no_device(lib, pkg):
     assert lib.alpha_conv3d_forward_ex(C.byref(s), 16, 32, None, 48, 2, -1, None) == -1      # math mode 2 does not exist
     assert lib.alpha_conv3d_deltaX_ex(C.byref(s), 16, 32, 48, -1, 9, None) == -1             # nor algo 9
     assert lib.alpha_conv3d_deltaW_ex(C.byref(s), None, 32, 48, -1, -1, None) == -1          # null X, default settings
+    assert lib.alpha_matMul(None, 16, None, 32, 8, 8, 8, None) == -1 and b"null" in lib.alpha_conv_last_error()
+    assert lib.alpha_matMulT1(16, 32, 48, 8, 0, 8, None) == -1                               # M = 0
+    assert lib.alpha_matMulT2(16, 32, None, 48, 8, 8, 6, None) == -1                         # K = 6: not a multiple of 4
+    assert lib.alpha_Cuda_matMul_SKbuf_summary(0, None, None, 3, 64) == -1
     n = C.c_size_t(0)
     assert lib.alpha_conv_workspace_bytes(C.byref(s), 17, C.byref(n)) == -1                  # unknown op
     assert lib.alpha_conv_workspace_bytes(None, 0, C.byref(n)) == -1

@@ -132,3 +132,23 @@ def test_field_sum_follows_the_reference_loop(oracle_mod):
     assert np.array_equal(got, want)
     d, mag = oracle_mod.field_sum_f64(A, 12)
     assert np.all(np.abs(d - want) <= 1e-5 * mag)
+
+
+def test_matmul_oracle_against_the_reference_loops(oracle_mod):
+    """The float loops of the three matrix products reproduce the stored outputs of the reference's own
+    multiply / multiplyT1 / multiplyT2 (tests/golden/matmul_golden.npz) bit for bit, and sit within fp32
+    rounding of the double-precision product."""
+    import os
+    O = oracle_mod
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "matmul_golden.npz"))
+    keys = sorted({k.rsplit("/", 1)[0] for k in g.files})
+    assert len(keys) == 12
+    for key in keys:
+        variant = key.split("/")[1]
+        A, B, ref = g[key + "/A"], g[key + "/B"], g[key + "/ref_C"]
+        got = O.matmul(A, B, variant)
+        assert np.array_equal(got, ref), key
+        c64, S = O.matmul_f64(A, B, variant)
+        assert (np.abs(got - c64) <= 1e-5 * S + 1e-30).all(), key
+        if O.ref_lib() is not None:
+            assert np.array_equal(O.ref_matmul(A, B, variant), ref), key
