@@ -684,6 +684,22 @@ static void halo_launch_fw(const HaloLaunch& L, int JH, int JW, bool row)
 #undef HALO_J
 }
 
+// Split-K parts for a launch of `tiles` macro tiles whose reduction has `kchunks` chunks of `taps` W-tile
+// stages each: 1 unless the tiles cover less than half of the SMs and the reduction is long enough.
+static int halo_ksplit(const IgemmPlan& pl, long long tiles, int kchunks, int sm_count)
+{
+    const bool dense_out = pl.oSH == 1 && pl.oSW == 1 && pl.oNH == 0 && pl.oNW == 0;
+    const int taps = pl.FH * pl.FW;
+    if (!dense_out || !opt(OPT_SKINNY) || kchunks < 2 || 2 * tiles > sm_count || (long long)kchunks * taps < 16) return 1;
+    int ksplit = (int)(sm_count / tiles);
+    if (ksplit > 16) ksplit = 16;
+    if (ksplit > kchunks) ksplit = kchunks;
+    // every part gets at least four W-tile stages to amortise its prologue and epilogue
+    while (ksplit > 1 && (long long)((kchunks + ksplit - 1) / ksplit) * taps < 4) --ksplit;
+    const int cps = (kchunks + ksplit - 1) / ksplit;
+    return (kchunks + cps - 1) / cps;
+}
+
 static HaloChoice plan_halo(const IgemmPlan& pl, int BN, int mode3x, int b_mn, int sm_count)
 {
     HaloChoice best;
@@ -763,7 +779,11 @@ static HaloChoice plan_halo(const IgemmPlan& pl, int BN, int mode3x, int b_mn, i
             if (!stat) t *= 1.3; else if (!row) t *= 1.05;
             // whole-launch cost: the busiest persistent CTA walks ceil(tiles / SMs) macro tiles
             const long long n_macro = (long long)((pl.ncols + BN - 1) / BN) * ((pl.aN + NI - 1) / NI) * rbk * cbk;
-            const double cost = t * (double)((n_macro + sm_count - 1) / sm_count);
+            double cost = t * (double)((n_macro + sm_count - 1) / sm_count);
+            // few tiles: the launch splits the reduction over idle SMs (halo_ksplit), so a wide tile that
+            // moves fewer bytes per FLOP no longer costs parallelism
+            const int ks = halo_ksplit(pl, n_macro, kchunks, sm_count);
+            if (ks > 1) cost = t / ks + 4000.0;
             if (!best.valid || cost < best.cost) {
                 best.valid = true; best.JH = JH; best.JW = JW; best.npb = npb; best.sb = sb;
                 best.acc_bufs = acc_bufs; best.cost = cost; best.eff = eff; best.row = row; best.stat = stat; best.NI = NI; best.wide = wide != 0;
@@ -1013,19 +1033,8 @@ static int launch_halo(DeviceCtx* c, const IgemmPlan& pl_in, int mode3x, cudaStr
     // computed as ksplit partial sums over disjoint ranges of the reduction chunks, each by its own
     // CTA, into scratch laid out as ksplit copies of the output; a second kernel adds them in order
     // (with the bias and the activation, which the partial sums must not see).
-    int ksplit = 1;
-    const bool dense_out = pl.oSH == 1 && pl.oSW == 1 && pl.oNH == 0 && pl.oNW == 0;
-    if (dense_out && opt(OPT_SKINNY) && p.kchunks >= 2 && 2 * p.total_tiles <= sm_budget(c) &&
-        (long long)p.kchunks * pl.FH * pl.FW >= 16) {
-        ksplit = sm_budget(c) / p.total_tiles;
-        if (ksplit > 16) ksplit = 16;
-        if (ksplit > p.kchunks) ksplit = p.kchunks;
-        // every part gets at least four W-tile stages to amortise its prologue and epilogue
-        while (ksplit > 1 && (long long)((p.kchunks + ksplit - 1) / ksplit) * pl.FH * pl.FW < 4) --ksplit;
-        const int cps = (p.kchunks + ksplit - 1) / ksplit;
-        ksplit = (p.kchunks + cps - 1) / cps;
-        p.cps = cps;
-    }
+    const int ksplit = halo_ksplit(pl, p.total_tiles, p.kchunks, sm_budget(c));
+    p.cps = (p.kchunks + ksplit - 1) / ksplit;
     p.ksplit = ksplit;
     float* out_ptr = pl.out;
     const size_t out_floats = (size_t)pl.aN * pl.oH * pl.oW * pl.ncols;
