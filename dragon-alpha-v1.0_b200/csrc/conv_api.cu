@@ -57,7 +57,7 @@ enum Opt {
     OPT_HALO_ROW, OPT_HALO_JH, OPT_HALO_JW, OPT_HALO_STACK, OPT_HALO_WIDE, OPT_HALO_PAIR, OPT_HALO_FLAT,
     OPT_HALO_NARROW, OPT_HALO_DUAL, OPT_PATCH_MATRIX, OPT_DX_PHASES, OPT_DX_COL2IM, OPT_DX_TRANSPOSE,
     OPT_DW_STACKED, OPT_DW_DIAG, OPT_DW_CW, OPT_DW_R, OPT_DW_STATIC, OPT_CONV_PROF, OPT_SM_BUDGET,
-    OPT_SKINNY, OPT_HALO_DEEP,
+    OPT_SKINNY, OPT_HALO_DEEP, OPT_HALO_SPLITB,
     OPT_COUNT
 };
 struct OptDef { const char* name; int dflt; };
@@ -66,7 +66,7 @@ static const OptDef kOptDefs[OPT_COUNT] = {
     {"HALO_ROW", 1}, {"HALO_JH", 0}, {"HALO_JW", 0}, {"HALO_STACK", 1}, {"HALO_WIDE", -1}, {"HALO_PAIR", -1}, {"HALO_FLAT", 1},
     {"HALO_NARROW", 1}, {"HALO_DUAL", 1}, {"PATCH_MATRIX", 1}, {"DX_PHASES", 1}, {"DX_COL2IM", 1}, {"DX_TRANSPOSE", 1},
     {"DW_STACKED", -1}, {"DW_DIAG", 1}, {"DW_CW", 0}, {"DW_R", 0}, {"DW_STATIC", 1}, {"CONV_PROF", 0}, {"SM_BUDGET", 0},
-    {"SKINNY", 1}, {"HALO_DEEP", 1},
+    {"SKINNY", 1}, {"HALO_DEEP", 1}, {"HALO_SPLITB", 0},
 };
 static std::atomic<int> g_opt[OPT_COUNT];
 static std::once_flag g_opt_once;
@@ -1011,7 +1011,14 @@ static int launch_halo(DeviceCtx* c, const IgemmPlan& pl_in, int mode3x, cudaStr
     // 3xTF32: split W into hi/lo planes once per call (scratch of this stream), load both by TMA
     const float* w_hi = pl.W;
     const float* w_lo = pl.W_lo ? pl.W_lo : pl.W;
-    if (mode3x && !pl.W_lo) {
+    // Option HALO_SPLITB (off by default): a 1x1 product loads only W itself and its split warps form the lo
+    // plane of each W tile in shared memory, which halves the W traffic out of L2 and drops the pass over W.
+    // Measured: no gain on the L2-bound tiny-image layers (3.84 against 3.82 ms for the ResNet-18 stack) and a
+    // loss on large products (8192^3 C = A * B^T: 187 against 212 TFLOP/s), where the extra shared-memory
+    // traffic of the split competes with the operand reads of the MMAs.
+    p.split_b = (mode3x && !pl.W_lo && !pl.b_mn && pl.FH * pl.FW == 1 && opt(OPT_HALO_SPLITB) &&
+                 !(t_prepared_lo.W == pl.W && t_prepared_lo.lo)) ? 1 : 0;
+    if (mode3x && !pl.W_lo && !p.split_b) {
         rc = forward_lo_plane(c, stream, pl.W, (size_t)pl.wOC * pl.FH * pl.FW * pl.wIC, &w_lo);
         if (rc) return rc;
     }
@@ -1307,9 +1314,11 @@ static void dw_halo_set_attr()
 }
 
 // Returns 1 when the shape is left to the split-K im2col kernel, 0 on launch, < 0 on error.
+// deltaB != nullptr: the kernel also sums the columns of deltaY (bias gradient); *bias_fused tells whether it did.
 static int launch_dw_halo(DeviceCtx* c, const AlphaConvShape* s_in, const float* X, const float* dY, float* dW,
-                          int mode3x, cudaStream_t stream)
+                          int mode3x, cudaStream_t stream, float* deltaB = nullptr, bool* bias_fused = nullptr)
 {
+    if (bias_fused) *bias_fused = false;
     if (opt(OPT_CONV_DW) == 1) return 1;
     AlphaConvShape flat = *s_in;
     const AlphaConvShape* s = s_in;
@@ -1411,6 +1420,14 @@ static int launch_dw_halo(DeviceCtx* c, const AlphaConvShape* s_in, const float*
     }
     p.part_stride = sizeW;
     const size_t smem = (size_t)stages * stage_bytes(R) + (3 * stages + 2) * 8 + 1024;
+    // fused bias gradient: per-CTA partial column sums, added in CTA order afterwards.  The cross-thread
+    // sum borrows 16 KB of the operand ring.
+    float* bias_parts = nullptr;
+    if (deltaB && (size_t)stages * stage_bytes(R) >= 16384 && s->OC % 4 == 0) {
+        int rc = get_workspace(c, stream, (size_t)parts * s->OC * sizeof(float), &bias_parts);
+        if (rc) return rc;
+        p.bias_out = bias_parts;
+    }
 
     CUtensorMap tmX, tmDY;
     cuuint64_t xd[4] = {(cuuint64_t)s->IC, (cuuint64_t)s->IW, (cuuint64_t)s->IH, (cuuint64_t)s->N};
@@ -1458,6 +1475,15 @@ static int launch_dw_halo(DeviceCtx* c, const AlphaConvShape* s_in, const float*
         if (!t_dry) dw_reduce_kernel<<<(unsigned)((n4 + 63) / 64), 64, 0, stream>>>(ws, sizeW, parts * nsub, dW, n4, 0);
         note_launch("dw_halo");
         rc = check_launch("dw_reduce_kernel");
+    }
+    if (!rc && bias_parts) {
+        // the `parts` partial rows are a matrix whose columns want summing: 4 float4 columns x 64 row lanes per CTA
+        const int cols4 = s->OC / 4, CT2 = cols4 < 4 ? cols4 : 4;
+        if (!t_dry) field_sum_partial_kernel<<<dim3(1, (unsigned)((cols4 + CT2 - 1) / CT2)), kFieldSumThreads, 0, stream>>>(
+            reinterpret_cast<const float4*>(bias_parts), parts, cols4, CT2, 64, reinterpret_cast<float4*>(deltaB));
+        note_launch("dw_halo");
+        rc = check_launch("field_sum_partial_kernel");
+        if (bias_fused) *bias_fused = true;
     }
     return rc;
 }
@@ -2115,6 +2141,34 @@ int alpha_conv_workspace_bytes(const AlphaConvShape* s, int op, size_t* bytes)
     t_dry = false;
     *bytes = t_dry_peak;
     return rc;
+}
+
+int alpha_conv3d_deltaW_bias(const AlphaConvShape* s, const float* X, const float* deltaY, float* deltaW, float* deltaB,
+                             alpha_stream_t stream_)
+{
+    if (!deltaB) return alpha_conv3d_deltaW(s, X, deltaY, deltaW, stream_);
+    int rc = check_shape(s, X, deltaY, deltaW);
+    if (rc) return rc;
+    if ((uintptr_t)deltaB & 15) return fail(ALPHA_E_ARG, "deltaW_bias: deltaB must be 16-byte aligned");
+    DeviceCtx* c;
+    rc = get_ctx(&c);
+    if (rc) return rc;
+    cudaStream_t stream = (cudaStream_t)stream_;
+    // the halo-tile kernel (stride 1, IC % 32 == 0, images larger than 3 x 3) sums the columns of the deltaY
+    // tiles it stages anyway; every other shape runs the two passes one after the other
+    const bool tensor_ok = (s->IC % 32 == 0) && s->ph < 128 && s->pw < 128 && s->FH <= 256 && s->FW <= 256;
+    const bool patch = patch_path_ok(s) && env_tile_mode() != 1 && (!tensor_ok || (s->OH * s->OW <= 9 && (s->FH > 1 || s->FW > 1)));
+    if (cur_algo() != ALPHA_ALGO_SIMT && tensor_ok && !patch) {
+        ws_begin(c, stream);
+        bool fused = false;
+        rc = launch_dw_halo(c, s, X, deltaY, deltaW, cur_mode3x(), stream, deltaB, &fused);
+        if (rc < 0) return rc;
+        if (rc == 0 && fused) return ALPHA_OK;
+        if (rc == 0) return alpha_conv_bias_grad(deltaY, (long long)s->N * s->OH * s->OW, s->OC, deltaB, stream_);
+    }
+    rc = alpha_conv3d_deltaW(s, X, deltaY, deltaW, stream_);
+    if (rc) return rc;
+    return alpha_conv_bias_grad(deltaY, (long long)s->N * s->OH * s->OW, s->OC, deltaB, stream_);
 }
 
 size_t alpha_conv3d_deltaW_noalloc_capacity(void) { return kNoAllocScratchBytes; }

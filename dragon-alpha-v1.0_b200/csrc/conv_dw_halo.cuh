@@ -26,6 +26,13 @@
 // diagonal quadrants dY_a*X_a and dY_b*X_b are the two partials and the off-diagonal ones are
 // ignored - twice the pixels per MMA where the 128-row operand would be half empty.
 //
+// Bias gradient (p.bias_out): deltaB[oc] = sum over pixels of deltaY[pix][oc] needs exactly the tiles the
+// groups with fh == 0 and ict == 0 already stage.  Their split threads add up the fp32 words of every
+// deltaY tile (thread t always meets the same four channels of a 32-channel block: its 16-byte chunk of the
+// 128-byte pixel row and, with the 32-byte-atom swizzle, the row index modulo 4 do not change while it
+// strides over 32 rows at a time), and after the loop the 32 threads of each channel quad are added in
+// thread order.  Pixels outside the image and channels beyond OC arrive as zeros from the TMA.
+//
 // Warps: 0 TMA producer, 1 MMA issuer, 2-9 operand split (3xTF32) during the loop, 2-5 epilogue after.
 #pragma once
 #include "conv_halo.cuh"
@@ -54,6 +61,10 @@ struct DwHaloParams {
     uint32_t idesc, tmem_cols;
     uint32_t dy_blk, x_blk;   // bytes of one 32-channel block of the deltaY / X tile (multiples of 1024)
     uint32_t dy_tx, x_tx;     // bytes one block load delivers
+    // Bias gradient fused into the pass over deltaY: when set, the CTAs of the accumulator groups with
+    // fh == 0 and ict == 0 (one group per output-channel tile) also sum the columns of the deltaY tiles
+    // they stage; CTA x of such a group writes its partial sums to bias_out[x * OC + oc].
+    float* bias_out;
 };
 
 // The MMAs of one staged pixel tile as straight-line code: all steps of one tap back to back.
@@ -212,7 +223,9 @@ __global__ void __launch_bounds__(kDwHaloThreads, 1)
             // ---- MMA issuer ----
             RingPos rp;
             const uint32_t dhi = smem_desc_hi(512, kSwizzle128B_Base32B);
-            const uint32_t wait_a = (p.mode3x == 1 || p.mode3x == 2) ? ready_a : full_a;
+            // a CTA that sums bias columns releases a stage only after its split threads have read it
+            const bool do_bias = p.bias_out != nullptr && fh == 0 && ict == 0;
+            const uint32_t wait_a = (p.mode3x == 1 || p.mode3x == 2 || do_bias) ? ready_a : full_a;
             const bool three = p.mode3x == 1;
             const uint32_t stage16 = stage_bytes >> 4, lo_off = plane_bytes >> 4;
             const uint32_t a_lo0 = smem_desc_lo(smem_a, p.dy_blk);              // LBO = block stride
@@ -251,26 +264,72 @@ __global__ void __launch_bounds__(kDwHaloThreads, 1)
         // ---- operand split while the loop runs (3xTF32): warps 2..9; epilogue afterwards: warps 2..5 ----
         const int tid128 = threadIdx.x - 64;   // index among the split threads
         bool ok = true;
-        if (p.mode3x == 1 || p.mode3x == 2) {
+        const bool split_on = p.mode3x == 1 || p.mode3x == 2;
+        const bool do_bias = p.bias_out != nullptr && fh == 0 && ict == 0;
+        float4 bsum[4] = {make_float4(0.f, 0.f, 0.f, 0.f), make_float4(0.f, 0.f, 0.f, 0.f), make_float4(0.f, 0.f, 0.f, 0.f),
+                          make_float4(0.f, 0.f, 0.f, 0.f)};
+        if (split_on || do_bias) {
             RingPos rp;
             unsigned long long w_full = 0;
             const long long t_begin = clock64();
+            const int halves = diag ? 2 : 1;
             for (int t = blockIdx.x; t < p.total_tiles; t += gridDim.x) {
                 if (!wait_prof(full_a + 8 * rp.idx, rp.phase, prof_on, w_full)) { report(p.status, kStatusSplitTimeout); ok = false; break; }
                 uint8_t* hi = smem + static_cast<size_t>(rp.idx) * stage_bytes;
-                if (stacked) {
-                    split_plane_lo_x4(hi, hi + dy_bytes, dy_bytes, tid128, kDwSplitThreads);
-                    split_plane_lo_x4(hi + x_off, hi + x_off + x_bytes, x_bytes, tid128, kDwSplitThreads);
-                } else {
-                    split_plane_lo_x4(hi, hi + plane_bytes, plane_bytes, tid128, kDwSplitThreads);
+                if (do_bias) {
+                    // the staged fp32 words of deltaY (the split below leaves them as they are)
+                    for (int h = 0; h < halves; ++h)
+#pragma unroll
+                        for (int b = 0; b < 4; ++b) {
+                            if (b >= dyb) break;
+                            const uint8_t* blk = hi + h * dy_bytes + b * p.dy_blk;
+                            for (uint32_t off = static_cast<uint32_t>(tid128) * 16u; off < p.dy_tx; off += kDwSplitThreads * 16u) {
+                                const float4 v = *reinterpret_cast<const float4*>(blk + off);
+                                bsum[b].x += v.x; bsum[b].y += v.y; bsum[b].z += v.z; bsum[b].w += v.w;
+                            }
+                        }
                 }
-                fence_proxy_async_smem();
+                if (split_on) {
+                    if (stacked) {
+                        split_plane_lo_x4(hi, hi + dy_bytes, dy_bytes, tid128, kDwSplitThreads);
+                        split_plane_lo_x4(hi + x_off, hi + x_off + x_bytes, x_bytes, tid128, kDwSplitThreads);
+                    } else {
+                        split_plane_lo_x4(hi, hi + plane_bytes, plane_bytes, tid128, kDwSplitThreads);
+                    }
+                    fence_proxy_async_smem();
+                }
                 mbar_arrive_a(ready_a + 8 * rp.idx);
                 rp.advance(S);
             }
             if (prof_on && tid128 == 0) {
                 p.prof[kProfSplitWait] = w_full;
                 p.prof[kProfSplitWork] = static_cast<unsigned long long>(clock64() - t_begin) - w_full;
+            }
+        }
+        if (do_bias) {
+            // all MMAs have finished reading shared memory once `accum` completes; the ring then serves as
+            // scratch for the cross-thread sum.  Every split thread takes part in the barrier, also one
+            // whose wait ran out (the CTA then reports through the status word and its sums are void).
+            const bool done = ok && mbar_wait(accum, 0);
+            if (ok && !done) { report(p.status, kStatusEpilogueTimeout); ok = false; }
+            float4* sc = reinterpret_cast<float4*>(smem);
+#pragma unroll
+            for (int b = 0; b < 4; ++b) sc[b * kDwSplitThreads + tid128] = bsum[b];
+            named_barrier_sync(2, kDwSplitThreads);
+            if (tid128 < dyb * 8) {
+                const int b = tid128 >> 3, q = tid128 & 7;
+                float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int t = 0; t < kDwSplitThreads; ++t) {
+                    // thread t reads 16-byte chunk (t & 7) of rows whose index modulo 4 is (t >> 3) & 3; the swizzle
+                    // exchanges the 32-byte atoms of a row by that row index
+                    const int quad = ((((t & 7) >> 1) ^ ((t >> 3) & 3)) << 1) | (t & 1);
+                    if (quad == q) {
+                        const float4 v = sc[b * kDwSplitThreads + t];
+                        a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
+                    }
+                }
+                const int oc = oc0 + b * 32 + q * 4;
+                if (oc < p.OC) *reinterpret_cast<float4*>(p.bias_out + static_cast<size_t>(blockIdx.x) * p.OC + oc) = a;
             }
         }
         if (warp >= 6) ok = false;   // the extra split warps take no part in the epilogue

@@ -71,6 +71,8 @@ struct HaloParams {
     int acc_bufs;        // 1 or 2 accumulator sets
     int mode3x, b_mn, flip;   // mode3x: 0 plain TF32, 1 three MMAs, 2 wide B
     int dual;                 // 1: two MMA-issuing threads take alternate W-tile stages (sb is even)
+    int split_b;              // 3xTF32: 1 = only the hi plane of every W tile is loaded and the split warps form its lo
+                              // plane in shared memory (1x1 products, whose W traffic from L2 is what binds them)
     int ksplit, cps;          // split-K: every tile is computed as ksplit partial sums over cps reduction chunks each;
                               // partial sp of image n is stored as image sp * N + n of the output map
     uint32_t idesc, idesc_wide, tmem_cols;   // idesc_wide: N = 2 * BN
@@ -300,13 +302,13 @@ __global__ void __launch_bounds__(kHaloThreads2, 1)
                     for (int st = 0; st < stages_per_chunk; ++st) {
                         if (!wait_prof(bempty_a + 8 * bp.idx, bp.phase ^ 1, prof_on, w_b)) { report(p.status, kStatusProducerTimeout); ok = false; break; }
                         const uint32_t bar = bfull_a + 8 * bp.idx;
-                        mbar_arrive_expect_tx_a(bar, p.b_tx * tps * planes);
+                        mbar_arrive_expect_tx_a(bar, p.b_tx * tps * (p.split_b ? 1u : planes));
                         for (int q = 0; q < tps; ++q) {
                             const int tap = st * tps + q;
                             const uint32_t b_dst = bring_a + bp.idx * b_stride + q * b_tile;
                             if (!p.b_mn) {
                                 tma_load_3d_a(b_dst, &tmB, bar, c * 32, tap, oc0);
-                                if (p.mode3x) tma_load_3d_a(b_dst + p.b_bytes, &tmBlo, bar, c * 32, tap, oc0);
+                                if (p.mode3x && !p.split_b) tma_load_3d_a(b_dst + p.b_bytes, &tmBlo, bar, c * 32, tap, oc0);
                             } else {
                                 const int tapw = p.flip ? (taps - 1 - tap) : tap;
                                 for (int j = 0; j < p.BN / 32; ++j) {
@@ -344,7 +346,8 @@ __global__ void __launch_bounds__(kHaloThreads2, 1)
             const uint32_t jh_step = 16u * row_step;          // 16 patch rows down
             const uint32_t patch_lo0 = smem_desc_lo(patches_a, 16), patch_stride16 = patch_stride >> 4;
             const uint32_t bring_lo0 = smem_desc_lo(bring_a, p.b_mn ? 4096u : 16u), b_stride16 = b_stride >> 4;
-            const uint32_t pwait_a = p.mode3x ? pready_a : pfull_a, bwait_a = bfull_a;  // weights arrive pre-split
+            // weights arrive pre-split unless the split warps form the lo plane of the W tiles (split_b)
+            const uint32_t pwait_a = p.mode3x ? pready_a : pfull_a, bwait_a = p.split_b ? smem_u32(b_ready) : bfull_a;
             const uint32_t accw = p.mode3x == 2 ? 2u * p.BN : p.BN;   // columns of one accumulator
             const uint32_t acc_cols = J * accw;
             const IssueConsts k{a_dhi, b_dhi, b_kstep, a_lo_off, b_lo_off, p.idesc, p.idesc_wide, accw};
@@ -537,7 +540,7 @@ __global__ void __launch_bounds__(kHaloThreads2, 1)
         // ---- operand split (3xTF32 only): warps 6..9 ----
         if (p.mode3x) {
             const int tid128 = threadIdx.x - 192;
-            RingPos pp;
+            RingPos pp, bpos;
             bool ok = true;
             unsigned long long w_in = 0;
             const long long t_begin = clock64();
@@ -550,6 +553,17 @@ __global__ void __launch_bounds__(kHaloThreads2, 1)
                     fence_proxy_async_smem();
                     mbar_arrive_a(pready_a + 8 * pp.idx);
                     pp.advance(p.npb);
+                    if (p.split_b) {
+                        // the W-tile stages of this chunk, in the producer's order
+                        for (int st = 0; st < stages_per_chunk && ok; ++st) {
+                            if (!mbar_wait_a(bfull_a + 8 * bpos.idx, bpos.phase)) { report(p.status, kStatusSplitTimeout); ok = false; break; }
+                            uint8_t* bt = bring + static_cast<size_t>(bpos.idx) * b_stride;
+                            for (int q = 0; q < tps; ++q) split_plane_lo_x4(bt + q * b_tile, bt + q * b_tile + p.b_bytes, p.b_tx, tid128, 128);
+                            fence_proxy_async_smem();
+                            mbar_arrive_a(smem_u32(b_ready) + 8 * bpos.idx);
+                            bpos.advance(p.sb);
+                        }
+                    }
                 }
             }
             if (prof_on && threadIdx.x == 192) {

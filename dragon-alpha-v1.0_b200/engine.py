@@ -307,6 +307,21 @@ class Engine:
         self.base.dconv3D_deltaW(dW, FH, FW, Xp, IH, IW, dYp, OH, OW, N, ic4, oc4, sh, sw, ph, pw)
         return dW if (ic4 == IC and oc4 == OC) else dW[:OC, :, :, :IC]
 
+    def dconv3D_deltaW_bias(self, X, deltaY, FH, FW, sh, sw, ph, pw):
+        """(deltaW, deltaB) of a biased Conv3D unit in one call: dconv3D_deltaW and field_sum(deltaY, OC) of
+        Conv3D.__backward__ (nn/unit/simple/Conv3D.java:150-160); stride-1 layers sum the bias columns inside
+        the deltaW kernel's pass over deltaY."""
+        N, IH, IW, IC = X.shape
+        _, OH, OW, OC = deltaY.shape
+        ic4, oc4 = _pad4(IC), _pad4(OC)
+        Xp, dYp = _pad_last(X, ic4), _pad_last(deltaY, oc4)
+        dW = torch.empty((oc4, FH, FW, ic4), dtype=torch.float32, device=X.device)
+        dB = torch.empty((oc4,), dtype=torch.float32, device=X.device)
+        shape = _l.AlphaConvShape(N, IH, IW, ic4, oc4, FH, FW, OH, OW, sh, sw, ph, pw)
+        a = self.base._addr
+        _l.check(self.base._lib.alpha_conv3d_deltaW_bias(C.byref(shape), a(Xp), a(dYp), a(dW), a(dB), _stream(self.base._stream)))
+        return (dW if (ic4 == IC and oc4 == OC) else dW[:OC, :, :, :IC]), (dB if oc4 == OC else dB[:OC])
+
     def dconv3D_deltaX(self, deltaY, W, IH, IW, sh, sw, ph, pw):
         N, OH, OW, OC = deltaY.shape
         _, FH, FW, IC = W.shape

@@ -43,6 +43,7 @@ def load():
     lib.alpha_conv3d_forward_leakyRelu.argtypes = [P, V, V, V, C.c_float, V, V]
     lib.alpha_conv3d_deltaW.argtypes = [P, V, V, V, V]
     lib.alpha_conv_bias_grad.argtypes = [V, C.c_longlong, I, V, V]
+    lib.alpha_conv3d_deltaW_bias.argtypes = [P, V, V, V, V, V]
     lib.alpha_conv3d_forward_ex.argtypes = [P, V, V, V, V, I, I, V]
     lib.alpha_conv3d_deltaX_ex.argtypes = [P, V, V, V, I, I, V]
     lib.alpha_conv3d_deltaW_ex.argtypes = [P, V, V, V, I, I, V]

@@ -179,6 +179,14 @@ int alpha_conv3d_deltaW(const AlphaConvShape* s, const float* X, const float* de
  * rows; the result is the same bits on every run. */
 int alpha_conv_bias_grad(const float* deltaY, long long rows, int OC, float* deltaB, alpha_stream_t stream);
 
+/* deltaW and the bias gradient deltaB[oc] = sum over pixels of deltaY in one call: what Conv3D.__backward__
+ * asks of the engine as dconv3D_deltaW followed by field_sum(deltaY, OC) (nn/unit/simple/Conv3D.java:150-160).
+ * For stride-1 layers the deltaW kernel adds up the columns of the deltaY tiles it stages anyway (no second
+ * pass over deltaY); other shapes run alpha_conv3d_deltaW and alpha_conv_bias_grad one after the other.
+ * deltaB == NULL is alpha_conv3d_deltaW.  Results do not depend on scheduling (fixed summation orders). */
+int alpha_conv3d_deltaW_bias(const AlphaConvShape* s, const float* X, const float* deltaY, float* deltaW,
+                             float* deltaB, alpha_stream_t stream);
+
 /* deltaW for callers that cannot allocate device memory when they call.
  * (No counterpart in the reference: its natives get every buffer, scratch included, from the Java
  * mempool.)  A host such as Dragon-Alpha's engine claims the card's memory for its own pool up front
@@ -345,7 +353,7 @@ int alpha_engine_dconv3D_deltaX(float* deltaX, int IH, int IW, const float* delt
                                 const float* W, int FH, int FW, int N, int IC, int OC, int sh,
                                 int sw, int ph, int pw, alpha_stream_t stream);
 
-/* ---- matrix products (the FullConnect path; SURVEY's next contraction after the convolutions) ----------
+/* ---- matrix products (the FullConnect path: the contraction next to the convolutions) ------------------
  *
  * Row-major fp32 matrices whose dimensions arrive padded to multiples of 4 like every tensor of the
  * engine.  A matrix product is a 1x1 convolution over rows, so each form runs on the kernels of the

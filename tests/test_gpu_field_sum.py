@@ -94,3 +94,46 @@ def test_bias_grad_of_a_biased_layer(pkg, eng, oracle_mod):
     scale = float(Y.double().norm() * dY.double().norm())
     assert abs(lhs - (dot(X, dX) + dot(B, dB))) <= 1e-5 * scale
     assert abs(lhs - (dot(W, dW) + dot(B, dB))) <= 1e-5 * scale
+
+
+# (N, IH, IW, IC, OC, F, stride, pad): shapes of every form of the deltaW halo kernel, and some it does not take
+FUSED_CASES = [
+    (16, 28, 28, 128, 128, 3, 1, 1),    # three MMAs per step (3xTF32) / plain
+    (8, 56, 56, 64, 64, 3, 1, 1),       # stacked planes (3xTF32) / diagonal half tiles (TF32)
+    (8, 14, 14, 256, 256, 3, 1, 1),     # two output-channel tiles
+    (4, 12, 12, 32, 96, 3, 1, 1),       # output channels do not fill the 128-channel tile
+    (4, 9, 7, 32, 36, 5, 1, 2),         # ragged image, 5x5, OC = 36
+    (16, 7, 7, 64, 72, 1, 1, 0),        # 1x1 (flat pixel view)
+    (8, 16, 16, 32, 64, 3, 2, 1),       # stride 2: not fused, two passes
+    (8, 32, 32, 4, 64, 7, 2, 3),        # IC = 4 stem: patch-matrix path, two passes
+    (32, 2, 2, 64, 64, 3, 1, 1),        # tiny images: patch-matrix path
+]
+
+
+@pytest.mark.parametrize("mode", ["3xtf32", "tf32"])
+@pytest.mark.parametrize("case", FUSED_CASES)
+def test_bias_gradient_inside_the_deltaW_pass(pkg, eng, oracle_mod, case, mode):
+    """alpha_conv3d_deltaW_bias: deltaW equals alpha_conv3d_deltaW's bit for bit (the bias columns are summed
+    beside the MMAs, not in them), deltaB agrees with the double-precision column sums and with the
+    stand-alone bias-gradient kernel to fp32 summation order, and repeats are bit-identical."""
+    import torch
+    lib = pkg.submodule("lib")
+    lib.set_math_mode(mode)
+    N, IH, IW, IC, OC, F, s, p = case
+    OH, OW = (IH + 2 * p - F) // s + 1, (IW + 2 * p - F) // s + 1
+    gen = torch.Generator(device="cuda:0").manual_seed(sum(case))
+    X = torch.randn((N, IH, IW, IC), device="cuda:0", generator=gen)
+    dY = torch.randn((N, OH, OW, OC), device="cuda:0", generator=gen)
+    try:
+        dW_ref = eng.dconv3D_deltaW(X, dY, F, F, s, s, p, p)
+        dB_ref = eng.field_sum(dY, OC)
+        dW, dB = eng.dconv3D_deltaW_bias(X, dY, F, F, s, s, p, p)
+        dW2, dB2 = eng.dconv3D_deltaW_bias(X, dY, F, F, s, s, p, p)
+        assert lib.device_status() == 0
+    finally:
+        lib.set_math_mode("3xtf32")
+    assert torch.equal(dW, dW_ref) and torch.equal(dW, dW2) and torch.equal(dB, dB2)
+    ref, mag = oracle_mod.field_sum_f64(dY.cpu().numpy(), OC)
+    got = dB.cpu().numpy()
+    assert np.all(np.abs(got - ref) <= REL * mag + 1e-30), float(np.max(np.abs(got - ref) / (mag + 1e-30)))
+    assert np.all(np.abs(got - dB_ref.cpu().numpy()) <= 2 * REL * mag + 1e-30)

@@ -217,6 +217,32 @@ def test_split_reduction_for_skinny_layers(pkg, eng, oracle_mod, name, mode):
     assert lib.device_status() == 0
 
 
+def test_lo_plane_of_w_formed_in_the_kernel_equals_the_presplit_plane(pkg, eng):
+    """Option HALO_SPLITB: a 1x1 product in 3xTF32 loads only W and lets the split warps form the lo plane of
+    every W tile in shared memory; by default the lo plane comes from a separate pass over W.  Same arithmetic,
+    same bits."""
+    import torch
+    lib = pkg.submodule("lib")
+    lib.set_math_mode("3xtf32")
+    dev = torch.device("cuda:0")
+    g = torch.Generator(device=dev).manual_seed(31)
+    for (N, HW, IC, OC, F, p_) in ((8, 14, 256, 192, 1, 0), (64, 2, 128, 256, 3, 1), (4, 32, 4, 64, 7, 3)):
+        s_ = 2 if F == 7 else 1
+        X = torch.randn((N, HW, HW, IC), device=dev, generator=g)
+        W = torch.randn((OC, F, F, IC), device=dev, generator=g) * 0.1
+        b = eng.conv3D(X, W, s_, s_, p_, p_)
+        n0 = lib.launch_count(); eng.conv3D(X, W, s_, s_, p_, p_); presplit = lib.launch_count() - n0
+        old = lib.set_option("HALO_SPLITB", 1)
+        try:
+            a = eng.conv3D(X, W, s_, s_, p_, p_)
+            n0 = lib.launch_count(); eng.conv3D(X, W, s_, s_, p_, p_); fused = lib.launch_count() - n0
+        finally:
+            lib.set_option("HALO_SPLITB", old)
+        assert torch.equal(a, b), (N, HW, IC, OC, F)
+        assert fused == presplit - 1          # the pass over W is gone
+    assert lib.device_status() == 0
+
+
 EDGE_CASES = {
     "one_pixel_image": (4, 1, 1, 32, 32, 3, 3, 1, 1, 1, 1),
     "single_image_tiny": (1, 3, 3, 8, 4, 3, 3, 1, 1, 1, 1),
