@@ -7,6 +7,8 @@
 #include "winograd.cuh"
 #include "host_common.h"
 
+#include <nvtx3/nvToolsExt.h>   // header-only: resolves a profiler's injection library at run time, no link dependency
+
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
@@ -57,7 +59,7 @@ enum Opt {
     OPT_HALO_ROW, OPT_HALO_JH, OPT_HALO_JW, OPT_HALO_STACK, OPT_HALO_WIDE, OPT_HALO_PAIR, OPT_HALO_FLAT,
     OPT_HALO_NARROW, OPT_HALO_DUAL, OPT_PATCH_MATRIX, OPT_DX_PHASES, OPT_DX_COL2IM, OPT_DX_TRANSPOSE,
     OPT_DW_STACKED, OPT_DW_DIAG, OPT_DW_CW, OPT_DW_R, OPT_DW_STATIC, OPT_CONV_PROF, OPT_SM_BUDGET,
-    OPT_SKINNY, OPT_HALO_DEEP, OPT_HALO_SPLITB,
+    OPT_SKINNY, OPT_HALO_DEEP, OPT_HALO_SPLITB, OPT_NVTX,
     OPT_COUNT
 };
 struct OptDef { const char* name; int dflt; };
@@ -66,7 +68,7 @@ static const OptDef kOptDefs[OPT_COUNT] = {
     {"HALO_ROW", 1}, {"HALO_JH", 0}, {"HALO_JW", 0}, {"HALO_STACK", 1}, {"HALO_WIDE", -1}, {"HALO_PAIR", -1}, {"HALO_FLAT", 1},
     {"HALO_NARROW", 1}, {"HALO_DUAL", 1}, {"PATCH_MATRIX", 1}, {"DX_PHASES", 1}, {"DX_COL2IM", 1}, {"DX_TRANSPOSE", 1},
     {"DW_STACKED", -1}, {"DW_DIAG", 1}, {"DW_CW", 0}, {"DW_R", 0}, {"DW_STATIC", 1}, {"CONV_PROF", 0}, {"SM_BUDGET", 0},
-    {"SKINNY", 1}, {"HALO_DEEP", 1}, {"HALO_SPLITB", 0},
+    {"SKINNY", 1}, {"HALO_DEEP", 1}, {"HALO_SPLITB", 0}, {"NVTX", 1},
 };
 static std::atomic<int> g_opt[OPT_COUNT];
 static std::once_flag g_opt_once;
@@ -123,6 +125,14 @@ struct CallOptions {
     int save_math, save_algo;
     CallOptions(int math, int algo) : save_math(t_math), save_algo(t_algo) { if (math >= 0) t_math = math; if (algo >= 0) t_algo = algo; }
     ~CallOptions() { t_math = save_math; t_algo = save_algo; }
+};
+
+// One NVTX range per operator call (option NVTX, on by default): a timeline tool attached to the process shows
+// which contraction the kernels of a call belong to; without a tool a push / pop is a few nanoseconds.
+struct OpRange {
+    bool on;
+    explicit OpRange(const char* name) : on(opt(OPT_NVTX) != 0 && !t_dry) { if (on) nvtxRangePushA(name); }
+    ~OpRange() { if (on) nvtxRangePop(); }
 };
 
 // ---- per-device context ----------------------------------------------------------------------
@@ -1847,6 +1857,7 @@ int alpha_conv_debug_counters(unsigned long long* out, int n)
 int alpha_conv3d_forward(const AlphaConvShape* s, const float* X, const float* W, const float* bias,
                          float* Y, alpha_stream_t stream_)
 {
+    OpRange range("alpha_conv3d_forward");
     int rc = check_shape(s, X, W, Y);
     if (rc) return rc;
     if (bias && ((uintptr_t)bias & 15)) return fail(ALPHA_E_ARG, "bias must be 16-byte aligned");
@@ -1862,6 +1873,7 @@ int alpha_conv3d_forward(const AlphaConvShape* s, const float* X, const float* W
 
 int alpha_conv_bias_grad(const float* deltaY, long long rows, int OC, float* deltaB, alpha_stream_t stream_)
 {
+    OpRange range("alpha_conv_bias_grad");
     if (!deltaY || !deltaB || rows <= 0 || OC <= 0) return fail(ALPHA_E_ARG, "bias_grad: null pointer or empty matrix");
     if (OC % 4 != 0) return fail(ALPHA_E_ARG, "bias_grad: OC must be a multiple of 4 (the engine pads channels to 4)");
     if (((uintptr_t)deltaY & 15) || ((uintptr_t)deltaB & 15)) return fail(ALPHA_E_ARG, "bias_grad: pointers must be 16-byte aligned");
@@ -1958,6 +1970,7 @@ extern "C" {
 int alpha_conv3d_deltaX(const AlphaConvShape* s, const float* deltaY, const float* W, float* deltaX,
                         alpha_stream_t stream_)
 {
+    OpRange range("alpha_conv3d_deltaX");
     int rc = check_shape(s, deltaY, W, deltaX);
     if (rc) return rc;
     DeviceCtx* c;
@@ -2030,6 +2043,7 @@ int alpha_conv3d_deltaX(const AlphaConvShape* s, const float* deltaY, const floa
 int alpha_conv3d_deltaW(const AlphaConvShape* s, const float* X, const float* deltaY, float* deltaW,
                         alpha_stream_t stream_)
 {
+    OpRange range("alpha_conv3d_deltaW");
     int rc = check_shape(s, X, deltaY, deltaW);
     if (rc) return rc;
     DeviceCtx* c;
