@@ -167,6 +167,9 @@ struct DeviceCtx {
     };
     struct WeightEntry { float* ptr = nullptr; size_t bytes = 0; bool valid = false; cudaEvent_t ready = nullptr; cudaStream_t stream = nullptr; };
     std::map<WeightKey, WeightEntry> weights;
+    // What each caller-owned block of prepared weights (alpha_conv_prepare_weights) holds: host-side record only.
+    struct PreparedDesc { WeightKey key; size_t bytes; };
+    std::map<const void*, PreparedDesc> prepared;
 };
 static DeviceCtx g_ctx[64];
 static std::mutex g_mu;
@@ -381,9 +384,35 @@ void set_prepared_lo(const float* W, const float* lo) { t_prepared_lo.W = W; t_p
 
 // Memory for one transform of `bytes`; *fresh says whether the caller still has to compute it (then
 // it calls weight_planes_ready after enqueuing the kernels that do).
+// Caller-owned prepared weights (alpha_conv_prepare_weights / *_prepared): for the duration of one call the
+// transform of tensor W lives in the caller's block.  mode 1 = compute it there (the call runs "dry": only
+// the transform is launched), 2 = it is there already, 3 = only report its size.
+struct PreparedHint { const float* W = nullptr; float* ptr = nullptr; size_t bytes = 0; int mode = 0; size_t need = 0; bool seen = false; };
+static thread_local PreparedHint t_prep;
+static inline bool transforms_run() { return !t_dry || t_prep.mode == 1; }
+
 static int weight_planes(DeviceCtx* c, cudaStream_t stream, const DeviceCtx::WeightKey& key, size_t bytes, float** out, bool* fresh)
 {
     *fresh = true;
+    if (t_prep.mode && t_prep.W == key.W) {
+        t_prep.need = bytes; t_prep.seen = true;
+        if (t_prep.mode == 3) { *out = reinterpret_cast<float*>(static_cast<uintptr_t>(1) << 30); return ALPHA_OK; }
+        if (bytes > t_prep.bytes)
+            return fail(ALPHA_E_NOSCRATCH, "the prepared-weights block holds %zu bytes, this layer's transform needs %zu "
+                        "(alpha_conv_prepared_weights_bytes tells in advance)", t_prep.bytes, bytes);
+        std::lock_guard<std::mutex> lock(g_mu);
+        if (t_prep.mode == 1) {
+            c->prepared[t_prep.ptr] = DeviceCtx::PreparedDesc{key, bytes};
+        } else {
+            auto it = c->prepared.find(t_prep.ptr);
+            if (it == c->prepared.end() || it->second.key < key || key < it->second.key)
+                return fail(ALPHA_E_ARG, "the prepared-weights block was not made by alpha_conv_prepare_weights for this tensor, "
+                            "shape, operator and math mode");
+            *fresh = false;
+        }
+        *out = t_prep.ptr;
+        return ALPHA_OK;
+    }
     if (t_dry || !g_weight_cache.load(std::memory_order_relaxed)) return get_workspace(c, stream, bytes, out);
     std::lock_guard<std::mutex> lock(g_mu);
     DeviceCtx::WeightEntry& e = c->weights[key];
@@ -435,7 +464,7 @@ static int forward_lo_plane(DeviceCtx* c, cudaStream_t stream, const float* W, s
         const size_t n4 = nW / 4;
         size_t blocks = (n4 + 255) / 256;
         if (blocks > (size_t)c->sm_count * 8) blocks = (size_t)c->sm_count * 8;
-        if (!t_dry) split_lo_kernel<<<(unsigned)blocks, 256, 0, stream>>>(reinterpret_cast<const float4*>(W), reinterpret_cast<float4*>(ws), n4);
+        if (transforms_run()) split_lo_kernel<<<(unsigned)blocks, 256, 0, stream>>>(reinterpret_cast<const float4*>(W), reinterpret_cast<float4*>(ws), n4);
         note_launch("split_w");
         rc = check_launch("split_lo_kernel");
         if (rc) return rc;
@@ -1202,7 +1231,7 @@ static int launch_dx_phases(DeviceCtx* c, const AlphaConvShape* s, const float* 
             woff += pn;
             if (fresh) {
                 dim3 tg((s->IC + 31) / 32, (s->OC + 31) / 32, ptaps);
-                if (!t_dry) transpose_weights_kernel<<<tg, 256, 0, stream>>>(W, whi, wlo, s->OC, s->IC, taps, map, mode3x);
+                if (transforms_run()) transpose_weights_kernel<<<tg, 256, 0, stream>>>(W, whi, wlo, s->OC, s->IC, taps, map, mode3x);
                 note_launch("transpose_w");
                 rc = check_launch("transpose_weights_kernel");
                 if (rc) return rc;
@@ -1287,7 +1316,7 @@ static int launch_dx_col2im(DeviceCtx* c, const AlphaConvShape* s, const float* 
         map.n = taps;
         for (int t = 0; t < taps; ++t) map.src[t] = t;
         dim3 tg((s->IC + 31) / 32, (s->OC + 31) / 32, taps);
-        if (!t_dry) transpose_weights_kernel<<<tg, 256, 0, stream>>>(W, ws, mode3x ? ws + nW : nullptr, s->OC, s->IC, taps, map, mode3x, tap_major);
+        if (transforms_run()) transpose_weights_kernel<<<tg, 256, 0, stream>>>(W, ws, mode3x ? ws + nW : nullptr, s->OC, s->IC, taps, map, mode3x, tap_major);
         note_launch("transpose_w");
         rc = check_launch("transpose_weights_kernel");
         if (rc) return rc;
@@ -2010,7 +2039,7 @@ int alpha_conv3d_deltaX(const AlphaConvShape* s, const float* deltaY, const floa
                 TapMap map{};
                 map.n = taps;
                 for (int t = 0; t < taps; ++t) map.src[t] = taps - 1 - t;
-                if (!t_dry) transpose_weights_kernel<<<tg, 256, 0, stream>>>(W, ws, mode3x ? ws + nW : nullptr, s->OC, s->IC, taps, map, mode3x);
+                if (transforms_run()) transpose_weights_kernel<<<tg, 256, 0, stream>>>(W, ws, mode3x ? ws + nW : nullptr, s->OC, s->IC, taps, map, mode3x);
                 note_launch("transpose_w");
                 rc = check_launch("transpose_weights_kernel");
                 if (rc) return rc;
@@ -2134,6 +2163,56 @@ int alpha_conv3d_deltaW_ex(const AlphaConvShape* s, const float* X, const float*
     if (rc) return rc;
     CallOptions guard(math_mode, algo);
     return alpha_conv3d_deltaW(s, X, deltaY, deltaW, stream);
+}
+
+// Runs operator `op` on placeholder activations with launches off, so that only its weight-side transform is
+// sized (mode 3) or computed into the caller's block (mode 1).
+static int run_weight_transform(const AlphaConvShape* s, int op, const float* W, void* prepared, size_t bytes, int mode,
+                                alpha_stream_t stream, size_t* need)
+{
+    if (!s || (op != ALPHA_OP_FORWARD && op != ALPHA_OP_DELTAX)) return fail(ALPHA_E_ARG, "prepared weights exist for ALPHA_OP_FORWARD and ALPHA_OP_DELTAX");
+    float* fake = reinterpret_cast<float*>(static_cast<uintptr_t>(1) << 31);
+    const float* w = W ? W : reinterpret_cast<const float*>(static_cast<uintptr_t>(3) << 30);
+    t_prep = PreparedHint{w, static_cast<float*>(prepared), bytes, mode, 0, false};
+    t_dry = true;
+    t_dry_cur = t_dry_peak = 0;
+    const int rc = op == ALPHA_OP_FORWARD ? alpha_conv3d_forward(s, fake, w, nullptr, fake, stream)
+                                          : alpha_conv3d_deltaX(s, fake, w, fake, stream);
+    t_dry = false;
+    if (need) *need = t_prep.seen ? t_prep.need : 0;
+    t_prep = PreparedHint{};
+    return rc;
+}
+
+int alpha_conv_prepared_weights_bytes(const AlphaConvShape* s, int op, size_t* bytes)
+{
+    if (!bytes) return fail(ALPHA_E_ARG, "prepared_weights_bytes: null argument");
+    return run_weight_transform(s, op, nullptr, nullptr, 0, 3, nullptr, bytes);
+}
+
+int alpha_conv_prepare_weights(const AlphaConvShape* s, int op, const float* W, void* prepared, size_t bytes, alpha_stream_t stream)
+{
+    if (!W || ((uintptr_t)W & 15)) return fail(ALPHA_E_ARG, "prepare_weights: W is null or not 16-byte aligned");
+    if (bytes && (!prepared || ((uintptr_t)prepared & 255))) return fail(ALPHA_E_ARG, "prepare_weights: the block must be 256-byte aligned");
+    return run_weight_transform(s, op, W, prepared, bytes, 1, stream, nullptr);
+}
+
+int alpha_conv3d_forward_prepared(const AlphaConvShape* s, const float* X, const float* W, const void* prepared, size_t bytes,
+                                  const float* bias, float* Y, alpha_stream_t stream)
+{
+    t_prep = PreparedHint{W, static_cast<float*>(const_cast<void*>(prepared)), bytes, prepared ? 2 : 0, 0, false};
+    const int rc = alpha_conv3d_forward(s, X, W, bias, Y, stream);
+    t_prep = PreparedHint{};
+    return rc;
+}
+
+int alpha_conv3d_deltaX_prepared(const AlphaConvShape* s, const float* deltaY, const float* W, const void* prepared, size_t bytes,
+                                 float* deltaX, alpha_stream_t stream)
+{
+    t_prep = PreparedHint{W, static_cast<float*>(const_cast<void*>(prepared)), bytes, prepared ? 2 : 0, 0, false};
+    const int rc = alpha_conv3d_deltaX(s, deltaY, W, deltaX, stream);
+    t_prep = PreparedHint{};
+    return rc;
 }
 
 int alpha_conv_workspace_bytes(const AlphaConvShape* s, int op, size_t* bytes)

@@ -174,6 +174,43 @@ class CudaFloat32EngineBase:
                                                        pw, _stream(self._stream)))
 
 
+    # ---- weight-side transforms in caller-owned memory --------------------------------------------------
+    def prepare_weights(self, op, W_address, FH, FW, N, IH, IW, OH, OW, IC, OC, sh, sw, ph, pw, stream=None):
+        """Enqueues the transform of W that `op` ('forward' / 'deltaX') needs for this layer on `stream` and returns
+        the block (a torch uint8 tensor, or None when the operator needs none).  A training loop runs these for
+        all layers on a side stream after the optimizer step; conv3D / dconv3D_deltaX then take the block through
+        their `prepared` argument.  The caller orders prepare before use."""
+        shp = _l.AlphaConvShape(N, IH, IW, IC, OC, FH, FW, OH, OW, sh, sw, ph, pw)
+        nbytes = _l.prepared_weights_bytes(shp, op)
+        if nbytes == 0:
+            return None
+        W = W_address if isinstance(W_address, torch.Tensor) else None
+        block = torch.empty(nbytes, dtype=torch.uint8, device=W.device if W is not None else "cuda")
+        self.prepare_weights_into(block, op, W_address, FH, FW, N, IH, IW, OH, OW, IC, OC, sh, sw, ph, pw, stream)
+        return block
+
+    def prepare_weights_into(self, block, op, W_address, FH, FW, N, IH, IW, OH, OW, IC, OC, sh, sw, ph, pw, stream=None):
+        shp = _l.AlphaConvShape(N, IH, IW, IC, OC, FH, FW, OH, OW, sh, sw, ph, pw)
+        _l.check(self._lib.alpha_conv_prepare_weights(C.byref(shp), _l.OPS[op], self._addr(W_address), self._addr(block),
+                                                      block.numel(), _stream(stream if stream is not None else self._stream)))
+
+    def conv3D_prepared(self, Y_address, OH, OW, X_address, IH, IW, W_address, FH, FW, N, IC, OC, sh, sw, ph, pw, prepared):
+        a = self._addr
+        shp = _l.AlphaConvShape(N, IH, IW, IC, OC, FH, FW, OH, OW, sh, sw, ph, pw)
+        _l.check(self._lib.alpha_conv3d_forward_prepared(C.byref(shp), a(X_address), a(W_address),
+                                                         a(prepared) if prepared is not None else None,
+                                                         prepared.numel() if prepared is not None else 0, None, a(Y_address),
+                                                         _stream(self._stream)))
+
+    def dconv3D_deltaX_prepared(self, deltaX_address, IH, IW, deltaY_address, OH, OW, W_address, FH, FW, N, IC, OC, sh, sw, ph, pw,
+                                prepared):
+        a = self._addr
+        shp = _l.AlphaConvShape(N, IH, IW, IC, OC, FH, FW, OH, OW, sh, sw, ph, pw)
+        _l.check(self._lib.alpha_conv3d_deltaX_prepared(C.byref(shp), a(deltaY_address), a(W_address),
+                                                        a(prepared) if prepared is not None else None,
+                                                        prepared.numel() if prepared is not None else 0, a(deltaX_address),
+                                                        _stream(self._stream)))
+
     # ---- matrix products (CudaFloat32EngineBase.java:1129-1245) ---------------------------------------
     def _mm(self, fn, *args):
         if self._math >= 0:

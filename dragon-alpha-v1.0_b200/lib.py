@@ -55,6 +55,10 @@ def load():
     lib.alpha_conv_set_workspace.argtypes = [V, V, C.c_size_t]
     lib.alpha_conv_reserve_workspace.argtypes = [V, C.c_size_t]
     lib.alpha_conv_workspace_in_use.restype = C.c_size_t
+    lib.alpha_conv_prepared_weights_bytes.argtypes = [P, I, C.POINTER(C.c_size_t)]
+    lib.alpha_conv_prepare_weights.argtypes = [P, I, V, V, C.c_size_t, V]
+    lib.alpha_conv3d_forward_prepared.argtypes = [P, V, V, V, C.c_size_t, V, V, V]
+    lib.alpha_conv3d_deltaX_prepared.argtypes = [P, V, V, V, C.c_size_t, V, V]
     lib.alpha_conv_weight_cache.argtypes = [I]
     lib.alpha_conv_weights_updated.argtypes = [V]
     lib.alpha_engine_conv3D.argtypes = [V, I, I, V, I, I, V, I, I] + [I] * 7 + [V]
@@ -188,6 +192,13 @@ def release_workspace():
 
 def workspace_in_use():
     return int(load().alpha_conv_workspace_in_use())
+
+
+def prepared_weights_bytes(shape, op):
+    """Bytes of the weight-side transform `op` ('forward' or 'deltaX') needs for `shape` (0 = none)."""
+    n = C.c_size_t(0)
+    check(load().alpha_conv_prepared_weights_bytes(C.byref(shape), OPS[op], C.byref(n)))
+    return n.value
 
 
 def weight_cache(enable):

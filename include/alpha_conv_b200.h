@@ -143,6 +143,24 @@ size_t alpha_conv_workspace_in_use(void);
 int alpha_conv_weight_cache(int enable);
 int alpha_conv_weights_updated(const float* W);
 
+/* The same transforms in memory the CALLER owns, for hosts that schedule them themselves: a training loop can
+ * enqueue the transforms of all layers on a side stream right after the optimizer step (they depend on W only)
+ * and keep them off the critical path of the forward and backward chains; the library allocates nothing and
+ * records no events, the caller orders prepare before use (stream order, or an event, or a graph edge).
+ *   alpha_conv_prepared_weights_bytes  size of the transform op (ALPHA_OP_FORWARD / ALPHA_OP_DELTAX) needs for this
+ *                                      shape under the current math mode and options; 0 = none (plain TF32 forward)
+ *   alpha_conv_prepare_weights         enqueues the transform of W into `prepared` (256-byte aligned) on `stream`
+ *   alpha_conv3d_forward_prepared /    the contraction with the transform taken from `prepared`; shape, W address,
+ *   alpha_conv3d_deltaX_prepared       operator and math mode must be those of the prepare call (checked on the
+ *                                      host: ALPHA_E_ARG otherwise).  prepared == NULL is the plain call. */
+int alpha_conv_prepared_weights_bytes(const AlphaConvShape* s, int op, size_t* bytes);
+int alpha_conv_prepare_weights(const AlphaConvShape* s, int op, const float* W, void* prepared, size_t bytes,
+                               alpha_stream_t stream);
+int alpha_conv3d_forward_prepared(const AlphaConvShape* s, const float* X, const float* W, const void* prepared,
+                                  size_t bytes, const float* bias, float* Y, alpha_stream_t stream);
+int alpha_conv3d_deltaX_prepared(const AlphaConvShape* s, const float* deltaY, const float* W, const void* prepared,
+                                 size_t bytes, float* deltaX, alpha_stream_t stream);
+
 /* ---- layer 1: one call per contraction ------------------------------------------------------ */
 
 /* Y = conv(X, W) (+ bias per output channel when bias != NULL).

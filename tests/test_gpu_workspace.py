@@ -215,3 +215,53 @@ def test_sm_budget_leaves_sms_free_without_changing_the_results(pkg):
     assert torch.equal(got[0], ref[0]) and torch.equal(got[1], ref[1])      # per-tile results do not depend on the grid
     assert float((got[2] - ref[2]).abs().max()) <= 1e-5 * float(ref[2].abs().max())   # deltaW: other partial sums
     assert L.device_status() == 0
+
+
+def test_prepared_weights_in_caller_memory(pkg):
+    """The weight-side transforms computed ahead of the contraction into blocks the caller owns: same bits as
+    the plain calls, one launch fewer per contraction, nothing allocated by the library, and a block made for
+    another math mode is refused."""
+    import torch
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda:0")
+    L = pkg.submodule("lib")
+    base = pkg.submodule("engine").CudaFloat32EngineBase()
+    L.set_math_mode("3xtf32")
+    for name in ("s1_pair", "s2_phases", "stem_ic4", "tiny_image"):
+        case = SHAPES[name]
+        N, IH, IW, IC, OC, FH, FW, sh, sw, ph, pw = case
+        X, W, dY, (OH, OW) = _tensors(case, dev, seed=8)
+        Y0, dX0 = torch.empty((N, OH, OW, OC), device=dev), torch.empty_like(X)
+        n0 = L.launch_count()
+        base.conv3D(Y0, OH, OW, X, IH, IW, W, FH, FW, N, IC, OC, sh, sw, ph, pw)
+        base.dconv3D_deltaX(dX0, IH, IW, dY, OH, OW, W, FH, FW, N, IC, OC, sh, sw, ph, pw)
+        plain = L.launch_count() - n0
+        held = L.workspace_in_use()
+        side = torch.cuda.Stream()
+        geo = (FH, FW, N, IH, IW, OH, OW, IC, OC, sh, sw, ph, pw)
+        with torch.cuda.stream(side):
+            pf = base.prepare_weights("forward", W, *geo, stream=side)
+            pd = base.prepare_weights("deltaX", W, *geo, stream=side)
+        torch.cuda.current_stream().wait_stream(side)
+        assert pd is not None and (pf is not None or sh > 1)      # the strided forward kernel splits W tiles itself
+        Y1, dX1 = torch.empty_like(Y0), torch.empty_like(dX0)
+        n0 = L.launch_count()
+        base.conv3D_prepared(Y1, OH, OW, X, IH, IW, W, FH, FW, N, IC, OC, sh, sw, ph, pw, pf)
+        base.dconv3D_deltaX_prepared(dX1, IH, IW, dY, OH, OW, W, FH, FW, N, IC, OC, sh, sw, ph, pw, pd)
+        used = L.launch_count() - n0
+        torch.cuda.synchronize()
+        assert torch.equal(Y0, Y1) and torch.equal(dX0, dX1), name
+        assert used == plain - (pf is not None) - (pd is not None), (name, plain, used)
+        assert L.workspace_in_use() <= held, name
+        # blocks swapped between the operators, or made under another math mode, are refused on the host
+        if pf is not None:
+            with pytest.raises(L.AlphaConvError):
+                base.dconv3D_deltaX_prepared(dX1, IH, IW, dY, OH, OW, W, FH, FW, N, IC, OC, sh, sw, ph, pw, pf)
+        L.set_math_mode("tf32")
+        try:
+            assert base.prepare_weights("forward", W, *geo) is None       # plain TF32 forward reads W as it is
+            with pytest.raises(L.AlphaConvError):
+                base.dconv3D_deltaX_prepared(dX1, IH, IW, dY, OH, OW, W, FH, FW, N, IC, OC, sh, sw, ph, pw, pd)
+        finally:
+            L.set_math_mode("3xtf32")
+    assert L.device_status() == 0
