@@ -536,35 +536,109 @@ class Config3:
             L["dW"] = self.bucket.view(i, L["W"].shape)
         self.flops = sum(3 * synth.conv_flops(global_batch, L["OH"], L["OH"], L["OC"], L["F"], L["F"], L["IC"]) for L in self.layers)
         self.streams = [torch.cuda.Stream() for _ in range(2)]
+        # Weight-side transforms (lo plane of W for the forward pass, transposed planes for deltaX) depend on W
+        # only: like a training loop after its optimizer step, the step enqueues them for all layers on a side
+        # stream into blocks of its own, off the critical path of the forward and backward chains.
+        self.prepare = os.environ.get("BENCH_C3_PREP", "1") != "0"
+        self.ops = os.environ.get("BENCH_C3_OPS", "fwd,dx,dw").split(",")     # analysis aid: a subset of the three chains
+        self.prep_stream = torch.cuda.Stream()
+        base = env["base"]
+        for L in self.layers:
+            geo = (L["F"], L["F"], self.n, L["IH"], L["IH"], L["OH"], L["OH"], L["IC"], L["OC"], L["s"], L["s"], L["p"], L["p"])
+            L["geo"] = geo
+            L["pf"] = base.prepare_weights("forward", L["W"], *geo) if self.prepare else None
+            L["pd"] = base.prepare_weights("deltaX", L["W"], *geo) if self.prepare else None
+        # The gradient bucket is reduced in pieces, in backward order, on a communication stream, each piece as
+        # soon as the deltaW kernels that fill it have run (layers are contiguous in the bucket).
+        self.comm_stream = torch.cuda.Stream()
+        n_chunks = max(1, int(os.environ.get("BENCH_C3_AR_BUCKETS", "4"))) if world > 1 else 1
+        total = self.bucket.flat.numel()
+        self.chunks, start = [], len(self.layers)       # (first layer, last layer + 1) in backward order
+        acc = 0
+        for i in range(len(self.layers) - 1, -1, -1):
+            acc += self.layers[i]["W"].numel()
+            if acc >= total / n_chunks or i == 0:
+                self.chunks.append((i, start)); start = i; acc = 0
 
-    def compute(self):
-        torch, base, n = self.env["torch"], self.env["base"], self.n
+    def chunk_view(self, lo, hi):
+        a = self.bucket.offsets[lo]
+        b = self.bucket.offsets[hi] if hi < len(self.layers) else self.bucket.flat.numel()
+        return self.bucket.flat[a:b]
+
+    def compute(self, with_reduce=False):
+        torch, base, n, dist = self.env["torch"], self.env["base"], self.n, self.env["dist"]
         cur = torch.cuda.current_stream()
         fork = torch.cuda.Event(); fork.record(cur)
-        for s_ in self.streams:
+        for s_ in self.streams + [self.prep_stream]:
             s_.wait_event(fork)
-        # backward order for deltaW, so that the bucket fills front to back as a real backward pass would
-        for L in self.layers:
+        ready_f, ready_d = {}, {}
+        if self.prepare:
+            with torch.cuda.stream(self.prep_stream):
+                for i, L in enumerate(self.layers):
+                    if L["pf"] is not None:
+                        base.prepare_weights_into(L["pf"], "forward", L["W"], *L["geo"], stream=self.prep_stream)
+                        ready_f[i] = torch.cuda.Event(); ready_f[i].record(self.prep_stream)
+                for i in range(len(self.layers) - 1, -1, -1):
+                    L = self.layers[i]
+                    if L["pd"] is not None:
+                        base.prepare_weights_into(L["pd"], "deltaX", L["W"], *L["geo"], stream=self.prep_stream)
+                        ready_d[i] = torch.cuda.Event(); ready_d[i].record(self.prep_stream)
+        for i, L in enumerate(self.layers):
+            if "fwd" not in self.ops:
+                break
             a = (L["IH"], L["IH"])
-            base.conv3D(L["Y"], L["OH"], L["OH"], L["X"], *a, L["W"], L["F"], L["F"], n, L["IC"], L["OC"], L["s"], L["s"], L["p"], L["p"])
-        for L in reversed(self.layers):
+            if i in ready_f:
+                cur.wait_event(ready_f[i])
+            base.conv3D_prepared(L["Y"], L["OH"], L["OH"], L["X"], *a, L["W"], L["F"], L["F"], n, L["IC"], L["OC"], L["s"], L["s"], L["p"], L["p"], L["pf"])
+        chunk_end = {lo: (lo, hi) for lo, hi in self.chunks}
+        for i in range(len(self.layers) - 1, -1, -1):
+            L = self.layers[i]
             a = (L["IH"], L["IH"])
             with torch.cuda.stream(self.streams[0]):
-                base.dconv3D_deltaX(L["dX"], *a, L["dY"], L["OH"], L["OH"], L["W"], L["F"], L["F"], n, L["IC"], L["OC"], L["s"], L["s"], L["p"], L["p"])
+                if i in ready_d:
+                    self.streams[0].wait_event(ready_d[i])
+                if "dx" in self.ops:
+                    base.dconv3D_deltaX_prepared(L["dX"], *a, L["dY"], L["OH"], L["OH"], L["W"], L["F"], L["F"], n, L["IC"], L["OC"], L["s"], L["s"], L["p"], L["p"], L["pd"])
             with torch.cuda.stream(self.streams[1]):
-                base.dconv3D_deltaW(L["dW"], L["F"], L["F"], L["X"], *a, L["dY"], L["OH"], L["OH"], n, L["IC"], L["OC"], L["s"], L["s"], L["p"], L["p"])
-        for s_ in self.streams:
+                if "dw" in self.ops:
+                    base.dconv3D_deltaW(L["dW"], L["F"], L["F"], L["X"], *a, L["dY"], L["OH"], L["OH"], n, L["IC"], L["OC"], L["s"], L["s"], L["p"], L["p"])
+                if with_reduce and i in chunk_end and self.env["world"] > 1:
+                    done = torch.cuda.Event(); done.record(self.streams[1])
+                    self.comm_stream.wait_event(done)
+                    with torch.cuda.stream(self.comm_stream):
+                        dist.all_reduce(self.chunk_view(*chunk_end[i]), op=dist.ReduceOp.SUM)
+        for s_ in self.streams + [self.prep_stream] + ([self.comm_stream] if with_reduce else []):
             cur.wait_stream(s_)
 
     def reduce(self):
         if self.env["world"] > 1:
             self.env["dist"].all_reduce(self.bucket.flat, op=self.env["dist"].ReduceOp.SUM)
 
+    def check_reduce(self):
+        """The bucket after the chunked, overlapped all-reduce against the double-precision sum of the per-rank
+        partial gradients of two layers (first and last), gathered before anything is timed."""
+        torch, dist, world = self.env["torch"], self.env["dist"], self.env["world"]
+        if world == 1:
+            return None
+        self.compute(with_reduce=False)
+        torch.cuda.synchronize()
+        want = {}
+        for i in (0, len(self.layers) - 1):
+            part = self.layers[i]["dW"].clone()
+            parts = [torch.empty_like(part) for _ in range(world)]
+            dist.all_gather(parts, part)
+            want[i] = (torch.stack([p.double() for p in parts]).sum(0), torch.stack([p.double().abs() for p in parts]).sum(0))
+        self.compute(with_reduce=True)
+        torch.cuda.synchronize()
+        bad = max(float(((self.layers[i]["dW"].double() - w).abs() - 1e-6 * sc).max()) for i, (w, sc) in want.items())
+        return "ok" if bad <= 0 else "MISMATCH (excess %.3e)" % bad
+
     def run(self, steps, repeats, barrier, use_graph=True):
         torch, lib, dist, world, dev = self.env["torch"], self.env["lib"], self.env["dist"], self.env["world"], self.env["dev"]
         for _ in range(3):
-            self.compute(); self.reduce()
+            self.compute(with_reduce=True)
         torch.cuda.synchronize()
+        ar_check = self.check_reduce()
         graph, in_graph, err, launches = None, False, None, None
         with_ar = world > 1 and os.environ.get("BENCH_GRAPH_AR", "1") != "0"
         for attempt in (() if not use_graph else (True, False) if with_ar else (False,)):
@@ -572,17 +646,13 @@ class Config3:
                 side = torch.cuda.Stream()
                 side.wait_stream(torch.cuda.current_stream())
                 with torch.cuda.stream(side):
-                    self.compute()
-                    if attempt:
-                        self.reduce()
+                    self.compute(with_reduce=attempt)
                 torch.cuda.current_stream().wait_stream(side)
                 torch.cuda.synchronize()
                 gobj = torch.cuda.CUDAGraph()
                 n0 = lib.launch_count()
                 with torch.cuda.graph(gobj, stream=side):
-                    self.compute()
-                    if attempt:
-                        self.reduce()
+                    self.compute(with_reduce=attempt)
                 launches = lib.launch_count() - n0
                 gobj.replay()
                 torch.cuda.synchronize()
@@ -598,11 +668,11 @@ class Config3:
                 if not in_graph:
                     self.reduce()
             else:
-                self.compute(); self.reduce()
+                self.compute(with_reduce=True)
         for _ in range(3):
             one()
         if launches is None:
-            n0 = lib.launch_count(); self.compute(); launches = lib.launch_count() - n0
+            n0 = lib.launch_count(); self.compute(with_reduce=True); launches = lib.launch_count() - n0
         regions = []
         for _ in range(repeats):
             barrier()
@@ -627,7 +697,10 @@ class Config3:
                 "ms_per_step_regions": [round(x, 4) for x in regions], "steps_per_region": steps,
                 "gpu_launches_per_step": int(launches), "allreduce_bytes": int(self.bucket.flat.numel() * 4) if world > 1 else 0,
                 "launch": ("CUDA graph" + (" incl. the all-reduce" if in_graph else "") if graph is not None else "eager launches"),
-                "graph_error": err, "kernel_status": status}
+                "allreduce": ("%d pieces in backward order on a communication stream, overlapped with the remaining kernels" % len(self.chunks)
+                              if world > 1 and (in_graph or graph is None) else ("one piece after the step" if world > 1 else None)),
+                "weight_transforms": "prepared on a side stream into caller-owned blocks" if self.prepare else "inside every call",
+                "allreduce_check": ar_check, "graph_error": err, "kernel_status": status}
 
 
 def cu32_baseline(env, sweep, iters=3):

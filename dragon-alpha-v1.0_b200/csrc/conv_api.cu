@@ -59,7 +59,7 @@ enum Opt {
     OPT_HALO_ROW, OPT_HALO_JH, OPT_HALO_JW, OPT_HALO_STACK, OPT_HALO_WIDE, OPT_HALO_PAIR, OPT_HALO_FLAT,
     OPT_HALO_NARROW, OPT_HALO_DUAL, OPT_PATCH_MATRIX, OPT_DX_PHASES, OPT_DX_COL2IM, OPT_DX_TRANSPOSE,
     OPT_DW_STACKED, OPT_DW_DIAG, OPT_DW_CW, OPT_DW_R, OPT_DW_STATIC, OPT_CONV_PROF, OPT_SM_BUDGET,
-    OPT_SKINNY, OPT_HALO_DEEP, OPT_HALO_SPLITB, OPT_NVTX,
+    OPT_SKINNY, OPT_HALO_DEEP, OPT_HALO_SPLITB, OPT_NVTX, OPT_DW_LANES,
     OPT_COUNT
 };
 struct OptDef { const char* name; int dflt; };
@@ -68,7 +68,7 @@ static const OptDef kOptDefs[OPT_COUNT] = {
     {"HALO_ROW", 1}, {"HALO_JH", 0}, {"HALO_JW", 0}, {"HALO_STACK", 1}, {"HALO_WIDE", -1}, {"HALO_PAIR", -1}, {"HALO_FLAT", 1},
     {"HALO_NARROW", 1}, {"HALO_DUAL", 1}, {"PATCH_MATRIX", 1}, {"DX_PHASES", 1}, {"DX_COL2IM", 1}, {"DX_TRANSPOSE", 1},
     {"DW_STACKED", -1}, {"DW_DIAG", 1}, {"DW_CW", 0}, {"DW_R", 0}, {"DW_STATIC", 1}, {"CONV_PROF", 0}, {"SM_BUDGET", 0},
-    {"SKINNY", 1}, {"HALO_DEEP", 1}, {"HALO_SPLITB", 0}, {"NVTX", 1},
+    {"SKINNY", 1}, {"HALO_DEEP", 1}, {"HALO_SPLITB", 0}, {"NVTX", 1}, {"DW_LANES", 0},
 };
 static std::atomic<int> g_opt[OPT_COUNT];
 static std::once_flag g_opt_once;
@@ -1511,7 +1511,7 @@ static int launch_dw_halo(DeviceCtx* c, const AlphaConvShape* s_in, const float*
     if (rc) return rc;
     if (parts * nsub > 1) {
         const size_t n4 = sizeW / 4;
-        if (!t_dry) dw_reduce_kernel<<<(unsigned)((n4 + 63) / 64), 64, 0, stream>>>(ws, sizeW, parts * nsub, dW, n4, 0);
+        if (!t_dry) launch_dw_reduce(ws, sizeW, parts * nsub, dW, n4, 0, stream, opt(OPT_DW_LANES));
         note_launch("dw_halo");
         rc = check_launch("dw_reduce_kernel");
     }
@@ -1531,7 +1531,7 @@ static int launch_dw_halo(DeviceCtx* c, const AlphaConvShape* s_in, const float*
 int launch_buf_summary(cudaStream_t stream, const float* buf, float* deltaW, int part, size_t sizeW)
 {
     const size_t n4 = sizeW / 4;
-    if (!t_dry) dw_reduce_kernel<<<(unsigned)((n4 + 63) / 64), 64, 0, stream>>>(buf, sizeW, part, deltaW, n4, 1);
+    if (!t_dry) launch_dw_reduce(buf, sizeW, part, deltaW, n4, 1, stream, opt(OPT_DW_LANES));
     note_launch("buf_summary");
     return check_launch("dw_reduce_kernel");
 }
@@ -1614,7 +1614,7 @@ static int launch_dw_split(const AlphaConvShape* s, const float* X, const float*
     if (rc) return rc;
     if (pl.splits > 1) {
         const size_t n4 = pl.sizeW / 4;
-        if (!t_dry) dw_reduce_kernel<<<(unsigned)((n4 + 63) / 64), 64, 0, stream>>>(partials, pl.sizeW, pl.splits, deltaW, n4, 0);
+        if (!t_dry) launch_dw_reduce(partials, pl.sizeW, pl.splits, deltaW, n4, 0, stream, opt(OPT_DW_LANES));
         note_launch(tag);
         rc = check_launch("dw_reduce_kernel");
     }

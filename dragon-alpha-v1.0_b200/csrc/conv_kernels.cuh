@@ -727,35 +727,72 @@ __global__ void __launch_bounds__(kIgemmThreads)
     if (warp == 1) tmem_dealloc(tmem_base, p.tmem_cols);
 }
 
-// out[i] = sum over splits of part[s][i], in split order, with Kahan compensation (the reference
-// sums its split-K buffers the same way: Cuda_dconv3D_deltaW/dconv3d_dW_GemmSK_bufSum.cuh:41-63).
-// When `accumulate` is set, out[i] itself is the first term (deltaW += sum of buffers).
+// out[i] = sum over splits of part[s][i] with Kahan compensation (the reference sums its split-K buffers the
+// same way: Cuda_dconv3D_deltaW/dconv3d_dW_GemmSK_bufSum.cuh:41-63).  When `accumulate` is set, out[i] itself is
+// the first term (deltaW += sum of buffers).  LANES threads share one output vector: lane l adds the partials
+// l, l + LANES, ... in that order, then the lanes' sums and compensations are added in lane order - a fixed
+// order, so the result does not depend on scheduling.  The loop is bound by load latency (few threads, one
+// dependent chain each), which is why many partials are spread over lanes.
+template <int LANES>
 __global__ void dw_reduce_kernel(const float* __restrict__ part, size_t split_stride, int splits,
                                  float* __restrict__ out, size_t n4, int accumulate)
 {
-    const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (i >= n4) return;
-    float4 s = accumulate ? reinterpret_cast<const float4*>(out)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    const size_t t = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const size_t i = t / LANES;
+    const int lane = static_cast<int>(t % LANES);
+    const bool live = i < n4;
+    float4 s = (live && accumulate && lane == 0) ? reinterpret_cast<const float4*>(out)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
     float4 c = make_float4(0.f, 0.f, 0.f, 0.f);
     auto add = [&](const float4& v) {
-        float y, t;
-        y = v.x - c.x; t = s.x + y; c.x = (t - s.x) - y; s.x = t;
-        y = v.y - c.y; t = s.y + y; c.y = (t - s.y) - y; s.y = t;
-        y = v.z - c.z; t = s.z + y; c.z = (t - s.z) - y; s.z = t;
-        y = v.w - c.w; t = s.w + y; c.w = (t - s.w) - y; s.w = t;
+        float y, u;
+        y = v.x - c.x; u = s.x + y; c.x = (u - s.x) - y; s.x = u;
+        y = v.y - c.y; u = s.y + y; c.y = (u - s.y) - y; s.y = u;
+        y = v.z - c.z; u = s.z + y; c.z = (u - s.z) - y; s.z = u;
+        y = v.w - c.w; u = s.w + y; c.w = (u - s.w) - y; s.w = u;
     };
-    // eight loads in flight, then the compensated additions in split order: there are few threads
-    // (one per four weights), so the loop is bound by load latency, not bandwidth
-    int k = 0;
-    for (; k + 8 <= splits; k += 8) {
-        float4 v[8];
+    if (live) {
+        // eight loads in flight, then the compensated additions in order
+        int k = lane;
+        for (; k + 7 * LANES < splits; k += 8 * LANES) {
+            float4 v[8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) v[j] = __ldg(reinterpret_cast<const float4*>(part + (k + j) * split_stride) + i);
+            for (int j = 0; j < 8; ++j) v[j] = __ldg(reinterpret_cast<const float4*>(part + (k + j * LANES) * split_stride) + i);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) add(v[j]);
+            for (int j = 0; j < 8; ++j) add(v[j]);
+        }
+        for (; k < splits; k += LANES) add(__ldg(reinterpret_cast<const float4*>(part + k * split_stride) + i));
     }
-    for (; k < splits; ++k) add(__ldg(reinterpret_cast<const float4*>(part + k * split_stride) + i));
-    reinterpret_cast<float4*>(out)[i] = s;
+    if (LANES > 1) {
+        // lane 0 adds the other lanes' sums, then takes off their compensations (what each lane's sum overshot)
+        const unsigned mask = 0xffffffffu;
+        const int base = (threadIdx.x & 31) - lane;
+#pragma unroll
+        for (int l = 1; l < LANES; ++l) {
+            float4 so, co;
+            so.x = __shfl_sync(mask, s.x, base + l); so.y = __shfl_sync(mask, s.y, base + l);
+            so.z = __shfl_sync(mask, s.z, base + l); so.w = __shfl_sync(mask, s.w, base + l);
+            co.x = __shfl_sync(mask, c.x, base + l); co.y = __shfl_sync(mask, c.y, base + l);
+            co.z = __shfl_sync(mask, c.z, base + l); co.w = __shfl_sync(mask, c.w, base + l);
+            if (lane == 0) {
+                add(so);
+                add(make_float4(-co.x, -co.y, -co.z, -co.w));
+            }
+        }
+    }
+    if (live && lane == 0) reinterpret_cast<float4*>(out)[i] = s;
+}
+
+// Launch helper: one lane per output vector for a handful of partials, four when there are many
+// (lanes: 0 = choose, 1 or 4 = forced).
+inline void launch_dw_reduce(const float* part, size_t split_stride, int splits, float* out, size_t n4, int accumulate,
+                             cudaStream_t stream, int lanes = 0)
+{
+    if (lanes == 4 || (lanes == 0 && splits >= 32)) {
+        const size_t threads = n4 * 4;
+        dw_reduce_kernel<4><<<static_cast<unsigned>((threads + 127) / 128), 128, 0, stream>>>(part, split_stride, splits, out, n4, accumulate);
+    } else {
+        dw_reduce_kernel<1><<<static_cast<unsigned>((n4 + 63) / 64), 64, 0, stream>>>(part, split_stride, splits, out, n4, accumulate);
+    }
 }
 
 // Column sums of a row-major matrix x[rows][cols4 * 4] (the bias gradient: deltaY summed over batch
