@@ -4,6 +4,7 @@
 #include "conv_halo.cuh"
 #include "conv_halo_pair.cuh"
 #include "conv_dw_halo.cuh"
+#include "conv_tapstack.cuh"
 #include "winograd.cuh"
 #include "host_common.h"
 
@@ -59,7 +60,7 @@ enum Opt {
     OPT_HALO_ROW, OPT_HALO_JH, OPT_HALO_JW, OPT_HALO_STACK, OPT_HALO_WIDE, OPT_HALO_PAIR, OPT_HALO_FLAT,
     OPT_HALO_NARROW, OPT_HALO_DUAL, OPT_PATCH_MATRIX, OPT_DX_PHASES, OPT_DX_COL2IM, OPT_DX_TRANSPOSE,
     OPT_DW_STACKED, OPT_DW_DIAG, OPT_DW_CW, OPT_DW_R, OPT_DW_STATIC, OPT_CONV_PROF, OPT_SM_BUDGET,
-    OPT_SKINNY, OPT_HALO_DEEP, OPT_HALO_SPLITB, OPT_NVTX, OPT_DW_LANES,
+    OPT_SKINNY, OPT_HALO_DEEP, OPT_HALO_SPLITB, OPT_NVTX, OPT_DW_LANES, OPT_HALO_TAPSTACK,
     OPT_COUNT
 };
 struct OptDef { const char* name; int dflt; };
@@ -68,7 +69,7 @@ static const OptDef kOptDefs[OPT_COUNT] = {
     {"HALO_ROW", 1}, {"HALO_JH", 0}, {"HALO_JW", 0}, {"HALO_STACK", 1}, {"HALO_WIDE", -1}, {"HALO_PAIR", -1}, {"HALO_FLAT", 1},
     {"HALO_NARROW", 1}, {"HALO_DUAL", 1}, {"PATCH_MATRIX", 1}, {"DX_PHASES", 1}, {"DX_COL2IM", 1}, {"DX_TRANSPOSE", 1},
     {"DW_STACKED", -1}, {"DW_DIAG", 1}, {"DW_CW", 0}, {"DW_R", 0}, {"DW_STATIC", 1}, {"CONV_PROF", 0}, {"SM_BUDGET", 0},
-    {"SKINNY", 1}, {"HALO_DEEP", 1}, {"HALO_SPLITB", 0}, {"NVTX", 1}, {"DW_LANES", 0},
+    {"SKINNY", 1}, {"HALO_DEEP", 1}, {"HALO_SPLITB", 0}, {"NVTX", 1}, {"DW_LANES", 0}, {"HALO_TAPSTACK", 1},
 };
 static std::atomic<int> g_opt[OPT_COUNT];
 static std::once_flag g_opt_once;
@@ -946,6 +947,108 @@ static int launch_halo_pair(DeviceCtx* c, const IgemmPlan& pl, int mode3x, cudaS
 }
 
 // Returns 1 when the shape is left to the per-tap kernel, 0 on launch, < 0 on error.
+// ---- plain TF32, few output channels: the taps of a filter row in one MMA ----------------------------
+//
+// conv_tapstack_kernel: tiles of 4 output rows x CB columns (32 patch columns), all of W resident in
+// shared memory, N = FW * BN columns per MMA.  The cost uses the units of plan_halo (clocks of the
+// busiest CTA), so the two plans compare directly.
+struct TapStackPlan {
+    bool valid = false;
+    int BN = 0, CB = 0, npb = 0, row_blocks = 0, col_blocks = 0;
+    uint32_t patch_bytes = 0, w_tile = 0, w_bytes = 0;
+    size_t smem = 0;
+    double cost = 0, eff = 0;
+};
+
+static TapStackPlan plan_tapstack(const IgemmPlan& pl, int mode3x, int sm_count)
+{
+    TapStackPlan ts;
+    const int mode = opt(OPT_HALO_TAPSTACK);
+    if (!mode || mode3x || pl.b_mn || pl.sh != 1 || pl.sw != 1 || pl.kdim % 32 != 0) return ts;
+    if (pl.oSH != 1 || pl.oSW != 1 || pl.oNH != 0 || pl.oNW != 0) return ts;
+    if (pl.FW < 2 || pl.FW > 8 || pl.ncols % 4 != 0) return ts;
+    const int BN = (pl.ncols + 15) / 16 * 16;
+    if (pl.FW * BN > 256) return ts;
+    const int kchunks = pl.kdim / 32;
+    const int PH = 4 + pl.FH - 1;
+    if (PH > 256) return ts;
+    ts.BN = BN;
+    ts.patch_bytes = (uint32_t)PH * 4096u;
+    ts.w_tile = (uint32_t)BN * 128u;
+    const size_t w_bytes = (size_t)kchunks * pl.FH * pl.FW * ts.w_tile;
+    const size_t cap = 227 * 1024, fixed = 1024 + 8192 + 256;
+    if (w_bytes > 1000000 || w_bytes + 2 * (size_t)ts.patch_bytes + fixed > cap) return ts;
+    ts.w_bytes = (uint32_t)w_bytes;
+    int npb = (int)((cap - fixed - w_bytes) / ts.patch_bytes);
+    if (npb > 6) npb = 6;
+    ts.npb = npb;
+    ts.smem = w_bytes + (size_t)npb * ts.patch_bytes + fixed;
+    const int max_cb = 32 - (pl.FW - 1);
+    ts.col_blocks = (pl.oW + max_cb - 1) / max_cb;
+    ts.CB = (pl.oW + ts.col_blocks - 1) / ts.col_blocks;
+    ts.row_blocks = (pl.oH + 3) / 4;
+    const long long tiles = (long long)pl.aN * ts.row_blocks * ts.col_blocks;
+    if (tiles > 2147483647LL) return ts;
+    ts.eff = (double)pl.oH * pl.oW / ((double)ts.row_blocks * ts.col_blocks * 128.0);
+    auto clk = [](double n) { return n / 2.0 > 59.0 ? n / 2.0 : 59.0; };
+    const double steps = (double)kchunks * pl.FH * 4;
+    const double t_mma = steps * clk((double)pl.FW * BN) + 600.0;
+    const double t_smem = (steps * (4096.0 + 32.0 * pl.FW * BN) + (double)kchunks * ts.patch_bytes + 4.0 * 128 * BN * 4) / 128.0 + 500.0;
+    const double t_l2 = ((double)kchunks * ts.patch_bytes + 128.0 * BN * 4) / 28.0;
+    double t = t_mma > t_smem ? t_mma : t_smem;
+    if (t_l2 > t) t = t_l2;
+    if (npb < 3) t *= 1.25;
+    // every CTA loads all of W before its first MMA
+    ts.cost = t * (double)((tiles + sm_count - 1) / sm_count) + (double)w_bytes / 28.0;
+    ts.valid = mode == 2 || ts.eff >= 0.6;
+    return ts;
+}
+
+static int launch_tapstack(DeviceCtx* c, const IgemmPlan& pl, const TapStackPlan& ts, cudaStream_t stream)
+{
+    TapStackParams p{};
+    p.out = pl.out; p.bias = pl.bias; p.act_on = pl.act_on; p.act_k = pl.act_k; p.status = c->status; p.prof = c->prof;
+    p.N = pl.aN; p.OH = pl.oH; p.OW = pl.oW; p.Ncols = pl.ncols; p.ldo = pl.ncols;
+    p.FH = pl.FH; p.FW = pl.FW; p.pad_h = pl.pad_h; p.pad_w = pl.pad_w;
+    p.kchunks = pl.kdim / 32; p.BN = ts.BN; p.CB = ts.CB;
+    p.row_blocks = ts.row_blocks; p.col_blocks = ts.col_blocks;
+    p.total_tiles = (int)((long long)pl.aN * ts.row_blocks * ts.col_blocks);
+    p.npb = ts.npb; p.patch_bytes = ts.patch_bytes; p.w_tile = ts.w_tile; p.w_bytes = ts.w_bytes;
+    p.accw = (uint32_t)pl.FW * ts.BN;
+    p.idesc = make_idesc_tf32(kBM, pl.FW * ts.BN, false, false);
+    // the epilogue reads 32 columns at a time; with BN % 32 != 0 its last read of a tap block runs up to 16
+    // columns past the second accumulator
+    p.tmem_cols = pow2_cols(2 * pl.FW * ts.BN + (ts.BN % 32 ? 32 : 0));
+
+    CUtensorMap tmA, tmB;
+    cuuint64_t ad[4] = {(cuuint64_t)pl.aC, (cuuint64_t)pl.aW, (cuuint64_t)pl.aH, (cuuint64_t)pl.aN};
+    cuuint64_t as[3] = {(cuuint64_t)pl.aC * 4, (cuuint64_t)pl.aW * pl.aC * 4, (cuuint64_t)pl.aH * pl.aW * pl.aC * 4};
+    cuuint32_t abox[4] = {32, 32, (cuuint32_t)(4 + pl.FH - 1), 1};
+    int rc = make_tiled_map(&tmA, pl.act, 4, ad, as, abox, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    cuuint64_t wd[3] = {(cuuint64_t)pl.wIC, (cuuint64_t)pl.FH * pl.FW, (cuuint64_t)pl.wOC};
+    cuuint64_t wst[2] = {(cuuint64_t)pl.wIC * 4, (cuuint64_t)pl.FH * pl.FW * pl.wIC * 4};
+    cuuint32_t wbox[3] = {32, 1, (cuuint32_t)ts.BN};
+    rc = make_tiled_map(&tmB, pl.W, 3, wd, wst, wbox, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    static bool attr_done = false;
+    if (!attr_done) {
+        cudaFuncSetAttribute(conv_tapstack_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        cudaFuncSetAttribute(conv_tapstack_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        cudaFuncSetAttribute(conv_tapstack_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        attr_done = true;
+    }
+    const int grid = sm_budget(c) < p.total_tiles ? sm_budget(c) : p.total_tiles;
+    if (!t_dry) {
+        if (pl.FW == 3) conv_tapstack_kernel<3><<<grid, kTapStackThreads, ts.smem, stream>>>(tmA, tmB, p);
+        else if (pl.FW == 2) conv_tapstack_kernel<2><<<grid, kTapStackThreads, ts.smem, stream>>>(tmA, tmB, p);
+        else conv_tapstack_kernel<0><<<grid, kTapStackThreads, ts.smem, stream>>>(tmA, tmB, p);
+    }
+    note_launch("halo_tapstack");
+    snprintf(g_plan, sizeof(g_plan), "tapstack BN=%d N=%d CB=%d npb=%d eff=%.2f", ts.BN, pl.FW * ts.BN, ts.CB, ts.npb, ts.eff);
+    return check_launch("conv_tapstack_kernel");
+}
+
 static int launch_halo(DeviceCtx* c, const IgemmPlan& pl_in, int mode3x, cudaStream_t stream)
 {
     const int tile_mode = env_tile_mode();
@@ -995,6 +1098,11 @@ static int launch_halo(DeviceCtx* c, const IgemmPlan& pl_in, int mode3x, cudaStr
         if (cand >= BN || pl.ncols % cand != 0 || !opt(OPT_HALO_NARROW)) continue;
         HaloChoice alt = plan_halo(pl, cand, mode3x, pl.b_mn, sm_budget(c));
         if (alt.valid && (!ch.valid || alt.cost < 0.9 * ch.cost)) { ch = alt; BN = cand; }
+    }
+    {
+        // plain TF32 with few output channels: one MMA per filter row where the model says it is faster
+        const TapStackPlan ts = plan_tapstack(pl, mode3x, sm_budget(c));
+        if (ts.valid && (opt(OPT_HALO_TAPSTACK) == 2 || !ch.valid || ts.cost < 0.8 * ch.cost)) return launch_tapstack(c, pl, ts, stream);
     }
     if (!ch.valid || (tile_mode == 0 && ch.eff < 0.6 && !pl.force)) {
         // a skinny shape whose tiles the single-CTA kernel would leave mostly empty: the pair kernel after all

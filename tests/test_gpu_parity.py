@@ -154,7 +154,7 @@ def test_bench_channel_configurations(pkg, eng, oracle_mod, name, mode):
     eng.conv3D(big_X, torch.from_numpy(W).to(dev), 1, 1, 1, 1)
     big = lib.last_plan()
     assert lib.device_status() == 0
-    assert res["fwd_algo"].startswith("halo") and big.startswith("halo"), (res["fwd_algo"], big)
+    assert res["fwd_algo"].startswith("halo") and big.startswith(("halo", "tapstack")), (res["fwd_algo"], big)
     if "halo_pair" in big:
         assert small == big, (small, big)   # the pair kernel's form does not depend on the batch
     if mode == "3xtf32":
@@ -164,6 +164,8 @@ def test_bench_channel_configurations(pkg, eng, oracle_mod, name, mode):
             assert "halo_pair" in big and "three+side" in big, big
     elif OC % 256 == 0:
         assert "halo_pair" in big, big
+    elif OC == 64:
+        assert big.startswith("tapstack"), big   # one MMA per filter row
 
 
 # Few output tiles and a long reduction (deep layers at a small batch): the forward / deltaX kernel
@@ -391,3 +393,69 @@ def test_pair_kernel_is_chosen_for_256_channel_blocks(pkg, eng, oracle_mod):
     res, _ = _run_case(pkg, eng, oracle_mod, "ic64_oc256_14x14", "tf32")
     assert res["fwd_algo"].startswith("halo_pair"), res["fwd_algo"]
     assert res["fwd"]["norm"] <= TOL["tf32"]["norm"] and res["fwd"]["comp"] <= TOL["tf32"]["comp"], res["fwd"]
+
+
+# Plain TF32 with few output channels: the taps of a filter row share one MMA (conv_tapstack_kernel).
+# (N, IH, IW, IC, OC, FH, FW, sh, sw, ph, pw)
+TAPSTACK_CASES = {
+    "ts_56x56x64": (2, 56, 56, 64, 64, 3, 3, 1, 1, 1, 1),        # the benchmark's first layer
+    "ts_ragged_oc48": (3, 13, 57, 32, 48, 3, 3, 1, 1, 1, 1),     # OH % 4 != 0, two column blocks of 29, BN % 32 != 0
+    "ts_fw2": (2, 7, 29, 96, 64, 3, 2, 1, 1, 1, 0),              # two taps per row, three channel chunks
+    "ts_5x5_oc16": (2, 9, 30, 32, 16, 5, 5, 1, 1, 2, 2),         # generic filter width, 16-column tap blocks
+    "ts_nopad": (2, 20, 31, 64, 32, 3, 3, 1, 1, 0, 0),
+    "ts_oc20": (2, 8, 28, 32, 20, 3, 3, 1, 1, 1, 1),             # output channels not a multiple of 16
+    "ts_wide_image": (1, 9, 112, 32, 64, 3, 3, 1, 1, 1, 1),      # four column blocks
+    "ts_small": (1, 5, 6, 32, 8, 3, 3, 1, 1, 1, 1),              # two partly filled tiles
+}
+CASES.update(TAPSTACK_CASES)
+
+
+@pytest.mark.parametrize("name", list(TAPSTACK_CASES))
+def test_tap_stacked_kernel(pkg, eng, oracle_mod, name):
+    """Forced on every case (option HALO_TAPSTACK = 2), against the oracle under the TF32 bounds, and against
+    the tap-by-tap kernels: both truncate the same operands, so they differ only by summation order."""
+    import torch
+    L = pkg.submodule("lib")
+    old = L.set_option("HALO_TAPSTACK", 2)
+    try:
+        res, (X, W, B, dY, Y, dX, dW) = _run_case(pkg, eng, oracle_mod, name, "tf32")
+        assert res["status"] == 0
+        assert res["fwd_algo"] == "halo_tapstack", res["fwd_algo"]
+        for op in ("fwd", "dx"):
+            m = res[op]
+            assert m["finite"] and m["norm"] <= TOL["tf32"]["norm"] and m["comp"] <= TOL["tf32"]["comp"], (op, res[op + "_algo"], m)
+        # bias + LeakyReLU in the epilogue
+        N, IH, IW, IC, OC, FH, FW, sh, sw, ph, pw = CASES[name]
+        dev = torch.device("cuda:0")
+        tX, tW, tB = (torch.from_numpy(a).to(dev) for a in (X, W, B))
+        Ya = eng.conv3D_leakyRelu(tX, tW, tB, 0.1, sh, sw, ph, pw)
+        assert L.last_algo() == "halo_tapstack"
+        want = np.where(Y > 0, Y, np.float32(0.1) * Y)
+        np.testing.assert_array_equal(Ya.cpu().numpy(), want)
+        L.set_option("HALO_TAPSTACK", 0)
+        Y0 = eng.conv3D_biased(tX, tW, tB, sh, sw, ph, pw)
+        assert L.last_algo() != "halo_tapstack"
+        scale = np.abs(Y).max()
+        assert np.abs(Y0.cpu().numpy() - Y).max() <= 5e-5 * scale   # the accumulators round once per MMA, in a different order
+    finally:
+        L.set_option("HALO_TAPSTACK", old)
+
+
+def test_tap_stacked_kernel_is_chosen_for_the_64_channel_layer(pkg, eng):
+    """At the benchmark's batch the planner takes it for forward and deltaX in plain TF32, never in 3xTF32."""
+    import torch
+    lib = pkg.submodule("lib")
+    dev = torch.device("cuda:0")
+    X = torch.zeros((256, 56, 56, 64), device=dev)
+    W = torch.zeros((64, 3, 3, 64), device=dev)
+    lib.set_math_mode("tf32")
+    try:
+        eng.conv3D(X, W, 1, 1, 1, 1)
+        assert lib.last_algo() == "halo_tapstack", lib.last_plan()
+        eng.dconv3D_deltaX(X, W, 56, 56, 1, 1, 1, 1)
+        assert lib.last_algo() == "halo_tapstack", lib.last_plan()
+    finally:
+        lib.set_math_mode("3xtf32")
+    eng.conv3D(X, W, 1, 1, 1, 1)
+    assert lib.last_algo() != "halo_tapstack"
+    assert lib.device_status() == 0
