@@ -976,7 +976,7 @@ static TapStackPlan plan_tapstack(const IgemmPlan& pl, int mode3x, int sm_count)
     ts.patch_bytes = (uint32_t)PH * 4096u;
     ts.w_tile = (uint32_t)BN * 128u;
     const size_t w_bytes = (size_t)kchunks * pl.FH * pl.FW * ts.w_tile;
-    const size_t cap = 227 * 1024, fixed = 1024 + 8192 + 256;
+    const size_t cap = 227 * 1024, fixed = 1024 + 256;   // alignment slack, barriers
     if (w_bytes > 1000000 || w_bytes + 2 * (size_t)ts.patch_bytes + fixed > cap) return ts;
     ts.w_bytes = (uint32_t)w_bytes;
     int npb = (int)((cap - fixed - w_bytes) / ts.patch_bytes);
@@ -1033,16 +1033,18 @@ static int launch_tapstack(DeviceCtx* c, const IgemmPlan& pl, const TapStackPlan
     if (rc) return rc;
     static bool attr_done = false;
     if (!attr_done) {
-        cudaFuncSetAttribute(conv_tapstack_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-        cudaFuncSetAttribute(conv_tapstack_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-        cudaFuncSetAttribute(conv_tapstack_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        cudaFuncSetAttribute(conv_tapstack_kernel<0, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        cudaFuncSetAttribute(conv_tapstack_kernel<2, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        cudaFuncSetAttribute(conv_tapstack_kernel<3, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        cudaFuncSetAttribute(conv_tapstack_kernel<3, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         attr_done = true;
     }
     const int grid = sm_budget(c) < p.total_tiles ? sm_budget(c) : p.total_tiles;
     if (!t_dry) {
-        if (pl.FW == 3) conv_tapstack_kernel<3><<<grid, kTapStackThreads, ts.smem, stream>>>(tmA, tmB, p);
-        else if (pl.FW == 2) conv_tapstack_kernel<2><<<grid, kTapStackThreads, ts.smem, stream>>>(tmA, tmB, p);
-        else conv_tapstack_kernel<0><<<grid, kTapStackThreads, ts.smem, stream>>>(tmA, tmB, p);
+        if (pl.FW == 3 && pl.FH == 3) conv_tapstack_kernel<3, 3><<<grid, kTapStackThreads, ts.smem, stream>>>(tmA, tmB, p);
+        else if (pl.FW == 3) conv_tapstack_kernel<3, 0><<<grid, kTapStackThreads, ts.smem, stream>>>(tmA, tmB, p);
+        else if (pl.FW == 2) conv_tapstack_kernel<2, 0><<<grid, kTapStackThreads, ts.smem, stream>>>(tmA, tmB, p);
+        else conv_tapstack_kernel<0, 0><<<grid, kTapStackThreads, ts.smem, stream>>>(tmA, tmB, p);
     }
     note_launch("halo_tapstack");
     snprintf(g_plan, sizeof(g_plan), "tapstack BN=%d N=%d CB=%d npb=%d eff=%.2f", ts.BN, pl.FW * ts.BN, ts.CB, ts.npb, ts.eff);

@@ -16,17 +16,27 @@
 //
 // All of W (kchunks x FH x FW tiles of BN x 32 floats) stays resident in shared memory; only the
 // input patches (32 channels x 32 columns x (4 + FH - 1) rows, zero-filled outside the image by the
-// TMA) stream through a ring.  Accumulators are double-buffered in tensor memory (2 x FW * BN
-// columns), so the gather / store of one tile overlaps the MMAs of the next.
+// TMA) stream through a ring.  Tensor memory holds two accumulators (2 x FW * BN columns), so the
+// gather / store of one tile overlaps the MMAs of the next.
 //
-// Warps: 0 TMA producer, 1 MMA issuer (owns tensor memory), 2-9 epilogue (two warps per tensor-memory
-// lane quadrant, each with half of the channels).
+// Two issuing threads: in a kernel one thread gets a tcgen05.mma started only every 100-120 clocks
+// (waits, fences and commits run in series with its MMAs), more than the 96 clocks an MMA of 192
+// columns keeps the pipe busy.  Issuer i owns accumulator i and every second tile of the CTA, so
+// each accumulator still sees one thread and one fixed order of MMAs (results are reproducible),
+// and the patches of two tiles are in use at a time.
+//
+// The epilogue uses no shared memory: after the gather a lane holds 32 channels of ONE pixel; a
+// 4 x 4 transpose of 16-byte pieces among groups of four lanes (two shuffle stages) leaves it with
+// 16 bytes of FOUR pixels, so that a store instruction writes 64 contiguous bytes per pixel.
+//
+// Warps: 0 TMA producer, 1 and 10 MMA issuers (1 owns tensor memory), 2-9 epilogue (two warps per
+// tensor-memory lane quadrant, each with half of the channels).
 #pragma once
 #include "conv_halo.cuh"
 
 namespace alpha {
 
-constexpr int kTapStackThreads = 320;   // warps: 0 TMA, 1 MMA, 2-9 epilogue
+constexpr int kTapStackThreads = 352;   // warps: 0 TMA, 1 and 10 MMA, 2-9 epilogue
 
 struct TapStackParams {
     float* out;          // [N][OH][OW][ldo]
@@ -107,7 +117,30 @@ __device__ __forceinline__ void tapstack_gather(uint32_t tcol, int BN, int FW, u
     }
 }
 
-template <int FW_T>
+// 4 x 4 transpose of 16-byte pieces among the four lanes 4k .. 4k + 3: on entry a[j] is piece j of this lane's
+// pixel, on return a[j] is piece (lane & 3) of the pixel of lane 4k + j.
+__device__ __forceinline__ void transpose4_lanes(float4 (&a)[4], int lane)
+{
+    const unsigned full = 0xffffffffu;
+    const bool b0 = lane & 1, b1 = lane & 2;
+#pragma unroll
+    for (int m = 0; m < 4; m += 2) {
+        // lanes with bit 0 clear give away their odd piece and receive the partner's even one, and vice versa
+        float4 s = b0 ? a[m] : a[m + 1];
+        s.x = __shfl_xor_sync(full, s.x, 1); s.y = __shfl_xor_sync(full, s.y, 1);
+        s.z = __shfl_xor_sync(full, s.z, 1); s.w = __shfl_xor_sync(full, s.w, 1);
+        if (b0) a[m] = s; else a[m + 1] = s;
+    }
+#pragma unroll
+    for (int m = 0; m < 2; ++m) {
+        float4 s = b1 ? a[m] : a[m + 2];
+        s.x = __shfl_xor_sync(full, s.x, 2); s.y = __shfl_xor_sync(full, s.y, 2);
+        s.z = __shfl_xor_sync(full, s.z, 2); s.w = __shfl_xor_sync(full, s.w, 2);
+        if (b1) a[m] = s; else a[m + 2] = s;
+    }
+}
+
+template <int FW_T, int FH_T>
 __global__ void __launch_bounds__(kTapStackThreads, 1)
     conv_tapstack_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                          const TapStackParams p)
@@ -118,8 +151,7 @@ __global__ void __launch_bounds__(kTapStackThreads, 1)
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     uint8_t* wres = smem;                                                   // resident W tiles
     uint8_t* patches = wres + p.w_bytes;                                    // ring of input patches
-    uint8_t* staging = patches + static_cast<size_t>(p.npb) * p.patch_bytes;   // 8 warps x 1 KB
-    uint64_t* bars = reinterpret_cast<uint64_t*>(staging + 8192);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(patches + static_cast<size_t>(p.npb) * p.patch_bytes);
     uint64_t* w_full = bars;
     uint64_t* patch_full = w_full + 1;
     uint64_t* patch_empty = patch_full + p.npb;
@@ -182,43 +214,66 @@ __global__ void __launch_bounds__(kTapStackThreads, 1)
             if (prof_on) p.prof[kProfProducerPatchWait] = w_patch;
         }
         __syncwarp();
-    } else if (warp == 1) {
+    } else if (warp == 1 || warp == 10) {
         if (lane == 0) {
-            // ---- MMA issuer ----
-            RingPos pp, ap;
+            // ---- MMA issuers: issuer `which` owns accumulator `which` and the tiles j = which, which + 2, ... of
+            // this CTA (tile j = blockIdx.x + j * gridDim.x); chunk c of tile j is load number j * kchunks + c ----
+            const uint32_t which = warp == 1 ? 0u : 1u;
+            const bool prof_me = prof_on && which == 0;
+            RingPos pp;
+            for (uint32_t i = 0; i < which * p.kchunks; ++i) pp.advance(p.npb);
+            uint32_t acc_phase = 0;
             unsigned long long w_patch = 0, w_b = 0, w_acc = 0;
             const long long t_begin = clock64();
-            bool ok = wait_prof(wfull_a, 0, prof_on, w_b);
+            bool ok = wait_prof(wfull_a, 0, prof_me, w_b);
             if (!ok) report(p.status, kStatusMmaTimeout);
             tc_fence_after_sync();
             const uint32_t dhi = smem_desc_hi(1024, kSwizzle128B);   // both operands: K-major rows of 128 B, 8-row groups 1024 B apart
             const uint32_t w_lo0 = smem_desc_lo(w_a, 16), patch_lo0 = smem_desc_lo(patches_a, 16);
             const uint32_t w_row16 = (p.FW * p.w_tile) >> 4;         // the FW tiles of one filter row
             const uint32_t patch16 = p.patch_bytes >> 4;
-            for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
-                if (!wait_prof(aempty_a + 8 * ap.idx, ap.phase ^ 1, prof_on, w_acc)) { report(p.status, kStatusMmaTimeout); ok = false; break; }
+            const uint32_t idesc = p.idesc;
+            const uint32_t d = tmem_base + which * p.accw;
+            const uint32_t my_full = afull_a + 8 * which, my_empty = aempty_a + 8 * which;
+            for (long long t = blockIdx.x + static_cast<long long>(which) * gridDim.x; t < p.total_tiles && ok; t += 2ll * gridDim.x) {
+                if (!wait_prof(my_empty, acc_phase ^ 1, prof_me, w_acc)) { report(p.status, kStatusMmaTimeout); ok = false; break; }
                 tc_fence_after_sync();
-                const uint32_t d = tmem_base + ap.idx * p.accw;
                 uint32_t acc = 0u;
                 uint32_t b_row = w_lo0;
                 for (int c = 0; c < p.kchunks && ok; ++c) {
-                    if (!wait_prof(pfull_a + 8 * pp.idx, pp.phase, prof_on, w_patch)) { report(p.status, kStatusMmaTimeout); ok = false; break; }
+                    if (!wait_prof(pfull_a + 8 * pp.idx, pp.phase, prof_me, w_patch)) { report(p.status, kStatusMmaTimeout); ok = false; break; }
                     tc_fence_after_sync();
                     uint32_t a_row = patch_lo0 + pp.idx * patch16;
-                    for (int fh = 0; fh < p.FH; ++fh, a_row += 256u, b_row += w_row16) {   // one patch row = 32 positions = 4096 B
+                    // one patch row = 32 positions = 4096 B = 256 descriptor units
+                    if constexpr (FH_T > 0) {
+                        // straight-line issue: a branch between two MMAs costs the issuing thread tens of clocks
+                        static_for<0, FH_T>([&](auto fh_) {
+                            constexpr uint32_t fh = decltype(fh_)::value;
+                            const uint32_t b_fh = b_row + fh * w_row16;
+                            static_for<0, 4>([&](auto kk_) {
+                                constexpr uint32_t kk = decltype(kk_)::value;
+                                mma_tf32_ss2_imm<fh * 256u + kk * 2u, kk * 2u>(d, a_row, dhi, b_fh, dhi, idesc, (fh == 0 && kk == 0) ? acc : 1u);
+                            });
+                        });
+                        acc = 1u;
+                        b_row += FH_T * w_row16;
+                    } else {
+                        for (int fh = 0; fh < p.FH; ++fh, a_row += 256u, b_row += w_row16) {
 #pragma unroll
-                        for (uint32_t kk = 0; kk < 4; ++kk) {
-                            mma_tf32_ss2(d, a_row + kk * 2u, dhi, b_row + kk * 2u, dhi, p.idesc, acc);
-                            acc = 1u;
+                            for (uint32_t kk = 0; kk < 4; ++kk) {
+                                mma_tf32_ss2(d, a_row + kk * 2u, dhi, b_row + kk * 2u, dhi, idesc, acc);
+                                acc = 1u;
+                            }
                         }
                     }
                     mma_commit_a(pempty_a + 8 * pp.idx);
                     pp.advance(p.npb);
                 }
-                mma_commit_a(afull_a + 8 * ap.idx);
-                ap.advance(2);
+                mma_commit_a(my_full);
+                acc_phase ^= 1u;
+                for (int i = 0; i < p.kchunks; ++i) pp.advance(p.npb);   // the other issuer's tile
             }
-            if (prof_on) {
+            if (prof_me) {
                 p.prof[kProfMmaPatchWait] = w_patch; p.prof[kProfMmaBWait] = w_b; p.prof[kProfMmaAccWait] = w_acc;
                 p.prof[kProfMmaTotal] = static_cast<unsigned long long>(clock64() - t_begin);
             }
@@ -230,7 +285,6 @@ __global__ void __launch_bounds__(kTapStackThreads, 1)
         const int quad = warp & 3, half = (warp - 2) >> 2;
         RingPos ap;
         const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
-        const uint32_t stage_w = smem_u32(staging) + (warp - 2) * 1024;
         unsigned long long w_acc = 0;
         const long long t_begin = clock64();
         for (int t = blockIdx.x; t < p.total_tiles; t += gridDim.x) {
@@ -253,31 +307,30 @@ __global__ void __launch_bounds__(kTapStackThreads, 1)
                     mbar_arrive_a(aempty_a + 8 * ap.idx);
                     released = true;
                 }
-                // per-warp transpose through 1 KB of shared memory, 8 channels at a time, so that a store
-                // instruction writes whole 32-byte sectors: 16-byte piece q of pixel x lives at piece q ^ ((x >> 2) & 1)
+                // bias and activation on this lane's pixel, then the lane transpose and the stores: slot j of lane
+                // 4k + i ends up with channels [4i, 4i + 4) of a 16-channel group of the pixel of lane 4k + j
+                const int li = lane & 3, px0 = lane & ~3;
 #pragma unroll
-                for (int rd = 0; rd < 4; ++rd) {
-                    const int ch = c0 + rd * 8;
+                for (int h = 0; h < 2; ++h) {
+                    const int ch = c0 + h * 16;
+                    float4 a[4];
 #pragma unroll
-                    for (int q = 0; q < 2; ++q) {
-                        float4 o = make_float4(__uint_as_float(y[rd * 8 + 4 * q]), __uint_as_float(y[rd * 8 + 4 * q + 1]),
-                                               __uint_as_float(y[rd * 8 + 4 * q + 2]), __uint_as_float(y[rd * 8 + 4 * q + 3]));
+                    for (int q = 0; q < 4; ++q) {
+                        a[q] = make_float4(__uint_as_float(y[h * 16 + 4 * q]), __uint_as_float(y[h * 16 + 4 * q + 1]),
+                                           __uint_as_float(y[h * 16 + 4 * q + 2]), __uint_as_float(y[h * 16 + 4 * q + 3]));
                         if (p.bias && ch + 4 * q < p.Ncols) {
                             const float4 b = *reinterpret_cast<const float4*>(p.bias + ch + 4 * q);
-                            o.x += b.x; o.y += b.y; o.z += b.z; o.w += b.w;
+                            a[q].x += b.x; a[q].y += b.y; a[q].z += b.z; a[q].w += b.w;
                         }
-                        if (p.act_on) leaky_relu4(o, p.act_k);
-                        st_shared_v4(stage_w + lane * 32 + ((q ^ ((lane >> 2) & 1)) << 4), o);
+                        if (p.act_on) leaky_relu4(a[q], p.act_k);
                     }
-                    __syncwarp();
+                    transpose4_lanes(a, lane);
 #pragma unroll
-                    for (int j = 0; j < 2; ++j) {
-                        const int px = j * 16 + (lane >> 1), q = lane & 1;
-                        const float4 o = ld_shared_v4(stage_w + px * 32 + ((q ^ ((px >> 2) & 1)) << 4));
-                        if (row_ok && px < p.CB && ow0 + px < p.OW && ch + 4 * q < p.Ncols)
-                            *reinterpret_cast<float4*>(orow + static_cast<size_t>(px) * p.ldo + ch + 4 * q) = o;
+                    for (int j = 0; j < 4; ++j) {
+                        const int px = px0 + j;
+                        if (row_ok && px < p.CB && ow0 + px < p.OW && ch + 4 * li < p.Ncols)
+                            *reinterpret_cast<float4*>(orow + static_cast<size_t>(px) * p.ldo + ch + 4 * li) = a[j];
                     }
-                    __syncwarp();
                 }
             }
             if (!released) {
