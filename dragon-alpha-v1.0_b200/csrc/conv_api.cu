@@ -617,6 +617,7 @@ struct IgemmPlan {
     // a stride phase of deltaX writes every oSH-th row and oSW-th column of an oNH x oNW image
     int oSH = 1, oSW = 1, oNH = 0, oNW = 0;
     bool force = false;              // take the halo kernel even when few tile pixels are real
+    int w_img_rows = 0;              // > 0: image n uses rows [n * w_img_rows, ...) of W (batched matrix products)
 };
 
 static int launch_igemm(DeviceCtx* c, const IgemmPlan& pl, int mode3x, cudaStream_t stream)
@@ -730,7 +731,7 @@ static int halo_ksplit(const IgemmPlan& pl, long long tiles, int kchunks, int sm
 {
     const bool dense_out = pl.oSH == 1 && pl.oSW == 1 && pl.oNH == 0 && pl.oNW == 0;
     const int taps = pl.FH * pl.FW;
-    if (!dense_out || !opt(OPT_SKINNY) || kchunks < 2 || 2 * tiles > sm_count || (long long)kchunks * taps < 16) return 1;
+    if (!dense_out || pl.w_img_rows || !opt(OPT_SKINNY) || kchunks < 2 || 2 * tiles > sm_count || (long long)kchunks * taps < 16) return 1;
     int ksplit = (int)(sm_count / tiles);
     if (ksplit > 16) ksplit = 16;
     if (ksplit > kchunks) ksplit = kchunks;
@@ -753,7 +754,7 @@ static HaloChoice plan_halo(const IgemmPlan& pl, int BN, int mode3x, int b_mn, i
     // small images: NI images stacked in one accumulator, each in a slot of SG = OH + FH - 1 rows
     const int SG = pl.oH + pl.FH - 1;
     int ni_max = 1;
-    if (SG <= 16 && opt(OPT_HALO_STACK)) ni_max = 1 + (16 - pl.oH) / SG;
+    if (SG <= 16 && opt(OPT_HALO_STACK) && !pl.w_img_rows) ni_max = 1 + (16 - pl.oH) / SG;
     // 3xTF32 with BN <= 128: the wide form (hi x [hi | lo] in one MMA of 2*BN columns, then lo x hi) needs
     // max(BN, 59) + max(BN / 2, 59) clocks per step instead of 3 * max(BN / 2, 59) and reads the A
     // operand twice instead of three times, at twice the tensor-memory columns per accumulator
@@ -1069,14 +1070,15 @@ static int launch_halo(DeviceCtx* c, const IgemmPlan& pl_in, int mode3x, cudaStr
     const bool pair_auto = mode3x ? pl.ncols % 128 == 0 : pl.ncols % 256 == 0;
     // few output tiles and a long reduction: the single-CTA kernel splits the reduction over the idle SMs
     bool skinny = false;
-    if (opt(OPT_SKINNY) && pl.oSH == 1 && pl.oSW == 1 && pl.oNH == 0 && pl.oNW == 0) {
+    if (opt(OPT_SKINNY) && !pl.w_img_rows && pl.oSH == 1 && pl.oSW == 1 && pl.oNH == 0 && pl.oNW == 0) {
         const int sg = pl.oH + pl.FH - 1;
         const int ni = (sg <= 16 && opt(OPT_HALO_STACK)) ? 1 + (16 - pl.oH) / sg : 1;
         const long long tiles128 = (long long)((pl.aN + ni - 1) / ni) * (ni > 1 ? 1 : (pl.oH + 15) / 16) * ((pl.oW + 7) / 8) *
                                    ((pl.ncols + 127) / 128);
         skinny = 2 * tiles128 <= sm_budget(c) && (long long)(pl.kdim / 32) * pl.FH * pl.FW >= 32;
     }
-    const bool try_pair = pair_env > 0 || (pair_env < 0 && pair_auto && tile_mode == 0);
+    // per-image weights: only the single-CTA kernel knows them (its W-tile loads add the image's first row)
+    const bool try_pair = !pl.w_img_rows && (pair_env > 0 || (pair_env < 0 && pair_auto && tile_mode == 0));
     if (try_pair && !skinny) {
         const int rc2 = launch_halo_pair(c, pl, mode3x, stream);
         if (rc2 != 1) return rc2;
@@ -1086,7 +1088,7 @@ static int launch_halo(DeviceCtx* c, const IgemmPlan& pl_in, int mode3x, cudaStr
     const long long flat_m = (long long)pl.aN * pl.aH * pl.aW;
     if (pl.FH == 1 && pl.FW == 1 && pl.pad_h == 0 && pl.pad_w == 0 && pl.oSH == 1 && pl.oSW == 1 && pl.oNH == 0 &&
         pl.oNW == 0 && pl.oH == pl.aH && pl.oW == pl.aW && flat_m % 8 == 0 && flat_m / 8 <= 2147483647LL &&
-        opt(OPT_HALO_FLAT)) {
+        opt(OPT_HALO_FLAT) && !pl.w_img_rows) {
         pl.aN = 1; pl.aW = 8; pl.aH = (int)(flat_m / 8);
         pl.oH = pl.aH; pl.oW = 8;
     }
@@ -1103,7 +1105,7 @@ static int launch_halo(DeviceCtx* c, const IgemmPlan& pl_in, int mode3x, cudaStr
     }
     {
         // plain TF32 with few output channels: one MMA per filter row where the model says it is faster
-        const TapStackPlan ts = plan_tapstack(pl, mode3x, sm_budget(c));
+        const TapStackPlan ts = pl.w_img_rows ? TapStackPlan{} : plan_tapstack(pl, mode3x, sm_budget(c));
         if (ts.valid && (opt(OPT_HALO_TAPSTACK) == 2 || !ch.valid || ts.cost < 0.8 * ch.cost)) return launch_tapstack(c, pl, ts, stream);
     }
     if (!ch.valid || (tile_mode == 0 && ch.eff < 0.6 && !pl.force)) {
@@ -1133,6 +1135,7 @@ static int launch_halo(DeviceCtx* c, const IgemmPlan& pl_in, int mode3x, cudaStr
     p.total_tiles = (int)total;
     p.npb = ch.npb; p.sb = ch.sb; p.acc_bufs = ch.acc_bufs;
     p.mode3x = ch.wide ? 2 : mode3x; p.b_mn = pl.b_mn; p.flip = pl.flip;
+    p.w_img_rows = pl.w_img_rows;
     // plain TF32 is bound by one thread's MMA issue interval, not by the tensor pipe: two issuing
     // threads alternate over the ring's stages (the ring then needs an even number of slots).
     // The 3xTF32 forms run N >= 128 per MMA, are pipe-bound and keep one issuer (and with it a
@@ -1464,18 +1467,21 @@ static void dw_halo_set_attr()
 
 // Returns 1 when the shape is left to the split-K im2col kernel, 0 on launch, < 0 on error.
 // deltaB != nullptr: the kernel also sums the columns of deltaY (bias gradient); *bias_fused tells whether it did.
+// per_image: dW receives N separate results, dW[n] = the sum over the pixels of image n only (batched matrix
+// products C[n] = A[n]^T * B[n]); every CTA column of the grid then owns one image and writes its result in place.
 static int launch_dw_halo(DeviceCtx* c, const AlphaConvShape* s_in, const float* X, const float* dY, float* dW,
-                          int mode3x, cudaStream_t stream, float* deltaB = nullptr, bool* bias_fused = nullptr)
+                          int mode3x, cudaStream_t stream, float* deltaB = nullptr, bool* bias_fused = nullptr,
+                          bool per_image = false)
 {
     if (bias_fused) *bias_fused = false;
-    if (opt(OPT_CONV_DW) == 1) return 1;
+    if (opt(OPT_CONV_DW) == 1 && !per_image) return 1;
     AlphaConvShape flat = *s_in;
     const AlphaConvShape* s = s_in;
     // a 1x1 deltaW sums over pixels in any order: one image of 16 columns fills every pixel tile
     const long long flat_m = (long long)s_in->N * s_in->OH * s_in->OW;
     if (s_in->FH == 1 && s_in->FW == 1 && s_in->ph == 0 && s_in->pw == 0 && s_in->sh == 1 && s_in->sw == 1 &&
         s_in->IH == s_in->OH && s_in->IW == s_in->OW && flat_m % 16 == 0 && flat_m / 16 <= 2147483647LL &&
-        opt(OPT_HALO_FLAT)) {
+        opt(OPT_HALO_FLAT) && !per_image) {
         flat.N = 1; flat.OW = flat.IW = 16; flat.OH = flat.IH = (int)(flat_m / 16);
         s = &flat;
     }
@@ -1490,7 +1496,7 @@ static int launch_dw_halo(DeviceCtx* c, const AlphaConvShape* s_in, const float*
     // An MMA of N columns costs max(N / 2, 59) clocks whatever its height, so the stacked form wins
     // where 128 output channels or 64 input channels would be half empty.
     bool stacked = false;
-    if (mode3x) {
+    if (mode3x && !per_image) {   // the stacked form leaves two partial planes to add
         int NTq = 0;
         for (int cand = 128; cand >= 32; cand >>= 1)
             if (s->IC % cand == 0 && s->FW * 2 * cand <= 512) { NTq = cand; break; }
@@ -1506,7 +1512,7 @@ static int launch_dw_halo(DeviceCtx* c, const AlphaConvShape* s_in, const float*
     }
     // plain TF32 with at most 64 output channels: two half tiles side by side ("diagonal" form)
     bool diag = false;
-    if (!mode3x && s->OC <= 64 && s->OH >= 2 && opt(OPT_DW_DIAG)) {
+    if (!mode3x && !per_image && s->OC <= 64 && s->OH >= 2 && opt(OPT_DW_DIAG)) {
         int NTd = 0;
         for (int cand = 128; cand >= 32; cand >>= 1)
             if (s->IC % cand == 0 && s->FW * 2 * cand <= 512) { NTd = cand; break; }
@@ -1552,6 +1558,11 @@ static int launch_dw_halo(DeviceCtx* c, const AlphaConvShape* s_in, const float*
     int parts = sm_budget(c) / groups;
     if (parts < 1) parts = 1;
     if (parts > p.total_tiles) parts = p.total_tiles;
+    if (per_image) {
+        if (s->N > 65535 * 32 || deltaB) return 1;
+        parts = s->N;
+        p.per_image = 1;
+    }
     p.parts = parts;
     p.stages = stages; p.mode3x = diag ? 3 : (stacked ? 2 : mode3x);
     p.idesc = make_idesc_tf32(kBM, stacked ? 2 * NT : NT, true, true);
@@ -1560,7 +1571,7 @@ static int launch_dw_halo(DeviceCtx* c, const AlphaConvShape* s_in, const float*
     p.x_tx = (uint32_t)R * PW * 128; p.x_blk = (p.x_tx + 1023) & ~1023u;
     const size_t sizeW = (size_t)s->OC * s->FH * s->FW * s->IC;
     float* ws = nullptr;
-    if (parts * nsub > 1) {
+    if (parts * nsub > 1 && !per_image) {
         int rc = get_workspace(c, stream, sizeW * parts * nsub * sizeof(float), &ws);
         if (rc) return rc;
         p.out = ws;
@@ -1618,7 +1629,7 @@ static int launch_dw_halo(DeviceCtx* c, const AlphaConvShape* s_in, const float*
     snprintf(g_plan, sizeof(g_plan), "dw_halo%s NT=%d R=%d CW=%d stages=%d parts=%d groups=%d", diag ? " diagonal" : (stacked ? " stacked" : ""), NT, R, CW,
              stages, parts, groups);
     rc = check_launch("conv_dw_halo_kernel");
-    if (rc) return rc;
+    if (rc || per_image) return rc;
     if (parts * nsub > 1) {
         const size_t n4 = sizeW / 4;
         if (!t_dry) launch_dw_reduce(ws, sizeW, parts * nsub, dW, n4, 0, stream, opt(OPT_DW_LANES));
@@ -1635,6 +1646,41 @@ static int launch_dw_halo(DeviceCtx* c, const AlphaConvShape* s_in, const float*
         if (bias_fused) *bias_fused = true;
     }
     return rc;
+}
+
+// Batched matrix products (the reference's Cuda_batchMatMul) on the convolution kernels: entry b of the batch is
+// image b of a 1x1 convolution that has its own weights.  Dense matrices (row pitch = row length).  Returns 1 when
+// the shape is outside what the tensor kernels take; the caller then runs its plain fp32 kernel.
+//   form 0: C[b][N][M] = A[b][N][K] * B[b][K][M]      deltaX form, B read in place as an MN-major operand
+//   form 1: C[b][N][M] = A[b][K][N]^T * B[b][K][M]    deltaW form, one CTA column per batch entry
+//   form 2: C[b][N][M] = A[b][N][K] * B[b][M][K]^T    forward form
+int launch_bmm_tensor(int form, const float* A, const float* B, float* C, int Batch, int N, int M, int K, cudaStream_t stream)
+{
+    if (cur_algo() == ALPHA_ALGO_SIMT) return 1;
+    DeviceCtx* c;
+    int rc = get_ctx(&c);
+    if (rc) return rc;
+    ws_begin(c, stream);
+    const int mode3x = cur_mode3x();
+    if (form == 1) {
+        // the K rows of A[b] and B[b] are the pixels of image b (16 per image row), OC = N, IC = M
+        if (M % 32 != 0 || K % 16 != 0 || N % 4 != 0) return 1;
+        AlphaConvShape s{};
+        s.N = Batch; s.IH = s.OH = K / 16; s.IW = s.OW = 16; s.IC = M; s.OC = N;
+        s.FH = s.FW = 1; s.sh = s.sw = 1; s.ph = s.pw = 0;
+        return launch_dw_halo(c, &s, B, A, C, mode3x, stream, nullptr, nullptr, true);
+    }
+    if (K % 32 != 0 || N % 4 != 0 || M % 4 != 0) return 1;
+    const int w = N % 8 == 0 ? 8 : 4;   // the N rows of A[b] as an image of w columns
+    IgemmPlan pl{};
+    pl.act = A; pl.aN = Batch; pl.aH = N / w; pl.aW = w; pl.aC = K;
+    pl.FH = 1; pl.FW = 1; pl.sh = 1; pl.sw = 1; pl.pad_h = 0; pl.pad_w = 0;
+    pl.out = C; pl.oH = N / w; pl.oW = w; pl.ncols = M;
+    pl.W = B; pl.bias = nullptr; pl.kdim = K; pl.flip = false; pl.force = true;
+    if (form == 2) { pl.wOC = Batch * M; pl.wIC = K; pl.b_mn = false; pl.w_img_rows = M; }
+    else { pl.wOC = Batch * K; pl.wIC = M; pl.b_mn = true; pl.w_img_rows = K; }
+    if ((long long)Batch * pl.w_img_rows > 2147483647LL) return 1;
+    return launch_halo(c, pl, mode3x, stream);
 }
 
 // deltaW += sum of `part` split-K buffers of sizeW floats each (the reference's buf_summary).

@@ -57,6 +57,7 @@ struct DwHaloParams {
     int row_blocks, col_blocks, tiles_per_img;
     int total_tiles;       // N * tiles_per_img
     int parts;             // CTAs per accumulator group = gridDim.x
+    int per_image;         // 1: part i sums exactly the tiles of image i (parts == N) and `out` receives N separate results
     int stages, mode3x;    // mode3x: 0 plain TF32, 1 three MMAs, 2 stacked planes, 3 diagonal (TF32, two half tiles)
     uint32_t idesc, tmem_cols;
     uint32_t dy_blk, x_blk;   // bytes of one 32-channel block of the deltaY / X tile (multiples of 1024)
@@ -188,6 +189,11 @@ __global__ void __launch_bounds__(kDwHaloThreads, 1)
     const int CW = kStatic ? CW_T : p.CW;
     const int PW = CW + FW - 1;
     const bool prof_on = p.prof != nullptr && blockIdx.x == 0 && blockIdx.y == 0;
+    // tiles of this CTA: every gridDim.x-th one, or (per_image) exactly the tiles of image blockIdx.x, whose sum
+    // then is that image's own result (batched matrix products) and goes straight to the output
+    const int t_first = p.per_image ? static_cast<int>(blockIdx.x) * p.tiles_per_img : static_cast<int>(blockIdx.x);
+    const int t_last = p.per_image ? t_first + p.tiles_per_img : p.total_tiles;
+    const int t_step = p.per_image ? 1 : static_cast<int>(gridDim.x);
     const long long t_kernel = clock64();
     const unsigned long long ns_kernel = prof_on ? globaltimer_ns() : 0ull;
 
@@ -196,7 +202,7 @@ __global__ void __launch_bounds__(kDwHaloThreads, 1)
             // ---- TMA producer ----
             RingPos rp;
             unsigned long long w_empty = 0;
-            for (int t = blockIdx.x; t < p.total_tiles; t += gridDim.x) {
+            for (int t = t_first; t < t_last; t += t_step) {
                 const int n = t / p.tiles_per_img;
                 const int r = t - n * p.tiles_per_img;
                 const int rb = r / p.col_blocks, cb = r - rb * p.col_blocks;
@@ -233,7 +239,7 @@ __global__ void __launch_bounds__(kDwHaloThreads, 1)
             uint32_t acc = 0u;  // the first MMA into each accumulator overwrites it
             unsigned long long w_in = 0, w_issue = 0, w_commit = 0;
             const long long t_begin = clock64();
-            for (int t = blockIdx.x; t < p.total_tiles; t += gridDim.x) {
+            for (int t = t_first; t < t_last; t += t_step) {
                 if (!wait_prof(wait_a + 8 * rp.idx, rp.phase, prof_on, w_in)) { report(p.status, kStatusMmaTimeout); break; }
                 tc_fence_after_sync();
                 const long long t_i0 = prof_on ? clock64() : 0;
@@ -273,7 +279,7 @@ __global__ void __launch_bounds__(kDwHaloThreads, 1)
             unsigned long long w_full = 0;
             const long long t_begin = clock64();
             const int halves = diag ? 2 : 1;
-            for (int t = blockIdx.x; t < p.total_tiles; t += gridDim.x) {
+            for (int t = t_first; t < t_last; t += t_step) {
                 if (!wait_prof(full_a + 8 * rp.idx, rp.phase, prof_on, w_full)) { report(p.status, kStatusSplitTimeout); ok = false; break; }
                 uint8_t* hi = smem + static_cast<size_t>(rp.idx) * stage_bytes;
                 if (do_bias) {

@@ -73,6 +73,8 @@ struct HaloParams {
     int dual;                 // 1: two MMA-issuing threads take alternate W-tile stages (sb is even)
     int split_b;              // 3xTF32: 1 = only the hi plane of every W tile is loaded and the split warps form its lo
                               // plane in shared memory (1x1 products, whose W traffic from L2 is what binds them)
+    int w_img_rows;           // > 0: every image has its own W (batched matrix products); rows of W per image, added to the
+                              // row coordinate of every W tile (stacked images and split-K are then off)
     int ksplit, cps;          // split-K: every tile is computed as ksplit partial sums over cps reduction chunks each;
                               // partial sp of image n is stored as image sp * N + n of the output map
     uint32_t idesc, idesc_wide, tmem_cols;   // idesc_wide: N = 2 * BN
@@ -294,6 +296,7 @@ __global__ void __launch_bounds__(kHaloThreads2, 1)
                 const int h0 = rb * 16 * p.JH - p.pad_h, w0 = cb * 8 * p.JW - p.pad_w;
                 const int n = nb * p.NI;
                 const int oc0 = tn * p.BN;
+                const int wrow0 = n * p.w_img_rows;   // first W row of this image's own weights (0: shared weights)
                 for (int c = tp.c0; c < tp.c1 && ok; ++c) {
                     if (!wait_prof(pempty_a + 8 * pp.idx, pp.phase ^ 1, prof_on, w_patch)) { report(p.status, kStatusProducerTimeout); ok = false; break; }
                     mbar_arrive_expect_tx_a(pfull_a + 8 * pp.idx, p.patch_tx);
@@ -307,13 +310,13 @@ __global__ void __launch_bounds__(kHaloThreads2, 1)
                             const int tap = st * tps + q;
                             const uint32_t b_dst = bring_a + bp.idx * b_stride + q * b_tile;
                             if (!p.b_mn) {
-                                tma_load_3d_a(b_dst, &tmB, bar, c * 32, tap, oc0);
-                                if (p.mode3x && !p.split_b) tma_load_3d_a(b_dst + p.b_bytes, &tmBlo, bar, c * 32, tap, oc0);
+                                tma_load_3d_a(b_dst, &tmB, bar, c * 32, tap, oc0 + wrow0);
+                                if (p.mode3x && !p.split_b) tma_load_3d_a(b_dst + p.b_bytes, &tmBlo, bar, c * 32, tap, oc0 + wrow0);
                             } else {
                                 const int tapw = p.flip ? (taps - 1 - tap) : tap;
                                 for (int j = 0; j < p.BN / 32; ++j) {
-                                    tma_load_3d_a(b_dst + j * 4096, &tmB, bar, oc0 + j * 32, tapw, c * 32);
-                                    if (p.mode3x) tma_load_3d_a(b_dst + p.b_bytes + j * 4096, &tmBlo, bar, oc0 + j * 32, tapw, c * 32);
+                                    tma_load_3d_a(b_dst + j * 4096, &tmB, bar, oc0 + j * 32, tapw, c * 32 + wrow0);
+                                    if (p.mode3x) tma_load_3d_a(b_dst + p.b_bytes + j * 4096, &tmBlo, bar, oc0 + j * 32, tapw, c * 32 + wrow0);
                                 }
                             }
                         }

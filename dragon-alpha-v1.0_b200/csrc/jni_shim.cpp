@@ -1,6 +1,6 @@
 // JNI entry points of the native classes this library replaces.  The exported names and
 // signatures are those of the reference's shims (Cuda_conv3D/A.cu:14-244, Cuda_dconv3D_deltaX/A.cu:14-325,
-// Cuda_dconv3D_deltaW/A.cu:16-154, Cuda_matMul/A.cu:18-120): each unpacks the Java stream array and forwards to the
+// Cuda_dconv3D_deltaW/A.cu:16-154, Cuda_matMul/A.cu:18-120, Cuda_batchMatMul/A.cu:17-135): each unpacks the Java stream array and forwards to the
 // alpha_Cuda_* function of the same name.  A non-zero status becomes a pending
 // z.dragon.engine.cuda.impl.CudaException carrying the library's error text (the reference looks up
 // the stale class path z/jcuda/exception/CudaException, Cuda_conv3D/JNITool.cuh:16).
@@ -362,6 +362,48 @@ JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1matMul_matMulT2
 {
     Streams st = get_streams(env, streamArray, length);
     raise(env, alpha_Cuda_matMul_matMulT2(st.v, st.n, fp(dA_address), fp(dB_address), fp(dC_address), N, M, K));
+}
+
+// ---- Cuda_batchMatMul (src/cu32_src/Cuda_batch_matMul/Cuda_batchMatMul/A.cu:17-135) -------------------
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1batchMatMul_batchMatMul(JNIEnv* env, jclass,
+    jlongArray streamArray, jint length, jlong dA_address, jlong dB_address, jlong dC_address, jint Batch, jint N, jint M,
+    jint BK, jint AK)
+{
+    Streams st = get_streams(env, streamArray, length);
+    raise(env, alpha_Cuda_batchMatMul_batchMatMul(st.v, st.n, fp(dA_address), fp(dB_address), fp(dC_address), Batch, N, M, BK, AK));
+}
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1batchMatMul_batchMatMul_1texture(JNIEnv* env, jclass,
+    jlongArray streamArray, jint length, jlong dA_address, jlong dB_address, jlong dC_address, jint Batch, jint N, jint M,
+    jint BK, jint AK)
+{
+    Streams st = get_streams(env, streamArray, length);
+    raise(env, alpha_Cuda_batchMatMul_batchMatMul_texture(st.v, st.n, fp(dA_address), fp(dB_address), fp(dC_address), Batch, N, M, BK, AK));
+}
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1batchMatMul_batchMatMulT1(JNIEnv* env, jclass,
+    jlongArray streamArray, jint length, jlong dA_address, jlong dB_address, jlong dC_address, jint Batch, jint CN, jint AN,
+    jint M, jint K)
+{
+    Streams st = get_streams(env, streamArray, length);
+    raise(env, alpha_Cuda_batchMatMul_batchMatMulT1(st.v, st.n, fp(dA_address), fp(dB_address), fp(dC_address), Batch, CN, AN, M, K));
+}
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1batchMatMul_batchMatMulT2(JNIEnv* env, jclass,
+    jlongArray streamArray, jint length, jlong dA_address, jlong dB_address, jlong dC_address, jint Batch, jint N, jint CM,
+    jint BM, jint K)
+{
+    Streams st = get_streams(env, streamArray, length);
+    raise(env, alpha_Cuda_batchMatMul_batchMatMulT2(st.v, st.n, fp(dA_address), fp(dB_address), fp(dC_address), Batch, N, CM, BM, K));
+}
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1batchMatMul_batchMatMulT2_1texture(JNIEnv* env, jclass,
+    jlongArray streamArray, jint length, jlong dA_address, jlong dB_address, jlong dC_address, jint Batch, jint N, jint CM,
+    jint BM, jint K)
+{
+    Streams st = get_streams(env, streamArray, length);
+    raise(env, alpha_Cuda_batchMatMul_batchMatMulT2_texture(st.v, st.n, fp(dA_address), fp(dB_address), fp(dC_address), Batch, N, CM, BM, K));
 }
 
 }  // extern "C"

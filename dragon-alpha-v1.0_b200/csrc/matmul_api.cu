@@ -4,12 +4,16 @@
 //   C = A * B    (matMul)    deltaX:   dX[row][ic] = sum_oc dY[row][oc] * W[oc][ic]
 //   C = A^T * B  (matMulT1)  deltaW:   dW[oc][ic] = sum_row dY[row][oc] * X[row][ic]
 // so each form runs the tensor-core kernel (and every fallback) of the contraction it maps to.
+// The batched products behind Cuda_batchMatMul run the same kernels with one image, and one set of weights, per
+// batch entry; shapes those kernels do not take (reduction lengths that are not a multiple of 32, padded row
+// pitches) run a plain fp32 kernel.
 #include "../../include/alpha_conv_b200.h"
 #include "host_common.h"
 
 namespace alpha {
 int launch_buf_summary(cudaStream_t stream, const float* buf, float* deltaW, int part, size_t sizeW);
 void set_caller_scratch(void* ptr, size_t bytes);
+int launch_bmm_tensor(int form, const float* A, const float* B, float* C, int Batch, int N, int M, int K, cudaStream_t stream);
 }
 using namespace alpha;
 
@@ -40,6 +44,46 @@ AlphaConvShape rows_as_pixels(long long rows, int IC, int OC)
     s.IC = IC; s.OC = OC; s.FH = s.FW = 1; s.sh = s.sw = 1; s.ph = s.pw = 0;
     return s;
 }
+
+// C[b][i][j] = sum over k < K of a(b, i, k) * b(b, k, j) for i < N, j < M, every matrix with its own strides
+// (element (i, k) of A[b] at A[b * a_b + i * a_i + k * a_k], and so on): the three batched forms with any row
+// pitch.  One thread per output element, k in ascending order, fp32 FMA - the arithmetic of the reference's
+// kernels (Cuda_batch_matMul/Cuda_batchMatMul/batchMatMul_kernel.cuh), results do not depend on the launch.
+struct BmmStrides { long long a_b, b_b, c_b; int a_i, a_k, b_k, b_j, c_i; };
+__global__ void bmm_simt_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ C,
+                                int N, int M, int K, BmmStrides st)
+{
+    const int j = blockIdx.x * 32 + (threadIdx.x & 31), i = blockIdx.y * 8 + (threadIdx.x >> 5);
+    if (i >= N || j >= M) return;
+    const float* a = A + static_cast<size_t>(blockIdx.z) * st.a_b + static_cast<size_t>(i) * st.a_i;
+    const float* b = B + static_cast<size_t>(blockIdx.z) * st.b_b + static_cast<size_t>(j) * st.b_j;
+    float acc = 0.f;
+    for (int k = 0; k < K; ++k) acc = fmaf(a[static_cast<size_t>(k) * st.a_k], b[static_cast<size_t>(k) * st.b_k], acc);
+    C[static_cast<size_t>(blockIdx.z) * st.c_b + static_cast<size_t>(i) * st.c_i + j] = acc;
+}
+
+int launch_bmm_simt(const float* A, const float* B, float* C, int Batch, int N, int M, int K, const BmmStrides& st,
+                    alpha_stream_t stream)
+{
+    for (int b0 = 0; b0 < Batch; b0 += 65535) {   // gridDim.z limit
+        const int nb = Batch - b0 < 65535 ? Batch - b0 : 65535;
+        dim3 grid((M + 31) / 32, (N + 7) / 8, nb);
+        bmm_simt_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(A + b0 * st.a_b, B + b0 * st.b_b, C + b0 * st.c_b, N, M, K, st);
+    }
+    note_launch("bmm_simt");
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(ALPHA_E_CUDA, "bmm_simt_kernel launch failed: %s", cudaGetErrorString(e));
+    return ALPHA_OK;
+}
+
+int check_batch(const char* what, const void* A, const void* B, const void* C, int Batch, int d0, int d1, int d2, int d3)
+{
+    if (!A || !B || !C) return fail(ALPHA_E_ARG, "%s: null matrix pointer", what);
+    if (Batch <= 0 || d0 <= 0 || d1 <= 0 || d2 <= 0 || d3 <= 0)
+        return fail(ALPHA_E_ARG, "%s: non-positive dimension (Batch=%d, %d %d %d %d)", what, Batch, d0, d1, d2, d3);
+    return ALPHA_OK;
+}
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 int check_dims(const char* what, const void* A, const void* B, const void* C, int N, int M, int K)
 {
@@ -93,6 +137,75 @@ int alpha_matMulT2(const float* A, const float* B, const float* bias, float* C, 
     // A[N][K] is X[row][IC = K]; B[M][K] is W[OC = M][IC = K]; C[N][M] is Y; the bias is fused into the epilogue
     AlphaConvShape s = rows_as_pixels(N, K, M);
     return alpha_conv3d_forward(&s, A, B, bias, C, stream);
+}
+
+// ---- batched products (src/cu32_src/Cuda_batch_matMul/Cuda_batchMatMul/test.cuh:95-140 states the three forms) ----
+
+// C[b][N][M] = A[b][N][AK] (first BK columns) * B[b][BK][M]
+int alpha_batchMatMul(const float* A, const float* B, float* C, int Batch, int N, int M, int BK, int AK, alpha_stream_t stream)
+{
+    int rc = check_batch("batchMatMul", A, B, C, Batch, N, M, BK, AK);
+    if (rc) return rc;
+    if (AK < BK) return fail(ALPHA_E_ARG, "batchMatMul: row pitch of A (AK=%d) below the reduction length (BK=%d)", AK, BK);
+    if (AK == BK && aligned16(A) && aligned16(B) && aligned16(C)) {
+        rc = launch_bmm_tensor(0, A, B, C, Batch, N, M, BK, static_cast<cudaStream_t>(stream));
+        if (rc != 1) return rc;
+    }
+    const BmmStrides st{(long long)N * AK, (long long)BK * M, (long long)N * M, AK, 1, M, 1, M};
+    return launch_bmm_simt(A, B, C, Batch, N, M, BK, st, stream);
+}
+
+// C[b][CN][M] = A[b][K][AN]^T (first CN columns) * B[b][K][M]
+int alpha_batchMatMulT1(const float* A, const float* B, float* C, int Batch, int CN, int AN, int M, int K, alpha_stream_t stream)
+{
+    int rc = check_batch("batchMatMulT1", A, B, C, Batch, CN, AN, M, K);
+    if (rc) return rc;
+    if (AN < CN) return fail(ALPHA_E_ARG, "batchMatMulT1: row pitch of A (AN=%d) below the rows of C (CN=%d)", AN, CN);
+    if (AN == CN && aligned16(A) && aligned16(B) && aligned16(C)) {
+        rc = launch_bmm_tensor(1, A, B, C, Batch, CN, M, K, static_cast<cudaStream_t>(stream));
+        if (rc != 1) return rc;
+    }
+    const BmmStrides st{(long long)K * AN, (long long)K * M, (long long)CN * M, 1, AN, M, 1, M};
+    return launch_bmm_simt(A, B, C, Batch, CN, M, K, st, stream);
+}
+
+// C[b][N][CM] (first BM columns) = A[b][N][K] * B[b][BM][K]^T
+int alpha_batchMatMulT2(const float* A, const float* B, float* C, int Batch, int N, int CM, int BM, int K, alpha_stream_t stream)
+{
+    int rc = check_batch("batchMatMulT2", A, B, C, Batch, N, CM, BM, K);
+    if (rc) return rc;
+    if (CM < BM) return fail(ALPHA_E_ARG, "batchMatMulT2: row pitch of C (CM=%d) below its columns (BM=%d)", CM, BM);
+    if (CM == BM && aligned16(A) && aligned16(B) && aligned16(C)) {
+        rc = launch_bmm_tensor(2, A, B, C, Batch, N, BM, K, static_cast<cudaStream_t>(stream));
+        if (rc != 1) return rc;
+    }
+    const BmmStrides st{(long long)N * K, (long long)BM * K, (long long)N * CM, K, 1, 1, K, CM};
+    return launch_bmm_simt(A, B, C, Batch, N, BM, K, st, stream);
+}
+
+// ---- Cuda_batchMatMul natives (src/cu32_src/Cuda_batch_matMul/Cuda_batchMatMul/A.cu:17-135) -------------
+int alpha_Cuda_batchMatMul_batchMatMul(const int64_t* streams, int length, float* A, float* B, float* C, int Batch, int N, int M, int BK, int AK)
+{
+    if (!streams || length < 1) return fail(ALPHA_E_ARG, "empty stream array");
+    return alpha_batchMatMul(A, B, C, Batch, N, M, BK, AK, first_stream(streams, length));
+}
+int alpha_Cuda_batchMatMul_batchMatMul_texture(const int64_t* streams, int length, float* A, float* B, float* C, int Batch, int N, int M, int BK, int AK)
+{
+    return alpha_Cuda_batchMatMul_batchMatMul(streams, length, A, B, C, Batch, N, M, BK, AK);
+}
+int alpha_Cuda_batchMatMul_batchMatMulT1(const int64_t* streams, int length, float* A, float* B, float* C, int Batch, int CN, int AN, int M, int K)
+{
+    if (!streams || length < 1) return fail(ALPHA_E_ARG, "empty stream array");
+    return alpha_batchMatMulT1(A, B, C, Batch, CN, AN, M, K, first_stream(streams, length));
+}
+int alpha_Cuda_batchMatMul_batchMatMulT2(const int64_t* streams, int length, float* A, float* B, float* C, int Batch, int N, int CM, int BM, int K)
+{
+    if (!streams || length < 1) return fail(ALPHA_E_ARG, "empty stream array");
+    return alpha_batchMatMulT2(A, B, C, Batch, N, CM, BM, K, first_stream(streams, length));
+}
+int alpha_Cuda_batchMatMul_batchMatMulT2_texture(const int64_t* streams, int length, float* A, float* B, float* C, int Batch, int N, int CM, int BM, int K)
+{
+    return alpha_Cuda_batchMatMul_batchMatMulT2(streams, length, A, B, C, Batch, N, CM, BM, K);
 }
 
 // ---- Cuda_matMul natives (src/cu32_src/Cuda_matMul/Cuda_matMul/A.cu:18-120) --------------------------
@@ -156,6 +269,20 @@ int alpha_engine_matMulT1(float* C, const float* A, const float* B, int N, int M
 int alpha_engine_matMulT2(float* C, const float* A, const float* B, int N, int M, int K, alpha_stream_t stream)
 {
     return alpha_matMulT2(A, B, nullptr, C, N, M, K, stream);
+}
+
+// CudaFloat32EngineBase.java:1256-1318
+int alpha_engine_batchMatMul(float* C, const float* A, const float* B, int Batch, int N, int M, int BK, int AK, alpha_stream_t stream)
+{
+    return alpha_batchMatMul(A, B, C, Batch, N, M, BK, AK, stream);
+}
+int alpha_engine_batchMatMulT1(float* C, const float* A, const float* B, int Batch, int CN, int AN, int M, int K, alpha_stream_t stream)
+{
+    return alpha_batchMatMulT1(A, B, C, Batch, CN, AN, M, K, stream);
+}
+int alpha_engine_batchMatMulT2(float* C, const float* A, const float* B, int Batch, int N, int CM, int BM, int K, alpha_stream_t stream)
+{
+    return alpha_batchMatMulT2(A, B, C, Batch, N, CM, BM, K, stream);
 }
 
 }  // extern "C"

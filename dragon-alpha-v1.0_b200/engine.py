@@ -244,6 +244,24 @@ class CudaFloat32EngineBase:
         a = self._addr
         self._mm(self._lib.alpha_engine_matMulT2, a(C_address), a(A_address), a(B_address), N, M, K, _stream(self._stream))
 
+    def batchMatMul(self, C_address, A_address, B_address, Batch, N, M, BK, AK):
+        """C[b] = A[b][N, AK](:, :BK) * B[b][BK, M] (CudaFloat32EngineBase.batchMatMul, :1256-1272)."""
+        a = self._addr
+        self._mm(self._lib.alpha_engine_batchMatMul, a(C_address), a(A_address), a(B_address), Batch, N, M, BK, AK,
+                 _stream(self._stream))
+
+    def batchMatMulT1(self, C_address, A_address, B_address, Batch, CN, AN, M, K):
+        """C[b][CN, M] = (A[b][K, AN](:, :CN))^T * B[b][K, M] (CudaFloat32EngineBase.batchMatMulT1, :1277-1287)."""
+        a = self._addr
+        self._mm(self._lib.alpha_engine_batchMatMulT1, a(C_address), a(A_address), a(B_address), Batch, CN, AN, M, K,
+                 _stream(self._stream))
+
+    def batchMatMulT2(self, C_address, A_address, B_address, Batch, N, CM, BM, K):
+        """C[b][N, CM](:, :BM) = A[b][N, K] * B[b][BM, K]^T (CudaFloat32EngineBase.batchMatMulT2, :1298-1318)."""
+        a = self._addr
+        self._mm(self._lib.alpha_engine_batchMatMulT2, a(C_address), a(A_address), a(B_address), Batch, N, CM, BM, K,
+                 _stream(self._stream))
+
 
 def _pad4(n):
     return (n + 3) & ~3
@@ -413,6 +431,39 @@ class Engine:
         C = torch.empty((Ap.shape[0], Bp.shape[0]), dtype=torch.float32, device=A.device)
         self.base.matMulT2(C, Ap, Bp, Ap.shape[0], Bp.shape[0], Ap.shape[1])
         return C[:N, :M]
+
+    # Batched products with the engine's memory rule (only the last dimension of a tensor is padded to a multiple
+    # of 4) and EngineCore's argument mapping (EngineCore.java:579-623): the row pitch and the logical row length
+    # go down separately.  The batch itself is not padded here (the reference rounds it up over zero matrices).
+    def batchMatMul(self, A, B):
+        """C[b] = A[b] * B[b]; A [Batch, N, K], B [Batch, K, M]."""
+        (Bt, N, K), (Bt2, K2, M) = A.shape, B.shape
+        if Bt != Bt2 or K != K2:
+            raise ValueError("batchMatMul: A %s against B %s" % (tuple(A.shape), tuple(B.shape)))
+        Ap, Bp = _pad_last(A, _pad4(K)), _pad_last(B, _pad4(M))
+        C = torch.zeros((Bt, N, _pad4(M)), dtype=torch.float32, device=A.device)
+        self.base.batchMatMul(C, Ap, Bp, Bt, N, _pad4(M), K, _pad4(K))
+        return C[..., :M]
+
+    def batchMatMulT1(self, A, B):
+        """C[b] = A[b]^T * B[b]; A [Batch, K, N], B [Batch, K, M]."""
+        (Bt, K, N), (Bt2, K2, M) = A.shape, B.shape
+        if Bt != Bt2 or K != K2:
+            raise ValueError("batchMatMulT1: A %s against B %s" % (tuple(A.shape), tuple(B.shape)))
+        Ap, Bp = _pad_last(A, _pad4(N)), _pad_last(B, _pad4(M))
+        C = torch.zeros((Bt, N, _pad4(M)), dtype=torch.float32, device=A.device)
+        self.base.batchMatMulT1(C, Ap, Bp, Bt, N, _pad4(N), _pad4(M), K)
+        return C[..., :M]
+
+    def batchMatMulT2(self, A, B):
+        """C[b] = A[b] * B[b]^T; A [Batch, N, K], B [Batch, M, K]."""
+        (Bt, N, K), (Bt2, M, K2) = A.shape, B.shape
+        if Bt != Bt2 or K != K2:
+            raise ValueError("batchMatMulT2: A %s against B %s" % (tuple(A.shape), tuple(B.shape)))
+        Ap, Bp = _pad_last(A, _pad4(K)), _pad_last(B, _pad4(K))
+        C = torch.zeros((Bt, N, _pad4(M)), dtype=torch.float32, device=A.device)
+        self.base.batchMatMulT2(C, Ap, Bp, Bt, N, _pad4(M), M, _pad4(K))
+        return C[..., :M]
 
     def dconv3D(self, X, W, sh, sw, ph, pw, OH=None, OW=None):
         """Deconv3D forward = dconv3D_deltaX with the roles of input and output swapped

@@ -118,6 +118,12 @@ def load():
     lib.alpha_Cuda_matMul_matMulT2.argtypes = mm
     lib.alpha_Cuda_matMul_matMulT1SK.argtypes = [SA, I, I, V, V, V, V, I, I, I]
     lib.alpha_Cuda_matMul_SKbuf_summary.argtypes = [L, V, V, I, I]
+    # batched matrix products: (A, B, C, Batch, 4 dimensions, stream) / engine order (C, A, B, ...) / natives
+    for name in ("alpha_batchMatMul", "alpha_batchMatMulT1", "alpha_batchMatMulT2",
+                 "alpha_engine_batchMatMul", "alpha_engine_batchMatMulT1", "alpha_engine_batchMatMulT2"):
+        getattr(lib, name).argtypes = [V, V, V, I, I, I, I, I, V]
+    for name in ("batchMatMul", "batchMatMul_texture", "batchMatMulT1", "batchMatMulT2", "batchMatMulT2_texture"):
+        getattr(lib, "alpha_Cuda_batchMatMul_" + name).argtypes = [SA, I, V, V, V, I, I, I, I, I]
     _lib = lib
     return lib
 

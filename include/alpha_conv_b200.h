@@ -400,6 +400,43 @@ int alpha_engine_matMul_biased(float* C, const float* A, const float* B, int N, 
 int alpha_engine_matMulT1(float* C, const float* A, const float* B, int N, int M, int K, alpha_stream_t stream);
 int alpha_engine_matMulT2(float* C, const float* A, const float* B, int N, int M, int K, alpha_stream_t stream);
 
+/* ---- batched matrix products (FullConnect / attention-style operators) ----------------------------------
+ * Replace the SIMT kernels behind src/cu32_src/Cuda_batch_matMul/Cuda_batchMatMul/batchMatMul.cuh,
+ * batchMatMulT1.cuh, batchMatMulT2.cuh (the three forms are stated as CPU loops in its test.cuh:95-140).
+ * Only the last dimension of a tensor is padded to a multiple of 4 in the engine's memory, so a row pitch can
+ * exceed the row length (EngineCore.java:587-622 passes both).  Dense shapes with a reduction length that is a
+ * multiple of 32 (16 for T1, which also wants M % 32 == 0) run the tensor-core kernels, one image with its own
+ * weights per batch entry; every other shape runs a plain fp32 kernel with the reference's arithmetic. */
+/* C[b][N][M] = A[b][N][AK](:, 0:BK) * B[b][BK][M] */
+int alpha_batchMatMul(const float* A, const float* B, float* C, int Batch, int N, int M, int BK, int AK, alpha_stream_t stream);
+/* C[b][CN][M] = (A[b][K][AN](:, 0:CN))^T * B[b][K][M] */
+int alpha_batchMatMulT1(const float* A, const float* B, float* C, int Batch, int CN, int AN, int M, int K, alpha_stream_t stream);
+/* C[b][N][CM](:, 0:BM) = A[b][N][K] * B[b][BM][K]^T; the columns BM..CM of C are left as they are */
+int alpha_batchMatMulT2(const float* A, const float* B, float* C, int Batch, int N, int CM, int BM, int K, alpha_stream_t stream);
+
+/* Cuda_batchMatMul natives: src/cu32_src/Cuda_batch_matMul/Cuda_batchMatMul/A.cu:17 (batchMatMul), :38
+ * (batchMatMul_texture), :66 (batchMatMulT1), :92 (batchMatMulT2), :112 (batchMatMulT2_texture); the texture
+ * variants are the same call here. */
+int alpha_Cuda_batchMatMul_batchMatMul(const int64_t* streams, int length, float* A, float* B, float* C, int Batch, int N,
+                                       int M, int BK, int AK);
+int alpha_Cuda_batchMatMul_batchMatMul_texture(const int64_t* streams, int length, float* A, float* B, float* C, int Batch,
+                                               int N, int M, int BK, int AK);
+int alpha_Cuda_batchMatMul_batchMatMulT1(const int64_t* streams, int length, float* A, float* B, float* C, int Batch, int CN,
+                                         int AN, int M, int K);
+int alpha_Cuda_batchMatMul_batchMatMulT2(const int64_t* streams, int length, float* A, float* B, float* C, int Batch, int N,
+                                         int CM, int BM, int K);
+int alpha_Cuda_batchMatMul_batchMatMulT2_texture(const int64_t* streams, int length, float* A, float* B, float* C, int Batch,
+                                                 int N, int CM, int BM, int K);
+
+/* CudaFloat32EngineBase.batchMatMul / batchMatMulT1 / batchMatMulT2 (CudaFloat32EngineBase.java:1256-1318) in the
+ * Java argument order. */
+int alpha_engine_batchMatMul(float* C, const float* A, const float* B, int Batch, int N, int M, int BK, int AK,
+                             alpha_stream_t stream);
+int alpha_engine_batchMatMulT1(float* C, const float* A, const float* B, int Batch, int CN, int AN, int M, int K,
+                               alpha_stream_t stream);
+int alpha_engine_batchMatMulT2(float* C, const float* A, const float* B, int Batch, int N, int CM, int BM, int K,
+                               alpha_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -166,6 +166,29 @@ JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1matMul_matMulT1
 JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1matMul_matMulT2(JNIEnv* env, jclass cls,
     jlongArray streamArray, jint length, jlong dA_address, jlong dB_address, jlong dC_address, jint N, jint M, jint K);
 
+/* Cuda_batchMatMul: src/cu32_src/Cuda_batch_matMul/Cuda_batchMatMul/A.cu:17 (batchMatMul), :38 (batchMatMul_texture),
+ * :66 (batchMatMulT1), :92 (batchMatMulT2), :112 (batchMatMulT2_texture); Java declarations in
+ * z/dragon/engine/cuda/impl/math/Cuda_batchMatMul.java:91-270. */
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1batchMatMul_batchMatMul(JNIEnv* env, jclass cls,
+    jlongArray streamArray, jint length, jlong dA_address, jlong dB_address, jlong dC_address, jint Batch, jint N, jint M,
+    jint BK, jint AK);
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1batchMatMul_batchMatMul_1texture(JNIEnv* env, jclass cls,
+    jlongArray streamArray, jint length, jlong dA_address, jlong dB_address, jlong dC_address, jint Batch, jint N, jint M,
+    jint BK, jint AK);
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1batchMatMul_batchMatMulT1(JNIEnv* env, jclass cls,
+    jlongArray streamArray, jint length, jlong dA_address, jlong dB_address, jlong dC_address, jint Batch, jint CN, jint AN,
+    jint M, jint K);
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1batchMatMul_batchMatMulT2(JNIEnv* env, jclass cls,
+    jlongArray streamArray, jint length, jlong dA_address, jlong dB_address, jlong dC_address, jint Batch, jint N, jint CM,
+    jint BM, jint K);
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1batchMatMul_batchMatMulT2_1texture(JNIEnv* env, jclass cls,
+    jlongArray streamArray, jint length, jlong dA_address, jlong dB_address, jlong dC_address, jint Batch, jint N, jint CM,
+    jint BM, jint K);
+
 #ifdef __cplusplus
 }
 #endif

@@ -427,3 +427,56 @@ void oracle_matmul_f64(const float *A, const float *B, double *C, double *S, int
             S[(size_t)i * M + j] = sa;
         }
 }
+
+/* Batched matrix products with the engine's padded row pitches (TEST INFRASTRUCTURE).  Follows the reference's CPU
+ * loops bmm / bmmT1 / bmmT2 (src/cu32_src/Cuda_batch_matMul/Cuda_batchMatMul/test.cuh:95-140): k outermost, float
+ * multiply then float add into C, which is zeroed first.
+ *   variant 0: C[b][N][M]       = A[b][N][AK](:, 0:K) * B[b][K][M]          (p = AK)
+ *   variant 1: C[b][N][M]       = (A[b][K][AN](:, 0:N))^T * B[b][K][M]      (p = AN)
+ *   variant 2: C[b][N][CM](:, 0:M) = A[b][N][K] * B[b][M][K]^T              (p = CM)
+ * The f64 form also returns S = sum_k |a||b| (the scale of the forward error bound); padding columns of C
+ * (variant 2) are set to zero in both.
+ */
+static inline size_t bmm_a(int v, int b, int i, int k, int N, int K, int p)
+{
+    return v == 1 ? ((size_t)b * K + k) * p + i : (v == 0 ? ((size_t)b * N + i) * p + k : ((size_t)b * N + i) * K + k);
+}
+static inline size_t bmm_b(int v, int b, int k, int j, int M, int K)
+{
+    return v == 2 ? ((size_t)b * M + j) * K + k : ((size_t)b * K + k) * M + j;
+}
+void oracle_bmm(const float *A, const float *B, float *C, int Batch, int N, int M, int K, int p, int variant)
+{
+    const int cm = variant == 2 ? p : M;
+    memset(C, 0, sizeof(float) * (size_t)Batch * N * cm);
+    for (int b = 0; b < Batch; b++)
+        for (int k = 0; k < K; k++)
+            for (int i = 0; i < N; i++) {
+                const float a = A[bmm_a(variant, b, i, k, N, K, p)];
+                for (int j = 0; j < M; j++)
+                    C[((size_t)b * N + i) * cm + j] += a * B[bmm_b(variant, b, k, j, M, K)];
+            }
+}
+void oracle_bmm_f64(const float *A, const float *B, double *C, double *S, int Batch, int N, int M, int K, int p,
+                    int variant, int threads)
+{
+    const int cm = variant == 2 ? p : M;
+    (void)threads;
+    memset(C, 0, sizeof(double) * (size_t)Batch * N * cm);
+    memset(S, 0, sizeof(double) * (size_t)Batch * N * cm);
+#if defined(_OPENMP)
+#pragma omp parallel for schedule(static) num_threads(threads > 0 ? threads : 1)
+#endif
+    for (int b = 0; b < Batch; b++)
+        for (int i = 0; i < N; i++)
+            for (int j = 0; j < M; j++) {
+                double v = 0, sa = 0;
+                for (int k = 0; k < K; k++) {
+                    const double a = A[bmm_a(variant, b, i, k, N, K, p)], w = B[bmm_b(variant, b, k, j, M, K)];
+                    v += a * w;
+                    sa += fabs(a * w);
+                }
+                C[((size_t)b * N + i) * cm + j] = v;
+                S[((size_t)b * N + i) * cm + j] = sa;
+            }
+}

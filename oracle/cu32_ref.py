@@ -347,3 +347,61 @@ class Cu32Reference:
             self._call(self.dw, P + "buf_1summary", ("long", self.streams[0].cuda_stream), buf, dW, GridZ - 1, sizeW)
         torch.cuda.synchronize()
         return dW
+
+
+def batch_matmul_available():
+    return os.path.exists(os.path.join(_HERE, "_ref", "libcu32_Cuda_batchMatMul.so"))
+
+
+class Cu32BatchMatMul(Cu32MatMul):
+    """The reference's batchMatMul / batchMatMulT1 / batchMatMulT2 on the GPU, natives and texture switch as in
+    CudaFloat32EngineBase (:1256-1318), on tensors in the engine's memory layout (last dimension padded to 4)."""
+
+    def __init__(self, lib=None, env=None):
+        super().__init__(lib if lib is not None else _lib("Cuda_batchMatMul"), env)
+
+    def _call(self, name, *args):
+        f = getattr(self.lib, "Java_z_dragon_engine_cuda_impl_math_Cuda_1batchMatMul_" + name)
+        f.restype = None
+        conv = []
+        for a in args:
+            if isinstance(a, torch.Tensor):
+                conv.append(C.c_int64(a.data_ptr()))
+            elif a == "streams":
+                conv.append(C.c_void_p(0x5EED))
+            else:
+                conv.append(C.c_int(int(a)))
+        f(self.env.env, None, *conv)
+        self.called.append(name)
+
+    def batchMatMul(self, A, B, texture=True):
+        """A [Batch, N, AK], B [Batch, BK, M] -> C [Batch, N, M]."""
+        (Bt, N, AK), (_, BK, M) = A.shape, B.shape
+        Cm = torch.full((Bt, N, M), float("nan"), device=A.device, dtype=torch.float32)
+        torch.cuda.synchronize()
+        name = "batchMatMul_1texture" if (texture and N > 47 and M > 47) else "batchMatMul"
+        self._call(name, "streams", 10, A, B, Cm, Bt, N, M, BK, AK)
+        torch.cuda.synchronize()
+        return Cm
+
+    def batchMatMulT1(self, A, B, CN=None):
+        """A [Batch, K, AN], B [Batch, K, M] -> C [Batch, CN, M]."""
+        (Bt, K, AN), (_, _, M) = A.shape, B.shape
+        CN = AN if CN is None else CN
+        Cm = torch.full((Bt, CN, M), float("nan"), device=A.device, dtype=torch.float32)
+        torch.cuda.synchronize()
+        self._call("batchMatMulT1", "streams", 10, A, B, Cm, Bt, CN, AN, M, K)
+        torch.cuda.synchronize()
+        return Cm
+
+    def batchMatMulT2(self, A, B, texture=True):
+        """A [Batch, N, K], B [Batch, BM, K] -> C [Batch, N, CM], CM = BM rounded up to 4 (padding columns zero on entry)."""
+        (Bt, N, K), (_, BM, _) = A.shape, B.shape
+        CM = (BM + 3) & ~3
+        Cm = torch.zeros((Bt, N, CM), device=A.device, dtype=torch.float32)
+        Cm[..., :BM] = float("nan")
+        torch.cuda.synchronize()
+        name = "batchMatMulT2_1texture" if (texture and N > 47 and CM > 47) else "batchMatMulT2"
+        self._call(name, "streams", 10, A, B, Cm, Bt, N, CM, BM, K)
+        torch.cuda.synchronize()
+        return Cm

@@ -324,3 +324,62 @@ def ref_matmul(A, B, variant="matMul"):
     fn = getattr(ref_lib(), ("ref_multiply", "ref_multiplyT1", "ref_multiplyT2")[v])
     fn(pa, pb, Cm.ctypes.data_as(_F), _i(N), _i(M), _i(K))
     return Cm
+
+
+_BMM_VARIANT = {"batchMatMul": 0, "batchMatMulT1": 1, "batchMatMulT2": 2}
+
+
+def _bmm_dims(A, B, v, M):
+    """Logical (Batch, N, M, K) and the padded pitch p of a batched product from the MEMORY shapes of A and B
+    (last dimension padded to 4 by the engine) and the logical M (variant 2: rows of B = M)."""
+    if v == 0:      # A [Batch, N, AK], B [Batch, K, M]
+        (Bt, N, p), (_, K, M) = A.shape, B.shape
+    elif v == 1:    # A [Batch, K, AN], B [Batch, K, M]; N given through M's slot is not needed: C rows = CN
+        (Bt, K, p), (_, _, M) = A.shape, B.shape
+        N = None
+    else:           # A [Batch, N, K], B [Batch, BM, K]; p = CM
+        (Bt, N, K), (_, M, _) = A.shape, B.shape
+        p = (M + 3) & ~3
+    return Bt, N, M, K, p
+
+
+def batch_matmul(A, B, variant="batchMatMul", rows=None, threads=1, f64=False):
+    """The reference's batched products on the engine's memory layout (Cuda_batchMatMul/test.cuh:95-140):
+    'batchMatMul'   C[b][N, M]  = A[b][N, AK](:, :K) * B[b][K, M]          (K = B.shape[1])
+    'batchMatMulT1' C[b][CN, M] = (A[b][K, AN](:, :CN))^T * B[b][K, M]     (CN = rows, default AN)
+    'batchMatMulT2' C[b][N, CM](:, :BM) = A[b][N, K] * B[b][BM, K]^T       (CM = BM rounded up to 4)
+    float loops by default; f64=True returns (C, S) in double with S = sum_k |a||b|."""
+    v = _BMM_VARIANT[variant]
+    A, pa = _f(A)
+    B, pb = _f(B)
+    Bt, N, M, K, p = _bmm_dims(A, B, v, None)
+    if v == 1:
+        N = p if rows is None else rows
+    cm = p if v == 2 else M
+    if f64:
+        Cm, S = np.empty((Bt, N, cm), np.float64), np.empty((Bt, N, cm), np.float64)
+        lib().oracle_bmm_f64(pa, pb, Cm.ctypes.data_as(_D), S.ctypes.data_as(_D), _i(Bt), _i(N), _i(M), _i(K), _i(p), _i(v), _i(threads))
+        return Cm, S
+    Cm = np.empty((Bt, N, cm), np.float32)
+    lib().oracle_bmm(pa, pb, Cm.ctypes.data_as(_F), _i(Bt), _i(N), _i(M), _i(K), _i(p), _i(v))
+    return Cm
+
+
+def ref_batch_matmul(A, B, variant="batchMatMul", rows=None):
+    """The reference project's own C++ loops bmm / bmmT1 / bmmT2 (Cuda_batchMatMul/test.cuh:95-140)."""
+    v = _BMM_VARIANT[variant]
+    A, pa = _f(A)
+    B, pb = _f(B)
+    Bt, N, M, K, p = _bmm_dims(A, B, v, None)
+    if v == 1:
+        N = p if rows is None else rows
+    cm = p if v == 2 else M
+    Cm = np.zeros((Bt, N, cm), np.float32)
+    L = ref_lib()
+    if v == 0:
+        L.ref_bmm(pa, pb, Cm.ctypes.data_as(_F), _i(Bt), _i(N), _i(M), _i(K), _i(p))
+    elif v == 1:
+        L.ref_bmmT1(pa, pb, Cm.ctypes.data_as(_F), _i(Bt), _i(N), _i(p), _i(M), _i(K))
+    else:
+        L.ref_bmmT2(pa, pb, Cm.ctypes.data_as(_F), _i(Bt), _i(N), _i(cm), _i(M), _i(K))
+    return Cm

@@ -9,8 +9,9 @@
 //   deconv3D_deltaW_img2col2  src/cu32_src/Cuda_dconv3D_deltaW/Cuda_dconv3D_deltaW/test.cuh:77-121
 // and, for the matrix products of the FullConnect path,
 //   multiply, multiplyT1, multiplyT2   src/cu32_src/Cuda_matMul/Cuda_matMul/test.cuh:59-81
+//   bmm, bmmT1, bmmT2                  src/cu32_src/Cuda_batch_matMul/Cuda_batchMatMul/test.cuh:95-140
 // This file only supplies the indexing macros they use (get4d, micro.cuh:93 of each conv library; get,
-// Cuda_matMul/micro.cuh:21) and exports them with C linkage.  No reference source text is stored in this repository.
+// Cuda_matMul/micro.cuh:21; get3d, Cuda_batchMatMul/micro.cuh:9) and exports them with C linkage.  No reference source text is stored in this repository.
 #include <cstddef>
 #include <cmath>
 
@@ -18,12 +19,17 @@
 
 #define get(A, i, j, stride) A[(i) * (stride) + (j)]
 
+#define get3d(A, z, y, x, Sy, Sx) A[(((z) * (Sy)) + (y)) * (Sx) + (x)]
+
 #include "conv3D_naive.inc"
 #include "deltaX_img2col.inc"
 #include "deltaW_img2col2.inc"
 #include "matmul.inc"
 #include "matmulT1.inc"
 #include "matmulT2.inc"
+#include "bmm.inc"
+#include "bmmT1.inc"
+#include "bmmT2.inc"
 
 extern "C" {
 
@@ -51,5 +57,10 @@ void ref_deconv3D_deltaW_img2col2(float *X, int IH, int IW, float *deltaY, int O
 void ref_multiply(float *A, float *B, float *C, int N, int M, int K) { multiply(A, B, C, N, M, K); }
 void ref_multiplyT1(float *A, float *B, float *C, int N, int M, int K) { multiplyT1(A, B, C, N, M, K); }
 void ref_multiplyT2(float *A, float *B, float *C, int N, int M, int K) { multiplyT2(A, B, C, N, M, K); }
+
+// Batched products; C must be zero on entry.  Argument order of the reference's functions.
+void ref_bmm(float *A, float *B, float *C, int Batch, int N, int CM, int BK, int AK) { bmm(A, B, C, Batch, N, CM, BK, AK); }
+void ref_bmmT1(float *A, float *B, float *C, int Batch, int CN, int AN, int CM, int K) { bmmT1(A, B, C, Batch, CN, AN, CM, K); }
+void ref_bmmT2(float *A, float *B, float *C, int Batch, int N, int CM, int BM, int K) { bmmT2(A, B, C, Batch, N, CM, BM, K); }
 
 }  // extern "C"

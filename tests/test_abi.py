@@ -22,17 +22,18 @@ def _declared_symbols():
     for fn in sorted(os.listdir(INCLUDE)):
         text = open(os.path.join(INCLUDE, fn)).read()
         text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-        names.update(re.findall(r"\b(alpha_(?:conv|Cuda|engine|matMul)\w*)\s*\(", text))
+        names.update(re.findall(r"\b(alpha_(?:conv|Cuda|engine|matMul|batchMatMul)\w*)\s*\(", text))
         names.update(re.findall(r"\b(Java_z_dragon_\w+)\s*\(", text))
     return sorted(names)
 
 
 def test_every_declared_symbol_is_exported(lib):
     names = _declared_symbols()
-    # 29 natives of the three convolution classes + 5 of Cuda_matMul
-    assert len([n for n in names if n.startswith("Java_")]) == 34
-    assert len([n for n in names if n.startswith("alpha_Cuda_")]) == 34
+    # 29 natives of the three convolution classes + 5 of Cuda_matMul + 5 of Cuda_batchMatMul
+    assert len([n for n in names if n.startswith("Java_")]) == 39
+    assert len([n for n in names if n.startswith("alpha_Cuda_")]) == 39
     assert len([n for n in names if n.startswith("alpha_matMul")]) == 3
+    assert len([n for n in names if n.startswith("alpha_batchMatMul")]) == 3
     missing = [n for n in names if not hasattr(lib, n)]
     assert not missing, missing
 
@@ -77,6 +78,8 @@ def test_options_and_per_call_settings_need_no_device(lib, pkg):
     assert lib.alpha_matMul(None, 16, None, 32, 8, 8, 8, None) == -1 and b"null" in lib.alpha_conv_last_error()
     assert lib.alpha_matMulT1(16, 32, 48, 8, 0, 8, None) == -1                               # M = 0
     assert lib.alpha_matMulT2(16, 32, None, 48, 8, 8, 6, None) == -1                         # K = 6: not a multiple of 4
+    assert lib.alpha_batchMatMul(16, 32, 48, 2, 8, 8, 8, 4, None) == -1 and b"row pitch" in lib.alpha_conv_last_error()
+    assert lib.alpha_batchMatMulT2(16, 32, 48, 0, 8, 8, 8, 8, None) == -1                    # empty batch
     assert lib.alpha_Cuda_matMul_SKbuf_summary(0, None, None, 3, 64) == -1
     n = C.c_size_t(0)
     assert lib.alpha_conv_workspace_bytes(C.byref(s), 17, C.byref(n)) == -1                  # unknown op
