@@ -39,6 +39,7 @@ inline void raise(JNIEnv* env, int rc)
 }
 
 inline float* fp(jlong a) { return reinterpret_cast<float*>(static_cast<intptr_t>(a)); }
+inline int* ip(jlong a) { return reinterpret_cast<int*>(static_cast<intptr_t>(a)); }
 
 }  // namespace
 
@@ -404,6 +405,78 @@ JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1batchMatMul_bat
 {
     Streams st = get_streams(env, streamArray, length);
     raise(env, alpha_Cuda_batchMatMul_batchMatMulT2_texture(st.v, st.n, fp(dA_address), fp(dB_address), fp(dC_address), Batch, N, CM, BM, K));
+}
+
+// ---- Cuda_pool2D / Cuda_upool2D (src/cu32_src/Cuda_pool2D/Cuda_pool2D/A.cu, src/cu32_src/Cuda_upool2D/Cuda_upool2D/A.cu:9-145) ----
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1pool2D_pool2D_1max(JNIEnv* env, jclass,
+    jlongArray streamArray, jint length, jlong dX_address, jint IH, jint IW, jint FH, jint FW, jlong dY_address, jint OH, jint OW, jint N, jint IC, jint sh, jint sw, jint ph, jint pw)
+{
+    Streams st = get_streams(env, streamArray, length);
+    raise(env, alpha_Cuda_pool2D_pool2D_max(st.v, st.n, fp(dX_address), IH, IW, FH, FW, fp(dY_address), OH, OW, N, IC, sh, sw, ph, pw));
+}
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1pool2D_pool2D_1max_1indexed(JNIEnv* env, jclass,
+    jlongArray streamArray, jint length, jlong dX_address, jint IH, jint IW, jint FH, jint FW, jlong dY_address, jlong dIndex_address, jint OH, jint OW, jint N, jint IC, jint sh, jint sw, jint ph, jint pw)
+{
+    Streams st = get_streams(env, streamArray, length);
+    raise(env, alpha_Cuda_pool2D_pool2D_max_indexed(st.v, st.n, fp(dX_address), IH, IW, FH, FW, fp(dY_address), ip(dIndex_address), OH, OW, N, IC, sh, sw, ph, pw));
+}
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1pool2D_pool2D_1avg(JNIEnv* env, jclass,
+    jlongArray streamArray, jint length, jlong dX_address, jint IH, jint IW, jint FH, jint FW, jlong dY_address, jint OH, jint OW, jint N, jint IC, jint sh, jint sw, jint ph, jint pw)
+{
+    Streams st = get_streams(env, streamArray, length);
+    raise(env, alpha_Cuda_pool2D_pool2D_avg(st.v, st.n, fp(dX_address), IH, IW, FH, FW, fp(dY_address), OH, OW, N, IC, sh, sw, ph, pw));
+}
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1pool2D_pool2D_1avg_1ignore_1padding(JNIEnv* env, jclass,
+    jlongArray streamArray, jint length, jlong dX_address, jint IH, jint IW, jint FH, jint FW, jlong dY_address, jint OH, jint OW, jint N, jint IC, jint sh, jint sw, jint ph, jint pw)
+{
+    Streams st = get_streams(env, streamArray, length);
+    raise(env, alpha_Cuda_pool2D_pool2D_avg_ignore_padding(st.v, st.n, fp(dX_address), IH, IW, FH, FW, fp(dY_address), OH, OW, N, IC, sh, sw, ph, pw));
+}
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1upool2D_upool2D_1max(JNIEnv* env, jclass,
+    jlongArray streamArray, jint length, jlong d_deltaY_address, jlong dY_address, jint OH, jint OW, jint FH, jint FW, jlong d_deltaX_address, jlong dX_address, jint IH, jint IW, jint N, jint IC, jint sh, jint sw, jint ph, jint pw)
+{
+    Streams st = get_streams(env, streamArray, length);
+    raise(env, alpha_Cuda_upool2D_upool2D_max(st.v, st.n, fp(d_deltaY_address), fp(dY_address), OH, OW, FH, FW, fp(d_deltaX_address), fp(dX_address), IH, IW, N, IC, sh, sw, ph, pw));
+}
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1upool2D_upool2D_1max_1Indexed(JNIEnv* env, jclass,
+    jlongArray streamArray, jint length, jlong d_deltaY_address, jlong dIndex_address, jint OH, jint OW, jint FH, jint FW, jlong d_deltaX_address, jint IH, jint IW, jint N, jint IC, jint sh, jint sw, jint ph, jint pw)
+{
+    Streams st = get_streams(env, streamArray, length);
+    raise(env, alpha_Cuda_upool2D_upool2D_max_Indexed(st.v, st.n, fp(d_deltaY_address), ip(dIndex_address), OH, OW, FH, FW, fp(d_deltaX_address), IH, IW, N, IC, sh, sw, ph, pw));
+}
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1upool2D_upool2D_1avg(JNIEnv* env, jclass,
+    jlongArray streamArray, jint length, jlong d_deltaY_address, jint OH, jint OW, jint FH, jint FW, jlong d_deltaX_address, jint IH, jint IW, jint N, jint IC, jint sh, jint sw, jint ph, jint pw)
+{
+    Streams st = get_streams(env, streamArray, length);
+    raise(env, alpha_Cuda_upool2D_upool2D_avg(st.v, st.n, fp(d_deltaY_address), OH, OW, FH, FW, fp(d_deltaX_address), IH, IW, N, IC, sh, sw, ph, pw));
+}
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1upool2D_upool2D_1avg_1tiled(JNIEnv* env, jclass,
+    jlongArray streamArray, jint length, jlong d_deltaY_address, jint OH, jint OW, jint FH, jint FW, jlong d_deltaX_address, jint IH, jint IW, jint N, jint IC, jint sh, jint sw, jint ph, jint pw)
+{
+    Streams st = get_streams(env, streamArray, length);
+    raise(env, alpha_Cuda_upool2D_upool2D_avg_tiled(st.v, st.n, fp(d_deltaY_address), OH, OW, FH, FW, fp(d_deltaX_address), IH, IW, N, IC, sh, sw, ph, pw));
+}
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1upool2D_upool2D_1avg_1ignore_1padding(JNIEnv* env, jclass,
+    jlongArray streamArray, jint length, jlong d_deltaY_address, jint OH, jint OW, jint FH, jint FW, jlong d_deltaX_address, jint IH, jint IW, jint N, jint IC, jint sh, jint sw, jint ph, jint pw)
+{
+    Streams st = get_streams(env, streamArray, length);
+    raise(env, alpha_Cuda_upool2D_upool2D_avg_ignore_padding(st.v, st.n, fp(d_deltaY_address), OH, OW, FH, FW, fp(d_deltaX_address), IH, IW, N, IC, sh, sw, ph, pw));
+}
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1upool2D_upool2D_1avg_1ignore_1padding_1tiled(JNIEnv* env, jclass,
+    jlongArray streamArray, jint length, jlong d_deltaY_address, jint OH, jint OW, jint FH, jint FW, jlong d_deltaX_address, jint IH, jint IW, jint N, jint IC, jint sh, jint sw, jint ph, jint pw)
+{
+    Streams st = get_streams(env, streamArray, length);
+    raise(env, alpha_Cuda_upool2D_upool2D_avg_ignore_padding_tiled(st.v, st.n, fp(d_deltaY_address), OH, OW, FH, FW, fp(d_deltaX_address), IH, IW, N, IC, sh, sw, ph, pw));
 }
 
 }  // extern "C"

@@ -465,6 +465,66 @@ class Engine:
         self.base.batchMatMulT2(C, Ap, Bp, Bt, N, _pad4(M), M, _pad4(K))
         return C[..., :M]
 
+    # ---- 2D pooling (Engine.pool2D_max / pool2D_avg and their gradients; CudaFloat32EngineBase.java:2012-2215) ----
+    def _pool_shape(self, X, FH, FW, sh, sw, ph, pw):
+        N, IH, IW, IC = X.shape
+        OH, OW = (IH + 2 * ph - FH) // sh + 1, (IW + 2 * pw - FW) // sw + 1
+        return _l.AlphaPoolShape(N, IH, IW, _pad4(IC), FH, FW, OH, OW, sh, sw, ph, pw), OH, OW
+
+    def pool2D_max(self, X, FH, FW, sh, sw, ph, pw, indexed=False):
+        """Y (and, with indexed=True, the int32 index tensor the indexed gradient reads)."""
+        s, OH, OW = self._pool_shape(X, FH, FW, sh, sw, ph, pw)
+        IC = X.shape[3]
+        Xp = _pad_last(X, s.IC)
+        Y = torch.empty((s.N, OH, OW, s.IC), dtype=torch.float32, device=X.device)
+        a, st = self.base._addr, _stream(self.base._stream)
+        if indexed:
+            Index = torch.empty((s.N, OH, OW, s.IC), dtype=torch.int32, device=X.device)
+            _l.check(self.base._lib.alpha_pool2D_max_indexed(C.byref(s), a(Xp), a(Y), a(Index), st))
+            return (Y if s.IC == IC else Y[..., :IC]), Index
+        _l.check(self.base._lib.alpha_pool2D_max(C.byref(s), a(Xp), a(Y), st))
+        return Y if s.IC == IC else Y[..., :IC]
+
+    def pool2D_avg(self, X, FH, FW, sh, sw, ph, pw, ignore_padding=False):
+        s, OH, OW = self._pool_shape(X, FH, FW, sh, sw, ph, pw)
+        IC = X.shape[3]
+        Xp = _pad_last(X, s.IC)
+        Y = torch.empty((s.N, OH, OW, s.IC), dtype=torch.float32, device=X.device)
+        a = self.base._addr
+        _l.check(self.base._lib.alpha_pool2D_avg(C.byref(s), a(Xp), a(Y), int(bool(ignore_padding)), _stream(self.base._stream)))
+        return Y if s.IC == IC else Y[..., :IC]
+
+    def upool2D_max(self, deltaY, Y, X, FH, FW, sh, sw, ph, pw):
+        """deltaX of pool2D_max from X and Y of the forward pass."""
+        s, OH, OW = self._pool_shape(X, FH, FW, sh, sw, ph, pw)
+        IC = X.shape[3]
+        Xp, Yp, dYp = _pad_last(X, s.IC), _pad_last(Y, s.IC), _pad_last(deltaY, s.IC)
+        dX = torch.empty_like(Xp)
+        a = self.base._addr
+        _l.check(self.base._lib.alpha_upool2D_max(C.byref(s), a(dYp), a(Yp), a(Xp), a(dX), _stream(self.base._stream)))
+        return dX if s.IC == IC else dX[..., :IC]
+
+    def upool2D_max_indexed(self, deltaY, Index, IH, IW, FH, FW, sh, sw, ph, pw):
+        """deltaX of pool2D_max from the index tensor of the forward pass (its channel count is the padded one)."""
+        N, OH, OW, IC = deltaY.shape
+        ic4 = Index.shape[3]
+        s = _l.AlphaPoolShape(N, IH, IW, ic4, FH, FW, OH, OW, sh, sw, ph, pw)
+        dYp = _pad_last(deltaY, ic4)
+        dX = torch.empty((N, IH, IW, ic4), dtype=torch.float32, device=deltaY.device)
+        a = self.base._addr
+        _l.check(self.base._lib.alpha_upool2D_max_indexed(C.byref(s), a(dYp), a(Index), a(dX), _stream(self.base._stream)))
+        return dX if ic4 == IC else dX[..., :IC]
+
+    def upool2D_avg(self, deltaY, IH, IW, FH, FW, sh, sw, ph, pw, ignore_padding=False):
+        N, OH, OW, IC = deltaY.shape
+        ic4 = _pad4(IC)
+        s = _l.AlphaPoolShape(N, IH, IW, ic4, FH, FW, OH, OW, sh, sw, ph, pw)
+        dYp = _pad_last(deltaY, ic4)
+        dX = torch.empty((N, IH, IW, ic4), dtype=torch.float32, device=deltaY.device)
+        a = self.base._addr
+        _l.check(self.base._lib.alpha_upool2D_avg(C.byref(s), a(dYp), a(dX), int(bool(ignore_padding)), _stream(self.base._stream)))
+        return dX if ic4 == IC else dX[..., :IC]
+
     def dconv3D(self, X, W, sh, sw, ph, pw, OH=None, OW=None):
         """Deconv3D forward = dconv3D_deltaX with the roles of input and output swapped
         (Engine.java:1819-1829); W is [IC_in, FH, FW, OC_out]."""

@@ -14,6 +14,10 @@ class AlphaConvShape(C.Structure):
                 ("N", "IH", "IW", "IC", "OC", "FH", "FW", "OH", "OW", "sh", "sw", "ph", "pw")]
 
 
+class AlphaPoolShape(C.Structure):
+    _fields_ = [(n, C.c_int) for n in ("N", "IH", "IW", "IC", "FH", "FW", "OH", "OW", "sh", "sw", "ph", "pw")]
+
+
 class AlphaConvError(RuntimeError):
     """A call into the library returned a non-zero status; .code holds the ALPHA_E_* value."""
 
@@ -124,6 +128,23 @@ def load():
         getattr(lib, name).argtypes = [V, V, V, I, I, I, I, I, V]
     for name in ("batchMatMul", "batchMatMul_texture", "batchMatMulT1", "batchMatMulT2", "batchMatMulT2_texture"):
         getattr(lib, "alpha_Cuda_batchMatMul_" + name).argtypes = [SA, I, V, V, V, I, I, I, I, I]
+    # pooling
+    PS = C.POINTER(AlphaPoolShape)
+    lib.alpha_pool2D_max.argtypes = [PS, V, V, V]
+    lib.alpha_pool2D_max_indexed.argtypes = [PS, V, V, V, V]
+    lib.alpha_pool2D_avg.argtypes = [PS, V, V, I, V]
+    lib.alpha_upool2D_max.argtypes = [PS, V, V, V, V, V]
+    lib.alpha_upool2D_max_indexed.argtypes = [PS, V, V, V, V]
+    lib.alpha_upool2D_avg.argtypes = [PS, V, V, I, V]
+    fwd = [SA, I, V, I, I, I, I, V, I, I, I, I, I, I, I, I]
+    lib.alpha_Cuda_pool2D_pool2D_max.argtypes = fwd
+    lib.alpha_Cuda_pool2D_pool2D_avg.argtypes = fwd
+    lib.alpha_Cuda_pool2D_pool2D_avg_ignore_padding.argtypes = fwd
+    lib.alpha_Cuda_pool2D_pool2D_max_indexed.argtypes = [SA, I, V, I, I, I, I, V, V, I, I, I, I, I, I, I, I]
+    lib.alpha_Cuda_upool2D_upool2D_max.argtypes = [SA, I, V, V, I, I, I, I, V, V, I, I, I, I, I, I, I, I]
+    lib.alpha_Cuda_upool2D_upool2D_max_Indexed.argtypes = [SA, I, V, V, I, I, I, I, V, I, I, I, I, I, I, I, I]
+    for name in ("avg", "avg_tiled", "avg_ignore_padding", "avg_ignore_padding_tiled"):
+        getattr(lib, "alpha_Cuda_upool2D_upool2D_" + name).argtypes = [SA, I, V, I, I, I, I, V, I, I, I, I, I, I, I, I]
     _lib = lib
     return lib
 

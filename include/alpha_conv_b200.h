@@ -437,6 +437,62 @@ int alpha_engine_batchMatMulT1(float* C, const float* A, const float* B, int Bat
 int alpha_engine_batchMatMulT2(float* C, const float* A, const float* B, int Batch, int N, int CM, int BM, int K,
                                alpha_stream_t stream);
 
+/* ---- 2D pooling (the operators between the convolutions of a network) ---------------------------------------
+ * Replace the kernels behind src/cu32_src/Cuda_pool2D/Cuda_pool2D/pool2D.cuh and
+ * src/cu32_src/Cuda_upool2D/Cuda_upool2D/upool2D.cuh.  NHWC fp32, any channel count (16-byte accesses when
+ * IC % 4 == 0, which the engine's padding guarantees).  HBM-bound elementwise kernels; the backward forms gather
+ * (no atomics, no zero fill of deltaX needed, results independent of the launch).
+ * OH = (IH + 2 ph - FH) / sh + 1, likewise OW; padding must be smaller than the window. */
+typedef struct AlphaPoolShape {
+    int N, IH, IW, IC;   /* X[N][IH][IW][IC] */
+    int FH, FW;          /* window */
+    int OH, OW;          /* Y[N][OH][OW][IC] */
+    int sh, sw, ph, pw;
+} AlphaPoolShape;
+
+/* Y = max over the window positions inside the image (Cuda_pool2D.pool2D_max, pool2D_max_kernel.cuh:44-76) */
+int alpha_pool2D_max(const AlphaPoolShape* s, const float* X, float* Y, alpha_stream_t stream);
+/* the same, and Index[n][oh][ow][c] = offset into X (in floats, from X[0]) of the element that gave the maximum, the
+ * last one of several equal ones (pool2D_max_indexed_kernel.cuh:41-96) */
+int alpha_pool2D_max_indexed(const AlphaPoolShape* s, const float* X, float* Y, int* Index, alpha_stream_t stream);
+/* Y = sum over the window positions inside the image / (FH * FW), or with ignore_padding / their number
+ * (pool2D_avg_kernel.cuh, pool2D_avg_ip_kernel.cuh) */
+int alpha_pool2D_avg(const AlphaPoolShape* s, const float* X, float* Y, int ignore_padding, alpha_stream_t stream);
+/* deltaX = sum over the windows that contain the element of (X >= Y) * deltaY (upool2D_max_kernel.cuh:52-100) */
+int alpha_upool2D_max(const AlphaPoolShape* s, const float* deltaY, const float* Y, const float* X, float* deltaX,
+                      alpha_stream_t stream);
+/* deltaX = sum over the windows that contain the element of (Index == its offset) * deltaY
+ * (upool2d_max_indexed_kernel.cuh:44-100) */
+int alpha_upool2D_max_indexed(const AlphaPoolShape* s, const float* deltaY, const int* Index, float* deltaX, alpha_stream_t stream);
+/* deltaX = sum over the windows that contain the element of deltaY / (FH * FW), or with ignore_padding / (positions of
+ * that window inside the image) (upool2D_avg_kernel.cuh, upool2D_avg_ip_kernel.cuh) */
+int alpha_upool2D_avg(const AlphaPoolShape* s, const float* deltaY, float* deltaX, int ignore_padding, alpha_stream_t stream);
+
+/* Cuda_pool2D natives (z/dragon/engine/cuda/impl/math/Cuda_pool2D.java:124, :183, :241, :298) */
+int alpha_Cuda_pool2D_pool2D_max(const int64_t* streams, int length, float* X, int IH, int IW, int FH, int FW, float* Y, int OH,
+                                 int OW, int N, int IC, int sh, int sw, int ph, int pw);
+int alpha_Cuda_pool2D_pool2D_max_indexed(const int64_t* streams, int length, float* X, int IH, int IW, int FH, int FW, float* Y,
+                                         int* Index, int OH, int OW, int N, int IC, int sh, int sw, int ph, int pw);
+int alpha_Cuda_pool2D_pool2D_avg(const int64_t* streams, int length, float* X, int IH, int IW, int FH, int FW, float* Y, int OH,
+                                 int OW, int N, int IC, int sh, int sw, int ph, int pw);
+int alpha_Cuda_pool2D_pool2D_avg_ignore_padding(const int64_t* streams, int length, float* X, int IH, int IW, int FH, int FW,
+                                                float* Y, int OH, int OW, int N, int IC, int sh, int sw, int ph, int pw);
+/* Cuda_upool2D natives (src/cu32_src/Cuda_upool2D/Cuda_upool2D/A.cu:9, :33, :57, :79, :102, :124); the tiled variants
+ * (window == stride) are the same call here */
+int alpha_Cuda_upool2D_upool2D_max(const int64_t* streams, int length, float* deltaY, float* Y, int OH, int OW, int FH, int FW,
+                                   float* deltaX, float* X, int IH, int IW, int N, int IC, int sh, int sw, int ph, int pw);
+int alpha_Cuda_upool2D_upool2D_max_Indexed(const int64_t* streams, int length, float* deltaY, int* Index, int OH, int OW, int FH,
+                                           int FW, float* deltaX, int IH, int IW, int N, int IC, int sh, int sw, int ph, int pw);
+int alpha_Cuda_upool2D_upool2D_avg(const int64_t* streams, int length, float* deltaY, int OH, int OW, int FH, int FW, float* deltaX,
+                                   int IH, int IW, int N, int IC, int sh, int sw, int ph, int pw);
+int alpha_Cuda_upool2D_upool2D_avg_tiled(const int64_t* streams, int length, float* deltaY, int OH, int OW, int FH, int FW,
+                                         float* deltaX, int IH, int IW, int N, int IC, int sh, int sw, int ph, int pw);
+int alpha_Cuda_upool2D_upool2D_avg_ignore_padding(const int64_t* streams, int length, float* deltaY, int OH, int OW, int FH, int FW,
+                                                  float* deltaX, int IH, int IW, int N, int IC, int sh, int sw, int ph, int pw);
+int alpha_Cuda_upool2D_upool2D_avg_ignore_padding_tiled(const int64_t* streams, int length, float* deltaY, int OH, int OW, int FH,
+                                                        int FW, float* deltaX, int IH, int IW, int N, int IC, int sh, int sw, int ph,
+                                                        int pw);
+
 #ifdef __cplusplus
 }
 #endif

@@ -189,6 +189,38 @@ JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1batchMatMul_bat
     jlongArray streamArray, jint length, jlong dA_address, jlong dB_address, jlong dC_address, jint Batch, jint N, jint CM,
     jint BM, jint K);
 
+/* Cuda_pool2D (z/dragon/engine/cuda/impl/math/Cuda_pool2D.java:124-302; src/cu32_src/Cuda_pool2D/Cuda_pool2D/A.cu) and
+ * Cuda_upool2D (src/cu32_src/Cuda_upool2D/Cuda_upool2D/A.cu:9-145). */
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1pool2D_pool2D_1max(JNIEnv* env, jclass cls,
+    jlongArray streamArray, jint length, jlong dX_address, jint IH, jint IW, jint FH, jint FW, jlong dY_address, jint OH, jint OW, jint N, jint IC, jint sh, jint sw, jint ph, jint pw);
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1pool2D_pool2D_1max_1indexed(JNIEnv* env, jclass cls,
+    jlongArray streamArray, jint length, jlong dX_address, jint IH, jint IW, jint FH, jint FW, jlong dY_address, jlong dIndex_address, jint OH, jint OW, jint N, jint IC, jint sh, jint sw, jint ph, jint pw);
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1pool2D_pool2D_1avg(JNIEnv* env, jclass cls,
+    jlongArray streamArray, jint length, jlong dX_address, jint IH, jint IW, jint FH, jint FW, jlong dY_address, jint OH, jint OW, jint N, jint IC, jint sh, jint sw, jint ph, jint pw);
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1pool2D_pool2D_1avg_1ignore_1padding(JNIEnv* env, jclass cls,
+    jlongArray streamArray, jint length, jlong dX_address, jint IH, jint IW, jint FH, jint FW, jlong dY_address, jint OH, jint OW, jint N, jint IC, jint sh, jint sw, jint ph, jint pw);
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1upool2D_upool2D_1max(JNIEnv* env, jclass cls,
+    jlongArray streamArray, jint length, jlong d_deltaY_address, jlong dY_address, jint OH, jint OW, jint FH, jint FW, jlong d_deltaX_address, jlong dX_address, jint IH, jint IW, jint N, jint IC, jint sh, jint sw, jint ph, jint pw);
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1upool2D_upool2D_1max_1Indexed(JNIEnv* env, jclass cls,
+    jlongArray streamArray, jint length, jlong d_deltaY_address, jlong dIndex_address, jint OH, jint OW, jint FH, jint FW, jlong d_deltaX_address, jint IH, jint IW, jint N, jint IC, jint sh, jint sw, jint ph, jint pw);
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1upool2D_upool2D_1avg(JNIEnv* env, jclass cls,
+    jlongArray streamArray, jint length, jlong d_deltaY_address, jint OH, jint OW, jint FH, jint FW, jlong d_deltaX_address, jint IH, jint IW, jint N, jint IC, jint sh, jint sw, jint ph, jint pw);
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1upool2D_upool2D_1avg_1tiled(JNIEnv* env, jclass cls,
+    jlongArray streamArray, jint length, jlong d_deltaY_address, jint OH, jint OW, jint FH, jint FW, jlong d_deltaX_address, jint IH, jint IW, jint N, jint IC, jint sh, jint sw, jint ph, jint pw);
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1upool2D_upool2D_1avg_1ignore_1padding(JNIEnv* env, jclass cls,
+    jlongArray streamArray, jint length, jlong d_deltaY_address, jint OH, jint OW, jint FH, jint FW, jlong d_deltaX_address, jint IH, jint IW, jint N, jint IC, jint sh, jint sw, jint ph, jint pw);
+
+JNIEXPORT void JNICALL Java_z_dragon_engine_cuda_impl_math_Cuda_1upool2D_upool2D_1avg_1ignore_1padding_1tiled(JNIEnv* env, jclass cls,
+    jlongArray streamArray, jint length, jlong d_deltaY_address, jint OH, jint OW, jint FH, jint FW, jlong d_deltaX_address, jint IH, jint IW, jint N, jint IC, jint sh, jint sw, jint ph, jint pw);
+
 #ifdef __cplusplus
 }
 #endif

@@ -480,3 +480,90 @@ void oracle_bmm_f64(const float *A, const float *B, double *C, double *S, int Ba
                 S[((size_t)b * N + i) * cm + j] = sa;
             }
 }
+
+/* ---- 2D pooling (TEST INFRASTRUCTURE) ---------------------------------------------------------------------------
+ * Forward: the reference's CPU loops Pool2D_max_img2col / Pool2D_avg_img2col
+ * (src/cu32_src/Cuda_pool2D/Cuda_pool2D/test.cuh:79-157; the average there divides by the number of window positions
+ * inside the image = the ignore_padding variant); op 2 divides by FH * FW as pool2D_avg_kernel.cuh does, op 1 also
+ * writes the index of pool2D_max_indexed_kernel.cuh:41-96 (offset into X of the winning element; among equal maxima
+ * the last one in (fh, fw) order; 0 + image offset for a window without positions).
+ *   op 0 max, 1 max + index, 2 avg, 3 avg ignoring padding.  X[N][IH][IW][IC], Y[N][OH][OW][IC].
+ */
+#define ORACLE_FLOAT_MIN (-3.4028234E38f)   /* Cuda_pool2D/micro.cuh:40 */
+void oracle_pool2D(const float *X, float *Y, int *Index, int N, int IH, int IW, int IC, int FH, int FW, int OH, int OW,
+                   int sh, int sw, int ph, int pw, int op)
+{
+    for (int n = 0; n < N; n++)
+        for (int oh = 0; oh < OH; oh++)
+            for (int ow = 0; ow < OW; ow++)
+                for (int ic = 0; ic < IC; ic++) {
+                    float v = op <= 1 ? ORACLE_FLOAT_MIN : 0.f;
+                    int count = 0;
+                    long long idx = 0;
+                    for (int fh = 0; fh < FH; fh++)
+                        for (int fw = 0; fw < FW; fw++) {
+                            const int ih = oh * sh - ph + fh, iw = ow * sw - pw + fw;
+                            if (ih < 0 || iw < 0 || ih >= IH || iw >= IW) continue;
+                            const long long off = ((long long)ih * IW + iw) * IC + ic;
+                            const float x = X[(long long)n * IH * IW * IC + off];
+                            if (op <= 1) {
+                                if (!(x < v)) idx = off;
+                                if (v < x) v = x;
+                            } else {
+                                v += x;
+                                count++;
+                            }
+                        }
+                    if (op == 2) v = v / (float)(FH * FW);
+                    if (op == 3) v = v / (float)count;
+                    const long long yo = (((long long)n * OH + oh) * OW + ow) * IC + ic;
+                    Y[yo] = v;
+                    if (op == 1) Index[yo] = (int)(idx + (long long)n * IH * IW * IC);
+                }
+}
+
+/* Backward: the reference's CPU loops unpool2D_max_img2col_plus / unpooling_avg_img2col_plus
+ * (src/cu32_src/Cuda_upool2D/Cuda_upool2D/test.cuh:90-229): every input element sums, in ascending (oh, ow) order,
+ * over the output windows that contain it.
+ *   op 0 max:      deltaY where !(Y > X)                         (needs X, Y)
+ *   op 1 indexed:  deltaY where Index == offset of the element   (upool2d_max_indexed_kernel.cuh:44-100)
+ *   op 2 avg:      (sum of deltaY) / (FH * FW)                   (upool2D_avg_kernel.cuh)
+ *   op 3 avg ip:   sum of deltaY / (positions of that window inside the image)
+ */
+void oracle_upool2D(const float *deltaY, const float *Y, const float *X, const int *Index, float *deltaX, int N, int IH,
+                    int IW, int IC, int FH, int FW, int OH, int OW, int sh, int sw, int ph, int pw, int op)
+{
+    for (int n = 0; n < N; n++)
+        for (int ih = 0; ih < IH; ih++)
+            for (int iw = 0; iw < IW; iw++)
+                for (int ic = 0; ic < IC; ic++) {
+                    const long long xo = (((long long)n * IH + ih) * IW + iw) * IC + ic;
+                    float v = 0.f;
+                    for (int oh = 0; oh < OH; oh++) {
+                        const int fh = ih - (oh * sh - ph);
+                        if (fh < 0 || fh >= FH) continue;
+                        for (int ow = 0; ow < OW; ow++) {
+                            const int fw = iw - (ow * sw - pw);
+                            if (fw < 0 || fw >= FW) continue;
+                            const long long yo = (((long long)n * OH + oh) * OW + ow) * IC + ic;
+                            if (op == 0) {
+                                if (Y[yo] > X[xo]) continue;
+                                v += deltaY[yo];
+                            } else if (op == 1) {
+                                if (Index[yo] == (int)xo) v += deltaY[yo];
+                            } else if (op == 2) {
+                                v += deltaY[yo];
+                            } else {
+                                int h0 = oh * sh - ph, h1 = h0 + FH, w0 = ow * sw - pw, w1 = w0 + FW;
+                                if (h0 < 0) h0 = 0;
+                                if (h1 > IH) h1 = IH;
+                                if (w0 < 0) w0 = 0;
+                                if (w1 > IW) w1 = IW;
+                                v += deltaY[yo] / (float)((h1 - h0) * (w1 - w0));
+                            }
+                        }
+                    }
+                    if (op == 2) v = v / (float)(FH * FW);
+                    deltaX[xo] = v;
+                }
+}

@@ -405,3 +405,69 @@ class Cu32BatchMatMul(Cu32MatMul):
         self._call(name, "streams", 10, A, B, Cm, Bt, N, CM, BM, K)
         torch.cuda.synchronize()
         return Cm
+
+
+def pool_available():
+    return all(os.path.exists(os.path.join(_HERE, "_ref", "libcu32_%s.so" % n)) for n in ("Cuda_pool2D", "Cuda_upool2D"))
+
+
+class Cu32Pool:
+    """The reference's pooling natives on the GPU (Cuda_pool2D, Cuda_upool2D) with the engine's choice of the tiled
+    average gradient (CudaFloat32EngineBase.java:2147-2215).  The natives copy at most 4 stream handles
+    (Cuda_pool2D/A.cu:18), so the harness passes 4.  Their kernels want IC % 4 == 0 and N * IH * IW % 4 == 0, which the
+    engine's padding provides; callers of this class pad the same way.
+    `libs` = (pool library, upool library), the rebuilt reference by default."""
+
+    def __init__(self, libs=None, env=None):
+        self.pool, self.upool = libs if libs is not None else (_lib("Cuda_pool2D"), _lib("Cuda_upool2D"))
+        self.env = env if env is not None else _FakeEnv()
+        self.streams = [torch.cuda.Stream() for _ in range(4)]
+        self.env.streams = [s.cuda_stream for s in self.streams]
+        self.called = []
+
+    def _call(self, lib, cls, name, *args):
+        f = getattr(lib, "Java_z_dragon_engine_cuda_impl_math_%s_%s" % (cls, name))
+        f.restype = None
+        conv = []
+        for a in args:
+            if isinstance(a, torch.Tensor):
+                conv.append(C.c_int64(a.data_ptr()))
+            elif a == "streams":
+                conv.append(C.c_void_p(0x5EED))
+            else:
+                conv.append(C.c_int(int(a)))
+        torch.cuda.synchronize()
+        f(self.env.env, None, *conv)
+        torch.cuda.synchronize()
+        self.called.append(name)
+
+    @staticmethod
+    def _out_hw(IH, IW, FH, FW, sh, sw, ph, pw):
+        return (IH + 2 * ph - FH) // sh + 1, (IW + 2 * pw - FW) // sw + 1
+
+    def pool2D(self, X, FH, FW, sh, sw, ph, pw, op="max"):
+        N, IH, IW, IC = X.shape
+        OH, OW = self._out_hw(IH, IW, FH, FW, sh, sw, ph, pw)
+        Y = torch.full((N, OH, OW, IC), float("nan"), device=X.device, dtype=torch.float32)
+        if op == "max_indexed":
+            Index = torch.full((N, OH, OW, IC), -1, device=X.device, dtype=torch.int32)
+            self._call(self.pool, "Cuda_1pool2D", "pool2D_1max_1indexed", "streams", 4, X, IH, IW, FH, FW, Y, Index, OH, OW, N, IC, sh, sw, ph, pw)
+            return Y, Index
+        name = {"max": "pool2D_1max", "avg": "pool2D_1avg", "avg_ignore_padding": "pool2D_1avg_1ignore_1padding"}[op]
+        self._call(self.pool, "Cuda_1pool2D", name, "streams", 4, X, IH, IW, FH, FW, Y, OH, OW, N, IC, sh, sw, ph, pw)
+        return Y
+
+    def upool2D(self, deltaY, IH, IW, FH, FW, sh, sw, ph, pw, op="max", Y=None, X=None, Index=None):
+        N, OH, OW, IC = deltaY.shape
+        # the tiled kernels write only the elements a window covers: the engine hands them a zeroed tensor
+        dX = torch.zeros((N, IH, IW, IC), device=deltaY.device, dtype=torch.float32)
+        if op == "max":
+            self._call(self.upool, "Cuda_1upool2D", "upool2D_1max", "streams", 4, deltaY, Y, OH, OW, FH, FW, dX, X, IH, IW, N, IC, sh, sw, ph, pw)
+        elif op == "max_indexed":
+            self._call(self.upool, "Cuda_1upool2D", "upool2D_1max_1Indexed", "streams", 4, deltaY, Index, OH, OW, FH, FW, dX, IH, IW, N, IC, sh, sw, ph, pw)
+        else:
+            name = "upool2D_1avg" if op == "avg" else "upool2D_1avg_1ignore_1padding"
+            if FH == sh and FW == sw:
+                name += "_1tiled"
+            self._call(self.upool, "Cuda_1upool2D", name, "streams", 4, deltaY, OH, OW, FH, FW, dX, IH, IW, N, IC, sh, sw, ph, pw)
+        return dX

@@ -383,3 +383,70 @@ def ref_batch_matmul(A, B, variant="batchMatMul", rows=None):
     else:
         L.ref_bmmT2(pa, pb, Cm.ctypes.data_as(_F), _i(Bt), _i(N), _i(cm), _i(M), _i(K))
     return Cm
+
+
+_POOL_OP = {"max": 0, "max_indexed": 1, "avg": 2, "avg_ignore_padding": 3}
+_I32 = C.POINTER(C.c_int)
+
+
+def pool_out_hw(IH, IW, FH, FW, sh, sw, ph, pw):
+    return (IH + 2 * ph - FH) // sh + 1, (IW + 2 * pw - FW) // sw + 1
+
+
+def pool2D(X, FH, FW, sh, sw, ph, pw, op="max"):
+    """Forward pooling of X[N, IH, IW, IC] (Cuda_pool2D/test.cuh:79-157 and the avg / indexed kernels beside it);
+    'max_indexed' returns (Y, Index)."""
+    X, px = _f(X)
+    N, IH, IW, IC = X.shape
+    OH, OW = pool_out_hw(IH, IW, FH, FW, sh, sw, ph, pw)
+    Y = np.empty((N, OH, OW, IC), np.float32)
+    Index = np.zeros((N, OH, OW, IC), np.int32)
+    lib().oracle_pool2D(px, Y.ctypes.data_as(_F), Index.ctypes.data_as(_I32), _i(N), _i(IH), _i(IW), _i(IC), _i(FH), _i(FW),
+                        _i(OH), _i(OW), _i(sh), _i(sw), _i(ph), _i(pw), _i(_POOL_OP[op]))
+    return (Y, Index) if op == "max_indexed" else Y
+
+
+def upool2D(deltaY, IH, IW, FH, FW, sh, sw, ph, pw, op="max", Y=None, X=None, Index=None):
+    """Gradient of the pooling operators (Cuda_upool2D/test.cuh:90-229 and the avg / indexed kernels beside it)."""
+    deltaY, pdy = _f(deltaY)
+    N, OH, OW, IC = deltaY.shape
+    dX = np.empty((N, IH, IW, IC), np.float32)
+    null = C.cast(None, _F)
+    py = px = null
+    pidx = C.cast(None, _I32)
+    if op == "max":
+        Y, py = _f(Y)
+        X, px = _f(X)
+    if op == "max_indexed":
+        Index = np.ascontiguousarray(Index, np.int32)
+        pidx = Index.ctypes.data_as(_I32)
+    lib().oracle_upool2D(pdy, py, px, pidx, dX.ctypes.data_as(_F), _i(N), _i(IH), _i(IW), _i(IC), _i(FH), _i(FW), _i(OH), _i(OW),
+                         _i(sh), _i(sw), _i(ph), _i(pw), _i(_POOL_OP[op]))
+    return dX
+
+
+def ref_pool2D(X, FH, FW, sh, sw, ph, pw, op="max"):
+    """The reference project's own C++ loops Pool2D_max_img2col / Pool2D_avg_img2col (the latter ignores padding)."""
+    X, px = _f(X)
+    N, IH, IW, IC = X.shape
+    OH, OW = pool_out_hw(IH, IW, FH, FW, sh, sw, ph, pw)
+    Y = np.empty((N, OH, OW, IC), np.float32)
+    fn = {"max": ref_lib().ref_Pool2D_max, "avg_ignore_padding": ref_lib().ref_Pool2D_avg}[op]
+    fn(px, _i(IH), _i(IW), _i(FH), _i(FW), Y.ctypes.data_as(_F), _i(OH), _i(OW), _i(N), _i(IC), _i(sh), _i(sw), _i(ph), _i(pw))
+    return Y
+
+
+def ref_upool2D(deltaY, IH, IW, FH, FW, sh, sw, ph, pw, op="max", Y=None, X=None):
+    """The reference project's own C++ loops unpool2D_max_img2col_plus / unpooling_avg_img2col_plus (ignores padding)."""
+    deltaY, pdy = _f(deltaY)
+    N, OH, OW, IC = deltaY.shape
+    dX = np.empty((N, IH, IW, IC), np.float32)
+    if op == "max":
+        Y, py = _f(Y)
+        X, px = _f(X)
+        ref_lib().ref_unpool2D_max(pdy, py, _i(OH), _i(OW), _i(FH), _i(FW), dX.ctypes.data_as(_F), px, _i(IH), _i(IW), _i(N), _i(IC),
+                                   _i(sh), _i(sw), _i(ph), _i(pw))
+    else:
+        ref_lib().ref_unpool2D_avg(pdy, _i(OH), _i(OW), _i(FH), _i(FW), dX.ctypes.data_as(_F), _i(IH), _i(IW), _i(N), _i(IC),
+                                   _i(sh), _i(sw), _i(ph), _i(pw))
+    return dX

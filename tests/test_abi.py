@@ -22,16 +22,17 @@ def _declared_symbols():
     for fn in sorted(os.listdir(INCLUDE)):
         text = open(os.path.join(INCLUDE, fn)).read()
         text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-        names.update(re.findall(r"\b(alpha_(?:conv|Cuda|engine|matMul|batchMatMul)\w*)\s*\(", text))
+        names.update(re.findall(r"\b(alpha_(?:conv|Cuda|engine|matMul|batchMatMul|pool2D|upool2D)\w*)\s*\(", text))
         names.update(re.findall(r"\b(Java_z_dragon_\w+)\s*\(", text))
     return sorted(names)
 
 
 def test_every_declared_symbol_is_exported(lib):
     names = _declared_symbols()
-    # 29 natives of the three convolution classes + 5 of Cuda_matMul + 5 of Cuda_batchMatMul
-    assert len([n for n in names if n.startswith("Java_")]) == 39
-    assert len([n for n in names if n.startswith("alpha_Cuda_")]) == 39
+    # 29 natives of the three convolution classes + 5 of Cuda_matMul + 5 of Cuda_batchMatMul + 4 of Cuda_pool2D + 6 of Cuda_upool2D
+    assert len([n for n in names if n.startswith("Java_")]) == 49
+    assert len([n for n in names if n.startswith("alpha_Cuda_")]) == 49
+    assert len([n for n in names if n.startswith(("alpha_pool2D", "alpha_upool2D"))]) == 6
     assert len([n for n in names if n.startswith("alpha_matMul")]) == 3
     assert len([n for n in names if n.startswith("alpha_batchMatMul")]) == 3
     missing = [n for n in names if not hasattr(lib, n)]
