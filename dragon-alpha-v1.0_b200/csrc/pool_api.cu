@@ -23,8 +23,30 @@ namespace {
 
 constexpr float kFloatMin = -3.4028234e38f;   // the reference's FLOAT_MIN (Cuda_pool2D/micro.cuh:40)
 
+// Division of x < 2^31 by a positive constant d as a multiplication: floor(x / d) == (x * m) >> s with
+// s = 31 + ceil(log2 d), m = floor(2^s / d) + 1 (the error term x * (m * d - 2^s) stays below 2^s).  These kernels
+// spend a few loads per element; a handful of hardware divisions per element would cost more than the loads.
+struct FastDiv {
+    unsigned long long m;
+    unsigned d;
+    int s;
+    __host__ __device__ unsigned div(unsigned x) const { return static_cast<unsigned>((static_cast<unsigned long long>(x) * m) >> s); }
+    __host__ __device__ void divmod(unsigned x, unsigned& q, unsigned& r) const { q = div(x); r = x - q * d; }
+};
+FastDiv fast_div(int d_)
+{
+    const unsigned d = static_cast<unsigned>(d_);
+    int b = 0;
+    while ((1ull << b) < d) ++b;
+    FastDiv f;
+    f.d = d; f.s = 31 + b;
+    f.m = (1ull << f.s) / d + 1;
+    return f;
+}
+
 struct PoolDims {
     int N, IH, IW, IC, FH, FW, OH, OW, sh, sw, ph, pw;
+    FastDiv by_cq4, by_cq1, by_IW, by_IH, by_OW, by_OH, by_sh, by_sw;   // by_cq: channel groups of 4 / of 1
 };
 
 template <int V> struct Vec;
@@ -71,17 +93,19 @@ __global__ void __launch_bounds__(256) pool_fwd_kernel(const float* __restrict__
 {
     using F = typename Vec<V>::F;
     using I = typename Vec<V>::I;
-    const int cq = d.IC / V;
-    const long long total = static_cast<long long>(d.N) * d.OH * d.OW * cq;
-    for (long long e = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; e < total;
-         e += static_cast<long long>(gridDim.x) * blockDim.x) {
-        const int c = static_cast<int>(e % cq) * V;
-        long long pix = e / cq;
-        const int ow = static_cast<int>(pix % d.OW);
-        pix /= d.OW;
-        const int oh = static_cast<int>(pix % d.OH), n = static_cast<int>(pix / d.OH);
+    // element counts fit 31 bits (checked on the host), so the index arithmetic is 32-bit: 64-bit divisions per
+    // element cost more than the memory traffic of these kernels
+    const unsigned cq = static_cast<unsigned>(d.IC / V);
+    const unsigned total = static_cast<unsigned>(d.N) * d.OH * d.OW * cq;
+    const FastDiv by_cq = V == 4 ? d.by_cq4 : d.by_cq1;
+    for (unsigned e = blockIdx.x * blockDim.x + threadIdx.x; e < total; e += gridDim.x * blockDim.x) {
+        unsigned pix, cc, uow, uoh, un;
+        by_cq.divmod(e, pix, cc);
+        d.by_OW.divmod(pix, pix, uow);
+        d.by_OH.divmod(pix, un, uoh);
+        const int c = static_cast<int>(cc) * V, ow = static_cast<int>(uow), oh = static_cast<int>(uoh), n = static_cast<int>(un);
         const int ih0 = oh * d.sh - d.ph, iw0 = ow * d.sw - d.pw;
-        const long long img = static_cast<long long>(n) * d.IH * d.IW * d.IC;
+        const size_t img = static_cast<size_t>(n) * d.IH * d.IW * d.IC;
         const float* x = X + img;
         F v = splat<V>(OP <= kMaxIndexed ? kFloatMin : 0.f);
         I idx{};
@@ -105,7 +129,7 @@ __global__ void __launch_bounds__(256) pool_fwd_kernel(const float* __restrict__
         }
         if (OP == kAvg) v = vdiv(v, static_cast<float>(d.FH * d.FW));
         if (OP == kAvgIp) v = vdiv(v, static_cast<float>(count));
-        const long long yoff = e * V;
+        const size_t yoff = static_cast<size_t>(e) * V;
         *reinterpret_cast<F*>(Y + yoff) = v;
         if (OP == kMaxIndexed) {
             iadd(idx, static_cast<int>(img));
@@ -123,32 +147,32 @@ __global__ void __launch_bounds__(256) pool_bwd_kernel(const float* __restrict__
 {
     using F = typename Vec<V>::F;
     using I = typename Vec<V>::I;
-    const int cq = d.IC / V;
-    const long long total = static_cast<long long>(d.N) * d.IH * d.IW * cq;
-    for (long long e = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; e < total;
-         e += static_cast<long long>(gridDim.x) * blockDim.x) {
-        const int c = static_cast<int>(e % cq) * V;
-        long long pix = e / cq;
-        const int iw = static_cast<int>(pix % d.IW);
-        pix /= d.IW;
-        const int ih = static_cast<int>(pix % d.IH), n = static_cast<int>(pix / d.IH);
+    const unsigned cq = static_cast<unsigned>(d.IC / V);
+    const unsigned total = static_cast<unsigned>(d.N) * d.IH * d.IW * cq;
+    const FastDiv by_cq = V == 4 ? d.by_cq4 : d.by_cq1;
+    for (unsigned e = blockIdx.x * blockDim.x + threadIdx.x; e < total; e += gridDim.x * blockDim.x) {
+        unsigned pix, cc, uiw, uih, un;
+        by_cq.divmod(e, pix, cc);
+        d.by_IW.divmod(pix, pix, uiw);
+        d.by_IH.divmod(pix, un, uih);
+        const int c = static_cast<int>(cc) * V, iw = static_cast<int>(uiw), ih = static_cast<int>(uih), n = static_cast<int>(un);
         // output windows that contain (ih, iw): oh * sh - ph <= ih < oh * sh - ph + FH
         int t = ih + d.ph - d.FH + 1;
-        const int oh_lo = t <= 0 ? 0 : (t + d.sh - 1) / d.sh;
-        int oh_hi = (ih + d.ph) / d.sh;
+        const int oh_lo = t <= 0 ? 0 : static_cast<int>(d.by_sh.div(static_cast<unsigned>(t + d.sh - 1)));
+        int oh_hi = static_cast<int>(d.by_sh.div(static_cast<unsigned>(ih + d.ph)));
         if (oh_hi > d.OH - 1) oh_hi = d.OH - 1;
         t = iw + d.pw - d.FW + 1;
-        const int ow_lo = t <= 0 ? 0 : (t + d.sw - 1) / d.sw;
-        int ow_hi = (iw + d.pw) / d.sw;
+        const int ow_lo = t <= 0 ? 0 : static_cast<int>(d.by_sw.div(static_cast<unsigned>(t + d.sw - 1)));
+        int ow_hi = static_cast<int>(d.by_sw.div(static_cast<unsigned>(iw + d.pw)));
         if (ow_hi > d.OW - 1) ow_hi = d.OW - 1;
-        const long long xoff = e * V;
-        const long long yimg = static_cast<long long>(n) * d.OH * d.OW * d.IC;
+        const size_t xoff = static_cast<size_t>(e) * V;
+        const size_t yimg = static_cast<size_t>(n) * d.OH * d.OW * d.IC;
         F xv = splat<V>(0.f);
         if (OP == kBwdMax) xv = *reinterpret_cast<const F*>(X + xoff);
         F v = splat<V>(0.f);
         for (int oh = oh_lo; oh <= oh_hi; ++oh)
             for (int ow = ow_lo; ow <= ow_hi; ++ow) {
-                const long long yo = yimg + (static_cast<long long>(oh) * d.OW + ow) * d.IC + c;
+                const size_t yo = yimg + static_cast<size_t>((oh * d.OW + ow) * d.IC + c);
                 const F dy = *reinterpret_cast<const F*>(dY + yo);
                 if (OP == kBwdMax) {
                     vsel_ge(v, xv, *reinterpret_cast<const F*>(Y + yo), dy);
@@ -182,14 +206,20 @@ int check_pool(const char* what, const AlphaPoolShape* s, const void* a, const v
     const int OH = (s->IH + 2 * s->ph - s->FH) / s->sh + 1, OW = (s->IW + 2 * s->pw - s->FW) / s->sw + 1;
     if (s->IH + 2 * s->ph < s->FH || s->IW + 2 * s->pw < s->FW || s->OH != OH || s->OW != OW)
         return fail(ALPHA_E_ARG, "%s: OH x OW = %d x %d does not follow from the input size (expected %d x %d)", what, s->OH, s->OW, OH, OW);
-    if (static_cast<long long>(s->N) * s->IH * s->IW * s->IC > 2147483647LL)
-        return fail(ALPHA_E_ARG, "%s: more than 2^31 - 1 input elements (the index tensor is 32-bit)", what);
+    if (static_cast<long long>(s->N) * s->IH * s->IW * s->IC > 2147483647LL || static_cast<long long>(s->N) * OH * OW * s->IC > 2147483647LL)
+        return fail(ALPHA_E_ARG, "%s: more than 2^31 - 1 elements in a tensor (the index tensor and the kernels' index arithmetic are 32-bit)", what);
     return ALPHA_OK;
 }
 
 PoolDims dims_of(const AlphaPoolShape* s)
 {
-    return PoolDims{s->N, s->IH, s->IW, s->IC, s->FH, s->FW, s->OH, s->OW, s->sh, s->sw, s->ph, s->pw};
+    PoolDims d{s->N, s->IH, s->IW, s->IC, s->FH, s->FW, s->OH, s->OW, s->sh, s->sw, s->ph, s->pw, {}, {}, {}, {}, {}, {}, {}, {}};
+    d.by_cq4 = fast_div(s->IC / 4 > 0 ? s->IC / 4 : 1);
+    d.by_cq1 = fast_div(s->IC);
+    d.by_IW = fast_div(s->IW); d.by_IH = fast_div(s->IH);
+    d.by_OW = fast_div(s->OW); d.by_OH = fast_div(s->OH);
+    d.by_sh = fast_div(s->sh); d.by_sw = fast_div(s->sw);
+    return d;
 }
 
 int sm_count()

@@ -90,6 +90,30 @@ def test_reference_cpu_loops_and_acceptance(pkg, eng, oracle_mod):
             assert same >= 0.999, (variant, dims, same)
 
 
+def test_golden_vectors_of_the_reference_loops(pkg, eng):
+    """The committed outputs of the reference's own bmm / bmmT1 / bmmT2 loops (tests/golden/bmm_golden.npz), through the
+    engine-level entry points with the padded pitches the golden matrices carry."""
+    import os
+    import torch
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "bmm_golden.npz"))
+    dev = torch.device("cuda:0")
+    base = eng.base
+    for key in sorted({k.rsplit("/", 1)[0] for k in g.files}):
+        variant = key.split("/")[1]
+        A, B, ref, rows = g[key + "/A"], g[key + "/B"], g[key + "/ref_C"], int(g[key + "/rows"])
+        tA, tB = torch.from_numpy(A).to(dev), torch.from_numpy(B).to(dev)
+        Cm = torch.zeros(ref.shape, device=dev)
+        Bt = A.shape[0]
+        if variant == "batchMatMul":        # A [Bt, N, AK], B [Bt, BK, M]
+            base.batchMatMul(Cm, tA, tB, Bt, A.shape[1], B.shape[2], B.shape[1], A.shape[2])
+        elif variant == "batchMatMulT1":    # A [Bt, K, AN], B [Bt, K, M], C [Bt, CN, M]
+            base.batchMatMulT1(Cm, tA, tB, Bt, rows, A.shape[2], B.shape[2], A.shape[1])
+        else:                               # A [Bt, N, K], B [Bt, BM, K], C [Bt, N, CM]
+            base.batchMatMulT2(Cm, tA, tB, Bt, A.shape[1], ref.shape[2], B.shape[1], A.shape[2])
+        got = Cm.cpu().numpy()
+        assert np.abs(got - ref).max() <= 1e-5 * np.abs(ref).max(), key
+
+
 def test_natives_against_the_rebuilt_reference(pkg):
     """Both implementations of the five Cuda_batchMatMul natives, driven by the same harness with the engine's
     texture switch, on identical device tensors in the engine's memory layout."""

@@ -152,3 +152,59 @@ def test_matmul_oracle_against_the_reference_loops(oracle_mod):
         assert (np.abs(got - c64) <= 1e-5 * S + 1e-30).all(), key
         if O.ref_lib() is not None:
             assert np.array_equal(O.ref_matmul(A, B, variant), ref), key
+
+
+def _golden(name):
+    import os
+    return np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", name))
+
+
+def test_batched_matmul_oracle_against_the_reference_loops(oracle_mod):
+    """The float loops of the three batched products, on the engine's padded memory layout, reproduce the stored
+    outputs of the reference's own bmm / bmmT1 / bmmT2 (tests/golden/bmm_golden.npz) bit for bit."""
+    O = oracle_mod
+    g = _golden("bmm_golden.npz")
+    keys = sorted({k.rsplit("/", 1)[0] for k in g.files})
+    assert len(keys) == 9
+    for key in keys:
+        variant = key.split("/")[1]
+        A, B, ref, rows = g[key + "/A"], g[key + "/B"], g[key + "/ref_C"], int(g[key + "/rows"])
+        got = O.batch_matmul(A, B, variant, rows=rows)
+        assert np.array_equal(got, ref), key
+        c64, S = O.batch_matmul(A, B, variant, rows=rows, f64=True)
+        assert (np.abs(got - c64) <= 1e-5 * S + 1e-30).all(), key
+        if O.ref_lib() is not None:
+            assert np.array_equal(O.ref_batch_matmul(A, B, variant, rows=rows), ref), key
+
+
+def test_pooling_oracle_against_the_reference_loops(oracle_mod):
+    """Forward max / average (padding ignored) and their gradients reproduce the stored outputs of the reference's own
+    CPU loops (tests/golden/pool_golden.npz) bit for bit on inputs with ties; the variants those loops do not have are
+    tied to them by identities: the index points at an element equal to the maximum, the indexed gradient hands
+    every output gradient to exactly one input element, the plain average equals the padded-count one where no
+    window leaves the image."""
+    O = oracle_mod
+    g = _golden("pool_golden.npz")
+    names = sorted({k.split("/")[0] for k in g.files})
+    assert len(names) == 6
+    for name in names:
+        N, IH, IW, IC, FH, FW, sh, sw, ph, pw = (int(v) for v in g[name + "/shape"])
+        X, dY = g[name + "/X"], g[name + "/dY"]
+        win = (FH, FW, sh, sw, ph, pw)
+        Y = O.pool2D(X, *win, op="max")
+        assert np.array_equal(Y, g[name + "/ref_max"]), name
+        assert np.array_equal(O.pool2D(X, *win, op="avg_ignore_padding"), g[name + "/ref_avg_ip"]), name
+        assert np.array_equal(O.upool2D(dY, IH, IW, *win, op="max", Y=Y, X=X), g[name + "/ref_d_max"]), name
+        assert np.array_equal(O.upool2D(dY, IH, IW, *win, op="avg_ignore_padding"), g[name + "/ref_d_avg_ip"]), name
+        Yi, Index = O.pool2D(X, *win, op="max_indexed")
+        assert np.array_equal(Yi, Y) and np.array_equal(X.reshape(-1)[Index], Y), name
+        dXi = O.upool2D(dY, IH, IW, *win, op="max_indexed", Index=Index)
+        assert abs(float(dXi.astype(np.float64).sum()) - float(dY.astype(np.float64).sum())) <= 1e-4 * np.abs(dY).sum()
+        assert np.count_nonzero(dXi) <= dY.size
+        if ph == 0 and pw == 0:
+            assert np.array_equal(O.pool2D(X, *win, op="avg"), O.pool2D(X, *win, op="avg_ignore_padding")), name
+            a, b = O.upool2D(dY, IH, IW, *win, op="avg"), O.upool2D(dY, IH, IW, *win, op="avg_ignore_padding")
+            assert np.abs(a - b).max() <= 1e-6 * np.abs(b).max(), name
+        if O.ref_lib() is not None:
+            assert np.array_equal(O.ref_pool2D(X, *win, op="max"), g[name + "/ref_max"]), name
+            assert np.array_equal(O.ref_upool2D(dY, IH, IW, *win, op="avg"), g[name + "/ref_d_avg_ip"]), name
