@@ -12,7 +12,7 @@
 //             avg_ip       Y = (sum over valid positions) / (number of them)   pool2D_avg_ip_kernel.cuh
 //   backward  max          dX = sum over covering windows of (X >= Y) * dY     upool2D_max_kernel.cuh:52-100
 //             max_indexed  dX = sum over covering windows of (Index == me) * dY upool2d_max_indexed_kernel.cuh:44-100
-//             avg / avg_ip dX = sum over covering windows of dY / (FH * FW)  or  / (valid positions of that window)
+//             avg / avg_ip dX = sum over covering windows of dY * (1 / (FH * FW))  or  dY / (valid positions of that window)
 // (file names under src/cu32_src/Cuda_pool2D/Cuda_pool2D and src/cu32_src/Cuda_upool2D/Cuda_upool2D).
 #include "../../include/alpha_conv_b200.h"
 #include "host_common.h"
@@ -63,6 +63,8 @@ __device__ __forceinline__ void vmax(float& a, float x) { a = fmaxf(a, x); }
 __device__ __forceinline__ void vmax(float4& a, const float4& x) { a.x = fmaxf(a.x, x.x); a.y = fmaxf(a.y, x.y); a.z = fmaxf(a.z, x.z); a.w = fmaxf(a.w, x.w); }
 __device__ __forceinline__ void vadd(float& a, float x) { a += x; }
 __device__ __forceinline__ void vadd(float4& a, const float4& x) { a.x += x.x; a.y += x.y; a.z += x.z; a.w += x.w; }
+__device__ __forceinline__ void vfma(float& a, float s, float x) { a = fmaf(s, x, a); }
+__device__ __forceinline__ void vfma(float4& a, float s, const float4& x) { a.x = fmaf(s, x.x, a.x); a.y = fmaf(s, x.y, a.y); a.z = fmaf(s, x.z, a.z); a.w = fmaf(s, x.w, a.w); }
 __device__ __forceinline__ float vdiv(float a, float d) { return a / d; }
 __device__ __forceinline__ float4 vdiv(const float4& a, float d) { return make_float4(a.x / d, a.y / d, a.z / d, a.w / d); }
 // the index follows the maximum: it moves to `off` unless x < v (so the last of several equal maxima wins)
@@ -150,6 +152,7 @@ __global__ void __launch_bounds__(256) pool_bwd_kernel(const float* __restrict__
     const unsigned cq = static_cast<unsigned>(d.IC / V);
     const unsigned total = static_cast<unsigned>(d.N) * d.IH * d.IW * cq;
     const FastDiv by_cq = V == 4 ? d.by_cq4 : d.by_cq1;
+    const float alpha = 1.0f / static_cast<float>(d.FH * d.FW);
     for (unsigned e = blockIdx.x * blockDim.x + threadIdx.x; e < total; e += gridDim.x * blockDim.x) {
         unsigned pix, cc, uiw, uih, un;
         by_cq.divmod(e, pix, cc);
@@ -179,7 +182,7 @@ __global__ void __launch_bounds__(256) pool_bwd_kernel(const float* __restrict__
                 } else if (OP == kBwdMaxIndexed) {
                     vsel_eq(v, *reinterpret_cast<const I*>(Index + yo), static_cast<int>(xoff), dy);
                 } else if (OP == kBwdAvg) {
-                    vadd(v, dy);
+                    vfma(v, alpha, dy);   // v += alpha * deltaY per window, as upool2D_avg_kernel.cuh:84-94 does
                 } else {
                     // positions of this window that lie inside the image
                     int h0 = oh * d.sh - d.ph, h1 = h0 + d.FH, w0 = ow * d.sw - d.pw, w1 = w0 + d.FW;
@@ -190,7 +193,6 @@ __global__ void __launch_bounds__(256) pool_bwd_kernel(const float* __restrict__
                     vadd(v, vdiv(dy, static_cast<float>((h1 - h0) * (w1 - w0))));
                 }
             }
-        if (OP == kBwdAvg) v = vdiv(v, static_cast<float>(d.FH * d.FW));
         *reinterpret_cast<F*>(dX + xoff) = v;
     }
 }

@@ -464,8 +464,8 @@ int alpha_upool2D_max(const AlphaPoolShape* s, const float* deltaY, const float*
 /* deltaX = sum over the windows that contain the element of (Index == its offset) * deltaY
  * (upool2d_max_indexed_kernel.cuh:44-100) */
 int alpha_upool2D_max_indexed(const AlphaPoolShape* s, const float* deltaY, const int* Index, float* deltaX, alpha_stream_t stream);
-/* deltaX = sum over the windows that contain the element of deltaY / (FH * FW), or with ignore_padding / (positions of
- * that window inside the image) (upool2D_avg_kernel.cuh, upool2D_avg_ip_kernel.cuh) */
+/* deltaX = sum over the windows that contain the element of deltaY * (1 / (FH * FW)), or with ignore_padding of
+ * deltaY / (positions of that window inside the image) (upool2D_avg_kernel.cuh:84-94, upool2D_avg_ip_kernel.cuh) */
 int alpha_upool2D_avg(const AlphaPoolShape* s, const float* deltaY, float* deltaX, int ignore_padding, alpha_stream_t stream);
 
 /* Cuda_pool2D natives (z/dragon/engine/cuda/impl/math/Cuda_pool2D.java:124, :183, :241, :298) */

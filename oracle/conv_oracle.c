@@ -527,7 +527,7 @@ void oracle_pool2D(const float *X, float *Y, int *Index, int N, int IH, int IW, 
  * over the output windows that contain it.
  *   op 0 max:      deltaY where !(Y > X)                         (needs X, Y)
  *   op 1 indexed:  deltaY where Index == offset of the element   (upool2d_max_indexed_kernel.cuh:44-100)
- *   op 2 avg:      (sum of deltaY) / (FH * FW)                   (upool2D_avg_kernel.cuh)
+ *   op 2 avg:      sum of alpha * deltaY, alpha = 1 / (FH * FW)  (upool2D_avg_kernel.cuh:84-94)
  *   op 3 avg ip:   sum of deltaY / (positions of that window inside the image)
  */
 void oracle_upool2D(const float *deltaY, const float *Y, const float *X, const int *Index, float *deltaX, int N, int IH,
@@ -538,6 +538,7 @@ void oracle_upool2D(const float *deltaY, const float *Y, const float *X, const i
             for (int iw = 0; iw < IW; iw++)
                 for (int ic = 0; ic < IC; ic++) {
                     const long long xo = (((long long)n * IH + ih) * IW + iw) * IC + ic;
+                    const float alpha = 1.0f / (float)(FH * FW);
                     float v = 0.f;
                     for (int oh = 0; oh < OH; oh++) {
                         const int fh = ih - (oh * sh - ph);
@@ -552,7 +553,7 @@ void oracle_upool2D(const float *deltaY, const float *Y, const float *X, const i
                             } else if (op == 1) {
                                 if (Index[yo] == (int)xo) v += deltaY[yo];
                             } else if (op == 2) {
-                                v += deltaY[yo];
+                                v += alpha * deltaY[yo];
                             } else {
                                 int h0 = oh * sh - ph, h1 = h0 + FH, w0 = ow * sw - pw, w1 = w0 + FW;
                                 if (h0 < 0) h0 = 0;
@@ -563,7 +564,6 @@ void oracle_upool2D(const float *deltaY, const float *Y, const float *X, const i
                             }
                         }
                     }
-                    if (op == 2) v = v / (float)(FH * FW);
                     deltaX[xo] = v;
                 }
 }
