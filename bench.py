@@ -895,6 +895,9 @@ def run_ours(args):
             lib.set_math_mode(args.math)
         wino["note"] = "TFLOP/s credited with the direct convolution's FLOPs; AUTO never selects this variant"
 
+    # ---- operators next to the convolutions: batched matrix products and pooling (rank 0, single GPU runs only) ----
+    neighbours = neighbour_ops(env) if (extras and rank == 0 and world == 1) else None
+
     # ---- the reference's own GPU kernels on the same tensors (rank 0, single GPU runs only) ----
     cu32 = cu32_baseline(env, sweep) if (extras and rank == 0 and world == 1 and not args.no_cu32) else None
 
@@ -942,12 +945,69 @@ def run_ours(args):
             "roofline": roofline, "tf32_peak": tf32_peak, "cpu_baseline": cpu, "cu32_baseline": cu32, "e2e": e2e,
             "gpu_launches": int(launches), "clocks": clocks,
             "per_op_tflops": {k: round(v, 1) for k, v in per_op_tflops.items()},
-            "tf32": tf32, "winograd": wino, "config3": config3, "allreduce_check": ar_check,
+            "tf32": tf32, "winograd": wino, "neighbours": neighbours, "config3": config3, "allreduce_check": ar_check,
             "graph_error": headline_graph_error,
         }
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+def neighbour_ops(env):
+    """Batched matrix products (Cuda_batchMatMul) and pooling (Cuda_pool2D / Cuda_upool2D) through the same library:
+    CUDA events over 20 calls each after 3 warm-up calls, device tensors resident.  Products: the shape of the
+    reference's own table (batch 32 x 8, N = M = 128, K = 256) in TFLOP/s; pooling: the max pool after an ImageNet
+    stem (256 x 112 x 112 x 64, 3x3 s2 p1) and its gradient as algorithmic bytes per second against the measured
+    copy bandwidth."""
+    from __graft_entry__ import submodule
+    torch, lib = env["torch"], env["lib"]
+    E = submodule("engine").Engine()
+    dev = env["dev"]
+
+    def timed(f, iters=20):
+        for _ in range(3):
+            f()
+        torch.cuda.synchronize()
+        e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            f()
+        e1.record(); torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / iters
+
+    out = {}
+    try:
+        g = torch.Generator(device=dev); g.manual_seed(11)
+        Bt, N, M, K = 256, 128, 128, 256
+        A = torch.randn((Bt, N, K), device=dev, generator=g); Bm = torch.randn((Bt, K, M), device=dev, generator=g)
+        A1 = torch.randn((Bt, K, N), device=dev, generator=g); B2 = torch.randn((Bt, M, K), device=dev, generator=g)
+        fl = 2.0 * Bt * N * M * K
+        bm = {"shape": "batch 256, N = M = 128, K = 256", "unit": "TFLOP/s"}
+        for name, f in (("batchMatMul", lambda: E.batchMatMul(A, Bm)), ("batchMatMulT1", lambda: E.batchMatMulT1(A1, Bm)),
+                        ("batchMatMulT2", lambda: E.batchMatMulT2(A, B2))):
+            ms = timed(f)
+            bm[name] = {"ms": round(ms, 4), "tflops": round(fl / ms / 1e9, 1), "algo": lib.last_algo()}
+        out["batch_matmul"] = bm
+        del A, Bm, A1, B2
+        X = torch.randn((256, 112, 112, 64), device=dev, generator=g)
+        win = (3, 3, 2, 2, 1, 1)
+        Y = E.pool2D_max(X, *win)
+        dY = torch.randn(Y.shape, device=dev, generator=g)
+        xb, yb = 4.0 * X.numel(), 4.0 * Y.numel()
+        peak = measured_peaks()["hbm_gbs"]
+        pl = {"shape": "256 x 112 x 112 x 64, 3x3 s2 p1", "unit": "GB/s of algorithmic bytes", "hbm_peak_gbs": peak}
+        for name, f, nbytes in (("pool2D_max", lambda: E.pool2D_max(X, *win), xb + yb),
+                                ("pool2D_avg", lambda: E.pool2D_avg(X, *win), xb + yb),
+                                ("upool2D_max", lambda: E.upool2D_max(dY, Y, X, *win), 2 * xb + 2 * yb),
+                                ("upool2D_avg", lambda: E.upool2D_avg(dY, 112, 112, *win), xb + yb)):
+            ms = timed(f)
+            gbs = nbytes / ms / 1e6
+            pl[name] = {"ms": round(ms, 4), "gbs": round(gbs, 0), "frac_of_hbm_peak": round(gbs / peak, 3)}
+        out["pool"] = pl
+        out["kernel_status"] = lib.device_status()
+    except Exception as e:      # a sub-record must not take the headline down with it
+        out["error"] = "%s: %s" % (type(e).__name__, str(e)[:200])
+    return out
 
 
 def run_e2e(args, torch, dist, dev, world, layers, run_op, step_flops, B, comm_stream):
