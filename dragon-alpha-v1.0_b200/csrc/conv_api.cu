@@ -60,7 +60,7 @@ enum Opt {
     OPT_HALO_ROW, OPT_HALO_JH, OPT_HALO_JW, OPT_HALO_STACK, OPT_HALO_WIDE, OPT_HALO_PAIR, OPT_HALO_FLAT,
     OPT_HALO_NARROW, OPT_HALO_DUAL, OPT_PATCH_MATRIX, OPT_DX_PHASES, OPT_DX_COL2IM, OPT_DX_TRANSPOSE,
     OPT_DW_STACKED, OPT_DW_DIAG, OPT_DW_CW, OPT_DW_R, OPT_DW_STATIC, OPT_CONV_PROF, OPT_SM_BUDGET,
-    OPT_SKINNY, OPT_HALO_DEEP, OPT_HALO_SPLITB, OPT_NVTX, OPT_DW_LANES, OPT_HALO_TAPSTACK,
+    OPT_SKINNY, OPT_HALO_DEEP, OPT_HALO_SPLITB, OPT_NVTX, OPT_DW_LANES, OPT_HALO_TAPSTACK, OPT_HALO_FLAT32,
     OPT_COUNT
 };
 struct OptDef { const char* name; int dflt; };
@@ -69,7 +69,7 @@ static const OptDef kOptDefs[OPT_COUNT] = {
     {"HALO_ROW", 1}, {"HALO_JH", 0}, {"HALO_JW", 0}, {"HALO_STACK", 1}, {"HALO_WIDE", -1}, {"HALO_PAIR", -1}, {"HALO_FLAT", 1},
     {"HALO_NARROW", 1}, {"HALO_DUAL", 1}, {"PATCH_MATRIX", 1}, {"DX_PHASES", 1}, {"DX_COL2IM", 1}, {"DX_TRANSPOSE", 1},
     {"DW_STACKED", -1}, {"DW_DIAG", 1}, {"DW_CW", 0}, {"DW_R", 0}, {"DW_STATIC", 1}, {"CONV_PROF", 0}, {"SM_BUDGET", 0},
-    {"SKINNY", 1}, {"HALO_DEEP", 1}, {"HALO_SPLITB", 0}, {"NVTX", 1}, {"DW_LANES", 0}, {"HALO_TAPSTACK", 1},
+    {"SKINNY", 1}, {"HALO_DEEP", 1}, {"HALO_SPLITB", 0}, {"NVTX", 1}, {"DW_LANES", 0}, {"HALO_TAPSTACK", 1}, {"HALO_FLAT32", 1},
 };
 static std::atomic<int> g_opt[OPT_COUNT];
 static std::once_flag g_opt_once;
@@ -834,15 +834,15 @@ static HaloChoice plan_halo(const IgemmPlan& pl, int BN, int mode3x, int b_mn, i
 }
 
 // ---- halo kernel on CTA pairs ----------------------------------------------------------------------
-template <int FW_T, bool ROW_T>
+template <int FW_T, bool ROW_T, bool FLAT_T = false>
 static void halo_pair_launch_one(const HaloLaunch& L)
 {
     static bool attr_done = false;
     if (!attr_done) {
-        cudaFuncSetAttribute(conv_halo_pair_kernel<FW_T, ROW_T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        cudaFuncSetAttribute(conv_halo_pair_kernel<FW_T, ROW_T, FLAT_T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         attr_done = true;
     }
-    if (!t_dry) conv_halo_pair_kernel<FW_T, ROW_T><<<L.grid, kHaloThreads, L.smem, L.stream>>>(*L.tmA, *L.tmB, *L.tmBlo, *L.tmO, *L.p);
+    if (!t_dry) conv_halo_pair_kernel<FW_T, ROW_T, FLAT_T><<<L.grid, kHaloThreads, L.smem, L.stream>>>(*L.tmA, *L.tmB, *L.tmBlo, *L.tmO, *L.p);
 }
 
 // One 16 x 8 pixel accumulator per CTA, two CTAs per MMA.  Returns 1 when the shape does not fit.
@@ -880,6 +880,17 @@ static int launch_halo_pair(DeviceCtx* c, const IgemmPlan& pl, int mode3x, cudaS
     if (p.PH > 256) return 1;
     p.row_blocks = NI > 1 ? 1 : (pl.oH + 15) / 16;
     p.col_blocks = (pl.oW + 7) / 8;
+    // accumulators of 4 rows x 32 patch columns where they hold more real pixels than 16 x 8 ones (option HALO_FLAT32:
+    // 0 never, 2 wherever the shape allows)
+    bool flat32 = false;
+    if (NI == 1 && pl.oW + pl.FW - 1 <= 32 && pl.oSH == 1 && pl.oSW == 1 && pl.oNH == 0 && pl.oNW == 0 && opt(OPT_HALO_FLAT32)) {
+        const long long lanes16 = (long long)p.row_blocks * p.col_blocks * 128, lanes4 = (long long)((pl.oH + 3) / 4) * 128;
+        flat32 = lanes4 * 10 <= lanes16 * 9 || opt(OPT_HALO_FLAT32) == 2;
+    }
+    if (flat32) {
+        p.PH = 4 + pl.FH - 1; p.PW = 32;
+        p.row_blocks = (pl.oH + 3) / 4; p.col_blocks = 1;
+    }
     p.n_blocks = (p.N + NI - 1) / NI;
     const long long per_ntile = (long long)p.n_blocks * p.row_blocks * p.col_blocks;
     if (per_ntile % 2 != 0) return 1;   // the two tiles of a pair must share their W tiles
@@ -934,16 +945,17 @@ static int launch_halo_pair(DeviceCtx* c, const IgemmPlan& pl, int mode3x, cudaS
     cuuint64_t od[4] = {(cuuint64_t)pl.ncols, (cuuint64_t)pl.oW, (cuuint64_t)pl.oH, (cuuint64_t)pl.aN};
     cuuint64_t ost[3] = {(cuuint64_t)pl.oSW * pl.ncols * 4, (cuuint64_t)pl.oSH * oNW * pl.ncols * 4,
                          (cuuint64_t)oNH * oNW * pl.ncols * 4};
-    cuuint32_t obox[4] = {32, 8, (cuuint32_t)(NI > 1 ? pl.oH : 16), 1};
+    cuuint32_t obox[4] = {32, (cuuint32_t)(flat32 ? 32 : 8), (cuuint32_t)(flat32 ? 4 : (NI > 1 ? pl.oH : 16)), 1};
     rc = make_tiled_map(&tmO, pl.out, 4, od, ost, obox, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
     int pairs = sm_budget(c) / 2;
     if (pairs > p.total_tiles / 2) pairs = p.total_tiles / 2;
     HaloLaunch L{2 * pairs, smem, stream, &tmA, &tmB, &tmBlo, &tmO, &p};
-    if (row) halo_pair_launch_one<3, true>(L); else halo_pair_launch_one<3, false>(L);
+    if (flat32) { if (row) halo_pair_launch_one<3, true, true>(L); else halo_pair_launch_one<3, false, true>(L); }
+    else if (row) halo_pair_launch_one<3, true>(L); else halo_pair_launch_one<3, false>(L);
     note_launch(row ? "halo_pair_row" : "halo_pair_tap");
-    snprintf(g_plan, sizeof(g_plan), "halo_pair%s%s NI=%d BN=%d npb=%d sb=%d acc=%d", row ? "_row" : "_tap", wide ? " wide" : (three ? (side3 ? " three+side" : " three") : ""), NI, BN,
-             p.npb, sb, p.acc_bufs);
+    snprintf(g_plan, sizeof(g_plan), "halo_pair%s%s%s NI=%d BN=%d npb=%d sb=%d acc=%d", row ? "_row" : "_tap", wide ? " wide" : (three ? (side3 ? " three+side" : " three") : ""),
+             flat32 ? " flat32" : "", NI, BN, p.npb, sb, p.acc_bufs);
     return check_launch("conv_halo_pair_kernel");
 }
 

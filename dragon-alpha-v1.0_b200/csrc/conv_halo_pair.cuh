@@ -58,9 +58,14 @@ __device__ __forceinline__ void issue_chunk_pair(uint32_t d, uint32_t a_lo, uint
 }
 
 // FW_T: compile-time filter width; ROW_T: one B stage holds the FW_T taps of a filter row.
+// FLAT_T: the accumulator is 4 output rows x 32 patch columns instead of 16 x 8: the patch has a pitch of exactly 32
+// pixels, so the 128 lanes are 128 CONSECUTIVE patch positions (8-row groups 1024 B apart), a tap is still a constant
+// shift (fh * 32 + fw positions), and the columns 30, 31 of every row are idle lanes.  For images at most 30 pixels
+// wide whose height 16 x 8 tiles fill badly (28 x 28: 0.875 of the lanes instead of 0.77); the epilogue's 32-column
+// store box is clipped at the image edge by the TMA.
 // p.mode3x is 0 (plain TF32), 1 (3xTF32, three MMAs), 4 (the same with side columns) or 2 (wide 3xTF32); p.JH == p.JW == 1; p.total_tiles is even and the
 // tiles 2k, 2k+1 lie in the same output-channel block.  p.b_bytes = bytes of one tap's W tile per CTA.
-template <int FW_T, bool ROW_T>
+template <int FW_T, bool ROW_T, bool FLAT_T = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kHaloThreads, 1)
     conv_halo_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                           const __grid_constant__ CUtensorMap tmBlo, const __grid_constant__ CUtensorMap tmO,
@@ -152,7 +157,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kHaloThreads, 1)
                 const int nb = r / per_img;
                 r -= nb * per_img;
                 const int rb = r / p.col_blocks, cb = r - rb * p.col_blocks;
-                const int h0 = rb * 16 - p.pad_h, w0 = cb * 8 - p.pad_w;
+                const int h0 = rb * (FLAT_T ? 4 : 16) - p.pad_h, w0 = FLAT_T ? -p.pad_w : cb * 8 - p.pad_w;
                 const int n = nb * p.NI;
                 const int oc0 = tn * p.BN;
                 for (int c = 0; c < p.kchunks && ok; ++c) {
@@ -200,8 +205,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kHaloThreads, 1)
             // ---- MMA issuer (leader CTA only) ----
             RingPos pp, bp, ap;
             bool ok = true;
-            constexpr uint32_t kPW8 = (8 + FW_T - 1) * 8;   // one patch row, in 16-byte units
-            const uint32_t a_dhi = smem_desc_hi(p.PW * 128, kSwizzle128B);
+            constexpr uint32_t kPW8 = FLAT_T ? 256u : (8 + FW_T - 1) * 8;   // one patch row, in 16-byte units
+            const uint32_t a_dhi = smem_desc_hi(FLAT_T ? 1024u : p.PW * 128, kSwizzle128B);
             const uint32_t b_dhi = smem_desc_hi(1024, kSwizzle128B);
             const uint32_t a_lo_off = p.patch_bytes >> 4;
             const uint32_t q_off = ((three ? 1u : 2u) * half_rows * 128) >> 4;   // region Q of a wide W tile / the W_lo rows
@@ -317,7 +322,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kHaloThreads, 1)
             const int rb = r / p.col_blocks, cb = r - rb * p.col_blocks;
             const int n = nb * p.NI;
             const int n0 = tn * p.BN;
-            const int oh0 = rb * 16, ow0 = cb * 8;
+            const int oh0 = rb * (FLAT_T ? 4 : 16), ow0 = FLAT_T ? 0 : cb * 8;
             const uint32_t tcol = lane_base + ap.idx * accw;
             for (int c = 0; c < p.BN; c += 32) {
                 const int col0 = n0 + c;

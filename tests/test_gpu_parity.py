@@ -459,3 +459,64 @@ def test_tap_stacked_kernel_is_chosen_for_the_64_channel_layer(pkg, eng):
     eng.conv3D(X, W, 1, 1, 1, 1)
     assert lib.last_algo() != "halo_tapstack"
     assert lib.device_status() == 0
+
+
+# CTA-pair kernel with accumulators of 4 rows x 32 patch columns (images at most 30 pixels wide).
+FLAT32_CASES = {
+    "flat_28x28x128": (4, 28, 28, 128, 128, 3, 3, 1, 1, 1, 1),     # the benchmark's second layer
+    "flat_ragged_rows": (4, 13, 30, 64, 128, 3, 3, 1, 1, 1, 1),    # OH % 4 != 0, the widest image the form takes
+    "flat_narrow": (6, 9, 5, 32, 64, 3, 3, 1, 1, 1, 1),
+    "flat_nopad": (4, 18, 22, 64, 128, 3, 3, 1, 1, 0, 0),
+    "flat_oc256": (2, 12, 28, 64, 256, 3, 3, 1, 1, 1, 1),
+}
+CASES.update(FLAT32_CASES)
+
+
+@pytest.mark.parametrize("mode", ["3xtf32", "tf32"])
+@pytest.mark.parametrize("name", list(FLAT32_CASES))
+def test_pair_kernel_with_flat_tiles(pkg, eng, oracle_mod, name, mode):
+    """Forced (options HALO_PAIR, HALO_FLAT32) on shapes it would not always be chosen for, against the oracle, and
+    bit for bit against the same kernel with 16 x 8 tiles in 3xTF32 (same products, same order per output)."""
+    import torch
+    L = pkg.submodule("lib")
+    old_pair, old_flat = L.set_option("HALO_PAIR", 3 if mode == "3xtf32" else 1), L.set_option("HALO_FLAT32", 2)
+    old_skinny = L.set_option("SKINNY", 0)     # at these batches the layers have few tiles; the benchmark's batch does not
+    try:
+        res, (X, W, B, dY, Y, dX, dW) = _run_case(pkg, eng, oracle_mod, name, mode)
+        assert res["status"] == 0 and res["fwd_algo"].startswith("halo_pair"), res["fwd_algo"]
+        tol = TOL[mode]
+        for op in ("fwd", "dx"):
+            m = res[op]
+            assert m["finite"] and m["norm"] <= tol["norm"] and m["comp"] <= tol["comp"], (name, op, res[op + "_algo"], m)
+        dev = torch.device("cuda:0")
+        N, IH, IW, IC, OC, FH, FW, sh, sw, ph, pw = CASES[name]
+        tX, tW, tB = (torch.from_numpy(a).to(dev) for a in (X, W, B))
+        eng.conv3D_biased(tX, tW, tB, sh, sw, ph, pw)
+        assert "flat32" in L.last_plan(), L.last_plan()
+        L.set_option("HALO_FLAT32", 0)
+        Y0 = eng.conv3D_biased(tX, tW, tB, sh, sw, ph, pw).cpu().numpy()
+        assert "flat32" not in L.last_plan() and L.last_plan().startswith("halo_pair"), L.last_plan()
+        if mode == "3xtf32":
+            np.testing.assert_array_equal(Y0, Y)
+        else:
+            assert np.abs(Y0 - Y).max() <= 5e-5 * np.abs(Y).max()
+    finally:
+        L.set_option("HALO_PAIR", old_pair)
+        L.set_option("HALO_FLAT32", old_flat)
+        L.set_option("SKINNY", old_skinny)
+
+
+def test_flat_tiles_are_chosen_for_28x28(pkg, eng):
+    import torch
+    lib = pkg.submodule("lib")
+    dev = torch.device("cuda:0")
+    lib.set_math_mode("3xtf32")
+    X = torch.zeros((256, 28, 28, 128), device=dev)
+    W = torch.zeros((128, 3, 3, 128), device=dev)
+    eng.conv3D(X, W, 1, 1, 1, 1)
+    assert "halo_pair" in lib.last_plan() and "flat32" in lib.last_plan(), lib.last_plan()
+    X = torch.zeros((256, 14, 14, 256), device=dev)
+    W = torch.zeros((256, 3, 3, 256), device=dev)
+    eng.conv3D(X, W, 1, 1, 1, 1)
+    assert "halo_pair" in lib.last_plan() and "flat32" not in lib.last_plan(), lib.last_plan()
+    assert lib.device_status() == 0
