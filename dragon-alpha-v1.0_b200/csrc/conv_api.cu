@@ -681,6 +681,7 @@ struct HaloChoice {
     bool valid = false;
     int JH = 1, JW = 1, npb = 1, sb = 2, acc_bufs = 1, NI = 1;
     bool row = false, stat = false, wide = false;
+    bool flat = false;   // accumulators of 4 rows x 32 patch columns, one patch each (JH * JW of them per macro tile)
     double cost = 0, eff = 0;
 };
 
@@ -702,15 +703,15 @@ struct HaloLaunch {
     const HaloParams* p;
 };
 
-template <int FW_T, int JH_T, int JW_T, bool ROW_T>
+template <int FW_T, int JH_T, int JW_T, bool ROW_T, bool FLAT_T = false>
 static void halo_launch_one(const HaloLaunch& L)
 {
     static bool attr_done = false;  // per instantiation; the attribute is per function, any device
     if (!attr_done) {
-        cudaFuncSetAttribute(conv_halo_kernel<FW_T, JH_T, JW_T, ROW_T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        cudaFuncSetAttribute(conv_halo_kernel<FW_T, JH_T, JW_T, ROW_T, FLAT_T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         attr_done = true;
     }
-    if (!t_dry) conv_halo_kernel<FW_T, JH_T, JW_T, ROW_T><<<L.grid, kHaloThreads2, L.smem, L.stream>>>(*L.tmA, *L.tmB, *L.tmBlo, *L.tmO, *L.p);
+    if (!t_dry) conv_halo_kernel<FW_T, JH_T, JW_T, ROW_T, FLAT_T><<<L.grid, kHaloThreads2, L.smem, L.stream>>>(*L.tmA, *L.tmB, *L.tmBlo, *L.tmO, *L.p);
 }
 
 template <int FW_T>
@@ -830,6 +831,55 @@ static HaloChoice plan_halo(const IgemmPlan& pl, int BN, int mode3x, int b_mn, i
                 best.acc_bufs = acc_bufs; best.cost = cost; best.eff = eff; best.row = row; best.stat = stat; best.NI = NI; best.wide = wide != 0;
             }
         }
+    // Flat tiles (images at most 30 pixels wide, 3x3 filters, K-major W): two accumulators of 4 rows x 32 patch
+    // columns per W tile, each with its own patch, taken from the list of all four-row blocks of the batch - a
+    // 28 x 28 image is seven of them, which 16 x 8 tiles cover with 0.77 of their lanes and these with 0.875.
+    if (opt(OPT_HALO_FLAT32) && allow_row && !b_mn && pl.FW == 3 && pl.oW + pl.FW - 1 <= 32 && !pl.w_img_rows &&
+        pl.oSH == 1 && pl.oSW == 1 && pl.oNH == 0 && pl.oNW == 0 && 2 * 2 * BN <= 512 && !force_jh && !force_jw) {
+        const int J = 2, wide = (mode3x && BN <= 128 && wide_env != 0) ? 1 : 0;
+        const int accw = wide ? 2 * BN : BN;
+        const int PHf = 4 + pl.FH - 1;
+        const uint32_t patch_stride = (uint32_t)J * PHf * 32 * 128 * planes;
+        bool row = true;
+        uint32_t b_stride = b_tile * pl.FW;
+        if ((size_t)patch_stride + 2 * (size_t)b_stride + 32768 + 1536 > smem_cap) { row = false; b_stride = b_tile; }
+        const int max_sb = row ? pl.FH * 2 : 8;
+        int npb = 2, sb = row ? 3 : 4;
+        auto need = [&](int a, int b) { return (size_t)a * patch_stride + (size_t)b * b_stride + 32768 + 512 + 1024; };
+        while (need(npb, sb) > smem_cap && sb > 2) --sb;
+        if (need(npb, sb) > smem_cap) { npb = 1; sb = 4; while (need(npb, sb) > smem_cap && sb > 2) --sb; }
+        if (need(npb, sb) <= smem_cap && J * accw * 1 <= 512) {
+            while (sb < max_sb && need(npb, sb + 1) <= smem_cap && sb < taps) ++sb;
+            const int acc_bufs = (2 * J * accw <= 512) ? 2 : 1;
+            const long long rb4 = (pl.oH + 3) / 4, blocks = (long long)pl.aN * rb4, macro = (blocks + J - 1) / J;
+            const double eff = (double)pl.aN * pl.oH * pl.oW / ((double)macro * J * 128.0);
+            auto clk = [](double n) { return n / 2.0 > 59.0 ? n / 2.0 : 59.0; };
+            const double step_clk = wide ? clk(2.0 * BN) + clk(BN) : (mode3x ? 3 : 1) * clk(BN);
+            const double t_mma = (double)taps * kchunks * 4 * J * step_clk;
+            const double step_bytes = wide ? (4096.0 + 64.0 * BN) + (4096.0 + 32.0 * BN) : (mode3x ? 3 : 1) * (4096.0 + 32.0 * BN);
+            const double patch_b = (double)J * PHf * 32 * 128;
+            const double tma_bytes = (double)kchunks * (patch_b + (double)taps * b_tx * planes);
+            const double smem_bytes = (double)taps * kchunks * 4 * J * step_bytes + tma_bytes + (mode3x ? 2.0 * kchunks * patch_b : 0.0) +
+                                      2.0 * 128 * J * BN * 4;
+            const double t_smem = smem_bytes / 128.0;
+            const double bytes = (double)kchunks * (patch_b + 0.5 * taps * b_tx * planes) + 128.0 * J * BN * 4;
+            double t = t_mma + 1500.0;
+            if (t_smem + 500.0 > t) t = t_smem + 500.0;
+            if (bytes / 28.0 > t) t = bytes / 28.0;
+            if (npb == 1) t *= 1.25;
+            if (acc_bufs == 1) t *= 1.15;
+            if (!row) t *= 1.05;
+            const long long n_macro = (long long)((pl.ncols + BN - 1) / BN) * macro;
+            const double cost = t * (double)((n_macro + sm_count - 1) / sm_count);
+            const bool forced = opt(OPT_HALO_FLAT32) == 2;
+            // (few macro tiles: the 16 x 8 forms can split the reduction over idle SMs, this one cannot)
+            if (forced || (2 * n_macro > sm_count && (!best.valid || cost < 0.97 * best.cost))) {
+                best = HaloChoice{};
+                best.valid = true; best.JH = 2; best.JW = 1; best.npb = npb; best.sb = sb; best.acc_bufs = acc_bufs;
+                best.cost = cost; best.eff = eff; best.row = row; best.stat = true; best.NI = 1; best.wide = wide != 0; best.flat = true;
+            }
+        }
+    }
     return best;
 }
 
@@ -1142,6 +1192,16 @@ static int launch_halo(DeviceCtx* c, const IgemmPlan& pl_in, int mode3x, cudaStr
     p.row_blocks = ch.NI > 1 ? 1 : (pl.oH + 16 * ch.JH - 1) / (16 * ch.JH);
     p.col_blocks = (pl.oW + 8 * ch.JW - 1) / (8 * ch.JW);
     p.n_blocks = (p.N + ch.NI - 1) / ch.NI;
+    const int Jflat = ch.JH * ch.JW;
+    if (ch.flat) {
+        // the macro tiles index the list of all four-row blocks of the batch: row_blocks of them, in one "image block"
+        p.flat = 1; p.flat_rb4 = (pl.oH + 3) / 4;
+        const long long blocks = (long long)p.N * p.flat_rb4;
+        if (blocks > 2147483647LL) return 1;
+        p.flat_total = (int)blocks;
+        p.PH = 4 + pl.FH - 1; p.PW = 32;
+        p.n_blocks = 1; p.col_blocks = 1; p.row_blocks = (int)((blocks + Jflat - 1) / Jflat);
+    }
     const long long total = (long long)p.n_tiles * p.n_blocks * p.row_blocks * p.col_blocks;
     if (total > 2147483647LL) return 1;
     p.total_tiles = (int)total;
@@ -1157,7 +1217,7 @@ static int launch_halo(DeviceCtx* c, const IgemmPlan& pl_in, int mode3x, cudaStr
     p.idesc = make_idesc_tf32(kBM, BN, false, pl.b_mn);
     p.idesc_wide = make_idesc_tf32(kBM, ch.wide ? 2 * BN : BN, false, pl.b_mn);
     p.tmem_cols = pow2_cols(ch.acc_bufs * ch.JH * ch.JW * BN * (ch.wide ? 2 : 1));
-    p.patch_tx = (uint32_t)p.PH * p.PW * 128;
+    p.patch_tx = (uint32_t)p.PH * p.PW * 128 * (ch.flat ? Jflat : 1);
     p.patch_bytes = (p.patch_tx + 1023) & ~1023u;
     p.b_tx = pl.b_mn ? (BN / 32) * 4096 : BN * 128;
     p.b_bytes = (p.b_tx + 1023) & ~1023u;
@@ -1204,7 +1264,7 @@ static int launch_halo(DeviceCtx* c, const IgemmPlan& pl_in, int mode3x, cudaStr
     // computed as ksplit partial sums over disjoint ranges of the reduction chunks, each by its own
     // CTA, into scratch laid out as ksplit copies of the output; a second kernel adds them in order
     // (with the bias and the activation, which the partial sums must not see).
-    const int ksplit = halo_ksplit(pl, p.total_tiles, p.kchunks, sm_budget(c));
+    const int ksplit = ch.flat ? 1 : halo_ksplit(pl, p.total_tiles, p.kchunks, sm_budget(c));
     p.cps = (p.kchunks + ksplit - 1) / ksplit;
     p.ksplit = ksplit;
     float* out_ptr = pl.out;
@@ -1220,20 +1280,21 @@ static int launch_halo(DeviceCtx* c, const IgemmPlan& pl_in, int mode3x, cudaStr
     cuuint64_t od[4] = {(cuuint64_t)pl.ncols, (cuuint64_t)pl.oW, (cuuint64_t)pl.oH, (cuuint64_t)pl.aN * ksplit};
     cuuint64_t ost[3] = {(cuuint64_t)pl.oSW * pl.ncols * 4, (cuuint64_t)pl.oSH * oNW * pl.ncols * 4,
                          (cuuint64_t)oNH * oNW * pl.ncols * 4};
-    cuuint32_t obox[4] = {32, 8, (cuuint32_t)(ch.NI > 1 ? pl.oH : 16), 1};
+    cuuint32_t obox[4] = {32, (cuuint32_t)(ch.flat ? 32 : 8), (cuuint32_t)(ch.flat ? 4 : (ch.NI > 1 ? pl.oH : 16)), 1};
     rc = make_tiled_map(&tmO, out_ptr, 4, od, ost, obox, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
     const long long vtiles = (long long)p.total_tiles * ksplit;
     int grid = sm_budget(c) < vtiles ? sm_budget(c) : (int)vtiles;
     HaloLaunch L{grid, smem, stream, &tmA, &tmB, &tmBlo, &tmO, &p};
-    if (!ch.stat) halo_launch_one<0, 0, 0, false>(L);
+    if (ch.flat) { if (ch.row) halo_launch_one<3, 2, 1, true, true>(L); else halo_launch_one<3, 2, 1, false, true>(L); }
+    else if (!ch.stat) halo_launch_one<0, 0, 0, false>(L);
     else if (pl.FW == 1) halo_launch_fw<1>(L, ch.JH, ch.JW, ch.row);
     else if (pl.FW == 2) halo_launch_fw<2>(L, ch.JH, ch.JW, ch.row);
     else if (pl.FW == 3) halo_launch_fw<3>(L, ch.JH, ch.JW, ch.row);
     else halo_launch_fw<5>(L, ch.JH, ch.JW, ch.row);
     note_launch(ch.row ? "halo_row" : (ch.stat ? "halo_tap" : "halo"));
-    snprintf(g_plan, sizeof(g_plan), "halo%s%s%s JH=%d JW=%d NI=%d BN=%d npb=%d sb=%d acc=%d eff=%.2f ksplit=%d", ch.row ? "_row" : (ch.stat ? "_tap" : ""),
-             ch.wide ? " wide" : "", p.dual ? " dual" : "", ch.JH, ch.JW, ch.NI, BN, ch.npb, p.sb, ch.acc_bufs, ch.eff, ksplit);
+    snprintf(g_plan, sizeof(g_plan), "halo%s%s%s%s JH=%d JW=%d NI=%d BN=%d npb=%d sb=%d acc=%d eff=%.2f ksplit=%d", ch.row ? "_row" : (ch.stat ? "_tap" : ""),
+             ch.wide ? " wide" : "", p.dual ? " dual" : "", ch.flat ? " flat32" : "", ch.JH, ch.JW, ch.NI, BN, ch.npb, p.sb, ch.acc_bufs, ch.eff, ksplit);
     rc = check_launch("conv_halo_kernel");
     if (rc || ksplit == 1) return rc;
     const size_t n4 = out_floats / 4;

@@ -73,6 +73,9 @@ struct HaloParams {
     int dual;                 // 1: two MMA-issuing threads take alternate W-tile stages (sb is even)
     int split_b;              // 3xTF32: 1 = only the hi plane of every W tile is loaded and the split warps form its lo
                               // plane in shared memory (1x1 products, whose W traffic from L2 is what binds them)
+    int flat, flat_rb4, flat_total;   // flat = 1: accumulators of 4 output rows x 32 patch columns, each with its own patch of
+                              // FH + 3 rows x 32 pixels (images at most 30 pixels wide); macro tile t holds the accumulators
+                              // t * J ... of the flat_total = N * flat_rb4 four-row blocks of the batch (flat_rb4 per image)
     int w_img_rows;           // > 0: every image has its own W (batched matrix products); rows of W per image, added to the
                               // row coordinate of every W tile (stacked images and split-K are then off)
     int ksplit, cps;          // split-K: every tile is computed as ksplit partial sums over cps reduction chunks each;
@@ -174,35 +177,38 @@ __device__ __forceinline__ void issue_chunk_imm(uint32_t d, uint32_t d_side, uin
 
 // One filter tap into the JH_T x JW_T accumulators of a macro tile.  a_row / a_row_lo: descriptor
 // low halves of the patch row of this filter row (hi / lo plane); TAP_OFF = fw * 8.
-template <int MODE, int JH_T, int JW_T, uint32_t kPW8, uint32_t TAP_OFF>
+// FLAT_T: accumulator j reads its own patch, 6 rows x 32 pixels x 128 B = 1536 descriptor units after the previous one.
+template <int MODE, int JH_T, int JW_T, uint32_t kPW8, uint32_t TAP_OFF, bool FLAT_T = false>
 __device__ __forceinline__ void issue_tap(uint32_t d0, uint32_t a_row, uint32_t a_row_lo, uint32_t bl, const IssueConsts& k,
                                           uint32_t acc_first)
 {
     const uint32_t bl_lo = bl + k.b_lo_off;
     static_for<0, JH_T * JW_T>([&](auto j_) {
         constexpr uint32_t j = decltype(j_)::value, jh = j / JW_T, jw = j % JW_T;
+        constexpr uint32_t a_off = FLAT_T ? TAP_OFF + j * 1536u : TAP_OFF + jh * 16 * kPW8 + jw * 64;
         const uint32_t d = d0 + j * k.accw;
-        issue_chunk_imm<MODE, TAP_OFF + jh * 16 * kPW8 + jw * 64>(d, d + (k.accw >> 1), a_row, a_row_lo, k.a_dhi, bl, bl_lo, k.b_dhi,
-                                                                   k.idesc, k.idesc_wide, acc_first);
+        issue_chunk_imm<MODE, a_off>(d, d + (k.accw >> 1), a_row, a_row_lo, k.a_dhi, bl, bl_lo, k.b_dhi,
+                                     k.idesc, k.idesc_wide, acc_first);
     });
 }
 
 // The FW_T taps of one filter row (B stage holds them back to back, b_tile16 apart).
-template <int MODE, int FW_T, int JH_T, int JW_T, uint32_t kPW8>
+template <int MODE, int FW_T, int JH_T, int JW_T, uint32_t kPW8, bool FLAT_T = false>
 __device__ __forceinline__ void issue_row(uint32_t d0, uint32_t a_row, uint32_t bl, uint32_t b_tile16, const IssueConsts& k,
                                           uint32_t acc_first)
 {
     const uint32_t a_row_lo = a_row + k.a_lo_off;
     static_for<0, FW_T>([&](auto fw_) {
         constexpr uint32_t fw = decltype(fw_)::value;
-        issue_tap<MODE, JH_T, JW_T, kPW8, fw * 8>(d0, a_row, a_row_lo, bl + fw * b_tile16, k, fw == 0 ? acc_first : 1u);
+        issue_tap<MODE, JH_T, JW_T, kPW8, fw * 8, FLAT_T>(d0, a_row, a_row_lo, bl + fw * b_tile16, k, fw == 0 ? acc_first : 1u);
     });
 }
 
 // FW_T > 0 selects a specialisation with compile-time FW, JH and JW whose MMAs are issued as
 // straight-line code with immediate descriptor offsets; with ROW_T one B stage holds the FW taps of
 // one filter row, otherwise one tap.  FW_T == 0 is the generic form: any filter, one tap per stage.
-template <int FW_T, int JH_T, int JW_T, bool ROW_T>
+// FLAT_T (static forms only): the JH_T * JW_T accumulators are flat tiles of 4 rows x 32 patch columns, see HaloParams::flat.
+template <int FW_T, int JH_T, int JW_T, bool ROW_T, bool FLAT_T = false>
 __global__ void __launch_bounds__(kHaloThreads2, 1)
     conv_halo_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                      const __grid_constant__ CUtensorMap tmBlo, const __grid_constant__ CUtensorMap tmO,
@@ -300,7 +306,19 @@ __global__ void __launch_bounds__(kHaloThreads2, 1)
                 for (int c = tp.c0; c < tp.c1 && ok; ++c) {
                     if (!wait_prof(pempty_a + 8 * pp.idx, pp.phase ^ 1, prof_on, w_patch)) { report(p.status, kStatusProducerTimeout); ok = false; break; }
                     mbar_arrive_expect_tx_a(pfull_a + 8 * pp.idx, p.patch_tx);
-                    tma_load_4d_a(patches_a + pp.idx * patch_stride, &tmA, pfull_a + 8 * pp.idx, c * 32, w0, h0, n);
+                    if (FLAT_T) {
+                        // one patch per accumulator; rb is the macro tile's index, a block past the end repeats the last one
+                        const uint32_t sub = p.patch_tx / static_cast<uint32_t>(J);
+                        for (int j = 0; j < J; ++j) {
+                            int a = rb * J + j;
+                            if (a >= p.flat_total) a = p.flat_total - 1;
+                            const int an = a / p.flat_rb4, arb = a - an * p.flat_rb4;
+                            tma_load_4d_a(patches_a + pp.idx * patch_stride + j * sub, &tmA, pfull_a + 8 * pp.idx, c * 32, -p.pad_w,
+                                          arb * 4 - p.pad_h, an);
+                        }
+                    } else {
+                        tma_load_4d_a(patches_a + pp.idx * patch_stride, &tmA, pfull_a + 8 * pp.idx, c * 32, w0, h0, n);
+                    }
                     pp.advance(p.npb);
                     for (int st = 0; st < stages_per_chunk; ++st) {
                         if (!wait_prof(bempty_a + 8 * bp.idx, bp.phase ^ 1, prof_on, w_b)) { report(p.status, kStatusProducerTimeout); ok = false; break; }
@@ -340,7 +358,7 @@ __global__ void __launch_bounds__(kHaloThreads2, 1)
             unsigned long long w_patch = 0, w_b = 0, w_acc = 0;
             const long long t_begin = clock64();
             // descriptor halves that never change, and the steps of the low half (16-byte units)
-            const uint32_t a_dhi = smem_desc_hi(p.PW * 128, kSwizzle128B);
+            const uint32_t a_dhi = smem_desc_hi(FLAT_T ? 1024u : p.PW * 128, kSwizzle128B);
             const uint32_t b_dhi = p.b_mn ? smem_desc_hi(512, kSwizzle128B_Base32B) : smem_desc_hi(1024, kSwizzle128B);
             const uint32_t b_kstep = p.b_mn ? 64u : 2u;       // 1024 B or 32 B per K=8 step
             const uint32_t a_lo_off = p.patch_bytes >> 4;     // hi plane -> lo plane
@@ -369,7 +387,7 @@ __global__ void __launch_bounds__(kHaloThreads2, 1)
                     tc_fence_after_sync();
                     uint32_t a_row = patch_lo0 + pp.idx * patch_stride16;
                     if constexpr (kRow) {
-                        constexpr uint32_t kPW8 = (8 * JW_T + FW_T - 1) * 8;  // one patch row, in 16-byte units
+                        constexpr uint32_t kPW8 = FLAT_T ? 256u : (8 * JW_T + FW_T - 1) * 8;  // one patch row, in 16-byte units
                         const uint32_t b_tile16 = b_tile >> 4;
                         for (int fh = 0; fh < p.FH; ++fh, a_row += kPW8, bp.advance(p.sb)) {
                             if (dual && ((sg++) & 1u) != which) continue;   // the other issuer's stage
@@ -381,15 +399,15 @@ __global__ void __launch_bounds__(kHaloThreads2, 1)
                             if (!wait_prof(bwait_a + 8 * bp.idx, bp.phase, prof_on, w_b)) { report(p.status, kStatusMmaTimeout); ok = false; break; }
                             tc_fence_after_sync();
                             const uint32_t bl = bring_lo0 + bp.idx * b_stride16;
-                            if (p.mode3x == 1) issue_row<1, FW_T, JH_T, JW_T, kPW8>(d0, a_row, bl, b_tile16, k, acc_first);
-                            else if (p.mode3x == 2) issue_row<2, FW_T, JH_T, JW_T, kPW8>(d0, a_row, bl, b_tile16, k, acc_first);
-                            else issue_row<0, FW_T, JH_T, JW_T, kPW8>(d0, a_row, bl, b_tile16, k, acc_first);
+                            if (p.mode3x == 1) issue_row<1, FW_T, JH_T, JW_T, kPW8, FLAT_T>(d0, a_row, bl, b_tile16, k, acc_first);
+                            else if (p.mode3x == 2) issue_row<2, FW_T, JH_T, JW_T, kPW8, FLAT_T>(d0, a_row, bl, b_tile16, k, acc_first);
+                            else issue_row<0, FW_T, JH_T, JW_T, kPW8, FLAT_T>(d0, a_row, bl, b_tile16, k, acc_first);
                             acc_first = 1u;
                             if (announce) { tc_fence_before_sync(); mbar_arrive_a(started_a + 8 * ap.idx); announce = false; }
                             mma_commit_a(bempty_a + 8 * bp.idx);
                         }
                     } else if constexpr (kStatic) {
-                        constexpr uint32_t kPW8 = (8 * JW_T + FW_T - 1) * 8;
+                        constexpr uint32_t kPW8 = FLAT_T ? 256u : (8 * JW_T + FW_T - 1) * 8;
                         for (int fh = 0; fh < p.FH && ok; ++fh, a_row += kPW8) {
                             const uint32_t a_row_lo = a_row + a_lo_off;
                             static_for<0, FW_T>([&](auto fw_) {
@@ -405,9 +423,9 @@ __global__ void __launch_bounds__(kHaloThreads2, 1)
                                     if (!wait_prof(bwait_a + 8 * bp.idx, bp.phase, prof_on, w_b)) { report(p.status, kStatusMmaTimeout); ok = false; return; }
                                     tc_fence_after_sync();
                                     const uint32_t bl = bring_lo0 + bp.idx * b_stride16;
-                                    if (p.mode3x == 1) issue_tap<1, JH_T, JW_T, kPW8, fw * 8>(d0, a_row, a_row_lo, bl, k, acc_first);
-                                    else if (p.mode3x == 2) issue_tap<2, JH_T, JW_T, kPW8, fw * 8>(d0, a_row, a_row_lo, bl, k, acc_first);
-                                    else issue_tap<0, JH_T, JW_T, kPW8, fw * 8>(d0, a_row, a_row_lo, bl, k, acc_first);
+                                    if (p.mode3x == 1) issue_tap<1, JH_T, JW_T, kPW8, fw * 8, FLAT_T>(d0, a_row, a_row_lo, bl, k, acc_first);
+                                    else if (p.mode3x == 2) issue_tap<2, JH_T, JW_T, kPW8, fw * 8, FLAT_T>(d0, a_row, a_row_lo, bl, k, acc_first);
+                                    else issue_tap<0, JH_T, JW_T, kPW8, fw * 8, FLAT_T>(d0, a_row, a_row_lo, bl, k, acc_first);
                                     acc_first = 1u;
                                     if (announce) { tc_fence_before_sync(); mbar_arrive_a(started_a + 8 * ap.idx); announce = false; }
                                     mma_commit_a(bempty_a + 8 * bp.idx);
@@ -482,7 +500,14 @@ __global__ void __launch_bounds__(kHaloThreads2, 1)
             int j = 0;
             for (int jh = 0; jh < p.JH; ++jh)
                 for (int jw = 0; jw < p.JW; ++jw, ++j) {
-                    const int oh0 = (rb * p.JH + jh) * 16, ow0 = (cb * p.JW + jw) * 8;
+                    int oh0 = (rb * p.JH + jh) * 16, ow0 = (cb * p.JW + jw) * 8, n_img = n;
+                    if (FLAT_T) {
+                        const int a = rb * J + j;
+                        if (a >= p.flat_total) continue;          // the repeated block of the last macro tile
+                        n_img = a / p.flat_rb4;
+                        oh0 = (a - n_img * p.flat_rb4) * 4;
+                        ow0 = 0;
+                    }
                     if (oh0 >= p.OH || ow0 >= p.OW) continue;  // accumulator entirely outside the image
                     const uint32_t tcol = lane_base + (ap.idx * J + j) * accw;
                     for (int c = 0; c < p.BN; c += 32) {
@@ -518,7 +543,7 @@ __global__ void __launch_bounds__(kHaloThreads2, 1)
                         named_barrier_sync(1, 128);
                         if (threadIdx.x == 64) {
                             if (p.NI == 1) {
-                                tma_store_4d_a(&tmO, stage_a + sbuf * 16384, col0, ow0, oh0, n + tp.sp * p.N);
+                                tma_store_4d_a(&tmO, stage_a + sbuf * 16384, col0, ow0, oh0, n_img + tp.sp * p.N);
                             } else {
                                 // stacked images: image i starts SG groups (of 8 rows) further down the slab
                                 for (int img = 0; img < p.NI; ++img)

@@ -520,3 +520,39 @@ def test_flat_tiles_are_chosen_for_28x28(pkg, eng):
     eng.conv3D(X, W, 1, 1, 1, 1)
     assert "halo_pair" in lib.last_plan() and "flat32" not in lib.last_plan(), lib.last_plan()
     assert lib.device_status() == 0
+
+
+CASES["flat_odd_blocks"] = (3, 12, 28, 32, 64, 3, 3, 1, 1, 1, 1)     # 3 images x 3 four-row blocks: the last macro tile is half empty
+
+
+@pytest.mark.parametrize("mode", ["3xtf32", "tf32"])
+@pytest.mark.parametrize("name", [n for n in FLAT32_CASES if n != "flat_narrow"] + ["flat_odd_blocks"])   # flat_narrow fills too few lanes for this kernel
+def test_single_cta_kernel_with_flat_tiles(pkg, eng, oracle_mod, name, mode):
+    """The single-CTA halo kernel with two flat accumulators per W tile, each with its own patch (the pair kernel is
+    switched off), against the oracle and against its 16 x 8 form."""
+    import torch
+    L = pkg.submodule("lib")
+    old = {k: L.set_option(k, v) for k, v in (("HALO_PAIR", 0), ("HALO_FLAT32", 2), ("SKINNY", 0), ("HALO_TAPSTACK", 0))}
+    try:
+        res, (X, W, B, dY, Y, dX, dW) = _run_case(pkg, eng, oracle_mod, name, mode)
+        assert res["status"] == 0 and res["fwd_algo"] in ("halo_row", "halo_tap"), res["fwd_algo"]
+        tol = TOL[mode]
+        for op in ("fwd", "dx"):
+            m = res[op]
+            assert m["finite"] and m["norm"] <= tol["norm"] and m["comp"] <= tol["comp"], (name, op, res[op + "_algo"], m)
+        dev = torch.device("cuda:0")
+        N, IH, IW, IC, OC, FH, FW, sh, sw, ph, pw = CASES[name]
+        tX, tW, tB = (torch.from_numpy(a).to(dev) for a in (X, W, B))
+        eng.conv3D_biased(tX, tW, tB, sh, sw, ph, pw)
+        assert "flat32" in L.last_plan(), L.last_plan()
+        L.set_option("HALO_FLAT32", 0)
+        Y0 = eng.conv3D_biased(tX, tW, tB, sh, sw, ph, pw).cpu().numpy()
+        assert "flat32" not in L.last_plan(), L.last_plan()
+        if mode == "3xtf32":
+            np.testing.assert_array_equal(Y0, Y)
+        else:
+            assert np.abs(Y0 - Y).max() <= 5e-5 * np.abs(Y).max()
+    finally:
+        for k, v in old.items():
+            L.set_option(k, v)
+
