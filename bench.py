@@ -66,6 +66,8 @@ def parse_args():
     ap.add_argument("--no-config3", action="store_true")
     ap.add_argument("--config3-only", action="store_true",
                     help="profiling aid: run only the ResNet-18 conv stack (with --no-graph: eager launches) and print its record")
+    ap.add_argument("--neighbours-only", action="store_true",
+                    help="profiling aid: run only the batched matrix products and the pooling operators and print their record")
     ap.add_argument("--config3-batch", type=int, default=None,
                     help="global batch of the ResNet-18 stack (default 512); 64 on one GPU shows the per-GPU compute of the 8-GPU case")
     ap.add_argument("--no-cpu", action="store_true")
@@ -764,6 +766,13 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    if args.neighbours_only:
+        rec = neighbour_ops(env) if rank == 0 else None
+        if rank == 0:
+            print(json.dumps({"metric": "batched matrix products and pooling (profiling aid)", "n_gpus": world, "neighbours": rec}))
+        if world > 1:
+            dist.destroy_process_group()
+        return
     if args.config3_only:
         rec = Config3(env, args.config3_batch or synth.RESNET18_BATCH).run(args.steps, args.repeats, barrier, use_graph=not args.no_graph)
         if rank == 0:
