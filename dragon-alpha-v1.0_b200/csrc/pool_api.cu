@@ -46,7 +46,7 @@ FastDiv fast_div(int d_)
 
 struct PoolDims {
     int N, IH, IW, IC, FH, FW, OH, OW, sh, sw, ph, pw;
-    FastDiv by_cq4, by_cq1, by_IW, by_IH, by_OW, by_OH, by_sh, by_sw;   // by_cq: channel groups of 4 / of 1
+    FastDiv by_cqu, by_IW, by_IH, by_OW, by_OH, by_sh, by_sw;   // by_cqu: channel groups per thread step, IC / (V * U)
 };
 
 template <int V> struct Vec;
@@ -89,7 +89,11 @@ __device__ __forceinline__ void vsel_eq(float4& a, const int4& idx, int off, con
 
 enum FwdOp { kMax = 0, kMaxIndexed = 1, kAvg = 2, kAvgIp = 3 };
 
-template <int V, int OP>
+// V = 4 (16-byte accesses) or 1; U = channel groups per thread: a thread owns the groups g, g + cq / U, ... of one
+// element (cq = IC / V groups per element), so that the index arithmetic of the element - the larger part of the
+// instructions of these kernels - is shared by U loads per window position, while consecutive threads still touch
+// consecutive groups (a warp reads 32 / (cq / U) elements x cq / U x 16 contiguous bytes per instruction).
+template <int V, int U, int OP>
 __global__ void __launch_bounds__(256) pool_fwd_kernel(const float* __restrict__ X, float* __restrict__ Y,
                                                        int* __restrict__ Index, PoolDims d)
 {
@@ -97,20 +101,24 @@ __global__ void __launch_bounds__(256) pool_fwd_kernel(const float* __restrict__
     using I = typename Vec<V>::I;
     // element counts fit 31 bits (checked on the host), so the index arithmetic is 32-bit: 64-bit divisions per
     // element cost more than the memory traffic of these kernels
-    const unsigned cq = static_cast<unsigned>(d.IC / V);
-    const unsigned total = static_cast<unsigned>(d.N) * d.OH * d.OW * cq;
-    const FastDiv by_cq = V == 4 ? d.by_cq4 : d.by_cq1;
+    const unsigned cqu = static_cast<unsigned>(d.IC / (V * U));   // groups per thread step
+    const unsigned total = static_cast<unsigned>(d.N) * d.OH * d.OW * cqu;
+    const FastDiv by_cq = d.by_cqu;
+    const int cstep = static_cast<int>(cqu) * V;                  // channels between two groups of one thread
     for (unsigned e = blockIdx.x * blockDim.x + threadIdx.x; e < total; e += gridDim.x * blockDim.x) {
         unsigned pix, cc, uow, uoh, un;
         by_cq.divmod(e, pix, cc);
+        const unsigned opix = pix;
         d.by_OW.divmod(pix, pix, uow);
         d.by_OH.divmod(pix, un, uoh);
         const int c = static_cast<int>(cc) * V, ow = static_cast<int>(uow), oh = static_cast<int>(uoh), n = static_cast<int>(un);
         const int ih0 = oh * d.sh - d.ph, iw0 = ow * d.sw - d.pw;
         const size_t img = static_cast<size_t>(n) * d.IH * d.IW * d.IC;
         const float* x = X + img;
-        F v = splat<V>(OP <= kMaxIndexed ? kFloatMin : 0.f);
-        I idx{};
+        F v[U];
+        I idx[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) { v[u] = splat<V>(OP <= kMaxIndexed ? kFloatMin : 0.f); idx[u] = I{}; }
         int count = 0;
         for (int fh = 0; fh < d.FH; ++fh) {
             const int ih = ih0 + fh;
@@ -119,43 +127,53 @@ __global__ void __launch_bounds__(256) pool_fwd_kernel(const float* __restrict__
                 const int iw = iw0 + fw;
                 if (iw < 0 || iw >= d.IW) continue;
                 const int off = (ih * d.IW + iw) * d.IC + c;
-                const F xv = *reinterpret_cast<const F*>(x + off);
-                if (OP <= kMaxIndexed) {
-                    if (OP == kMaxIndexed) vidx(idx, xv, v, off);
-                    vmax(v, xv);
-                } else {
-                    vadd(v, xv);
-                    ++count;
+                F xv[U];
+#pragma unroll
+                for (int u = 0; u < U; ++u) xv[u] = *reinterpret_cast<const F*>(x + off + u * cstep);
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    if (OP <= kMaxIndexed) {
+                        if (OP == kMaxIndexed) vidx(idx[u], xv[u], v[u], off + u * cstep);
+                        vmax(v[u], xv[u]);
+                    } else {
+                        vadd(v[u], xv[u]);
+                    }
                 }
+                ++count;
             }
         }
-        if (OP == kAvg) v = vdiv(v, static_cast<float>(d.FH * d.FW));
-        if (OP == kAvgIp) v = vdiv(v, static_cast<float>(count));
-        const size_t yoff = static_cast<size_t>(e) * V;
-        *reinterpret_cast<F*>(Y + yoff) = v;
-        if (OP == kMaxIndexed) {
-            iadd(idx, static_cast<int>(img));
-            *reinterpret_cast<I*>(Index + yoff) = idx;
+        const size_t yoff = static_cast<size_t>(opix) * d.IC + c;
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            if (OP == kAvg) v[u] = vdiv(v[u], static_cast<float>(d.FH * d.FW));
+            if (OP == kAvgIp) v[u] = vdiv(v[u], static_cast<float>(count));
+            *reinterpret_cast<F*>(Y + yoff + u * cstep) = v[u];
+            if (OP == kMaxIndexed) {
+                iadd(idx[u], static_cast<int>(img));
+                *reinterpret_cast<I*>(Index + yoff + u * cstep) = idx[u];
+            }
         }
     }
 }
 
 enum BwdOp { kBwdMax = 0, kBwdMaxIndexed = 1, kBwdAvg = 2, kBwdAvgIp = 3 };
 
-template <int V, int OP>
+template <int V, int U, int OP>
 __global__ void __launch_bounds__(256) pool_bwd_kernel(const float* __restrict__ dY, const float* __restrict__ Y,
                                                        const float* __restrict__ X, const int* __restrict__ Index,
                                                        float* __restrict__ dX, PoolDims d)
 {
     using F = typename Vec<V>::F;
     using I = typename Vec<V>::I;
-    const unsigned cq = static_cast<unsigned>(d.IC / V);
-    const unsigned total = static_cast<unsigned>(d.N) * d.IH * d.IW * cq;
-    const FastDiv by_cq = V == 4 ? d.by_cq4 : d.by_cq1;
+    const unsigned cqu = static_cast<unsigned>(d.IC / (V * U));
+    const unsigned total = static_cast<unsigned>(d.N) * d.IH * d.IW * cqu;
+    const FastDiv by_cq = d.by_cqu;
+    const int cstep = static_cast<int>(cqu) * V;
     const float alpha = 1.0f / static_cast<float>(d.FH * d.FW);
     for (unsigned e = blockIdx.x * blockDim.x + threadIdx.x; e < total; e += gridDim.x * blockDim.x) {
         unsigned pix, cc, uiw, uih, un;
         by_cq.divmod(e, pix, cc);
+        const unsigned ipix = pix;
         d.by_IW.divmod(pix, pix, uiw);
         d.by_IH.divmod(pix, un, uih);
         const int c = static_cast<int>(cc) * V, iw = static_cast<int>(uiw), ih = static_cast<int>(uih), n = static_cast<int>(un);
@@ -168,32 +186,45 @@ __global__ void __launch_bounds__(256) pool_bwd_kernel(const float* __restrict__
         const int ow_lo = t <= 0 ? 0 : static_cast<int>(d.by_sw.div(static_cast<unsigned>(t + d.sw - 1)));
         int ow_hi = static_cast<int>(d.by_sw.div(static_cast<unsigned>(iw + d.pw)));
         if (ow_hi > d.OW - 1) ow_hi = d.OW - 1;
-        const size_t xoff = static_cast<size_t>(e) * V;
+        const size_t xoff = static_cast<size_t>(ipix) * d.IC + c;
         const size_t yimg = static_cast<size_t>(n) * d.OH * d.OW * d.IC;
-        F xv = splat<V>(0.f);
-        if (OP == kBwdMax) xv = *reinterpret_cast<const F*>(X + xoff);
-        F v = splat<V>(0.f);
+        F xv[U], v[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            v[u] = splat<V>(0.f);
+            xv[u] = OP == kBwdMax ? *reinterpret_cast<const F*>(X + xoff + u * cstep) : splat<V>(0.f);
+        }
         for (int oh = oh_lo; oh <= oh_hi; ++oh)
             for (int ow = ow_lo; ow <= ow_hi; ++ow) {
                 const size_t yo = yimg + static_cast<size_t>((oh * d.OW + ow) * d.IC + c);
-                const F dy = *reinterpret_cast<const F*>(dY + yo);
-                if (OP == kBwdMax) {
-                    vsel_ge(v, xv, *reinterpret_cast<const F*>(Y + yo), dy);
-                } else if (OP == kBwdMaxIndexed) {
-                    vsel_eq(v, *reinterpret_cast<const I*>(Index + yo), static_cast<int>(xoff), dy);
-                } else if (OP == kBwdAvg) {
-                    vfma(v, alpha, dy);   // v += alpha * deltaY per window, as upool2D_avg_kernel.cuh:84-94 does
-                } else {
+                float scale = alpha;
+                if (OP == kBwdAvgIp) {
                     // positions of this window that lie inside the image
                     int h0 = oh * d.sh - d.ph, h1 = h0 + d.FH, w0 = ow * d.sw - d.pw, w1 = w0 + d.FW;
                     if (h0 < 0) h0 = 0;
                     if (h1 > d.IH) h1 = d.IH;
                     if (w0 < 0) w0 = 0;
                     if (w1 > d.IW) w1 = d.IW;
-                    vadd(v, vdiv(dy, static_cast<float>((h1 - h0) * (w1 - w0))));
+                    scale = static_cast<float>((h1 - h0) * (w1 - w0));
+                }
+                F dy[U];
+#pragma unroll
+                for (int u = 0; u < U; ++u) dy[u] = *reinterpret_cast<const F*>(dY + yo + u * cstep);
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    if (OP == kBwdMax) {
+                        vsel_ge(v[u], xv[u], *reinterpret_cast<const F*>(Y + yo + u * cstep), dy[u]);
+                    } else if (OP == kBwdMaxIndexed) {
+                        vsel_eq(v[u], *reinterpret_cast<const I*>(Index + yo + u * cstep), static_cast<int>(xoff) + u * cstep, dy[u]);
+                    } else if (OP == kBwdAvg) {
+                        vfma(v[u], scale, dy[u]);   // v += alpha * deltaY per window, as upool2D_avg_kernel.cuh:84-94 does
+                    } else {
+                        vadd(v[u], vdiv(dy[u], scale));
+                    }
                 }
             }
-        *reinterpret_cast<F*>(dX + xoff) = v;
+#pragma unroll
+        for (int u = 0; u < U; ++u) *reinterpret_cast<F*>(dX + xoff + u * cstep) = v[u];
     }
 }
 
@@ -213,11 +244,10 @@ int check_pool(const char* what, const AlphaPoolShape* s, const void* a, const v
     return ALPHA_OK;
 }
 
-PoolDims dims_of(const AlphaPoolShape* s)
+PoolDims dims_of(const AlphaPoolShape* s, int V, int U)
 {
-    PoolDims d{s->N, s->IH, s->IW, s->IC, s->FH, s->FW, s->OH, s->OW, s->sh, s->sw, s->ph, s->pw, {}, {}, {}, {}, {}, {}, {}, {}};
-    d.by_cq4 = fast_div(s->IC / 4 > 0 ? s->IC / 4 : 1);
-    d.by_cq1 = fast_div(s->IC);
+    PoolDims d{s->N, s->IH, s->IW, s->IC, s->FH, s->FW, s->OH, s->OW, s->sh, s->sw, s->ph, s->pw, {}, {}, {}, {}, {}, {}, {}};
+    d.by_cqu = fast_div(s->IC / (V * U));
     d.by_IW = fast_div(s->IW); d.by_IH = fast_div(s->IH);
     d.by_OW = fast_div(s->OW); d.by_OH = fast_div(s->OH);
     d.by_sh = fast_div(s->sh); d.by_sw = fast_div(s->sw);
@@ -263,13 +293,14 @@ int run_fwd(const char* what, const AlphaPoolShape* s, const float* X, float* Y,
     int rc = check_pool(what, s, X, Y);
     if (rc) return rc;
     if (OP == kMaxIndexed && !Index) return fail(ALPHA_E_ARG, "%s: null index tensor", what);
-    const PoolDims d = dims_of(s);
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     const long long outs = static_cast<long long>(s->N) * s->OH * s->OW * s->IC;
-    if (vec4_ok(s, X, Y, Index))
-        pool_fwd_kernel<4, OP><<<grid_for(outs / 4), 256, 0, stream>>>(X, Y, Index, d);
+    if (vec4_ok(s, X, Y, Index) && s->IC % 16 == 0)
+        pool_fwd_kernel<4, 4, OP><<<grid_for(outs / 16), 256, 0, stream>>>(X, Y, Index, dims_of(s, 4, 4));
+    else if (vec4_ok(s, X, Y, Index))
+        pool_fwd_kernel<4, 1, OP><<<grid_for(outs / 4), 256, 0, stream>>>(X, Y, Index, dims_of(s, 4, 1));
     else
-        pool_fwd_kernel<1, OP><<<grid_for(outs), 256, 0, stream>>>(X, Y, Index, d);
+        pool_fwd_kernel<1, 1, OP><<<grid_for(outs), 256, 0, stream>>>(X, Y, Index, dims_of(s, 1, 1));
     return finish("pool_fwd_kernel", "pool_fwd");
 }
 
@@ -281,13 +312,15 @@ int run_bwd(const char* what, const AlphaPoolShape* s, const float* dY, const fl
     if (rc) return rc;
     if (OP == kBwdMax && (!Y || !X)) return fail(ALPHA_E_ARG, "%s: needs X and Y of the forward pass", what);
     if (OP == kBwdMaxIndexed && !Index) return fail(ALPHA_E_ARG, "%s: null index tensor", what);
-    const PoolDims d = dims_of(s);
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     const long long ins = static_cast<long long>(s->N) * s->IH * s->IW * s->IC;
-    if (vec4_ok(s, dY, dX, Y, X) && (reinterpret_cast<uintptr_t>(Index) & 15) == 0)
-        pool_bwd_kernel<4, OP><<<grid_for(ins / 4), 256, 0, stream>>>(dY, Y, X, Index, dX, d);
+    const bool v4 = vec4_ok(s, dY, dX, Y, X) && (reinterpret_cast<uintptr_t>(Index) & 15) == 0;
+    if (v4 && s->IC % 16 == 0)
+        pool_bwd_kernel<4, 4, OP><<<grid_for(ins / 16), 256, 0, stream>>>(dY, Y, X, Index, dX, dims_of(s, 4, 4));
+    else if (v4)
+        pool_bwd_kernel<4, 1, OP><<<grid_for(ins / 4), 256, 0, stream>>>(dY, Y, X, Index, dX, dims_of(s, 4, 1));
     else
-        pool_bwd_kernel<1, OP><<<grid_for(ins), 256, 0, stream>>>(dY, Y, X, Index, dX, d);
+        pool_bwd_kernel<1, 1, OP><<<grid_for(ins), 256, 0, stream>>>(dY, Y, X, Index, dX, dims_of(s, 1, 1));
     return finish("pool_bwd_kernel", "pool_bwd");
 }
 
