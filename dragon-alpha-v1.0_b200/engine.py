@@ -262,6 +262,46 @@ class CudaFloat32EngineBase:
         self._mm(self._lib.alpha_engine_batchMatMulT2, a(C_address), a(A_address), a(B_address), Batch, N, CM, BM, K,
                  _stream(self._stream))
 
+    # ---- pooling, Java argument order (CudaFloat32EngineBase.java:2012-2215) ----
+    def _pool(self, fn, N, IH, IW, IC, FH, FW, OH, OW, sh, sw, ph, pw, *ptrs_and_flags):
+        s = _l.AlphaPoolShape(N, IH, IW, IC, FH, FW, OH, OW, sh, sw, ph, pw)
+        _l.check(fn(C.byref(s), *ptrs_and_flags, _stream(self._stream)))
+
+    def pool2D_max(self, Y_address, OH, OW, X_address, IH, IW, FH, FW, N, IC, sh, sw, ph, pw):
+        a = self._addr
+        self._pool(self._lib.alpha_pool2D_max, N, IH, IW, IC, FH, FW, OH, OW, sh, sw, ph, pw, a(X_address), a(Y_address))
+
+    def pool2D_max_indexed(self, Y_address, Index_address, OH, OW, X_address, IH, IW, FH, FW, N, IC, sh, sw, ph, pw):
+        a = self._addr
+        self._pool(self._lib.alpha_pool2D_max_indexed, N, IH, IW, IC, FH, FW, OH, OW, sh, sw, ph, pw, a(X_address), a(Y_address),
+                   a(Index_address))
+
+    def pool2D_avg(self, Y_address, OH, OW, X_address, IH, IW, FH, FW, N, IC, sh, sw, ph, pw):
+        a = self._addr
+        self._pool(self._lib.alpha_pool2D_avg, N, IH, IW, IC, FH, FW, OH, OW, sh, sw, ph, pw, a(X_address), a(Y_address), 0)
+
+    def pool2D_avg_ignore_padding(self, Y_address, OH, OW, X_address, IH, IW, FH, FW, N, IC, sh, sw, ph, pw):
+        a = self._addr
+        self._pool(self._lib.alpha_pool2D_avg, N, IH, IW, IC, FH, FW, OH, OW, sh, sw, ph, pw, a(X_address), a(Y_address), 1)
+
+    def upool2D_max(self, deltaX_address, X_address, IH, IW, deltaY_address, Y_address, OH, OW, FH, FW, N, IC, sh, sw, ph, pw):
+        a = self._addr
+        self._pool(self._lib.alpha_upool2D_max, N, IH, IW, IC, FH, FW, OH, OW, sh, sw, ph, pw, a(deltaY_address), a(Y_address),
+                   a(X_address), a(deltaX_address))
+
+    def upool2D_max_Indexed(self, deltaX_address, IH, IW, deltaY_address, Index_address, OH, OW, FH, FW, N, IC, sh, sw, ph, pw):
+        a = self._addr
+        self._pool(self._lib.alpha_upool2D_max_indexed, N, IH, IW, IC, FH, FW, OH, OW, sh, sw, ph, pw, a(deltaY_address),
+                   a(Index_address), a(deltaX_address))
+
+    def upool2D_avg(self, deltaX_address, IH, IW, deltaY_address, OH, OW, FH, FW, N, IC, sh, sw, ph, pw):
+        a = self._addr
+        self._pool(self._lib.alpha_upool2D_avg, N, IH, IW, IC, FH, FW, OH, OW, sh, sw, ph, pw, a(deltaY_address), a(deltaX_address), 0)
+
+    def upool2D_avg_ignore_padding(self, deltaX_address, IH, IW, deltaY_address, OH, OW, FH, FW, N, IC, sh, sw, ph, pw):
+        a = self._addr
+        self._pool(self._lib.alpha_upool2D_avg, N, IH, IW, IC, FH, FW, OH, OW, sh, sw, ph, pw, a(deltaY_address), a(deltaX_address), 1)
+
 
 def _pad4(n):
     return (n + 3) & ~3
@@ -477,12 +517,11 @@ class Engine:
         IC = X.shape[3]
         Xp = _pad_last(X, s.IC)
         Y = torch.empty((s.N, OH, OW, s.IC), dtype=torch.float32, device=X.device)
-        a, st = self.base._addr, _stream(self.base._stream)
         if indexed:
             Index = torch.empty((s.N, OH, OW, s.IC), dtype=torch.int32, device=X.device)
-            _l.check(self.base._lib.alpha_pool2D_max_indexed(C.byref(s), a(Xp), a(Y), a(Index), st))
+            self.base.pool2D_max_indexed(Y, Index, OH, OW, Xp, s.IH, s.IW, FH, FW, s.N, s.IC, sh, sw, ph, pw)
             return (Y if s.IC == IC else Y[..., :IC]), Index
-        _l.check(self.base._lib.alpha_pool2D_max(C.byref(s), a(Xp), a(Y), st))
+        self.base.pool2D_max(Y, OH, OW, Xp, s.IH, s.IW, FH, FW, s.N, s.IC, sh, sw, ph, pw)
         return Y if s.IC == IC else Y[..., :IC]
 
     def pool2D_avg(self, X, FH, FW, sh, sw, ph, pw, ignore_padding=False):

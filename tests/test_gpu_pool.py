@@ -108,6 +108,40 @@ def test_golden_vectors_of_the_reference_loops(pkg, eng):
             assert np.abs(got.cpu().numpy() - want).max() <= 1e-6 * np.abs(want).max(), (name, key)
 
 
+def test_engine_base_methods_in_the_java_argument_order(pkg, eng, oracle_mod):
+    """CudaFloat32EngineBase.pool2D_* / upool2D_* with the reference's argument order (CudaFloat32EngineBase.java:2012-2215)."""
+    import torch
+    O = oracle_mod
+    base = eng.base
+    dev = torch.device("cuda:0")
+    N, IH, IW, IC, FH, FW, sh, sw, ph, pw = CASES["overlap_3x3_s1"]
+    X, dY = _inputs("overlap_3x3_s1", ties=True)
+    OH, OW = dY.shape[1:3]
+    win = (FH, FW, sh, sw, ph, pw)
+    tX, tdY = torch.from_numpy(X).to(dev), torch.from_numpy(dY).to(dev)
+    Y = torch.empty((N, OH, OW, IC), device=dev)
+    Index = torch.empty((N, OH, OW, IC), device=dev, dtype=torch.int32)
+    dX = torch.empty_like(tX)
+    dims = (FH, FW, N, IC, sh, sw, ph, pw)
+    base.pool2D_max(Y, OH, OW, tX, IH, IW, *dims)
+    oY = O.pool2D(X, *win, op="max")
+    np.testing.assert_array_equal(Y.cpu().numpy(), oY)
+    base.pool2D_max_indexed(Y, Index, OH, OW, tX, IH, IW, *dims)
+    np.testing.assert_array_equal(Index.cpu().numpy(), O.pool2D(X, *win, op="max_indexed")[1])
+    base.upool2D_max(dX, tX, IH, IW, tdY, Y, OH, OW, *dims)
+    np.testing.assert_array_equal(dX.cpu().numpy(), O.upool2D(dY, IH, IW, *win, op="max", Y=oY, X=X))
+    base.upool2D_max_Indexed(dX, IH, IW, tdY, Index, OH, OW, *dims)
+    np.testing.assert_array_equal(dX.cpu().numpy(), O.upool2D(dY, IH, IW, *win, op="max_indexed", Index=Index.cpu().numpy()))
+    for fwd, bwd, op in ((base.pool2D_avg, base.upool2D_avg, "avg"),
+                         (base.pool2D_avg_ignore_padding, base.upool2D_avg_ignore_padding, "avg_ignore_padding")):
+        fwd(Y, OH, OW, tX, IH, IW, *dims)
+        want = O.pool2D(X, *win, op=op)
+        assert np.abs(Y.cpu().numpy() - want).max() <= 1e-6 * np.abs(want).max(), op
+        bwd(dX, IH, IW, tdY, OH, OW, *dims)
+        want = O.upool2D(dY, IH, IW, *win, op=op)
+        assert np.abs(dX.cpu().numpy() - want).max() <= 1e-6 * np.abs(want).max(), op
+
+
 def test_adjoint_identity_of_the_average(pkg, eng):
     """<pool_avg(X), dY> == <X, upool_avg(dY)> at a size the oracle would not finish (a property of the pair)."""
     import torch
