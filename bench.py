@@ -751,7 +751,20 @@ def run_ours(args):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        # NCCL announces its version on stdout when the first communicator comes up; the line of this program is the
+        # only thing that belongs there, so file descriptor 1 points at stderr until that has happened
+        sys.stdout.flush()
+        saved = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            dist.init_process_group("nccl", device_id=dev)
+            warm = torch.zeros(1, device=dev)
+            dist.all_reduce(warm)
+            torch.cuda.synchronize()
+        finally:
+            sys.stdout.flush()
+            os.dup2(saved, 1)
+            os.close(saved)
 
     lib = submodule("lib")
     synth = submodule("synth")
@@ -964,8 +977,15 @@ def run_ours(args):
             "tf32": tf32, "winograd": wino, "neighbours": neighbours, "config3": config3, "allreduce_check": ar_check,
             "graph_error": headline_graph_error,
         }
-        print(json.dumps(line))
+        print(json.dumps(line), flush=True)
     if world > 1:
+        # graphs that captured the all-reduce must be gone, and every rank done, before the communicator goes
+        sweep.graph = None
+        import gc
+        gc.collect()
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
         dist.destroy_process_group()
 
 
