@@ -554,18 +554,10 @@ class Config3:
         # soon as the deltaW kernels that fill it have run (layers are contiguous in the bucket).
         self.comm_stream = torch.cuda.Stream()
         n_chunks = max(1, int(os.environ.get("BENCH_C3_AR_BUCKETS", "4"))) if world > 1 else 1
-        total = self.bucket.flat.numel()
-        self.chunks, start = [], len(self.layers)       # (first layer, last layer + 1) in backward order
-        acc = 0
-        for i in range(len(self.layers) - 1, -1, -1):
-            acc += self.layers[i]["W"].numel()
-            if acc >= total / n_chunks or i == 0:
-                self.chunks.append((i, start)); start = i; acc = 0
+        self.chunks = self.bucket.pieces(n_chunks)       # (first layer, last layer + 1) in backward order
 
     def chunk_view(self, lo, hi):
-        a = self.bucket.offsets[lo]
-        b = self.bucket.offsets[hi] if hi < len(self.layers) else self.bucket.flat.numel()
-        return self.bucket.flat[a:b]
+        return self.bucket.piece_view(lo, hi)
 
     def compute(self, with_reduce=False):
         torch, base, n, dist = self.env["torch"], self.env["base"], self.n, self.env["dist"]

@@ -40,6 +40,27 @@ class GradientBucket:
         o = self.offsets[i]
         return self.flat[o:o + self.numels[i]].view(shape)
 
+    def pieces(self, n):
+        """The bucket as at most n contiguous runs of layers of about equal size, LAST layers first - the order in
+        which a backward pass completes its weight gradients - as (first layer, last layer + 1) pairs.  Reducing
+        piece after piece on a communication stream, each as soon as its layers' deltaW kernels are enqueued,
+        overlaps the collective with the rest of the backward pass."""
+        n = max(1, int(n))
+        total = sum(self.numels)
+        out, end, acc = [], len(self.numels), 0
+        for i in range(len(self.numels) - 1, -1, -1):
+            acc += self.numels[i]
+            if acc >= total / n or i == 0:
+                out.append((i, end))
+                end, acc = i, 0
+        return out
+
+    def piece_view(self, lo, hi):
+        """Flat view of the layers lo .. hi - 1 (with the alignment padding between them)."""
+        a = self.offsets[lo]
+        b = self.offsets[hi] if hi < len(self.offsets) else self.flat.numel()
+        return self.flat[a:b]
+
     def all_reduce(self, group=None, async_op=True):
         if dist.is_initialized() and dist.get_world_size(group) > 1:
             self._work = dist.all_reduce(self.flat, op=dist.ReduceOp.SUM, group=group, async_op=async_op)

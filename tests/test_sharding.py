@@ -61,8 +61,20 @@ def _worker(rank, world, port, out_dir):
     bucket.view(1, (10,)).fill_(float(rank + 1))
     bucket.all_reduce(async_op=True)
     bucket.wait()
+    # the same bucket reduced piece by piece in backward order, as an overlapped backward pass does
+    numels = [12, 40, 7, 64, 20, 33]
+    whole, parts = sharding.GradientBucket(numels, torch.device("cpu")), sharding.GradientBucket(numels, torch.device("cpu"))
+    g = torch.Generator().manual_seed(100 + rank)
+    for i, n in enumerate(numels):
+        v = torch.randn(n, generator=g)
+        whole.view(i, (n,)).copy_(v)
+        parts.view(i, (n,)).copy_(v)
+    whole.all_reduce(async_op=False)
+    for lo, hi in parts.pieces(3):
+        dist.all_reduce(parts.piece_view(lo, hi), op=dist.ReduceOp.SUM)
     np.savez(os.path.join(out_dir, "rank%d.npz" % rank), Y=Y.numpy(), dX=dX.numpy(), dW=dW.numpy(),
-             bW=bucket.view(0, dW.shape).numpy(), b1=bucket.view(1, (10,)).numpy())
+             bW=bucket.view(0, dW.shape).numpy(), b1=bucket.view(1, (10,)).numpy(),
+             whole=whole.flat.numpy(), parts=parts.flat.numpy())
     dist.destroy_process_group()
 
 
@@ -75,6 +87,22 @@ def test_shard_bounds(pkg):
             assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
             sizes = [b - a for a, b in spans]
             assert max(sizes) - min(sizes) <= 1
+
+
+def test_bucket_pieces_cover_the_bucket_in_backward_order(pkg):
+    sh = pkg.submodule("sharding")
+    for numels in ([12, 40, 7, 64, 20, 33], [4], [1000, 4, 4, 4], [4, 4, 4, 1000], [36864] * 20):
+        b = sh.GradientBucket(numels, torch.device("cpu"))
+        for n in (1, 2, 3, 4, 8, 64):
+            pieces = b.pieces(n)
+            assert 1 <= len(pieces) <= min(n, len(numels))
+            assert pieces[0][1] == len(numels) and pieces[-1][0] == 0
+            assert all(a[0] == c[1] and a[0] < a[1] for a, c in zip(pieces, pieces[1:]))   # contiguous, last layers first
+            assert sum(b.piece_view(lo, hi).numel() for lo, hi in pieces) == b.flat.numel()
+            for lo, hi in pieces:   # a piece starts at its first layer and is 16-byte aligned like every view
+                v = b.piece_view(lo, hi)
+                assert v.data_ptr() == b.view(lo, (numels[lo],)).data_ptr() and v.data_ptr() % 16 == 0
+        assert b.pieces(1) == [(0, len(numels))]
 
 
 @pytest.mark.timeout(180)
@@ -99,3 +127,6 @@ def test_two_rank_batch_sharding_matches_single_rank(tmp_path, oracle_mod):
     assert (np.abs(r[0]["dW"] - dW64) <= 1e-6 * S + 1e-30).all()
     assert np.array_equal(r[0]["bW"], r[0]["dW"])
     assert np.array_equal(r[0]["b1"], np.full(10, 3.0, np.float32))
+    # reducing the bucket in pieces gives the same bits as reducing it whole, on every rank
+    assert np.array_equal(r[0]["whole"], r[0]["parts"]) and np.array_equal(r[0]["parts"], r[1]["parts"])
+    assert np.abs(r[0]["whole"]).max() > 0
