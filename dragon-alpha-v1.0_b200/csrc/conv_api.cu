@@ -1615,8 +1615,18 @@ static int launch_dw_halo(DeviceCtx* c, const AlphaConvShape* s_in, const float*
         return (size_t)planes * (dyb * dyblk + (NT / 32) * xbk);
     };
     if (!R) {
-        R = 8;
-        while (R > 1 && (2 * stage_bytes(R) > 210 * 1024 || R * (diag ? 2 : 1) > s->OH)) R >>= 1;
+        // Tile height: a tile costs its R * CW / 8 steps of 8 pixels plus a fixed share (the refill of its ring
+        // slot is not hidden behind so few MMAs: about 8 steps' worth measured in plain TF32, 4 with the three times
+        // longer steps of 3xTF32), and rows past the image edge are idle slots.  7 rows cover 7, 14, 28 and 56 pixel
+        // high images exactly where 8 leave up to one slot in eight idle.  The taller tile on a tie.
+        const int halves = diag ? 2 : 1, fixed = (mode3x && !diag) ? 4 : 8;
+        long long best = -1;
+        for (int cand : {8, 7, 4, 2, 1}) {
+            if (cand > 1 && (2 * stage_bytes(cand) > 210 * 1024 || cand * halves > s->OH)) continue;
+            const long long blocks = (s->OH + cand * halves - 1) / (cand * halves);
+            const long long cost = blocks * ((long long)cand * (CW / 8) + fixed);   // diagonal: one MMA serves both halves
+            if (best < 0 || cost < best) { best = cost; R = cand; }
+        }
     }
     if (2 * stage_bytes(R) > 220 * 1024) return 1;
     int stages = (int)((220 * 1024) / stage_bytes(R));
@@ -1680,6 +1690,7 @@ static int launch_dw_halo(DeviceCtx* c, const AlphaConvShape* s_in, const float*
         dw_halo_set_attr<0, 0, 0>();
         dw_halo_set_attr<3, 1, 16>(); dw_halo_set_attr<3, 2, 16>(); dw_halo_set_attr<3, 4, 16>(); dw_halo_set_attr<3, 8, 16>();
         dw_halo_set_attr<3, 2, 8>(); dw_halo_set_attr<3, 4, 8>(); dw_halo_set_attr<3, 8, 8>();
+        dw_halo_set_attr<3, 7, 16>(); dw_halo_set_attr<3, 7, 8>();
         dw_halo_set_attr<1, 2, 16>(); dw_halo_set_attr<1, 4, 16>(); dw_halo_set_attr<1, 8, 16>();
         attr_done = true;
     }
@@ -1693,6 +1704,8 @@ static int launch_dw_halo(DeviceCtx* c, const AlphaConvShape* s_in, const float*
     else if (st && R == 2 && CW == 8) DWH_LAUNCH(3, 2, 8);
     else if (st && R == 4 && CW == 8) DWH_LAUNCH(3, 4, 8);
     else if (st && R == 8 && CW == 8) DWH_LAUNCH(3, 8, 8);
+    else if (st && R == 7 && CW == 16) DWH_LAUNCH(3, 7, 16);
+    else if (st && R == 7 && CW == 8) DWH_LAUNCH(3, 7, 8);
     else if (st1 && R == 2) DWH_LAUNCH(1, 2, 16);
     else if (st1 && R == 4) DWH_LAUNCH(1, 4, 16);
     else if (st1 && R == 8) DWH_LAUNCH(1, 8, 16);

@@ -556,3 +556,58 @@ def test_single_cta_kernel_with_flat_tiles(pkg, eng, oracle_mod, name, mode):
         for k, v in old.items():
             L.set_option(k, v)
 
+
+
+# deltaW pixel tiles of 7 rows: exact cover of 7, 14, 21, 28 ... pixel high images.  Forced on shapes of every
+# kernel form (plain, three-MMA and stacked 3xTF32, the diagonal TF32 form with two half tiles, 8- and 16-column
+# tiles, a tile row that ends inside the tile), then the planner's own choice at the benchmark's 7x7x512 layer.
+SEVEN_ROW_CASES = {
+    "dw7_7x7x64_oc128": (4, 7, 7, 64, 128, 3, 3, 1, 1, 1, 1),
+    "dw7_14x14x32_oc64": (3, 14, 14, 32, 64, 3, 3, 1, 1, 1, 1),
+    "dw7_21x9x32_oc96": (2, 21, 9, 32, 96, 3, 3, 1, 1, 1, 1),
+    "dw7_28x28x32_oc64": (2, 28, 28, 32, 64, 3, 3, 1, 1, 1, 1),
+    "dw7_10x12x32": (3, 10, 12, 32, 32, 3, 3, 1, 1, 1, 1),
+}
+CASES.update(SEVEN_ROW_CASES)
+
+
+@pytest.mark.parametrize("mode", ["3xtf32", "tf32"])
+@pytest.mark.parametrize("name", list(SEVEN_ROW_CASES))
+def test_deltaW_with_seven_row_tiles(pkg, eng, oracle_mod, name, mode):
+    import torch
+    O, lib = oracle_mod, pkg.submodule("lib")
+    N, IH, IW, IC, OC, FH, FW, sh, sw, ph, pw = CASES[name]
+    rng = np.random.default_rng(zlib.crc32(name.encode()))
+    X, dY = gen((N, IH, IW, IC), "relu", rng), gen((N, IH, IW, OC), "n01", rng)
+    dev = torch.device("cuda:0")
+    lib.set_math_mode(mode)
+    old = lib.set_option("DW_R", 7)
+    try:
+        dW = eng.dconv3D_deltaW(torch.from_numpy(X).to(dev), torch.from_numpy(dY).to(dev), FH, FW, sh, sw, ph, pw).cpu().numpy()
+        plan = lib.last_plan()
+    finally:
+        lib.set_option("DW_R", old)
+        lib.set_math_mode("3xtf32")
+    assert lib.device_status() == 0
+    assert plan.startswith("dw_halo") and "R=7" in plan, plan
+    dW64, SW = O.deconv3D_deltaW_f64(X, dY, FH, FW, sh, sw, ph, pw, threads=8)
+    m = metrics(dW, dW64, SW)
+    record(dict(case=name, mode=mode, tile="dw R=7", dw=m))
+    assert m["finite"] and m["norm"] <= TOL[mode]["norm"] and m["comp"] <= TOL[mode]["comp"], (plan, m)
+
+
+def test_seven_row_tiles_are_chosen_where_they_cover_the_image(pkg, eng):
+    import torch
+    lib = pkg.submodule("lib")
+    dev = torch.device("cuda:0")
+    lib.set_math_mode("tf32")
+    try:
+        for (N, HW, Cc), want in (((256, 7, 512), "R=7"), ((256, 56, 64), "R=7"), ((256, 14, 256), "R=4"), ((256, 28, 128), "R=4")):
+            X, dY = torch.zeros((N, HW, HW, Cc), device=dev), torch.zeros((N, HW, HW, Cc), device=dev)
+            dW = eng.dconv3D_deltaW(X, dY, 3, 3, 1, 1, 1, 1)
+            plan = lib.last_plan()
+            assert plan.startswith("dw_halo") and want in plan, plan
+            assert float(dW.abs().max()) == 0.0
+    finally:
+        lib.set_math_mode("3xtf32")
+    assert lib.device_status() == 0
