@@ -61,6 +61,7 @@ enum Opt {
     OPT_HALO_NARROW, OPT_HALO_DUAL, OPT_PATCH_MATRIX, OPT_DX_PHASES, OPT_DX_COL2IM, OPT_DX_TRANSPOSE,
     OPT_DW_STACKED, OPT_DW_DIAG, OPT_DW_CW, OPT_DW_R, OPT_DW_STATIC, OPT_CONV_PROF, OPT_SM_BUDGET,
     OPT_SKINNY, OPT_HALO_DEEP, OPT_HALO_SPLITB, OPT_NVTX, OPT_DW_LANES, OPT_HALO_TAPSTACK, OPT_HALO_FLAT32,
+    OPT_DW_STRIDED,     // 0 = strided deltaW on the split-K im2col kernel only
     OPT_COUNT
 };
 struct OptDef { const char* name; int dflt; };
@@ -70,6 +71,7 @@ static const OptDef kOptDefs[OPT_COUNT] = {
     {"HALO_NARROW", 1}, {"HALO_DUAL", 1}, {"PATCH_MATRIX", 1}, {"DX_PHASES", 1}, {"DX_COL2IM", 1}, {"DX_TRANSPOSE", 1},
     {"DW_STACKED", -1}, {"DW_DIAG", 1}, {"DW_CW", 0}, {"DW_R", 0}, {"DW_STATIC", 1}, {"CONV_PROF", 0}, {"SM_BUDGET", 0},
     {"SKINNY", 1}, {"HALO_DEEP", 1}, {"HALO_SPLITB", 0}, {"NVTX", 1}, {"DW_LANES", 0}, {"HALO_TAPSTACK", 1}, {"HALO_FLAT32", 1},
+    {"DW_STRIDED", 1},
 };
 static std::atomic<int> g_opt[OPT_COUNT];
 static std::once_flag g_opt_once;
@@ -1530,13 +1532,14 @@ static int launch_dx_col2im(DeviceCtx* c, const AlphaConvShape* s, const float* 
     return check_launch("col2im_gather_kernel");
 }
 
-// ---- deltaW, halo-tile kernel (stride 1): plan and launch -----------------------------------------
+// ---- deltaW, halo-tile kernel (strides 1 and 2): plan and launch -----------------------------------
 
-template <int FW_T, int R_T, int CW_T>
+template <int FW_T, int R_T, int CW_T, bool STR_T = false>
 static void dw_halo_set_attr()
 {
-    cudaFuncSetAttribute(conv_dw_halo_kernel<FW_T, R_T, CW_T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    cudaFuncSetAttribute(conv_dw_halo_kernel<FW_T, R_T, CW_T, STR_T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
 }
+static inline int floor_div(int a, int b) { return a >= 0 ? a / b : -((-a + b - 1) / b); }
 
 // Returns 1 when the shape is left to the split-K im2col kernel, 0 on launch, < 0 on error.
 // deltaB != nullptr: the kernel also sums the columns of deltaY (bias gradient); *bias_fused tells whether it did.
@@ -1558,8 +1561,24 @@ static int launch_dw_halo(DeviceCtx* c, const AlphaConvShape* s_in, const float*
         flat.N = 1; flat.OW = flat.IW = 16; flat.OH = flat.IH = (int)(flat_m / 16);
         s = &flat;
     }
-    if (s->sh != 1 || s->sw != 1 || s->IC % 32 != 0) return 1;
+    if (s->sh < 1 || s->sh > 2 || s->sw < 1 || s->sw > 2 || s->IC % 32 != 0) return 1;
+    const bool strided = s->sh != 1 || s->sw != 1;
+    if (strided && (per_image || !opt(OPT_DW_STRIDED))) return 1;
     if (s->FW > 8 || s->ph >= s->FH || s->pw >= s->FW) return 1;
+    // column phases of the taps: tap fw meets lattice column floor((fw - pw) / sw) + (output column) of phase (fw - pw) mod sw
+    int nph = 0, ph_psi[2] = {0, 0}, ph_qmin[2] = {0, 0}, ph_qmax[2] = {0, 0}, tap_k[8], tap_q[8];
+    for (int fw = 0; fw < s->FW; ++fw) {
+        const int q = floor_div(fw - s->pw, s->sw), psi = fw - s->pw - q * s->sw;
+        int k = 0;
+        while (k < nph && ph_psi[k] != psi) ++k;
+        if (k == nph) { ph_psi[k] = psi; ph_qmin[k] = ph_qmax[k] = q; ++nph; }
+        if (q < ph_qmin[k]) ph_qmin[k] = q;
+        if (q > ph_qmax[k]) ph_qmax[k] = q;
+        tap_k[fw] = k; tap_q[fw] = q;
+    }
+    for (int k = 0; k < nph; ++k)
+        if (ph_psi[k] >= s->IW) return 1;                 // a lattice without a column
+    if (s->sh > s->IH) return 1;
     // input channels per CTA: FW accumulators of NT columns must fit the 512 tensor-memory columns
     int NT = 0;
     for (int cand = 256; cand >= 32; cand >>= 1)
@@ -1612,7 +1631,7 @@ static int launch_dw_halo(DeviceCtx* c, const AlphaConvShape* s_in, const float*
     int R = opt(OPT_DW_R);
     auto stage_bytes = [&](int r) {
         const uint32_t dyblk = ((uint32_t)r * CW * 128 + 1023) & ~1023u, xbk = ((uint32_t)r * PW * 128 + 1023) & ~1023u;
-        return (size_t)planes * (dyb * dyblk + (NT / 32) * xbk);
+        return (size_t)planes * (dyb * dyblk + (size_t)nph * (NT / 32) * xbk);
     };
     if (!R) {
         // Tile height: a tile costs its R * CW / 8 steps of 8 pixels plus a fixed share (the refill of its ring
@@ -1629,6 +1648,17 @@ static int launch_dw_halo(DeviceCtx* c, const AlphaConvShape* s_in, const float*
         }
     }
     if (2 * stage_bytes(R) > 220 * 1024) return 1;
+    if (strided && !opt(OPT_DW_R) && opt(OPT_DW_STRIDED) != 2) {
+        // Few pixels per image leave tiles of one or two steps, whose fixed share dominates; below a fifth (3xTF32;
+        // a seventh in plain TF32) of the steps doing work the split-K im2col kernel, whose tiles span images, is
+        // faster (measured at 8x8x256 -> 4x4x512: 0.29 against 0.18 ms in 3xTF32, 0.131 against 0.126 ms in TF32).
+        const int halves = diag ? 2 : 1, fixed = (mode3x && !diag) ? 4 : 8;
+        long long cost = 0;
+        for (int top = 0; top < s->OH; top += R * halves) cost += (long long)R * (CW / 8) + fixed;
+        cost *= (s->OW + CW - 1) / CW;
+        const double eff = (double)s->OH * s->OW / 8.0 / (double)(cost * halves);
+        if (eff < (mode3x ? 0.2 : 0.15)) return 1;
+    }
     int stages = (int)((220 * 1024) / stage_bytes(R));
     if (stages > 4) stages = 4;
     p.R = R; p.CW = CW; p.PW = PW;
@@ -1652,6 +1682,13 @@ static int launch_dw_halo(DeviceCtx* c, const AlphaConvShape* s_in, const float*
     p.tmem_cols = pow2_cols(s->FW * (stacked ? 2 * NT : NT));
     p.dy_tx = (uint32_t)R * CW * 128; p.dy_blk = (p.dy_tx + 1023) & ~1023u;
     p.x_tx = (uint32_t)R * PW * 128; p.x_blk = (p.x_tx + 1023) & ~1023u;
+    p.sh = s->sh; p.sw = s->sw; p.nph = nph;
+    {
+        const uint32_t xph = (uint32_t)(NT / 32) * p.x_blk, xph_stride = stacked ? 2 * xph : xph;
+        for (int k = 0; k < nph; ++k) p.col_q0[k] = ph_qmin[k];
+        for (int fw = 0; fw < s->FW; ++fw)
+            p.tap_off16[fw] = (tap_k[fw] * xph_stride + (uint32_t)(tap_q[fw] - ph_qmin[tap_k[fw]]) * 128u) >> 4;
+    }
     const size_t sizeW = (size_t)s->OC * s->FH * s->FW * s->IC;
     float* ws = nullptr;
     if (parts * nsub > 1 && !per_image) {
@@ -1672,12 +1709,21 @@ static int launch_dw_halo(DeviceCtx* c, const AlphaConvShape* s_in, const float*
         p.bias_out = bias_parts;
     }
 
-    CUtensorMap tmX, tmDY;
-    cuuint64_t xd[4] = {(cuuint64_t)s->IC, (cuuint64_t)s->IW, (cuuint64_t)s->IH, (cuuint64_t)s->N};
-    cuuint64_t xs[3] = {(cuuint64_t)s->IC * 4, (cuuint64_t)s->IW * s->IC * 4, (cuuint64_t)s->IH * s->IW * s->IC * 4};
-    cuuint32_t xbox[4] = {32, (cuuint32_t)PW, (cuuint32_t)R, 1};
-    int rc = make_tiled_map(&tmX, X, 4, xd, xs, xbox, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
-    if (rc) return rc;
+    // X through one map per lattice phase [row phase][column phase]: rows phi, phi + sh, ... and columns psi, psi + sw, ...
+    DwXMaps tmXs;
+    CUtensorMap tmDY;
+    int rc = 0;
+    for (int phi = 0; phi < s->sh; ++phi)
+        for (int k = 0; k < nph; ++k) {
+            const int psi = ph_psi[k];
+            cuuint64_t xd[4] = {(cuuint64_t)s->IC, (cuuint64_t)((s->IW - psi + s->sw - 1) / s->sw),
+                                (cuuint64_t)((s->IH - phi + s->sh - 1) / s->sh), (cuuint64_t)s->N};
+            cuuint64_t xs[3] = {(cuuint64_t)s->sw * s->IC * 4, (cuuint64_t)s->sh * s->IW * s->IC * 4, (cuuint64_t)s->IH * s->IW * s->IC * 4};
+            cuuint32_t xbox[4] = {32, (cuuint32_t)PW, (cuuint32_t)R, 1};
+            rc = make_tiled_map(&tmXs.m[phi * nph + k], X + ((size_t)phi * s->IW + psi) * s->IC, 4, xd, xs, xbox, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
+            if (rc) return rc;
+        }
+    for (int i = s->sh * nph; i < 4; ++i) tmXs.m[i] = tmXs.m[0];
     cuuint64_t yd[4] = {(cuuint64_t)s->OC, (cuuint64_t)s->OW, (cuuint64_t)s->OH, (cuuint64_t)s->N};
     cuuint64_t ys[3] = {(cuuint64_t)s->OC * 4, (cuuint64_t)s->OW * s->OC * 4, (cuuint64_t)s->OH * s->OW * s->OC * 4};
     cuuint32_t ybox[4] = {32, (cuuint32_t)CW, (cuuint32_t)R, 1};
@@ -1692,12 +1738,30 @@ static int launch_dw_halo(DeviceCtx* c, const AlphaConvShape* s_in, const float*
         dw_halo_set_attr<3, 2, 8>(); dw_halo_set_attr<3, 4, 8>(); dw_halo_set_attr<3, 8, 8>();
         dw_halo_set_attr<3, 7, 16>(); dw_halo_set_attr<3, 7, 8>();
         dw_halo_set_attr<1, 2, 16>(); dw_halo_set_attr<1, 4, 16>(); dw_halo_set_attr<1, 8, 16>();
+        dw_halo_set_attr<3, 2, 16, true>(); dw_halo_set_attr<3, 4, 16, true>(); dw_halo_set_attr<3, 8, 16, true>(); dw_halo_set_attr<3, 7, 16, true>();
+        dw_halo_set_attr<3, 4, 8, true>(); dw_halo_set_attr<3, 8, 8, true>(); dw_halo_set_attr<3, 7, 8, true>();
+        dw_halo_set_attr<4, 2, 16, true>(); dw_halo_set_attr<4, 4, 16, true>(); dw_halo_set_attr<4, 8, 16, true>();
+        dw_halo_set_attr<4, 4, 8, true>(); dw_halo_set_attr<4, 8, 8, true>();
         attr_done = true;
     }
-#define DWH_LAUNCH(FW_, R_, CW_) do { if (!t_dry) conv_dw_halo_kernel<FW_, R_, CW_><<<grid, kDwHaloThreads, smem, stream>>>(tmX, tmDY, p); } while (0)
-    const bool st = s->FW == 3 && opt(OPT_DW_STATIC) != 0;
-    const bool st1 = s->FW == 1 && CW == 16 && opt(OPT_DW_STATIC) != 0;   // 1x1 (flat 16-column view)
-    if (st && R == 1 && CW == 16) DWH_LAUNCH(3, 1, 16);
+#define DWH_LAUNCH(FW_, R_, CW_) do { if (!t_dry) conv_dw_halo_kernel<FW_, R_, CW_><<<grid, kDwHaloThreads, smem, stream>>>(tmXs, tmDY, p); } while (0)
+#define DWH_LAUNCH_S(FW_, R_, CW_) do { if (!t_dry) conv_dw_halo_kernel<FW_, R_, CW_, true><<<grid, kDwHaloThreads, smem, stream>>>(tmXs, tmDY, p); } while (0)
+    const bool st = s->FW == 3 && !strided && opt(OPT_DW_STATIC) != 0;
+    const bool st1 = s->FW == 1 && CW == 16 && opt(OPT_DW_STATIC) != 0;   // 1x1 (flat 16-column view; with a stride: one phase, start 0)
+    const bool ss3 = s->FW == 3 && strided && opt(OPT_DW_STATIC) != 0, ss4 = s->FW == 4 && strided && opt(OPT_DW_STATIC) != 0;
+    if (ss3 && R == 2 && CW == 16) DWH_LAUNCH_S(3, 2, 16);
+    else if (ss3 && R == 4 && CW == 16) DWH_LAUNCH_S(3, 4, 16);
+    else if (ss3 && R == 8 && CW == 16) DWH_LAUNCH_S(3, 8, 16);
+    else if (ss3 && R == 7 && CW == 16) DWH_LAUNCH_S(3, 7, 16);
+    else if (ss3 && R == 4 && CW == 8) DWH_LAUNCH_S(3, 4, 8);
+    else if (ss3 && R == 8 && CW == 8) DWH_LAUNCH_S(3, 8, 8);
+    else if (ss3 && R == 7 && CW == 8) DWH_LAUNCH_S(3, 7, 8);
+    else if (ss4 && R == 2 && CW == 16) DWH_LAUNCH_S(4, 2, 16);
+    else if (ss4 && R == 4 && CW == 16) DWH_LAUNCH_S(4, 4, 16);
+    else if (ss4 && R == 8 && CW == 16) DWH_LAUNCH_S(4, 8, 16);
+    else if (ss4 && R == 4 && CW == 8) DWH_LAUNCH_S(4, 4, 8);
+    else if (ss4 && R == 8 && CW == 8) DWH_LAUNCH_S(4, 8, 8);
+    else if (st && R == 1 && CW == 16) DWH_LAUNCH(3, 1, 16);
     else if (st && R == 2 && CW == 16) DWH_LAUNCH(3, 2, 16);
     else if (st && R == 4 && CW == 16) DWH_LAUNCH(3, 4, 16);
     else if (st && R == 8 && CW == 16) DWH_LAUNCH(3, 8, 16);
@@ -1711,9 +1775,10 @@ static int launch_dw_halo(DeviceCtx* c, const AlphaConvShape* s_in, const float*
     else if (st1 && R == 8) DWH_LAUNCH(1, 8, 16);
     else DWH_LAUNCH(0, 0, 0);
 #undef DWH_LAUNCH
+#undef DWH_LAUNCH_S
     note_launch("dw_halo");
-    snprintf(g_plan, sizeof(g_plan), "dw_halo%s NT=%d R=%d CW=%d stages=%d parts=%d groups=%d", diag ? " diagonal" : (stacked ? " stacked" : ""), NT, R, CW,
-             stages, parts, groups);
+    snprintf(g_plan, sizeof(g_plan), "dw_halo%s%s NT=%d R=%d CW=%d stages=%d parts=%d groups=%d", diag ? " diagonal" : (stacked ? " stacked" : ""),
+             strided ? (nph == 2 ? " strided 2 phases" : " strided") : "", NT, R, CW, stages, parts, groups);
     rc = check_launch("conv_dw_halo_kernel");
     if (rc || per_image) return rc;
     if (parts * nsub > 1) {

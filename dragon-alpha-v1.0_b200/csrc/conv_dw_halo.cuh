@@ -33,6 +33,12 @@
 // strides over 32 rows at a time), and after the loop the 32 threads of each channel quad are added in
 // thread order.  Pixels outside the image and channels beyond OC arrive as zeros from the TMA.
 //
+// Strides 1 and 2.  With a stride the X pixels one tap meets lie sw columns (sh rows) apart, so X is addressed
+// through one tensor map per phase of that lattice - rows (fh - ph) mod sh, fixed for a CTA, and columns
+// (fw - pw) mod sw - whose tiles are dense again: a pixel tile stages one X tile per column phase its taps use
+// (two for 3x3 and 4x4 stride 2, one for 1x1), and a tap starts its descriptor at its phase's tile plus
+// floor((fw - pw) / sw) pixels.  Stride 1 is the case of one phase and a start of fw pixels.
+//
 // Warps: 0 TMA producer, 1 MMA issuer, 2-9 operand split (3xTF32) during the loop, 2-5 epilogue after.
 #pragma once
 #include "conv_halo.cuh"
@@ -66,13 +72,24 @@ struct DwHaloParams {
     // fh == 0 and ict == 0 (one group per output-channel tile) also sum the columns of the deltaY tiles
     // they stage; CTA x of such a group writes its partial sums to bias_out[x * OC + oc].
     float* bias_out;
+    // strided convolutions (see above): one X tile per column phase; all zero / one phase for stride 1
+    int sh, sw;               // strides, 1 or 2
+    int nph;                  // column phases staged per pixel tile (1 or 2)
+    int col_q0[2];            // first lattice column of phase k's tile, relative to the tile's first output column
+    uint32_t tap_off16[8];    // start of tap fw's X tile within the X region of a stage, in 16-byte units
+};
+
+// X tensor maps by [row phase][column phase]; stride 1 uses entry 0
+struct DwXMaps {
+    CUtensorMap m[4];
 };
 
 // The MMAs of one staged pixel tile as straight-line code: all steps of one tap back to back.
 // MODE 1 issues lo*hi, hi*lo, hi*hi per step; MODE 0 one MMA (plain TF32, or stacked planes).
-template <int MODE, int FW_T, int R_T, int CW_T>
+template <int MODE, int FW_T, int R_T, int CW_T, bool STR_T>
 __device__ __forceinline__ void dw_issue_tile(uint32_t tmem_base, uint32_t acc_cols, uint32_t a_s, uint32_t b_s,
-                                              uint32_t lo_off, uint32_t dhi, uint32_t idesc, uint32_t acc)
+                                              uint32_t lo_off, uint32_t dhi, uint32_t idesc, uint32_t acc,
+                                              const uint32_t* __restrict__ toff)
 {
     constexpr int kPW = CW_T + FW_T - 1;
 #pragma unroll
@@ -83,7 +100,7 @@ __device__ __forceinline__ void dw_issue_tile(uint32_t tmem_base, uint32_t acc_c
 #pragma unroll
             for (int g = 0; g < CW_T / 8; ++g) {
                 const uint32_t a_k = a_s + (r * CW_T + g * 8) * 8;
-                const uint32_t b_k = b_s + (r * kPW + g * 8 + fw) * 8;
+                const uint32_t b_k = b_s + (STR_T ? toff[fw] : fw * 8) + (r * kPW + g * 8) * 8;
                 const uint32_t first = (r | g) ? 1u : acc;
                 if (MODE == 1) {
                     mma_tf32_ss2(d, a_k + lo_off, dhi, b_k, dhi, idesc, first);
@@ -100,11 +117,12 @@ __device__ __forceinline__ void dw_issue_tile(uint32_t tmem_base, uint32_t acc_c
 // parameter so that no branch sits between two MMAs.
 template <int MODE>
 __device__ __forceinline__ void dw_issue_tile_rt(uint32_t tmem_base, uint32_t acc_cols, uint32_t a_s, uint32_t b_s, uint32_t lo_off,
-                                                 uint32_t dhi, uint32_t idesc, uint32_t acc, int FW, int R, int CW, int PW)
+                                                 uint32_t dhi, uint32_t idesc, uint32_t acc, int FW, int R, int CW, int PW,
+                                                 const uint32_t* __restrict__ toff)
 {
-    uint32_t d = tmem_base, b_tap = b_s;
-    for (int fw = 0; fw < FW; ++fw, b_tap += 8, d += acc_cols) {
-        uint32_t a_row = a_s, b_row = b_tap;
+    uint32_t d = tmem_base;
+    for (int fw = 0; fw < FW; ++fw, d += acc_cols) {
+        uint32_t a_row = a_s, b_row = b_s + toff[fw];
         uint32_t first = acc;
         for (int r = 0; r < R; ++r, a_row += CW * 8, b_row += PW * 8) {
             uint32_t a_k = a_row, b_k = b_row;
@@ -123,10 +141,10 @@ __device__ __forceinline__ void dw_issue_tile_rt(uint32_t tmem_base, uint32_t ac
 }
 
 // FW_T > 0: FW, R and CW are compile-time and the MMAs of a stage are straight-line code.
-template <int FW_T, int R_T, int CW_T>
+template <int FW_T, int R_T, int CW_T, bool STR_T = false>
 __global__ void __launch_bounds__(kDwHaloThreads, 1)
-    conv_dw_halo_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmDY,
-                        const DwHaloParams p)
+    conv_dw_halo_kernel(const __grid_constant__ DwXMaps tmXs, const __grid_constant__ CUtensorMap tmDY,
+                        const __grid_constant__ DwHaloParams p)
 {
     constexpr bool kStatic = FW_T > 0;
     extern __shared__ uint8_t smem_raw[];
@@ -140,11 +158,13 @@ __global__ void __launch_bounds__(kDwHaloThreads, 1)
     const bool stacked = p.mode3x == 2 || diag;   // layout [dY a][dY b] [X a][X b], M = 64 + 64, N = NT + NT
     const int dyb = stacked ? 2 : 4;                // deltaY blocks per plane: 64 or 128 output channels
     const uint32_t dy_bytes = dyb * p.dy_blk;
-    const uint32_t x_bytes = xb * p.x_blk;
+    const uint32_t xph = xb * p.x_blk;             // X tile of one column phase
+    const uint32_t x_bytes = p.nph * xph;
     const uint32_t plane_bytes = dy_bytes + x_bytes;
     const uint32_t stage_bytes = plane_bytes * planes;
-    // stage layout.  modes 0/1: [dY hi][X hi] [dY lo][X lo];  mode 2: [dY hi][dY lo] [X hi][X lo]
+    // stage layout.  modes 0/1: [dY hi][X hi] [dY lo][X lo];  mode 2: [dY hi][dY lo] then per column phase [X hi][X lo]
     const uint32_t x_off = stacked ? 2 * dy_bytes : dy_bytes;
+    const uint32_t xph_stride = stacked ? 2 * xph : xph;   // between the tiles of two column phases
     const int oc_tile = stacked ? 64 : 128;
     const uint32_t acc_cols = stacked ? 2 * p.NT : p.NT;
 
@@ -163,7 +183,7 @@ __global__ void __launch_bounds__(kDwHaloThreads, 1)
         }
         mbar_init(accum, 1);
         fence_barrier_init();
-        prefetch_tmap(&tmX);
+        prefetch_tmap(&tmXs.m[0]);
         prefetch_tmap(&tmDY);
     }
     if (warp == 1) {
@@ -181,6 +201,10 @@ __global__ void __launch_bounds__(kDwHaloThreads, 1)
     const int ict = (grp / p.FH) % p.ic_tiles;
     const int oct = grp / (p.FH * p.ic_tiles);
     const int ic0 = ict * p.NT, oc0 = oct * oc_tile;
+    // X rows of this filter row: lattice row qrow + (output row) of row phase phi
+    const int drow = fh - p.ph;
+    const int qrow = drow >= 0 ? drow / p.sh : -((-drow + p.sh - 1) / p.sh);
+    const int phi = drow - qrow * p.sh;
 
     const uint32_t smem_a = smem_u32(smem);
     const uint32_t full_a = smem_u32(full), ready_a = smem_u32(ready), empty_a = smem_u32(empty);
@@ -210,14 +234,16 @@ __global__ void __launch_bounds__(kDwHaloThreads, 1)
                 const uint32_t bar = full_a + 8 * rp.idx;
                 const uint32_t dst = smem_a + rp.idx * stage_bytes;
                 const int halves = diag ? 2 : 1;
-                mbar_arrive_expect_tx_a(bar, halves * (dyb * p.dy_tx + xb * p.x_tx));
+                mbar_arrive_expect_tx_a(bar, halves * (dyb * p.dy_tx + p.nph * xb * p.x_tx));
                 const int ow0 = cb * CW;
                 for (int h = 0; h < halves; ++h) {
                     const int oh0 = (rb * halves + h) * R;   // diagonal: the tile is 2R rows, one half per slot
                     for (int b = 0; b < dyb; ++b)
                         tma_load_4d_a(dst + h * dy_bytes + b * p.dy_blk, &tmDY, bar, oc0 + b * 32, ow0, oh0, n);
-                    for (int b = 0; b < xb; ++b)
-                        tma_load_4d_a(dst + x_off + h * x_bytes + b * p.x_blk, &tmX, bar, ic0 + b * 32, ow0 - p.pw, oh0 + fh - p.ph, n);
+                    for (int k = 0; k < p.nph; ++k)
+                        for (int b = 0; b < xb; ++b)
+                            tma_load_4d_a(dst + x_off + k * xph_stride + h * xph + b * p.x_blk, &tmXs.m[phi * p.nph + k], bar,
+                                          ic0 + b * 32, ow0 + p.col_q0[k], oh0 + qrow, n);
                 }
                 rp.advance(S);
             }
@@ -247,11 +273,11 @@ __global__ void __launch_bounds__(kDwHaloThreads, 1)
                 if constexpr (kStatic) {
                     // the mode test stays outside the unrolled MMAs: a branch per MMA costs the issuing
                     // thread more than the MMA takes
-                    if (three) dw_issue_tile<1, FW_T, R_T, CW_T>(tmem_base, acc_cols, a_s, b_s, lo_off, dhi, p.idesc, acc);
-                    else dw_issue_tile<0, FW_T, R_T, CW_T>(tmem_base, acc_cols, a_s, b_s, lo_off, dhi, p.idesc, acc);
+                    if (three) dw_issue_tile<1, FW_T, R_T, CW_T, STR_T>(tmem_base, acc_cols, a_s, b_s, lo_off, dhi, p.idesc, acc, p.tap_off16);
+                    else dw_issue_tile<0, FW_T, R_T, CW_T, STR_T>(tmem_base, acc_cols, a_s, b_s, lo_off, dhi, p.idesc, acc, p.tap_off16);
                 } else {
-                    if (three) dw_issue_tile_rt<1>(tmem_base, acc_cols, a_s, b_s, lo_off, dhi, p.idesc, acc, FW, R, CW, PW);
-                    else dw_issue_tile_rt<0>(tmem_base, acc_cols, a_s, b_s, lo_off, dhi, p.idesc, acc, FW, R, CW, PW);
+                    if (three) dw_issue_tile_rt<1>(tmem_base, acc_cols, a_s, b_s, lo_off, dhi, p.idesc, acc, FW, R, CW, PW, p.tap_off16);
+                    else dw_issue_tile_rt<0>(tmem_base, acc_cols, a_s, b_s, lo_off, dhi, p.idesc, acc, FW, R, CW, PW, p.tap_off16);
                 }
                 acc = 1u;
                 const long long t_i1 = prof_on ? clock64() : 0;
@@ -298,7 +324,8 @@ __global__ void __launch_bounds__(kDwHaloThreads, 1)
                 if (split_on) {
                     if (stacked) {
                         split_plane_lo_x4(hi, hi + dy_bytes, dy_bytes, tid128, kDwSplitThreads);
-                        split_plane_lo_x4(hi + x_off, hi + x_off + x_bytes, x_bytes, tid128, kDwSplitThreads);
+                        for (int k = 0; k < p.nph; ++k)
+                            split_plane_lo_x4(hi + x_off + k * xph_stride, hi + x_off + k * xph_stride + xph, xph, tid128, kDwSplitThreads);
                     } else {
                         split_plane_lo_x4(hi, hi + plane_bytes, plane_bytes, tid128, kDwSplitThreads);
                     }

@@ -611,3 +611,69 @@ def test_seven_row_tiles_are_chosen_where_they_cover_the_image(pkg, eng):
     finally:
         lib.set_math_mode("3xtf32")
     assert lib.device_status() == 0
+
+
+# Strided deltaW on the halo-tile kernel: X through one tensor map per phase of the stride lattice.  Two column
+# phases (3x3, 4x4 and 5x5 stride 2), one (1x1 stride 2; stride 2 along H only), odd image sizes whose lattices
+# differ in length, no padding, and the stacked / diagonal / three-MMA forms of both math modes.
+STRIDED_DW_CASES = {
+    "sdw_3x3_s2_16x16x32": (4, 16, 16, 32, 32, 3, 3, 2, 2, 1, 1),
+    "sdw_3x3_s2_15x17x32_oc64": (4, 15, 17, 32, 64, 3, 3, 2, 2, 1, 1),
+    "sdw_3x3_s2x1_12x12x64_oc96": (3, 12, 12, 64, 96, 3, 3, 2, 1, 1, 1),
+    "sdw_3x3_s1x2_12x12x64_oc96": (3, 12, 12, 64, 96, 3, 3, 1, 2, 1, 1),
+    "sdw_4x4_s2_8x8x64_oc128": (4, 8, 8, 64, 128, 4, 4, 2, 2, 1, 1),
+    "sdw_4x4_s2_32x32x32_oc64": (2, 32, 32, 32, 64, 4, 4, 2, 2, 1, 1),
+    "sdw_1x1_s2_16x16x64_oc128": (4, 16, 16, 64, 128, 1, 1, 2, 2, 0, 0),
+    "sdw_5x5_s2_20x20x32": (2, 20, 20, 32, 32, 5, 5, 2, 2, 2, 2),
+    "sdw_3x3_s2_nopad_9x9x32": (2, 9, 9, 32, 32, 3, 3, 2, 2, 0, 0),
+    "sdw_3x3_s2_14x14x256": (2, 14, 14, 256, 256, 3, 3, 2, 2, 1, 1),
+}
+CASES.update(STRIDED_DW_CASES)
+
+
+@pytest.mark.parametrize("mode", ["3xtf32", "tf32"])
+@pytest.mark.parametrize("name", list(STRIDED_DW_CASES))
+def test_strided_deltaW_on_the_halo_kernel(pkg, eng, oracle_mod, name, mode):
+    import torch
+    O, lib = oracle_mod, pkg.submodule("lib")
+    N, IH, IW, IC, OC, FH, FW, sh, sw, ph, pw = CASES[name]
+    OH, OW = out_hw(IH, IW, FH, FW, sh, sw, ph, pw)
+    rng = np.random.default_rng(zlib.crc32(name.encode()))
+    X, dY = gen((N, IH, IW, IC), "relu", rng), gen((N, OH, OW, OC), "n01", rng)
+    dev = torch.device("cuda:0")
+    lib.set_math_mode(mode)
+    old = lib.set_option("DW_STRIDED", 2)     # also where the planner would leave few-pixel images to the split-K kernel
+    try:
+        tX, tdY = torch.from_numpy(X).to(dev), torch.from_numpy(dY).to(dev)
+        dW = eng.dconv3D_deltaW(tX, tdY, FH, FW, sh, sw, ph, pw).cpu().numpy()
+        plan = lib.last_plan()
+        lib.set_option("DW_STRIDED", 0)
+        other = eng.dconv3D_deltaW(tX, tdY, FH, FW, sh, sw, ph, pw).cpu().numpy()
+    finally:
+        lib.set_option("DW_STRIDED", old)
+        lib.set_math_mode("3xtf32")
+    assert lib.device_status() == 0
+    assert plan.startswith("dw_halo") and "strided" in plan, plan
+    dW64, SW = O.deconv3D_deltaW_f64(X, dY, FH, FW, sh, sw, ph, pw, threads=8)
+    m = metrics(dW, dW64, SW)
+    record(dict(case=name, mode=mode, tile="dw strided", dw=m))
+    assert m["finite"] and m["norm"] <= TOL[mode]["norm"] and m["comp"] <= TOL[mode]["comp"], (plan, m)
+    # and against the split-K im2col kernel on the same tensors
+    assert np.abs(dW - other).max() <= TOL[mode]["norm"] * np.abs(other).max(), plan
+
+
+def test_strided_deltaW_plan_choice(pkg, eng):
+    """Down-sampling layers at the benchmark's batch take the halo kernel; images of a few pixels stay on the split-K kernel in 3xTF32."""
+    import torch
+    lib = pkg.submodule("lib")
+    dev = torch.device("cuda:0")
+    lib.set_math_mode("3xtf32")
+    for (N, IH, IC, OC, F, p), halo in (((512, 32, 64, 128, 3, 1), True), ((512, 16, 128, 256, 3, 1), True), ((512, 8, 256, 512, 3, 1), False),
+                                        ((512, 32, 64, 128, 1, 0), True), ((256, 16, 128, 256, 4, 1), True)):
+        OH = (IH + 2 * p - F) // 2 + 1
+        X, dY = torch.zeros((N, IH, IH, IC), device=dev), torch.zeros((N, OH, OH, OC), device=dev)
+        dW = eng.dconv3D_deltaW(X, dY, F, F, 2, 2, p, p)
+        algo, plan = lib.last_algo(), lib.last_plan()
+        assert (algo.startswith("dw_halo") and "strided" in plan) == halo, (IH, IC, OC, F, algo, plan)
+        assert float(dW.abs().max()) == 0.0
+    assert lib.device_status() == 0
