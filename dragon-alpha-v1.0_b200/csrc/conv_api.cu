@@ -1489,7 +1489,16 @@ static int launch_dx_col2im(DeviceCtx* c, const AlphaConvShape* s, const float* 
     // cost 2 * |P| of HBM traffic and the phases win.
     const bool planes = s->IC <= 8 && cols <= 512;
     const bool small_p = opt(OPT_DX_COL2IM) >= 1 && M * (size_t)cols * sizeof(float) <= (size_t)96 << 20 && cols <= 65536;
-    if (!planes && !small_p) return 1;
+    // Phase images of a few pixels (a 4x4 s2 generator layer growing 4x4 to 8x8: four phases of 4x4 pixels) fill a
+    // fraction of a 16 x 8 pixel accumulator tile, while the dense product has no idle lane and no wasted product
+    // (every deltaY pixel times every tap is used exactly once), so it wins although P then passes through HBM:
+    // phases of at most 4x4 pixels in both math modes, of at most 8x8 in 3xTF32, whose longer MMAs hide the passes
+    // over P (batch 1024, 4x4 s2: 8x8x256 from 4x4x512 0.72 -> 0.41 ms, 16x16x128 from 8x8x256 0.88 -> 0.53 ms).
+    const int pa = (s->IH + s->sh - 1) / s->sh, pb = (s->IW + s->sw - 1) / s->sw;
+    const bool tiny_phase = (s->sh > 1 || s->sw > 1) && opt(OPT_DX_COL2IM) >= 1 && cols <= 65536 && s->IC % 32 == 0 &&
+                            M * (size_t)cols * sizeof(float) <= (size_t)2 << 30 && (pa * pb <= 16 || (mode3x && pa * pb <= 64));
+    const bool forced_p = opt(OPT_DX_COL2IM) == 2 && cols <= 65536 && M * (size_t)cols * sizeof(float) <= (size_t)8 << 30;
+    if (!planes && !small_p && !tiny_phase && !forced_p) return 1;
     const int tap_major = planes ? 0 : 1;
     float* ws = nullptr;
     bool fresh = true;
