@@ -6,7 +6,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libalpha_conv_b200.so")
 SOURCES = ["conv_api.cu", "native_api.cu", "matmul_api.cu", "pool_api.cu", "jni_shim.cpp"]
-HEADERS = ["conv_kernels.cuh", "conv_halo.cuh", "conv_halo_pair.cuh", "conv_dw_halo.cuh", "winograd.cuh", "sm100_ptx.cuh",
+HEADERS = ["conv_kernels.cuh", "conv_halo.cuh", "conv_halo_pair.cuh", "conv_dw_halo.cuh", "winograd.cuh", "conv_tapstack.cuh", "sm100_ptx.cuh", "fast_div.cuh",
            "host_common.h"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-shared", "-Xcompiler", "-fPIC"]
