@@ -1328,7 +1328,13 @@ static int make_patch_matrix(DeviceCtx* c, PatchShape ps, const float* X, cudaSt
     const size_t total = M * (Kp / 4);
     size_t blocks = (total + 255) / 256;
     if (blocks > (size_t)c->sm_count * 16) blocks = (size_t)c->sm_count * 16;
-    if (!t_dry) patch_matrix_kernel<<<(unsigned)blocks, 256, 0, stream>>>(X, ws, ps);
+    const bool idx32 = M * (size_t)Kp <= 2147483647ull && (size_t)ps.N * ps.IH * ps.IW * ps.IC <= 2147483647ull;
+    if (idx32) {
+        const PatchDivs dv{fast_div(Kp / 4), fast_div(ps.IC), fast_div(ps.FW), fast_div(ps.OW), fast_div(ps.OH)};
+        if (!t_dry) patch_matrix32_kernel<<<(unsigned)blocks, 256, 0, stream>>>(X, ws, ps, dv);
+    } else {
+        if (!t_dry) patch_matrix_kernel<<<(unsigned)blocks, 256, 0, stream>>>(X, ws, ps);
+    }
     note_launch("patch_matrix");
     rc = check_launch("patch_matrix_kernel");
     if (rc) return rc;

@@ -187,6 +187,35 @@ __global__ void __launch_bounds__(256) patch_matrix_kernel(const float* __restri
     }
 }
 
+// The same for matrices and tensors of fewer than 2^31 elements: 32-bit indices, divisions as multiplications
+// (the kernel is a gather of 16-byte pieces; five divisions per piece, three of them 64-bit, cost more than the loads).
+struct PatchDivs {
+    FastDiv by_k4n, by_IC, by_FW, by_OW, by_OH;
+};
+__global__ void __launch_bounds__(256) patch_matrix32_kernel(const float* __restrict__ X, float* __restrict__ A, const PatchShape s,
+                                                             const PatchDivs dv)
+{
+    const unsigned k4n = static_cast<unsigned>(s.Kp) >> 2;
+    const unsigned total = static_cast<unsigned>(s.N) * s.OH * s.OW * k4n;
+    for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+        unsigned m, k4;
+        dv.by_k4n.divmod(i, m, k4);
+        const unsigned k = k4 << 2;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (k < static_cast<unsigned>(s.K)) {
+            unsigned tap, ic, fh, fw, t, ow, n, oh;
+            dv.by_IC.divmod(k, tap, ic);
+            dv.by_FW.divmod(tap, fh, fw);
+            dv.by_OW.divmod(m, t, ow);
+            dv.by_OH.divmod(t, n, oh);
+            const int ih = static_cast<int>(oh) * s.sh - s.ph + static_cast<int>(fh), iw = static_cast<int>(ow) * s.sw - s.pw + static_cast<int>(fw);
+            if (ih >= 0 && ih < s.IH && iw >= 0 && iw < s.IW)
+                v = __ldg(reinterpret_cast<const float4*>(X + static_cast<size_t>((n * s.IH + ih) * s.IW + iw) * s.IC + ic));
+        }
+        reinterpret_cast<float4*>(A)[i] = v;
+    }
+}
+
 // dst[r][0..K) = src[r][0..K) of a matrix with row pitch Kp (drops the zero padding columns).
 __global__ void __launch_bounds__(256) unpad_rows_kernel(const float* __restrict__ src, float* __restrict__ dst, int rows, int K, int Kp)
 {
