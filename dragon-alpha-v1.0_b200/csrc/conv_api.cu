@@ -1539,9 +1539,12 @@ static int launch_dx_col2im(DeviceCtx* c, const AlphaConvShape* s, const float* 
     size_t blocks = (total + 255) / 256;
     if (blocks > (size_t)c->sm_count * 16) blocks = (size_t)c->sm_count * 16;
     const bool idx32 = total * 4 <= 2147483647ull && M * (size_t)cols <= 2147483647ull;   // dX and P indexable in 31 bits
-    if (tap_major && idx32) {
+    if (idx32) {
         const GatherDivs dv{fast_div(s->IC / 4), fast_div(s->IW), fast_div(s->IH), fast_div(s->sh), fast_div(s->sw)};
-        if (!t_dry) col2im_gather_tapmajor32_kernel<<<(unsigned)blocks, 256, 0, stream>>>(P, dX, ps, dv);
+        if (!t_dry) {
+            if (tap_major) col2im_gather_tapmajor32_kernel<<<(unsigned)blocks, 256, 0, stream>>>(P, dX, ps, dv);
+            else col2im_gather32_kernel<<<(unsigned)blocks, 256, 0, stream>>>(P, dX, ps, dv);
+        }
     } else if (tap_major) {
         if (!t_dry) col2im_gather_tapmajor_kernel<<<(unsigned)blocks, 256, 0, stream>>>(P, dX, ps);
     } else {

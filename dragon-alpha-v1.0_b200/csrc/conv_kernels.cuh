@@ -347,6 +347,38 @@ __global__ void __launch_bounds__(256) col2im_gather_tapmajor32_kernel(const flo
     }
 }
 
+// The channel-major gather (image planes, P[pixel][ic][tap]) with 32-bit indices and divisions as multiplications.
+__global__ void __launch_bounds__(256) col2im_gather32_kernel(const float* __restrict__ P, float* __restrict__ dX, const PatchShape s,
+                                                              const GatherDivs dv)
+{
+    const unsigned c4n = static_cast<unsigned>(s.IC) >> 2;
+    const unsigned taps = static_cast<unsigned>(s.FH) * s.FW, ldp = static_cast<unsigned>(s.IC) * taps;
+    const unsigned total = static_cast<unsigned>(s.N) * s.IH * s.IW * c4n;
+    for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+        unsigned t, c4, iw, ih, n;
+        dv.by_c4n.divmod(i, t, c4);
+        dv.by_IW.divmod(t, t, iw);
+        dv.by_IH.divmod(t, n, ih);
+        unsigned qh, fh0, qw, fw0;
+        dv.by_sh.divmod(ih + s.ph, qh, fh0);
+        dv.by_sw.divmod(iw + s.pw, qw, fw0);
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        int oh = static_cast<int>(qh);
+        for (int fh = static_cast<int>(fh0); fh < s.FH && oh >= 0; fh += s.sh, --oh) {
+            if (oh >= s.OH) continue;
+            const float* prow = P + static_cast<size_t>((n * s.OH + oh) * s.OW) * ldp + (c4 << 2) * taps;
+            int ow = static_cast<int>(qw);
+            for (int fw = static_cast<int>(fw0); fw < s.FW && ow >= 0; fw += s.sw, --ow) {
+                if (ow >= s.OW) continue;
+                const float* row = prow + static_cast<size_t>(ow) * ldp + fh * s.FW + fw;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) acc[q] += __ldg(row + q * taps);
+            }
+        }
+        *reinterpret_cast<float4*>(dX + static_cast<size_t>(i) * 4) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    }
+}
+
 // hi/lo planes of a whole tensor in global memory (weights are split once per call, not per tile).
 __global__ void split_tensor_kernel(const float4* __restrict__ src, float4* __restrict__ hi, float4* __restrict__ lo, size_t n4)
 {
