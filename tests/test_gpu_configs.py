@@ -155,3 +155,51 @@ def test_positive_inputs_long_reduction(pkg, eng, oracle_mod, shape):
     assert lib.device_status() == 0
     for op, m in res.items():
         assert m["finite"] and m["norm"] <= 1e-4 and m["comp"] <= 1e-4, (op, m)
+
+
+@pytest.mark.parametrize("case", [
+    ("stress_3x3_s2_full", 128, 112, 128, 64, 3, 2, 1),       # strided forward, phase deltaX, strided halo-tile deltaW
+    ("dcgan_8x8_to_16x16_full", 1024, 16, 128, 256, 4, 2, 1),  # generator layer: deltaX through the dense product + col2im
+    ("dcgan_16x16_to_32x32_full", 1024, 32, 64, 128, 4, 2, 1),
+    ("resnet_1x1_s2_full", 512, 32, 64, 128, 1, 2, 0),
+])
+def test_strided_layers_full_size_adjoint_identity(pkg, eng, case):
+    """The strided layers of the large-shape and generator configurations at their full batch, where the oracle is
+    too slow: forward, deltaX and deltaW run on three different kernel families (im2col, phases or dense product +
+    col2im, halo tiles over the stride lattice) and are tied together by
+    <conv(X,W), dY> = <X, deltaX(dY,W)> = <W, deltaW(X,dY)>; deltaW also against the split-K kernel."""
+    import torch
+    tag, N, IH, IC, OC, F, s, p = case
+    lib = pkg.submodule("lib")
+    lib.set_math_mode("3xtf32")
+    dev = torch.device("cuda:0")
+    g = torch.Generator(device=dev).manual_seed(zlib.crc32(tag.encode()))
+    OH, _ = out_hw(IH, IH, F, F, s, s, p, p)
+    X = torch.empty((N, IH, IH, IC), device=dev).uniform_(-1, 1, generator=g)
+    W = torch.empty((OC, F, F, IC), device=dev).uniform_(-1, 1, generator=g) * 0.05
+    dY = torch.empty((N, OH, OH, OC), device=dev).uniform_(-1, 1, generator=g)
+    Y = eng.conv3D(X, W, s, s, p, p)
+    dX = eng.dconv3D_deltaX(dY, W, IH, IH, s, s, p, p)
+    dx_algo = lib.last_algo()
+    dW = eng.dconv3D_deltaW(X, dY, F, F, s, s, p, p)
+    dw_plan = lib.last_plan()
+    old = lib.set_option("DW_STRIDED", 0)
+    try:
+        dW_split = eng.dconv3D_deltaW(X, dY, F, F, s, s, p, p)
+    finally:
+        lib.set_option("DW_STRIDED", old)
+    assert lib.device_status() == 0
+    assert "strided" in dw_plan, dw_plan
+    if tag.startswith("dcgan_8x8"):
+        assert dx_algo == "dx_col2im", dx_algo
+
+    def dot(a, b):
+        acc = 0.0
+        for i in range(0, a.shape[0], 16):
+            acc += float((a[i:i + 16].double() * b[i:i + 16].double()).sum())
+        return acc
+    a, b, c = dot(Y, dY), dot(X, dX), dot(W, dW)
+    tol_b = 1e-4 * float(Y.double().norm() * dY.double().norm()) / (Y.numel() ** 0.5)
+    tol_c = 1e-6 * (N * OH * OH * 0.25) * float(W.double().norm())
+    assert abs(a - b) <= tol_b and abs(a - c) <= tol_c, (a, b, c, tol_b, tol_c)
+    assert float((dW - dW_split).abs().max()) <= 1e-4 * float(dW_split.abs().max())
