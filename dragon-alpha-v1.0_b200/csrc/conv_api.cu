@@ -62,6 +62,7 @@ enum Opt {
     OPT_DW_STACKED, OPT_DW_DIAG, OPT_DW_CW, OPT_DW_R, OPT_DW_STATIC, OPT_CONV_PROF, OPT_SM_BUDGET,
     OPT_SKINNY, OPT_HALO_DEEP, OPT_HALO_SPLITB, OPT_NVTX, OPT_DW_LANES, OPT_HALO_TAPSTACK, OPT_HALO_FLAT32,
     OPT_DW_STRIDED,     // 0 = strided deltaW on the split-K im2col kernel only
+    OPT_DW_TAPGROUPS,   // 0 = a CTA always owns a whole filter row, 2 = rows of more than three taps always split
     OPT_COUNT
 };
 struct OptDef { const char* name; int dflt; };
@@ -71,7 +72,7 @@ static const OptDef kOptDefs[OPT_COUNT] = {
     {"HALO_NARROW", 1}, {"HALO_DUAL", 1}, {"PATCH_MATRIX", 1}, {"DX_PHASES", 1}, {"DX_COL2IM", 1}, {"DX_TRANSPOSE", 1},
     {"DW_STACKED", -1}, {"DW_DIAG", 1}, {"DW_CW", 0}, {"DW_R", 0}, {"DW_STATIC", 1}, {"CONV_PROF", 0}, {"SM_BUDGET", 0},
     {"SKINNY", 1}, {"HALO_DEEP", 1}, {"HALO_SPLITB", 0}, {"NVTX", 1}, {"DW_LANES", 0}, {"HALO_TAPSTACK", 1}, {"HALO_FLAT32", 1},
-    {"DW_STRIDED", 1},
+    {"DW_STRIDED", 1}, {"DW_TAPGROUPS", 1},
 };
 static std::atomic<int> g_opt[OPT_COUNT];
 static std::once_flag g_opt_once;
@@ -1601,55 +1602,71 @@ static int launch_dw_halo(DeviceCtx* c, const AlphaConvShape* s_in, const float*
     for (int k = 0; k < nph; ++k)
         if (ph_psi[k] >= s->IW) return 1;                 // a lattice without a column
     if (s->sh > s->IH) return 1;
-    // input channels per CTA: FW accumulators of NT columns must fit the 512 tensor-memory columns
-    int NT = 0;
-    for (int cand = 256; cand >= 32; cand >>= 1)
-        if (s->IC % cand == 0 && s->FW * cand <= 512) { NT = cand; break; }
-    if (!NT) return 1;
-    // 3xTF32: three MMAs of (128 x NT), or one MMA on stacked hi/lo planes (64 + 64) x (NTq + NTq).
-    // An MMA of N columns costs max(N / 2, 59) clocks whatever its height, so the stacked form wins
-    // where 128 output channels or 64 input channels would be half empty.
-    bool stacked = false;
-    if (mode3x && !per_image) {   // the stacked form leaves two partial planes to add
-        int NTq = 0;
-        for (int cand = 128; cand >= 32; cand >>= 1)
-            if (s->IC % cand == 0 && s->FW * 2 * cand <= 512) { NTq = cand; break; }
-        if (NTq) {
-            auto mma_clk = [](int n) { return n / 2 > 59 ? n / 2 : 59; };
-            const long long std_cost = 3LL * mma_clk(NT) * ((s->OC + 127) / 128) * (s->IC / NT);
-            const long long stk_cost = 1LL * mma_clk(2 * NTq) * ((s->OC + 63) / 64) * (s->IC / NTq);
-            stacked = stk_cost < std_cost;
-            const int force = opt(OPT_DW_STACKED);
-            if (force >= 0) stacked = force != 0;
-            if (stacked) NT = NTq;
+    // Input channels per CTA: the accumulators of a CTA's G taps, NT columns each, must fit the 512 tensor-memory
+    // columns.  A CTA owns a whole filter row (G = FW) unless rows of more than three taps do better split over
+    // several CTAs of three taps (5x5, 7x7: three accumulators of 128 columns instead of five or seven of 64; an MMA of
+    // N columns costs max(N / 2, 59) clocks whatever its height, and a last group with fewer taps idles its spare slots).
+    struct DwForm { int G, NT; bool stacked, diag; long long cost; };
+    auto mma_clk = [](int n) { return n / 2 > 59 ? n / 2 : 59; };
+    auto nt_for = [&](int slots_cols, int top) {
+        for (int cand = top; cand >= 32; cand >>= 1)
+            if (s->IC % cand == 0 && slots_cols * cand <= 512) return cand;
+        return 0;
+    };
+    auto pick = [&](int G) {
+        DwForm f{G, nt_for(G, 256), false, false, 0};
+        if (!f.NT) { f.cost = -1; return f; }
+        const long long slots = (long long)((s->FW + G - 1) / G) * G;   // MMAs per 8 pixels and channel tile
+        f.cost = slots * (mode3x ? 3 : 1) * mma_clk(f.NT) * ((s->OC + 127) / 128) * (s->IC / f.NT);
+        // 3xTF32: three MMAs of (128 x NT), or one MMA on stacked hi/lo planes (64 + 64) x (NTq + NTq): the
+        // stacked form wins where 128 output channels or 64 input channels would be half empty
+        if (mode3x && !per_image) {   // the stacked form leaves two partial planes to add
+            const int NTq = nt_for(2 * G, 128);
+            if (NTq) {
+                const long long stk_cost = slots * mma_clk(2 * NTq) * ((s->OC + 63) / 64) * (s->IC / NTq);
+                bool stacked = stk_cost < f.cost;
+                const int force = opt(OPT_DW_STACKED);
+                if (force >= 0) stacked = force != 0;
+                if (stacked) { f.stacked = true; f.NT = NTq; f.cost = stk_cost; }
+            }
         }
-    }
-    // plain TF32 with at most 64 output channels: two half tiles side by side ("diagonal" form)
-    bool diag = false;
-    if (!mode3x && !per_image && s->OC <= 64 && s->OH >= 2 && opt(OPT_DW_DIAG)) {
-        int NTd = 0;
-        for (int cand = 128; cand >= 32; cand >>= 1)
-            if (s->IC % cand == 0 && s->FW * 2 * cand <= 512) { NTd = cand; break; }
-        if (NTd) {
-            auto mma_clk = [](int n) { return n / 2 > 59 ? n / 2 : 59; };
-            // clocks per 8 pixels: one MMA of NT columns, or half an MMA of 2 * NTd columns
-            const long long std2 = 2LL * mma_clk(NT) * (s->IC / NT), dg2 = 1LL * mma_clk(2 * NTd) * (s->IC / NTd);
-            if (dg2 < std2) { diag = true; stacked = true; NT = NTd; }
+        // plain TF32 with at most 64 output channels: two half tiles side by side ("diagonal" form), half an MMA of
+        // 2 * NTd columns per 8 pixels
+        if (!mode3x && !per_image && s->OC <= 64 && s->OH >= 2 && opt(OPT_DW_DIAG)) {
+            const int NTd = nt_for(2 * G, 128);
+            if (NTd) {
+                const long long dg2 = slots * mma_clk(2 * NTd) * (s->IC / NTd);
+                if (dg2 < 2 * f.cost) { f.diag = true; f.stacked = true; f.NT = NTd; f.cost = (dg2 + 1) / 2; }
+            }
         }
+        return f;
+    };
+    DwForm form = pick(s->FW);
+    if (s->FW > 3 && !strided && !per_image && opt(OPT_DW_TAPGROUPS)) {
+        // groups of three run the kernel whose MMAs are straight-line code; a whole row of four or more taps runs the
+        // looped form, whose issuing thread needs about twice as long per MMA (5x5, 64 -> 128 channels at 112 x 112
+        // in plain TF32: 3.06 ms as one row of five, 1.50 ms as 3 + 2 although that issues six MMAs for five taps)
+        const DwForm g3 = pick(3);
+        if (g3.cost >= 0 && (form.cost < 0 || 10 * g3.cost <= 16 * form.cost || opt(OPT_DW_TAPGROUPS) == 2)) form = g3;
     }
+    if (form.cost < 0) return 1;
+    const int G = form.G, tgroups = (s->FW + G - 1) / G;
+    int NT = form.NT;
+    const bool stacked = form.stacked, diag = form.diag;
     const int oc_tile = stacked ? 64 : 128, dyb = stacked ? 2 : 4, nsub = stacked ? 2 : 1;
     DwHaloParams p{};
     p.status = c->status; p.prof = c->prof;
     p.N = s->N; p.OH = s->OH; p.OW = s->OW;
     p.IC = s->IC; p.OC = s->OC; p.FH = s->FH; p.FW = s->FW; p.ph = s->ph; p.pw = s->pw;
     p.NT = NT; p.ic_tiles = s->IC / NT; p.oc_tiles = (s->OC + oc_tile - 1) / oc_tile;
-    const int groups = s->FH * p.ic_tiles * p.oc_tiles;
+    const int groups = tgroups * s->FH * p.ic_tiles * p.oc_tiles;
     if (groups > 65535) return 1;
+    p.G = G; p.tgroups = tgroups;
     // pixel tile: CW columns of 8-pixel groups, R rows, sized so that three stages fit shared memory
     const int planes = (mode3x || diag) ? 2 : 1;   // diagonal: the second plane holds the second half tile
     int CW = opt(OPT_DW_CW);
     if (!CW) CW = (s->OW <= 8 || (s->OW % 16 != 0 && s->OW % 16 <= 8)) ? 8 : 16;  // fewer idle columns
-    const int PW = CW + s->FW - 1;
+    const int PW = CW + G - 1;
     int R = opt(OPT_DW_R);
     auto stage_bytes = [&](int r) {
         const uint32_t dyblk = ((uint32_t)r * CW * 128 + 1023) & ~1023u, xbk = ((uint32_t)r * PW * 128 + 1023) & ~1023u;
@@ -1701,15 +1718,21 @@ static int launch_dw_halo(DeviceCtx* c, const AlphaConvShape* s_in, const float*
     p.parts = parts;
     p.stages = stages; p.mode3x = diag ? 3 : (stacked ? 2 : mode3x);
     p.idesc = make_idesc_tf32(kBM, stacked ? 2 * NT : NT, true, true);
-    p.tmem_cols = pow2_cols(s->FW * (stacked ? 2 * NT : NT));
+    p.tmem_cols = pow2_cols(G * (stacked ? 2 * NT : NT));
     p.dy_tx = (uint32_t)R * CW * 128; p.dy_blk = (p.dy_tx + 1023) & ~1023u;
     p.x_tx = (uint32_t)R * PW * 128; p.x_blk = (p.x_tx + 1023) & ~1023u;
     p.sh = s->sh; p.sw = s->sw; p.nph = nph;
     {
         const uint32_t xph = (uint32_t)(NT / 32) * p.x_blk, xph_stride = stacked ? 2 * xph : xph;
-        for (int k = 0; k < nph; ++k) p.col_q0[k] = ph_qmin[k];
-        for (int fw = 0; fw < s->FW; ++fw)
-            p.tap_off16[fw] = (tap_k[fw] * xph_stride + (uint32_t)(tap_q[fw] - ph_qmin[tap_k[fw]]) * 128u) >> 4;
+        if (tgroups == 1) {
+            for (int k = 0; k < nph; ++k) p.col_q0[k] = ph_qmin[k];
+            for (int fw = 0; fw < s->FW; ++fw)
+                p.tap_off16[fw] = (tap_k[fw] * xph_stride + (uint32_t)(tap_q[fw] - ph_qmin[tap_k[fw]]) * 128u) >> 4;
+        } else {
+            // stride 1, tap group tg: its tile starts at column fw_base - pw and tap fw_base + j starts j pixels later
+            for (int tg = 0; tg < tgroups; ++tg) p.col_q0[tg] = tg * G - s->pw;
+            for (int j = 0; j < 8; ++j) p.tap_off16[j] = (uint32_t)(j < G ? j : G - 1) * 8u;
+        }
     }
     const size_t sizeW = (size_t)s->OC * s->FH * s->FW * s->IC;
     float* ws = nullptr;
@@ -1768,7 +1791,7 @@ static int launch_dw_halo(DeviceCtx* c, const AlphaConvShape* s_in, const float*
     }
 #define DWH_LAUNCH(FW_, R_, CW_) do { if (!t_dry) conv_dw_halo_kernel<FW_, R_, CW_><<<grid, kDwHaloThreads, smem, stream>>>(tmXs, tmDY, p); } while (0)
 #define DWH_LAUNCH_S(FW_, R_, CW_) do { if (!t_dry) conv_dw_halo_kernel<FW_, R_, CW_, true><<<grid, kDwHaloThreads, smem, stream>>>(tmXs, tmDY, p); } while (0)
-    const bool st = s->FW == 3 && !strided && opt(OPT_DW_STATIC) != 0;
+    const bool st = G == 3 && !strided && opt(OPT_DW_STATIC) != 0;
     const bool st1 = s->FW == 1 && CW == 16 && opt(OPT_DW_STATIC) != 0;   // 1x1 (flat 16-column view; with a stride: one phase, start 0)
     const bool ss3 = s->FW == 3 && strided && opt(OPT_DW_STATIC) != 0, ss4 = s->FW == 4 && strided && opt(OPT_DW_STATIC) != 0;
     if (ss3 && R == 2 && CW == 16) DWH_LAUNCH_S(3, 2, 16);
@@ -1800,7 +1823,7 @@ static int launch_dw_halo(DeviceCtx* c, const AlphaConvShape* s_in, const float*
 #undef DWH_LAUNCH_S
     note_launch("dw_halo");
     snprintf(g_plan, sizeof(g_plan), "dw_halo%s%s NT=%d R=%d CW=%d stages=%d parts=%d groups=%d", diag ? " diagonal" : (stacked ? " stacked" : ""),
-             strided ? (nph == 2 ? " strided 2 phases" : " strided") : "", NT, R, CW, stages, parts, groups);
+             strided ? (nph == 2 ? " strided 2 phases" : " strided") : (tgroups > 1 ? " tap groups of 3" : ""), NT, R, CW, stages, parts, groups);
     rc = check_launch("conv_dw_halo_kernel");
     if (rc || per_image) return rc;
     if (parts * nsub > 1) {

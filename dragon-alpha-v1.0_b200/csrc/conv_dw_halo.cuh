@@ -27,7 +27,7 @@
 // ignored - twice the pixels per MMA where the 128-row operand would be half empty.
 //
 // Bias gradient (p.bias_out): deltaB[oc] = sum over pixels of deltaY[pix][oc] needs exactly the tiles the
-// groups with fh == 0 and ict == 0 already stage.  Their split threads add up the fp32 words of every
+// groups with fh == 0, ict == 0 (and the first tap group) already stage.  Their split threads add up the fp32 words of every
 // deltaY tile (thread t always meets the same four channels of a 32-channel block: its 16-byte chunk of the
 // 128-byte pixel row and, with the 32-byte-atom swizzle, the row index modulo 4 do not change while it
 // strides over 32 rows at a time), and after the loop the 32 threads of each channel quad are added in
@@ -38,6 +38,11 @@
 // (fw - pw) mod sw - whose tiles are dense again: a pixel tile stages one X tile per column phase its taps use
 // (two for 3x3 and 4x4 stride 2, one for 1x1), and a tap starts its descriptor at its phase's tile plus
 // floor((fw - pw) / sw) pixels.  Stride 1 is the case of one phase and a start of fw pixels.
+//
+// Filter rows of more than three taps (5x5, 7x7) at stride 1 may be split over several CTAs of G = 3 taps each, so
+// that three accumulators of 128 columns fit tensor memory where five or seven would have to be 64 wide: tap group tg
+// stages the X tile that starts G * tg columns further right; a last group with fewer taps runs its spare
+// accumulator on the tile's last tap and never stores it.
 //
 // Warps: 0 TMA producer, 1 MMA issuer, 2-9 operand split (3xTF32) during the loop, 2-5 epilogue after.
 #pragma once
@@ -75,7 +80,10 @@ struct DwHaloParams {
     // strided convolutions (see above): one X tile per column phase; all zero / one phase for stride 1
     int sh, sw;               // strides, 1 or 2
     int nph;                  // column phases staged per pixel tile (1 or 2)
-    int col_q0[2];            // first lattice column of phase k's tile, relative to the tile's first output column
+    int G, tgroups;           // taps (accumulators) per CTA and CTAs per filter row: G = FW, tgroups = 1 unless a row of more
+                              // than three taps is split (stride 1 only); the last group may own fewer than G real taps
+    int col_q0[4];            // first lattice column of the X tile, relative to the tile's first output column: by column
+                              // phase k (tgroups == 1) or by tap group (tgroups > 1, one phase)
     uint32_t tap_off16[8];    // start of tap fw's X tile within the X region of a stage, in 16-byte units
 };
 
@@ -196,7 +204,10 @@ __global__ void __launch_bounds__(kDwHaloThreads, 1)
     const uint32_t tmem_base = *tmem_holder;
 
     // accumulator group of this CTA
-    const int grp = blockIdx.y;
+    const int grp0 = blockIdx.y;
+    const int tg = grp0 % p.tgroups;          // tap group within the filter row
+    const int grp = grp0 / p.tgroups;
+    const int fw_base = tg * p.G;
     const int fh = grp % p.FH;
     const int ict = (grp / p.FH) % p.ic_tiles;
     const int oct = grp / (p.FH * p.ic_tiles);
@@ -208,7 +219,7 @@ __global__ void __launch_bounds__(kDwHaloThreads, 1)
 
     const uint32_t smem_a = smem_u32(smem);
     const uint32_t full_a = smem_u32(full), ready_a = smem_u32(ready), empty_a = smem_u32(empty);
-    const int FW = kStatic ? FW_T : p.FW;
+    const int FW = kStatic ? FW_T : p.G;      // accumulators of this CTA
     const int R = kStatic ? R_T : p.R;
     const int CW = kStatic ? CW_T : p.CW;
     const int PW = CW + FW - 1;
@@ -243,7 +254,7 @@ __global__ void __launch_bounds__(kDwHaloThreads, 1)
                     for (int k = 0; k < p.nph; ++k)
                         for (int b = 0; b < xb; ++b)
                             tma_load_4d_a(dst + x_off + k * xph_stride + h * xph + b * p.x_blk, &tmXs.m[phi * p.nph + k], bar,
-                                          ic0 + b * 32, ow0 + p.col_q0[k], oh0 + qrow, n);
+                                          ic0 + b * 32, ow0 + p.col_q0[tg * p.nph + k], oh0 + qrow, n);
                 }
                 rp.advance(S);
             }
@@ -256,7 +267,7 @@ __global__ void __launch_bounds__(kDwHaloThreads, 1)
             RingPos rp;
             const uint32_t dhi = smem_desc_hi(512, kSwizzle128B_Base32B);
             // a CTA that sums bias columns releases a stage only after its split threads have read it
-            const bool do_bias = p.bias_out != nullptr && fh == 0 && ict == 0;
+            const bool do_bias = p.bias_out != nullptr && fh == 0 && ict == 0 && tg == 0;
             const uint32_t wait_a = (p.mode3x == 1 || p.mode3x == 2 || do_bias) ? ready_a : full_a;
             const bool three = p.mode3x == 1;
             const uint32_t stage16 = stage_bytes >> 4, lo_off = plane_bytes >> 4;
@@ -297,7 +308,7 @@ __global__ void __launch_bounds__(kDwHaloThreads, 1)
         const int tid128 = threadIdx.x - 64;   // index among the split threads
         bool ok = true;
         const bool split_on = p.mode3x == 1 || p.mode3x == 2;
-        const bool do_bias = p.bias_out != nullptr && fh == 0 && ict == 0;
+        const bool do_bias = p.bias_out != nullptr && fh == 0 && ict == 0 && tg == 0;
         float4 bsum[4] = {make_float4(0.f, 0.f, 0.f, 0.f), make_float4(0.f, 0.f, 0.f, 0.f), make_float4(0.f, 0.f, 0.f, 0.f),
                           make_float4(0.f, 0.f, 0.f, 0.f)};
         if (split_on || do_bias) {
@@ -378,7 +389,8 @@ __global__ void __launch_bounds__(kDwHaloThreads, 1)
             const bool has_tiles = static_cast<int>(blockIdx.x) < p.total_tiles;
             float* obase = p.out + (static_cast<size_t>(blockIdx.x) * nsub + sub) * p.part_stride;
             for (int fw = 0; fw < FW; ++fw) {
-                const int tap = fh * p.FW + fw;
+                if (fw_base + fw >= p.FW) break;   // spare accumulator of the row's last tap group
+                const int tap = fh * p.FW + fw_base + fw;
                 for (int c = 0; c < p.NT; c += 32) {
                     uint32_t v[32];
                     const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + fw * acc_cols + c;

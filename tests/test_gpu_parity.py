@@ -677,3 +677,50 @@ def test_strided_deltaW_plan_choice(pkg, eng):
         assert (algo.startswith("dw_halo") and "strided" in plan) == halo, (IH, IC, OC, F, algo, plan)
         assert float(dW.abs().max()) == 0.0
     assert lib.device_status() == 0
+
+
+# deltaW filter rows of more than three taps split over CTAs of three taps each (5x5: taps 0-2 and 3-4 with a spare
+# accumulator; 7x7: three groups), in the stacked, three-MMA and plain forms, with and without padding, against the
+# oracle and against whole-row CTAs; the fused bias gradient must come from one tap group only.
+TAPGROUP_CASES = {
+    "tg_5x5_16x16x64_oc128": (3, 16, 16, 64, 128, 5, 5, 1, 1, 2, 2),
+    "tg_5x5_12x20x128": (2, 12, 20, 128, 128, 5, 5, 1, 1, 2, 2),
+    "tg_5x5_nopad_14x14x32_oc64": (2, 14, 14, 32, 64, 5, 5, 1, 1, 0, 0),
+    "tg_7x7_14x14x128_oc64": (2, 14, 14, 128, 64, 7, 7, 1, 1, 3, 3),
+    "tg_3x5_10x12x64": (3, 10, 12, 64, 64, 3, 5, 1, 1, 1, 2),
+}
+CASES.update(TAPGROUP_CASES)
+
+
+@pytest.mark.parametrize("mode", ["3xtf32", "tf32"])
+@pytest.mark.parametrize("name", list(TAPGROUP_CASES))
+def test_deltaW_with_tap_groups(pkg, eng, oracle_mod, name, mode):
+    import torch
+    O, lib = oracle_mod, pkg.submodule("lib")
+    N, IH, IW, IC, OC, FH, FW, sh, sw, ph, pw = CASES[name]
+    OH, OW = out_hw(IH, IW, FH, FW, sh, sw, ph, pw)
+    rng = np.random.default_rng(zlib.crc32(name.encode()))
+    X, dY = gen((N, IH, IW, IC), "relu", rng), gen((N, OH, OW, OC), "n01", rng)
+    dev = torch.device("cuda:0")
+    tX, tdY = torch.from_numpy(X).to(dev), torch.from_numpy(dY).to(dev)
+    lib.set_math_mode(mode)
+    old = lib.set_option("DW_TAPGROUPS", 2)
+    try:
+        dW, dB = eng.dconv3D_deltaW_bias(tX, tdY, FH, FW, sh, sw, ph, pw)
+        plan = lib.last_plan()
+        dW, dB = dW.cpu().numpy(), dB.cpu().numpy()
+        lib.set_option("DW_TAPGROUPS", 0)
+        whole = eng.dconv3D_deltaW(tX, tdY, FH, FW, sh, sw, ph, pw).cpu().numpy()
+        plan0 = lib.last_plan()
+    finally:
+        lib.set_option("DW_TAPGROUPS", old)
+        lib.set_math_mode("3xtf32")
+    assert lib.device_status() == 0
+    assert "tap groups" in plan and "tap groups" not in plan0, (plan, plan0)
+    dW64, SW = O.deconv3D_deltaW_f64(X, dY, FH, FW, sh, sw, ph, pw, threads=8)
+    m = metrics(dW, dW64, SW)
+    record(dict(case=name, mode=mode, tile="dw tap groups", dw=m))
+    assert m["finite"] and m["norm"] <= TOL[mode]["norm"] and m["comp"] <= TOL[mode]["comp"], (plan, m)
+    assert np.abs(dW - whole).max() <= TOL[mode]["norm"] * np.abs(whole).max(), (plan, plan0)
+    ref_b = dY.astype(np.float64).sum(axis=(0, 1, 2))
+    assert np.abs(dB - ref_b).max() <= 1e-5 * np.abs(dY).astype(np.float64).sum(axis=(0, 1, 2)).max(), plan
