@@ -1787,6 +1787,7 @@ static int launch_dw_halo(DeviceCtx* c, const AlphaConvShape* s_in, const float*
         dw_halo_set_attr<3, 4, 8, true>(); dw_halo_set_attr<3, 8, 8, true>(); dw_halo_set_attr<3, 7, 8, true>();
         dw_halo_set_attr<4, 2, 16, true>(); dw_halo_set_attr<4, 4, 16, true>(); dw_halo_set_attr<4, 8, 16, true>();
         dw_halo_set_attr<4, 4, 8, true>(); dw_halo_set_attr<4, 8, 8, true>();
+        dw_halo_set_attr<3, 2, 8, true>(); dw_halo_set_attr<4, 2, 8, true>(); dw_halo_set_attr<4, 7, 8, true>(); dw_halo_set_attr<4, 7, 16, true>();
         attr_done = true;
     }
 #define DWH_LAUNCH(FW_, R_, CW_) do { if (!t_dry) conv_dw_halo_kernel<FW_, R_, CW_><<<grid, kDwHaloThreads, smem, stream>>>(tmXs, tmDY, p); } while (0)
@@ -1806,6 +1807,10 @@ static int launch_dw_halo(DeviceCtx* c, const AlphaConvShape* s_in, const float*
     else if (ss4 && R == 8 && CW == 16) DWH_LAUNCH_S(4, 8, 16);
     else if (ss4 && R == 4 && CW == 8) DWH_LAUNCH_S(4, 4, 8);
     else if (ss4 && R == 8 && CW == 8) DWH_LAUNCH_S(4, 8, 8);
+    else if (ss3 && R == 2 && CW == 8) DWH_LAUNCH_S(3, 2, 8);
+    else if (ss4 && R == 2 && CW == 8) DWH_LAUNCH_S(4, 2, 8);
+    else if (ss4 && R == 7 && CW == 8) DWH_LAUNCH_S(4, 7, 8);
+    else if (ss4 && R == 7 && CW == 16) DWH_LAUNCH_S(4, 7, 16);
     else if (st && R == 1 && CW == 16) DWH_LAUNCH(3, 1, 16);
     else if (st && R == 2 && CW == 16) DWH_LAUNCH(3, 2, 16);
     else if (st && R == 4 && CW == 16) DWH_LAUNCH(3, 4, 16);
