@@ -62,6 +62,55 @@ def test_random_shapes(pkg, oracle_mod, mode):
     assert not bad, bad
 
 
+def _dw_shapes(seed, count):
+    """Shapes that reach the halo-tile deltaW kernel's forms: 32-channel multiples, strides 1 and 2 in either
+    direction, filter rows of 1 to 7 taps, odd images whose stride lattices differ in length."""
+    rng = np.random.default_rng(seed)
+    out = []
+    while len(out) < count:
+        N = int(rng.integers(1, 7))
+        FH, FW = int(rng.choice([1, 2, 3, 3, 4, 5, 7])), int(rng.choice([1, 2, 3, 3, 4, 5, 7]))
+        sh, sw = int(rng.choice([1, 1, 2])), int(rng.choice([1, 1, 2]))
+        ph, pw = int(rng.integers(0, FH)), int(rng.integers(0, FW))
+        OH, OW = int(rng.integers(1, 30)), int(rng.integers(1, 30))
+        IH = (OH - 1) * sh + FH - 2 * ph + int(rng.integers(0, sh))
+        IW = (OW - 1) * sw + FW - 2 * pw + int(rng.integers(0, sw))
+        if IH < sh or IW < sw or IH < 1 or IW < 1:
+            continue
+        IC = 32 * int(rng.choice([1, 1, 2, 4, 8])); OC = 4 * int(rng.integers(1, 72))
+        out.append((N, IH, IW, IC, OC, FH, FW, sh, sw, ph, pw, OH, OW))
+    return out
+
+
+@pytest.mark.parametrize("mode", ["3xtf32", "tf32"])
+def test_random_deltaW_forms(pkg, oracle_mod, mode):
+    import torch
+    eng = pkg.submodule("engine").Engine()
+    lib = pkg.submodule("lib")
+    lib.set_math_mode(mode)
+    O = oracle_mod
+    dev = torch.device("cuda:0")
+    tol = TOL[mode]
+    bad, seen = [], set()
+    try:
+        for i, (N, IH, IW, IC, OC, FH, FW, sh, sw, ph, pw, OH, OW) in enumerate(_dw_shapes(77, 60)):
+            rng = np.random.default_rng(5000 + i)
+            X = gen((N, IH, IW, IC), "relu", rng); dY = gen((N, OH, OW, OC), "n01", rng)
+            dW = eng.dconv3D_deltaW(torch.from_numpy(X).to(dev), torch.from_numpy(dY).to(dev), FH, FW, sh, sw, ph, pw).cpu().numpy()
+            algo, plan = lib.last_algo(), lib.last_plan()
+            assert lib.device_status() == 0, (i, algo, plan)
+            if algo.startswith("dw_halo"):
+                seen.update(k for k in ("strided", "2 phases", "tap groups", "stacked", "diagonal") if k in plan)
+            m = metrics(dW, *O.deconv3D_deltaW_f64(X, dY, FH, FW, sh, sw, ph, pw, threads=8))
+            record(dict(case="random_dw_%d" % i, shape=(N, IH, IW, IC, OC, FH, FW, sh, sw, ph, pw), mode=mode, dw_algo=algo, dw=m))
+            if not (m["finite"] and m["norm"] <= tol["norm"] and m["comp"] <= tol["comp"]):
+                bad.append((i, (N, IH, IW, IC, OC, FH, FW, sh, sw, ph, pw), algo, plan, m["norm"], m["comp"]))
+    finally:
+        lib.set_math_mode("3xtf32")
+    assert not bad, bad
+    assert {"strided", "2 phases", "tap groups"} <= seen, seen     # the sample reaches the forms it is meant for
+
+
 GUARD_FLOATS = 1024      # 4 KB of poison on either side of every output
 
 
